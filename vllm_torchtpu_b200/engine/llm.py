@@ -1,0 +1,99 @@
+"""Offline inference API: ``LLM(...).generate(prompts, sampling_params)``.
+
+Mirrors the ``vllm.LLM`` surface the reference is used through
+(reference: README.md:63-82): token-id or text prompts in, ``RequestOutput``
+objects out, in input order.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence, Union
+
+from ..config import (CacheConfig, EngineConfig, ModelConfig, ParallelConfig, SchedulerConfig,
+                      model_preset)
+from ..outputs import RequestOutput
+from ..sampling_params import SamplingParams
+from .llm_engine import LLMEngine
+
+
+class LLM:
+    def __init__(self, model: Union[str, ModelConfig] = "tiny-llama", *, tokenizer=None,
+                 tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1,
+                 data_parallel_size: int = 1, enable_expert_parallel: bool = False,
+                 prefill_context_parallel_size: int = 1, decode_context_parallel_size: int = 1,
+                 max_model_len: Optional[int] = None, max_num_seqs: int = 256,
+                 max_num_batched_tokens: int = 8192, block_size: int = 16,
+                 gpu_memory_utilization: float = 0.9, num_gpu_blocks_override: Optional[int] = None,
+                 enable_prefix_caching: bool = False, enforce_eager: bool = False,
+                 kv_cache_dtype: str = "auto", quantization: Optional[str] = None,
+                 async_scheduling: bool = False, scheduler_cls: str = "default",
+                 device: str = "cuda", dtype=None, seed: int = 0,
+                 speculative_config: Optional[dict] = None, kv_transfer_config: Optional[dict] = None,
+                 additional_config: Optional[dict] = None, load_format: str = "auto",
+                 world_size: Optional[int] = None, init_dist: bool = True):
+        import os
+        model_path = None
+        if isinstance(model, ModelConfig):
+            mc = model
+        elif os.path.isdir(str(model)):
+            mc = ModelConfig.from_pretrained(model)
+            model_path = model
+        else:
+            mc = model_preset(model)
+        if max_model_len:
+            mc.max_model_len = max_model_len
+        if dtype is not None:
+            from ..config import parse_dtype
+            mc.dtype = parse_dtype(dtype)
+        if quantization:
+            mc.quantization = quantization
+        mc.seed = seed
+        ws = world_size if world_size is not None else int(os.environ.get("WORLD_SIZE", 1))
+        pc = ParallelConfig(tensor_parallel_size, data_parallel_size, pipeline_parallel_size,
+                            enable_expert_parallel, prefill_context_parallel_size,
+                            decode_context_parallel_size, world_size=ws,
+                            rank=int(os.environ.get("RANK", 0)),
+                            local_rank=int(os.environ.get("LOCAL_RANK", 0)),
+                            backend="nccl" if device == "cuda" else "gloo")
+        cfg = EngineConfig(
+            model=mc, parallel=pc,
+            cache=CacheConfig(block_size, gpu_memory_utilization, num_gpu_blocks_override, None,
+                              enable_prefix_caching, kv_cache_dtype),
+            scheduler=SchedulerConfig(max_num_seqs, max_num_batched_tokens, True, scheduler_cls,
+                                      async_scheduling),
+            device=device, enforce_eager=enforce_eager,
+            load_format="dummy" if (load_format == "auto" and model_path is None) else
+            ("safetensors" if load_format == "auto" else load_format),
+            model_path=model_path, speculative=speculative_config, kv_transfer=kv_transfer_config,
+            additional=additional_config or {})
+        self.engine = LLMEngine(cfg, init_dist=init_dist)
+        self.tokenizer = tokenizer
+        if tokenizer is None and model_path:
+            try:
+                from transformers import AutoTokenizer
+                self.tokenizer = AutoTokenizer.from_pretrained(model_path)
+            except Exception:
+                self.tokenizer = None
+        if self.tokenizer is not None and getattr(self.tokenizer, "eos_token_id", None) is not None:
+            self.engine.eos_token_id = self.tokenizer.eos_token_id
+
+    def _encode(self, prompt) -> list:
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("text prompts need a tokenizer")
+            return self.tokenizer.encode(prompt)
+        if isinstance(prompt, dict):
+            return list(prompt["prompt_token_ids"])
+        return list(prompt)
+
+    def generate(self, prompts: Sequence, sampling_params: Union[SamplingParams, Sequence, None] = None,
+                 ) -> list:
+        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        sps = sampling_params if isinstance(sampling_params, (list, tuple)) else \
+            [sampling_params or SamplingParams()] * len(prompts)
+        ids = [self.engine.add_request(self._encode(p), sp) for p, sp in zip(prompts, sps)]
+        self.engine.run_until_done()
+        reqs = self.engine.scheduler.requests
+        detok = self.tokenizer.decode if self.tokenizer is not None else None
+        outs = [RequestOutput.from_request(reqs.pop(i), detok) for i in ids]
+        return outs

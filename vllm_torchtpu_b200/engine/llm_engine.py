@@ -1,0 +1,156 @@
+"""Engine core: scheduler + model runner + the step loop.
+
+One engine drives one model replica (all TP/PP ranks of that replica run this
+same loop in lockstep: the scheduler is deterministic, so every rank derives
+the same SchedulerOutput from the same request stream and no per-step broadcast
+is needed).  With async scheduling the loop keeps one step in flight: step n+1
+is scheduled and launched while step n's tokens travel back to the host.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from typing import Optional
+
+import torch
+
+from .. import envs
+from ..config import EngineConfig
+from ..logger import init_logger
+from ..parallel.state import get_state, init_distributed
+from ..platform import B200Platform
+from ..runner.model_runner import ModelRunner
+from ..sampling_params import SamplingParams
+from .request import Request
+from .scheduler import Scheduler
+
+logger = init_logger(__name__)
+
+
+def make_scheduler(cfg: EngineConfig, num_blocks: int, connector=None, num_spec_tokens: int = 0):
+    name = cfg.scheduler.scheduler_cls
+    kw = dict(connector=connector, num_spec_tokens=num_spec_tokens,
+              sliding_window=cfg.model.sliding_window,
+              abort_on_preemption=bool(cfg.additional.get("abort_on_preemption",
+                                                          envs.B200_ABORT_ON_PREEMPTION)))
+    if name == "default":
+        return Scheduler(cfg.scheduler, cfg.cache, num_blocks, **kw)
+    from ..schedulers import get_scheduler_class
+    return get_scheduler_class(name)(cfg.scheduler, cfg.cache, num_blocks, **kw)
+
+
+class LLMEngine:
+    def __init__(self, cfg: EngineConfig, *, init_dist: bool = True):
+        self.cfg = cfg.finalize() if not cfg.token_buckets else cfg
+        if init_dist:
+            init_distributed(cfg.parallel, backend=None if cfg.device == "cuda" else "gloo")
+        st = get_state()
+        dev = cfg.device
+        if dev == "cuda":
+            dev = f"cuda:{st.local_rank}"
+            torch.cuda.set_device(st.local_rank)
+        self.runner = ModelRunner(self.cfg, dev)
+        self.runner.load_model()
+        num_blocks = self.runner.determine_num_blocks()
+        if st.world_size > 1 and st.world.cpu_group is not None:
+            import torch.distributed as dist
+            t = torch.tensor([num_blocks], dtype=torch.int64)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=st.world.cpu_group)
+            num_blocks = int(t.item())
+        self.runner.init_kv_cache(num_blocks)
+        self.connector = None
+        if cfg.kv_transfer:
+            from ..kv_transfer.factory import create_connector
+            self.connector = create_connector(cfg, self.runner)
+        self.spec = None
+        num_spec = 0
+        if cfg.speculative:
+            from ..spec_decode import create_proposer
+            self.spec = create_proposer(cfg, self.runner)
+            num_spec = self.spec.num_speculative_tokens
+        self.scheduler = make_scheduler(self.cfg, num_blocks,
+                                        self.connector.scheduler if self.connector else None, num_spec)
+        self.runner.capture_model()
+        self._inflight: deque = deque()
+        self._next_id = 0
+        self.eos_token_id: Optional[int] = None
+        self.step_count = 0
+
+    # ---- requests ---------------------------------------------------------------
+    def add_request(self, prompt_token_ids: list, sampling_params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, kv_transfer_params: Optional[dict] = None) -> str:
+        sp = sampling_params or SamplingParams()
+        B200Platform.validate_request(sp)
+        if len(prompt_token_ids) + sp.max_tokens > self.cfg.model.max_model_len:
+            raise ValueError(f"prompt ({len(prompt_token_ids)}) + max_tokens ({sp.max_tokens}) exceeds "
+                             f"max_model_len ({self.cfg.model.max_model_len})")
+        if not prompt_token_ids:
+            raise ValueError("empty prompt")
+        rid = request_id or f"req-{self._next_id}"
+        self._next_id += 1
+        self.scheduler.add_request(Request(rid, list(prompt_token_ids), sp, self.eos_token_id,
+                                           kv_transfer_params=kv_transfer_params))
+        return rid
+
+    def abort_request(self, request_id: str) -> None:
+        self.scheduler.abort_request(request_id)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished() or bool(self._inflight)
+
+    # ---- stepping ---------------------------------------------------------------
+    def _launch(self):
+        out = self.scheduler.schedule()
+        if self.connector is not None:
+            self.connector.worker.start_load_kv(out.kv_connector_metadata)
+        res = self.runner.execute_model(out)
+        if self.connector is not None:
+            self.connector.worker.save_kv(out.kv_connector_metadata)
+        return out, res
+
+    def _retire(self, out, res) -> list:
+        sampled = res.get()
+        self.runner.note_sampled(sampled)
+        spec_next = None
+        if self.spec is not None and sampled:
+            spec_next = self.spec.propose(out, sampled)
+        finished = self.scheduler.update_from_output(out, sampled, spec_next)
+        if self.connector is not None:
+            for rid in self.connector.worker.get_finished_sending():
+                self.scheduler.free_delayed(rid)
+        return finished
+
+    def step(self) -> list:
+        """Advance the engine; returns requests that finished."""
+        self.step_count += 1
+        if not self.scheduler.async_mode:
+            out, res = self._launch()
+            return self._retire(out, res)
+        finished = []
+        if self.scheduler.has_unfinished():
+            self._inflight.append(self._launch())
+        if len(self._inflight) > 1 or (self._inflight and not self.scheduler.has_unfinished()):
+            out, res = self._inflight.popleft()
+            finished = self._retire(out, res)
+        elif self._inflight and not self._inflight[-1][0].scheduled:
+            out, res = self._inflight.popleft()
+            finished = self._retire(out, res)
+        return finished
+
+    def drain(self) -> list:
+        finished = []
+        while self._inflight:
+            out, res = self._inflight.popleft()
+            finished += self._retire(out, res)
+        return finished
+
+    def run_until_done(self) -> list:
+        done = []
+        idle = 0
+        while self.has_unfinished():
+            f = self.step()
+            done += f
+            idle = 0 if f or self._inflight else idle + 1
+            if idle > 10000:
+                raise RuntimeError("engine made no progress for 10000 steps")
+        return done

@@ -1,0 +1,25 @@
+"""Architecture name → model class."""
+from __future__ import annotations
+
+from ..config import ModelConfig
+
+
+def get_model_class(cfg: ModelConfig):
+    a = cfg.architecture
+    if a == "llama":
+        from .llama import LlamaForCausalLM
+        return LlamaForCausalLM
+    if a == "qwen3_moe":
+        from .qwen3_moe import Qwen3MoeForCausalLM
+        return Qwen3MoeForCausalLM
+    if a == "deepseek_v3":
+        from .deepseek_v3 import DeepseekV3ForCausalLM
+        return DeepseekV3ForCausalLM
+    if a == "qwen3_next":
+        from .qwen3_next import Qwen3NextForCausalLM
+        return Qwen3NextForCausalLM
+    raise ValueError(f"no model class for architecture {a!r}")
+
+
+def supported_architectures() -> list[str]:
+    return ["llama", "qwen3_moe", "deepseek_v3", "qwen3_next"]

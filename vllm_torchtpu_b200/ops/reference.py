@@ -1,0 +1,296 @@
+"""Plain-PyTorch statements of every op, computed in fp32.
+
+These are the oracles the CUDA kernels are tested against, and the code path
+the engine runs on CPU tensors (unit tests, the CPU plumbing configuration).
+Nothing here is tuned for speed.
+
+KV cache layout (one tensor per layer): ``[num_blocks, 2, kv_heads, block_size,
+head_dim]``; ``[:, 0]`` is K, ``[:, 1]`` is V.  A token's slot is
+``block_id * block_size + offset``.
+
+Batch description for attention, as in the reference's metadata
+(reference: src/vllm_torchtpu/layers/core/attention_metadata.py:83-141):
+``seq_lens[r]`` is the KV length of request r including this step's tokens,
+``query_start_loc[r]:query_start_loc[r+1]`` are its rows in the packed token
+dimension, ``block_tables[r]`` its pages.  New K/V are written at positions
+``[seq_len - q_len, seq_len)`` before attention
+(reference: src/vllm_torchtpu/kernels/ragged_paged_attention/v3/kernel.py:155-168).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    var = xf.pow(2).mean(-1, keepdim=True)
+    return (xf * torch.rsqrt(var + eps) * weight.float()).to(x.dtype)
+
+
+def fused_add_rms_norm(x, residual, weight, eps):
+    """residual' = round_to_dtype(x + residual); y = rms_norm(residual').
+    The sum is rounded to the activation dtype before normalising
+    (reference: src/vllm_torchtpu/layers/adapter/ir_ops.py:50-88)."""
+    r = (x.float() + residual.float()).to(x.dtype)
+    return rms_norm(r, weight, eps), r
+
+
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    d = x.shape[-1] // 2
+    g, u = x[..., :d].float(), x[..., d:].float()
+    return (F.silu(g) * u).to(x.dtype)
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[T,N] = x[T,K] @ w[N,K]^T (+ bias), fp32 accumulate."""
+    y = x.float() @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype)
+
+
+def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None,
+                  rotary_dim: Optional[int] = None) -> torch.Tensor:
+    rd = rotary_dim or head_dim
+    inv = 1.0 / (theta ** (torch.arange(0, rd, 2, dtype=torch.float64) / rd))
+    if scaling and scaling.get("rope_type", scaling.get("type")) == "llama3":
+        factor = scaling["factor"]
+        lo, hi = scaling["low_freq_factor"], scaling["high_freq_factor"]
+        old = scaling["original_max_position_embeddings"]
+        wavelen = 2 * math.pi / inv
+        smooth = (old / wavelen - lo) / (hi - lo)
+        scaled = torch.where(wavelen > old / lo, inv / factor,
+                             torch.where(wavelen < old / hi, inv,
+                                         (1 - smooth) * inv / factor + smooth * inv))
+        inv = scaled
+    elif scaling and scaling.get("rope_type", scaling.get("type")) == "linear":
+        inv = inv / scaling["factor"]
+    return inv.float()
+
+
+def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+               interleaved: bool = False) -> torch.Tensor:
+    """x: [T, H, D]; rotates the first 2*len(inv_freq) dims in fp32
+    (reference: src/vllm_torchtpu/layers/adapter/rotary_embedding.py:14-44)."""
+    rd = inv_freq.numel() * 2
+    ang = positions.float()[:, None] * inv_freq.float()[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    xr = x[..., :rd].float()
+    if interleaved:
+        x1, x2 = xr[..., 0::2], xr[..., 1::2]
+        o = torch.stack((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).flatten(-2)
+    else:
+        x1, x2 = xr[..., : rd // 2], xr[..., rd // 2:]
+        o = torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1)
+    out = x.clone()
+    out[..., :rd] = o.to(x.dtype)
+    return out
+
+
+def head_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """Per-head RMSNorm over the last dim of [T, H, D] (Qwen3 q/k norm)."""
+    return rms_norm(x, weight, eps)
+
+
+def write_kv_cache(kv_cache: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                   slot_mapping: torch.Tensor) -> None:
+    """k, v: [T, Hkv, D]; slot < 0 skips the token (padding)."""
+    bs = kv_cache.shape[3]
+    valid = slot_mapping >= 0
+    slots = slot_mapping[valid].long()
+    blk, off = slots // bs, slots % bs
+    kv_cache[blk, 0, :, off] = k[valid].to(kv_cache.dtype)
+    kv_cache[blk, 1, :, off] = v[valid].to(kv_cache.dtype)
+
+
+def rope_and_cache(qkv, positions, inv_freq, kv_cache, slot_mapping, num_q_heads, num_kv_heads,
+                   head_dim, interleaved=False, q_norm_w=None, k_norm_w=None, eps=1e-6,
+                   k_scale: float = 1.0, v_scale: float = 1.0):
+    """Split packed qkv, optional per-head q/k RMSNorm, RoPE on q and k, write k/v
+    to the paged cache.  Returns q [T, Hq, D]."""
+    T = qkv.shape[0]
+    q, k, v = qkv.split([num_q_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * head_dim], -1)
+    q = q.reshape(T, num_q_heads, head_dim)
+    k = k.reshape(T, num_kv_heads, head_dim)
+    v = v.reshape(T, num_kv_heads, head_dim)
+    if q_norm_w is not None:
+        q = head_rms_norm(q, q_norm_w, eps)
+        k = head_rms_norm(k, k_norm_w, eps)
+    q = apply_rope(q, positions, inv_freq, interleaved)
+    k = apply_rope(k, positions, inv_freq, interleaved)
+    if kv_cache is not None:
+        if kv_cache.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+            write_kv_cache(kv_cache, k.float() / k_scale, v.float() / v_scale, slot_mapping)
+        else:
+            write_kv_cache(kv_cache, k, v, slot_mapping)
+    return q.contiguous()
+
+
+def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, *,
+                    num_reqs: Optional[int] = None, sliding_window: Optional[int] = None,
+                    softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
+                    k_scale: float = 1.0, v_scale: float = 1.0, return_lse: bool = False):
+    """Causal attention of packed ragged queries over the paged cache.
+
+    q: [T, Hq, D]; returns [T, Hq, D] (rows beyond query_start_loc[num_reqs] are zero).
+    Query j of request r sits at absolute position seq_len - q_len + j.
+    """
+    T, Hq, D = q.shape
+    Hkv, bs = kv_cache.shape[2], kv_cache.shape[3]
+    G = Hq // Hkv
+    out = torch.zeros_like(q)
+    lse = torch.full((T, Hq), float("-inf"), dtype=torch.float32, device=q.device)
+    R = int(num_reqs if num_reqs is not None else seq_lens.shape[0])
+    qsl = query_start_loc.tolist()
+    sl = seq_lens.tolist()
+    for r in range(R):
+        qs, qe = qsl[r], qsl[r + 1]
+        q_len, kv_len = qe - qs, sl[r]
+        if q_len <= 0 or kv_len <= 0:
+            continue
+        nblk = -(-kv_len // bs)
+        blocks = block_tables[r, :nblk].long()
+        k = kv_cache[blocks, 0].float() * k_scale        # [nblk, Hkv, bs, D]
+        v = kv_cache[blocks, 1].float() * v_scale
+        k = k.permute(1, 0, 2, 3).reshape(Hkv, nblk * bs, D)[:, :kv_len]
+        v = v.permute(1, 0, 2, 3).reshape(Hkv, nblk * bs, D)[:, :kv_len]
+        qr = q[qs:qe].float().permute(1, 0, 2).reshape(Hkv, G, q_len, D)
+        s = torch.einsum("hgqd,hkd->hgqk", qr, k) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        qpos = torch.arange(kv_len - q_len, kv_len, device=q.device)[:, None]
+        kpos = torch.arange(kv_len, device=q.device)[None, :]
+        mask = kpos <= qpos
+        if sliding_window:
+            mask &= kpos > qpos - sliding_window
+        s = s.masked_fill(~mask, float("-inf"))
+        if sinks is not None:
+            sink = sinks.float().reshape(Hkv, G, 1, 1).expand(Hkv, G, q_len, 1)
+            s_all = torch.cat([s, sink], dim=-1)
+            l = torch.logsumexp(s_all, dim=-1)
+        else:
+            l = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - l[..., None])
+        o = torch.einsum("hgqk,hkd->hgqd", p, v)
+        out[qs:qe] = o.reshape(Hq, q_len, D).permute(1, 0, 2).to(q.dtype)
+        lse[qs:qe] = l.reshape(Hq, q_len).t()
+    if return_lse:
+        return out, lse
+    return out
+
+
+def merge_attn_states(outs: list, lses: list):
+    """Combine partial attention results by their log-sum-exp
+    (reference: src/vllm_torchtpu/distributed/dcp_comm.py:23-46)."""
+    lse = torch.stack(lses).float()                      # [P, T, H]
+    m = lse.max(0).values
+    m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+    w = torch.exp(lse - m)
+    w = torch.where(torch.isfinite(lse), w, torch.zeros_like(w))
+    denom = w.sum(0)
+    o = sum(torch.where(w[i][..., None] > 0, outs[i].float() * w[i][..., None],
+                        torch.zeros_like(outs[i], dtype=torch.float32)) for i in range(len(outs)))
+    o = o / denom.clamp_min(1e-38)[..., None]
+    return o.to(outs[0].dtype), m + torch.log(denom.clamp_min(1e-38))
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    return table[ids.long()]
+
+
+# ---- sampling ------------------------------------------------------------------
+def apply_top_k_top_p(logits: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor) -> torch.Tensor:
+    """Mask logits outside each row's top-k / nucleus to -inf.  top_k<=0 and top_p>=1 are off."""
+    logits = logits.float().clone()
+    V = logits.shape[-1]
+    sorted_logits, idx = logits.sort(dim=-1, descending=True)
+    k = torch.where(top_k <= 0, torch.full_like(top_k, V), top_k).clamp(max=V).long()
+    ranks = torch.arange(V, device=logits.device)[None, :]
+    keep = ranks < k[:, None]
+    probs = torch.softmax(sorted_logits.masked_fill(~keep, float("-inf")), dim=-1)
+    cum = probs.cumsum(-1)
+    keep &= (cum - probs) < top_p[:, None].float()
+    keep[:, 0] = True
+    masked = sorted_logits.masked_fill(~keep, float("-inf"))
+    out = torch.empty_like(logits)
+    out.scatter_(1, idx, masked)
+    return out
+
+
+def gumbel_from_uniform(u: torch.Tensor) -> torch.Tensor:
+    return -torch.log(-torch.log(u.clamp(1e-20, 1.0 - 1e-7)))
+
+
+def sample(logits, temperature, top_k, top_p, uniform: Optional[torch.Tensor] = None):
+    """Greedy where temperature <= 1e-5, else Gumbel-max over the masked, tempered
+    logits (reference: src/vllm_torchtpu/runner/tpu_runner.py:9240-9274)."""
+    logits = logits.float()
+    greedy = logits.argmax(-1)
+    if uniform is None or bool((temperature <= 1e-5).all()):
+        return greedy
+    t = temperature.clamp_min(1e-5)[:, None].float()
+    masked = apply_top_k_top_p(logits / t, top_k, top_p)
+    noisy = masked + gumbel_from_uniform(uniform.float())
+    rnd = noisy.argmax(-1)
+    return torch.where(temperature <= 1e-5, greedy, rnd)
+
+
+def gather_logprobs(logits, token_ids, k: int):
+    """fp32 log-softmax; returns (logprob of token_ids, top-k logprobs, top-k ids, rank)."""
+    lp = torch.log_softmax(logits.float(), dim=-1)
+    tok = lp.gather(1, token_ids.long()[:, None]).squeeze(1)
+    topv, topi = lp.topk(k, dim=-1) if k > 0 else (lp[:, :0], token_ids[:, None][:, :0])
+    rank = (lp > tok[:, None]).sum(-1) + 1
+    return tok, topv, topi, rank
+
+
+# ---- MoE ------------------------------------------------------------------------
+def moe_route(router_logits, top_k: int, scoring: str = "softmax", renormalize: bool = True,
+              routed_scaling: float = 1.0, score_bias: Optional[torch.Tensor] = None,
+              n_group: int = 1, topk_group: int = 1):
+    """scoring → (bias / grouped top-k) → top-k → renormalise → scale
+    (reference: src/vllm_torchtpu/layers/adapter/moe_routing.py:161-343)."""
+    x = router_logits.float()
+    scores = torch.softmax(x, dim=-1) if scoring == "softmax" else torch.sigmoid(x)
+    choice = scores if score_bias is None else scores + score_bias.float()[None, :]
+    T, E = scores.shape
+    if n_group > 1:
+        g = choice.view(T, n_group, E // n_group)
+        if score_bias is not None:
+            gs = g.topk(2, dim=-1).values.sum(-1)
+        else:
+            gs = g.max(-1).values
+        gidx = gs.topk(topk_group, dim=-1).indices
+        gmask = torch.zeros(T, n_group, dtype=torch.bool, device=x.device).scatter_(1, gidx, True)
+        choice = choice.masked_fill(~gmask[:, :, None].expand(T, n_group, E // n_group).reshape(T, E),
+                                    float("-inf"))
+    ids = choice.topk(top_k, dim=-1).indices
+    w = scores.gather(1, ids)
+    if renormalize:
+        w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
+    return ids.to(torch.int32), (w * routed_scaling).float()
+
+
+def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0):
+    """Σ_k w_k · FFN_e(x) over the experts this rank owns.  w13: [E_local, 2I, H] (gate rows first),
+    w2: [E_local, H, I]."""
+    T, H = x.shape
+    E_local = w13.shape[0]
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    xf = x.float()
+    for e in range(E_local):
+        sel = (topk_ids == e + expert_offset)
+        rows = sel.any(-1).nonzero().squeeze(-1)
+        if rows.numel() == 0:
+            continue
+        wt = (topk_w * sel).sum(-1)[rows]
+        h = xf[rows] @ w13[e].float().t()
+        I = h.shape[-1] // 2
+        a = (F.silu(h[:, :I]) * h[:, I:]).to(x.dtype).float()
+        y = (a @ w2[e].float().t()).to(x.dtype).float()
+        out[rows] += y * wt[:, None]
+    return out.to(x.dtype)

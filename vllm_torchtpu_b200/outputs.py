@@ -1,0 +1,38 @@
+"""Result objects returned by ``LLM.generate`` and the server."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+
+@dataclass
+class CompletionOutput:
+    index: int
+    token_ids: list
+    text: Optional[str] = None
+    finish_reason: Optional[str] = None
+    logprobs: Optional[list] = None
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt_token_ids: list
+    outputs: list = field(default_factory=list)
+    finished: bool = True
+    num_cached_tokens: int = 0
+    ttft_s: Optional[float] = None
+    latency_s: Optional[float] = None
+    kv_transfer_params: Optional[dict] = None
+    error: Optional[str] = None
+
+    @staticmethod
+    def from_request(req, detokenize=None) -> "RequestOutput":
+        text = detokenize(req.output_token_ids) if detokenize else None
+        ttft = (req.first_token_time - req.arrival_time) if req.first_token_time else None
+        lat = (req.finish_time - req.arrival_time) if req.finish_time else None
+        return RequestOutput(
+            req.request_id, req.prompt_token_ids,
+            [CompletionOutput(0, list(req.output_token_ids), text, req.status.value,
+                              req.logprobs or None)],
+            req.status.finished, req.num_cached_tokens, ttft, lat, req.kv_transfer_params, req.error)

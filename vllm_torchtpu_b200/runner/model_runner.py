@@ -1,0 +1,401 @@
+"""Model runner: turns a SchedulerOutput into one device step.
+
+Responsibilities (the reference's runner has the same ones,
+reference: src/vllm_torchtpu/runner/tpu_runner.py:4287-4776, 5440-5998):
+persistent batch bookkeeping, input preparation with the batch ordered
+``[decode][prefill/mixed]``, padding of every device-side shape to a bucket,
+the forward pass, logits for the sampling rows, sampling, and an asynchronous
+copy of the sampled tokens back to the host.  Where the reference pre-compiles
+one XLA program per token bucket (``capture_model``, tpu_runner.py:7496), this
+runner captures one CUDA graph per decode request bucket and runs prefill/mixed
+steps eagerly (they are long enough to hide launch latency).
+
+Sampled tokens also stay on the device in ``last_tokens[batch_slot]`` so the next
+step can be launched before the host has read them (async scheduling): input
+rows whose token the host does not know yet carry ``token_src = batch_slot`` and
+the embedding kernel reads the id from ``last_tokens``.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import envs, ops
+from ..config import EngineConfig
+from ..logger import init_logger
+from ..models.registry import get_model_class
+from ..parallel.state import get_state
+from ..platform import B200Platform, pad_to_bucket
+from .attn_metadata import AttentionMetadata
+from .input_batch import InputBatch, StepBuffers
+
+logger = init_logger(__name__)
+
+
+@dataclass
+class StepResult:
+    """Handle on a launched step; ``get()`` waits for the token copy."""
+    req_ids: list
+    samples: list                   # bool per request
+    tokens_host: Optional[torch.Tensor]
+    event: Optional[object]
+    num_reqs: int
+    d2h_bytes: int = 0
+    extra: dict = field(default_factory=dict)
+
+    def get(self) -> dict:
+        if self.event is not None:
+            self.event.synchronize()
+        if self.tokens_host is None:
+            return {}
+        toks = self.tokens_host[: self.num_reqs].tolist()
+        return {rid: [t] for rid, t, s in zip(self.req_ids, toks, self.samples) if s}
+
+
+class ModelRunner:
+    def __init__(self, cfg: EngineConfig, device: Optional[str] = None):
+        self.cfg = cfg
+        self.device = torch.device(device or cfg.device)
+        self.is_cuda = self.device.type == "cuda"
+        self.mcfg = cfg.model
+        self.block_size = cfg.cache.block_size
+        self.max_reqs = cfg.scheduler.max_num_seqs
+        self.max_tokens = cfg.scheduler.max_num_batched_tokens
+        self.batch = InputBatch(self.max_reqs, self.mcfg.max_model_len, self.block_size)
+        self.model = None
+        self.kv_caches: list = []
+        self.num_blocks = 0
+        self.graphs: dict = {}
+        self.graph_pool = None
+        self.launch_counter = 0          # kernels launched by this runner (bench accounting)
+        self.kernels_per_graph: dict = {}
+        self.stats = {"steps": 0, "graph_steps": 0, "eager_steps": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+        self._gen = torch.Generator(device=self.device)
+        self._gen.manual_seed(self.mcfg.seed + 1234)
+        self._stage_timers = None
+        if envs.B200_STAGE_TIMING and self.is_cuda:
+            from ..tracing.stage_timing import RunnerStageTiming
+            self._stage_timers = RunnerStageTiming()
+
+    # ------------------------------------------------------------------ setup
+    def load_model(self) -> None:
+        t0 = time.time()
+        cls = get_model_class(self.mcfg)
+        st = get_state()
+        layer_range = None
+        if st.pp.size > 1:
+            from ..parallel.pp import partition_layers
+            layer_range = partition_layers(self.mcfg.num_layers, st.pp.size)[st.pp.rank_in_group]
+        self.model = cls(self.mcfg, self.device, layer_range=layer_range)
+        if self.cfg.load_format == "dummy" or not self.cfg.model_path:
+            self.model.init_dummy()
+        else:
+            from ..models.loader import load_safetensors
+            load_safetensors(self.model, self.cfg.model_path)
+        logger.info("model %s loaded: %.2f GB weights on this rank in %.1fs", self.mcfg.name,
+                    self.model.weight_bytes() / 1e9, time.time() - t0)
+
+    def _alloc_step_buffers(self) -> None:
+        mb = self.batch.max_blocks
+        self.bufs_prefill = StepBuffers(self.max_tokens, self.max_reqs, mb, self.device)
+        self.bufs_decode = StepBuffers(self.max_reqs, self.max_reqs, mb, self.device)
+        self.last_tokens = torch.zeros(self.max_reqs, dtype=torch.int32, device=self.device)
+        self.tokens_host = [torch.zeros(self.max_reqs, dtype=torch.int32, pin_memory=self.is_cuda)
+                            for _ in range(4)]
+        self._tok_ring = 0
+
+    def determine_num_blocks(self) -> int:
+        c = self.cfg.cache
+        if c.num_gpu_blocks_override:
+            return c.num_gpu_blocks_override
+        kv_dtype = B200Platform.kv_cache_torch_dtype(c.kv_cache_dtype, self.mcfg.dtype)
+        per_block = self.model.kv_bytes_per_block(self.block_size, kv_dtype)
+        if c.kv_cache_memory_bytes:
+            return max(2, c.kv_cache_memory_bytes // per_block)
+        if not self.is_cuda:
+            need = self.max_reqs * self.batch.max_blocks
+            return min(need, 4096) + 1
+        # peak activation of a full-size step, measured with an eager dummy run
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        self.init_kv_cache(2)
+        self._dummy_run(self.max_tokens, min(self.max_reqs, max(1, self.max_tokens // 128)))
+        torch.cuda.synchronize()
+        peak = torch.cuda.max_memory_allocated() - base
+        self.kv_caches = []
+        torch.cuda.empty_cache()
+        budget = B200Platform.compute_hbm_budget(self.cfg, self.model.weight_bytes(), peak)
+        free, total = torch.cuda.mem_get_info()
+        kv_bytes = min(budget.kv_cache, int(free * 0.95) - peak)
+        n = max(2, kv_bytes // per_block)
+        logger.info("HBM: total %.1f GB, weights %.1f GB, activation peak %.2f GB -> KV %.1f GB = %d blocks",
+                    total / 1e9, self.model.weight_bytes() / 1e9, peak / 1e9, kv_bytes / 1e9, n)
+        return int(n)
+
+    def init_kv_cache(self, num_blocks: int) -> None:
+        self.num_blocks = num_blocks
+        kv_dtype = B200Platform.kv_cache_torch_dtype(self.cfg.cache.kv_cache_dtype, self.mcfg.dtype)
+        self.kv_caches = self.model.allocate_kv_caches(num_blocks, self.block_size, kv_dtype, self.device) \
+            if hasattr(self.model, "allocate_kv_caches") else [
+                torch.zeros(self.model.kv_cache_shape(num_blocks, self.block_size), dtype=kv_dtype,
+                            device=self.device) for _ in self.model.layers]
+        if not hasattr(self, "bufs_prefill"):
+            self._alloc_step_buffers()
+
+    # ------------------------------------------------------------ input prep
+    def _update_batch(self, out) -> None:
+        for rid in out.finished_ids:
+            self.batch.remove(rid)
+        for rid in out.preempted_ids:
+            self.batch.remove(rid)
+        for s in out.scheduled:
+            if s.is_new or s.request.request_id not in self.batch.slot_of:
+                self.batch.add(s.request, s.request.block_ids)
+            else:
+                self.batch.append_blocks(self.batch.slot_of[s.request.request_id], s.new_block_ids)
+
+    def _prepare_inputs(self, out):
+        scheds = out.scheduled
+        n = len(scheds)
+        b = self.batch
+        is_dec = [s.num_new_tokens == 1 and s.start > 0 for s in scheds]
+        order = [i for i in range(n) if is_dec[i]] + [i for i in range(n) if not is_dec[i]]
+        scheds = [scheds[i] for i in order]
+        num_decode = sum(is_dec)
+        slots = np.fromiter((b.slot_of[s.request.request_id] for s in scheds), dtype=np.int64, count=n)
+        num_new = np.fromiter((s.num_new_tokens for s in scheds), dtype=np.int64, count=n)
+        starts = np.fromiter((s.start for s in scheds), dtype=np.int64, count=n)
+        T = int(num_new.sum())
+        decode_only = num_decode == n
+        bufs = self.bufs_decode if decode_only else self.bufs_prefill
+        if decode_only and not self.cfg.enforce_eager and self.is_cuda:
+            R_pad = pad_to_bucket(n, self.cfg.request_buckets)
+            T_pad = R_pad
+        else:
+            R_pad, T_pad = n, T
+        qsl = np.zeros(n + 1, dtype=np.int64)
+        np.cumsum(num_new, out=qsl[1:])
+        if decode_only:
+            req_idx = np.arange(n)
+            pos = starts
+        else:
+            req_idx = np.repeat(np.arange(n), num_new)
+            pos = starts[req_idx] + (np.arange(T) - qsl[req_idx])
+        tslots = slots[req_idx]
+        known = pos < b.num_known[tslots]
+        ids = b.token_ids[tslots, np.minimum(pos, b.token_ids.shape[1] - 1)]
+        blk = b.block_table[tslots, pos // self.block_size]
+        slot_map = blk.astype(np.int64) * self.block_size + pos % self.block_size
+
+        hv = bufs.host_view
+        v = hv("input_ids", T_pad); v[:T] = ids; v[T:] = 0
+        v = hv("positions", T_pad); v[:T] = pos; v[T:] = 0
+        v = hv("slot_mapping", T_pad); v[:T] = slot_map; v[T:] = -1
+        v = hv("token_src", T_pad); v[:T] = np.where(known, -1, tslots); v[T:] = -1
+        v = hv("query_start_loc", R_pad + 1); v[:n + 1] = qsl; v[n + 1:] = T
+        v = hv("seq_lens", R_pad); v[:n] = starts + num_new; v[n:] = 0
+        v = hv("logits_indices", R_pad); v[:n] = qsl[1:] - 1; v[n:] = 0
+        v = hv("top_k", R_pad); v[:n] = b.top_k[slots]; v[n:] = 0
+        v = hv("batch_slots", R_pad); v[:n] = slots; v[n:] = -1
+        v = hv("temperature", R_pad, np.float32); v[:n] = b.temperature[slots]; v[n:] = 0
+        v = hv("top_p", R_pad, np.float32); v[:n] = b.top_p[slots]; v[n:] = 1
+        bufs.np_bt[:n] = b.block_table[slots]
+        if R_pad > n:
+            bufs.np_bt[n:R_pad] = 0
+        all_greedy = bool((b.temperature[slots] <= 1e-5).all())
+        seq_lens_np = starts + num_new
+        return dict(scheds=scheds, n=n, T=T, R_pad=R_pad, T_pad=T_pad, num_decode=num_decode,
+                    decode_only=decode_only, bufs=bufs, all_greedy=all_greedy,
+                    max_q=int(num_new.max()) if n else 0, max_seq=int(seq_lens_np.max()) if n else 0,
+                    seq_lens_np=seq_lens_np, qsl_np=qsl)
+
+    def _make_meta(self, p) -> AttentionMetadata:
+        bufs, R, T = p["bufs"], p["R_pad"], p["T_pad"]
+        dv = bufs.dev_view
+        return AttentionMetadata(
+            positions=dv("positions", T), slot_mapping=dv("slot_mapping", T),
+            block_tables=bufs.dev_bt[:R], seq_lens=dv("seq_lens", R),
+            query_start_loc=dv("query_start_loc", R + 1), num_reqs=p["n"], num_tokens=p["T"],
+            num_decode_reqs=p["num_decode"], max_query_len=p["max_q"], max_seq_len=p["max_seq"],
+            logits_indices=dv("logits_indices", R),
+            request_distribution=(p["num_decode"], p["num_decode"], p["n"]),
+            padded_num_reqs=R, padded_num_tokens=T,
+            seq_lens_cpu=torch.from_numpy(p["seq_lens_np"]), query_start_loc_cpu=torch.from_numpy(p["qsl_np"]))
+
+    # --------------------------------------------------------------- forward
+    def _forward_and_sample(self, bufs, meta, T, R, all_greedy: bool):
+        """Everything that runs on the device for one step (also the captured region)."""
+        dv = bufs.dev_view
+        ids = dv("input_ids", T)
+        hidden0 = self._embed(ids, dv("token_src", T))
+        hidden, residual = self.model.forward(ids, meta, self.kv_caches, hidden=hidden0)
+        rows = self._select_rows(hidden, residual, meta.logits_indices)
+        h = self.model.finalize(*rows)
+        logits = self.model.compute_logits(h)
+        uniform = None
+        if not all_greedy:
+            uniform = torch.rand(logits.shape, generator=self._gen, device=self.device, dtype=torch.float32)
+        tokens = ops.sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
+                            dv("top_p", R, torch.float32), uniform, all_greedy).to(torch.int32)
+        self._store_last_tokens(tokens, dv("batch_slots", R))
+        return tokens, logits
+
+    def _embed(self, ids, token_src):
+        if self.model.embed is None:
+            return None
+        if self.is_cuda:
+            return ops.cuda_ops().embedding(ids, self.model.embed, token_src, self.last_tokens)
+        use_last = token_src >= 0
+        real = torch.where(use_last, self.last_tokens[token_src.clamp_min(0).long()], ids)
+        return ops.embedding(real, self.model.embed)
+
+    def _select_rows(self, hidden, residual, idx):
+        if self.is_cuda:
+            return ops.cuda_ops().gather_rows(hidden, residual, idx)
+        i = idx.long()
+        return hidden[i], (residual[i] if residual is not None else None)
+
+    def _store_last_tokens(self, tokens, batch_slots):
+        if self.is_cuda:
+            ops.cuda_ops().scatter_tokens(tokens, batch_slots, self.last_tokens)
+        else:
+            valid = batch_slots >= 0
+            self.last_tokens[batch_slots[valid].long()] = tokens[valid]
+
+    def execute_model(self, out) -> StepResult:
+        if not out.scheduled:
+            self._update_batch(out)
+            return StepResult([], [], None, None, 0)
+        self._update_batch(out)
+        p = self._prepare_inputs(out)
+        bufs, n, R, T = p["bufs"], p["n"], p["R_pad"], p["T_pad"]
+        self.stats["h2d_bytes"] += bufs.upload(R)
+        meta = self._make_meta(p)
+        self.stats["steps"] += 1
+        use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
+                     and envs.B200_CUDA_GRAPHS)
+        if use_graph:
+            key = (R, p["all_greedy"])
+            g = self.graphs.get(key)
+            if g is None:
+                if envs.B200_CHECK_RECAPTURE and self.graphs:
+                    raise RuntimeError(f"decode bucket {key} was not captured at warm-up")
+                g = self._capture(key, bufs, meta, T, R, p["all_greedy"])
+            g["graph"].replay()
+            tokens = g["tokens"]
+            self.stats["graph_steps"] += 1
+            self.launch_counter += g["launches"]
+        else:
+            from ..ops import launch_count
+            c0 = launch_count()
+            tokens, _ = self._forward_and_sample(bufs, meta, T, R, p["all_greedy"])
+            self.launch_counter += launch_count() - c0
+            self.stats["eager_steps"] += 1
+        host = self.tokens_host[self._tok_ring]
+        self._tok_ring = (self._tok_ring + 1) % len(self.tokens_host)
+        ev = None
+        if self.is_cuda:
+            host[:R].copy_(tokens[:R], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        else:
+            host[:R] = tokens[:R]
+        self.stats["d2h_bytes"] += R * 4
+        return StepResult([s.request.request_id for s in p["scheds"]], [s.samples for s in p["scheds"]],
+                          host, ev, n, R * 4)
+
+    def note_sampled(self, result: dict) -> None:
+        """Host learnt the tokens of a finished step: extend the persistent rows."""
+        for rid, toks in result.items():
+            slot = self.batch.slot_of.get(rid)
+            if slot is not None:
+                for t in toks:
+                    self.batch.append_token(slot, t)
+
+    # ------------------------------------------------------------ CUDA graphs
+    def _capture(self, key, bufs, meta, T, R, all_greedy):
+        from ..ops import launch_count
+        logger.debug("capturing decode graph for bucket %s", key)
+        # warm-up on a side stream so lazy initialisation does not end up in the graph
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._forward_and_sample(bufs, meta, T, R, all_greedy)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        c0 = launch_count()
+        with torch.cuda.graph(g, pool=self.graph_pool):
+            tokens, _ = self._forward_and_sample(bufs, meta, T, R, all_greedy)
+        if self.graph_pool is None:
+            self.graph_pool = g.pool()
+        entry = {"graph": g, "tokens": tokens, "launches": launch_count() - c0}
+        self.graphs[key] = entry
+        return entry
+
+    def capture_model(self) -> None:
+        """Capture every decode request bucket (greedy variant) ahead of serving."""
+        if not (self.is_cuda and envs.B200_CUDA_GRAPHS) or self.cfg.enforce_eager:
+            return
+        t0 = time.time()
+        for R in reversed(self.cfg.request_buckets):
+            self._dummy_decode(R, capture=True)
+        torch.cuda.synchronize()
+        logger.info("captured %d decode graphs in %.1fs", len(self.graphs), time.time() - t0)
+
+    def _dummy_decode(self, R: int, capture: bool = False) -> None:
+        bufs = self.bufs_decode
+        hv = bufs.host_view
+        hv("input_ids", R)[:] = 0
+        hv("positions", R)[:] = 0
+        hv("slot_mapping", R)[:] = -1
+        hv("token_src", R)[:] = -1
+        hv("query_start_loc", R + 1)[:] = np.arange(R + 1)
+        hv("seq_lens", R)[:] = 1
+        hv("logits_indices", R)[:] = np.arange(R)
+        hv("top_k", R)[:] = 0
+        hv("batch_slots", R)[:] = -1
+        hv("temperature", R, np.float32)[:] = 0
+        hv("top_p", R, np.float32)[:] = 1
+        bufs.np_bt[:R] = 0
+        bufs.upload(R)
+        p = dict(bufs=bufs, n=R, T=R, R_pad=R, T_pad=R, num_decode=R, max_q=1, max_seq=1,
+                 seq_lens_np=np.ones(R, dtype=np.int64), qsl_np=np.arange(R + 1, dtype=np.int64))
+        meta = self._make_meta(p)
+        if capture:
+            self._capture((R, True), bufs, meta, R, R, True)
+        else:
+            self._forward_and_sample(bufs, meta, R, R, True)
+
+    def _dummy_run(self, T: int, R: int) -> None:
+        """Eager full-size prefill-shaped step for memory profiling / warm-up."""
+        if not hasattr(self, "bufs_prefill"):
+            self._alloc_step_buffers()
+        bufs = self.bufs_prefill
+        R = max(1, min(R, self.max_reqs))
+        per = max(1, T // R)
+        per = min(per, self.mcfg.max_model_len)
+        T = per * R
+        hv = bufs.host_view
+        hv("input_ids", T)[:] = 0
+        hv("positions", T)[:] = np.tile(np.arange(per), R)
+        hv("slot_mapping", T)[:] = -1
+        hv("token_src", T)[:] = -1
+        qsl = np.arange(R + 1, dtype=np.int64) * per
+        hv("query_start_loc", R + 1)[:] = qsl
+        hv("seq_lens", R)[:] = per
+        hv("logits_indices", R)[:] = qsl[1:] - 1
+        hv("top_k", R)[:] = 0
+        hv("batch_slots", R)[:] = -1
+        hv("temperature", R, np.float32)[:] = 0
+        hv("top_p", R, np.float32)[:] = 1
+        bufs.np_bt[:R] = 0
+        bufs.upload(R)
+        p = dict(bufs=bufs, n=R, T=T, R_pad=R, T_pad=T, num_decode=0, max_q=per, max_seq=per,
+                 seq_lens_np=np.full(R, per, dtype=np.int64), qsl_np=qsl)
+        self._forward_and_sample(bufs, self._make_meta(p), T, R, True)
