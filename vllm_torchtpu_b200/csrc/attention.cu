@@ -1,0 +1,651 @@
+// Ragged paged attention over the block-table KV cache.
+//
+// Batch description (one launch covers a contiguous range of requests):
+//   seq_lens[r]            KV length including this step's tokens
+//   query_start_loc[r..r+1] rows of request r in the packed q tensor
+//   block_tables[r, :]      pages; cache layout [blocks, 2, Hkv, block_size, D]
+// Query j of request r sits at absolute position seq_len - q_len + j and attends
+// keys <= that position (minus an optional sliding window).  The step's K/V were
+// already written to the pages by the RoPE/cache kernel, so prefix context,
+// chunked prefill and decode are one code path.  Semantics follow the reference's
+// ragged paged attention (reference: src/vllm_torchtpu/kernels/ragged_paged_attention/v3/kernel.py:74-214).
+//
+// Two kernels, both flash-attention style with bf16 mma.sync m16n8k16 tiles, fp32
+// online softmax in the log2 domain:
+//  * decode / spec-verify: q_len * G <= 16 rows (G = q heads per kv head) form ONE
+//    16-row MMA tile, so a kv head's group shares every K/V byte read.  Split-KV
+//    over (split, warp); each warp streams 16-token pages through its own
+//    3-stage cp.async ring.  Partials are merged in shared memory, then across
+//    splits by the CTA that arrives last on the (request, kv head) counter.
+//  * prefill / mixed: 64 query rows per CTA (4 warps x 16), KV streamed in
+//    64-token chunks through a 2-stage cp.async ring shared by the CTA.
+// The decode path is bound by HBM bandwidth, which mma.sync tiles already
+// saturate; the tcgen05 path is reserved for the GEMMs.
+#include "common.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, const uint32_t* b) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16(uint32_t smem, const void* gptr) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct AttnParams {
+  const __nv_bfloat16* q;        // [T, Hq, D]
+  const __nv_bfloat16* kv;       // [blocks, 2, Hkv, bs, D]
+  __nv_bfloat16* out;            // [T, Hq, D]
+  float* lse;                    // optional [T, Hq] natural-log LSE
+  const int* block_tables;       // [R, max_blocks]
+  const int* seq_lens;           // [R]
+  const int* qsl;                // [R+1]
+  float* part_o;                 // decode scratch [R, Hkv, S, 16, D] fp32
+  float* part_ml;                // decode scratch [R, Hkv, S, 16, 2]
+  int* counters;                 // decode scratch [R * Hkv]
+  const float* sinks;            // optional [Hq]
+  int max_blocks, block_size, Hq, Hkv, req_begin, req_end, num_splits, window;
+  long long num_blocks;
+  float scale_log2, softcap;
+};
+
+// Copy `rows` tokens x D of one K or V page region into swizzled shared memory.
+// 16-byte chunk c of row r lands at chunk (c ^ (r & 7)).
+template <int D, int NTHREADS>
+__device__ __forceinline__ void load_rows_async(uint32_t smem_base, const __nv_bfloat16* g, int rows,
+                                                int tid) {
+  constexpr int CPR = D / 8;                     // chunks per row
+  for (int idx = tid; idx < rows * CPR; idx += NTHREADS) {
+    const int r = idx / CPR, c = idx % CPR;
+    cp_async16(smem_base + (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4)), g + (size_t)r * D + c * 8);
+  }
+}
+
+// S[16 x 16 tokens] += Q(frags) * K^T for one 16-token group at shared address kbase
+template <int D>
+__device__ __forceinline__ void qk_16(float s[2][4], const uint32_t (*qf)[4], uint32_t kbase, int lane) {
+  const int mi = lane >> 3, rr = lane & 7;
+  const int tok = (mi >> 1) * 8 + rr;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const int c = 2 * ks + (mi & 1);
+    uint32_t b[4];
+    ldsm_x4(b, kbase + (uint32_t)(tok * D * 2 + ((c ^ (tok & 7)) << 4)));
+    mma_bf16_16816(s[0], qf[ks], &b[0]);
+    mma_bf16_16816(s[1], qf[ks], &b[2]);
+  }
+}
+// O[16 x D] += P[16 x 16 tokens] * V for one 16-token group at shared address vbase
+template <int D>
+__device__ __forceinline__ void pv_16(float (*o)[4], const uint32_t* pa, uint32_t vbase, int lane) {
+  const int mi = lane >> 3, rr = lane & 7;
+  const int tok = (mi & 1) * 8 + rr;
+#pragma unroll
+  for (int np = 0; np < D / 16; ++np) {
+    const int c = 2 * np + (mi >> 1);
+    uint32_t b[4];
+    ldsm_x4_t(b, vbase + (uint32_t)(tok * D * 2 + ((c ^ (tok & 7)) << 4)));
+    mma_bf16_16816(o[2 * np], pa, &b[0]);
+    mma_bf16_16816(o[2 * np + 1], pa, &b[2]);
+  }
+}
+
+// ------------------------------------------------------------------------ decode
+template <int D>
+__global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p) {
+  constexpr int STAGES = 3;
+  constexpr int PAGE_BYTES = 16 * D * 2;          // 16 tokens of K (or V)
+  constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
+  constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ float s_ml[4][16][2];
+  __shared__ int s_last;
+
+  const int h = blockIdx.x, r = p.req_begin + blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.Hq / p.Hkv;
+  const int qs = p.qsl[r], q_len = p.qsl[r + 1] - qs, seq_len = p.seq_lens[r];
+  if (q_len <= 0 || seq_len <= 0) return;       // padded request (uniform for the CTA)
+  const int ctx = seq_len - q_len;
+  const int rows_valid = min(q_len * G, 16);
+
+  // Q fragments straight from global memory: tile row = j * G + g
+  uint32_t qf[D / 16][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    const int cb = 2 * (lane & 3);
+    const __nv_bfloat16* q0 = nullptr;
+    const __nv_bfloat16* q1 = nullptr;
+    if (r0 < rows_valid) q0 = p.q + ((size_t)(qs + r0 / G) * p.Hq + h * G + r0 % G) * D;
+    if (r1 < rows_valid) q1 = p.q + ((size_t)(qs + r1 / G) * p.Hq + h * G + r1 % G) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + cb) : 0u;
+      qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + cb) : 0u;
+      qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + cb) : 0u;
+      qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + cb) : 0u;
+    }
+  }
+
+  // this (split, warp) unit's range of 16-token chunks
+  int first_tok = 0;
+  if (p.window > 0) first_tok = max(0, ctx - p.window + 1);
+  const int c_lo = first_tok >> 4;
+  const int C = ((seq_len + 15) >> 4) - c_lo;
+  const int units = p.num_splits * 4;
+  const int per = (C + units - 1) / units;
+  const int u = split * 4 + warp;
+  const int cb0 = c_lo + min(C, u * per);
+  const int cb1 = c_lo + min(C, (u + 1) * per);
+
+  const uint32_t wbase = smem_u32(smem) + warp * WARP_BYTES;
+  const int* bt = p.block_tables + (size_t)r * p.max_blocks;
+  const size_t head_stride = (size_t)p.block_size * D;          // one (k|v, head) slab of a page
+  auto issue = [&](int chunk, int stage) {
+    const int tok = chunk << 4;
+    const int page = tok / p.block_size, off = tok - page * p.block_size;
+    long long blk = bt[page];
+    if (blk < 0 || blk >= p.num_blocks) blk = 0;
+    const __nv_bfloat16* kp = p.kv + (((size_t)blk * 2 + 0) * p.Hkv + h) * head_stride + (size_t)off * D;
+    const __nv_bfloat16* vp = p.kv + (((size_t)blk * 2 + 1) * p.Hkv + h) * head_stride + (size_t)off * D;
+    const uint32_t sb = wbase + stage * STAGE_BYTES;
+    load_rows_async<D, 32>(sb, kp, 16, lane);
+    load_rows_async<D, 32>(sb + PAGE_BYTES, vp, 16, lane);
+  };
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int row0 = lane >> 2, row1 = row0 + 8;
+  const int lim0 = ctx + row0 / G, lim1 = ctx + row1 / G;       // last visible key per row
+
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (cb0 + s < cb1) issue(cb0 + s, s);
+    cp_async_commit();
+  }
+  for (int c = cb0; c < cb1; ++c) {
+    const int stage = (c - cb0) % STAGES;
+    cp_async_wait<STAGES - 2>();
+    __syncwarp();
+    if (c + STAGES - 1 < cb1) issue(c + STAGES - 1, (c - cb0 + STAGES - 1) % STAGES);
+    cp_async_commit();
+
+    const uint32_t sb = wbase + stage * STAGE_BYTES;
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    qk_16<D>(s, qf, sb, lane);
+    const int tk = (c << 4) + 2 * (lane & 3);
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int tok = tk + nb * 8 + (e & 1);
+        const int lim = (e < 2) ? lim0 : lim1;
+        float v = s[nb][e] * p.scale_log2;
+        if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
+        const bool ok = tok <= lim && (p.window <= 0 || tok > lim - p.window);
+        v = ok ? v : -INFINITY;
+        s[nb][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+    const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+    const float a0 = ex2(m[0] - base0), a1 = ex2(m[1] - base1);
+    m[0] = mn0; m[1] = mn1;
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      s[nb][0] = ex2(s[nb][0] - base0); s[nb][1] = ex2(s[nb][1] - base0);
+      s[nb][2] = ex2(s[nb][2] - base1); s[nb][3] = ex2(s[nb][3] - base1);
+      ps0 += s[nb][0] + s[nb][1];
+      ps1 += s[nb][2] + s[nb][3];
+    }
+    l[0] = l[0] * a0 + ps0;
+    l[1] = l[1] * a1 + ps1;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1;
+    }
+    uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
+                      pack_bf16(s[1][2], s[1][3])};
+    pv_16<D>(o, pa, sb + PAGE_BYTES, lane);
+  }
+  cp_async_wait<0>();
+  // row sums over the 4 lanes that share a row
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+  __syncwarp();
+
+  // ---- merge the 4 warps in shared memory (each warp reuses its own ring)
+  float* wo = reinterpret_cast<float*>(smem + warp * WARP_BYTES);        // [16][D] fp32 (<= 8 KB)
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) {
+    const int col = i * 8 + 2 * (lane & 3);
+    *reinterpret_cast<float2*>(wo + row0 * D + col) = make_float2(o[i][0], o[i][1]);
+    *reinterpret_cast<float2*>(wo + row1 * D + col) = make_float2(o[i][2], o[i][3]);
+  }
+  if ((lane & 3) == 0) {
+    s_ml[warp][row0][0] = m[0]; s_ml[warp][row0][1] = l[0];
+    s_ml[warp][row1][0] = m[1]; s_ml[warp][row1][1] = l[1];
+  }
+  __syncthreads();
+  const int row = threadIdx.x >> 3;               // 16 rows x 8 threads
+  const int seg = threadIdx.x & 7;
+  constexpr int SEG = D / 8;                      // dims per thread
+  float mm = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) mm = fmaxf(mm, s_ml[w][row][0]);
+  float L = 0.f, acc[SEG];
+#pragma unroll
+  for (int d = 0; d < SEG; ++d) acc[d] = 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const float mw = s_ml[w][row][0];
+    const float sc = (mw == -INFINITY) ? 0.f : ex2(mw - mm);
+    L += s_ml[w][row][1] * sc;
+    const float* src = reinterpret_cast<const float*>(smem + w * WARP_BYTES) + row * D + seg * SEG;
+#pragma unroll
+    for (int d = 0; d < SEG; ++d) acc[d] += src[d] * sc;
+  }
+  const bool row_ok = row < rows_valid;
+  const int tok_row = qs + row / G, head = h * G + row % G;
+
+  auto finish = [&](float mfin, float Lfin, const float* a) {
+    if (!row_ok) return;
+    if (p.sinks != nullptr) {
+      // attention sink: one extra logit per head that only joins the normaliser
+      const float sk = p.sinks[head] * 1.4426950408889634f;
+      const float mnew = fmaxf(mfin, sk);
+      const float sc = (mfin == -INFINITY) ? 0.f : ex2(mfin - mnew);
+      Lfin = Lfin * sc + ex2(sk - mnew);
+      mfin = mnew;
+      const float inv = 1.f / Lfin;
+      __nv_bfloat16* dst = p.out + ((size_t)tok_row * p.Hq + head) * D + seg * SEG;
+#pragma unroll
+      for (int d = 0; d < SEG; ++d) dst[d] = __float2bfloat16(a[d] * sc * inv);
+    } else {
+      const float inv = Lfin > 0.f ? 1.f / Lfin : 0.f;
+      __nv_bfloat16* dst = p.out + ((size_t)tok_row * p.Hq + head) * D + seg * SEG;
+#pragma unroll
+      for (int d = 0; d < SEG; ++d) dst[d] = __float2bfloat16(a[d] * inv);
+    }
+    if (p.lse != nullptr && seg == 0)
+      p.lse[(size_t)tok_row * p.Hq + head] =
+          Lfin > 0.f ? (mfin + log2f(Lfin)) * 0.6931471805599453f : -INFINITY;
+  };
+
+  if (p.num_splits == 1) {
+    finish(mm, L, acc);
+    return;
+  }
+  // ---- cross-split merge by the last CTA of this (request, kv head)
+  const size_t unit = ((size_t)blockIdx.y * p.Hkv + h) * p.num_splits;
+  float* po = p.part_o + ((unit + split) * 16 + row) * D + seg * SEG;
+#pragma unroll
+  for (int d = 0; d < SEG; ++d) po[d] = acc[d];
+  if (seg == 0) {
+    p.part_ml[((unit + split) * 16 + row) * 2 + 0] = mm;
+    p.part_ml[((unit + split) * 16 + row) * 2 + 1] = L;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(&p.counters[blockIdx.y * p.Hkv + h], 1);
+    s_last = (old == p.num_splits - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float mfin = -INFINITY;
+  for (int s2 = 0; s2 < p.num_splits; ++s2)
+    mfin = fmaxf(mfin, __ldcg(&p.part_ml[((unit + s2) * 16 + row) * 2]));
+  float Lfin = 0.f;
+#pragma unroll
+  for (int d = 0; d < SEG; ++d) acc[d] = 0.f;
+  for (int s2 = 0; s2 < p.num_splits; ++s2) {
+    const float ms = __ldcg(&p.part_ml[((unit + s2) * 16 + row) * 2]);
+    const float sc = (ms == -INFINITY) ? 0.f : ex2(ms - mfin);
+    Lfin += __ldcg(&p.part_ml[((unit + s2) * 16 + row) * 2 + 1]) * sc;
+    const float* src = p.part_o + ((unit + s2) * 16 + row) * D + seg * SEG;
+#pragma unroll
+    for (int d = 0; d < SEG; ++d) acc[d] += __ldcg(src + d) * sc;
+  }
+  finish(mfin, Lfin, acc);
+  if (threadIdx.x == 0) p.counters[blockIdx.y * p.Hkv + h] = 0;
+}
+
+// ----------------------------------------------------------------------- prefill
+template <int D>
+__global__ void __launch_bounds__(128, 2) attn_prefill_kernel(const AttnParams p) {
+  constexpr int BQ = 64, BKV = 64, STAGES = 2;
+  constexpr int TILE_BYTES = BKV * D * 2;          // K (or V) chunk
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int hq = blockIdx.x;
+  const int G = p.Hq / p.Hkv;
+  const int h = hq / G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // find (request, q block) of this tile: linear scan over the ragged batch
+  int r = -1, q0 = 0;
+  {
+    int tile = blockIdx.y;
+    for (int i = p.req_begin; i < p.req_end; ++i) {
+      const int ql = p.qsl[i + 1] - p.qsl[i];
+      const int nt = (ql + BQ - 1) / BQ;
+      if (tile < nt) { r = i; q0 = tile * BQ; break; }
+      tile -= nt;
+    }
+  }
+  if (r < 0) return;
+  const int qs = p.qsl[r], q_len = p.qsl[r + 1] - qs, seq_len = p.seq_lens[r];
+  if (seq_len <= 0) return;
+  const int ctx = seq_len - q_len;
+  const int row0 = q0 + warp * 16 + (lane >> 2), row1 = row0 + 8;   // rows inside the request
+
+  uint32_t qf[D / 16][4];
+  {
+    const int cb = 2 * (lane & 3);
+    const __nv_bfloat16* qa = row0 < q_len ? p.q + ((size_t)(qs + row0) * p.Hq + hq) * D : nullptr;
+    const __nv_bfloat16* qb = row1 < q_len ? p.q + ((size_t)(qs + row1) * p.Hq + hq) * D : nullptr;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qf[ks][0] = qa ? *reinterpret_cast<const uint32_t*>(qa + ks * 16 + cb) : 0u;
+      qf[ks][1] = qb ? *reinterpret_cast<const uint32_t*>(qb + ks * 16 + cb) : 0u;
+      qf[ks][2] = qa ? *reinterpret_cast<const uint32_t*>(qa + ks * 16 + 8 + cb) : 0u;
+      qf[ks][3] = qb ? *reinterpret_cast<const uint32_t*>(qb + ks * 16 + 8 + cb) : 0u;
+    }
+  }
+  const int kv_end = min(seq_len, ctx + q0 + BQ);               // causal bound of the tile
+  int kv_begin = 0;
+  if (p.window > 0) kv_begin = max(0, ctx + q0 - p.window + 1) / BKV * BKV;
+  const int nchunks = (kv_end - kv_begin + BKV - 1) / BKV;
+
+  const int* bt = p.block_tables + (size_t)r * p.max_blocks;
+  const size_t head_stride = (size_t)p.block_size * D;
+  const uint32_t sbase = smem_u32(smem);
+  auto issue = [&](int chunk, int stage) {
+    const int tok0 = kv_begin + chunk * BKV;
+    const uint32_t sb = sbase + stage * STAGE_BYTES;
+    // 64 tokens = 4 groups of 16; a group never straddles a page (block_size % 16 == 0)
+#pragma unroll
+    for (int g = 0; g < BKV / 16; ++g) {
+      const int tok = tok0 + g * 16;
+      if (tok >= kv_end) break;
+      const int page = tok / p.block_size, off = tok - page * p.block_size;
+      long long blk = bt[page];
+      if (blk < 0 || blk >= p.num_blocks) blk = 0;
+      const __nv_bfloat16* kp = p.kv + (((size_t)blk * 2 + 0) * p.Hkv + h) * head_stride + (size_t)off * D;
+      const __nv_bfloat16* vp = p.kv + (((size_t)blk * 2 + 1) * p.Hkv + h) * head_stride + (size_t)off * D;
+      load_rows_async<D, 128>(sb + g * 16 * D * 2, kp, 16, threadIdx.x);
+      load_rows_async<D, 128>(sb + TILE_BYTES + g * 16 * D * 2, vp, 16, threadIdx.x);
+    }
+  };
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int lim0 = ctx + row0, lim1 = ctx + row1;
+
+  if (nchunks > 0) issue(0, 0);
+  cp_async_commit();
+  for (int c = 0; c < nchunks; ++c) {
+    const int stage = c & 1;
+    if (c + 1 < nchunks) issue(c + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t sb = sbase + stage * STAGE_BYTES;
+    const int tok0 = kv_begin + c * BKV;
+    // skip groups entirely above this warp's diagonal
+    const int warp_max_key = ctx + q0 + warp * 16 + 15;
+    float s[BKV / 8][4];
+#pragma unroll
+    for (int i = 0; i < BKV / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int g = 0; g < BKV / 16; ++g) {
+      if (tok0 + g * 16 <= warp_max_key && tok0 + g * 16 < kv_end)
+        qk_16<D>(reinterpret_cast<float(*)[4]>(&s[2 * g][0]), qf, sb + g * 16 * D * 2, lane);
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < BKV / 8; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int tok = tok0 + nb * 8 + 2 * (lane & 3) + (e & 1);
+        const int lim = (e < 2) ? lim0 : lim1;
+        float v = s[nb][e] * p.scale_log2;
+        if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
+        const bool ok = tok <= lim && tok < kv_end && (p.window <= 0 || tok > lim - p.window);
+        v = ok ? v : -INFINITY;
+        s[nb][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+    const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+    const float a0 = ex2(m[0] - base0), a1 = ex2(m[1] - base1);
+    m[0] = mn0; m[1] = mn1;
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < BKV / 8; ++nb) {
+      s[nb][0] = ex2(s[nb][0] - base0); s[nb][1] = ex2(s[nb][1] - base0);
+      s[nb][2] = ex2(s[nb][2] - base1); s[nb][3] = ex2(s[nb][3] - base1);
+      ps0 += s[nb][0] + s[nb][1];
+      ps1 += s[nb][2] + s[nb][3];
+    }
+    l[0] = l[0] * a0 + ps0;
+    l[1] = l[1] * a1 + ps1;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1;
+    }
+#pragma unroll
+    for (int g = 0; g < BKV / 16; ++g) {
+      if (tok0 + g * 16 <= warp_max_key && tok0 + g * 16 < kv_end) {
+        uint32_t pa[4] = {pack_bf16(s[2 * g][0], s[2 * g][1]), pack_bf16(s[2 * g][2], s[2 * g][3]),
+                          pack_bf16(s[2 * g + 1][0], s[2 * g + 1][1]),
+                          pack_bf16(s[2 * g + 1][2], s[2 * g + 1][3])};
+        pv_16<D>(o, pa, sb + TILE_BYTES + g * 16 * D * 2, lane);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+
+  float sc0 = 1.f, sc1 = 1.f;
+  if (p.sinks != nullptr) {
+    const float sk = p.sinks[hq] * 1.4426950408889634f;
+    const float n0 = fmaxf(m[0], sk), n1 = fmaxf(m[1], sk);
+    sc0 = (m[0] == -INFINITY) ? 0.f : ex2(m[0] - n0);
+    sc1 = (m[1] == -INFINITY) ? 0.f : ex2(m[1] - n1);
+    l[0] = l[0] * sc0 + ex2(sk - n0);
+    l[1] = l[1] * sc1 + ex2(sk - n1);
+    m[0] = n0; m[1] = n1;
+  }
+  const float inv0 = l[0] > 0.f ? sc0 / l[0] : 0.f, inv1 = l[1] > 0.f ? sc1 / l[1] : 0.f;
+  if (row0 < q_len) {
+    __nv_bfloat16* dst = p.out + ((size_t)(qs + row0) * p.Hq + hq) * D + 2 * (lane & 3);
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+      *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+    if (p.lse != nullptr && (lane & 3) == 0)
+      p.lse[(size_t)(qs + row0) * p.Hq + hq] =
+          l[0] > 0.f ? (m[0] + log2f(l[0])) * 0.6931471805599453f : -INFINITY;
+  }
+  if (row1 < q_len) {
+    __nv_bfloat16* dst = p.out + ((size_t)(qs + row1) * p.Hq + hq) * D + 2 * (lane & 3);
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+      *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+    if (p.lse != nullptr && (lane & 3) == 0)
+      p.lse[(size_t)(qs + row1) * p.Hq + hq] =
+          l[1] > 0.f ? (m[1] + log2f(l[1])) * 0.6931471805599453f : -INFINITY;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+static void fill_params(AttnParams& p, const void* q, const void* kv, void* out, float* lse,
+                        const int* block_tables, const int* seq_lens, const int* qsl, int max_blocks,
+                        int block_size, long long num_blocks, int Hq, int Hkv, int D, float scale, int window,
+                        float softcap, const float* sinks) {
+  p.q = (const __nv_bfloat16*)q;
+  p.kv = (const __nv_bfloat16*)kv;
+  p.out = (__nv_bfloat16*)out;
+  p.lse = lse;
+  p.block_tables = block_tables;
+  p.seq_lens = seq_lens;
+  p.qsl = qsl;
+  p.max_blocks = max_blocks;
+  p.block_size = block_size;
+  p.num_blocks = num_blocks;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.softcap = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  p.sinks = sinks;
+  (void)D;
+}
+
+// Scratch sizes of the decode kernel for (num_reqs, Hkv, splits, D).
+extern "C" size_t b200_attn_decode_scratch_bytes(int num_reqs, int Hkv, int splits, int D) {
+  if (splits <= 1) return 0;
+  return (size_t)num_reqs * Hkv * splits * 16 * (D + 2) * sizeof(float);
+}
+
+// Requests [req_begin, req_end) must have q_len * (Hq/Hkv) <= 16.  scratch holds part_o then
+// part_ml; counters: [num_reqs * Hkv] ints, zero before first use (re-armed by the kernel).
+extern "C" int b200_attn_decode(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                                const int* seq_lens, const int* qsl, int req_begin, int req_end,
+                                int max_blocks, int block_size, long long num_blocks, int Hq, int Hkv, int D,
+                                float scale, int window, float softcap, const float* sinks, int num_splits,
+                                void* scratch, int* counters, cudaStream_t stream) {
+  const int R = req_end - req_begin;
+  if (R <= 0) return 0;
+  if (block_size % 16 || (Hq % Hkv) || Hq / Hkv > 16) {
+    b200_set_last_error("attn_decode: block_size % 16 == 0 and q heads per kv head <= 16 required", __FILE__,
+                        __LINE__);
+    return -1;
+  }
+  AttnParams p;
+  fill_params(p, q, kv, out, lse, block_tables, seq_lens, qsl, max_blocks, block_size, num_blocks, Hq, Hkv, D,
+              scale, window, softcap, sinks);
+  p.req_begin = req_begin;
+  p.req_end = req_end;
+  if (num_splits < 1) num_splits = 1;
+  if (num_splits > 1 && (scratch == nullptr || counters == nullptr)) num_splits = 1;
+  p.num_splits = num_splits;
+  p.part_o = (float*)scratch;
+  p.part_ml = p.part_o + (size_t)R * Hkv * num_splits * 16 * D;
+  p.counters = counters;
+  dim3 grid(Hkv, R, num_splits);
+  if (D == 128) {
+    const int smem = 4 * 3 * 2 * 16 * 128 * 2;
+    static bool set = false;
+    if (!set) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(attn_decode_kernel<128>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      set = true;
+    }
+    attn_decode_kernel<128><<<grid, 128, smem, stream>>>(p);
+  } else if (D == 64) {
+    const int smem = 4 * 3 * 2 * 16 * 64 * 2 < 4 * 16 * 64 * 4 ? 4 * 16 * 64 * 4 : 4 * 3 * 2 * 16 * 64 * 2;
+    static bool set = false;
+    if (!set) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(attn_decode_kernel<64>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      set = true;
+    }
+    attn_decode_kernel<64><<<grid, 128, smem, stream>>>(p);
+  } else {
+    b200_set_last_error("attn_decode: head_dim must be 64 or 128", __FILE__, __LINE__);
+    return -1;
+  }
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// num_tiles = sum over requests of ceil(q_len / 64) (computed by the caller from host metadata).
+extern "C" int b200_attn_prefill(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                                 const int* seq_lens, const int* qsl, int req_begin, int req_end,
+                                 int num_tiles, int max_blocks, int block_size, long long num_blocks, int Hq,
+                                 int Hkv, int D, float scale, int window, float softcap, const float* sinks,
+                                 cudaStream_t stream) {
+  if (req_end <= req_begin || num_tiles <= 0) return 0;
+  if (block_size % 16 || (Hq % Hkv)) {
+    b200_set_last_error("attn_prefill: block_size % 16 == 0 required", __FILE__, __LINE__);
+    return -1;
+  }
+  AttnParams p;
+  fill_params(p, q, kv, out, lse, block_tables, seq_lens, qsl, max_blocks, block_size, num_blocks, Hq, Hkv, D,
+              scale, window, softcap, sinks);
+  p.req_begin = req_begin;
+  p.req_end = req_end;
+  p.num_splits = 1;
+  p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr;
+  dim3 grid(Hq, num_tiles);
+  if (D == 128) {
+    const int smem = 2 * 2 * 64 * 128 * 2;
+    static bool set = false;
+    if (!set) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(attn_prefill_kernel<128>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      set = true;
+    }
+    attn_prefill_kernel<128><<<grid, 128, smem, stream>>>(p);
+  } else if (D == 64) {
+    const int smem = 2 * 2 * 64 * 64 * 2;
+    attn_prefill_kernel<64><<<grid, 128, smem, stream>>>(p);
+  } else {
+    b200_set_last_error("attn_prefill: head_dim must be 64 or 128", __FILE__, __LINE__);
+    return -1;
+  }
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,443 @@
+// bf16 GEMM  Y[T,N] = X[T,K] * W[N,K]^T (+bias)  on tcgen05 tensor cores.
+//
+// Orientation: the weight is the 128-row UMMA "A" operand and the activations are
+// the "B" operand, so the accumulator in TMEM is D[n (128 lanes), t (BN columns)].
+// A decode step with 16..256 tokens therefore still fills the 128-row MMA with
+// weight rows and only narrows N, and one kernel covers decode (BN = 32/64/128)
+// and prefill (BN = 256).  Both operands are K-major in global memory
+// (nn.Linear weight layout, row-major activations) and are staged by TMA with the
+// 128-byte swizzle that the UMMA shared-memory descriptor expects.
+//
+// CTA = 6 warps, persistent over (tile, split) work items:
+//   warp 0   TMA producer (one elected lane), ring of STAGES {A 128x64, B BNx64}
+//   warp 1   TMEM allocation + tcgen05.mma issue (one lane), commits free stages
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (double buffered in TMEM so the
+//            epilogue of tile i overlaps the main loop of tile i+1), bias, bf16 store
+// Split-K (decode shapes with few output tiles): each split writes an fp32 partial
+// to scratch; the CTA that arrives last on the tile's counter sums the partials in
+// split order (deterministic), writes bf16 and re-arms the counter.
+//
+// No reference counterpart as CUDA: the reference's dense matmuls are XLA dots and
+// Pallas quantized_matmul kernels (reference: src/vllm_torchtpu/kernels/quantized_matmul/).
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "gemm_tcgen05.h"
+
+namespace b200 {
+
+constexpr int BM = 128;          // weight rows per tile (UMMA M)
+constexpr int BK = 64;           // bf16 elements per 128-byte swizzled row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_N = 16;      // raster group: 16 weight tiles share activations in L2
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+};
+
+struct GemmParams {
+  __nv_bfloat16* Y;
+  const __nv_bfloat16* bias;
+  float* ws;
+  int* counters;
+  int* status;
+  int T, N, K, ldy;
+  int n_tiles, t_tiles, splits, kb_total, kb_per_split;
+  int w_evict_first;
+};
+
+__device__ __forceinline__ void decode_work(int w, const GemmParams& p, int& n_tile, int& t_tile,
+                                            int& split, int& tile) {
+  tile = w / p.splits;
+  split = w - tile * p.splits;
+  const int per_group = GROUP_N * p.t_tiles;
+  const int g = tile / per_group;
+  const int first_n = g * GROUP_N;
+  const int gsize = min(GROUP_N, p.n_tiles - first_n);
+  const int r = tile - g * per_group;
+  n_tile = first_n + r % gsize;
+  t_tile = r / gsize;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], 4);
+    mbar_init(&tempty[1], 4);
+    *abort_flag = 0;
+    *last_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_work = p.n_tiles * p.t_tiles * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t armed = 0;       // bit s: stage s has a load whose completion nobody has consumed yet
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        int n_tile, t_tile, split, tile;
+        decode_work(w, p, n_tile, t_tile, split, tile);
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* a = smem + s * Cfg::STAGE_BYTES;
+          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          if (p.w_evict_first)
+            tma_load_2d_hint(a, &tmW, &full[s], kb * BK, n_tile * BM, L2_EVICT_FIRST);
+          else
+            tma_load_2d(a, &tmW, &full[s], kb * BK, n_tile * BM);
+          tma_load_2d(a + Cfg::A_BYTES, &tmX, &full[s], kb * BK, t_tile * BN);
+          armed |= 1u << s;
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (*abort_flag) {
+        // give this CTA's bulk copies in flight a bounded time to land before the CTA exits
+        for (int it = 0; it < 20000; ++it) __nanosleep(100);
+      }
+      (void)armed;
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      int s = 0;
+      uint32_t ph = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
+        int n_tile, t_tile, split, tile;
+        decode_work(w, p, n_tile, t_tile, split, tile);
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        const int acc = iter & 1;
+        const uint32_t acc_ph = (iter >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint64_t adesc = umma_desc_k_sw128(a_addr);
+          const uint64_t bdesc = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // +32 bytes per K step inside the 128-byte swizzle atom (address field is >>4)
+            umma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);      // stage reusable once these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;                       // TMEM lane quarter this warp may access
+    const int row = q * 32 + lane;                // 0..127 inside the tile
+    int iter = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++iter) {
+      int n_tile, t_tile, split, tile;
+      decode_work(w, p, n_tile, t_tile, split, tile);
+      const int acc = iter & 1;
+      const uint32_t acc_ph = (iter >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+      tc_fence_after();
+      const int n = n_tile * BM + row;
+      const int t0 = t_tile * BN;
+      const int t_valid = min(BN, p.T - t0);
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      if (p.splits == 1) {
+        const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (c0 >= t_valid) break;               // warp-uniform
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c0, r);
+          tmem_ld_wait();
+          if (n < p.N) {
+            __nv_bfloat16* yp = p.Y + (size_t)(t0 + c0) * p.ldy + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (c0 + j < t_valid) yp[(size_t)j * p.ldy] = __float2bfloat16(__uint_as_float(r[j]) + bias);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+      } else {
+        float* wsp = p.ws + ((size_t)tile * p.splits + split) * (size_t)(BM * BN);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (c0 >= t_valid) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) wsp[(c0 + j) * BM + row] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const int old = atomicAdd(&p.counters[tile], 1);
+          *last_flag = (old == p.splits - 1) ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+          const float* base = p.ws + (size_t)tile * p.splits * (size_t)(BM * BN);
+          if (n < p.N) {
+            for (int c = 0; c < t_valid; ++c) {
+              float acc_v = 0.f;
+              for (int s2 = 0; s2 < p.splits; ++s2)
+                acc_v += __ldcg(base + (size_t)s2 * (BM * BN) + c * BM + row);
+              p.Y[(size_t)(t0 + c) * p.ldy + n] = __float2bfloat16(acc_v + bias);
+            }
+          }
+          if (threadIdx.x == 64) p.counters[tile] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is rewritten next iteration
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// --------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+}  // namespace b200
+
+extern "C" int b200_make_tmap_2d(void* out_map, const void* ptr, int elem_bytes, uint64_t rows, uint64_t cols,
+                                 uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols) {
+  auto fn = b200::get_encode_fn();
+  if (!fn) {
+    b200_set_last_error("cuTensorMapEncodeTiled not available", __FILE__, __LINE__);
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (row_stride_bytes & 15)) {
+    b200_set_last_error("TMA operand must be 16-byte aligned with a 16-byte multiple row stride", __FILE__,
+                        __LINE__);
+    return -2;
+  }
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), dt, 2, const_cast<void*>(ptr), gdim, gstride, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    b200_set_last_error("cuTensorMapEncodeTiled failed", __FILE__, __LINE__);
+    return (int)r;
+  }
+  return 0;
+}
+
+namespace b200 {
+
+struct TmapKey {
+  const void* ptr;
+  uint64_t rows, cols, stride;
+  uint32_t box_rows;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && stride == o.stride && box_rows == o.box_rows;
+  }
+};
+struct TmapHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= k.cols * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+    h ^= (k.stride + k.box_rows) * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+static int cached_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride_bytes,
+                       uint32_t box_rows, int elem_bytes = 2, uint32_t box_cols = BK) {
+  static std::unordered_map<TmapKey, CUtensorMap, TmapHash> cache;
+  static std::mutex mu;
+  TmapKey key{ptr, rows, cols | ((uint64_t)elem_bytes << 56), stride_bytes, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  int rc = b200_make_tmap_2d(out, ptr, elem_bytes, rows, cols, stride_bytes, box_rows, box_cols);
+  if (rc != 0) return rc;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int grid,
+                       cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM));
+    attr_set = true;
+  }
+  gemm_bf16_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM, stream>>>(tmW, tmX, p);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace b200
+
+extern "C" int b200_gemm_plan(int T, int N, int K, int num_sms, int* bn_out, int* splits_out,
+                              size_t* ws_bytes, int* counters_needed) {
+  using namespace b200;
+  int bn = T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : 256));
+  int n_tiles = (N + BM - 1) / BM, t_tiles = (T + bn - 1) / bn;
+  int tiles = n_tiles * t_tiles;
+  int kb_total = (K + BK - 1) / BK;
+  int splits = 1;
+  if (tiles * 2 <= num_sms) {
+    splits = num_sms / tiles;
+    int max_by_k = kb_total / 8 > 0 ? kb_total / 8 : 1;    // at least 8 k-blocks (512 of K) per split
+    if (splits > max_by_k) splits = max_by_k;
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+  }
+  *bn_out = bn;
+  *splits_out = splits;
+  *ws_bytes = splits > 1 ? (size_t)tiles * splits * BM * bn * sizeof(float) : 0;
+  *counters_needed = splits > 1 ? tiles : 0;
+  return 0;
+}
+
+// X [T,K] row stride ldx, W [N,K] row stride ldw, Y [T,N] row stride ldy (elements).
+// ws / counters: scratch for split-K (counters must be zero on first use; the kernel re-arms them).
+extern "C" int b200_gemm_bf16(const void* X, const void* W, void* Y, const void* bias, int T, int N, int K,
+                              int ldx, int ldw, int ldy, void* ws, size_t ws_bytes, int* counters,
+                              int counters_len, int* status, int num_sms, int force_splits,
+                              cudaStream_t stream) {
+  using namespace b200;
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 || ldx % 8 || ldw % 8) {
+    b200_set_last_error("gemm_bf16: K and row strides must be multiples of 8 elements", __FILE__, __LINE__);
+    return -3;
+  }
+  int bn, splits, cneed;
+  size_t need;
+  b200_gemm_plan(T, N, K, num_sms, &bn, &splits, &need, &cneed);
+  if (force_splits > 0) splits = force_splits;
+  GemmParams p;
+  p.Y = reinterpret_cast<__nv_bfloat16*>(Y);
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.ws = reinterpret_cast<float*>(ws);
+  p.counters = counters;
+  p.status = status;
+  p.T = T; p.N = N; p.K = K; p.ldy = ldy;
+  p.n_tiles = (N + BM - 1) / BM;
+  p.t_tiles = (T + bn - 1) / bn;
+  p.kb_total = (K + BK - 1) / BK;
+  if (splits > p.kb_total) splits = p.kb_total;
+  int tiles = p.n_tiles * p.t_tiles;
+  if (splits > 1) {
+    size_t req = (size_t)tiles * splits * BM * bn * sizeof(float);
+    if (ws == nullptr || req > ws_bytes || counters == nullptr || tiles > counters_len) splits = 1;
+  }
+  p.splits = splits;
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  // every split must own at least one k-block
+  while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= p.kb_total) {
+    --p.splits;
+    p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+  }
+  p.w_evict_first = (p.t_tiles == 1) ? 1 : 0;
+  CUtensorMap tmW, tmX;
+  int rc = cached_tmap(&tmW, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, BM);
+  if (rc) return rc;
+  rc = cached_tmap(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn);
+  if (rc) return rc;
+  int total = tiles * p.splits;
+  int grid = total < num_sms ? total : num_sms;
+  switch (bn) {
+    case 32: return launch_gemm<32>(tmW, tmX, p, grid, stream);
+    case 64: return launch_gemm<64>(tmW, tmX, p, grid, stream);
+    case 128: return launch_gemm<128>(tmW, tmX, p, grid, stream);
+    default: return launch_gemm<256>(tmW, tmX, p, grid, stream);
+  }
+}

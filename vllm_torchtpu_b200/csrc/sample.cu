@@ -1,0 +1,312 @@
+// Sampling kernels: greedy argmax, and temperature / top-k / top-p / Gumbel-max
+// sampling without a sort.
+//
+// Top-k and top-p thresholds are found by 32-step bisection over the
+// order-preserving integer image of the fp32 logits, the same sort-free idea as
+// the reference's sampler (reference: src/vllm_torchtpu/layers/adapter/sample/top_k_top_p.py:33-366);
+// the draw itself is argmax(logit/T + Gumbel(u)) over the kept set
+// (reference: src/vllm_torchtpu/runner/tpu_runner.py:9240-9274).  Uniform noise is
+// either supplied (tests) or generated in the kernel with Philox keyed by
+// (seed, step, row, column), so every tensor-parallel rank draws the same token.
+// One CTA per row; each pass re-reads the row (bf16, L2 resident).
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int SAMPLE_THREADS = 1024;
+
+__device__ __forceinline__ uint32_t f2key(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key2f(uint32_t k) {
+  uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(u);
+}
+
+// Philox-4x32-10
+__device__ __forceinline__ uint4 philox(uint4 ctr, uint2 key) {
+  constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint32_t hi0 = __umulhi(M0, ctr.x), lo0 = M0 * ctr.x;
+    const uint32_t hi1 = __umulhi(M1, ctr.z), lo1 = M1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += W0;
+    key.y += W1;
+  }
+  return ctr;
+}
+__device__ __forceinline__ float uniform_at(unsigned long long seed, unsigned long long step, int row,
+                                            int col) {
+  const uint4 r = philox(make_uint4((uint32_t)col, (uint32_t)row, (uint32_t)step, (uint32_t)(step >> 32)),
+                         make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
+  return (float)(r.x >> 8) * (1.0f / 16777216.0f) + (0.5f / 16777216.0f);     // (0, 1)
+}
+
+template <typename T>
+__device__ __forceinline__ float load_logit(const T* p, int i);
+template <>
+__device__ __forceinline__ float load_logit<__nv_bfloat16>(const __nv_bfloat16* p, int i) {
+  return __bfloat162float(p[i]);
+}
+template <>
+__device__ __forceinline__ float load_logit<float>(const float* p, int i) {
+  return p[i];
+}
+
+struct ArgMax {
+  float v;
+  int i;
+};
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+__device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax b{__shfl_xor_sync(0xffffffffu, a.v, o), __shfl_xor_sync(0xffffffffu, a.i, o)};
+    a = better(a, b);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = a;
+  __syncthreads();
+  ArgMax t = lane < nw ? red[lane] : ArgMax{-INFINITY, 0x7fffffff};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax b{__shfl_xor_sync(0xffffffffu, t.v, o), __shfl_xor_sync(0xffffffffu, t.i, o)};
+    t = better(t, b);
+  }
+  return t;
+}
+__device__ __forceinline__ float block_sum_f(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ int block_sum_i(int v, int* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  int t = lane < nw ? red[lane] : 0;
+  return warp_sum(t);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const T* __restrict__ logits, int ld, int V, int* __restrict__ out) {
+  __shared__ ArgMax red[32];
+  const T* row = logits + (size_t)blockIdx.x * ld;
+  ArgMax a{-INFINITY, 0x7fffffff};
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = load_logit(row, i);
+    if (v > a.v) a = ArgMax{v, i};
+  }
+  a = block_argmax(a, red);
+  if (threadIdx.x == 0) out[blockIdx.x] = a.i < V ? a.i : 0;
+}
+
+// Full sampler.  temperature <= 1e-5 -> greedy.  top_k <= 0 and top_p >= 1 disable the filters.
+template <typename T>
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const T* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const float* __restrict__ uniform, unsigned long long seed, unsigned long long step,
+              const long long* __restrict__ step_ptr, int* __restrict__ out) {
+  if (step_ptr != nullptr) step += (unsigned long long)(*step_ptr);   // graph replays read a fresh offset
+  __shared__ ArgMax red[32];
+  __shared__ float redf[32];
+  __shared__ int redi[32];
+  const int r = blockIdx.x;
+  const T* row = logits + (size_t)r * ld;
+  const float temp = temperature[r];
+  if (temp <= 1e-5f) {
+    ArgMax a{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = load_logit(row, i);
+      if (v > a.v) a = ArgMax{v, i};
+    }
+    a = block_argmax(a, red);
+    if (threadIdx.x == 0) out[r] = a.i < V ? a.i : 0;
+    return;
+  }
+  const float inv_t = 1.f / temp;
+  int k = top_k[r];
+  if (k <= 0 || k > V) k = V;
+  const float pp = top_p[r];
+
+  // ---- top-k threshold: largest key with count(x >= key) >= k
+  uint32_t kth = 0;                                     // keep everything
+  if (k < V) {
+    uint32_t lo = 0, hi = 0xffffffffu;                  // invariant: count(>= lo) >= k
+    for (int it = 0; it < 32 && lo < hi; ++it) {
+      const uint32_t mid = lo + ((hi - lo) >> 1) + 1;   // upper mid so the loop terminates
+      int c = 0;
+      for (int i = threadIdx.x; i < V; i += blockDim.x) c += f2key(load_logit(row, i) * inv_t) >= mid;
+      c = block_sum_i(c, redi);
+      if (c >= k) lo = mid; else hi = mid - 1;
+    }
+    kth = lo;
+  }
+  // ---- softmax statistics over the kept set
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float x = load_logit(row, i) * inv_t;
+    if (f2key(x) >= kth) mx = fmaxf(mx, x);
+  }
+  {
+    ArgMax a = block_argmax(ArgMax{mx, 0}, red);
+    mx = a.v;
+  }
+  uint32_t thr = kth;
+  if (pp < 1.f) {
+    float z = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float x = load_logit(row, i) * inv_t;
+      if (f2key(x) >= kth) z += __expf(x - mx);
+    }
+    z = block_sum_f(z, redf);
+    // largest key such that mass(x >= key) >= top_p * Z  (ties at the threshold are all kept)
+    uint32_t lo = kth, hi = f2key(mx);
+    const float want = pp * z;
+    for (int it = 0; it < 32 && lo < hi; ++it) {
+      const uint32_t mid = lo + ((hi - lo) >> 1) + 1;
+      float ms = 0.f;
+      for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float x = load_logit(row, i) * inv_t;
+        if (f2key(x) >= mid) ms += __expf(x - mx);
+      }
+      ms = block_sum_f(ms, redf);
+      if (ms >= want) lo = mid; else hi = mid - 1;
+    }
+    thr = lo;
+  }
+  // ---- Gumbel-max over the kept set
+  ArgMax a{-INFINITY, 0x7fffffff};
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float x = load_logit(row, i) * inv_t;
+    if (f2key(x) >= thr) {
+      float u = uniform != nullptr ? uniform[(size_t)r * V + i] : uniform_at(seed, step, r, i);
+      u = fminf(fmaxf(u, 1e-20f), 1.f - 1e-7f);
+      const float g = -__logf(-__logf(u));
+      const float v = x + g;
+      if (v > a.v) a = ArgMax{v, i};
+    }
+  }
+  a = block_argmax(a, red);
+  if (threadIdx.x == 0) out[r] = a.i < V ? a.i : 0;
+}
+
+// logprob of chosen token + top-k logprobs (k <= 32) with fp32 logsumexp
+template <typename T>
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+logprobs_kernel(const T* __restrict__ logits, int ld, int V, const int* __restrict__ token_ids, int k,
+                float* __restrict__ tok_lp, float* __restrict__ top_lp, int* __restrict__ top_id,
+                int* __restrict__ rank) {
+  __shared__ ArgMax red[32];
+  __shared__ float redf[32];
+  __shared__ int redi[32];
+  const int r = blockIdx.x;
+  const T* row = logits + (size_t)r * ld;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, load_logit(row, i));
+  mx = block_argmax(ArgMax{mx, 0}, red).v;
+  float z = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) z += __expf(load_logit(row, i) - mx);
+  z = block_sum_f(z, redf);
+  const float lse = mx + __logf(z);
+  const int tok = token_ids[r];
+  const float tv = load_logit(row, min(max(tok, 0), V - 1));
+  int c = 0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) c += load_logit(row, i) > tv;
+  c = block_sum_i(c, redi);
+  if (threadIdx.x == 0) {
+    tok_lp[r] = tv - lse;
+    rank[r] = c + 1;
+  }
+  // top-k by repeated arg-max below the previous winner (k is small)
+  float prev_v = INFINITY;
+  int prev_i = -1;
+  for (int j = 0; j < k; ++j) {
+    ArgMax a{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = load_logit(row, i);
+      const bool below = v < prev_v || (v == prev_v && i > prev_i);
+      if (below && (v > a.v || (v == a.v && i < a.i))) a = ArgMax{v, i};
+    }
+    a = block_argmax(a, red);
+    if (threadIdx.x == 0) {
+      top_lp[(size_t)r * k + j] = a.v - lse;
+      top_id[(size_t)r * k + j] = a.i < V ? a.i : 0;
+    }
+    prev_v = a.v;
+    prev_i = a.i;
+  }
+}
+
+__global__ void philox_uniform_kernel(float* out, int R, int V, unsigned long long seed,
+                                      unsigned long long step) {
+  const size_t n = (size_t)R * V;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = uniform_at(seed, step, (int)(i / V), (int)(i % V));
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// dtype: 0 = bf16 logits, 1 = fp32 logits
+extern "C" int b200_argmax(const void* logits, int dtype, int R, int V, int ld, int* out, cudaStream_t stream) {
+  if (R == 0) return 0;
+  if (dtype == 0)
+    argmax_kernel<__nv_bfloat16><<<R, SAMPLE_THREADS, 0, stream>>>((const __nv_bfloat16*)logits, ld, V, out);
+  else
+    argmax_kernel<float><<<R, SAMPLE_THREADS, 0, stream>>>((const float*)logits, ld, V, out);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_sample(const void* logits, int dtype, int R, int V, int ld, const float* temperature,
+                           const int* top_k, const float* top_p, const float* uniform,
+                           unsigned long long seed, unsigned long long step, const long long* step_ptr,
+                           int* out, cudaStream_t stream) {
+  if (R == 0) return 0;
+  if (dtype == 0)
+    sample_kernel<__nv_bfloat16><<<R, SAMPLE_THREADS, 0, stream>>>((const __nv_bfloat16*)logits, ld, V,
+                                                                  temperature, top_k, top_p, uniform, seed,
+                                                                  step, step_ptr, out);
+  else
+    sample_kernel<float><<<R, SAMPLE_THREADS, 0, stream>>>((const float*)logits, ld, V, temperature, top_k,
+                                                          top_p, uniform, seed, step, step_ptr, out);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_logprobs(const void* logits, int dtype, int R, int V, int ld, const int* token_ids, int k,
+                             float* tok_lp, float* top_lp, int* top_id, int* rank, cudaStream_t stream) {
+  if (R == 0) return 0;
+  if (dtype == 0)
+    logprobs_kernel<__nv_bfloat16><<<R, SAMPLE_THREADS, 0, stream>>>((const __nv_bfloat16*)logits, ld, V,
+                                                                    token_ids, k, tok_lp, top_lp, top_id, rank);
+  else
+    logprobs_kernel<float><<<R, SAMPLE_THREADS, 0, stream>>>((const float*)logits, ld, V, token_ids, k, tok_lp,
+                                                            top_lp, top_id, rank);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_philox_uniform(float* out, int R, int V, unsigned long long seed, unsigned long long step,
+                                   cudaStream_t stream) {
+  if (R == 0) return 0;
+  philox_uniform_kernel<<<148 * 4, 256, 0, stream>>>(out, R, V, seed, step);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}

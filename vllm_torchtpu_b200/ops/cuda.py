@@ -1,0 +1,332 @@
+"""ctypes bindings of the in-tree sm_100a kernel library.
+
+The library is ``csrc/libb200_kernels.so`` (built by ``csrc/build.py``; plain C
+ABI, raw device pointers, the caller's CUDA stream).  Importing this module on a
+machine with a GPU but without the built library raises: there is no PyTorch
+fallback for CUDA tensors.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_size_t, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from .. import envs
+from . import count_launch
+
+_lib = None
+_sms = 148
+
+
+def lib():
+    global _lib, _sms
+    if _lib is not None:
+        return _lib
+    from ..csrc import build as _build
+    path = envs.B200_KERNEL_LIB or _build.lib_path()
+    if not os.path.exists(path):
+        raise RuntimeError(f"kernel library {path} is missing; run `python -m vllm_torchtpu_b200.csrc.build`")
+    _lib = ctypes.CDLL(path)
+    _lib.b200_get_last_error.restype = ctypes.c_char_p
+    _lib.b200_attn_decode_scratch_bytes.restype = c_size_t
+    if torch.cuda.is_available():
+        _sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _lib
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib().b200_get_last_error().decode()
+        raise RuntimeError(f"{what} failed (rc={rc}): {msg}")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+class Workspace:
+    """Per-device scratch shared by all launches on the engine's stream."""
+
+    _by_device: dict = {}
+
+    def __init__(self, device):
+        self.device = device
+        self.gemm_ws = torch.empty(64 * 2**20, dtype=torch.uint8, device=device)
+        self.gemm_counters = torch.zeros(16384, dtype=torch.int32, device=device)
+        self.attn_scratch = torch.empty(48 * 2**20, dtype=torch.uint8, device=device)
+        self.attn_counters = torch.zeros(65536, dtype=torch.int32, device=device)
+        self.status = torch.zeros(16, dtype=torch.int32, device=device)
+        self.rng_step = torch.zeros(1, dtype=torch.int64, device=device)
+
+    @classmethod
+    def get(cls, device) -> "Workspace":
+        key = torch.device(device).index or 0
+        ws = cls._by_device.get(key)
+        if ws is None:
+            ws = cls._by_device[key] = Workspace(device)
+        return ws
+
+
+def check_status(device=None) -> int:
+    """Read (and clear) the status word that bounded device waits write on timeout."""
+    ws = Workspace.get(device or torch.cuda.current_device())
+    v = int(ws.status[0].item())
+    if v:
+        ws.status.zero_()
+    return v
+
+
+# ------------------------------------------------------------------ elementwise
+def _require_bf16(*ts):
+    for t in ts:
+        if t is not None and t.dtype != torch.bfloat16:
+            raise TypeError(f"sm_100a kernels take bfloat16 tensors, got {t.dtype}")
+
+
+def rms_norm(x, weight, eps):
+    _require_bf16(x, weight)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    T, H = x.numel() // x.shape[-1], x.shape[-1]
+    _check(lib().b200_rms_norm(_p(x), c_void_p(0), _p(weight), _p(y), c_int(T), c_int(H), c_float(eps),
+                               _stream()), "rms_norm")
+    count_launch()
+    return y
+
+
+def fused_add_rms_norm(x, residual, weight, eps):
+    """In-place on ``residual`` (residual += x), returns (normed, residual)."""
+    _require_bf16(x, residual, weight)
+    x = x.contiguous()
+    assert residual.is_contiguous()
+    y = torch.empty_like(x)
+    T, H = x.numel() // x.shape[-1], x.shape[-1]
+    _check(lib().b200_rms_norm(_p(x), _p(residual), _p(weight), _p(y), c_int(T), c_int(H), c_float(eps),
+                               _stream()), "fused_add_rms_norm")
+    count_launch()
+    return y, residual
+
+
+def silu_and_mul(x):
+    _require_bf16(x)
+    x = x.contiguous()
+    T, I2 = x.shape
+    y = torch.empty((T, I2 // 2), dtype=x.dtype, device=x.device)
+    _check(lib().b200_silu_and_mul(_p(x), _p(y), c_int(T), c_int(I2 // 2), _stream()), "silu_and_mul")
+    count_launch()
+    return y
+
+
+def embedding(ids, table, token_src=None, last_tokens=None):
+    _require_bf16(table)
+    T = ids.numel()
+    out = torch.empty((T, table.shape[1]), dtype=table.dtype, device=table.device)
+    assert ids.dtype == torch.int32
+    _check(lib().b200_embedding(_p(ids), _p(token_src), _p(last_tokens), _p(table), _p(out), c_int(T),
+                                c_int(table.shape[1]), c_int(table.shape[0]), _stream()), "embedding")
+    count_launch()
+    return out
+
+
+def gather_rows(hidden, residual, idx):
+    R, H = idx.numel(), hidden.shape[1]
+    oh = torch.empty((R, H), dtype=hidden.dtype, device=hidden.device)
+    orr = torch.empty_like(oh) if residual is not None else None
+    _check(lib().b200_gather_rows(_p(hidden), _p(residual), _p(idx), _p(oh), _p(orr), c_int(R), c_int(H),
+                                  c_int(hidden.shape[0]), _stream()), "gather_rows")
+    count_launch()
+    return oh, orr
+
+
+def scatter_tokens(tokens, slots, last_tokens):
+    _check(lib().b200_scatter_tokens(_p(tokens), _p(slots), _p(last_tokens), c_int(tokens.numel()),
+                                     c_int(last_tokens.numel()), _stream()), "scatter_tokens")
+    count_launch()
+
+
+def rope_and_cache(qkv, positions, inv_freq, kv_cache, slot_mapping, num_q_heads, num_kv_heads, head_dim,
+                   interleaved=False, q_norm_w=None, k_norm_w=None, eps=1e-6, k_scale=1.0, v_scale=1.0):
+    _require_bf16(qkv, q_norm_w, k_norm_w)
+    qkv = qkv.contiguous()
+    T = qkv.shape[0]
+    q = torch.empty((T, num_q_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    rot_pairs = inv_freq.numel()
+    if not interleaved and rot_pairs * 2 != head_dim:
+        raise NotImplementedError("partial rotary with half-rotation layout")
+    if positions.dtype != torch.int32:
+        positions = positions.to(torch.int32)
+    if kv_cache is not None:
+        nb, bs = kv_cache.shape[0], kv_cache.shape[3]
+        eb = kv_cache.element_size()
+    else:
+        nb, bs, eb = 0, 16, 2
+    _check(lib().b200_rope_and_cache(
+        _p(qkv), _p(positions), _p(inv_freq), c_int(rot_pairs), _p(slot_mapping), _p(q), _p(kv_cache),
+        _p(q_norm_w), _p(k_norm_w), c_float(eps), c_int(T), c_int(num_q_heads), c_int(num_kv_heads),
+        c_int(head_dim), c_int(bs), c_longlong(nb), c_int(1 if interleaved else 0), c_int(eb),
+        c_float(k_scale), c_float(v_scale), _stream()), "rope_and_cache")
+    count_launch()
+    return q
+
+
+# ------------------------------------------------------------------------ GEMM
+def gemm(x, w, bias=None, out=None, force_splits: int = 0):
+    """y[T,N] = x[T,K] @ w[N,K]^T (+bias) on the tcgen05 kernel."""
+    _require_bf16(x, w, bias)
+    if envs.B200_GEMM_IMPL == "cublas":
+        y = torch.nn.functional.linear(x, w, bias)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    T, K = x2.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and w.stride(1) == 1
+    y = out if out is not None else torch.empty((T, N), dtype=x.dtype, device=x.device)
+    if T == 0:
+        return y.reshape(*lead, N)
+    ws = Workspace.get(x.device)
+    _check(lib().b200_gemm_bf16(
+        _p(x2), _p(w), _p(y), _p(bias), c_int(T), c_int(N), c_int(K), c_int(x2.stride(0)), c_int(w.stride(0)),
+        c_int(y.stride(0)), _p(ws.gemm_ws), c_size_t(ws.gemm_ws.numel()), _p(ws.gemm_counters),
+        c_int(ws.gemm_counters.numel()), _p(ws.status), c_int(_sms), c_int(force_splits), _stream()), "gemm")
+    count_launch()
+    return y.reshape(*lead, N)
+
+
+def gemm_plan(T, N, K):
+    bn, sp, wsb, cn = c_int(), c_int(), c_size_t(), c_int()
+    lib().b200_gemm_plan(c_int(T), c_int(N), c_int(K), c_int(_sms), ctypes.byref(bn), ctypes.byref(sp),
+                         ctypes.byref(wsb), ctypes.byref(cn))
+    return bn.value, sp.value, wsb.value, cn.value
+
+
+# ------------------------------------------------------------------- attention
+def decode_splits(num_reqs: int, num_kv_heads: int) -> int:
+    if envs.B200_ATTN_SPLIT_KV > 0:
+        return envs.B200_ATTN_SPLIT_KV
+    target = 4 * _sms
+    s = -(-target // max(1, num_reqs * num_kv_heads))
+    return max(1, min(16, s))
+
+
+def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=None, sinks=None,
+                    k_scale=1.0, v_scale=1.0, return_lse=False):
+    """Ragged paged attention over [decode | prefill/mixed] request ranges of the batch."""
+    _require_bf16(q)
+    if kv_cache.dtype != torch.bfloat16:
+        raise NotImplementedError("fp8 KV cache attention kernel")
+    T, Hq, D = q.shape
+    nb, _, Hkv, bs, _ = kv_cache.shape
+    out = torch.zeros_like(q)
+    lse = torch.full((T, Hq), float("-inf"), dtype=torch.float32, device=q.device) if return_lse else None
+    ws = Workspace.get(q.device)
+    G = Hq // Hkv
+    R = meta.num_reqs
+    R_launch = meta.padded_num_reqs if meta.padded_num_reqs is not None else R
+    nd = meta.num_decode_reqs
+    max_blocks = meta.block_tables.shape[1]
+    window = int(sliding_window) if sliding_window else 0
+    cap = float(softcap) if softcap else 0.0
+    L = lib()
+    if nd > 0 and G <= 16:
+        # decode range; in a padded (graph) step all launched requests are decode-shaped
+        n_dec = R_launch if nd == R else nd
+        splits = decode_splits(n_dec, Hkv)
+        need = L.b200_attn_decode_scratch_bytes(c_int(n_dec), c_int(Hkv), c_int(splits), c_int(D))
+        if need > ws.attn_scratch.numel() or n_dec * Hkv > ws.attn_counters.numel():
+            splits = 1
+        _check(L.b200_attn_decode(
+            _p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
+            _p(meta.query_start_loc), c_int(0), c_int(n_dec), c_int(max_blocks), c_int(bs), c_longlong(nb),
+            c_int(Hq), c_int(Hkv), c_int(D), c_float(scale), c_int(window), c_float(cap), _p(sinks),
+            c_int(splits), _p(ws.attn_scratch), _p(ws.attn_counters), _stream()), "attn_decode")
+        count_launch()
+    else:
+        nd = 0
+    if R > nd:
+        qsl = meta.query_start_loc_cpu
+        if qsl is not None:
+            ql = (qsl[nd + 1:R + 1] - qsl[nd:R])
+            tiles = int(((ql + 63) // 64).sum())
+        else:
+            tiles = (T + 63) // 64 + (R - nd)
+        _check(L.b200_attn_prefill(
+            _p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
+            _p(meta.query_start_loc), c_int(nd), c_int(R), c_int(tiles), c_int(max_blocks), c_int(bs),
+            c_longlong(nb), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale), c_int(window), c_float(cap),
+            _p(sinks), _stream()), "attn_prefill")
+        count_launch()
+    if return_lse:
+        return out, lse
+    return out
+
+
+# -------------------------------------------------------------------- sampling
+def _logit_dtype(t):
+    if t.dtype == torch.bfloat16:
+        return 0
+    if t.dtype == torch.float32:
+        return 1
+    raise TypeError(f"logits must be bf16 or fp32, got {t.dtype}")
+
+
+def argmax(logits):
+    R, V = logits.shape
+    out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    _check(lib().b200_argmax(_p(logits), c_int(_logit_dtype(logits)), c_int(R), c_int(V),
+                             c_int(logits.stride(0)), _p(out), _stream()), "argmax")
+    count_launch()
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, uniform=None, all_greedy=False, seed: int = 0,
+           step_tensor=None):
+    if all_greedy:
+        return argmax(logits)
+    R, V = logits.shape
+    out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    _check(lib().b200_sample(_p(logits), c_int(_logit_dtype(logits)), c_int(R), c_int(V),
+                             c_int(logits.stride(0)), _p(temperature), _p(top_k), _p(top_p), _p(uniform),
+                             c_ulonglong(seed), c_ulonglong(0), _p(step_tensor), _p(out), _stream()), "sample")
+    count_launch()
+    return out
+
+
+def gather_logprobs(logits, token_ids, k: int):
+    R, V = logits.shape
+    dev = logits.device
+    tok_lp = torch.empty(R, dtype=torch.float32, device=dev)
+    top_lp = torch.empty((R, max(k, 1)), dtype=torch.float32, device=dev)
+    top_id = torch.empty((R, max(k, 1)), dtype=torch.int32, device=dev)
+    rank = torch.empty(R, dtype=torch.int32, device=dev)
+    _check(lib().b200_logprobs(_p(logits), c_int(_logit_dtype(logits)), c_int(R), c_int(V),
+                               c_int(logits.stride(0)), _p(token_ids.to(torch.int32)), c_int(k), _p(tok_lp),
+                               _p(top_lp), _p(top_id), _p(rank), _stream()), "logprobs")
+    count_launch()
+    return tok_lp, top_lp[:, :k], top_id[:, :k], rank
+
+
+def philox_uniform(R, V, seed, step, device):
+    out = torch.empty((R, V), dtype=torch.float32, device=device)
+    _check(lib().b200_philox_uniform(_p(out), c_int(R), c_int(V), c_ulonglong(seed), c_ulonglong(step),
+                                     _stream()), "philox_uniform")
+    return out
+
+
+def flush_l2(device=None):
+    ws = Workspace.get(device or torch.cuda.current_device())
+    if not hasattr(ws, "flush_buf"):
+        ws.flush_buf = torch.empty(256 * 2**20, dtype=torch.uint8, device=ws.device)
+    _check(lib().b200_flush_l2(_p(ws.flush_buf), c_size_t(ws.flush_buf.numel()), _stream()), "flush_l2")

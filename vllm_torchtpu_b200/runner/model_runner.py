@@ -204,6 +204,7 @@ class ModelRunner:
         v = hv("batch_slots", R_pad); v[:n] = slots; v[n:] = -1
         v = hv("temperature", R_pad, np.float32); v[:n] = b.temperature[slots]; v[n:] = 0
         v = hv("top_p", R_pad, np.float32); v[:n] = b.top_p[slots]; v[n:] = 1
+        hv("rng_step").view(np.int64)[0] = self.stats["steps"]
         bufs.np_bt[:n] = b.block_table[slots]
         if R_pad > n:
             bufs.np_bt[n:R_pad] = 0
@@ -237,11 +238,17 @@ class ModelRunner:
         rows = self._select_rows(hidden, residual, meta.logits_indices)
         h = self.model.finalize(*rows)
         logits = self.model.compute_logits(h)
-        uniform = None
-        if not all_greedy:
-            uniform = torch.rand(logits.shape, generator=self._gen, device=self.device, dtype=torch.float32)
-        tokens = ops.sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
-                            dv("top_p", R, torch.float32), uniform, all_greedy).to(torch.int32)
+        if self.is_cuda:
+            # noise comes from Philox inside the kernel, keyed by (seed, step counter in device memory)
+            tokens = ops.cuda_ops().sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
+                                           dv("top_p", R, torch.float32), None, all_greedy,
+                                           seed=self.mcfg.seed, step_tensor=dv("rng_step").view(torch.int64))
+        else:
+            uniform = None
+            if not all_greedy:
+                uniform = torch.rand(logits.shape, generator=self._gen, dtype=torch.float32)
+            tokens = ops.sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
+                                dv("top_p", R, torch.float32), uniform, all_greedy).to(torch.int32)
         self._store_last_tokens(tokens, dv("batch_slots", R))
         return tokens, logits
 
