@@ -53,3 +53,14 @@ def test_prefix_caching_reuses_blocks():
     b = llm.generate([p], sp)[0]
     assert a.outputs[0].token_ids == b.outputs[0].token_ids
     assert b.num_cached_tokens == 48      # 3 full blocks of the 64-token prompt (last token recomputed)
+
+
+def test_tiny_moe_matches_dense_reference():
+    llm = LLM("tiny-moe", device="cpu", max_num_seqs=8, max_num_batched_tokens=48, block_size=16,
+              init_dist=False)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    outs = llm.generate(_prompts()[:3], sp)
+    model = llm.engine.runner.model
+    for p, o in zip(_prompts()[:3], outs):
+        want, _ = dense_greedy_generate(model, p, 8)
+        assert o.outputs[0].token_ids == want

@@ -19,6 +19,7 @@
 //
 // No reference counterpart as CUDA: the reference's dense matmuls are XLA dots and
 // Pallas quantized_matmul kernels (reference: src/vllm_torchtpu/kernels/quantized_matmul/).
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -53,7 +54,38 @@ struct GemmParams {
   int T, N, K, ldy;
   int n_tiles, t_tiles, splits, kb_total, kb_per_split;
   int w_evict_first;
+  // ---- fused cross-rank reduction over NVLink peer memory (world == 1: plain GEMM)
+  int world, rank, ar_mode;              // ar_mode 0: all-reduce (sum lands on every rank), 1: reduce-scatter
+  uint8_t* peer[8];                      // heap base of every rank (own heap at [rank])
+  unsigned long long part_off, out_off;  // heap offsets: partial [T,N] bf16, reduced output [T,N] bf16
+  unsigned long long tile_flag_off;      // heap offset: int[world][max_tiles], written by producers at the owner
+  unsigned long long done_flag_off;      // heap offset: int[max_tiles], written by the owner at every reader
+  int max_tiles;
+  int* epoch_ptr;                        // local: epoch of the last completed fused launch
+  int* cta_done;                         // local: CTA exit counter
+  unsigned int spin_limit;
 };
+
+constexpr int NUM_THREADS_FUSED = NUM_THREADS + 128;   // + 4 reducer warps
+
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void decode_tile(int tile, const GemmParams& p, int& n_tile, int& t_tile) {
+  const int per_group = GROUP_N * p.t_tiles;
+  const int g = tile / per_group;
+  const int first_n = g * GROUP_N;
+  const int gsize = min(GROUP_N, p.n_tiles - first_n);
+  const int r = tile - g * per_group;
+  n_tile = first_n + r % gsize;
+  t_tile = r / gsize;
+}
 
 __device__ __forceinline__ void decode_work(int w, const GemmParams& p, int& n_tile, int& t_tile,
                                             int& split, int& tile) {
@@ -69,7 +101,7 @@ __device__ __forceinline__ void decode_work(int w, const GemmParams& p, int& n_t
 }
 
 template <int BN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS_FUSED, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  const GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -84,6 +116,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  volatile int* red_ok = reinterpret_cast<volatile int*>(tmem_slot + 3);
+  const bool fused = p.world > 1;
+  // every thread reads the epoch before any CTA of this launch can have bumped it
+  const int epoch = fused ? (*reinterpret_cast<volatile int*>(p.epoch_ptr) + 1) : 0;
+  __nv_bfloat16* const dst_base = fused ? reinterpret_cast<__nv_bfloat16*>(p.peer[p.rank] + p.part_off) : p.Y;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -99,6 +136,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     mbar_init(&tempty[1], 4);
     *abort_flag = 0;
     *last_flag = 0;
+    *red_ok = 1;
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
@@ -179,7 +217,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         if (ok) umma_commit(&tfull[acc]);
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;                       // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;                // 0..127 inside the tile
@@ -204,7 +242,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           tmem_ld_32x32(taddr + c0, r);
           tmem_ld_wait();
           if (n < p.N) {
-            __nv_bfloat16* yp = p.Y + (size_t)(t0 + c0) * p.ldy + n;
+            __nv_bfloat16* yp = dst_base + (size_t)(t0 + c0) * p.ldy + n;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (c0 + j < t_valid) yp[(size_t)j * p.ldy] = __float2bfloat16(__uint_as_float(r[j]) + bias);
@@ -214,6 +252,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
+        if (fused) {
+          // partial tile is in this rank's heap: make it visible system-wide, then tell the tile's owner
+          __threadfence_system();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 64) {
+            int* flag = reinterpret_cast<int*>(p.peer[tile % p.world] + p.tile_flag_off) +
+                        (size_t)p.rank * p.max_tiles + tile;
+            st_release_sys(flag, epoch);
+          }
+        }
       } else {
         float* wsp = p.ws + ((size_t)tile * p.splits + split) * (size_t)(BM * BN);
 #pragma unroll 1
@@ -244,13 +292,90 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
               float acc_v = 0.f;
               for (int s2 = 0; s2 < p.splits; ++s2)
                 acc_v += __ldcg(base + (size_t)s2 * (BM * BN) + c * BM + row);
-              p.Y[(size_t)(t0 + c) * p.ldy + n] = __float2bfloat16(acc_v + bias);
+              dst_base[(size_t)(t0 + c) * p.ldy + n] = __float2bfloat16(acc_v + bias);
             }
           }
           if (threadIdx.x == 64) p.counters[tile] = 0;
+          if (fused) {
+            __threadfence_system();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+              int* flag = reinterpret_cast<int*>(p.peer[tile % p.world] + p.tile_flag_off) +
+                          (size_t)p.rank * p.max_tiles + tile;
+              st_release_sys(flag, epoch);
+            }
+          }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is rewritten next iteration
       }
+    }
+  }
+
+  else if (fused) {
+    // ------------------------------------------- reducer warps (threads 192..319)
+    // Tile `tile` is owned by rank tile % world.  The owner waits until every rank has published
+    // its partial of that tile, sums the partials in rank order (fp32), writes bf16 to the output
+    // buffer of every rank (all-reduce) or its own (reduce-scatter) and raises the tile's done flag
+    // there.  Reads and writes of peer heaps are plain NVLink loads/stores.
+    const int rt = threadIdx.x - NUM_THREADS;        // 0..127
+    const int tiles = p.n_tiles * p.t_tiles;
+    const int* my_tile_flags = reinterpret_cast<const int*>(p.peer[p.rank] + p.tile_flag_off);
+    int owned_idx = 0;
+    for (int tile = p.rank; tile < tiles; tile += p.world, ++owned_idx) {
+      if (owned_idx % (int)gridDim.x != (int)blockIdx.x) continue;
+      if (rt < p.world) {
+        if (!wait_flag_ge(my_tile_flags + (size_t)rt * p.max_tiles + tile, epoch, p.status, p.spin_limit))
+          *red_ok = 0;
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (*red_ok) {
+        int n_tile, t_tile;
+        decode_tile(tile, p, n_tile, t_tile);
+        const int n0 = n_tile * BM, t0 = t_tile * BN;
+        const int t_valid = min(BN, p.T - t0);
+        const int n_vecs = min(BM, p.N - n0) >> 3;             // 16-byte vectors per row (N % 8 == 0)
+        for (int idx = rt; idx < t_valid * (BM / 8); idx += 128) {
+          const int row = idx / (BM / 8), v = idx % (BM / 8);
+          if (v >= n_vecs) continue;
+          const size_t off = ((size_t)(t0 + row) * p.ldy + n0 + v * 8) * sizeof(__nv_bfloat16);
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int r = 0; r < p.world; ++r) {
+            const uint4 raw = ld_relaxed_sys_v4(p.peer[r] + p.part_off + off);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __bfloat1622float2(h[j]);
+              acc[2 * j] += f.x;
+              acc[2 * j + 1] += f.y;
+            }
+          }
+          uint4 o;
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+          if (p.ar_mode == 0) {
+            for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.peer[r] + p.out_off + off) = o;
+          } else {
+            *reinterpret_cast<uint4*>(p.peer[p.rank] + p.out_off + off) = o;
+          }
+        }
+        __threadfence_system();
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (*red_ok) {
+        if (p.ar_mode == 0) {
+          if (rt < p.world)
+            st_release_sys(reinterpret_cast<int*>(p.peer[rt] + p.done_flag_off) + tile, epoch);
+        } else if (rt == 0) {
+          st_release_sys(reinterpret_cast<int*>(p.peer[p.rank] + p.done_flag_off) + tile, epoch);
+        }
+      }
+    }
+    // this rank's output is complete once every tile it reads has its done flag
+    const int* done = reinterpret_cast<const int*>(p.peer[p.rank] + p.done_flag_off);
+    for (int tile = blockIdx.x * 128 + rt; tile < tiles; tile += gridDim.x * 128) {
+      if (p.ar_mode == 1 && tile % p.world != p.rank) continue;
+      wait_flag_ge(done + tile, epoch, p.status, p.spin_limit);
     }
   }
 
@@ -259,6 +384,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+  if (fused && threadIdx.x == 0) {
+    __threadfence();
+    const int arrived = atomicAdd(p.cta_done, 1) + 1;
+    if (arrived == (int)gridDim.x) {
+      *p.cta_done = 0;
+      *p.epoch_ptr = epoch;       // every CTA of this launch has read the old value by now
+      __threadfence();
+    }
   }
 }
 
@@ -358,7 +492,7 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gem
                                          Cfg::SMEM));
     attr_set = true;
   }
-  gemm_bf16_kernel<BN><<<grid, NUM_THREADS, Cfg::SMEM, stream>>>(tmW, tmX, p);
+  gemm_bf16_kernel<BN><<<grid, p.world > 1 ? NUM_THREADS_FUSED : NUM_THREADS, Cfg::SMEM, stream>>>(tmW, tmX, p);
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
@@ -404,6 +538,8 @@ extern "C" int b200_gemm_bf16(const void* X, const void* W, void* Y, const void*
   b200_gemm_plan(T, N, K, num_sms, &bn, &splits, &need, &cneed);
   if (force_splits > 0) splits = force_splits;
   GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.world = 1;
   p.Y = reinterpret_cast<__nv_bfloat16*>(Y);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.ws = reinterpret_cast<float*>(ws);
@@ -427,6 +563,80 @@ extern "C" int b200_gemm_bf16(const void* X, const void* W, void* Y, const void*
     p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
   }
   p.w_evict_first = (p.t_tiles == 1) ? 1 : 0;
+  CUtensorMap tmW, tmX;
+  int rc = cached_tmap(&tmW, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, BM);
+  if (rc) return rc;
+  rc = cached_tmap(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn);
+  if (rc) return rc;
+  int total = tiles * p.splits;
+  int grid = total < num_sms ? total : num_sms;
+  switch (bn) {
+    case 32: return launch_gemm<32>(tmW, tmX, p, grid, stream);
+    case 64: return launch_gemm<64>(tmW, tmX, p, grid, stream);
+    case 128: return launch_gemm<128>(tmW, tmX, p, grid, stream);
+    default: return launch_gemm<256>(tmW, tmX, p, grid, stream);
+  }
+}
+
+// Row-parallel GEMM fused with the cross-rank reduction: Y = sum over ranks of X_r * W_r^T.
+// Every rank of the group launches this with identical T/N (K is the local shard).  The partial
+// tile of each rank goes to its symmetric heap; the owner of a tile (tile % world) sums the
+// partials over NVLink and writes the bf16 result into the output buffer (heap offset out_off)
+// of every rank (mode 0, all-reduce) or only its own (mode 1, reduce-scatter by tile ownership).
+// peers: `world` heap base pointers; ctrl: local device int[4] {epoch, cta_done, -, -}.
+extern "C" int b200_gemm_bf16_fused_reduce(const void* X, const void* W, int T, int N, int K, int ldx, int ldw,
+                                           void* const* peers, int rank, int world, int mode,
+                                           unsigned long long part_off, unsigned long long out_off,
+                                           unsigned long long tile_flag_off,
+                                           unsigned long long done_flag_off, int max_tiles, int* ctrl,
+                                           void* ws, size_t ws_bytes, int* counters, int counters_len,
+                                           int* status, int num_sms, unsigned int spin_limit,
+                                           cudaStream_t stream) {
+  using namespace b200;
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 || ldx % 8 || ldw % 8 || N % 8 || world < 2 || world > 8) {
+    b200_set_last_error("gemm_fused_reduce: K, N, strides multiples of 8 and 2 <= world <= 8 required",
+                        __FILE__, __LINE__);
+    return -3;
+  }
+  int bn, splits, cneed;
+  size_t need;
+  b200_gemm_plan(T, N, K, num_sms, &bn, &splits, &need, &cneed);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.Y = nullptr;
+  p.bias = nullptr;
+  p.ws = reinterpret_cast<float*>(ws);
+  p.counters = counters;
+  p.status = status;
+  p.T = T; p.N = N; p.K = K; p.ldy = N;
+  p.n_tiles = (N + BM - 1) / BM;
+  p.t_tiles = (T + bn - 1) / bn;
+  p.kb_total = (K + BK - 1) / BK;
+  int tiles = p.n_tiles * p.t_tiles;
+  if (tiles > max_tiles) {
+    b200_set_last_error("gemm_fused_reduce: more tiles than flag slots", __FILE__, __LINE__);
+    return -4;
+  }
+  if (splits > p.kb_total) splits = p.kb_total;
+  if (splits > 1) {
+    size_t req = (size_t)tiles * splits * BM * bn * sizeof(float);
+    if (ws == nullptr || req > ws_bytes || counters == nullptr || tiles > counters_len) splits = 1;
+  }
+  p.splits = splits;
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= p.kb_total) {
+    --p.splits;
+    p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+  }
+  p.w_evict_first = (p.t_tiles == 1) ? 1 : 0;
+  p.world = world; p.rank = rank; p.ar_mode = mode;
+  for (int i = 0; i < 8; ++i) p.peer[i] = i < world ? (uint8_t*)peers[i] : nullptr;
+  p.part_off = part_off; p.out_off = out_off;
+  p.tile_flag_off = tile_flag_off; p.done_flag_off = done_flag_off;
+  p.max_tiles = max_tiles;
+  p.epoch_ptr = ctrl; p.cta_done = ctrl + 1;
+  p.spin_limit = spin_limit;
   CUtensorMap tmW, tmX;
   int rc = cached_tmap(&tmW, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, BM);
   if (rc) return rc;

@@ -120,7 +120,8 @@ class RowParallelLinear(LinearBase):
         if self.tp_size == 1 or not self.reduce_results:
             return self.method.apply(self, x, self.bias)
         comm = get_tp_comm()
-        if x.is_cuda and envs.B200_FUSED_TP and comm.heap is not None and self.method.supports_fused_reduce:
+        if (x.is_cuda and comm.heap is not None and comm.heap.fused_tp is not None
+                and self.method.supports_fused_reduce):
             y = self.method.apply_fused_all_reduce(self, x, comm)
         else:
             y = comm.all_reduce(self.method.apply(self, x, None))

@@ -1,0 +1,104 @@
+"""Mixture-of-experts layer: router, expert ownership, dispatch / experts / combine.
+
+Routing follows the reference (scoring → optional bias / grouped top-k → top-k →
+renormalise → scale, reference: src/vllm_torchtpu/layers/adapter/moe_routing.py:161-343).
+Expert ownership under expert parallelism is linear by ``experts_start``
+(reference: src/vllm_torchtpu/layers/core/fused_moe_gmm.py:749-753) or a static
+permutation (``expert_placement``).  Three data planes, as in the reference
+(reference: src/vllm_torchtpu/layers/adapter/custom_ops/moe_runner.py:41-169):
+
+* no EP: every rank holds all experts with the intermediate dim sharded over TP;
+* EP, all-gather/reduce-scatter plane: ``DeviceCommunicator.dispatch`` gathers
+  tokens, every rank runs its experts on all tokens, ``combine`` reduce-scatters;
+* EP, fused plane: the dispatch/combine all-to-all runs inside the expert kernel
+  over NVLink peer memory (``ops.cuda.moe_ep_fused``).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import envs, ops
+from ..parallel.communicator import get_ep_comm, get_tp_comm
+from ..parallel.state import get_state
+from ..quantization import get_moe_method
+from .linear import ReplicatedLinear
+
+
+def expert_placement(num_experts: int, ep_size: int, policy: str = "linear",
+                     static_perm: Optional[list] = None) -> list:
+    """``owner[e]`` = (rank, local index) for every global expert id."""
+    per = num_experts // ep_size
+    if policy == "linear":
+        return [(e // per, e % per) for e in range(num_experts)]
+    if policy == "round_robin":
+        return [(e % ep_size, e // ep_size) for e in range(num_experts)]
+    if policy == "static":
+        assert static_perm is not None and sorted(static_perm) == list(range(num_experts))
+        pos = {e: i for i, e in enumerate(static_perm)}
+        return [(pos[e] // per, pos[e] % per) for e in range(num_experts)]
+    raise ValueError(policy)
+
+
+class FusedMoE:
+    def __init__(self, name: str, cfg, device, quant_config=None):
+        st = get_state()
+        self.name = name
+        self.cfg = cfg
+        self.device = device
+        self.dtype = cfg.dtype
+        self.hidden_size = cfg.hidden_size
+        self.num_experts = cfg.num_experts
+        self.top_k = cfg.num_experts_per_tok
+        self.use_ep = st.expert_parallel and st.ep.size > 1
+        self.ep_size = st.ep.size if self.use_ep else 1
+        self.ep_rank = st.ep.rank_in_group if self.use_ep else 0
+        self.tp_size = 1 if self.use_ep else st.tp.size
+        self.tp_rank = 0 if self.use_ep else st.tp.rank_in_group
+        self.intermediate_size = cfg.moe_intermediate_size // self.tp_size
+        self.num_local_experts = self.num_experts // self.ep_size
+        lo = self.ep_rank * self.num_local_experts
+        self.expert_range = (lo, lo + self.num_local_experts)
+        self.gate = ReplicatedLinear(f"{name}.gate", cfg.hidden_size, cfg.num_experts, dtype=cfg.dtype,
+                                     device=device, quant_config=None)
+        self.score_bias = None
+        if cfg.moe_score_bias:
+            self.score_bias = torch.zeros(cfg.num_experts, dtype=torch.float32, device=device)
+        self.method = get_moe_method(quant_config, name)
+        self.method.create_weights(self)
+
+    def init_dummy(self, std: float, seed: int) -> None:
+        # router logits come from N(0,1) gate weights so that routing is well spread
+        self.gate.init_dummy(1.0, seed)
+        self.method.init_dummy(self, std, seed)
+        if self.score_bias is not None:
+            from .linear import seeded_normal
+            self.score_bias = seeded_normal(f"{self.name}.bias", (self.num_experts,), 0.01, torch.float32,
+                                            self.device, seed)
+
+    def weight_bytes(self) -> int:
+        return self.method.weight_bytes(self) + self.gate.weight_bytes()
+
+    def route(self, x: torch.Tensor):
+        logits = self.gate(x)
+        c = self.cfg
+        return ops.moe_route(logits, self.top_k, scoring=c.moe_scoring, renormalize=c.moe_renormalize,
+                             routed_scaling=c.moe_routed_scaling, score_bias=self.score_bias,
+                             n_group=c.moe_n_group, topk_group=c.moe_topk_group)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        topk_ids, topk_w = self.route(x)
+        if not self.use_ep:
+            y = self.method.apply(self, x, topk_ids, topk_w)
+            if self.tp_size > 1:
+                y = get_tp_comm().all_reduce(y)
+            return y
+        comm = get_ep_comm()
+        if (x.is_cuda and envs.B200_MOE_FUSED_EP and comm.heap is not None
+                and x.shape[0] >= envs.B200_MOE_FUSED_EP_MIN_TOKENS and hasattr(self.method, "apply_fused_ep")):
+            return self.method.apply_fused_ep(self, x, topk_ids, topk_w, comm)
+        # all-gather / reduce-scatter plane: rows must be equal on every rank (DP lockstep pads them)
+        hx, hw, hi = comm.dispatch(x, topk_w, topk_ids)
+        y = self.method.apply(self, hx, hi, hw)
+        return comm.combine(y)

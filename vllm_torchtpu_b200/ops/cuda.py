@@ -330,3 +330,72 @@ def flush_l2(device=None):
     if not hasattr(ws, "flush_buf"):
         ws.flush_buf = torch.empty(256 * 2**20, dtype=torch.uint8, device=ws.device)
     _check(lib().b200_flush_l2(_p(ws.flush_buf), c_size_t(ws.flush_buf.numel()), _stream()), "flush_l2")
+
+
+# ------------------------------------------------- fused compute + collective (NVLink P2P)
+class FusedTP:
+    """Heap layout and launch state of the fused row-parallel GEMM + reduction."""
+
+    MAX_TILES = 8192
+
+    def __init__(self, heap, max_tokens: int, max_n: int):
+        self.heap = heap
+        self.max_elems = max_tokens * max_n
+        nbytes = self.max_elems * 2
+        self.part = heap.alloc("tp_part", nbytes)
+        self.outs = [heap.alloc("tp_out0", nbytes), heap.alloc("tp_out1", nbytes)]
+        self.tile_flags = heap.alloc("tp_tile_flags", heap.world * self.MAX_TILES * 4)
+        self.done_flags = heap.alloc("tp_done_flags", self.MAX_TILES * 4)
+        self.ctrl = torch.zeros(4, dtype=torch.int32, device=heap.device)
+        self.flip = 0
+
+    @staticmethod
+    def heap_bytes(max_tokens: int, max_n: int, world: int) -> int:
+        return 3 * max_tokens * max_n * 2 + world * FusedTP.MAX_TILES * 4 + FusedTP.MAX_TILES * 4 + (1 << 20)
+
+
+def gemm_all_reduce(x, w, heap, mode: int = 0):
+    """Row-parallel ``x @ w.T`` summed over the ranks of ``heap`` inside one kernel."""
+    _require_bf16(x, w)
+    st = heap.fused_tp
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    x2 = x.reshape(-1, x.shape[-1])
+    T, K = x2.shape
+    N = w.shape[0]
+    if T * N > st.max_elems:
+        raise RuntimeError(f"fused TP buffers hold {st.max_elems} elements, need {T * N}")
+    out = st.outs[st.flip]
+    st.flip ^= 1
+    ws = Workspace.get(x.device)
+    _check(lib().b200_gemm_bf16_fused_reduce(
+        _p(x2), _p(w), c_int(T), c_int(N), c_int(K), c_int(x2.stride(0)), c_int(w.stride(0)),
+        heap.peers_c, c_int(heap.rank), c_int(heap.world), c_int(mode),
+        c_ulonglong(st.part.offset), c_ulonglong(out.offset), c_ulonglong(st.tile_flags.offset),
+        c_ulonglong(st.done_flags.offset), c_int(FusedTP.MAX_TILES), _p(st.ctrl), _p(ws.gemm_ws),
+        c_size_t(ws.gemm_ws.numel()), _p(ws.gemm_counters), c_int(ws.gemm_counters.numel()), _p(ws.status),
+        c_int(_sms), ctypes.c_uint(min(heap.spin_limit, 2**31 - 1)), _stream()), "gemm_fused_reduce")
+    count_launch()
+    return heap.tensor(out, (T, N), torch.bfloat16)
+
+
+def p2p_all_reduce(x, heap):
+    """All-reduce of a bf16 tensor through a staging buffer in the symmetric heap."""
+    _require_bf16(x)
+    n = x.numel()
+    pad = (-n) % 8
+    buf = heap.alloc("ar_stage", heap.ar_stage_bytes)
+    if (n + pad) * 2 > buf.nbytes:
+        raise RuntimeError("all-reduce staging buffer too small")
+    stage = heap.tensor(buf, (n + pad,), torch.bfloat16)
+    stage[:n].copy_(x.reshape(-1))
+    if pad:
+        stage[n:].zero_()
+    ws = Workspace.get(x.device)
+    _check(lib().b200_p2p_all_reduce(
+        heap.peers_c, c_int(heap.rank), c_int(heap.world), c_size_t(buf.offset), c_size_t(heap.flags.offset),
+        _p(heap.ctrl), c_size_t(n + pad), _p(ws.status), ctypes.c_uint(min(heap.spin_limit, 2**31 - 1)),
+        _stream()), "p2p_all_reduce")
+    count_launch()
+    x.copy_(stage[:n].view(x.shape))
+    return x

@@ -135,6 +135,21 @@ def get_dcp_comm() -> DeviceCommunicator:
 
 
 _heaps: dict = {}
+_heap_min_bytes = 0
+
+
+def ensure_tp_heap(max_tokens: int, max_n: int):
+    """Create the TP group's symmetric heap sized for the fused row-parallel GEMMs (GPU, tp > 1)."""
+    global _heap_min_bytes
+    st = get_state()
+    if st.tp.size == 1 or not torch.cuda.is_available() or envs.B200_TP_COMM == "nccl":
+        return None
+    from ..ops import cuda
+    _heap_min_bytes = cuda.FusedTP.heap_bytes(max_tokens, max_n, st.tp.size) + 64 * 2**20
+    comm = get_tp_comm()
+    if comm.heap is not None and envs.B200_FUSED_TP:
+        comm.heap.configure_fused_tp(max_tokens, max_n)
+    return comm.heap
 
 
 def _heap_for(group: Group):
@@ -144,7 +159,7 @@ def _heap_for(group: Group):
     key = (group.name, tuple(group.ranks))
     if key not in _heaps:
         from .symm_heap import SymmetricHeap
-        _heaps[key] = SymmetricHeap.create(group, envs.B200_SYMM_HEAP_MB * 2**20)
+        _heaps[key] = SymmetricHeap.create(group, max(envs.B200_SYMM_HEAP_MB * 2**20, _heap_min_bytes))
     return _heaps[key]
 
 

@@ -77,6 +77,7 @@ class ModelRunner:
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(self.mcfg.seed + 1234)
         self._stage_timers = None
+        self.timing_events = None        # list of (start, end) CUDA events per step when enabled
         if envs.B200_STAGE_TIMING and self.is_cuda:
             from ..tracing.stage_timing import RunnerStageTiming
             self._stage_timers = RunnerStageTiming()
@@ -96,6 +97,9 @@ class ModelRunner:
         else:
             from ..models.loader import load_safetensors
             load_safetensors(self.model, self.cfg.model_path)
+        if self.is_cuda and st.tp.size > 1:
+            from ..parallel.communicator import ensure_tp_heap
+            ensure_tp_heap(self.max_tokens, self.mcfg.hidden_size)
         logger.info("model %s loaded: %.2f GB weights on this rank in %.1fs", self.mcfg.name,
                     self.model.weight_bytes() / 1e9, time.time() - t0)
 
@@ -284,6 +288,10 @@ class ModelRunner:
         self.stats["h2d_bytes"] += bufs.upload(R)
         meta = self._make_meta(p)
         self.stats["steps"] += 1
+        ev0 = None
+        if self.timing_events is not None and self.is_cuda:
+            ev0 = torch.cuda.Event(enable_timing=True)
+            ev0.record()
         use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
                      and envs.B200_CUDA_GRAPHS)
         if use_graph:
@@ -303,6 +311,10 @@ class ModelRunner:
             tokens, _ = self._forward_and_sample(bufs, meta, T, R, p["all_greedy"])
             self.launch_counter += launch_count() - c0
             self.stats["eager_steps"] += 1
+        if ev0 is not None:
+            ev1 = torch.cuda.Event(enable_timing=True)
+            ev1.record()
+            self.timing_events.append((ev0, ev1))
         host = self.tokens_host[self._tok_ring]
         self._tok_ring = (self._tok_ring + 1) % len(self.tokens_host)
         ev = None
