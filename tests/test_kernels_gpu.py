@@ -164,4 +164,7 @@ def test_logprobs():
     b = ref.gather_logprobs(logits, tok, 5)
     _close(a[0], b[0], 1e-3, 1e-3)
     _close(a[1], b[1], 1e-3, 1e-3)
-    assert torch.equal(a[2].long(), b[2]) and torch.equal(a[3].long(), b[3])
+    # bf16 logits tie often: ids may differ among equal values, the values they point at may not
+    lf = logits.float()
+    assert torch.equal(lf.gather(1, a[2].long()), lf.gather(1, b[2]))
+    assert torch.equal(a[3].long(), b[3])

@@ -68,6 +68,21 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
                                return_lse=return_lse)
 
 
+def mla_write_cache(cache, kv_c, k_pe, slot_mapping):
+    if _on_gpu(cache):
+        return cuda_ops().mla_write_cache(cache, kv_c, k_pe, slot_mapping)
+    return ref.mla_write_cache(cache, kv_c, k_pe, slot_mapping)
+
+
+def mla_paged_attention(q_latent, cache, meta, scale, kv_lora_rank, *, topk_indices=None, return_lse=False):
+    if _on_gpu(q_latent):
+        return cuda_ops().mla_paged_attention(q_latent, cache, meta, scale, kv_lora_rank,
+                                              topk_indices=topk_indices, return_lse=return_lse)
+    return ref.mla_paged_attention(q_latent, cache, meta.block_tables, meta.seq_lens, meta.query_start_loc,
+                                   scale, kv_lora_rank, num_reqs=meta.num_reqs, topk_indices=topk_indices,
+                                   return_lse=return_lse)
+
+
 def sample(logits, temperature, top_k, top_p, uniform=None, all_greedy=False):
     if _on_gpu(logits):
         return cuda_ops().sample(logits, temperature, top_k, top_p, uniform, all_greedy)

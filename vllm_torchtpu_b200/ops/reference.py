@@ -294,3 +294,56 @@ def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0):
         y = (a @ w2[e].float().t()).to(x.dtype).float()
         out[rows] += y * wt[:, None]
     return out.to(x.dtype)
+
+
+# ---- MLA -------------------------------------------------------------------------
+def mla_write_cache(cache: torch.Tensor, kv_c: torch.Tensor, k_pe: torch.Tensor,
+                    slot_mapping: torch.Tensor) -> None:
+    """cache: [num_blocks, block_size, kv_lora + rope]; row = kv_c_normed ‖ k_pe
+    (reference: src/vllm_torchtpu/layers/adapter/attention.py:2718-2727)."""
+    bs = cache.shape[1]
+    valid = slot_mapping >= 0
+    slots = slot_mapping[valid].long()
+    row = torch.cat([kv_c[valid], k_pe[valid]], dim=-1).to(cache.dtype)
+    cache[slots // bs, slots % bs] = row
+
+
+def mla_paged_attention(q_latent, cache, block_tables, seq_lens, query_start_loc, scale, kv_lora_rank: int,
+                        *, num_reqs: Optional[int] = None, topk_indices: Optional[torch.Tensor] = None,
+                        return_lse: bool = False):
+    """Absorbed-query MLA: q_latent [T, H, kv_lora + rope] against latent rows; the value of a
+    row is its first ``kv_lora_rank`` dims.  Returns [T, H, kv_lora_rank].
+    ``topk_indices`` [T, K] (sparse MLA): each query attends only the listed positions (-1 = unused)."""
+    T, H, Dq = q_latent.shape
+    bs = cache.shape[1]
+    out = torch.zeros(T, H, kv_lora_rank, dtype=q_latent.dtype, device=q_latent.device)
+    lse = torch.full((T, H), float("-inf"), dtype=torch.float32, device=q_latent.device)
+    R = int(num_reqs if num_reqs is not None else seq_lens.shape[0])
+    qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
+    for r in range(R):
+        qs, qe = qsl[r], qsl[r + 1]
+        q_len, kv_len = qe - qs, sl[r]
+        if q_len <= 0 or kv_len <= 0:
+            continue
+        nblk = -(-kv_len // bs)
+        rows = cache[block_tables[r, :nblk].long()].reshape(nblk * bs, Dq)[:kv_len].float()
+        s = torch.einsum("qhd,kd->hqk", q_latent[qs:qe].float(), rows) * scale
+        qpos = torch.arange(kv_len - q_len, kv_len, device=s.device)[:, None]
+        kpos = torch.arange(kv_len, device=s.device)[None, :]
+        mask = kpos <= qpos
+        if topk_indices is not None:
+            sel = torch.zeros(q_len, kv_len, dtype=torch.bool, device=s.device)
+            idx = topk_indices[qs:qe].long()
+            ok = (idx >= 0) & (idx < kv_len)
+            sel.scatter_(1, idx.clamp(0, kv_len - 1), ok)
+            mask = mask & sel
+        s = s.masked_fill(~mask[None], float("-inf"))
+        l = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - l[..., None])
+        p = torch.where(torch.isfinite(l)[..., None], p, torch.zeros_like(p))
+        o = torch.einsum("hqk,kd->qhd", p, rows[:, :kv_lora_rank])
+        out[qs:qe] = o.to(out.dtype)
+        lse[qs:qe] = l.t()
+    if return_lse:
+        return out, lse
+    return out
