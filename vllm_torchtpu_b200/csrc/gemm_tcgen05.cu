@@ -34,15 +34,22 @@ constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int GROUP_N = 16;      // raster group: 16 weight tiles share activations in L2
 
-template <int BN>
+constexpr int MAX_GROUPS = 1024;  // experts per launch in grouped mode
+
+// NACC = 2: two weight tiles (gate rows, up rows) share one activation tile and the epilogue
+// writes silu(gate) * up, so a SwiGLU projection needs no separate activation kernel.
+template <int BN, int NACC>
 struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int STAGE_BYTES = NACC * A_BYTES + B_BYTES;
+  static constexpr int STAGES_RAW = 196608 / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int PREFIX_BYTES = (MAX_GROUPS + 1) * 4;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + PREFIX_BYTES + 1024;  // + alignment slack
+  static constexpr int TMEM_COLS = 2 * NACC * BN < 32 ? 32 : 2 * NACC * BN;
+  static_assert(TMEM_COLS <= 512, "accumulators exceed TMEM");
 };
 
 struct GemmParams {
@@ -54,6 +61,10 @@ struct GemmParams {
   int T, N, K, ldy;
   int n_tiles, t_tiles, splits, kb_total, kb_per_split;
   int w_evict_first;
+  // ---- SwiGLU pairs and grouped (per-expert) mode
+  int up_row_off;                        // NACC == 2: weight-row distance from a gate tile to its up tile
+  const int* group_off;                  // grouped: int[num_groups + 1] row offsets into X / Y (null = dense)
+  int num_groups, w_rows_per_group;      // grouped: weight rows of one expert
   // ---- fused cross-rank reduction over NVLink peer memory (world == 1: plain GEMM)
   int world, rank, ar_mode;              // ar_mode 0: all-reduce (sum lands on every rank), 1: reduce-scatter
   uint8_t* peer[8];                      // heap base of every rank (own heap at [rank])
@@ -100,12 +111,51 @@ __device__ __forceinline__ void decode_work(int w, const GemmParams& p, int& n_t
   t_tile = r / gsize;
 }
 
+struct Work {
+  int w_row, t_row, t_valid, n0, kb0, kb1, tile, split;
+};
+
+// dense: tiles rastered in groups of GROUP_N weight tiles; grouped: work = (token tile of an expert, n tile)
 template <int BN>
+__device__ __forceinline__ Work get_work(int w, const GemmParams& p, const int* s_prefix) {
+  Work k;
+  if (p.group_off == nullptr) {
+    int n_tile, t_tile;
+    decode_work(w, p, n_tile, t_tile, k.split, k.tile);
+    k.w_row = n_tile * BM;
+    k.n0 = n_tile * BM;
+    k.t_row = t_tile * BN;
+    k.t_valid = min(BN, p.T - k.t_row);
+    k.kb0 = k.split * p.kb_per_split;
+    k.kb1 = min(p.kb_total, k.kb0 + p.kb_per_split);
+  } else {
+    const int tt = w / p.n_tiles, n_tile = w - tt * p.n_tiles;
+    int lo = 0, hi = p.num_groups;                       // largest e with prefix[e] <= tt
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s_prefix[mid] <= tt) lo = mid; else hi = mid;
+    }
+    const int e = lo, t_tile = tt - s_prefix[e];
+    const int r0 = p.group_off[e], rows = p.group_off[e + 1] - r0;
+    k.w_row = e * p.w_rows_per_group + n_tile * BM;
+    k.n0 = n_tile * BM;
+    k.t_row = r0 + t_tile * BN;
+    k.t_valid = min(BN, rows - t_tile * BN);
+    k.kb0 = 0;
+    k.kb1 = p.kb_total;
+    k.tile = w;
+    k.split = 0;
+  }
+  return k;
+}
+
+template <int BN, int NACC>
 __global__ void __launch_bounds__(NUM_THREADS_FUSED, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  const GemmParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, NACC>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int ACC_COLS = NACC * BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
@@ -117,6 +167,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
   volatile int* red_ok = reinterpret_cast<volatile int*>(tmem_slot + 3);
+  int* s_prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES);
   const bool fused = p.world > 1;
   // every thread reads the epoch before any CTA of this launch can have bumped it
   const int epoch = fused ? (*reinterpret_cast<volatile int*>(p.epoch_ptr) + 1) : 0;
@@ -145,11 +196,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  if (p.group_off != nullptr) {
+    // token tiles per expert -> exclusive prefix (serial scan: at most MAX_GROUPS short steps)
+    for (int e = threadIdx.x; e < p.num_groups; e += blockDim.x)
+      s_prefix[e + 1] = (p.group_off[e + 1] - p.group_off[e] + BN - 1) / BN;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      s_prefix[0] = 0;
+      for (int e = 0; e < p.num_groups; ++e) s_prefix[e + 1] += s_prefix[e];
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total_work = p.n_tiles * p.t_tiles * p.splits;
+  const int total_work = p.group_off != nullptr ? s_prefix[p.num_groups] * p.n_tiles
+                                                : p.n_tiles * p.t_tiles * p.splits;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -159,19 +221,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       uint32_t armed = 0;       // bit s: stage s has a load whose completion nobody has consumed yet
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        int n_tile, t_tile, split, tile;
-        decode_work(w, p, n_tile, t_tile, split, tile);
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        const Work k = get_work<BN>(w, p, s_prefix);
+        for (int kb = k.kb0; kb < k.kb1; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* a = smem + s * Cfg::STAGE_BYTES;
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
-          if (p.w_evict_first)
-            tma_load_2d_hint(a, &tmW, &full[s], kb * BK, n_tile * BM, L2_EVICT_FIRST);
-          else
-            tma_load_2d(a, &tmW, &full[s], kb * BK, n_tile * BM);
-          tma_load_2d(a + Cfg::A_BYTES, &tmX, &full[s], kb * BK, t_tile * BN);
+          if (p.w_evict_first) {
+            tma_load_2d_hint(a, &tmW, &full[s], kb * BK, k.w_row, L2_EVICT_FIRST);
+            if (NACC == 2)
+              tma_load_2d_hint(a + Cfg::A_BYTES, &tmW, &full[s], kb * BK, k.w_row + p.up_row_off, L2_EVICT_FIRST);
+          } else {
+            tma_load_2d(a, &tmW, &full[s], kb * BK, k.w_row);
+            if (NACC == 2) tma_load_2d(a + Cfg::A_BYTES, &tmW, &full[s], kb * BK, k.w_row + p.up_row_off);
+          }
+          tma_load_2d(a + NACC * Cfg::A_BYTES, &tmX, &full[s], kb * BK, k.t_row);
           armed |= 1u << s;
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -191,25 +254,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       int iter = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
-        int n_tile, t_tile, split, tile;
-        decode_work(w, p, n_tile, t_tile, split, tile);
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        const Work wk = get_work<BN>(w, p, s_prefix);
+        const int kb0 = wk.kb0, kb1 = wk.kb1;
         const int acc = iter & 1;
         const uint32_t acc_ph = (iter >> 1) & 1;
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
           const uint64_t adesc = umma_desc_k_sw128(a_addr);
-          const uint64_t bdesc = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
+          const uint64_t a2desc = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
+          const uint64_t bdesc = umma_desc_k_sw128(a_addr + NACC * Cfg::A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // +32 bytes per K step inside the 128-byte swizzle atom (address field is >>4)
             umma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (NACC == 2)
+              umma_f16(d_tmem + BN, a2desc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty[s]);      // stage reusable once these MMAs have read it
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -223,17 +287,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const int row = q * 32 + lane;                // 0..127 inside the tile
     int iter = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++iter) {
-      int n_tile, t_tile, split, tile;
-      decode_work(w, p, n_tile, t_tile, split, tile);
+      const Work wk = get_work<BN>(w, p, s_prefix);
+      const int tile = wk.tile, split = wk.split;
       const int acc = iter & 1;
       const uint32_t acc_ph = (iter >> 1) & 1;
       if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
-      const int n = n_tile * BM + row;
-      const int t0 = t_tile * BN;
-      const int t_valid = min(BN, p.T - t0);
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      if (p.splits == 1) {
+      const int n = wk.n0 + row;
+      const int t0 = wk.t_row;
+      const int t_valid = wk.t_valid;
+      const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      if (NACC == 2) {
+        // SwiGLU: accumulator 0 holds the gate tile, accumulator 1 the up tile of the same columns
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (c0 >= t_valid) break;               // warp-uniform
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + c0, g);
+          tmem_ld_32x32(taddr + BN + c0, u);
+          tmem_ld_wait();
+          if (n < p.N) {
+            __nv_bfloat16* yp = dst_base + (size_t)(t0 + c0) * p.ldy + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (c0 + j < t_valid) {
+                const float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+                yp[(size_t)j * p.ldy] = __float2bfloat16(gv / (1.f + __expf(-gv)) * uv);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+      } else if (p.splits == 1) {
         const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -482,17 +569,18 @@ static int cached_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_
   return 0;
 }
 
-template <int BN>
+template <int BN, int NACC = 1>
 static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int grid,
                        cudaStream_t stream) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, NACC>;
   static bool attr_set = false;
   if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::SMEM));
+    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN, NACC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     attr_set = true;
   }
-  gemm_bf16_kernel<BN><<<grid, p.world > 1 ? NUM_THREADS_FUSED : NUM_THREADS, Cfg::SMEM, stream>>>(tmW, tmX, p);
+  gemm_bf16_kernel<BN, NACC><<<grid, p.world > 1 ? NUM_THREADS_FUSED : NUM_THREADS, Cfg::SMEM, stream>>>(
+      tmW, tmX, p);
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
@@ -644,6 +732,92 @@ extern "C" int b200_gemm_bf16_fused_reduce(const void* X, const void* W, int T, 
   if (rc) return rc;
   int total = tiles * p.splits;
   int grid = total < num_sms ? total : num_sms;
+  switch (bn) {
+    case 32: return launch_gemm<32>(tmW, tmX, p, grid, stream);
+    case 64: return launch_gemm<64>(tmW, tmX, p, grid, stream);
+    case 128: return launch_gemm<128>(tmW, tmX, p, grid, stream);
+    default: return launch_gemm<256>(tmW, tmX, p, grid, stream);
+  }
+}
+
+namespace b200 {
+static void init_params(GemmParams& p, void* Y, int T, int N, int K, int ldy, int bn, int* status) {
+  memset(&p, 0, sizeof(p));
+  p.world = 1;
+  p.Y = reinterpret_cast<__nv_bfloat16*>(Y);
+  p.status = status;
+  p.T = T; p.N = N; p.K = K; p.ldy = ldy;
+  p.n_tiles = (N + BM - 1) / BM;
+  p.t_tiles = (T + bn - 1) / bn;
+  p.kb_total = (K + BK - 1) / BK;
+  p.splits = 1;
+  p.kb_per_split = p.kb_total;
+}
+}  // namespace b200
+
+// Y[T, I] = silu(X * Wg^T) * (X * Wu^T) with W = [gate rows (I) ; up rows (I)] x K packed as [2I, K].
+extern "C" int b200_gemm_bf16_swiglu(const void* X, const void* W, void* Y, int T, int I, int K, int ldx,
+                                     int ldw, int ldy, int* status, int num_sms, cudaStream_t stream) {
+  using namespace b200;
+  if (T <= 0 || I <= 0 || K <= 0) return 0;
+  if (K % 8 || ldx % 8 || ldw % 8) {
+    b200_set_last_error("gemm_swiglu: K and row strides must be multiples of 8 elements", __FILE__, __LINE__);
+    return -3;
+  }
+  const int bn = T <= 32 ? 32 : (T <= 64 ? 64 : 128);
+  GemmParams p;
+  init_params(p, Y, T, I, K, ldy, bn, status);
+  p.up_row_off = I;
+  p.w_evict_first = (p.t_tiles == 1) ? 1 : 0;
+  CUtensorMap tmW, tmX;
+  int rc = cached_tmap(&tmW, W, (uint64_t)2 * I, (uint64_t)K, (uint64_t)ldw * 2, BM);
+  if (rc) return rc;
+  rc = cached_tmap(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn);
+  if (rc) return rc;
+  const int total = p.n_tiles * p.t_tiles;
+  const int grid = total < num_sms ? total : num_sms;
+  switch (bn) {
+    case 32: return launch_gemm<32, 2>(tmW, tmX, p, grid, stream);
+    case 64: return launch_gemm<64, 2>(tmW, tmX, p, grid, stream);
+    default: return launch_gemm<128, 2>(tmW, tmX, p, grid, stream);
+  }
+}
+
+// Grouped (per-expert) GEMM over rows sorted by expert:
+//   rows [group_off[e], group_off[e+1]) of X use weight W[e] ([N, K], or [2N, K] gate/up when swiglu).
+// X: [R, K]; Y: [R, N].  group_off lives in device memory, so the launch is CUDA-graph safe; the
+// grid is one persistent CTA per SM and CTAs without work exit.  avg_rows_hint picks the token tile.
+extern "C" int b200_grouped_gemm_bf16(const void* X, const void* W, void* Y, const int* group_off,
+                                      int num_groups, int R, int N, int K, int swiglu, int avg_rows_hint,
+                                      int* status, int num_sms, cudaStream_t stream) {
+  using namespace b200;
+  if (R <= 0 || N <= 0 || K <= 0 || num_groups <= 0) return 0;
+  if (K % 8 || N % BM || num_groups > MAX_GROUPS) {
+    b200_set_last_error("grouped_gemm: K % 8 == 0, N % 128 == 0 and <= 1024 groups required", __FILE__,
+                        __LINE__);
+    return -3;
+  }
+  int bn = avg_rows_hint <= 32 ? 32 : (avg_rows_hint <= 64 ? 64 : (avg_rows_hint <= 128 || swiglu ? 128 : 256));
+  GemmParams p;
+  init_params(p, Y, R, N, K, N, bn, status);
+  p.group_off = group_off;
+  p.num_groups = num_groups;
+  p.w_rows_per_group = swiglu ? 2 * N : N;
+  p.up_row_off = N;
+  p.w_evict_first = avg_rows_hint <= bn ? 1 : 0;
+  CUtensorMap tmW, tmX;
+  int rc = cached_tmap(&tmW, W, (uint64_t)num_groups * p.w_rows_per_group, (uint64_t)K, (uint64_t)K * 2, BM);
+  if (rc) return rc;
+  rc = cached_tmap(&tmX, X, (uint64_t)R, (uint64_t)K, (uint64_t)K * 2, (uint32_t)bn);
+  if (rc) return rc;
+  const int grid = num_sms;
+  if (swiglu) {
+    switch (bn) {
+      case 32: return launch_gemm<32, 2>(tmW, tmX, p, grid, stream);
+      case 64: return launch_gemm<64, 2>(tmW, tmX, p, grid, stream);
+      default: return launch_gemm<128, 2>(tmW, tmX, p, grid, stream);
+    }
+  }
   switch (bn) {
     case 32: return launch_gemm<32>(tmW, tmX, p, grid, stream);
     case 64: return launch_gemm<64>(tmW, tmX, p, grid, stream);

@@ -1,0 +1,159 @@
+"""Kernel micro-benchmarks with roofline fractions.
+
+    python -m vllm_torchtpu_b200.ops.bench_kernels gemm --T 64 --N 4096 --K 4096
+    python -m vllm_torchtpu_b200.ops.bench_kernels gemm-sweep
+    python -m vllm_torchtpu_b200.ops.bench_kernels attn-decode --reqs 64 --ctx 1100
+    python -m vllm_torchtpu_b200.ops.bench_kernels attn-prefill --reqs 8 --q 1024
+
+Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed
+(a 256 MB buffer is rewritten) before every timed launch, median of the timed
+launches.  Fractions are against the measured peaks in ``MEASURED_PEAKS.json`` at
+the repository root when that file exists, else the fallback figures below.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+
+FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"]}, "of measured"
+    return dict(FALLBACK), "of fallback"
+
+
+def time_fn(fn, iters: int = 20, warmup: int = 3, flush: bool = True) -> float:
+    from . import cuda
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            cuda.flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return statistics.median(ts)
+
+
+def bench_gemm(T, N, K, iters=20, impl="tcgen05", check=True) -> dict:
+    from . import cuda
+    pk, tag = peaks()
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    if impl == "tcgen05":
+        fn = lambda: cuda.gemm(x, w, out=y)
+    else:
+        fn = lambda: torch.matmul(x, w.t(), out=y)
+    ms = time_fn(fn, iters)
+    err = None
+    if check and impl == "tcgen05":
+        want = x.float() @ w.float().t()
+        err = float((y.float() - want).abs().max() / want.abs().max())
+    flops = 2.0 * T * N * K
+    byts = 2.0 * (T * K + N * K + T * N)
+    tf = flops / ms / 1e9
+    gbs = byts / ms / 1e6
+    t_roof = max(flops / (pk["bf16_tflops"] * 1e12), byts / (pk["hbm_gbs"] * 1e9)) * 1e3
+    bn, splits, _, _ = cuda.gemm_plan(T, N, K)
+    return {"op": "gemm", "impl": impl, "T": T, "N": N, "K": K, "ms": round(ms, 4), "tflops": round(tf, 1),
+            "gbs": round(gbs, 1), "roofline_ms": round(t_roof, 4), "frac_of_roofline": round(t_roof / ms, 3),
+            "peaks": tag, "bn": bn, "splits": splits, "rel_err": err, "status": cuda.check_status()}
+
+
+def bench_attn_decode(reqs, ctx, Hq=32, Hkv=8, D=128, iters=20) -> dict:
+    from ..runner.attn_metadata import AttentionMetadata
+    from . import cuda
+    pk, tag = peaks()
+    bs = 16
+    nblk_per = -(-ctx // bs)
+    nb = reqs * nblk_per + 1
+    cache = (torch.randn(nb, 2, Hkv, bs, D, device="cuda") * 0.5).bfloat16()
+    bt = (torch.randperm(nb - 1, device="cuda") + 1).to(torch.int32).view(reqs, nblk_per).contiguous()
+    q = torch.randn(reqs, Hq, D, device="cuda").bfloat16()
+    qsl = torch.arange(reqs + 1, device="cuda", dtype=torch.int32)
+    sl = torch.full((reqs,), ctx, device="cuda", dtype=torch.int32)
+    meta = AttentionMetadata(None, None, bt, sl, qsl, reqs, reqs, num_decode_reqs=reqs, max_seq_len=ctx,
+                             padded_num_reqs=reqs, padded_num_tokens=reqs)
+    fn = lambda: cuda.paged_attention(q, cache, meta, D ** -0.5)
+    ms = time_fn(fn, iters)
+    byts = reqs * ctx * 2 * Hkv * D * 2.0
+    gbs = byts / ms / 1e6
+    return {"op": "attn_decode", "reqs": reqs, "ctx": ctx, "Hq": Hq, "Hkv": Hkv, "ms": round(ms, 4),
+            "kv_gbs": round(gbs, 1), "frac_of_hbm": round(gbs / pk["hbm_gbs"], 3), "peaks": tag,
+            "splits": cuda.decode_splits(reqs, Hkv)}
+
+
+def bench_attn_prefill(reqs, qlen, Hq=32, Hkv=8, D=128, iters=10) -> dict:
+    from ..runner.attn_metadata import AttentionMetadata
+    from . import cuda
+    pk, tag = peaks()
+    bs = 16
+    nblk_per = -(-qlen // bs)
+    nb = reqs * nblk_per + 1
+    cache = (torch.randn(nb, 2, Hkv, bs, D, device="cuda") * 0.5).bfloat16()
+    bt = (torch.randperm(nb - 1, device="cuda") + 1).to(torch.int32).view(reqs, nblk_per).contiguous()
+    T = reqs * qlen
+    q = torch.randn(T, Hq, D, device="cuda").bfloat16()
+    qsl = (torch.arange(reqs + 1, device="cuda", dtype=torch.int32) * qlen)
+    sl = torch.full((reqs,), qlen, device="cuda", dtype=torch.int32)
+    meta = AttentionMetadata(None, None, bt, sl, qsl, reqs, T, num_decode_reqs=0, max_query_len=qlen,
+                             max_seq_len=qlen, padded_num_reqs=reqs, padded_num_tokens=T,
+                             query_start_loc_cpu=qsl.cpu().long())
+    fn = lambda: cuda.paged_attention(q, cache, meta, D ** -0.5)
+    ms = time_fn(fn, iters)
+    flops = reqs * Hq * 4.0 * D * qlen * qlen / 2
+    return {"op": "attn_prefill", "reqs": reqs, "q": qlen, "ms": round(ms, 4),
+            "tflops_causal": round(flops / ms / 1e9, 1),
+            "frac_of_bf16_peak": round(flops / ms / 1e9 / pk["bf16_tflops"], 3), "peaks": tag}
+
+
+LLAMA8B_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128256, 4096)]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "gemm-sweep", "attn-decode", "attn-prefill", "all"])
+    ap.add_argument("--T", type=int, default=64)
+    ap.add_argument("--N", type=int, default=4096)
+    ap.add_argument("--K", type=int, default=4096)
+    ap.add_argument("--reqs", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=1100)
+    ap.add_argument("--q", type=int, default=1024)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--impl", default="tcgen05", choices=["tcgen05", "cublas"])
+    a = ap.parse_args()
+    if a.what == "gemm":
+        print(json.dumps(bench_gemm(a.T, a.N, a.K, a.iters, a.impl)))
+    elif a.what in ("gemm-sweep", "all"):
+        for T in (64, 256, 1024, 8192):
+            for N, K in LLAMA8B_SHAPES:
+                if T == 8192 and N > 100000:
+                    continue
+                for impl in ("tcgen05", "cublas"):
+                    print(json.dumps(bench_gemm(T, N, K, max(5, a.iters // 2), impl, check=(T <= 1024))))
+    if a.what in ("attn-decode", "all"):
+        for reqs, ctx in ((a.reqs, a.ctx),) if a.what == "attn-decode" else ((64, 1100), (256, 2048), (8, 8000)):
+            print(json.dumps(bench_attn_decode(reqs, ctx, iters=a.iters)))
+    if a.what in ("attn-prefill", "all"):
+        for reqs, q in ((a.reqs, a.q),) if a.what == "attn-prefill" else ((8, 1024), (2, 4096)):
+            print(json.dumps(bench_attn_prefill(reqs, q, iters=max(5, a.iters // 2))))
+
+
+if __name__ == "__main__":
+    main()

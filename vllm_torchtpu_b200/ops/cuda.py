@@ -399,3 +399,7 @@ def p2p_all_reduce(x, heap):
     count_launch()
     x.copy_(stage[:n].view(x.shape))
     return x
+
+
+from .cuda_moe import (gemm_swiglu, grouped_gemm, moe_experts, moe_permute, moe_route,  # noqa: E402,F401
+                       moe_unpermute)
