@@ -169,10 +169,20 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
   const uint32_t wbase = smem_u32(smem) + warp * WARP_BYTES;
   const int* bt = p.block_tables + (size_t)r * p.max_blocks;
   const size_t head_stride = (size_t)p.block_size * D;          // one (k|v, head) slab of a page
+  // Block ids of this warp's page range are fetched 32 at a time (one per lane) and handed out by
+  // shuffle, so the address of a chunk never waits on a dependent global load.
+  const int page_lo = (cb0 << 4) / p.block_size;
+  const int page_hi = cb1 > cb0 ? (((cb1 << 4) - 1) / p.block_size) : page_lo - 1;
+  int bt_base = page_lo;
+  int bt_reg = (page_lo + lane <= page_hi) ? bt[page_lo + lane] : 0;
   auto issue = [&](int chunk, int stage) {
     const int tok = chunk << 4;
     const int page = tok / p.block_size, off = tok - page * p.block_size;
-    long long blk = bt[page];
+    if (page >= bt_base + 32) {                       // warp-uniform
+      bt_base = page;
+      bt_reg = (page + lane <= page_hi) ? bt[page + lane] : 0;
+    }
+    long long blk = __shfl_sync(0xffffffffu, bt_reg, page - bt_base);
     if (blk < 0 || blk >= p.num_blocks) blk = 0;
     const __nv_bfloat16* kp = p.kv + (((size_t)blk * 2 + 0) * p.Hkv + h) * head_stride + (size_t)off * D;
     const __nv_bfloat16* vp = p.kv + (((size_t)blk * 2 + 1) * p.Hkv + h) * head_stride + (size_t)off * D;

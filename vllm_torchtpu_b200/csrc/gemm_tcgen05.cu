@@ -372,14 +372,51 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*last_flag) {
           __threadfence();
-          const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+          // partial layout is [column c][row]: lane owns rows 4*lane..4*lane+3 (one float4 per split),
+          // warp q takes columns c = q, q+4, ...; four columns are in flight per iteration
           const float* base = p.ws + (size_t)tile * p.splits * (size_t)(BM * BN);
-          if (n < p.N) {
-            for (int c = 0; c < t_valid; ++c) {
-              float acc_v = 0.f;
-              for (int s2 = 0; s2 < p.splits; ++s2)
-                acc_v += __ldcg(base + (size_t)s2 * (BM * BN) + c * BM + row);
-              dst_base[(size_t)(t0 + c) * p.ldy + n] = __float2bfloat16(acc_v + bias);
+          const int n4 = wk.n0 + 4 * lane;
+          float b4[4] = {0.f, 0.f, 0.f, 0.f};
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (n4 + j < p.N) b4[j] = __bfloat162float(p.bias[n4 + j]);
+          }
+          const bool vec_ok = (n4 + 3 < p.N) && ((p.ldy & 3) == 0) &&
+                              ((reinterpret_cast<uintptr_t>(dst_base) & 7) == 0);
+          for (int c0 = q; c0 < t_valid; c0 += 16) {
+            float4 a4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) a4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s2 = 0; s2 < p.splits; ++s2) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int c = c0 + 4 * u;
+                if (c < t_valid) {
+                  const float4 v = __ldcg(reinterpret_cast<const float4*>(
+                      base + (size_t)s2 * (BM * BN) + (size_t)c * BM + 4 * lane));
+                  a4[u].x += v.x; a4[u].y += v.y; a4[u].z += v.z; a4[u].w += v.w;
+                }
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int c = c0 + 4 * u;
+              if (c >= t_valid) continue;
+              __nv_bfloat16* yp = dst_base + (size_t)(t0 + c) * p.ldy + n4;
+              if (vec_ok) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a4[u].x + b4[0], a4[u].y + b4[1]);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(a4[u].z + b4[2], a4[u].w + b4[3]);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(yp) = pk;
+              } else {
+                const float vals[4] = {a4[u].x, a4[u].y, a4[u].z, a4[u].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+              }
             }
           }
           if (threadIdx.x == 64) p.counters[tile] = 0;
