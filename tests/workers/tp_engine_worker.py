@@ -1,0 +1,38 @@
+"""Child process: the same prompts through a TP engine (fused NVLink plane or NCCL plane);
+rank 0 prints the generated tokens as JSON."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def main():
+    from vllm_torchtpu_b200 import SamplingParams
+    from vllm_torchtpu_b200.config import ModelConfig
+    from vllm_torchtpu_b200.engine.llm import LLM
+    from vllm_torchtpu_b200.ops import cuda
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    cfg = ModelConfig(name="tp-test", num_layers=2, hidden_size=1024, num_q_heads=8, num_kv_heads=8, head_dim=128,
+                      intermediate_size=2048, vocab_size=4096, max_model_len=512, dtype=torch.bfloat16)
+    llm = LLM(cfg, device="cuda", tensor_parallel_size=world, max_num_seqs=8, max_num_batched_tokens=256,
+              num_gpu_blocks_override=256, enforce_eager="--eager" in sys.argv)
+    rng = np.random.RandomState(0)
+    prompts = [rng.randint(0, 4096, size=n).tolist() for n in (8, 33, 70, 150)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    torch.cuda.synchronize()
+    status = cuda.check_status()
+    if int(os.environ.get("RANK", "0")) == 0:
+        print("RESULT " + json.dumps({"tokens": [o.outputs[0].token_ids for o in outs], "status": status}),
+              flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

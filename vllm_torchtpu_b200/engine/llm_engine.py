@@ -116,6 +116,10 @@ class LLMEngine:
             spec_next = self.spec.propose(out, sampled)
         finished = self.scheduler.update_from_output(out, sampled, spec_next)
         if self.connector is not None:
+            if finished:
+                # requests that just finished may have blocks to publish or store: do it now rather
+                # than at the next schedule(), which may never come
+                self.connector.worker.save_kv(self.connector.scheduler.build_connector_meta(None))
             for rid in self.connector.worker.get_finished_sending():
                 self.scheduler.free_delayed(rid)
         return finished

@@ -70,6 +70,7 @@ class Scheduler:
         self.async_mode = scheduler_config.async_scheduling
         self.stats = {"preemptions": 0, "prefix_hit_tokens": 0, "scheduled_tokens": 0}
         self._in_batch: set[str] = set()
+        self._delayed_blocks: dict = {}
 
     # ---- admission ---------------------------------------------------------
     def add_request(self, req: Request) -> None:
@@ -315,11 +316,15 @@ class Scheduler:
                 req.kv_transfer_params = params
         if not delay_free:
             self.kv.free(req)
+        else:
+            # the connector still needs the blocks; they are released by free_delayed()
+            self._delayed_blocks[req.request_id] = req.block_ids
+            req.block_ids = []
         self._in_batch.discard(req.request_id)
         self.finished_since_last.append(req.request_id)
 
     def free_delayed(self, request_id: str) -> None:
         """Called when a connector has finished sending a finished request's blocks."""
-        req = self.requests.get(request_id)
-        if req is not None and req.block_ids:
-            self.kv.free(req)
+        blocks = self._delayed_blocks.pop(request_id, None)
+        if blocks:
+            self.kv.pool.release(blocks)
