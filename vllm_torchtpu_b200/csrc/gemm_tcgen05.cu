@@ -62,6 +62,7 @@ struct GemmParams {
   int n_tiles, t_tiles, splits, kb_total, kb_per_split;
   int w_evict_first;
   // ---- SwiGLU pairs and grouped (per-expert) mode
+  int cluster_splitk;                    // splits of a tile form a thread-block cluster; reduce over DSMEM
   int up_row_off;                        // NACC == 2: weight-row distance from a gate tile to its up tile
   const int* group_off;                  // grouped: int[num_groups + 1] row offsets into X / Y (null = dense)
   int num_groups, w_rows_per_group;      // grouped: weight rows of one expert
@@ -349,6 +350,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             st_release_sys(flag, epoch);
           }
         }
+      } else if (p.cluster_splitk) {
+        // split-K inside a thread-block cluster: the partial stays on chip.  This CTA has exactly one
+        // work item, so the stage ring is free once the accumulator is complete; it is reused as the
+        // fp32 partial [column][row] that the other CTAs of the cluster read through DSMEM.
+        float* part = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (c0 >= t_valid) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) part[(c0 + j) * BM + row] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
       } else {
         float* wsp = p.ws + ((size_t)tile * p.splits + split) * (size_t)(BM * BN);
 #pragma unroll 1
@@ -442,6 +460,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     // buffer of every rank (all-reduce) or its own (reduce-scatter) and raises the tile's done flag
     // there.  Reads and writes of peer heaps are plain NVLink loads/stores.
     const int rt = threadIdx.x - NUM_THREADS;        // 0..127
+    if (p.cluster_splitk) {
+      // take part in both cluster barriers of the split-K reduction up front: the flags this role
+      // waits for are only raised after them
+      cluster_arrive_release();
+      cluster_wait_acquire();
+      cluster_arrive_release();
+      cluster_wait_acquire();
+    }
     const int tiles = p.n_tiles * p.t_tiles;
     const int* my_tile_flags = reinterpret_cast<const int*>(p.peer[p.rank] + p.tile_flag_off);
     int owned_idx = 0;
@@ -500,6 +526,61 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     for (int tile = blockIdx.x * 128 + rt; tile < tiles; tile += gridDim.x * 128) {
       if (p.ar_mode == 1 && tile % p.world != p.rank) continue;
       wait_flag_ge(done + tile, epoch, p.status, p.spin_limit);
+    }
+  }
+
+  if (p.cluster_splitk && warp < 6) {
+    // ---- cluster split-K reduction over distributed shared memory: CTA `rank` of the cluster sums
+    // columns c = rank, rank + S, ... of all S partials (fixed order) and writes them as bf16.
+    __syncwarp();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (warp >= 2 && warp < 6 && !*abort_flag && blockIdx.x < total_work) {
+      const Work wk = get_work<BN>(blockIdx.x, p, s_prefix);
+      const int q = warp & 3;
+      const uint32_t rank = cluster_ctarank();
+      const int S = p.splits;
+      const int n4 = wk.n0 + 4 * lane;
+      float b4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n4 + j < p.N) b4[j] = __bfloat162float(p.bias[n4 + j]);
+      }
+      const bool vec_ok = (n4 + 3 < p.N) && ((p.ldy & 3) == 0) &&
+                          ((reinterpret_cast<uintptr_t>(dst_base) & 7) == 0);
+      const uint32_t part_local = smem_u32(smem);
+      for (int c = (int)rank + S * q; c < wk.t_valid; c += 4 * S) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r2 = 0; r2 < S; ++r2) {
+          const float4 v = ld_dsmem_v4(mapa_shared(part_local + (uint32_t)((c * BM + 4 * lane) * 4), r2));
+          a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        __nv_bfloat16* yp = dst_base + (size_t)(wk.t_row + c) * p.ldy + n4;
+        if (vec_ok) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(a.x + b4[0], a.y + b4[1]);
+          __nv_bfloat162 hi = __floats2bfloat162_rn(a.z + b4[2], a.w + b4[3]);
+          uint2 pk;
+          pk.x = *reinterpret_cast<uint32_t*>(&lo);
+          pk.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(yp) = pk;
+        } else {
+          const float vals[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+        }
+      }
+      if (fused) __threadfence_system();
+    }
+    __syncwarp();
+    cluster_arrive_release();          // nobody leaves while its partial may still be read
+    cluster_wait_acquire();
+    if (fused && cluster_ctarank() == 0 && threadIdx.x == 64 && blockIdx.x < total_work) {
+      const Work wk = get_work<BN>(blockIdx.x, p, s_prefix);
+      int* flag = reinterpret_cast<int*>(p.peer[wk.tile % p.world] + p.tile_flag_off) +
+                  (size_t)p.rank * p.max_tiles + wk.tile;
+      st_release_sys(flag, epoch);
     }
   }
 
@@ -616,8 +697,24 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gem
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     attr_set = true;
   }
-  gemm_bf16_kernel<BN, NACC><<<grid, p.world > 1 ? NUM_THREADS_FUSED : NUM_THREADS, Cfg::SMEM, stream>>>(
-      tmW, tmX, p);
+  const int threads = p.world > 1 ? NUM_THREADS_FUSED : NUM_THREADS;
+  if (p.cluster_splitk) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, NACC>, tmW, tmX, p));
+    return 0;
+  }
+  gemm_bf16_kernel<BN, NACC><<<grid, threads, Cfg::SMEM, stream>>>(tmW, tmX, p);
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
@@ -636,7 +733,7 @@ extern "C" int b200_gemm_plan(int T, int N, int K, int num_sms, int* bn_out, int
     splits = num_sms / tiles;
     int max_by_k = kb_total / 8 > 0 ? kb_total / 8 : 1;    // at least 8 k-blocks (512 of K) per split
     if (splits > max_by_k) splits = max_by_k;
-    if (splits > 16) splits = 16;
+    if (splits > 8) splits = 8;       // one thread-block cluster per tile
     if (splits < 1) splits = 1;
   }
   *bn_out = bn;
@@ -688,13 +785,14 @@ extern "C" int b200_gemm_bf16(const void* X, const void* W, void* Y, const void*
     p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
   }
   p.w_evict_first = (p.t_tiles == 1) ? 1 : 0;
+  p.cluster_splitk = (p.splits > 1 && p.splits <= 8) ? 1 : 0;
   CUtensorMap tmW, tmX;
   int rc = cached_tmap(&tmW, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, BM);
   if (rc) return rc;
   rc = cached_tmap(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn);
   if (rc) return rc;
   int total = tiles * p.splits;
-  int grid = total < num_sms ? total : num_sms;
+  int grid = p.cluster_splitk ? total : (total < num_sms ? total : num_sms);
   switch (bn) {
     case 32: return launch_gemm<32>(tmW, tmX, p, grid, stream);
     case 64: return launch_gemm<64>(tmW, tmX, p, grid, stream);
@@ -755,6 +853,7 @@ extern "C" int b200_gemm_bf16_fused_reduce(const void* X, const void* W, int T, 
     p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
   }
   p.w_evict_first = (p.t_tiles == 1) ? 1 : 0;
+  p.cluster_splitk = (p.splits > 1 && p.splits <= 8) ? 1 : 0;
   p.world = world; p.rank = rank; p.ar_mode = mode;
   for (int i = 0; i < 8; ++i) p.peer[i] = i < world ? (uint8_t*)peers[i] : nullptr;
   p.part_off = part_off; p.out_off = out_off;
@@ -768,7 +867,7 @@ extern "C" int b200_gemm_bf16_fused_reduce(const void* X, const void* W, int T, 
   rc = cached_tmap(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn);
   if (rc) return rc;
   int total = tiles * p.splits;
-  int grid = total < num_sms ? total : num_sms;
+  int grid = p.cluster_splitk ? total : (total < num_sms ? total : num_sms);
   switch (bn) {
     case 32: return launch_gemm<32>(tmW, tmX, p, grid, stream);
     case 64: return launch_gemm<64>(tmW, tmX, p, grid, stream);

@@ -241,6 +241,16 @@ class ModelRunner:
         hidden, residual = self.model.forward(ids, meta, self.kv_caches, hidden=hidden0)
         rows = self._select_rows(hidden, residual, meta.logits_indices)
         h = self.model.finalize(*rows)
+        st = get_state()
+        if (self.is_cuda and all_greedy and st.tp.size > 1 and envs.B200_GREEDY_TOP_TOKENS
+                and self.model.vocab_shard is not None):
+            # vocab-parallel arg-max: exchange (value, index) pairs instead of gathering the logits
+            from ..ops import cuda_tp
+            from ..parallel.communicator import get_tp_comm
+            local = self.model.local_logits(h)
+            tokens = cuda_tp.greedy_top_tokens(local, get_tp_comm(), self.model.vocab_shard)
+            self._store_last_tokens(tokens, dv("batch_slots", R))
+            return tokens, local
         logits = self.model.compute_logits(h)
         if self.is_cuda:
             # noise comes from Philox inside the kernel, keyed by (seed, step counter in device memory)
