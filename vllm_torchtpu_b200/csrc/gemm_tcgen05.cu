@@ -687,6 +687,54 @@ static int cached_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_
   return 0;
 }
 
+// How many clusters of `splits` CTAs of this kernel can be resident at once (GPC granularity).
+template <int BN>
+static int max_active_clusters_t(int splits, int threads) {
+  using Cfg = GemmCfg<BN, 1>;
+  cudaFuncSetAttribute(gemm_bf16_kernel<BN, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits * 64);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = Cfg::SMEM;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<BN, 1>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+static int max_active_clusters(int bn, int splits, int threads) {
+  static int cache[4][9][2];
+  static bool init = false;
+  if (!init) { memset(cache, -1, sizeof(cache)); init = true; }
+  const int bi = bn == 32 ? 0 : (bn == 64 ? 1 : (bn == 128 ? 2 : 3));
+  const int ti = threads > NUM_THREADS ? 1 : 0;
+  if (splits < 2 || splits > 8) return 0;
+  int& c = cache[bi][splits][ti];
+  if (c < 0) {
+    switch (bn) {
+      case 32: c = max_active_clusters_t<32>(splits, threads); break;
+      case 64: c = max_active_clusters_t<64>(splits, threads); break;
+      case 128: c = max_active_clusters_t<128>(splits, threads); break;
+      default: c = max_active_clusters_t<256>(splits, threads); break;
+    }
+  }
+  return c;
+}
+// Largest split count <= want whose clusters (one per tile) are all resident in one wave.
+static int fit_cluster_splits(int want, int tiles, int bn, int threads) {
+  int s = want > 8 ? 8 : want;
+  while (s > 1 && max_active_clusters(bn, s, threads) < tiles) --s;
+  return s;
+}
+
 template <int BN, int NACC = 1>
 static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int grid,
                        cudaStream_t stream) {
@@ -777,6 +825,7 @@ extern "C" int b200_gemm_bf16(const void* X, const void* W, void* Y, const void*
     size_t req = (size_t)tiles * splits * BM * bn * sizeof(float);
     if (ws == nullptr || req > ws_bytes || counters == nullptr || tiles > counters_len) splits = 1;
   }
+  if (splits > 1 && force_splits <= 0) splits = fit_cluster_splits(splits, tiles, bn, NUM_THREADS);
   p.splits = splits;
   p.kb_per_split = (p.kb_total + splits - 1) / splits;
   // every split must own at least one k-block
@@ -846,6 +895,7 @@ extern "C" int b200_gemm_bf16_fused_reduce(const void* X, const void* W, int T, 
     size_t req = (size_t)tiles * splits * BM * bn * sizeof(float);
     if (ws == nullptr || req > ws_bytes || counters == nullptr || tiles > counters_len) splits = 1;
   }
+  if (splits > 1) splits = fit_cluster_splits(splits, tiles, bn, NUM_THREADS_FUSED);
   p.splits = splits;
   p.kb_per_split = (p.kb_total + splits - 1) / splits;
   while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= p.kb_total) {

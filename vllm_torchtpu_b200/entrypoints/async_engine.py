@@ -1,0 +1,118 @@
+"""Asynchronous front of the engine: a background thread runs the step loop, callers
+submit requests and await token streams.  The serving API and the proxy use it."""
+from __future__ import annotations
+
+import asyncio
+import queue
+import threading
+import time
+from dataclasses import dataclass
+from typing import AsyncIterator, Optional
+
+from ..engine.llm_engine import LLMEngine
+from ..logger import init_logger
+from ..sampling_params import SamplingParams
+
+logger = init_logger(__name__)
+
+
+@dataclass
+class StreamItem:
+    request_id: str
+    new_token_ids: list
+    finished: bool
+    finish_reason: Optional[str] = None
+    kv_transfer_params: Optional[dict] = None
+    error: Optional[str] = None
+    num_prompt_tokens: int = 0
+    num_cached_tokens: int = 0
+
+
+class AsyncEngine:
+    def __init__(self, engine: LLMEngine):
+        self.engine = engine
+        self._inbox: "queue.Queue" = queue.Queue()
+        self._streams: dict = {}
+        self._sent: dict = {}
+        self._stop = False
+        self._loop: Optional[asyncio.AbstractEventLoop] = None
+        self.metrics = {"requests": 0, "output_tokens": 0, "prompt_tokens": 0, "steps": 0,
+                        "ttft_sum": 0.0, "ttft_n": 0}
+        self._thread = threading.Thread(target=self._run, name="EngineLoop", daemon=True)
+        self._thread.start()
+
+    # ---- engine thread -------------------------------------------------------------
+    def _run(self):
+        eng = self.engine
+        while not self._stop:
+            try:
+                while True:
+                    kind, payload = self._inbox.get_nowait()
+                    if kind == "add":
+                        rid, toks, sp, kvp = payload
+                        try:
+                            eng.add_request(toks, sp, request_id=rid, kv_transfer_params=kvp)
+                        except Exception as e:       # noqa: BLE001 - reported to the caller
+                            self._emit(StreamItem(rid, [], True, "error", error=str(e)))
+                    elif kind == "abort":
+                        eng.abort_request(payload)
+            except queue.Empty:
+                pass
+            if not eng.has_unfinished():
+                time.sleep(0.001)
+                continue
+            finished = eng.step()
+            self.metrics["steps"] += 1
+            for rid in list(self._streams):
+                req = eng.scheduler.requests.get(rid)
+                if req is None:
+                    continue
+                sent = self._sent.get(rid, 0)
+                new = req.output_token_ids[sent:]
+                done = req.status.finished
+                if new or done:
+                    self._sent[rid] = sent + len(new)
+                    if sent == 0 and new and req.first_token_time:
+                        self.metrics["ttft_sum"] += req.first_token_time - req.arrival_time
+                        self.metrics["ttft_n"] += 1
+                    self.metrics["output_tokens"] += len(new)
+                    self._emit(StreamItem(rid, list(new), done, req.status.value if done else None,
+                                          req.kv_transfer_params if done else None, req.error,
+                                          req.num_prompt_tokens, req.num_cached_tokens))
+                    if done:
+                        eng.scheduler.requests.pop(rid, None)
+            del finished
+
+    def _emit(self, item: StreamItem):
+        q = self._streams.get(item.request_id)
+        if q is None:
+            return
+        if self._loop is not None:
+            self._loop.call_soon_threadsafe(q.put_nowait, item)
+        if item.finished:
+            self._streams.pop(item.request_id, None)
+            self._sent.pop(item.request_id, None)
+
+    # ---- caller side -----------------------------------------------------------------
+    async def generate(self, request_id: str, prompt_token_ids: list, sp: SamplingParams,
+                       kv_transfer_params: Optional[dict] = None) -> AsyncIterator[StreamItem]:
+        self._loop = asyncio.get_running_loop()
+        q: asyncio.Queue = asyncio.Queue()
+        self._streams[request_id] = q
+        self.metrics["requests"] += 1
+        self.metrics["prompt_tokens"] += len(prompt_token_ids)
+        self._inbox.put(("add", (request_id, list(prompt_token_ids), sp, kv_transfer_params)))
+        try:
+            while True:
+                item = await q.get()
+                yield item
+                if item.finished:
+                    return
+        finally:
+            if request_id in self._streams:
+                self._inbox.put(("abort", request_id))
+                self._streams.pop(request_id, None)
+
+    def shutdown(self):
+        self._stop = True
+        self._thread.join(timeout=2.0)

@@ -1,0 +1,168 @@
+"""OpenAI-compatible HTTP server.
+
+Routes: ``/v1/completions``, ``/v1/chat/completions`` (both with SSE streaming),
+``/v1/models``, ``/health``, ``/metrics`` (Prometheus text), ``/start_profile`` and
+``/stop_profile``.  ``kv_transfer_params`` is accepted in requests and returned in
+responses so the disaggregation proxy can chain a prefill and a decode instance
+(reference surface: README.md:63-82, docs/user_guide/disaggregated_serving.md:98-108).
+
+Prompts may be text (needs a tokenizer) or token-id lists; a model without a tokenizer
+answers with token ids rendered as text.
+"""
+from __future__ import annotations
+
+import json
+import time
+import uuid
+from typing import Optional
+
+from ..sampling_params import SamplingParams
+from .async_engine import AsyncEngine
+
+
+def _sampling_from_body(body: dict) -> SamplingParams:
+    return SamplingParams(
+        temperature=float(body.get("temperature", 1.0) if body.get("temperature") is not None else 1.0),
+        top_k=int(body.get("top_k", 0) or 0), top_p=float(body.get("top_p", 1.0) or 1.0),
+        max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
+        min_tokens=int(body.get("min_tokens", 0) or 0), ignore_eos=bool(body.get("ignore_eos", False)),
+        stop_token_ids=list(body.get("stop_token_ids") or []), logprobs=body.get("logprobs"),
+        seed=body.get("seed"), structured=body.get("structured_outputs") or body.get("guided") or None)
+
+
+def build_app(engine, model_name: str, tokenizer=None):
+    from fastapi import FastAPI, HTTPException, Request
+    from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+    app = FastAPI(title="b200 serving")
+    aeng = AsyncEngine(engine)
+    app.state.async_engine = aeng
+    profiler = {"active": None}
+
+    def encode(prompt) -> list:
+        if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
+            return prompt
+        if isinstance(prompt, list) and prompt and isinstance(prompt[0], list):
+            return prompt[0]
+        if tokenizer is None:
+            raise HTTPException(400, "this model has no tokenizer: send token ids")
+        return tokenizer.encode(prompt if isinstance(prompt, str) else prompt[0])
+
+    def decode(ids: list) -> str:
+        if tokenizer is None:
+            return " ".join(str(i) for i in ids)
+        return tokenizer.decode(ids)
+
+    def chat_prompt(messages: list) -> list:
+        if tokenizer is not None and hasattr(tokenizer, "apply_chat_template"):
+            return tokenizer.apply_chat_template(messages, add_generation_prompt=True, tokenize=True)
+        text = "\n".join(f"{m.get('role', 'user')}: {m.get('content', '')}" for m in messages) + "\nassistant:"
+        return encode(text)
+
+    async def run(body: dict, prompt_ids: list, chat: bool):
+        try:
+            sp = _sampling_from_body(body)
+            from ..platform import B200Platform
+            B200Platform.validate_request(sp)
+        except ValueError as e:
+            raise HTTPException(400, str(e))
+        rid = f"{'chatcmpl' if chat else 'cmpl'}-{uuid.uuid4().hex}"
+        created = int(time.time())
+        kvp = body.get("kv_transfer_params")
+        obj = "chat.completion" if chat else "text_completion"
+
+        def chunk_payload(text, finish, final_item=None):
+            choice = {"index": 0, "finish_reason": finish}
+            if chat:
+                choice["delta" if body.get("stream") else "message"] = {"role": "assistant", "content": text}
+            else:
+                choice["text"] = text
+            out = {"id": rid, "object": obj + (".chunk" if chat and body.get("stream") else ""),
+                   "created": created, "model": model_name, "choices": [choice]}
+            if final_item is not None:
+                out["usage"] = {"prompt_tokens": final_item.num_prompt_tokens,
+                                "completion_tokens": final_item_tokens[0],
+                                "total_tokens": final_item.num_prompt_tokens + final_item_tokens[0],
+                                "prompt_tokens_details": {"cached_tokens": final_item.num_cached_tokens}}
+                if final_item.kv_transfer_params:
+                    out["kv_transfer_params"] = final_item.kv_transfer_params
+            return out
+
+        final_item_tokens = [0]
+        if body.get("stream"):
+            async def sse():
+                async for item in aeng.generate(rid, prompt_ids, sp, kvp):
+                    final_item_tokens[0] += len(item.new_token_ids)
+                    if item.error:
+                        yield f"data: {json.dumps({'error': item.error})}\n\n"
+                        break
+                    payload = chunk_payload(decode(item.new_token_ids), item.finish_reason,
+                                            item if item.finished else None)
+                    yield f"data: {json.dumps(payload)}\n\n"
+                yield "data: [DONE]\n\n"
+            return StreamingResponse(sse(), media_type="text/event-stream")
+        toks, last = [], None
+        async for item in aeng.generate(rid, prompt_ids, sp, kvp):
+            toks += item.new_token_ids
+            last = item
+        if last is not None and last.error:
+            raise HTTPException(500, last.error)
+        final_item_tokens[0] = len(toks)
+        payload = chunk_payload(decode(toks), last.finish_reason if last else None, last)
+        payload["choices"][0]["token_ids"] = toks
+        return JSONResponse(payload)
+
+    @app.post("/v1/completions")
+    async def completions(request: Request):
+        body = await request.json()
+        return await run(body, encode(body.get("prompt", "")), chat=False)
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(request: Request):
+        body = await request.json()
+        return await run(body, chat_prompt(body.get("messages", [])), chat=True)
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "b200",
+                                            "max_model_len": engine.cfg.model.max_model_len}]}
+
+    @app.get("/health")
+    @app.get("/healthcheck")
+    async def health():
+        return {"status": "ok"}
+
+    @app.get("/metrics")
+    async def metrics():
+        m = aeng.metrics
+        sch = engine.scheduler
+        lines = [f"b200_requests_total {m['requests']}", f"b200_prompt_tokens_total {m['prompt_tokens']}",
+                 f"b200_generation_tokens_total {m['output_tokens']}", f"b200_engine_steps_total {m['steps']}",
+                 f"b200_num_requests_running {len(sch.running)}", f"b200_num_requests_waiting {len(sch.waiting)}",
+                 f"b200_kv_cache_usage {sch.kv.pool.usage:.6f}", f"b200_preemptions_total {sch.stats['preemptions']}",
+                 f"b200_prefix_cache_hit_tokens_total {sch.stats['prefix_hit_tokens']}"]
+        if m["ttft_n"]:
+            lines.append(f"b200_time_to_first_token_seconds_mean {m['ttft_sum'] / m['ttft_n']:.6f}")
+        return PlainTextResponse("\n".join(lines) + "\n")
+
+    @app.post("/start_profile")
+    async def start_profile(request: Request):
+        from ..tracing.profiler import start_profile as sp
+        body = await request.json() if await request.body() else {}
+        profiler["active"] = sp(body.get("prefix", ""))
+        return {"status": "started", "dir": profiler["active"].out_dir}
+
+    @app.post("/stop_profile")
+    async def stop_profile():
+        if profiler["active"] is None:
+            raise HTTPException(400, "no profile is running")
+        path = profiler["active"].stop()
+        profiler["active"] = None
+        return {"status": "stopped", "trace": path}
+
+    return app
+
+
+def serve(engine, model_name: str, tokenizer=None, host: str = "0.0.0.0", port: int = 8000):
+    import uvicorn
+    uvicorn.run(build_app(engine, model_name, tokenizer), host=host, port=port, log_level="warning")

@@ -32,18 +32,32 @@ def peaks() -> tuple[dict, str]:
     return dict(FALLBACK), "of fallback"
 
 
-def time_fn(fn, iters: int = 20, warmup: int = 3, flush: bool = True) -> float:
+def time_fn(fn, iters: int = 20, warmup: int = 3, flush: bool = True, use_graph: bool = True) -> float:
     from . import cuda
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    # the op is captured into a CUDA graph so that host launch latency (ctypes, Python) between the
+    # events does not count: small kernels would otherwise be timed as launch-bound
+    replay = fn
+    if use_graph:
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            fn()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        replay = g.replay
     ts = []
     for _ in range(iters):
         if flush:
             cuda.flush_l2()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        fn()
+        replay()
         b.record()
         torch.cuda.synchronize()
         ts.append(a.elapsed_time(b))

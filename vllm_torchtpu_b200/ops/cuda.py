@@ -216,9 +216,13 @@ def gemm_plan(T, N, K):
 def decode_splits(num_reqs: int, num_kv_heads: int) -> int:
     if envs.B200_ATTN_SPLIT_KV > 0:
         return envs.B200_ATTN_SPLIT_KV
-    target = 4 * _sms
-    s = -(-target // max(1, num_reqs * num_kv_heads))
-    return max(1, min(16, s))
+    # two CTAs are resident per SM.  Splitting costs a scratch round trip and a second merge, so the
+    # (request, kv head) pairs are split only when they cannot fill one wave of resident CTAs.
+    slots = 2 * _sms
+    pairs = max(1, num_reqs * num_kv_heads)
+    if pairs >= slots:
+        return 1
+    return max(1, min(16, slots // pairs))
 
 
 def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=None, sinks=None,
