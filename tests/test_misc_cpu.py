@@ -1,0 +1,81 @@
+"""Envs registry, env validation, profile options, phase classification, parallel layouts, CLI parsing."""
+import pytest
+
+from vllm_torchtpu_b200 import env_validation, envs
+from vllm_torchtpu_b200.parallel.state import dcp_groups, layout_ranks
+from vllm_torchtpu_b200.tracing.profiler import classify_phase, parse_profile_options
+
+
+def test_envs_typed_lazy_and_validated(monkeypatch):
+    assert envs.B200_FUSED_TP is True
+    monkeypatch.setenv("B200_FUSED_TP", "0")
+    assert envs.B200_FUSED_TP is True            # cached
+    envs.reset()
+    assert envs.B200_FUSED_TP is False
+    monkeypatch.setenv("B200_TP_COMM", "carrier-pigeon")
+    envs.reset()
+    with pytest.raises(ValueError):
+        envs.B200_TP_COMM
+    with pytest.raises(AttributeError):
+        envs.B200_DOES_NOT_EXIST
+    monkeypatch.setenv("B200_TOKEN_BUCKET_EXTRA", "48, 96")
+    envs.reset()
+    assert envs.B200_TOKEN_BUCKET_EXTRA == [48, 96]
+
+
+def test_env_validation_flags_typos():
+    unknown = env_validation.find_unknown({"B200_FUSED_TPP": "1", "B200_FUSED_TP": "1", "HOME": "/x"})
+    assert [u.name for u in unknown] == ["B200_FUSED_TPP"] and unknown[0].suggestion == "B200_FUSED_TP"
+    assert env_validation.validate_values({"B200_SYMM_HEAP_MB": "abc"})
+
+
+def test_profile_options_and_phases():
+    o = parse_profile_options("dir:/tmp/x;python:1;shapes:0")
+    assert o["dir"] == "/tmp/x" and o["python"] and not o["shapes"]
+    with pytest.raises(ValueError):
+        parse_profile_options("bogus:1")
+    assert classify_phase(900, 10) == "prefill_heavy" and classify_phase(0, 64) == "decode_heavy"
+    assert classify_phase(100, 100) == "balanced" and classify_phase(0, 0) == "idle"
+
+
+def test_rank_layouts():
+    lay = layout_ranks(16, tp=4, pp=2, dp=2)
+    assert lay["tp"][0] == [0, 1, 2, 3] and lay["pp"][0] == [0, 4] and lay["dp"][0] == [0, 8]
+    assert lay["ep"][0] == [0, 1, 2, 3, 8, 9, 10, 11]
+    assert dcp_groups([0, 1, 2, 3], 2) == [[0, 1], [2, 3]]
+    lay = layout_ranks(8, tp=2, pp=1, dp=2, pcp=2)
+    assert lay["pcp"][0] == [0, 2] and lay["tp"][1] == [2, 3]
+
+
+def test_cli_parses_vllm_style_flags():
+    import argparse
+    from vllm_torchtpu_b200.entrypoints.cli import add_engine_args
+    ap = argparse.ArgumentParser()
+    add_engine_args(ap)
+    a = ap.parse_args(["llama-3.1-8b", "-tp", "8", "--enable-expert-parallel", "--kv-cache-dtype", "fp8",
+                       "--kv-transfer-config", '{"kv_connector": "B200P2PConnector", "kv_role": "kv_producer"}',
+                       "--speculative-config", '{"method": "ngram", "num_speculative_tokens": 3}'])
+    assert a.tensor_parallel_size == 8 and a.kv_transfer_config["kv_role"] == "kv_producer"
+    assert a.speculative_config["method"] == "ngram"
+
+
+def test_platform_rejects_bad_configs():
+    from vllm_torchtpu_b200.config import EngineConfig, model_preset
+    from vllm_torchtpu_b200.platform import B200Platform
+    from vllm_torchtpu_b200.sampling_params import SamplingParams
+    cfg = EngineConfig(model=model_preset("tiny-llama"))
+    cfg.model.quantization = "int3"
+    with pytest.raises(ValueError):
+        cfg.finalize()
+    cfg = EngineConfig(model=model_preset("tiny-llama"))
+    cfg.parallel.tensor_parallel_size = 3
+    cfg.parallel.world_size = 3
+    with pytest.raises(ValueError):
+        cfg.finalize()
+    with pytest.raises(ValueError):
+        B200Platform.validate_request(SamplingParams(seed=1))
+    with pytest.raises(ValueError):
+        B200Platform.validate_request(SamplingParams(logprobs=-1))
+    cfg = EngineConfig(model=model_preset("tiny-llama"), kv_transfer={"kv_connector": "Nope"})
+    with pytest.raises(ValueError):
+        cfg.finalize()

@@ -32,6 +32,7 @@ class ScheduledRequest:
     samples: bool = True            # produces a token this step
     num_spec_tokens: int = 0
     new_block_ids: list = field(default_factory=list)
+    spec_token_ids: list = field(default_factory=list)
 
 
 @dataclass
@@ -227,7 +228,8 @@ class Scheduler:
         samples = end >= req.num_tokens_with_placeholders
         is_new = req.request_id not in self._in_batch
         self._in_batch.add(req.request_id)
-        return ScheduledRequest(req, n, start, is_new, samples, n_spec, new_blocks)
+        return ScheduledRequest(req, n, start, is_new, samples, n_spec, new_blocks,
+                                list(req.spec_token_ids[:n_spec]))
 
     def _update_after_schedule(self, out: SchedulerOutput) -> None:
         for s in out.scheduled:

@@ -52,8 +52,24 @@ class StepResult:
             self.event.synchronize()
         if self.tokens_host is None:
             return {}
-        toks = self.tokens_host[: self.num_reqs].tolist()
-        return {rid: [t] for rid, t, s in zip(self.req_ids, toks, self.samples) if s}
+        if not self.extra:
+            toks = self.tokens_host[: self.num_reqs].tolist()
+            return {rid: [t] for rid, t, s in zip(self.req_ids, toks, self.samples) if s}
+        # speculative verification: request i owns spec_k[i] + 1 consecutive rows of target tokens;
+        # a draft is kept while it equals the target's token at its position
+        from ..sample.rejection_sampler import greedy_accept
+        spec_k, drafts, stats = self.extra["spec_k"], self.extra["drafts"], self.extra["stats"]
+        rows = self.tokens_host[: int(spec_k.sum()) + self.num_reqs].tolist()
+        out, off = {}, 0
+        for rid, k, d, s in zip(self.req_ids, spec_k.tolist(), drafts, self.samples):
+            tgt = rows[off:off + k + 1]
+            off += k + 1
+            if s:
+                acc = greedy_accept(d, tgt)
+                out[rid] = acc
+                stats["spec_accepted"] = stats.get("spec_accepted", 0) + len(acc) - 1
+                stats["spec_drafted"] = stats.get("spec_drafted", 0) + k
+        return out
 
 
 class ModelRunner:
@@ -108,7 +124,7 @@ class ModelRunner:
         self.bufs_prefill = StepBuffers(self.max_tokens, self.max_reqs, mb, self.device)
         self.bufs_decode = StepBuffers(self.max_reqs, self.max_reqs, mb, self.device)
         self.last_tokens = torch.zeros(self.max_reqs, dtype=torch.int32, device=self.device)
-        self.tokens_host = [torch.zeros(self.max_reqs, dtype=torch.int32, pin_memory=self.is_cuda)
+        self.tokens_host = [torch.zeros(self.max_reqs * 9, dtype=torch.int32, pin_memory=self.is_cuda)
                             for _ in range(4)]
         self._tok_ring = 0
 
@@ -191,7 +207,23 @@ class ModelRunner:
             req_idx = np.repeat(np.arange(n), num_new)
             pos = starts[req_idx] + (np.arange(T) - qsl[req_idx])
         tslots = slots[req_idx]
-        known = pos < b.num_known[tslots]
+        spec_k = np.fromiter((len(s.spec_token_ids) for s in scheds), dtype=np.int64, count=n)
+        has_spec = bool(spec_k.any())
+        if has_spec:
+            # draft tokens are staged behind the known tokens of their row (not counted as known)
+            for i, s in enumerate(scheds):
+                if s.spec_token_ids:
+                    nk = int(b.num_known[slots[i]])
+                    b.token_ids[slots[i], nk:nk + len(s.spec_token_ids)] = s.spec_token_ids
+            known = pos < (b.num_known[tslots] + spec_k[req_idx])
+            rows = np.concatenate([np.arange(qsl[i + 1] - 1 - spec_k[i], qsl[i + 1]) for i in range(n)])
+            row_req = np.repeat(np.arange(n), spec_k + 1)
+        else:
+            known = pos < b.num_known[tslots]
+            rows, row_req = qsl[1:] - 1, np.arange(n)
+        L = len(rows)
+        L_pad = L if has_spec else R_pad
+        rslots = slots[row_req]
         ids = b.token_ids[tslots, np.minimum(pos, b.token_ids.shape[1] - 1)]
         blk = b.block_table[tslots, pos // self.block_size]
         slot_map = blk.astype(np.int64) * self.block_size + pos % self.block_size
@@ -203,11 +235,11 @@ class ModelRunner:
         v = hv("token_src", T_pad); v[:T] = np.where(known, -1, tslots); v[T:] = -1
         v = hv("query_start_loc", R_pad + 1); v[:n + 1] = qsl; v[n + 1:] = T
         v = hv("seq_lens", R_pad); v[:n] = starts + num_new; v[n:] = 0
-        v = hv("logits_indices", R_pad); v[:n] = qsl[1:] - 1; v[n:] = 0
-        v = hv("top_k", R_pad); v[:n] = b.top_k[slots]; v[n:] = 0
+        v = hv("logits_indices", L_pad); v[:L] = rows; v[L:] = 0
+        v = hv("top_k", L_pad); v[:L] = b.top_k[rslots]; v[L:] = 0
         v = hv("batch_slots", R_pad); v[:n] = slots; v[n:] = -1
-        v = hv("temperature", R_pad, np.float32); v[:n] = b.temperature[slots]; v[n:] = 0
-        v = hv("top_p", R_pad, np.float32); v[:n] = b.top_p[slots]; v[n:] = 1
+        v = hv("temperature", L_pad, np.float32); v[:L] = b.temperature[rslots]; v[L:] = 0
+        v = hv("top_p", L_pad, np.float32); v[:L] = b.top_p[rslots]; v[L:] = 1
         hv("rng_step").view(np.int64)[0] = self.stats["steps"]
         bufs.np_bt[:n] = b.block_table[slots]
         if R_pad > n:
@@ -217,7 +249,8 @@ class ModelRunner:
         return dict(scheds=scheds, n=n, T=T, R_pad=R_pad, T_pad=T_pad, num_decode=num_decode,
                     decode_only=decode_only, bufs=bufs, all_greedy=all_greedy,
                     max_q=int(num_new.max()) if n else 0, max_seq=int(seq_lens_np.max()) if n else 0,
-                    seq_lens_np=seq_lens_np, qsl_np=qsl)
+                    seq_lens_np=seq_lens_np, qsl_np=qsl, L=L, L_pad=L_pad, has_spec=has_spec,
+                    row_req=row_req, spec_k=spec_k)
 
     def _make_meta(self, p) -> AttentionMetadata:
         bufs, R, T = p["bufs"], p["R_pad"], p["T_pad"]
@@ -227,15 +260,18 @@ class ModelRunner:
             block_tables=bufs.dev_bt[:R], seq_lens=dv("seq_lens", R),
             query_start_loc=dv("query_start_loc", R + 1), num_reqs=p["n"], num_tokens=p["T"],
             num_decode_reqs=p["num_decode"], max_query_len=p["max_q"], max_seq_len=p["max_seq"],
-            logits_indices=dv("logits_indices", R),
+            logits_indices=dv("logits_indices", p.get("L_pad", R)),
             request_distribution=(p["num_decode"], p["num_decode"], p["n"]),
             padded_num_reqs=R, padded_num_tokens=T,
             seq_lens_cpu=torch.from_numpy(p["seq_lens_np"]), query_start_loc_cpu=torch.from_numpy(p["qsl_np"]))
 
     # --------------------------------------------------------------- forward
-    def _forward_and_sample(self, bufs, meta, T, R, all_greedy: bool):
-        """Everything that runs on the device for one step (also the captured region)."""
+    def _forward_and_sample(self, bufs, meta, T, R, all_greedy: bool, L=None):
+        """Everything that runs on the device for one step (also the captured region).
+        ``L`` = number of sampled rows when it differs from the request count (spec-verify steps)."""
         dv = bufs.dev_view
+        n_req_pad, verify = R, L is not None
+        R = L if verify else R
         ids = dv("input_ids", T)
         hidden0 = self._embed(ids, dv("token_src", T))
         hidden, residual = self.model.forward(ids, meta, self.kv_caches, hidden=hidden0)
@@ -249,7 +285,8 @@ class ModelRunner:
             from ..parallel.communicator import get_tp_comm
             local = self.model.local_logits(h)
             tokens = cuda_tp.greedy_top_tokens(local, get_tp_comm(), self.model.vocab_shard)
-            self._store_last_tokens(tokens, dv("batch_slots", R))
+            if not verify:
+                self._store_last_tokens(tokens, dv("batch_slots", n_req_pad))
             return tokens, local
         logits = self.model.compute_logits(h)
         if self.is_cuda:
@@ -263,7 +300,8 @@ class ModelRunner:
                 uniform = torch.rand(logits.shape, generator=self._gen, dtype=torch.float32)
             tokens = ops.sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
                                 dv("top_p", R, torch.float32), uniform, all_greedy).to(torch.int32)
-        self._store_last_tokens(tokens, dv("batch_slots", R))
+        if not verify:
+            self._store_last_tokens(tokens, dv("batch_slots", n_req_pad))
         return tokens, logits
 
     def _embed(self, ids, token_src):
@@ -318,7 +356,8 @@ class ModelRunner:
         else:
             from ..ops import launch_count
             c0 = launch_count()
-            tokens, _ = self._forward_and_sample(bufs, meta, T, R, p["all_greedy"])
+            tokens, _ = self._forward_and_sample(bufs, meta, T, R, p["all_greedy"],
+                                                 L=p["L_pad"] if p.get("has_spec") else None)
             self.launch_counter += launch_count() - c0
             self.stats["eager_steps"] += 1
         if ev0 is not None:
@@ -328,15 +367,20 @@ class ModelRunner:
         host = self.tokens_host[self._tok_ring]
         self._tok_ring = (self._tok_ring + 1) % len(self.tokens_host)
         ev = None
+        rows = p["L_pad"] if p.get("has_spec") else R
         if self.is_cuda:
-            host[:R].copy_(tokens[:R], non_blocking=True)
+            host[:rows].copy_(tokens[:rows], non_blocking=True)
             ev = torch.cuda.Event()
             ev.record()
         else:
-            host[:R] = tokens[:R]
-        self.stats["d2h_bytes"] += R * 4
-        return StepResult([s.request.request_id for s in p["scheds"]], [s.samples for s in p["scheds"]],
-                          host, ev, n, R * 4)
+            host[:rows] = tokens[:rows]
+        self.stats["d2h_bytes"] += rows * 4
+        res = StepResult([s.request.request_id for s in p["scheds"]], [s.samples for s in p["scheds"]],
+                         host, ev, n, rows * 4)
+        if p.get("has_spec"):
+            res.extra = {"spec_k": p["spec_k"], "drafts": [list(s.spec_token_ids) for s in p["scheds"]],
+                         "stats": self.stats}
+        return res
 
     def note_sampled(self, result: dict) -> None:
         """Host learnt the tokens of a finished step: extend the persistent rows."""

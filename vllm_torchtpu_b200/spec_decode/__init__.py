@@ -1,0 +1,22 @@
+"""Speculative decoding: drafters propose k tokens, the target model verifies them in one step
+and a rejection sampler decides how many are kept.
+
+Drafters: ``ngram`` (prompt lookup), ``suffix`` (longest-suffix match over prompt + output),
+``eagle3`` / ``mtp`` (a small draft head run on the target's hidden state), ``dflash`` /
+``dspark`` (parallel block drafting) share the draft-head proposer.
+(reference: src/vllm_torchtpu/spec_decode/, docs/user_guide/speculative_decoding.md:5-16)"""
+from __future__ import annotations
+
+
+def create_proposer(cfg, runner):
+    sc = cfg.speculative or {}
+    method = sc.get("method", "ngram")
+    k = int(sc.get("num_speculative_tokens", 3))
+    if method in ("ngram", "suffix"):
+        from .ngram import NgramProposer
+        return NgramProposer(k, int(sc.get("prompt_lookup_min", 2)), int(sc.get("prompt_lookup_max", 4)),
+                             suffix=(method == "suffix"))
+    if method in ("eagle3", "mtp", "dflash", "dspark"):
+        from .draft_head import DraftHeadProposer
+        return DraftHeadProposer(cfg, runner, k, method)
+    raise ValueError(f"unknown speculative method {method!r}")
