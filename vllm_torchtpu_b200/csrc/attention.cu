@@ -118,56 +118,16 @@ __device__ __forceinline__ void pv_16(float (*o)[4], const uint32_t* pa, uint32_
   }
 }
 
-// Padded-row variants for the decode kernel: rows are D*2 + 16 bytes apart, which spreads the eight
-// rows of an ldmatrix over all banks without a swizzle (the rows are written by bulk copies).
-template <int D>
-__device__ __forceinline__ void qk_16p(float s[2][4], const uint32_t (*qf)[4], uint32_t kbase, int lane) {
-  constexpr int ROWB = D * 2 + 16;
-  const int mi = lane >> 3, rr = lane & 7;
-  const uint32_t a0 = kbase + (uint32_t)(((mi >> 1) * 8 + rr) * ROWB + ((mi & 1) << 4));
-#pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks) {
-    uint32_t b[4];
-    ldsm_x4(b, a0 + ks * 32);
-    mma_bf16_16816(s[0], qf[ks], &b[0]);
-    mma_bf16_16816(s[1], qf[ks], &b[2]);
-  }
-}
-template <int D>
-__device__ __forceinline__ void pv_16p(float (*o)[4], const uint32_t* pa, uint32_t vbase, int lane) {
-  constexpr int ROWB = D * 2 + 16;
-  const int mi = lane >> 3, rr = lane & 7;
-  const uint32_t a0 = vbase + (uint32_t)(((mi & 1) * 8 + rr) * ROWB + ((mi >> 1) << 4));
-#pragma unroll
-  for (int np = 0; np < D / 16; ++np) {
-    uint32_t b[4];
-    ldsm_x4_t(b, a0 + np * 32);
-    mma_bf16_16816(o[2 * np], pa, &b[0]);
-    mma_bf16_16816(o[2 * np + 1], pa, &b[2]);
-  }
-}
-// one row (D bf16) global -> shared by the bulk-copy engine; completion is counted on `bar`
-__device__ __forceinline__ void bulk_copy_row(uint32_t dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      :
-      : "r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-      : "memory");
-}
-
 // ------------------------------------------------------------------------ decode
 template <int D>
 __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p) {
   constexpr int STAGES = 3;
-  constexpr int ROWB = D * 2 + 16;                // padded row
-  constexpr int PAGE_BYTES = 16 * ROWB;           // 16 tokens of K (or V)
+  constexpr int PAGE_BYTES = 16 * D * 2;          // 16 tokens of K (or V)
   constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
   constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float s_ml[4][16][2];
   __shared__ int s_last;
-  __shared__ __align__(8) uint64_t s_bar[4][STAGES];
-  __shared__ int s_abort;
 
   const int h = blockIdx.x, r = p.req_begin + blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -226,12 +186,9 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
     if (blk < 0 || blk >= p.num_blocks) blk = 0;
     const __nv_bfloat16* kp = p.kv + (((size_t)blk * 2 + 0) * p.Hkv + h) * head_stride + (size_t)off * D;
     const __nv_bfloat16* vp = p.kv + (((size_t)blk * 2 + 1) * p.Hkv + h) * head_stride + (size_t)off * D;
-    // lanes 0-15 copy the 16 K rows, lanes 16-31 the 16 V rows: one bulk copy per lane
     const uint32_t sb = wbase + stage * STAGE_BYTES;
-    if (lane == 0) mbar_expect_tx(&s_bar[warp][stage], 32 * D * 2);
-    __syncwarp();
-    const __nv_bfloat16* src = (lane < 16 ? kp : vp) + (size_t)(lane & 15) * D;
-    bulk_copy_row(sb + (uint32_t)(lane * ROWB), src, D * 2, &s_bar[warp][stage]);
+    load_rows_async<D, 32>(sb, kp, 16, lane);
+    load_rows_async<D, 32>(sb + PAGE_BYTES, vp, 16, lane);
   };
 
   float o[D / 8][4];
@@ -241,27 +198,21 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
   const int row0 = lane >> 2, row1 = row0 + 8;
   const int lim0 = ctx + row0 / G, lim1 = ctx + row1 / G;       // last visible key per row
 
-  if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s) mbar_init(&s_bar[warp][s], 1);
-    mbar_fence_init();
-  }
-  if (threadIdx.x == 0) s_abort = 0;
-  __syncwarp();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
     if (cb0 + s < cb1) issue(cb0 + s, s);
+    cp_async_commit();
   }
   for (int c = cb0; c < cb1; ++c) {
-    const int it = c - cb0;
-    const int stage = it % STAGES;
-    if (!mbar_wait(&s_bar[warp][stage], (uint32_t)((it / STAGES) & 1), &s_abort, nullptr, ST_TIMEOUT_FULL)) break;
-    __syncwarp();                                 // every lane is done with the stage refilled below
-    if (c + STAGES - 1 < cb1) issue(c + STAGES - 1, (it + STAGES - 1) % STAGES);
+    const int stage = (c - cb0) % STAGES;
+    cp_async_wait<STAGES - 2>();
+    __syncwarp();
+    if (c + STAGES - 1 < cb1) issue(c + STAGES - 1, (c - cb0 + STAGES - 1) % STAGES);
+    cp_async_commit();
 
     const uint32_t sb = wbase + stage * STAGE_BYTES;
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    qk_16p<D>(s, qf, sb, lane);
+    qk_16<D>(s, qf, sb, lane);
     const int tk = (c << 4) + 2 * (lane & 3);
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -304,8 +255,9 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
     }
     uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
                       pack_bf16(s[1][2], s[1][3])};
-    pv_16p<D>(o, pa, sb + PAGE_BYTES, lane);
+    pv_16<D>(o, pa, sb + PAGE_BYTES, lane);
   }
+  cp_async_wait<0>();
   // row sums over the 4 lanes that share a row
   l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
   l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
@@ -646,7 +598,7 @@ extern "C" int b200_attn_decode(const void* q, const void* kv, void* out, float*
   p.counters = counters;
   dim3 grid(Hkv, R, num_splits);
   if (D == 128) {
-    const int smem = 4 * 3 * 2 * 16 * (128 * 2 + 16);
+    const int smem = 4 * 3 * 2 * 16 * 128 * 2;
     static bool set = false;
     if (!set) {
       B200_CUDA_CHECK(cudaFuncSetAttribute(attn_decode_kernel<128>,
@@ -655,7 +607,7 @@ extern "C" int b200_attn_decode(const void* q, const void* kv, void* out, float*
     }
     attn_decode_kernel<128><<<grid, 128, smem, stream>>>(p);
   } else if (D == 64) {
-    const int smem = 4 * 3 * 2 * 16 * (64 * 2 + 16);
+    const int smem = 4 * 3 * 2 * 16 * 64 * 2 < 4 * 16 * 64 * 4 ? 4 * 16 * 64 * 4 : 4 * 3 * 2 * 16 * 64 * 2;
     static bool set = false;
     if (!set) {
       B200_CUDA_CHECK(cudaFuncSetAttribute(attn_decode_kernel<64>,

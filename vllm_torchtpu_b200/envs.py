@@ -61,7 +61,7 @@ _decl("B200_LOG_LEVEL", str, "INFO", "log level of the b200 logger",
 _decl("B200_BOUNDS_CHECK", bool, False,
       "use kernels built with index range checks that record the bad index in a status word")
 _decl("B200_KERNEL_LIB", str, "", "path of an alternative kernel .so (hot reload during development)")
-_decl("B200_SPIN_LIMIT", int, 200_000_000,
+_decl("B200_SPIN_LIMIT", int, 2_000_000,
       "iteration limit of every device-side flag wait before it reports TIMEOUT")
 # --- execution ---------------------------------------------------------------
 _decl("B200_CUDA_GRAPHS", bool, True, "capture decode steps per request bucket into CUDA graphs")
