@@ -23,3 +23,40 @@ def test_mla_moe_engine_matches_non_absorbed_dense_forward():
         for _ in range(6):
             toks.append(int(dense_mla_logits(model, toks)[-1].argmax()))
         assert o.outputs[0].token_ids == toks[len(p):]
+
+
+def _hf_cfg(arch, **kw):
+    d = {"architectures": [arch], "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4,
+         "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 512, "vocab_size": 1024,
+         "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 256, "torch_dtype": "float32"}
+    d.update(kw)
+    return d
+
+
+def test_safetensors_roundtrip_dense_and_moe(tmp_path):
+    from vllm_torchtpu_b200.models.loader import save_hf_checkpoint
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    for preset, hf in (("tiny-llama", _hf_cfg("LlamaForCausalLM")),
+                       ("tiny-moe", _hf_cfg("Qwen3MoeForCausalLM", num_experts=8, num_experts_per_tok=2,
+                                            moe_intermediate_size=128, norm_topk_prob=True))):
+        src = LLM(preset, device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+        want = [o.outputs[0].token_ids for o in src.generate(_prompts(), sp)]
+        d = tmp_path / preset
+        save_hf_checkpoint(src.engine.runner.model, str(d), hf)
+        dst = LLM(str(d), device="cpu", max_num_seqs=4, block_size=16, init_dist=False, dtype="float32")
+        got = [o.outputs[0].token_ids for o in dst.generate(_prompts(), sp)]
+        assert got == want, preset
+
+
+def test_hf_config_mapping():
+    from vllm_torchtpu_b200.config import ModelConfig
+    mc = ModelConfig.from_hf_dict({"architectures": ["DeepseekV3ForCausalLM"], "num_hidden_layers": 61,
+                                   "hidden_size": 7168, "num_attention_heads": 128, "vocab_size": 129280,
+                                   "n_routed_experts": 256, "num_experts_per_tok": 8, "moe_intermediate_size": 2048,
+                                   "n_shared_experts": 1, "first_k_dense_replace": 3, "scoring_func": "sigmoid",
+                                   "topk_method": "noaux_tc", "n_group": 8, "topk_group": 4, "kv_lora_rank": 512,
+                                   "q_lora_rank": 1536, "qk_nope_head_dim": 128, "qk_rope_head_dim": 64,
+                                   "v_head_dim": 128, "intermediate_size": 18432, "routed_scaling_factor": 2.5,
+                                   "quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}})
+    assert mc.architecture == "deepseek_v3" and mc.is_mla and mc.moe_score_bias and mc.quantization == "fp8_block"
+    assert mc.layer_is_moe(3) and not mc.layer_is_moe(2)

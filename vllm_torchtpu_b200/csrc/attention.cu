@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
   __shared__ float s_ml[4][16][2];
   __shared__ int s_last;
 
+  pdl_launch_dependents();      // o_proj may start and prefetch its weights while this grid drains
   const int h = blockIdx.x, r = p.req_begin + blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.Hq / p.Hkv;
@@ -368,6 +369,7 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_kernel(const AttnParams p
   constexpr int TILE_BYTES = BKV * D * 2;          // K (or V) chunk
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
   const int hq = blockIdx.x;
   const int G = p.Hq / p.Hkv;
   const int h = hq / G;

@@ -123,6 +123,7 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         "r"(z)
       : "memory");
 }
+constexpr uint64_t L2_EVICT_NORMAL = 0x1000000000000000ull;
 constexpr uint64_t L2_EVICT_FIRST = 0x12F0000000000000ull;
 constexpr uint64_t L2_EVICT_LAST = 0x14F0000000000000ull;
 
@@ -210,6 +211,15 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
 // kind::f8f6f4 with e4m3 operands (format 0), fp32 accumulate
 __host__ __device__ constexpr uint32_t umma_idesc_e4m3(int M, int N) {
   return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// ------------------------------------------------- programmatic dependent launch
+// wait: returns once every grid this launch depends on has completed and its writes are visible.
+// launch_dependents: lets the next kernel of the stream (if launched with the programmatic
+// attribute) start before this grid has finished.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // ------------------------------------------------- thread-block cluster / DSMEM

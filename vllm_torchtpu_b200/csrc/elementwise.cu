@@ -31,6 +31,7 @@ template <bool ADD>
 __global__ void rms_norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                                 const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int H,
                                 float eps) {
+  pdl_launch_dependents();      // the GEMM that follows may start and prefetch its weights now
   __shared__ float red[32];
   extern __shared__ __align__(16) uint8_t dyn[];
   bf16x8* row_cache = reinterpret_cast<bf16x8*>(dyn);     // the (summed) row, kept for the second pass

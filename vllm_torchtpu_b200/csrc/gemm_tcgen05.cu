@@ -197,6 +197,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
+  // Programmatic dependent launch: this grid may start while the previous kernel of the stream is
+  // still running.  Everything above touched only shared memory, TMEM and kernel parameters.
+  // Weights do not depend on the previous kernel, so in dense mode the producer prefetches weight
+  // tiles before it waits; every other thread waits here.  Grouped mode reads the expert offsets
+  // the previous kernel wrote, so all of it waits first.
+  const bool dense = p.group_off == nullptr;
+  pdl_launch_dependents();
+  if (!(dense && warp == 0)) pdl_wait();
   if (p.group_off != nullptr) {
     // token tiles per expert -> exclusive prefix (serial scan: at most MAX_GROUPS short steps)
     for (int e = threadIdx.x; e < p.num_groups; e += blockDim.x)
@@ -221,11 +229,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       uint32_t ph = 0;
       uint32_t armed = 0;       // bit s: stage s has a load whose completion nobody has consumed yet
       bool ok = true;
+      int npre = 0;             // weight tiles of the first work item already in flight (dense mode)
+      if (dense && (int)blockIdx.x < total_work) {
+        const Work k0 = get_work<BN>(blockIdx.x, p, s_prefix);
+        npre = min(STAGES, k0.kb1 - k0.kb0);
+        for (int i = 0; i < npre; ++i) {
+          uint8_t* a = smem + i * Cfg::STAGE_BYTES;
+          mbar_expect_tx(&full[i], Cfg::STAGE_BYTES);
+          tma_load_2d_hint(a, &tmW, &full[i], (k0.kb0 + i) * BK, k0.w_row,
+                           p.w_evict_first ? L2_EVICT_FIRST : L2_EVICT_NORMAL);
+          if (NACC == 2)
+            tma_load_2d_hint(a + Cfg::A_BYTES, &tmW, &full[i], (k0.kb0 + i) * BK, k0.w_row + p.up_row_off,
+                             p.w_evict_first ? L2_EVICT_FIRST : L2_EVICT_NORMAL);
+        }
+      }
+      if (dense) pdl_wait();
+      int issued = 0;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const Work k = get_work<BN>(w, p, s_prefix);
-        for (int kb = k.kb0; kb < k.kb1; ++kb) {
-          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+        for (int kb = k.kb0; kb < k.kb1; ++kb, ++issued) {
           uint8_t* a = smem + s * Cfg::STAGE_BYTES;
+          if (issued < npre) {
+            // barrier already armed and the weight tile already requested: add the activation tile
+            tma_load_2d(a + NACC * Cfg::A_BYTES, &tmX, &full[s], kb * BK, k.t_row);
+            armed |= 1u << s;
+            if (++s == STAGES) { s = 0; ph ^= 1; }
+            continue;
+          }
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
           if (p.w_evict_first) {
             tma_load_2d_hint(a, &tmW, &full[s], kb * BK, k.w_row, L2_EVICT_FIRST);
@@ -687,6 +718,8 @@ static int cached_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_
   return 0;
 }
 
+static int g_use_pdl = 1;
+
 // How many clusters of `splits` CTAs of this kernel can be resident at once (GPC granularity).
 template <int BN>
 static int max_active_clusters_t(int splits, int threads) {
@@ -746,23 +779,30 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gem
     attr_set = true;
   }
   const int threads = p.world > 1 ? NUM_THREADS_FUSED : NUM_THREADS;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = Cfg::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
   if (p.cluster_splitk) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(threads);
-    cfg.dynamicSmemBytes = Cfg::SMEM;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = p.splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, NACC>, tmW, tmX, p));
-    return 0;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = p.splits;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
   }
-  gemm_bf16_kernel<BN, NACC><<<grid, threads, Cfg::SMEM, stream>>>(tmW, tmX, p);
+  if (g_use_pdl) {
+    // let this grid start (and prefetch weights) while the previous kernel of the stream drains
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, NACC>, tmW, tmX, p));
+  return 0;
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
@@ -1011,3 +1051,5 @@ extern "C" int b200_grouped_gemm_bf16(const void* X, const void* W, void* Y, con
     default: return launch_gemm<256>(tmW, tmX, p, grid, stream);
   }
 }
+
+extern "C" void b200_set_pdl(int on) { b200::g_use_pdl = on ? 1 : 0; }
