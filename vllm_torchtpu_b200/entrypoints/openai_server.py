@@ -9,8 +9,6 @@ responses so the disaggregation proxy can chain a prefill and a decode instance
 Prompts may be text (needs a tokenizer) or token-id lists; a model without a tokenizer
 answers with token ids rendered as text.
 """
-from __future__ import annotations
-
 import json
 import time
 import uuid
