@@ -88,6 +88,13 @@ class LLMEngine:
             raise ValueError("empty prompt")
         rid = request_id or f"req-{self._next_id}"
         self._next_id += 1
+        if sp.structured:
+            if self.runner.structured is None:
+                from ..structured import StructuredDecodingManager
+                self.runner.structured = StructuredDecodingManager(self.cfg.model.vocab_size,
+                                                                   getattr(self, "vocab_strings", None),
+                                                                   self.eos_token_id)
+            self.runner.structured.add_request(rid, sp.structured)
         self.scheduler.add_request(Request(rid, list(prompt_token_ids), sp, self.eos_token_id,
                                            kv_transfer_params=kv_transfer_params))
         return rid
@@ -111,10 +118,15 @@ class LLMEngine:
     def _retire(self, out, res) -> list:
         sampled = res.get()
         self.runner.note_sampled(sampled)
+        if self.runner.structured is not None:
+            self.runner.structured.accept_tokens(sampled)
         spec_next = None
         if self.spec is not None and sampled:
             spec_next = self.spec.propose(out, sampled)
         finished = self.scheduler.update_from_output(out, sampled, spec_next)
+        if self.runner.structured is not None:
+            for r in finished:
+                self.runner.structured.remove_request(r.request_id)
         if self.connector is not None:
             if finished:
                 # requests that just finished may have blocks to publish or store: do it now rather

@@ -93,6 +93,8 @@ class ModelRunner:
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(self.mcfg.seed + 1234)
         self._stage_timers = None
+        self.structured = None           # StructuredDecodingManager when a request asks for it
+        self._step_bitmask = None
         self.timing_events = None        # list of (start, end) CUDA events per step when enabled
         if envs.B200_STAGE_TIMING and self.is_cuda:
             from ..tracing.stage_timing import RunnerStageTiming
@@ -289,6 +291,11 @@ class ModelRunner:
                 self._store_last_tokens(tokens, dv("batch_slots", n_req_pad))
             return tokens, local
         logits = self.model.compute_logits(h)
+        if self._step_bitmask is not None:
+            # structured decoding: tokens the grammars forbid get -inf before sampling
+            from ..structured import apply_token_bitmask
+            bm, rows = self._step_bitmask
+            apply_token_bitmask(logits, bm.to(logits.device), rows.to(logits.device))
         if self.is_cuda:
             # noise comes from Philox inside the kernel, keyed by (seed, step counter in device memory)
             tokens = ops.cuda_ops().sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
@@ -340,8 +347,13 @@ class ModelRunner:
         if self.timing_events is not None and self.is_cuda:
             ev0 = torch.cuda.Event(enable_timing=True)
             ev0.record()
+        self._step_bitmask = None
+        if self.structured is not None and self.structured.grammars:
+            bm, rows = self.structured.build_bitmask([s.request.request_id for s in p["scheds"]])
+            if bm is not None:
+                self._step_bitmask = (bm, rows)
         use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
-                     and envs.B200_CUDA_GRAPHS)
+                     and envs.B200_CUDA_GRAPHS and self._step_bitmask is None)
         if use_graph:
             key = (R, p["all_greedy"])
             g = self.graphs.get(key)
