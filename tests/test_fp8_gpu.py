@@ -1,0 +1,60 @@
+"""Block-scaled fp8 tcgen05 GEMM vs the fp32 statement of the same quantised computation."""
+import pytest
+import torch
+
+from vllm_torchtpu_b200.quantization import fp8 as q
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def cu():
+    from vllm_torchtpu_b200.ops import cuda
+    return cuda
+
+
+def test_quant_act_matches_reference():
+    x = (torch.randn(37, 640, device=DEV) * 3).bfloat16()
+    xq, xs = cu().quant_act_1x128(x)
+    rq, rs = q.quantize_act_1x128(x)
+    torch.testing.assert_close(xs, rs, rtol=1e-6, atol=0)
+    # e4m3 rounding of x/scale may differ by one ulp between the two conversions
+    assert (xq.float() - rq.float()).abs().max() <= 32.0
+    assert ((xq.float() * xs.repeat_interleave(128, 1)[:, :640]) - x.float()).abs().max() <= 0.07 * x.float().abs().max()
+
+
+@pytest.mark.parametrize("T,N,K", [(16, 256, 512), (64, 1280, 8192), (100, 384, 1024), (128, 7168, 2048),
+                                   (300, 1024, 640), (1, 128, 128)])
+def test_fp8_block_gemm(T, N, K):
+    g = torch.Generator(device=DEV).manual_seed(T + N)
+    x = torch.randn(T, K, device=DEV, generator=g).bfloat16()
+    w = torch.randn(N, K, device=DEV, generator=g) * 0.05
+    wq, ws = q.quantize_weight_block(w)
+    y = cu().fp8_block_gemm(x, wq, ws)
+    torch.cuda.synchronize()
+    assert cu().check_status() == 0
+    want = q.fp8_block_gemm_reference(x, wq, ws, out_dtype=torch.float32)
+    err = (y.float() - want).abs().max().item()
+    assert err <= 2e-2 * want.abs().max().item() + 1e-2, err
+
+
+def test_fp8_moe_experts():
+    from vllm_torchtpu_b200.ops import reference as ref
+    T, E, k, H, I = 50, 8, 2, 512, 256
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = torch.randn(T, H, device=DEV, generator=g).bfloat16()
+    w13 = torch.randn(E, 2 * I, H, device=DEV, generator=g) * 0.05
+    w2 = torch.randn(E, H, I, device=DEV, generator=g) * 0.05
+    q13 = [q.quantize_weight_block(w13[e]) for e in range(E)]
+    q2 = [q.quantize_weight_block(w2[e]) for e in range(E)]
+    w13q, s13 = torch.stack([a for a, _ in q13]), torch.stack([b for _, b in q13])
+    w2q, s2 = torch.stack([a for a, _ in q2]), torch.stack([b for _, b in q2])
+    ids, w = ref.moe_route(torch.randn(T, E, device=DEV, generator=g), k)
+    got = cu().moe_experts_fp8(x, w13q, s13, w2q, s2, ids, w, 0)
+    torch.cuda.synchronize()
+    assert cu().check_status() == 0
+    d13 = torch.stack([q.dequantize_weight_block(w13q[e], s13[e]) for e in range(E)]).bfloat16()
+    d2 = torch.stack([q.dequantize_weight_block(w2q[e], s2[e]) for e in range(E)]).bfloat16()
+    want = ref.moe_experts(x, d13, d2, ids, w, 0)
+    err = (got.float() - want.float()).abs().max().item()
+    assert err <= 6e-2 * want.float().abs().max().item() + 2e-2, err     # activations are fp8 in the kernel path

@@ -1,0 +1,496 @@
+// fp8 (e4m3) GEMM with 128x128 weight block scales and 1x128 activation scales on tcgen05.
+//
+//   Y[t, n] = sum_kb  ( sum_{k in block kb} Xq[t,k] * Wq[n,k] ) * xs[t,kb] * ws[n/128, kb]
+//
+// tcgen05.mma (kind::f8f6f4, fp32 accumulate) cannot apply a different scale to every 128-wide
+// K block inside one accumulation, so each K block is accumulated on its own in TMEM (two
+// partial buffers, ping-pong) and the four epilogue warps "promote" it: tcgen05.ld the partial,
+// multiply by the block's scale product and add into fp32 register accumulators while the tensor
+// core already works on the next block.  A weight tile is exactly one scale row (BM = 128), so
+// the weight scale is one scalar per (tile, K block); activation scales are one per column.
+// Layouts: Wq [N, K] e4m3 K-major (the checkpoint layout), ws [ceil(N/128), ceil(K/128)] fp32
+// (``weight_scale_inv``), Xq [T, K] e4m3, xs [T, ceil(K/128)] fp32 from the quantisation kernel
+// below.  Same orientation as the bf16 kernel: weight rows are the 128-row UMMA operand, tokens
+// are N (32/64/128), so decode batches keep full MMA rows.  Split-K runs as a thread-block
+// cluster with a DSMEM reduction; grouped (per-expert) mode takes device-side row offsets.
+//
+// Semantics of the reference's block-wise quantised matmul
+// (reference: src/vllm_torchtpu/layers/adapter/linear_common.py:69-133, kernels/megablox/gmm_v2.py).
+#include <cstring>
+
+#include "common.cuh"
+#include "gemm_tcgen05.h"
+
+namespace b200 {
+namespace f8 {
+
+constexpr int BM = 128;
+constexpr int BKB = 128;          // K elements (= bytes) per stage row: one scale block
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_GROUPS = 1024;
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BKB;
+  static constexpr int B_BYTES = BN * BKB;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES_RAW = 180224 / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int PREFIX_BYTES = (MAX_GROUPS + 1) * 4;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + PREFIX_BYTES + 1024;
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static_assert(BM * BN * 4 <= STAGES * STAGE_BYTES, "split-K partial must fit in the stage ring");
+};
+
+struct Params {
+  __nv_bfloat16* Y;
+  const __nv_bfloat16* bias;
+  const float* w_scale;
+  const float* x_scale;
+  int* status;
+  int T, N, K, ldy;
+  int n_tiles, t_tiles, kb_total, splits, kb_per_split;
+  int ws_ld, xs_ld;                 // row strides of the scale matrices
+  int cluster_splitk;
+  const int* group_off;             // grouped: int[num_groups + 1]
+  int num_groups, w_rows_per_group, ws_rows_per_group;
+};
+
+struct Work {
+  int w_row, ws_row, t_row, t_valid, n0, kb0, kb1;
+};
+
+template <int BN>
+__device__ __forceinline__ Work get_work(int w, const Params& p, const int* s_prefix) {
+  Work k;
+  if (p.group_off == nullptr) {
+    const int tile = w / p.splits, split = w - tile * p.splits;
+    const int n_tile = tile % p.n_tiles, t_tile = tile / p.n_tiles;
+    k.w_row = n_tile * BM;
+    k.ws_row = n_tile;
+    k.n0 = n_tile * BM;
+    k.t_row = t_tile * BN;
+    k.t_valid = min(BN, p.T - k.t_row);
+    k.kb0 = split * p.kb_per_split;
+    k.kb1 = min(p.kb_total, k.kb0 + p.kb_per_split);
+  } else {
+    const int tt = w / p.n_tiles, n_tile = w - tt * p.n_tiles;
+    int lo = 0, hi = p.num_groups;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s_prefix[mid] <= tt) lo = mid; else hi = mid;
+    }
+    const int e = lo, t_tile = tt - s_prefix[e];
+    const int r0 = p.group_off[e], rows = p.group_off[e + 1] - r0;
+    k.w_row = e * p.w_rows_per_group + n_tile * BM;
+    k.ws_row = e * p.ws_rows_per_group + n_tile;
+    k.n0 = n_tile * BM;
+    k.t_row = r0 + t_tile * BN;
+    k.t_valid = min(BN, rows - t_tile * BN);
+    k.kb0 = 0;
+    k.kb1 = p.kb_total;
+  }
+  return k;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                      const Params p) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* pfull = bars + 2 * STAGES;
+  uint64_t* pempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_prefix = reinterpret_cast<int*>(smem + STAGES * C::STAGE_BYTES + C::BAR_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&pfull[0], 1);
+    mbar_init(&pfull[1], 1);
+    mbar_init(&pempty[0], 4);
+    mbar_init(&pempty[1], 4);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  if (p.group_off != nullptr) {
+    for (int e = threadIdx.x; e < p.num_groups; e += blockDim.x)
+      s_prefix[e + 1] = (p.group_off[e + 1] - p.group_off[e] + BN - 1) / BN;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      s_prefix[0] = 0;
+      for (int e = 0; e < p.num_groups; ++e) s_prefix[e + 1] += s_prefix[e];
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_work = p.group_off != nullptr ? s_prefix[p.num_groups] * p.n_tiles
+                                                : p.n_tiles * p.t_tiles * p.splits;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const Work k = get_work<BN>(w, p, s_prefix);
+        for (int kb = k.kb0; kb < k.kb1; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* a = smem + s * C::STAGE_BYTES;
+          mbar_expect_tx(&full[s], C::STAGE_BYTES);
+          tma_load_2d(a, &tmW, &full[s], kb * BKB, k.w_row);
+          tma_load_2d(a + C::A_BYTES, &tmX, &full[s], kb * BKB, k.t_row);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (*abort_flag)
+        for (int it = 0; it < 20000; ++it) __nanosleep(100);
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_e4m3(BM, BN);
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t pc = 0;                         // K blocks issued by this CTA (selects the partial buffer)
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const Work k = get_work<BN>(w, p, s_prefix);
+        for (int kb = k.kb0; kb < k.kb1; ++kb, ++pc) {
+          const int pb = pc & 1;
+          if (!mbar_wait(&pempty[pb], ((pc >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint64_t adesc = umma_desc_k_sw128(a_addr);
+          const uint64_t bdesc = umma_desc_k_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)          // 4 x (K = 32 fp8) per 128-byte row; a fresh sum per block
+            umma_f8(tmem_base + pb * BN, adesc + 2 * q, bdesc + 2 * q, idesc, q > 0 ? 1u : 0u);
+          umma_commit(&empty[s]);
+          umma_commit(&pfull[pb]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    uint32_t pc = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      const Work k = get_work<BN>(w, p, s_prefix);
+      float acc[BN];
+#pragma unroll
+      for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+      for (int kb = k.kb0; kb < k.kb1; ++kb, ++pc) {
+        const int pb = pc & 1;
+        const float sw = p.w_scale[(size_t)k.ws_row * p.ws_ld + kb];
+        if (!mbar_wait(&pfull[pb], (pc >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + pb * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          // lane j fetches the activation scale of column c0 + j; it is handed round by shuffle
+          const int t = k.t_row + c0 + lane;
+          const float mine = (c0 + lane < k.t_valid) ? sw * p.x_scale[(size_t)t * p.xs_ld + kb] : 0.f;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            acc[c0 + j] = fmaf(__uint_as_float(r[j]), __shfl_sync(0xffffffffu, mine, j), acc[c0 + j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pempty[pb]);
+      }
+      if (!ok) break;
+      const int n = k.n0 + row;
+      if (p.cluster_splitk) {
+        float* part = reinterpret_cast<float*>(smem);      // ring is idle: this CTA has one work item
+#pragma unroll
+        for (int c = 0; c < BN; ++c) part[c * BM + row] = acc[c];
+      } else if (n < p.N) {
+        const float bias = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;
+        __nv_bfloat16* yp = p.Y + (size_t)k.t_row * p.ldy + n;
+#pragma unroll
+        for (int c = 0; c < BN; ++c)
+          if (c < k.t_valid) yp[(size_t)c * p.ldy] = __float2bfloat16(acc[c] + bias);
+      }
+    }
+  }
+
+  if (p.cluster_splitk) {
+    __syncwarp();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (warp >= 2 && !*abort_flag && (int)blockIdx.x < total_work) {
+      const Work k = get_work<BN>(blockIdx.x, p, s_prefix);
+      const int q = warp & 3;
+      const uint32_t rank = cluster_ctarank();
+      const int S = p.splits;
+      const int n4 = k.n0 + 4 * lane;
+      float b4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n4 + j < p.N) b4[j] = __bfloat162float(p.bias[n4 + j]);
+      }
+      const uint32_t part_local = smem_u32(smem);
+      for (int c = (int)rank + S * q; c < k.t_valid; c += 4 * S) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r2 = 0; r2 < S; ++r2) {
+          const float4 v = ld_dsmem_v4(mapa_shared(part_local + (uint32_t)((c * BM + 4 * lane) * 4), r2));
+          a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        const float vals[4] = {a.x, a.y, a.z, a.w};
+        __nv_bfloat16* yp = p.Y + (size_t)(k.t_row + c) * p.ldy + n4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+      }
+    }
+    __syncwarp();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// x [T, K] bf16 -> xq [T, K] e4m3 and xs [T, ceil(K/128)] fp32: one warp per (row, 128-column group)
+__global__ void quant_act_1x128_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_e4m3* __restrict__ xq,
+                                       float* __restrict__ xs, int T, int K, int ldx, int groups) {
+  pdl_launch_dependents();
+  const int warps_per_block = blockDim.x >> 5;
+  const long long gw = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (gw >= (long long)T * groups) return;
+  const int t = (int)(gw / groups), g = (int)(gw % groups);
+  const int c0 = g * 128 + lane * 4;
+  float v[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = (c0 + j < K) ? __bfloat162float(x[(size_t)t * ldx + c0 + j]) : 0.f;
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  amax = warp_max(amax);
+  const float scale = fmaxf(amax, 1e-12f) / 448.f;
+  const float inv = 1.f / scale;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (c0 + j < K) xq[(size_t)t * K + c0 + j] = __nv_fp8_e4m3(fminf(fmaxf(v[j] * inv, -448.f), 448.f));
+  if (lane == 0) xs[(size_t)t * groups + g] = scale;
+}
+
+template <int BN>
+static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int grid,
+                  cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_block_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::SMEM));
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = C::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (p.cluster_splitk) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = p.splits;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[na].val.programmaticStreamSerializationAllowed = 1;
+  ++na;
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_fp8_block_kernel<BN>, tmW, tmX, p));
+  return 0;
+}
+
+template <int BN>
+static int max_clusters(int splits) {
+  using C = Cfg<BN>;
+  cudaFuncSetAttribute(gemm_fp8_block_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits * 64);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = C::SMEM;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_fp8_block_kernel<BN>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+static int fit_splits(int want, int tiles, int bn) {
+  static int cache[3][9];
+  static bool init = false;
+  if (!init) { memset(cache, -1, sizeof(cache)); init = true; }
+  int s = want > 8 ? 8 : want;
+  const int bi = bn == 32 ? 0 : (bn == 64 ? 1 : 2);
+  while (s > 1) {
+    int& c = cache[bi][s];
+    if (c < 0) c = bn == 32 ? max_clusters<32>(s) : (bn == 64 ? max_clusters<64>(s) : max_clusters<128>(s));
+    if (c >= tiles) break;
+    --s;
+  }
+  return s;
+}
+
+}  // namespace f8
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_quant_act_1x128(const void* x, void* xq, float* xs, int T, int K, int ldx,
+                                    cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int groups = (K + 127) / 128;
+  const long long warps = (long long)T * groups;
+  const int blocks = (int)((warps + 7) / 8);
+  f8::quant_act_1x128_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_fp8_e4m3*)xq, xs, T, K,
+                                                         ldx, groups);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+static int fp8_common(f8::Params& p, const void* Xq, const void* Wq, int rowsW, int rowsX, int bn, int K,
+                      CUtensorMap* tmW, CUtensorMap* tmX) {
+  if (K % 16) {
+    b200_set_last_error("gemm_fp8_block: K must be a multiple of 16", __FILE__, __LINE__);
+    return -3;
+  }
+  int rc = b200_make_tmap_2d(tmW, Wq, 1, (uint64_t)rowsW, (uint64_t)K, (uint64_t)K, f8::BM, f8::BKB);
+  if (rc) return rc;
+  return b200_make_tmap_2d(tmX, Xq, 1, (uint64_t)rowsX, (uint64_t)K, (uint64_t)K, (uint32_t)bn, f8::BKB);
+}
+
+// Y[T,N] bf16 = dequant(Xq, xs) * dequant(Wq, ws)^T (+bias).  Xq [T,K], Wq [N,K] contiguous e4m3;
+// xs [T, ceil(K/128)], ws [ceil(N/128), ceil(K/128)] fp32.
+extern "C" int b200_gemm_fp8_block(const void* Xq, const float* xs, const void* Wq, const float* ws, void* Y,
+                                   const void* bias, int T, int N, int K, int ldy, int* status, int num_sms,
+                                   cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  const int bn = T <= 32 ? 32 : (T <= 64 ? 64 : 128);
+  f8::Params p;
+  memset(&p, 0, sizeof(p));
+  p.Y = (__nv_bfloat16*)Y;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.w_scale = ws;
+  p.x_scale = xs;
+  p.status = status;
+  p.T = T; p.N = N; p.K = K; p.ldy = ldy;
+  p.n_tiles = (N + f8::BM - 1) / f8::BM;
+  p.t_tiles = (T + bn - 1) / bn;
+  p.kb_total = (K + f8::BKB - 1) / f8::BKB;
+  p.ws_ld = p.kb_total;
+  p.xs_ld = p.kb_total;
+  const int tiles = p.n_tiles * p.t_tiles;
+  int splits = 1;
+  if (tiles * 2 <= num_sms) {
+    splits = num_sms / tiles;
+    const int by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;
+    if (splits > by_k) splits = by_k;
+    if (splits > 1) splits = f8::fit_splits(splits, tiles, bn);
+  }
+  p.splits = splits;
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= p.kb_total) {
+    --p.splits;
+    p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+  }
+  p.cluster_splitk = p.splits > 1 ? 1 : 0;
+  CUtensorMap tmW, tmX;
+  int rc = fp8_common(p, Xq, Wq, N, T, bn, K, &tmW, &tmX);
+  if (rc) return rc;
+  const int total = tiles * p.splits;
+  const int grid = p.cluster_splitk ? total : (total < num_sms ? total : num_sms);
+  switch (bn) {
+    case 32: return f8::launch<32>(tmW, tmX, p, grid, stream);
+    case 64: return f8::launch<64>(tmW, tmX, p, grid, stream);
+    default: return f8::launch<128>(tmW, tmX, p, grid, stream);
+  }
+}
+
+// Grouped variant: rows [group_off[e], group_off[e+1]) of Xq use expert e's Wq [N,K] and scale grid
+// [ceil(N/128), ceil(K/128)].
+extern "C" int b200_grouped_gemm_fp8_block(const void* Xq, const float* xs, const void* Wq, const float* ws,
+                                           void* Y, const int* group_off, int num_groups, int R, int N, int K,
+                                           int avg_rows_hint, int* status, int num_sms, cudaStream_t stream) {
+  if (R <= 0 || N <= 0 || K <= 0 || num_groups <= 0) return 0;
+  if (N % f8::BM || num_groups > f8::MAX_GROUPS) {
+    b200_set_last_error("grouped_gemm_fp8: N % 128 == 0 and <= 1024 groups required", __FILE__, __LINE__);
+    return -3;
+  }
+  const int bn = avg_rows_hint <= 32 ? 32 : (avg_rows_hint <= 64 ? 64 : 128);
+  f8::Params p;
+  memset(&p, 0, sizeof(p));
+  p.Y = (__nv_bfloat16*)Y;
+  p.w_scale = ws;
+  p.x_scale = xs;
+  p.status = status;
+  p.T = R; p.N = N; p.K = K; p.ldy = N;
+  p.n_tiles = N / f8::BM;
+  p.t_tiles = (R + bn - 1) / bn;
+  p.kb_total = (K + f8::BKB - 1) / f8::BKB;
+  p.ws_ld = p.kb_total;
+  p.xs_ld = p.kb_total;
+  p.splits = 1;
+  p.kb_per_split = p.kb_total;
+  p.group_off = group_off;
+  p.num_groups = num_groups;
+  p.w_rows_per_group = N;
+  p.ws_rows_per_group = N / f8::BM;
+  CUtensorMap tmW, tmX;
+  int rc = fp8_common(p, Xq, Wq, num_groups * N, R, bn, K, &tmW, &tmX);
+  if (rc) return rc;
+  switch (bn) {
+    case 32: return f8::launch<32>(tmW, tmX, p, num_sms, stream);
+    case 64: return f8::launch<64>(tmW, tmX, p, num_sms, stream);
+    default: return f8::launch<128>(tmW, tmX, p, num_sms, stream);
+  }
+}
