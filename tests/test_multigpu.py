@@ -19,9 +19,9 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(script, nproc, *args, env=None, timeout=600):
+def _run(script, nproc, *args, env=None, timeout=240):
     e = dict(os.environ)
-    e.update({"NCCL_NVLS_ENABLE": "0"})
+    e.update({"NCCL_NVLS_ENABLE": "0", "B200_SPIN_LIMIT": "300000"})
     e.update(env or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),

@@ -11,6 +11,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspa
 
 
 def main():
+    import faulthandler
+    faulthandler.dump_traceback_later(90, exit=True)      # a stuck rank prints where it is and exits
     from vllm_torchtpu_b200 import SamplingParams
     from vllm_torchtpu_b200.config import ModelConfig
     from vllm_torchtpu_b200.engine.llm import LLM
