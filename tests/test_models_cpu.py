@@ -60,3 +60,30 @@ def test_hf_config_mapping():
                                    "quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}})
     assert mc.architecture == "deepseek_v3" and mc.is_mla and mc.moe_score_bias and mc.quantization == "fp8_block"
     assert mc.layer_is_moe(3) and not mc.layer_is_moe(2)
+
+
+def test_gdn_recurrence_is_chunk_invariant_and_engine_runs_hybrid():
+    from vllm_torchtpu_b200.ops import gdn_reference as g
+    torch.manual_seed(0)
+    T, Hk, Hv, dk, dv = 23, 2, 4, 8, 8
+    q, k, v = torch.randn(T, Hk, dk), torch.randn(T, Hk, dk), torch.randn(T, Hv, dv)
+    gate, beta = -torch.rand(T, Hv), torch.rand(T, Hv)
+    s1 = torch.zeros(Hv, dk, dv)
+    full = g.gated_delta_rule(q, k, v, gate, beta, s1)
+    s2 = torch.zeros(Hv, dk, dv)
+    parts = [g.gated_delta_rule(q[a:b], k[a:b], v[a:b], gate[a:b], beta[a:b], s2) for a, b in ((0, 9), (9, 10), (10, 23))]
+    torch.testing.assert_close(torch.cat(parts), full, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(s1, s2, rtol=1e-5, atol=1e-5)
+    # conv window carried across chunks
+    x, w = torch.randn(T, 6), torch.randn(6, 4)
+    c1, c2 = torch.zeros(6, 3), torch.zeros(6, 3)
+    a = g.causal_conv1d_update(x, c1, w)
+    b = torch.cat([g.causal_conv1d_update(x[:5], c2, w), g.causal_conv1d_update(x[5:], c2, w)])
+    torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-5)
+    # hybrid engine: chunked prefill + batching must not change greedy tokens
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    one = LLM("tiny-gdn", device="cpu", max_num_seqs=4, max_num_batched_tokens=256, block_size=16, init_dist=False)
+    want = [one.generate([p], sp)[0].outputs[0].token_ids for p in _prompts()]
+    many = LLM("tiny-gdn", device="cpu", max_num_seqs=4, max_num_batched_tokens=16, block_size=16, init_dist=False)
+    got = [o.outputs[0].token_ids for o in many.generate(_prompts(), sp)]
+    assert got == want

@@ -409,3 +409,4 @@ from .cuda_moe import (gemm_swiglu, grouped_gemm, moe_experts, moe_permute, moe_
                        moe_unpermute)
 from .cuda_fp8 import (fp8_block_gemm, fp8_rowwise_gemm, grouped_fp8_gemm, moe_experts_fp8,  # noqa: E402,F401
                        quant_act_1x128)
+from .cuda_gdn import gdn_forward  # noqa: E402,F401

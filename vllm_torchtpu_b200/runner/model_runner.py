@@ -162,7 +162,8 @@ class ModelRunner:
     def init_kv_cache(self, num_blocks: int) -> None:
         self.num_blocks = num_blocks
         kv_dtype = B200Platform.kv_cache_torch_dtype(self.cfg.cache.kv_cache_dtype, self.mcfg.dtype)
-        self.kv_caches = self.model.allocate_kv_caches(num_blocks, self.block_size, kv_dtype, self.device) \
+        self.kv_caches = self.model.allocate_kv_caches(num_blocks, self.block_size, kv_dtype, self.device,
+                                                       self.max_reqs) \
             if hasattr(self.model, "allocate_kv_caches") else [
                 torch.zeros(self.model.kv_cache_shape(num_blocks, self.block_size), dtype=kv_dtype,
                             device=self.device) for _ in self.model.layers]
@@ -264,7 +265,7 @@ class ModelRunner:
             num_decode_reqs=p["num_decode"], max_query_len=p["max_q"], max_seq_len=p["max_seq"],
             logits_indices=dv("logits_indices", p.get("L_pad", R)),
             request_distribution=(p["num_decode"], p["num_decode"], p["n"]),
-            padded_num_reqs=R, padded_num_tokens=T,
+            padded_num_reqs=R, padded_num_tokens=T, state_slots=dv("batch_slots", R),
             seq_lens_cpu=torch.from_numpy(p["seq_lens_np"]), query_start_loc_cpu=torch.from_numpy(p["qsl_np"]))
 
     # --------------------------------------------------------------- forward
