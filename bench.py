@@ -233,8 +233,9 @@ def main():
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
-    return 0
+    # captured CUDA graphs hold NCCL kernels; destroying the communicator under them can block
+    sys.stdout.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":

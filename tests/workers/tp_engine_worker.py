@@ -33,7 +33,10 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
-        dist.destroy_process_group()
+    # captured CUDA graphs still hold NCCL kernels: tearing the communicator down under them can
+    # block, so the process leaves without destroying the group
+    sys.stdout.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":
