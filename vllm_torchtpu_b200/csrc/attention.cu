@@ -663,3 +663,110 @@ extern "C" int b200_attn_prefill(const void* q, const void* kv, void* out, float
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// Decode attention with built-in scratch, for callers that cannot allocate device memory.
+// The contract (limits, set-up, sharing rules) is written out in attention_no_alloc.h.
+// Nothing below calls an allocator: the scratch is part of this module's device image.
+// ---------------------------------------------------------------------------------------
+#include "attention_no_alloc.h"
+
+#include <cstdio>
+#include <mutex>
+
+static __device__ __align__(256) unsigned char g_attn_static_scratch[B200_ATTN_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+constexpr int kDecodeSmem128 = 4 * 3 * 2 * 16 * 128 * 2;
+constexpr int kDecodeSmem64 = 4 * 3 * 2 * 16 * 64 * 2;
+std::mutex g_static_mu;
+unsigned char* g_static_ptr[kMaxDevices] = {};   // device address of the array, per device
+}  // namespace
+
+// Address of the array on the current device, looked up on the first call there.
+static int attn_static_scratch(unsigned char** ptr_out) {
+  int dev = -1;
+  B200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    b200_set_last_error("attn_decode_static: device ordinal out of range", __FILE__, __LINE__);
+    return -1;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    unsigned char* ptr = nullptr;
+    B200_CUDA_CHECK(cudaGetSymbolAddress((void**)&ptr, g_attn_static_scratch));
+    if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 255) != 0) {
+      b200_set_last_error("attn_decode_static: scratch symbol has no 256-byte aligned address", __FILE__,
+                          __LINE__);
+      return -1;
+    }
+    B200_CUDA_CHECK(cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kDecodeSmem128));
+    B200_CUDA_CHECK(cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kDecodeSmem64));
+    g_static_ptr[dev] = ptr;
+  }
+  *ptr_out = g_static_ptr[dev];
+  return 0;
+}
+
+extern "C" int b200_attn_decode_static_setup(void) {
+  unsigned char* ptr = nullptr;
+  return attn_static_scratch(&ptr);
+}
+
+extern "C" int b200_attn_decode_static_reset(cudaStream_t stream) {
+  unsigned char* ptr = nullptr;
+  if (attn_static_scratch(&ptr) != 0) return -1;
+  B200_CUDA_CHECK(cudaMemsetAsync(ptr, 0, B200_ATTN_STATIC_COUNTER_BYTES, stream));
+  return 0;
+}
+
+extern "C" int b200_attn_decode_static(const void* q, const void* kv, void* out, float* lse,
+                                       const int* block_tables, const int* seq_lens, const int* qsl,
+                                       int num_reqs, int max_blocks, int block_size, long long num_blocks,
+                                       int Hq, int Hkv, int D, float scale, int window, float softcap,
+                                       const float* sinks, int num_splits, cudaStream_t stream) {
+  if (num_reqs <= 0) return 0;
+  if (Hkv <= 0 || block_size % 16 || (Hq % Hkv) || Hq / Hkv > 16) {
+    b200_set_last_error("attn_decode_static: block_size % 16 == 0 and q heads per kv head <= 16 required",
+                        __FILE__, __LINE__);
+    return -1;
+  }
+  if (D != 128 && D != 64) {
+    b200_set_last_error("attn_decode_static: head_dim must be 64 or 128", __FILE__, __LINE__);
+    return -1;
+  }
+  if (num_splits < 1) num_splits = 1;
+  const size_t counters = (size_t)num_reqs * Hkv;
+  const size_t part_bytes = num_splits > 1 ? counters * num_splits * 16 * (size_t)(D + 2) * sizeof(float) : 0;
+  if (num_splits > 1 && (counters * sizeof(int) > B200_ATTN_STATIC_COUNTER_BYTES ||
+                         part_bytes > B200_ATTN_STATIC_SCRATCH_BYTES - B200_ATTN_STATIC_COUNTER_BYTES)) {
+    char msg[256];
+    snprintf(msg, sizeof(msg),
+             "attn_decode_static: %d requests x %d kv heads x %d splits need %zu counters and %zu scratch "
+             "bytes; the built-in scratch holds %u counters and %u bytes",
+             num_reqs, Hkv, num_splits, counters, part_bytes,
+             (unsigned)(B200_ATTN_STATIC_COUNTER_BYTES / sizeof(int)),
+             (unsigned)(B200_ATTN_STATIC_SCRATCH_BYTES - B200_ATTN_STATIC_COUNTER_BYTES));
+    b200_set_last_error(msg, __FILE__, __LINE__);
+    return -1;
+  }
+  unsigned char* base = nullptr;
+  if (attn_static_scratch(&base) != 0) return -1;
+  AttnParams p;
+  fill_params(p, q, kv, out, lse, block_tables, seq_lens, qsl, max_blocks, block_size, num_blocks, Hq, Hkv, D,
+              scale, window, softcap, sinks);
+  p.req_begin = 0;
+  p.req_end = num_reqs;
+  p.num_splits = num_splits;
+  p.counters = reinterpret_cast<int*>(base);
+  p.part_o = reinterpret_cast<float*>(base + B200_ATTN_STATIC_COUNTER_BYTES);
+  p.part_ml = p.part_o + counters * num_splits * 16 * D;
+  dim3 grid(Hkv, num_reqs, num_splits);
+  if (D == 128) attn_decode_kernel<128><<<grid, 128, kDecodeSmem128, stream>>>(p);
+  else attn_decode_kernel<64><<<grid, 128, kDecodeSmem64, stream>>>(p);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
