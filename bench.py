@@ -192,7 +192,10 @@ def main():
     barrier()
     wall_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else {}
-    device_ms = sum(a.elapsed_time(b) for a, b in runner.timing_events)
+    durs = [(a.elapsed_time(b), dec, ntok) for a, b, dec, ntok in runner.timing_events]
+    device_ms = sum(d for d, _, _ in durs)
+    dec_ms = sorted(d for d, dec, _ in durs if dec)
+    pre_ms = sorted(d for d, dec, ntok in durs if not dec and ntok >= args.max_num_batched_tokens // 2)
     engine_steps = runner.stats["steps"] - steps0
     status = cuda_ops.check_status()
     t = torch.tensor([wall_s, device_ms], dtype=torch.float64, device="cuda")
@@ -223,6 +226,10 @@ def main():
                     "wall_s_per_step": round(wall_s / args.steps, 3)},
             "gpu_launches": runner.launch_counter - launches0,
             "engine_steps": engine_steps,
+            "decode_step_ms_p50": round(dec_ms[len(dec_ms) // 2], 3) if dec_ms else None,
+            "decode_steps": len(dec_ms),
+            "prefill_step_ms_p50": round(pre_ms[len(pre_ms) // 2], 3) if pre_ms else None,
+            "prefill_steps": len(pre_ms),
             "p50_ttft_ms": round(statistics.median(ttfts) * 1e3, 2) if ttfts else None,
             "p50_tpot_ms": round(statistics.median(tpots) * 1e3, 3) if tpots else None,
             "clocks": clocks, "device_status": status,

@@ -11,21 +11,6 @@
 
 namespace b200 {
 
-struct alignas(16) bf16x8 {
-  __nv_bfloat162 v[4];
-};
-
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float t = (lane < nw) ? red[lane] : 0.f;
-  t = warp_sum(t);
-  __syncthreads();
-  return t;
-}
-
 // One CTA per row; H % 8 == 0.  ADD: residual += x (rounded to bf16) first.
 template <bool ADD>
 __global__ void rms_norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,

@@ -47,7 +47,12 @@ struct GemmCfg {
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int BAR_BYTES = 256;
   static constexpr int PREFIX_BYTES = (MAX_GROUPS + 1) * 4;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + PREFIX_BYTES + 1024;  // + alignment slack
+  // fused launches stage [32 tokens][128 rows] bf16 chunks of a partial tile here (two buffers) and
+  // push each to its owner with one bulk copy
+  static constexpr int PUSH_CHUNK_BYTES = 32 * BM * 2;
+  static constexpr int PUSH_OFF = (STAGES * STAGE_BYTES + BAR_BYTES + PREFIX_BYTES + 127) / 128 * 128;
+  static constexpr int SMEM = PUSH_OFF + 2 * PUSH_CHUNK_BYTES + 1024;                 // + alignment slack
+  static_assert(SMEM <= 232448, "shared memory budget");
   static constexpr int TMEM_COLS = 2 * NACC * BN < 32 ? 32 : 2 * NACC * BN;
   static_assert(TMEM_COLS <= 512, "accumulators exceed TMEM");
 };
@@ -67,9 +72,11 @@ struct GemmParams {
   const int* group_off;                  // grouped: int[num_groups + 1] row offsets into X / Y (null = dense)
   int num_groups, w_rows_per_group;      // grouped: weight rows of one expert
   // ---- fused cross-rank reduction over NVLink peer memory (world == 1: plain GEMM)
-  int world, rank, ar_mode;              // ar_mode 0: all-reduce (sum lands on every rank), 1: reduce-scatter
+  int world, rank, ar_mode;              // 0: all-reduce via tile owners, 1: reduce-scatter, 2: one-shot
+                                         // all-reduce, 3: push to every rank, the consumer kernel sums
   uint8_t* peer[8];                      // heap base of every rank (own heap at [rank])
-  unsigned long long part_off, out_off;  // heap offsets: partial [T,N] bf16, reduced output [T,N] bf16
+  unsigned long long part_off, out_off;  // heap offsets: receive slabs (one per source rank), output [T,N] bf16
+  unsigned long long part_src_stride;    // bytes between the receive slabs of two source ranks
   unsigned long long tile_flag_off;      // heap offset: int[world][max_tiles], written by producers at the owner
   unsigned long long done_flag_off;      // heap offset: int[max_tiles], written by the owner at every reader
   int max_tiles;
@@ -79,15 +86,6 @@ struct GemmParams {
 };
 
 constexpr int NUM_THREADS_FUSED = NUM_THREADS + 128;   // + 4 reducer warps
-
-__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
 
 __device__ __forceinline__ void decode_tile(int tile, const GemmParams& p, int& n_tile, int& t_tile) {
   const int per_group = GROUP_N * p.t_tiles;
@@ -150,6 +148,111 @@ __device__ __forceinline__ Work get_work(int w, const GemmParams& p, const int* 
   return k;
 }
 
+// Where an output tile goes.  Element (column c, row) of the tile is base[c * cs + row].
+//   plain GEMM                Y[t, n]
+//   fused, via tile owners    the owner (tile % world) keeps, per source rank, a slab of its owned
+//                             tiles, each [BN][BM] bf16; partials are PUSHED there over NVLink
+//   fused, one-shot           every rank keeps a [T, N] matrix per source rank; each rank pushes its
+//                             partial to all of them and sums what it received
+struct TileDst {
+  __nv_bfloat16* base;
+  int cs;
+};
+template <int BN>
+__device__ __forceinline__ TileDst tile_dst(const GemmParams& p, const Work& wk, int d) {
+  TileDst t;
+  if (p.world == 1) {
+    t.base = p.Y + (size_t)wk.t_row * p.ldy + wk.n0;
+    t.cs = p.ldy;
+  } else if (p.ar_mode >= 2) {
+    t.base = reinterpret_cast<__nv_bfloat16*>(p.peer[d] + p.part_off + (size_t)p.rank * p.part_src_stride) +
+             (size_t)wk.t_row * p.N + wk.n0;
+    t.cs = p.N;
+  } else {
+    t.base = reinterpret_cast<__nv_bfloat16*>(p.peer[wk.tile % p.world] + p.part_off +
+                                              (size_t)p.rank * p.part_src_stride) +
+             (size_t)(wk.tile / p.world) * (BM * BN);
+    t.cs = BM;
+  }
+  return t;
+}
+
+// Tell the consumers of this rank's partial of `tile` that it has landed (t = index of the calling
+// thread inside its group; the group has fenced system-wide and synchronised before the call).
+__device__ __forceinline__ void publish_tile(const GemmParams& p, int tile, int epoch, int t) {
+  if (p.ar_mode >= 2) {
+    if (t < p.world)
+      st_release_sys(reinterpret_cast<int*>(p.peer[t] + p.tile_flag_off) + (size_t)p.rank * p.max_tiles + tile,
+                     epoch);
+  } else if (t == 0) {
+    st_release_sys(reinterpret_cast<int*>(p.peer[tile % p.world] + p.tile_flag_off) +
+                       (size_t)p.rank * p.max_tiles + tile, epoch);
+  }
+}
+
+// Sum `world` bf16 vectors (8 elements each) that live `stride` bytes apart.
+__device__ __forceinline__ uint4 sum_slabs(const uint8_t* src, size_t stride, int world) {
+  uint4 raw[8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r)
+    if (r < world) raw[r] = ld_relaxed_sys_v4(src + (size_t)r * stride);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    if (r < world) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+  }
+  uint4 o;
+  __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+  return o;
+}
+
+// Four vectors of a [rows][BM] bf16 slab per thread (idx, idx + 128, ...), summed over `world` slabs;
+// the loads of one source rank for all four are in flight together.
+__device__ __forceinline__ void sum_slabs4(const uint8_t* slab, size_t stride, int world, int idx0, int total,
+                                           int n_vecs, uint4 (&out)[4]) {
+  float acc[4][8];
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+  for (int r = 0; r < world; ++r) {
+    uint4 raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int idx = idx0 + u * 128;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (idx < total && (idx % (BM / 8)) < n_vecs)
+        raw[u] = ld_relaxed_sys_v4(slab + (size_t)r * stride + (size_t)idx * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[u][2 * j] += f.x;
+        acc[u][2 * j + 1] += f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out[u]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[u][2 * j], acc[u][2 * j + 1]);
+  }
+}
+
 template <int BN, int NACC>
 __global__ void __launch_bounds__(NUM_THREADS_FUSED, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
@@ -170,9 +273,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   volatile int* red_ok = reinterpret_cast<volatile int*>(tmem_slot + 3);
   int* s_prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES);
   const bool fused = p.world > 1;
-  // every thread reads the epoch before any CTA of this launch can have bumped it
-  const int epoch = fused ? (*reinterpret_cast<volatile int*>(p.epoch_ptr) + 1) : 0;
-  __nv_bfloat16* const dst_base = fused ? reinterpret_cast<__nv_bfloat16*>(p.peer[p.rank] + p.part_off) : p.Y;
+  __nv_bfloat16* const dst_base = p.Y;       // SwiGLU and grouped launches (never fused)
+  const int ndst = (fused && p.ar_mode >= 2) ? p.world : 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -205,6 +307,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   const bool dense = p.group_off == nullptr;
   pdl_launch_dependents();
   if (!(dense && warp == 0)) pdl_wait();
+  // The epoch is bumped by the last CTA of a fused launch to exit, so it must be read after the wait
+  // above (the previous launch may be a fused one that is still running) and is read by every thread
+  // before any CTA of this launch can bump it.  Warp 0 never uses it.
+  const int epoch = (fused && warp != 0) ? (*reinterpret_cast<volatile int*>(p.epoch_ptr) + 1) : 0;
   if (p.group_off != nullptr) {
     // token tiles per expert -> exclusive prefix (serial scan: at most MAX_GROUPS short steps)
     for (int e = threadIdx.x; e < p.num_groups; e += blockDim.x)
@@ -318,6 +424,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const int q = warp & 3;                       // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;                // 0..127 inside the tile
     int iter = 0;
+    uint32_t push_count = 0;                      // bulk copies issued so far (selects the staging buffer)
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++iter) {
       const Work wk = get_work<BN>(w, p, s_prefix);
       const int tile = wk.tile, split = wk.split;
@@ -352,6 +459,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
+      } else if (p.splits == 1 && fused && p.ar_mode < 2) {
+        // partial tile -> the owner's slab [BN][BM] bf16, 32 columns (8 KB) per bulk copy
+        uint8_t* slab = reinterpret_cast<uint8_t*>(tile_dst<BN>(p, wk, 0).base);
+        __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + Cfg::PUSH_OFF);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (c0 >= t_valid) break;               // uniform over the four epilogue warps
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c0, r);
+          tmem_ld_wait();
+          __nv_bfloat16* st = stg + (push_count & 1) * (32 * BM);
+          // the copy that last read this buffer was issued two chunks ago
+          if (threadIdx.x == 64) bulk_wait_group_read<1>();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 32; ++j) st[j * BM + row] = __float2bfloat16(__uint_as_float(r[j]));
+          fence_proxy_async_smem();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 64) {
+            bulk_store_s2g(slab + (size_t)c0 * BM * sizeof(__nv_bfloat16), st, Cfg::PUSH_CHUNK_BYTES);
+            bulk_commit_group();
+          }
+          ++push_count;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+        if (threadIdx.x == 64) {
+          bulk_wait_group<0>();                   // every chunk of this tile has been written
+          __threadfence_system();
+          publish_tile(p, tile, epoch, 0);
+        }
       } else if (p.splits == 1) {
         const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
 #pragma unroll 1
@@ -361,10 +500,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           tmem_ld_32x32(taddr + c0, r);
           tmem_ld_wait();
           if (n < p.N) {
-            __nv_bfloat16* yp = dst_base + (size_t)(t0 + c0) * p.ldy + n;
+            for (int d = 0; d < ndst; ++d) {
+              const TileDst td = tile_dst<BN>(p, wk, d);
+              __nv_bfloat16* yp = td.base + (size_t)c0 * td.cs + row;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (c0 + j < t_valid) yp[(size_t)j * p.ldy] = __float2bfloat16(__uint_as_float(r[j]) + bias);
+              for (int j = 0; j < 32; ++j) {
+                if (c0 + j < t_valid) yp[(size_t)j * td.cs] = __float2bfloat16(__uint_as_float(r[j]) + bias);
+              }
             }
           }
         }
@@ -372,14 +514,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
         if (fused) {
-          // partial tile is in this rank's heap: make it visible system-wide, then tell the tile's owner
+          // the partial tile has been pushed: make it visible system-wide, then raise its flag(s)
           __threadfence_system();
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (threadIdx.x == 64) {
-            int* flag = reinterpret_cast<int*>(p.peer[tile % p.world] + p.tile_flag_off) +
-                        (size_t)p.rank * p.max_tiles + tile;
-            st_release_sys(flag, epoch);
-          }
+          publish_tile(p, tile, epoch, (int)threadIdx.x - 64);
         }
       } else if (p.cluster_splitk) {
         // split-K inside a thread-block cluster: the partial stays on chip.  This CTA has exactly one
@@ -431,8 +569,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             for (int j = 0; j < 4; ++j)
               if (n4 + j < p.N) b4[j] = __bfloat162float(p.bias[n4 + j]);
           }
-          const bool vec_ok = (n4 + 3 < p.N) && ((p.ldy & 3) == 0) &&
-                              ((reinterpret_cast<uintptr_t>(dst_base) & 7) == 0);
           for (int c0 = q; c0 < t_valid; c0 += 16) {
             float4 a4[4];
 #pragma unroll
@@ -452,19 +588,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             for (int u = 0; u < 4; ++u) {
               const int c = c0 + 4 * u;
               if (c >= t_valid) continue;
-              __nv_bfloat16* yp = dst_base + (size_t)(t0 + c) * p.ldy + n4;
-              if (vec_ok) {
-                __nv_bfloat162 lo = __floats2bfloat162_rn(a4[u].x + b4[0], a4[u].y + b4[1]);
-                __nv_bfloat162 hi = __floats2bfloat162_rn(a4[u].z + b4[2], a4[u].w + b4[3]);
-                uint2 pk;
-                pk.x = *reinterpret_cast<uint32_t*>(&lo);
-                pk.y = *reinterpret_cast<uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>(yp) = pk;
-              } else {
-                const float vals[4] = {a4[u].x, a4[u].y, a4[u].z, a4[u].w};
+              for (int d = 0; d < ndst; ++d) {
+                const TileDst td = tile_dst<BN>(p, wk, d);
+                __nv_bfloat16* yp = td.base + (size_t)c * td.cs + 4 * lane;
+                const bool vec_ok = (n4 + 3 < p.N) && ((td.cs & 3) == 0) &&
+                                    ((reinterpret_cast<uintptr_t>(td.base) & 7) == 0);
+                if (vec_ok) {
+                  __nv_bfloat162 lo = __floats2bfloat162_rn(a4[u].x + b4[0], a4[u].y + b4[1]);
+                  __nv_bfloat162 hi = __floats2bfloat162_rn(a4[u].z + b4[2], a4[u].w + b4[3]);
+                  uint2 pk;
+                  pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                  pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                  *reinterpret_cast<uint2*>(yp) = pk;
+                } else {
+                  const float vals[4] = {a4[u].x, a4[u].y, a4[u].z, a4[u].w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+                  for (int j = 0; j < 4; ++j)
+                    if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+                }
               }
             }
           }
@@ -472,11 +613,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           if (fused) {
             __threadfence_system();
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) {
-              int* flag = reinterpret_cast<int*>(p.peer[tile % p.world] + p.tile_flag_off) +
-                          (size_t)p.rank * p.max_tiles + tile;
-              st_release_sys(flag, epoch);
-            }
+            publish_tile(p, tile, epoch, (int)threadIdx.x - 64);
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is rewritten next iteration
@@ -484,12 +621,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
   }
 
-  else if (fused) {
+  else if (fused) {      // (absent in ar_mode 3 launches, which have no reducer warps)
     // ------------------------------------------- reducer warps (threads 192..319)
-    // Tile `tile` is owned by rank tile % world.  The owner waits until every rank has published
-    // its partial of that tile, sums the partials in rank order (fp32), writes bf16 to the output
-    // buffer of every rank (all-reduce) or its own (reduce-scatter) and raises the tile's done flag
-    // there.  Reads and writes of peer heaps are plain NVLink loads/stores.
+    // All cross-rank traffic is stores: partials were pushed into this rank's receive slabs, so the
+    // sums below read local memory only (written by peers: L1 is bypassed).
+    //   via owners (ar_mode 0/1): rank tile % world sums the slabs of a tile once every rank's flag
+    //     for it is up, then pushes the bf16 result into the output buffer of every rank (all-reduce)
+    //     or keeps it (reduce-scatter) and raises the tile's done flag there.
+    //   one-shot (ar_mode 2): every rank received every partial; it sums all tiles for itself.
     const int rt = threadIdx.x - NUM_THREADS;        // 0..127
     if (p.cluster_splitk) {
       // take part in both cluster barriers of the split-K reduction up front: the flags this role
@@ -501,49 +640,64 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
     const int tiles = p.n_tiles * p.t_tiles;
     const int* my_tile_flags = reinterpret_cast<const int*>(p.peer[p.rank] + p.tile_flag_off);
-    int owned_idx = 0;
-    for (int tile = p.rank; tile < tiles; tile += p.world, ++owned_idx) {
-      if (owned_idx % (int)gridDim.x != (int)blockIdx.x) continue;
-      if (rt < p.world) {
-        if (!wait_flag_ge(my_tile_flags + (size_t)rt * p.max_tiles + tile, epoch, p.status, p.spin_limit))
-          *red_ok = 0;
+    const uint8_t* recv = p.peer[p.rank] + p.part_off;
+    const size_t stride = (size_t)p.part_src_stride;
+    if (p.ar_mode == 2) {
+      uint8_t* out = p.peer[p.rank] + p.out_off;
+      for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        if (rt < p.world) {
+          if (!wait_flag_ge(my_tile_flags + (size_t)rt * p.max_tiles + tile, epoch, p.status, p.spin_limit))
+            *red_ok = 0;
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (!*red_ok) break;
+        int n_tile, t_tile;
+        decode_tile(tile, p, n_tile, t_tile);
+        const int n0 = n_tile * BM, t0 = t_tile * BN;
+        const int t_valid = min(BN, p.T - t0);
+        const int n_vecs = min(BM, p.N - n0) >> 3;
+        for (int idx = rt; idx < t_valid * (BM / 8); idx += 128) {
+          const int row = idx / (BM / 8), v = idx % (BM / 8);
+          if (v >= n_vecs) continue;
+          const size_t off = ((size_t)(t0 + row) * p.N + n0 + v * 8) * sizeof(__nv_bfloat16);
+          *reinterpret_cast<uint4*>(out + off) = sum_slabs(recv + off, stride, p.world);
+        }
       }
-      asm volatile("bar.sync 2, 128;" ::: "memory");
-      if (*red_ok) {
+    } else {
+      int owned_idx = 0;
+      for (int tile = p.rank; tile < tiles; tile += p.world, ++owned_idx) {
+        if (owned_idx % (int)gridDim.x != (int)blockIdx.x) continue;
+        if (rt < p.world) {
+          if (!wait_flag_ge(my_tile_flags + (size_t)rt * p.max_tiles + tile, epoch, p.status, p.spin_limit))
+            *red_ok = 0;
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (!*red_ok) break;
         int n_tile, t_tile;
         decode_tile(tile, p, n_tile, t_tile);
         const int n0 = n_tile * BM, t0 = t_tile * BN;
         const int t_valid = min(BN, p.T - t0);
         const int n_vecs = min(BM, p.N - n0) >> 3;             // 16-byte vectors per row (N % 8 == 0)
-        for (int idx = rt; idx < t_valid * (BM / 8); idx += 128) {
-          const int row = idx / (BM / 8), v = idx % (BM / 8);
-          if (v >= n_vecs) continue;
-          const size_t off = ((size_t)(t0 + row) * p.ldy + n0 + v * 8) * sizeof(__nv_bfloat16);
-          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int r = 0; r < p.world; ++r) {
-            const uint4 raw = ld_relaxed_sys_v4(p.peer[r] + p.part_off + off);
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const uint8_t* slab = recv + (size_t)owned_idx * (BM * BN * sizeof(__nv_bfloat16));
+        const int total = t_valid * (BM / 8);
+        for (int base = 0; base < total; base += 128 * 4) {
+          uint4 o[4];
+          sum_slabs4(slab, stride, p.world, base + rt, total, n_vecs, o);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __bfloat1622float2(h[j]);
-              acc[2 * j] += f.x;
-              acc[2 * j + 1] += f.y;
+          for (int u = 0; u < 4; ++u) {
+            const int idx = base + rt + u * 128;
+            const int row = idx / (BM / 8), v = idx % (BM / 8);
+            if (idx >= total || v >= n_vecs) continue;
+            const size_t off = ((size_t)(t0 + row) * p.ldy + n0 + v * 8) * sizeof(__nv_bfloat16);
+            if (p.ar_mode == 0) {
+              for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.peer[r] + p.out_off + off) = o[u];
+            } else {
+              *reinterpret_cast<uint4*>(p.peer[p.rank] + p.out_off + off) = o[u];
             }
-          }
-          uint4 o;
-          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-          if (p.ar_mode == 0) {
-            for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.peer[r] + p.out_off + off) = o;
-          } else {
-            *reinterpret_cast<uint4*>(p.peer[p.rank] + p.out_off + off) = o;
           }
         }
         __threadfence_system();
-      }
-      asm volatile("bar.sync 2, 128;" ::: "memory");
-      if (*red_ok) {
+        asm volatile("bar.sync 2, 128;" ::: "memory");
         if (p.ar_mode == 0) {
           if (rt < p.world)
             st_release_sys(reinterpret_cast<int*>(p.peer[rt] + p.done_flag_off) + tile, epoch);
@@ -551,12 +705,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           st_release_sys(reinterpret_cast<int*>(p.peer[p.rank] + p.done_flag_off) + tile, epoch);
         }
       }
-    }
-    // this rank's output is complete once every tile it reads has its done flag
-    const int* done = reinterpret_cast<const int*>(p.peer[p.rank] + p.done_flag_off);
-    for (int tile = blockIdx.x * 128 + rt; tile < tiles; tile += gridDim.x * 128) {
-      if (p.ar_mode == 1 && tile % p.world != p.rank) continue;
-      wait_flag_ge(done + tile, epoch, p.status, p.spin_limit);
+      // this rank's output is complete once every tile it reads has its done flag
+      const int* done = reinterpret_cast<const int*>(p.peer[p.rank] + p.done_flag_off);
+      for (int tile = blockIdx.x * 128 + rt; tile < tiles; tile += gridDim.x * 128) {
+        if (p.ar_mode == 1 && tile % p.world != p.rank) continue;
+        wait_flag_ge(done + tile, epoch, p.status, p.spin_limit);
+      }
     }
   }
 
@@ -578,8 +732,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         for (int j = 0; j < 4; ++j)
           if (n4 + j < p.N) b4[j] = __bfloat162float(p.bias[n4 + j]);
       }
-      const bool vec_ok = (n4 + 3 < p.N) && ((p.ldy & 3) == 0) &&
-                          ((reinterpret_cast<uintptr_t>(dst_base) & 7) == 0);
       const uint32_t part_local = smem_u32(smem);
       for (int c = (int)rank + S * q; c < wk.t_valid; c += 4 * S) {
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -587,19 +739,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           const float4 v = ld_dsmem_v4(mapa_shared(part_local + (uint32_t)((c * BM + 4 * lane) * 4), r2));
           a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
         }
-        __nv_bfloat16* yp = dst_base + (size_t)(wk.t_row + c) * p.ldy + n4;
-        if (vec_ok) {
-          __nv_bfloat162 lo = __floats2bfloat162_rn(a.x + b4[0], a.y + b4[1]);
-          __nv_bfloat162 hi = __floats2bfloat162_rn(a.z + b4[2], a.w + b4[3]);
-          uint2 pk;
-          pk.x = *reinterpret_cast<uint32_t*>(&lo);
-          pk.y = *reinterpret_cast<uint32_t*>(&hi);
-          *reinterpret_cast<uint2*>(yp) = pk;
-        } else {
-          const float vals[4] = {a.x, a.y, a.z, a.w};
+        for (int d = 0; d < ndst; ++d) {
+          const TileDst td = tile_dst<BN>(p, wk, d);
+          __nv_bfloat16* yp = td.base + (size_t)c * td.cs + 4 * lane;
+          const bool vec_ok = (n4 + 3 < p.N) && ((td.cs & 3) == 0) &&
+                              ((reinterpret_cast<uintptr_t>(td.base) & 7) == 0);
+          if (vec_ok) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(a.x + b4[0], a.y + b4[1]);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(a.z + b4[2], a.w + b4[3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(yp) = pk;
+          } else {
+            const float vals[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+            for (int j = 0; j < 4; ++j)
+              if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+          }
         }
       }
       if (fused) __threadfence_system();
@@ -607,11 +764,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     __syncwarp();
     cluster_arrive_release();          // nobody leaves while its partial may still be read
     cluster_wait_acquire();
-    if (fused && cluster_ctarank() == 0 && threadIdx.x == 64 && blockIdx.x < total_work) {
+    if (fused && cluster_ctarank() == 0 && warp == 2 && blockIdx.x < total_work) {
       const Work wk = get_work<BN>(blockIdx.x, p, s_prefix);
-      int* flag = reinterpret_cast<int*>(p.peer[wk.tile % p.world] + p.tile_flag_off) +
-                  (size_t)p.rank * p.max_tiles + wk.tile;
-      st_release_sys(flag, epoch);
+      publish_tile(p, wk.tile, epoch, lane);
     }
   }
 
@@ -621,7 +776,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
-  if (fused && threadIdx.x == 0) {
+  if (fused && threadIdx.x == 64) {      // a thread that holds the epoch (warp 0 does not)
     __threadfence();
     const int arrived = atomicAdd(p.cta_done, 1) + 1;
     if (arrived == (int)gridDim.x) {
@@ -778,7 +933,7 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gem
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     attr_set = true;
   }
-  const int threads = p.world > 1 ? NUM_THREADS_FUSED : NUM_THREADS;
+  const int threads = (p.world > 1 && p.ar_mode != 3) ? NUM_THREADS_FUSED : NUM_THREADS;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(threads);
@@ -891,15 +1046,22 @@ extern "C" int b200_gemm_bf16(const void* X, const void* W, void* Y, const void*
 }
 
 // Row-parallel GEMM fused with the cross-rank reduction: Y = sum over ranks of X_r * W_r^T.
-// Every rank of the group launches this with identical T/N (K is the local shard).  The partial
-// tile of each rank goes to its symmetric heap; the owner of a tile (tile % world) sums the
-// partials over NVLink and writes the bf16 result into the output buffer (heap offset out_off)
-// of every rank (mode 0, all-reduce) or only its own (mode 1, reduce-scatter by tile ownership).
+// Every rank of the group launches this with identical T/N (K is the local shard).  All NVLink
+// traffic is stores.  mode 0 (all-reduce) and 1 (reduce-scatter by tile ownership): each rank
+// pushes its partial of a tile into the receive slab the tile's owner (tile % world) keeps for it,
+// the owner sums the slabs from local memory and pushes the bf16 result into the output buffer
+// (heap offset out_off) of every rank (mode 0) or keeps it (mode 1).  A mode-0 call whose pushed
+// bytes, T*N*2*(world-1), do not exceed one_shot_max_bytes runs one-shot instead: every rank pushes
+// its partial to every rank and each sums all of it for itself, one NVLink hop in total.
+// mode 3 pushes like the one-shot form but leaves the sum to the consumer
+// (b200_reduce_pushed_rms_norm), which finds the partials of all ranks in its own receive region.
+// part_off/part_bytes: receive region of this launch (callers alternate between two regions).
 // peers: `world` heap base pointers; ctrl: local device int[4] {epoch, cta_done, -, -}.
 extern "C" int b200_gemm_bf16_fused_reduce(const void* X, const void* W, int T, int N, int K, int ldx, int ldw,
                                            void* const* peers, int rank, int world, int mode,
-                                           unsigned long long part_off, unsigned long long out_off,
-                                           unsigned long long tile_flag_off,
+                                           unsigned long long part_off, unsigned long long part_bytes,
+                                           unsigned long long one_shot_max_bytes,
+                                           unsigned long long out_off, unsigned long long tile_flag_off,
                                            unsigned long long done_flag_off, int max_tiles, int* ctrl,
                                            void* ws, size_t ws_bytes, int* counters, int counters_len,
                                            int* status, int num_sms, unsigned int spin_limit,
@@ -935,7 +1097,7 @@ extern "C" int b200_gemm_bf16_fused_reduce(const void* X, const void* W, int T, 
     size_t req = (size_t)tiles * splits * BM * bn * sizeof(float);
     if (ws == nullptr || req > ws_bytes || counters == nullptr || tiles > counters_len) splits = 1;
   }
-  if (splits > 1) splits = fit_cluster_splits(splits, tiles, bn, NUM_THREADS_FUSED);
+  if (splits > 1) splits = fit_cluster_splits(splits, tiles, bn, mode == 3 ? NUM_THREADS : NUM_THREADS_FUSED);
   p.splits = splits;
   p.kb_per_split = (p.kb_total + splits - 1) / splits;
   while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= p.kb_total) {
@@ -945,6 +1107,17 @@ extern "C" int b200_gemm_bf16_fused_reduce(const void* X, const void* W, int T, 
   p.w_evict_first = (p.t_tiles == 1) ? 1 : 0;
   p.cluster_splitk = (p.splits > 1 && p.splits <= 8) ? 1 : 0;
   p.world = world; p.rank = rank; p.ar_mode = mode;
+  if (mode == 0 && (unsigned long long)T * N * 2ull * (world - 1) <= one_shot_max_bytes) p.ar_mode = 2;
+  if (p.ar_mode >= 2) {
+    p.part_src_stride = ((unsigned long long)T * N * 2ull + 255ull) & ~255ull;
+  } else {
+    const unsigned long long owned = (unsigned long long)(tiles + world - 1) / world;
+    p.part_src_stride = owned * BM * bn * 2ull;
+  }
+  if (p.part_src_stride * world > part_bytes) {
+    b200_set_last_error("gemm_fused_reduce: receive region too small for this shape", __FILE__, __LINE__);
+    return -5;
+  }
   for (int i = 0; i < 8; ++i) p.peer[i] = i < world ? (uint8_t*)peers[i] : nullptr;
   p.part_off = part_off; p.out_off = out_off;
   p.tile_flag_off = tile_flag_off; p.done_flag_off = done_flag_off;

@@ -80,6 +80,10 @@ _decl("B200_FUSED_TP", bool, True,
       "row-parallel GEMMs reduce across ranks inside the kernel over NVLink peer memory")
 _decl("B200_TP_COMM", str, "p2p", "data plane of the fused TP kernels",
       choices=("p2p", "multimem", "nccl"))
+_decl("B200_TP_ONE_SHOT_BYTES", int, 4 * 2**20,
+      "fused TP all-reduce: push partials to every rank (one NVLink hop) while T*N*2*(world-1) is at most this")
+_decl("B200_TP_DEFER_REDUCE", bool, True,
+      "small row-parallel outputs are pushed to every rank and summed inside the following add+RMSNorm kernel")
 _decl("B200_SYMM_HEAP_MB", int, 512, "size of the per-rank symmetric heap")
 _decl("B200_MOE_FUSED_EP", bool, True, "dispatch/combine inside the expert kernel over peer memory")
 _decl("B200_MOE_FUSED_EP_MIN_TOKENS", int, 0, "use the AG/RS path below this many tokens")

@@ -109,6 +109,9 @@ class RowParallelLinear(LinearBase):
         self.tp_size = tp_size if tp_size is not None else st.tp.size
         self.tp_rank = tp_rank if tp_rank is not None else st.tp.rank_in_group
         self.reduce_results = reduce_results
+        # set by a decoder layer whose next op is add + RMSNorm: small outputs may then be returned
+        # as a pending reduction that the norm kernel completes
+        self.defer_reduce = False
         self.full_in, self.full_out = in_features, out_features
         super().__init__(name, in_features // self.tp_size, out_features, **kw)
 
@@ -122,6 +125,10 @@ class RowParallelLinear(LinearBase):
         comm = get_tp_comm()
         if (x.is_cuda and comm.heap is not None and comm.heap.fused_tp is not None
                 and self.method.supports_fused_reduce):
+            ft = comm.heap.fused_tp
+            if (self.defer_reduce and self.bias is None and hasattr(self.method, "apply_push")
+                    and ft.can_push(x.numel() // x.shape[-1], self.out_features)):
+                return self.method.apply_push(self, x, comm)
             y = self.method.apply_fused_all_reduce(self, x, comm)
         else:
             y = comm.all_reduce(self.method.apply(self, x, None))

@@ -110,6 +110,10 @@ class LlamaDecoderLayer:
         self.post_ln = torch.ones(cfg.hidden_size, dtype=cfg.dtype, device=device)
         self.self_attn = LlamaAttention(f"{name}.self_attn", cfg, device, quant)
         self.mlp = self._make_ffn(name, cfg, device, quant)
+        # both row-parallel outputs of this layer feed an add + RMSNorm directly
+        self.self_attn.o.defer_reduce = True
+        if isinstance(self.mlp, LlamaMLP):
+            self.mlp.down.defer_reduce = True
 
     def _make_ffn(self, name, cfg, device, quant):
         return LlamaMLP(f"{name}.mlp", cfg, cfg.intermediate_size, device, quant)
@@ -196,7 +200,7 @@ class LlamaForCausalLM:
             hidden = ops.embedding(input_ids, self.embed)
         for i, layer in enumerate(self.layers):
             hidden, residual = layer.forward(hidden, residual, kv_caches[i], meta)
-        return hidden, residual
+        return ops.materialize(hidden), residual
 
     def finalize(self, hidden, residual):
         if residual is None:

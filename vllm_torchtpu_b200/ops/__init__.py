@@ -30,7 +30,14 @@ def rms_norm(x, weight, eps):
     return cuda_ops().rms_norm(x, weight, eps) if _on_gpu(x) else ref.rms_norm(x, weight, eps)
 
 
+def materialize(x):
+    """A row-parallel output whose cross-rank sum is still pending becomes a tensor."""
+    return x.materialize() if hasattr(x, "materialize") else x
+
+
 def fused_add_rms_norm(x, residual, weight, eps):
+    if hasattr(x, "add_rms_norm"):          # pushed partials: the sum rides in this kernel
+        return x.add_rms_norm(residual, weight, eps)
     if _on_gpu(x):
         return cuda_ops().fused_add_rms_norm(x, residual, weight, eps)
     return ref.fused_add_rms_norm(x, residual, weight, eps)

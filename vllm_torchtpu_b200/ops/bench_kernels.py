@@ -4,6 +4,7 @@
     python -m vllm_torchtpu_b200.ops.bench_kernels gemm-sweep
     python -m vllm_torchtpu_b200.ops.bench_kernels attn-decode --reqs 64 --ctx 1100
     python -m vllm_torchtpu_b200.ops.bench_kernels attn-prefill --reqs 8 --q 1024
+    python -m vllm_torchtpu_b200.ops.bench_kernels decode-layer --reqs 64 --ctx 1100
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed
 (a 256 MB buffer is rewritten) before every timed launch, median of the timed
@@ -137,12 +138,73 @@ def bench_attn_prefill(reqs, qlen, Hq=32, Hkv=8, D=128, iters=10) -> dict:
             "frac_of_bf16_peak": round(flops / ms / 1e9 / pk["bf16_tflops"], 3), "peaks": tag}
 
 
+def bench_decode_layer(reqs, ctx, layers=8, parts="all", iters=10, H=4096, I=14336, Hq=32, Hkv=8, D=128) -> dict:
+    """One CUDA graph of ``layers`` Llama-8B-shaped decoder layers (distinct weights and KV, so every
+    layer streams from HBM) on a batch of ``reqs`` decode tokens at context ``ctx``; reports device
+    time per layer.  ``parts`` keeps a subset: gemm | attn | elem | all."""
+    from ..runner.attn_metadata import AttentionMetadata
+    from . import cuda
+    from . import reference as ref
+    pk, tag = peaks()
+    bs = 16
+    nblk_per = -(-(ctx + 1) // bs)
+    nb = reqs * nblk_per + 1
+    T = reqs
+    dev = "cuda"
+    Ws = [dict(qkv=(torch.randn((Hq + 2 * Hkv) * D, H, device=dev) * 0.02).bfloat16(),
+               o=(torch.randn(H, Hq * D, device=dev) * 0.02).bfloat16(),
+               gu=(torch.randn(2 * I, H, device=dev) * 0.02).bfloat16(),
+               down=(torch.randn(H, I, device=dev) * 0.02).bfloat16(),
+               ln1=torch.ones(H, device=dev, dtype=torch.bfloat16), ln2=torch.ones(H, device=dev, dtype=torch.bfloat16),
+               kv=(torch.randn(nb, 2, Hkv, bs, D, device=dev) * 0.5).bfloat16()) for _ in range(layers)]
+    bt = (torch.randperm(nb - 1, device=dev) + 1).to(torch.int32).view(reqs, nblk_per).contiguous()
+    qsl = torch.arange(reqs + 1, device=dev, dtype=torch.int32)
+    sl = torch.full((reqs,), ctx + 1, device=dev, dtype=torch.int32)
+    pos = torch.full((T,), ctx, device=dev, dtype=torch.int32)
+    slots = (bt[:, ctx // bs].long() * bs + ctx % bs).to(torch.int32)
+    inv = ref.rope_inv_freq(D, 500000.0).to(dev)
+    meta = AttentionMetadata(pos, slots, bt, sl, qsl, reqs, T, num_decode_reqs=reqs, max_query_len=1,
+                             max_seq_len=ctx + 1, padded_num_reqs=reqs, padded_num_tokens=T)
+    x0 = torch.randn(T, H, device=dev).bfloat16()
+    res0 = torch.randn(T, H, device=dev).bfloat16()
+    qkv_fix = torch.randn(T, (Hq + 2 * Hkv) * D, device=dev).bfloat16()
+    q_fix = torch.randn(T, Hq, D, device=dev).bfloat16()
+    act_fix = torch.randn(T, I, device=dev).bfloat16()
+    g, a, e = parts in ("all", "gemm"), parts in ("all", "attn"), parts in ("all", "elem")
+
+    def fn():
+        h, res = x0, res0.clone()
+        for w in Ws:
+            if e:
+                h, res = cuda.fused_add_rms_norm(h, res, w["ln1"], 1e-5)
+            qkv = cuda.gemm(h, w["qkv"]) if g else qkv_fix
+            q = cuda.rope_and_cache(qkv, pos, inv, w["kv"], slots, Hq, Hkv, D) if e else q_fix
+            o = cuda.paged_attention(q, w["kv"], meta, D ** -0.5) if a else q
+            h = cuda.gemm(o.view(T, Hq * D), w["o"]) if g else x0
+            if e:
+                h, res = cuda.fused_add_rms_norm(h, res, w["ln2"], 1e-5)
+            if g:
+                h = cuda.gemm(cuda.gemm_swiglu(h, w["gu"]), w["down"])
+        return h
+
+    ms = time_fn(fn, iters, flush=False)
+    w_bytes = 2.0 * ((Hq + 2 * Hkv) * D * H + H * Hq * D + 2 * I * H + H * I)
+    kv_bytes = reqs * (ctx + 1) * 2 * Hkv * D * 2.0
+    byts = (w_bytes if g else 0) + (kv_bytes if a else 0)
+    us = ms * 1e3 / layers
+    roof_us = byts / (pk["hbm_gbs"] * 1e9) * 1e6
+    return {"op": "decode_layer", "parts": parts, "reqs": reqs, "ctx": ctx, "layers": layers,
+            "us_per_layer": round(us, 2), "hbm_roofline_us": round(roof_us, 2),
+            "frac_of_hbm": round(roof_us / us, 3) if us > 0 else None, "peaks": tag,
+            "status": cuda.check_status()}
+
+
 LLAMA8B_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128256, 4096)]
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm-sweep", "attn-decode", "attn-prefill", "all"])
+    ap.add_argument("what", choices=["gemm", "gemm-sweep", "attn-decode", "attn-prefill", "decode-layer", "all"])
     ap.add_argument("--T", type=int, default=64)
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
@@ -151,6 +213,8 @@ def main():
     ap.add_argument("--q", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--impl", default="tcgen05", choices=["tcgen05", "cublas"])
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--parts", default="all,gemm,attn,elem")
     a = ap.parse_args()
     if a.what == "gemm":
         print(json.dumps(bench_gemm(a.T, a.N, a.K, a.iters, a.impl)))
@@ -161,6 +225,9 @@ def main():
                     continue
                 for impl in ("tcgen05", "cublas"):
                     print(json.dumps(bench_gemm(T, N, K, max(5, a.iters // 2), impl, check=(T <= 1024))))
+    if a.what == "decode-layer":
+        for parts in a.parts.split(","):
+            print(json.dumps(bench_decode_layer(a.reqs, a.ctx, a.layers, parts, a.iters)))
     if a.what in ("attn-decode", "all"):
         for reqs, ctx in ((a.reqs, a.ctx),) if a.what == "attn-decode" else ((64, 1100), (256, 2048), (8, 8000)):
             print(json.dumps(bench_attn_decode(reqs, ctx, iters=a.iters)))

@@ -338,28 +338,48 @@ def flush_l2(device=None):
 
 # ------------------------------------------------- fused compute + collective (NVLink P2P)
 class FusedTP:
-    """Heap layout and launch state of the fused row-parallel GEMM + reduction."""
+    """Heap layout and launch state of the fused row-parallel GEMM + reduction.
+
+    Two receive regions and two output buffers alternate between launches, so a rank that runs one
+    launch ahead of a peer never overwrites data the peer still reads."""
 
     MAX_TILES = 8192
 
     def __init__(self, heap, max_tokens: int, max_n: int):
         self.heap = heap
         self.max_elems = max_tokens * max_n
-        nbytes = self.max_elems * 2
-        self.part = heap.alloc("tp_part", nbytes)
-        self.outs = [heap.alloc("tp_out0", nbytes), heap.alloc("tp_out1", nbytes)]
+        self.one_shot_bytes = envs.B200_TP_ONE_SHOT_BYTES
+        self.part_bytes = self.region_bytes(max_tokens, max_n, heap.world, self.one_shot_bytes)
+        self.parts = [heap.alloc("tp_part0", self.part_bytes), heap.alloc("tp_part1", self.part_bytes)]
+        self.outs = [heap.alloc("tp_out0", self.max_elems * 2), heap.alloc("tp_out1", self.max_elems * 2)]
         self.tile_flags = heap.alloc("tp_tile_flags", heap.world * self.MAX_TILES * 4)
         self.done_flags = heap.alloc("tp_done_flags", self.MAX_TILES * 4)
         self.ctrl = torch.zeros(4, dtype=torch.int32, device=heap.device)
         self.flip = 0
 
+    def can_push(self, T: int, N: int) -> bool:
+        """Shapes small enough for the push plane (every rank receives every partial)."""
+        return (envs.B200_TP_DEFER_REDUCE and N % 8 == 0 and N <= 16384
+                and T * N * 2 * (self.heap.world - 1) <= self.one_shot_bytes)
+
+    @staticmethod
+    def region_bytes(max_tokens: int, max_n: int, world: int, one_shot_bytes: int) -> int:
+        # via owners: every tile (padded to 128 x 256) lands in exactly one slab, plus one tile of
+        # rounding per (owner, source); one-shot: `world` matrices of at most one_shot_bytes/(world-1)
+        owners = (max_tokens + 256) * (max_n + 128) * 2 + world * world * 128 * 256 * 2
+        one_shot = world * (one_shot_bytes // max(1, world - 1) + 256)
+        return (max(owners, one_shot) + 255) // 256 * 256
+
     @staticmethod
     def heap_bytes(max_tokens: int, max_n: int, world: int) -> int:
-        return 3 * max_tokens * max_n * 2 + world * FusedTP.MAX_TILES * 4 + FusedTP.MAX_TILES * 4 + (1 << 20)
+        region = FusedTP.region_bytes(max_tokens, max_n, world, envs.B200_TP_ONE_SHOT_BYTES)
+        return (2 * region + 2 * max_tokens * max_n * 2 + world * FusedTP.MAX_TILES * 4 +
+                FusedTP.MAX_TILES * 4 + (1 << 20))
 
 
 def gemm_all_reduce(x, w, heap, mode: int = 0):
-    """Row-parallel ``x @ w.T`` summed over the ranks of ``heap`` inside one kernel."""
+    """Row-parallel ``x @ w.T`` summed over the ranks of ``heap`` inside one kernel
+    (mode 0: the sum lands on every rank; mode 1: only on the owner of each output tile)."""
     _require_bf16(x, w)
     st = heap.fused_tp
     if x.stride(-1) != 1:
@@ -369,18 +389,80 @@ def gemm_all_reduce(x, w, heap, mode: int = 0):
     N = w.shape[0]
     if T * N > st.max_elems:
         raise RuntimeError(f"fused TP buffers hold {st.max_elems} elements, need {T * N}")
-    out = st.outs[st.flip]
+    out, part = st.outs[st.flip], st.parts[st.flip]
     st.flip ^= 1
     ws = Workspace.get(x.device)
     _check(lib().b200_gemm_bf16_fused_reduce(
         _p(x2), _p(w), c_int(T), c_int(N), c_int(K), c_int(x2.stride(0)), c_int(w.stride(0)),
         heap.peers_c, c_int(heap.rank), c_int(heap.world), c_int(mode),
-        c_ulonglong(st.part.offset), c_ulonglong(out.offset), c_ulonglong(st.tile_flags.offset),
+        c_ulonglong(part.offset), c_ulonglong(st.part_bytes), c_ulonglong(st.one_shot_bytes),
+        c_ulonglong(out.offset), c_ulonglong(st.tile_flags.offset),
         c_ulonglong(st.done_flags.offset), c_int(FusedTP.MAX_TILES), _p(st.ctrl), _p(ws.gemm_ws),
         c_size_t(ws.gemm_ws.numel()), _p(ws.gemm_counters), c_int(ws.gemm_counters.numel()), _p(ws.status),
         c_int(_sms), ctypes.c_uint(min(heap.spin_limit, 2**31 - 1)), _stream()), "gemm_fused_reduce")
     count_launch()
     return heap.tensor(out, (T, N), torch.bfloat16)
+
+
+class PendingReduce:
+    """Output of a row-parallel GEMM whose partials have been pushed to every rank but not yet
+    summed.  The consumer (``add_rms_norm`` or ``materialize``) sums them from this rank's receive
+    region, so the all-reduce costs one NVLink store hop and rides in a kernel that runs anyway."""
+
+    def __init__(self, heap, part, T: int, N: int, lead_shape):
+        self.heap, self.part, self.T, self.N = heap, part, T, N
+        self.shape = tuple(lead_shape) + (N,)
+        self.dtype = torch.bfloat16
+        self.device = heap.device
+        self.is_cuda = True
+
+    def _run(self, residual, weight, eps):
+        st = self.heap.fused_tp
+        y = torch.empty((self.T, self.N), dtype=torch.bfloat16, device=self.device)
+        ws = Workspace.get(self.device)
+        stride = (self.T * self.N * 2 + 255) // 256 * 256
+        base = self.heap.local_ptr
+        _check(lib().b200_reduce_pushed_rms_norm(
+            c_void_p(base + self.part.offset), c_ulonglong(stride), c_void_p(base + st.tile_flags.offset),
+            c_int(FusedTP.MAX_TILES), _p(st.ctrl), _p(residual), _p(weight), _p(y), c_int(self.T), c_int(self.N),
+            c_int(self.heap.world), c_float(eps), _p(ws.status),
+            ctypes.c_uint(min(self.heap.spin_limit, 2**31 - 1)), _stream()), "reduce_pushed_rms_norm")
+        count_launch()
+        return y.view(self.shape)
+
+    def add_rms_norm(self, residual, weight, eps):
+        """(RMSNorm(sum + residual) * weight, residual += sum) like ``fused_add_rms_norm``."""
+        _require_bf16(residual, weight)
+        assert residual.is_contiguous() and residual.numel() == self.T * self.N
+        return self._run(residual, weight, eps), residual
+
+    def materialize(self):
+        return self._run(None, None, 0.0)
+
+
+def gemm_push(x, w, heap):
+    """Row-parallel ``x @ w.T`` whose partial is pushed to every rank of ``heap``; returns a
+    :class:`PendingReduce`.  For shapes within ``FusedTP.can_push``."""
+    _require_bf16(x, w)
+    st = heap.fused_tp
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    x2 = x.reshape(-1, x.shape[-1])
+    T, K = x2.shape
+    N = w.shape[0]
+    out, part = st.outs[st.flip], st.parts[st.flip]
+    st.flip ^= 1
+    ws = Workspace.get(x.device)
+    _check(lib().b200_gemm_bf16_fused_reduce(
+        _p(x2), _p(w), c_int(T), c_int(N), c_int(K), c_int(x2.stride(0)), c_int(w.stride(0)),
+        heap.peers_c, c_int(heap.rank), c_int(heap.world), c_int(3),
+        c_ulonglong(part.offset), c_ulonglong(st.part_bytes), c_ulonglong(st.one_shot_bytes),
+        c_ulonglong(out.offset), c_ulonglong(st.tile_flags.offset),
+        c_ulonglong(st.done_flags.offset), c_int(FusedTP.MAX_TILES), _p(st.ctrl), _p(ws.gemm_ws),
+        c_size_t(ws.gemm_ws.numel()), _p(ws.gemm_counters), c_int(ws.gemm_counters.numel()), _p(ws.status),
+        c_int(_sms), ctypes.c_uint(min(heap.spin_limit, 2**31 - 1)), _stream()), "gemm_push")
+    count_launch()
+    return PendingReduce(heap, part, T, N, x.shape[:-1])
 
 
 def p2p_all_reduce(x, heap):

@@ -46,6 +46,9 @@ class UnquantizedLinearMethod(LinearMethodBase):
     def apply_fused_all_reduce(self, layer, x, comm):
         return ops.cuda_ops().gemm_all_reduce(x, layer.weight, comm.heap)
 
+    def apply_push(self, layer, x, comm):
+        return ops.cuda_ops().gemm_push(x, layer.weight, comm.heap)
+
     def weight_bytes(self, layer) -> int:
         return layer.weight.numel() * layer.weight.element_size()
 

@@ -95,7 +95,7 @@ class ModelRunner:
         self._stage_timers = None
         self.structured = None           # StructuredDecodingManager when a request asks for it
         self._step_bitmask = None
-        self.timing_events = None        # list of (start, end) CUDA events per step when enabled
+        self.timing_events = None        # (start event, end event, decode-only?, tokens) per step when enabled
         if envs.B200_STAGE_TIMING and self.is_cuda:
             from ..tracing.stage_timing import RunnerStageTiming
             self._stage_timers = RunnerStageTiming()
@@ -376,7 +376,7 @@ class ModelRunner:
         if ev0 is not None:
             ev1 = torch.cuda.Event(enable_timing=True)
             ev1.record()
-            self.timing_events.append((ev0, ev1))
+            self.timing_events.append((ev0, ev1, bool(p["decode_only"]), n))
         host = self.tokens_host[self._tok_ring]
         self._tok_ring = (self._tok_ring + 1) % len(self.tokens_host)
         ev = None
