@@ -130,6 +130,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
   __shared__ int s_last;
 
   pdl_launch_dependents();      // o_proj may start and prefetch its weights while this grid drains
+  pdl_wait();                   // q and the new KV rows come from the kernel before this grid
   const int h = blockIdx.x, r = p.req_begin + blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.Hq / p.Hkv;
@@ -607,7 +608,7 @@ extern "C" int b200_attn_decode(const void* q, const void* kv, void* out, float*
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       set = true;
     }
-    attn_decode_kernel<128><<<grid, 128, smem, stream>>>(p);
+    B200_CUDA_CHECK(launch_pdl(attn_decode_kernel<128>, grid, dim3(128), smem, stream, p));
   } else if (D == 64) {
     const int smem = 4 * 3 * 2 * 16 * 64 * 2 < 4 * 16 * 64 * 4 ? 4 * 16 * 64 * 4 : 4 * 3 * 2 * 16 * 64 * 2;
     static bool set = false;
@@ -616,7 +617,7 @@ extern "C" int b200_attn_decode(const void* q, const void* kv, void* out, float*
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       set = true;
     }
-    attn_decode_kernel<64><<<grid, 128, smem, stream>>>(p);
+    B200_CUDA_CHECK(launch_pdl(attn_decode_kernel<64>, grid, dim3(128), smem, stream, p));
   } else {
     b200_set_last_error("attn_decode: head_dim must be 64 or 128", __FILE__, __LINE__);
     return -1;

@@ -347,3 +347,23 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
   } while (0)
 
 extern "C" void b200_set_last_error(const char* msg, const char* file, int line);
+extern "C" int b200_pdl_enabled();
+
+// Launch with the programmatic-stream-serialization attribute: the grid may be scheduled while the
+// previous kernel of the stream is still draining.  The kernel must execute griddepcontrol.wait
+// (pdl_wait()) before it reads anything an earlier kernel wrote.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = b200_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

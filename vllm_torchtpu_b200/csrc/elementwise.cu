@@ -17,6 +17,7 @@ __global__ void rms_norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
                                 const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int H,
                                 float eps) {
   pdl_launch_dependents();      // the GEMM that follows may start and prefetch its weights now
+  pdl_wait();                   // this grid may itself have started early
   __shared__ float red[32];
   extern __shared__ __align__(16) uint8_t dyn[];
   bf16x8* row_cache = reinterpret_cast<bf16x8*>(dyn);     // the (summed) row, kept for the second pass
@@ -134,6 +135,8 @@ __global__ void rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const i
                                   long long num_slots) {
   constexpr int EPL = D / 32;               // elements per lane
   __shared__ float cs[D];                   // cos[0..rot_pairs) | sin[0..rot_pairs)
+  pdl_launch_dependents();
+  pdl_wait();                               // qkv comes from the GEMM before this grid
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const float pos = (float)positions[t];
@@ -226,11 +229,13 @@ extern "C" int b200_rms_norm(const void* x, void* residual, const void* w, void*
   if (threads < 32) threads = 32;
   size_t smem = (size_t)H * 2;
   if (residual)
-    rms_norm_kernel<true><<<T, threads, smem, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)residual,
-                                                        (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps);
+    B200_CUDA_CHECK(launch_pdl(rms_norm_kernel<true>, dim3(T), dim3(threads), smem, stream,
+                               (const __nv_bfloat16*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)w,
+                               (__nv_bfloat16*)y, H, eps));
   else
-    rms_norm_kernel<false><<<T, threads, smem, stream>>>((const __nv_bfloat16*)x, nullptr,
-                                                         (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps);
+    B200_CUDA_CHECK(launch_pdl(rms_norm_kernel<false>, dim3(T), dim3(threads), smem, stream,
+                               (const __nv_bfloat16*)x, (__nv_bfloat16*)nullptr, (const __nv_bfloat16*)w,
+                               (__nv_bfloat16*)y, H, eps));
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
@@ -286,10 +291,10 @@ extern "C" int b200_rope_and_cache(const void* qkv, const int* positions, const 
   int heads = Hq + 2 * Hkv;
   int threads = heads >= 8 ? 256 : heads * 32;
 #define LAUNCH(DD, CT)                                                                                       \
-  rope_cache_kernel<DD, CT><<<T, threads, 0, stream>>>(                                                      \
+  B200_CUDA_CHECK(launch_pdl(rope_cache_kernel<DD, CT>, dim3(T), dim3(threads), 0, stream,                   \
       (const __nv_bfloat16*)qkv, positions, inv_freq, rot_pairs, slot_mapping, (__nv_bfloat16*)q_out,        \
       (CT*)kv_cache, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, eps, Hq, Hkv,           \
-      block_size, interleaved, 1.f / k_scale, 1.f / v_scale, num_slots)
+      block_size, interleaved, 1.f / k_scale, 1.f / v_scale, num_slots))
   if (cache_elem_bytes == 2) {
     if (D == 128) LAUNCH(128, __nv_bfloat16);
     else if (D == 64) LAUNCH(64, __nv_bfloat16);

@@ -873,7 +873,6 @@ static int cached_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_
   return 0;
 }
 
-static int g_use_pdl = 1;
 
 // How many clusters of `splits` CTAs of this kernel can be resident at once (GPC granularity).
 template <int BN>
@@ -948,7 +947,7 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gem
     attr[na].val.clusterDim.z = 1;
     ++na;
   }
-  if (g_use_pdl) {
+  if (b200_pdl_enabled()) {
     // let this grid start (and prefetch weights) while the previous kernel of the stream drains
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[na].val.programmaticStreamSerializationAllowed = 1;
@@ -1225,4 +1224,3 @@ extern "C" int b200_grouped_gemm_bf16(const void* X, const void* W, void* Y, con
   }
 }
 
-extern "C" void b200_set_pdl(int on) { b200::g_use_pdl = on ? 1 : 0; }

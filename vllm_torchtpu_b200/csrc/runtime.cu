@@ -17,6 +17,12 @@ extern "C" const char* b200_get_last_error() { return g_last_error; }
 
 extern "C" int b200_version() { return 1; }
 
+// Programmatic dependent launch: kernels launched through launch_pdl() may start while the previous
+// kernel of the stream drains (they call griddepcontrol.wait before touching its results).
+static int g_b200_pdl = 1;
+extern "C" int b200_pdl_enabled() { return g_b200_pdl; }
+extern "C" void b200_set_pdl(int on) { g_b200_pdl = on ? 1 : 0; }
+
 extern "C" int b200_device_info(int device, int* sms, int* cc_major, int* cc_minor, size_t* smem_optin) {
   cudaDeviceProp prop;
   B200_CUDA_CHECK(cudaGetDeviceProperties(&prop, device));

@@ -37,6 +37,7 @@ __device__ __forceinline__ int raster_tile(int n_tile, int t_tile, int n_tiles, 
 __global__ void __launch_bounds__(RP_THREADS)
 reduce_pushed_kernel(const ReducePushedParams p) {
   pdl_launch_dependents();             // the next GEMM may start prefetching its weights
+  pdl_wait();                          // the producer GEMM (and its epoch bump) is complete from here on
   __shared__ float red[32];
   __shared__ int s_ok;
   const int t = blockIdx.x;
@@ -153,7 +154,6 @@ extern "C" int b200_reduce_pushed_rms_norm(const void* recv, unsigned long long 
   p.t_tiles = (T + p.bn - 1) / p.bn;
   p.eps = eps;
   p.spin_limit = spin_limit;
-  reduce_pushed_kernel<<<T, RP_THREADS, 0, stream>>>(p);
-  B200_CUDA_CHECK(cudaGetLastError());
+  B200_CUDA_CHECK(launch_pdl(reduce_pushed_kernel, dim3(T), dim3(RP_THREADS), 0, stream, p));
   return 0;
 }

@@ -64,6 +64,21 @@ class Workspace:
         self.attn_counters = torch.zeros(65536, dtype=torch.int32, device=device)
         self.status = torch.zeros(16, dtype=torch.int32, device=device)
         self.rng_step = torch.zeros(1, dtype=torch.int64, device=device)
+        self._attn_out: dict = {}
+
+    def attn_out(self, T: int, Hq: int, D: int) -> torch.Tensor:
+        """Attention output buffer for (T, Hq, D): two per shape, used alternately (consecutive layers
+        consume the output before the next attention runs on the same stream)."""
+        key = (T, Hq, D)
+        ring = self._attn_out.get(key)
+        if ring is None:
+            if torch.cuda.is_current_stream_capturing():
+                # memory allocated during capture belongs to that graph: do not keep it
+                return torch.zeros(T, Hq, D, dtype=torch.bfloat16, device=self.device)
+            ring = self._attn_out[key] = [
+                [torch.zeros(T, Hq, D, dtype=torch.bfloat16, device=self.device) for _ in range(2)], 0]
+        ring[1] ^= 1
+        return ring[0][ring[1]]
 
     @classmethod
     def get(cls, device) -> "Workspace":
@@ -233,9 +248,15 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
         raise NotImplementedError("fp8 KV cache attention kernel")
     T, Hq, D = q.shape
     nb, _, Hkv, bs, _ = kv_cache.shape
-    out = torch.zeros_like(q)
-    lse = torch.full((T, Hq), float("-inf"), dtype=torch.float32, device=q.device) if return_lse else None
     ws = Workspace.get(q.device)
+    if return_lse:
+        # callers that merge partial results keep several outputs alive: fresh, fully defined tensors
+        out = torch.zeros_like(q)
+        lse = torch.full((T, Hq), float("-inf"), dtype=torch.float32, device=q.device)
+    else:
+        # rows of padded requests are never written; a reused zero-initialised buffer keeps them
+        # finite without a fill kernel per layer
+        out, lse = ws.attn_out(T, Hq, D), None
     G = Hq // Hkv
     R = meta.num_reqs
     R_launch = meta.padded_num_reqs if meta.padded_num_reqs is not None else R
