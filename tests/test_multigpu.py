@@ -56,3 +56,19 @@ def test_tp2_engine_fused_plane_equals_nccl_plane():
     # both planes sum bf16 partials in fp32 in rank order, so the tokens agree
     same = sum(a == b for a, b in zip(fused["tokens"], nccl["tokens"]))
     assert same >= 3, (fused, nccl)
+
+
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_fused_expert_parallel_plane_matches_dense_moe(nproc):
+    _need(nproc)
+    r = _run("ep_fused_worker.py", nproc)
+    assert "EP_FUSED_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_tp2_moe_engine_fused_ep_plane_equals_gather_plane():
+    _need(2)
+    fused = _tokens(_run("tp_engine_worker.py", 2, "--moe"))
+    gathered = _tokens(_run("tp_engine_worker.py", 2, "--moe", env={"B200_MOE_FUSED_EP": "0"}))
+    assert fused["status"] == 0 and gathered["status"] == 0
+    same = sum(a == b for a, b in zip(fused["tokens"], gathered["tokens"]))
+    assert same >= 3, (fused, gathered)

@@ -20,8 +20,14 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     cfg = ModelConfig(name="tp-test", num_layers=2, hidden_size=1024, num_q_heads=8, num_kv_heads=8, head_dim=128,
                       intermediate_size=2048, vocab_size=4096, max_model_len=512, dtype=torch.bfloat16)
+    ep = "--moe" in sys.argv
+    if ep:
+        cfg = ModelConfig(name="ep-test", architecture="qwen3_moe", num_layers=2, hidden_size=1024, num_q_heads=8,
+                          num_kv_heads=8, head_dim=128, intermediate_size=2048, vocab_size=4096,
+                          max_model_len=512, dtype=torch.bfloat16, qk_norm=True, num_experts=8,
+                          num_experts_per_tok=2, moe_intermediate_size=256)
     llm = LLM(cfg, device="cuda", tensor_parallel_size=world, max_num_seqs=8, max_num_batched_tokens=256,
-              num_gpu_blocks_override=256, enforce_eager="--eager" in sys.argv)
+              num_gpu_blocks_override=256, enforce_eager="--eager" in sys.argv, enable_expert_parallel=ep)
     rng = np.random.RandomState(0)
     prompts = [rng.randint(0, 4096, size=n).tolist() for n in (8, 33, 70, 150)]
     outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))

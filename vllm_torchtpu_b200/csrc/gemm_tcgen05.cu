@@ -80,6 +80,11 @@ struct GemmParams {
   unsigned long long tile_flag_off;      // heap offset: int[world][max_tiles], written by producers at the owner
   unsigned long long done_flag_off;      // heap offset: int[max_tiles], written by the owner at every reader
   int max_tiles;
+  // ---- routed rows (ar_mode 4, expert-parallel combine): output row r goes to the return slot
+  // row_route[r] = (rank, slot) in that rank's heap at route_ret_off; done_flag_off then names the
+  // int[world] "returned" flags that the last CTA raises at every rank
+  const int2* row_route;
+  unsigned long long route_ret_off;
   int* epoch_ptr;                        // local: epoch of the last completed fused launch
   int* cta_done;                         // local: CTA exit counter
   unsigned int spin_limit;
@@ -459,6 +464,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
+      } else if (p.row_route != nullptr) {
+        // expert-parallel combine: every output row is stored into the return slot of the rank that
+        // sent the token (a peer's heap or this rank's own)
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (c0 >= t_valid) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c0, r);
+          tmem_ld_wait();
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (c0 + j < t_valid) {
+                const int2 rt = __ldg(p.row_route + t0 + c0 + j);
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peer[rt.x] + p.route_ret_off) +
+                                     (size_t)rt.y * p.N + n;
+                *dst = __float2bfloat16(__uint_as_float(r[j]));
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+        __threadfence_system();
       } else if (p.splits == 1 && fused && p.ar_mode < 2) {
         // partial tile -> the owner's slab [BN][BM] bf16, 32 columns (8 KB) per bulk copy
         uint8_t* slab = reinterpret_cast<uint8_t*>(tile_dst<BN>(p, wk, 0).base);
@@ -781,7 +811,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const int arrived = atomicAdd(p.cta_done, 1) + 1;
     if (arrived == (int)gridDim.x) {
       *p.cta_done = 0;
-      *p.epoch_ptr = epoch;       // every CTA of this launch has read the old value by now
+      if (p.ar_mode == 4) {
+        // every CTA fenced its routed stores before it arrived: tell all ranks their rows are back
+        __threadfence_system();
+        const int ep_epoch = *reinterpret_cast<volatile int*>(p.epoch_ptr);
+        for (int r = 0; r < p.world; ++r)
+          st_release_sys(reinterpret_cast<int*>(p.peer[r] + p.done_flag_off) + p.rank, ep_epoch);
+      } else {
+        *p.epoch_ptr = epoch;       // every CTA of this launch has read the old value by now
+      }
       __threadfence();
     }
   }
@@ -932,7 +970,7 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gem
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     attr_set = true;
   }
-  const int threads = (p.world > 1 && p.ar_mode != 3) ? NUM_THREADS_FUSED : NUM_THREADS;
+  const int threads = (p.world > 1 && p.ar_mode < 3) ? NUM_THREADS_FUSED : NUM_THREADS;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(threads);
@@ -1221,6 +1259,48 @@ extern "C" int b200_grouped_gemm_bf16(const void* X, const void* W, void* Y, con
     case 64: return launch_gemm<64>(tmW, tmX, p, grid, stream);
     case 128: return launch_gemm<128>(tmW, tmX, p, grid, stream);
     default: return launch_gemm<256>(tmW, tmX, p, grid, stream);
+  }
+}
+
+// Grouped GEMM whose output rows are scattered to the ranks that sent the tokens (expert-parallel
+// combine inside the epilogue): row r of the product goes to slot route[r].y of rank route[r].x,
+// at heap offset ret_off, row length N.  The last CTA raises ret_flags[rank] (heap offset
+// ret_flag_off, int[world]) at every rank with the epoch in ctrl[0]; ctrl[1] is the CTA counter.
+extern "C" int b200_grouped_gemm_bf16_routed(const void* X, const void* W, const int* group_off, int num_groups,
+                                             int R, int N, int K, int avg_rows_hint, void* const* peers,
+                                             int rank, int world, const void* route,
+                                             unsigned long long ret_off, unsigned long long ret_flag_off,
+                                             int* ctrl, int* status, int num_sms, cudaStream_t stream) {
+  using namespace b200;
+  if (R <= 0 || N <= 0 || K <= 0 || num_groups <= 0) return 0;
+  if (K % 8 || N % BM || num_groups > MAX_GROUPS || world < 2 || world > 8) {
+    b200_set_last_error("grouped_gemm_routed: K % 8 == 0, N % 128 == 0, <= 1024 groups, 2 <= world <= 8",
+                        __FILE__, __LINE__);
+    return -3;
+  }
+  int bn = avg_rows_hint <= 32 ? 32 : (avg_rows_hint <= 64 ? 64 : (avg_rows_hint <= 128 ? 128 : 256));
+  GemmParams p;
+  init_params(p, nullptr, R, N, K, N, bn, status);
+  p.group_off = group_off;
+  p.num_groups = num_groups;
+  p.w_rows_per_group = N;
+  p.w_evict_first = avg_rows_hint <= bn ? 1 : 0;
+  p.world = world; p.rank = rank; p.ar_mode = 4;
+  for (int i = 0; i < 8; ++i) p.peer[i] = i < world ? (uint8_t*)peers[i] : nullptr;
+  p.row_route = reinterpret_cast<const int2*>(route);
+  p.route_ret_off = ret_off;
+  p.done_flag_off = ret_flag_off;
+  p.epoch_ptr = ctrl; p.cta_done = ctrl + 1;
+  CUtensorMap tmW, tmX;
+  int rc = cached_tmap(&tmW, W, (uint64_t)num_groups * N, (uint64_t)K, (uint64_t)K * 2, BM);
+  if (rc) return rc;
+  rc = cached_tmap(&tmX, X, (uint64_t)R, (uint64_t)K, (uint64_t)K * 2, (uint32_t)bn);
+  if (rc) return rc;
+  switch (bn) {
+    case 32: return launch_gemm<32>(tmW, tmX, p, num_sms, stream);
+    case 64: return launch_gemm<64>(tmW, tmX, p, num_sms, stream);
+    case 128: return launch_gemm<128>(tmW, tmX, p, num_sms, stream);
+    default: return launch_gemm<256>(tmW, tmX, p, num_sms, stream);
   }
 }
 

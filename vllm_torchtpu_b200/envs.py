@@ -86,6 +86,8 @@ _decl("B200_TP_DEFER_REDUCE", bool, True,
       "small row-parallel outputs are pushed to every rank and summed inside the following add+RMSNorm kernel")
 _decl("B200_SYMM_HEAP_MB", int, 512, "size of the per-rank symmetric heap")
 _decl("B200_MOE_FUSED_EP", bool, True, "dispatch/combine inside the expert kernel over peer memory")
+_decl("B200_MOE_EP_CAPACITY_FACTOR", float, 2.0,
+      "fused EP plane: rows an owner can receive per call, as a multiple of max_tokens * top_k")
 _decl("B200_MOE_FUSED_EP_MIN_TOKENS", int, 0, "use the AG/RS path below this many tokens")
 _decl("B200_MOE_SEQUENCE_PARALLEL", bool, False, "reduce-scatter after attention, all-gather before experts")
 _decl("B200_MOE_TOPK_WEIGHTS_FLOAT32", bool, True, "keep routing weights in fp32")

@@ -11,7 +11,7 @@ permutation (``expert_placement``).  Three data planes, as in the reference
 * EP, all-gather/reduce-scatter plane: ``DeviceCommunicator.dispatch`` gathers
   tokens, every rank runs its experts on all tokens, ``combine`` reduce-scatters;
 * EP, fused plane: the dispatch/combine all-to-all runs inside the expert kernel
-  over NVLink peer memory (``ops.cuda.moe_ep_fused``).
+  over NVLink peer memory (``ops.cuda.moe_experts_ep``).
 """
 from __future__ import annotations
 
@@ -96,9 +96,27 @@ class FusedMoE:
             return y
         comm = get_ep_comm()
         if (x.is_cuda and envs.B200_MOE_FUSED_EP and comm.heap is not None
+                and getattr(comm.heap, "ep_state", None) is not None
                 and x.shape[0] >= envs.B200_MOE_FUSED_EP_MIN_TOKENS and hasattr(self.method, "apply_fused_ep")):
-            return self.method.apply_fused_ep(self, x, topk_ids, topk_w, comm)
+            return self._forward_fused_ep(x, topk_ids, topk_w, comm)
         # all-gather / reduce-scatter plane: rows must be equal on every rank (DP lockstep pads them)
         hx, hw, hi = comm.dispatch(x, topk_w, topk_ids)
         y = self.method.apply(self, hx, hi, hw)
         return comm.combine(y)
+
+    def _forward_fused_ep(self, x, topk_ids, topk_w, comm):
+        """Fused dispatch/combine plane.  The ranks of a TP group hold identical tokens, so each
+        dispatches one contiguous slice of them and the slices are all-gathered afterwards (the
+        sequence-parallel MoE dataflow of the reference, models/vllm/qwen3_5_patch.py:95-141)."""
+        st = get_state()
+        tp = st.tp.size
+        if tp == 1:
+            return self.method.apply_fused_ep(self, x, topk_ids, topk_w, comm)
+        T = x.shape[0]
+        chunk = -(-T // tp)
+        lo = min(T, st.tp.rank_in_group * chunk)
+        hi = min(T, lo + chunk)
+        y = self.method.apply_fused_ep(self, x[lo:hi], topk_ids[lo:hi], topk_w[lo:hi], comm)
+        if hi - lo < chunk:
+            y = torch.cat([y, y.new_zeros(chunk - (hi - lo), y.shape[1])], 0)
+        return get_tp_comm().all_gather(y, 0)[:T]

@@ -508,8 +508,8 @@ def p2p_all_reduce(x, heap):
     return x
 
 
-from .cuda_moe import (gemm_swiglu, grouped_gemm, moe_experts, moe_permute, moe_route,  # noqa: E402,F401
-                       moe_unpermute)
+from .cuda_moe import (EpState, gemm_swiglu, grouped_gemm, moe_experts, moe_experts_ep,  # noqa: E402,F401
+                       moe_permute, moe_route, moe_unpermute)
 from .cuda_fp8 import (fp8_block_gemm, fp8_rowwise_gemm, grouped_fp8_gemm, moe_experts_fp8,  # noqa: E402,F401
                        quant_act_1x128)
 from .cuda_gdn import gdn_forward  # noqa: E402,F401

@@ -97,3 +97,86 @@ def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0):
     act = grouped_gemm(x_perm, w13, group_off, True, avg)
     y = grouped_gemm(act, w2, group_off, False, avg)
     return moe_unpermute(y, inv_pos, topk_w.contiguous(), T)
+
+
+# ----------------------------------------------------------------- expert parallel, fused plane
+class EpState:
+    """Heap regions and local scratch of the fused expert-parallel plane (one per EP heap).
+
+    ``cap`` rows can be received per call; a call that would need more sets the device status word
+    (``ops.cuda.check_status``) and drops the excess rows.  The worst case is world * T_max * k rows;
+    the default keeps ``capacity_factor`` times the balanced load."""
+
+    def __init__(self, heap, max_tokens: int, top_k: int, hidden: int, inter: int, num_experts: int,
+                 capacity_factor: float):
+        import ctypes
+        world = heap.world
+        self.heap, self.max_tokens, self.k, self.H, self.E = heap, max_tokens, top_k, hidden, num_experts
+        worst = world * max_tokens * top_k
+        self.cap = int(min(worst, max(1024, capacity_factor * max_tokens * top_k)))
+        self.cnt = heap.alloc("ep_cnt", world * num_experts * 4)
+        self.cnt_flag = heap.alloc("ep_cnt_flag", world * 4)
+        self.data_flag = heap.alloc("ep_data_flag", world * 4)
+        self.ret_flag = heap.alloc("ep_ret_flag", world * 4)
+        self.recv_x = heap.alloc("ep_recv_x", self.cap * hidden * 2)
+        self.recv_route = heap.alloc("ep_recv_route", self.cap * 8)
+        self.ret = heap.alloc("ep_ret", max_tokens * top_k * hidden * 2)
+        self.layout = (ctypes.c_ulonglong * 7)(self.cnt.offset, self.cnt_flag.offset, self.data_flag.offset,
+                                               self.ret_flag.offset, self.recv_x.offset, self.recv_route.offset,
+                                               self.ret.offset)
+        dev = heap.device
+        self.ctrl = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.fill = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.group_off = torch.zeros(num_experts // world + 1, dtype=torch.int32, device=dev)
+        self.act = torch.zeros(self.cap, inter, dtype=torch.bfloat16, device=dev)
+
+    @staticmethod
+    def heap_bytes(max_tokens, top_k, hidden, num_experts, world, capacity_factor) -> int:
+        worst = world * max_tokens * top_k
+        cap = int(min(worst, max(1024, capacity_factor * max_tokens * top_k)))
+        return (cap * hidden * 2 + cap * 8 + max_tokens * top_k * hidden * 2 + world * num_experts * 4
+                + (1 << 20))
+
+
+def moe_experts_ep(x, w13, w2, topk_ids, topk_w, heap, num_experts: int):
+    """MoE expert computation under expert parallelism with the dispatch / combine all-to-all done by
+    NVLink stores inside the pipeline: rows are PUT into the owners' receive buffers, the owners run
+    the grouped tcgen05 GEMMs on what they received, and the epilogue of the second GEMM stores each
+    output row into the return slot of the rank the token came from."""
+    import ctypes
+    from ctypes import c_size_t, c_ulonglong
+    _c._require_bf16(x, w13, w2)
+    st = heap.ep_state
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E_local, I = w13.shape[0], w2.shape[2]
+    if T > st.max_tokens or k != st.k or H != st.H or num_experts != st.E:
+        raise RuntimeError("fused EP plane was configured for a different shape")
+    L = _c.lib()
+    ws = _c.Workspace.get(x.device)
+    spin = ctypes.c_uint(min(heap.spin_limit, 2**31 - 1))
+    x = x.contiguous()
+    ids = topk_ids.contiguous()
+    _c._check(L.b200_ep_dispatch(heap.peers_c, c_int(heap.rank), c_int(heap.world), st.layout, _c._p(st.ctrl),
+                                 _c._p(st.fill), _c._p(st.group_off), _c._p(x), _c._p(ids), c_int(T), c_int(k),
+                                 c_int(H), c_int(num_experts), c_int(st.cap), _c._p(ws.status), spin,
+                                 _c._stream()), "ep_dispatch")
+    count_launch(3)
+    recv_x = heap.tensor(st.recv_x, (st.cap, H), torch.bfloat16)
+    avg = max(1, (T * k) // max(1, E_local))
+    grouped_gemm(recv_x, w13, st.group_off, True, avg, out=st.act)
+    _c._check(L.b200_grouped_gemm_bf16_routed(
+        _c._p(st.act), _c._p(w2), _c._p(st.group_off), c_int(E_local), c_int(st.cap), c_int(H), c_int(I),
+        c_int(avg), heap.peers_c, c_int(heap.rank), c_int(heap.world),
+        c_void_p(heap.local_ptr + st.recv_route.offset), c_ulonglong(st.ret.offset),
+        c_ulonglong(st.ret_flag.offset), _c._p(st.ctrl), _c._p(ws.status), c_int(_c._sms), _c._stream()),
+        "grouped_gemm_routed")
+    count_launch()
+    out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+    _c._check(L.b200_ep_combine(c_void_p(heap.local_ptr), c_ulonglong(st.ret.offset),
+                                c_ulonglong(st.ret_flag.offset), _c._p(st.ctrl), _c._p(ids),
+                                _c._p(topk_w.contiguous()), _c._p(out), c_int(T), c_int(k), c_int(H),
+                                c_int(num_experts), c_int(heap.world), _c._p(ws.status), spin, _c._stream()),
+              "ep_combine")
+    count_launch()
+    return out

@@ -152,6 +152,23 @@ def ensure_tp_heap(max_tokens: int, max_n: int):
     return comm.heap
 
 
+def ensure_ep_heap(max_tokens: int, top_k: int, hidden: int, inter: int, num_experts: int):
+    """Create the EP group's symmetric heap with the regions of the fused dispatch/combine plane."""
+    global _heap_min_bytes
+    st = get_state()
+    if (st.ep.size == 1 or not torch.cuda.is_available() or envs.B200_TP_COMM == "nccl"
+            or not envs.B200_MOE_FUSED_EP):
+        return None
+    from ..ops import cuda_moe
+    factor = envs.B200_MOE_EP_CAPACITY_FACTOR
+    need = cuda_moe.EpState.heap_bytes(max_tokens, top_k, hidden, num_experts, st.ep.size, factor) + 16 * 2**20
+    _heap_min_bytes = max(_heap_min_bytes, need)
+    comm = get_ep_comm()
+    if comm.heap is not None and getattr(comm.heap, "ep_state", None) is None:
+        comm.heap.ep_state = cuda_moe.EpState(comm.heap, max_tokens, top_k, hidden, inter, num_experts, factor)
+    return comm.heap
+
+
 def _heap_for(group: Group):
     """Symmetric heap of a group, created on first use on GPUs when fused collectives are on."""
     if group.size == 1 or not torch.cuda.is_available() or envs.B200_TP_COMM == "nccl":

@@ -52,6 +52,7 @@ class SymmetricHeap:
         self.spin_limit = int(envs.B200_SPIN_LIMIT)
         self.ar_stage_bytes = 32 * 2**20
         self.fused_tp = None
+        self.ep_state = None             # fused expert-parallel plane (ops.cuda_moe.EpState)
 
     def configure_fused_tp(self, max_tokens: int, max_n: int) -> None:
         from ..ops import cuda

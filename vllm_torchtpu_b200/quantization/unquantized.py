@@ -88,5 +88,8 @@ class UnquantizedMoEMethod:
             return ops.cuda_ops().moe_experts(x, moe.w13, moe.w2, topk_ids, topk_w, moe.expert_range[0])
         return ops.ref.moe_experts(x, moe.w13, moe.w2, topk_ids, topk_w, moe.expert_range[0])
 
+    def apply_fused_ep(self, moe, x, topk_ids, topk_w, comm):
+        return ops.cuda_ops().moe_experts_ep(x, moe.w13, moe.w2, topk_ids, topk_w, comm.heap, moe.num_experts)
+
     def weight_bytes(self, moe) -> int:
         return sum(t.numel() * t.element_size() for t in (moe.w13, moe.w2))

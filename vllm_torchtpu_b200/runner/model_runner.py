@@ -118,6 +118,12 @@ class ModelRunner:
         if self.is_cuda and st.tp.size > 1:
             from ..parallel.communicator import ensure_tp_heap
             ensure_tp_heap(self.max_tokens, self.mcfg.hidden_size)
+        if self.is_cuda and st.expert_parallel and st.ep.size > 1 and getattr(self.mcfg, "num_experts", 0):
+            from ..parallel.communicator import ensure_ep_heap
+            # tokens are identical on the ranks of a TP group: each of them dispatches one slice
+            per_rank = -(-self.max_tokens // st.tp.size)
+            ensure_ep_heap(per_rank, self.mcfg.num_experts_per_tok, self.mcfg.hidden_size,
+                           self.mcfg.moe_intermediate_size, self.mcfg.num_experts)
         logger.info("model %s loaded: %.2f GB weights on this rank in %.1fs", self.mcfg.name,
                     self.model.weight_bytes() / 1e9, time.time() - t0)
 
