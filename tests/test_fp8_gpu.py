@@ -58,3 +58,21 @@ def test_fp8_moe_experts():
     want = ref.moe_experts(x, d13, d2, ids, w, 0)
     err = (got.float() - want.float()).abs().max().item()
     assert err <= 6e-2 * want.float().abs().max().item() + 2e-2, err     # activations are fp8 in the kernel path
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 256, 512), (48, 1024, 4096), (64, 4096, 1024), (200, 640, 2048)])
+def test_int8_w8a8_gemm_matches_reference(T, N, K):
+    from vllm_torchtpu_b200.ops import cuda
+    from vllm_torchtpu_b200.quantization import int8 as q8
+    g = torch.Generator(device="cuda").manual_seed(T + N)
+    x = torch.randn(T, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    wq, ws = q8.quantize_weight_int8(w)
+    xq, xs = cuda.quant_act_int8(x)
+    rq, rs = q8.quantize_act_int8(x)
+    assert (xq.int() - rq.int()).abs().max() <= 1                    # rounding ties only
+    torch.testing.assert_close(xs, rs.squeeze(-1), rtol=1e-5, atol=1e-8)
+    got = cuda.int8_gemm(x, wq, ws)
+    want = q8.int8_gemm_reference(x, wq, ws)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2 * want.float().abs().max().item())
+    assert cuda.check_status() == 0

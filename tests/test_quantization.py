@@ -78,3 +78,20 @@ def test_linear_methods_apply_on_cpu(name):
     assert lin.weight_bytes() < 128 * 256 * 2
     assert get_linear_method(QuantConfig(name, ignored_layers=("lm_head",)), "lm_head").__class__.__name__ == \
         "UnquantizedLinearMethod"
+
+
+def test_turboquant_4bit_reference_roundtrip():
+    from vllm_torchtpu_b200.quantization import turboquant as tq
+    g = torch.Generator().manual_seed(0)
+    k = torch.randn(64, 128, generator=g)
+    v = torch.randn(64, 128, generator=g) * 0.5 + 0.1
+    h = tq.hadamard(128)
+    torch.testing.assert_close(h @ h.t(), torch.eye(128), atol=1e-5, rtol=0)
+    kc, kn, vc, vm = tq.encode(k, v)
+    assert kc.shape == (64, 64) and kc.dtype == torch.uint8 and vm.shape == (64, 2)
+    kd, vd = tq.decode(kc, kn, vc, vm, dtype=torch.float32)
+    cos = torch.nn.functional.cosine_similarity(kd, k, dim=-1)
+    assert cos.min() > 0.97                       # 4-bit Lloyd-Max keys: ~1 % relative MSE
+    assert (vd - v).abs().max() < (v.amax(-1) - v.amin(-1)).max() / 15 * 0.51 + 0.02
+    q8 = tq.quantize_kv_fp8(v.bfloat16(), 0.02)
+    assert (tq.dequantize_kv_fp8(q8, 0.02).float() - v).abs().max() < 0.1

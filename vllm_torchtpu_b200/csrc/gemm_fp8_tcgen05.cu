@@ -14,6 +14,10 @@
 // are N (32/64/128), so decode batches keep full MMA rows.  Split-K runs as a thread-block
 // cluster with a DSMEM reduction; grouped (per-expert) mode takes device-side row offsets.
 //
+// The same kernel, instantiated with KIND = 1, is the int8 W8A8 GEMM (per-output-channel weight
+// scales, per-token activation scales): tcgen05.mma kind::i8 gives exact s32 sums per K block, the
+// epilogue warps add them up in fp32 and apply ws[n] * xs[t] once at the end.
+//
 // Semantics of the reference's block-wise quantised matmul
 // (reference: src/vllm_torchtpu/layers/adapter/linear_common.py:69-133, kernels/megablox/gmm_v2.py).
 #include <cstring>
@@ -94,7 +98,7 @@ __device__ __forceinline__ Work get_work(int w, const Params& p, const int* s_pr
   return k;
 }
 
-template <int BN>
+template <int BN, int KIND>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                       const Params p) {
@@ -169,7 +173,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_e4m3(BM, BN);
+      constexpr uint32_t idesc = KIND == 1 ? umma_idesc_s8(BM, BN) : umma_idesc_e4m3(BM, BN);
       int s = 0;
       uint32_t ph = 0;
       uint32_t pc = 0;                         // K blocks issued by this CTA (selects the partial buffer)
@@ -188,8 +192,10 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
           const uint64_t adesc = umma_desc_k_sw128(a_addr);
           const uint64_t bdesc = umma_desc_k_sw128(a_addr + C::A_BYTES);
 #pragma unroll
-          for (int q = 0; q < 4; ++q)          // 4 x (K = 32 fp8) per 128-byte row; a fresh sum per block
-            umma_f8(tmem_base + pb * BN, adesc + 2 * q, bdesc + 2 * q, idesc, q > 0 ? 1u : 0u);
+          for (int q = 0; q < 4; ++q) {        // 4 x (K = 32 bytes) per 128-byte row; a fresh sum per block
+            if (KIND == 1) umma_i8(tmem_base + pb * BN, adesc + 2 * q, bdesc + 2 * q, idesc, q > 0 ? 1u : 0u);
+            else umma_f8(tmem_base + pb * BN, adesc + 2 * q, bdesc + 2 * q, idesc, q > 0 ? 1u : 0u);
+          }
           umma_commit(&empty[s]);
           umma_commit(&pfull[pb]);
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -208,7 +214,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       for (int c = 0; c < BN; ++c) acc[c] = 0.f;
       for (int kb = k.kb0; kb < k.kb1; ++kb, ++pc) {
         const int pb = pc & 1;
-        const float sw = p.w_scale[(size_t)k.ws_row * p.ws_ld + kb];
+        const float sw = KIND == 1 ? 1.f : p.w_scale[(size_t)k.ws_row * p.ws_ld + kb];
         if (!mbar_wait(&pfull[pb], (pc >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
         const uint32_t taddr = tmem_base + pb * BN + ((uint32_t)(q * 32) << 16);
@@ -216,13 +222,16 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         for (int c0 = 0; c0 < BN; c0 += 32) {
           // lane j fetches the activation scale of column c0 + j; it is handed round by shuffle
           const int t = k.t_row + c0 + lane;
-          const float mine = (c0 + lane < k.t_valid) ? sw * p.x_scale[(size_t)t * p.xs_ld + kb] : 0.f;
+          float mine = 0.f;
+          if (KIND == 0 && c0 + lane < k.t_valid) mine = sw * p.x_scale[(size_t)t * p.xs_ld + kb];
           uint32_t r[32];
           tmem_ld_32x32(taddr + c0, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            acc[c0 + j] = fmaf(__uint_as_float(r[j]), __shfl_sync(0xffffffffu, mine, j), acc[c0 + j]);
+          for (int j = 0; j < 32; ++j) {
+            if (KIND == 1) acc[c0 + j] += (float)(int)r[j];
+            else acc[c0 + j] = fmaf(__uint_as_float(r[j]), __shfl_sync(0xffffffffu, mine, j), acc[c0 + j]);
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -230,6 +239,16 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       }
       if (!ok) break;
       const int n = k.n0 + row;
+      if (KIND == 1) {
+        // per-channel weight scale (this thread's row) times per-token activation scale (the column)
+        const float wsn = n < p.N ? p.w_scale[k.ws_row * BM + row] : 0.f;
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          const float mine = (c0 + lane < k.t_valid) ? p.x_scale[k.t_row + c0 + lane] : 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c0 + j] *= wsn * __shfl_sync(0xffffffffu, mine, j);
+        }
+      }
       if (p.cluster_splitk) {
         float* part = reinterpret_cast<float*>(smem);      // ring is idle: this CTA has one work item
 #pragma unroll
@@ -310,13 +329,35 @@ __global__ void quant_act_1x128_kernel(const __nv_bfloat16* __restrict__ x, __nv
   if (lane == 0) xs[(size_t)t * groups + g] = scale;
 }
 
-template <int BN>
+// x [T, K] bf16 -> xq [T, K] int8 and xs [T] fp32 (amax / 127): one CTA per row
+__global__ void quant_act_int8_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ xq,
+                                      float* __restrict__ xs, int K, int ldx) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) amax = fmaxf(amax, fabsf(__bfloat162float(x[(size_t)t * ldx + i])));
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = (threadIdx.x & 31) < (blockDim.x >> 5) ? red[threadIdx.x & 31] : 0.f;
+  amax = warp_max(amax);
+  const float scale = fmaxf(amax, 1e-12f) / 127.f;
+  const float inv = 1.f / scale;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) {
+    const float v = rintf(__bfloat162float(x[(size_t)t * ldx + i]) * inv);
+    xq[(size_t)t * K + i] = (int8_t)fminf(fmaxf(v, -127.f), 127.f);
+  }
+  if (threadIdx.x == 0) xs[t] = scale;
+}
+
+template <int BN, int KIND = 0>
 static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int grid,
                   cudaStream_t stream) {
   using C = Cfg<BN>;
   static bool attr_set = false;
   if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_block_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_block_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM));
     attr_set = true;
   }
@@ -339,14 +380,14 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& 
   ++na;
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_fp8_block_kernel<BN>, tmW, tmX, p));
+  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_fp8_block_kernel<BN, KIND>, tmW, tmX, p));
   return 0;
 }
 
 template <int BN>
 static int max_clusters(int splits) {
   using C = Cfg<BN>;
-  cudaFuncSetAttribute(gemm_fp8_block_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+  cudaFuncSetAttribute(gemm_fp8_block_kernel<BN, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits * 64);
   cfg.blockDim = dim3(NUM_THREADS);
@@ -359,7 +400,7 @@ static int max_clusters(int splits) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm_fp8_block_kernel<BN>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_fp8_block_kernel<BN, 0>, &cfg) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
@@ -492,5 +533,56 @@ extern "C" int b200_grouped_gemm_fp8_block(const void* Xq, const float* xs, cons
     case 32: return f8::launch<32>(tmW, tmX, p, num_sms, stream);
     case 64: return f8::launch<64>(tmW, tmX, p, num_sms, stream);
     default: return f8::launch<128>(tmW, tmX, p, num_sms, stream);
+  }
+}
+
+extern "C" int b200_quant_act_int8(const void* x, void* xq, float* xs, int T, int K, int ldx, cudaStream_t stream) {
+  if (T == 0) return 0;
+  f8::quant_act_int8_kernel<<<T, 256, 0, stream>>>((const __nv_bfloat16*)x, (int8_t*)xq, xs, K, ldx);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// Y[T,N] bf16 = (Xq * Wq^T) * xs[t] * ws[n] (+bias): int8 operands [T,K] / [N,K] contiguous, K % 16 == 0.
+extern "C" int b200_gemm_int8(const void* Xq, const float* xs, const void* Wq, const float* ws, void* Y,
+                              const void* bias, int T, int N, int K, int ldy, int* status, int num_sms,
+                              cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  const int bn = T <= 32 ? 32 : (T <= 64 ? 64 : 128);
+  f8::Params p;
+  memset(&p, 0, sizeof(p));
+  p.Y = (__nv_bfloat16*)Y;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.w_scale = ws;
+  p.x_scale = xs;
+  p.status = status;
+  p.T = T; p.N = N; p.K = K; p.ldy = ldy;
+  p.n_tiles = (N + f8::BM - 1) / f8::BM;
+  p.t_tiles = (T + bn - 1) / bn;
+  p.kb_total = (K + f8::BKB - 1) / f8::BKB;
+  const int tiles = p.n_tiles * p.t_tiles;
+  int splits = 1;
+  if (tiles * 2 <= num_sms) {
+    splits = num_sms / tiles;
+    const int by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;
+    if (splits > by_k) splits = by_k;
+    if (splits > 1) splits = f8::fit_splits(splits, tiles, bn);
+  }
+  p.splits = splits;
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= p.kb_total) {
+    --p.splits;
+    p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+  }
+  p.cluster_splitk = p.splits > 1 ? 1 : 0;
+  CUtensorMap tmW, tmX;
+  int rc = fp8_common(p, Xq, Wq, N, T, bn, K, &tmW, &tmX);
+  if (rc) return rc;
+  const int total = tiles * p.splits;
+  const int grid = p.cluster_splitk ? total : (total < num_sms ? total : num_sms);
+  switch (bn) {
+    case 32: return f8::launch<32, 1>(tmW, tmX, p, grid, stream);
+    case 64: return f8::launch<64, 1>(tmW, tmX, p, grid, stream);
+    default: return f8::launch<128, 1>(tmW, tmX, p, grid, stream);
   }
 }

@@ -48,6 +48,7 @@ def fp8_block_gemm(x, wq, w_scale_inv, bias=None, block=(128, 128), out=None):
 def fp8_rowwise_gemm(xq, xs, wq, w_scale, out_dtype):
     """Per-tensor weight scale, per-row activation scale: expressed through the block kernel by
     broadcasting both scales over the K blocks (dequant happens block by block either way)."""
+    xq = xq.contiguous()
     T, K = xq.shape
     N = wq.shape[0]
     kb = (K + 127) // 128
@@ -56,7 +57,7 @@ def fp8_rowwise_gemm(xq, xs, wq, w_scale, out_dtype):
     y = torch.empty((T, N), dtype=torch.bfloat16, device=xq.device)
     ws = _c.Workspace.get(xq.device)
     _c._check(_c.lib().b200_gemm_fp8_block(
-        _c._p(xq.contiguous()), _c._p(xs_b), _c._p(wq), _c._p(ws_b), _c._p(y), c_void_p(0), c_int(T), c_int(N),
+        _c._p(xq), _c._p(xs_b), _c._p(wq), _c._p(ws_b), _c._p(y), c_void_p(0), c_int(T), c_int(N),
         c_int(K), c_int(y.stride(0)), _c._p(ws.status), c_int(_c._sms), _c._stream()), "gemm_fp8_block")
     count_launch()
     return y.to(out_dtype)
@@ -90,3 +91,40 @@ def moe_experts_fp8(x, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, expert_of
     a = _c.silu_and_mul(h)
     y = grouped_fp8_gemm(a, w2, w2_scale, group_off, avg)
     return cuda_moe.moe_unpermute(y, inv_pos, topk_w.contiguous(), T)
+
+
+def quant_act_int8(x):
+    """bf16 [T, K] -> (int8 [T, K], fp32 per-token scales [T])."""
+    _c._require_bf16(x)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    T, K = x.shape
+    xq = torch.empty((T, K), dtype=torch.int8, device=x.device)
+    xs = torch.empty((T,), dtype=torch.float32, device=x.device)
+    _c._check(_c.lib().b200_quant_act_int8(_c._p(x), _c._p(xq), _c._p(xs), c_int(T), c_int(K), c_int(x.stride(0)),
+                                           _c._stream()), "quant_act_int8")
+    count_launch()
+    return xq, xs
+
+
+def int8_gemm(x, wq, w_scale, bias=None):
+    """W8A8: x bf16 [T,K] is quantised per token, wq int8 [N,K] has per-output-channel scales [N];
+    tcgen05 kind::i8 with exact s32 sums -> bf16 [T,N]."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    T, K = x2.shape
+    N = wq.shape[0]
+    if K % 16:
+        raise NotImplementedError("int8 GEMM needs K % 16 == 0")
+    xq, xs = quant_act_int8(x2)
+    y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return y.reshape(*lead, N)
+    ws = _c.Workspace.get(x.device)
+    wq, w_scale = wq.contiguous(), w_scale.float().contiguous()
+    _c._check(_c.lib().b200_gemm_int8(
+        _c._p(xq), _c._p(xs), _c._p(wq), _c._p(w_scale), _c._p(y), _c._p(bias),
+        c_int(T), c_int(N), c_int(K), c_int(y.stride(0)), _c._p(ws.status), c_int(_c._sms), _c._stream()),
+        "gemm_int8")
+    count_launch()
+    return y.reshape(*lead, N)

@@ -173,9 +173,10 @@ def moe_experts_ep(x, w13, w2, topk_ids, topk_w, heap, num_experts: int):
         "grouped_gemm_routed")
     count_launch()
     out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+    topk_w = topk_w.contiguous()
     _c._check(L.b200_ep_combine(c_void_p(heap.local_ptr), c_ulonglong(st.ret.offset),
                                 c_ulonglong(st.ret_flag.offset), _c._p(st.ctrl), _c._p(ids),
-                                _c._p(topk_w.contiguous()), _c._p(out), c_int(T), c_int(k), c_int(H),
+                                _c._p(topk_w), _c._p(out), c_int(T), c_int(k), c_int(H),
                                 c_int(num_experts), c_int(heap.world), _c._p(ws.status), spin, _c._stream()),
               "ep_combine")
     count_launch()

@@ -95,6 +95,9 @@ def apply_token_bitmask(logits: torch.Tensor, bitmask: torch.Tensor, rows: Optio
     """logits [R, V]; bitmask [M, ceil(V/32)] int32; rows [M] = logits row of each mask row
     (None: row i ↔ mask i).  Disallowed tokens get -inf, in place."""
     V = logits.shape[1]
+    if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32) and logits.stride(-1) == 1:
+        from ..ops import cuda_misc
+        return cuda_misc.apply_token_bitmask(logits, bitmask, rows)
     bits = (bitmask.to(torch.int64)[:, :, None] >> torch.arange(32, device=bitmask.device)) & 1
     allow = bits.reshape(bitmask.shape[0], -1)[:, :V].bool()
     if rows is None:
