@@ -99,6 +99,34 @@ def main():
             print(f"[rank {rank}] gemm_push {(T, N, K)}: y {e1} residual {e2} sum {e3} tol {tol} "
                   f"status {cuda.check_status()}", flush=True)
 
+    # all-gather -> GEMM: row-sharded activations, gathered inside the column-parallel GEMM
+    for (T_loc, N, K) in [(32, 512, 256), (64, 1536, 4096), (256, 1024, 512), (1024, 3584, 4096)]:
+        g = torch.Generator(device=dev).manual_seed(31 * rank + T_loc)
+        x_loc = torch.randn(T_loc, K, device=dev, generator=g).bfloat16()
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+        gathered = [torch.empty_like(x_loc) for _ in range(world)]
+        dist.all_gather(gathered, x_loc)
+        want = torch.cat(gathered, 0).float() @ w.float().t()
+        for rep in range(3):
+            y = cuda.gemm_all_gather(x_loc, w, heap)
+        torch.cuda.synchronize()
+        err = (y.float() - want).abs().max().item()
+        tol = 3e-2 * want.abs().max().item() + 2e-2
+        status = cuda.check_status()
+        if err > tol or status != 0:
+            ok = False
+            print(f"[rank {rank}] gemm_all_gather {(T_loc, N, K)}: err {err} tol {tol} status {status}", flush=True)
+    for (T_loc, N, K) in [(8192 // world, 6144 // world, 4096), (8192 // world, 28672 // world, 4096)]:
+        x_loc = torch.randn(T_loc, K, device=dev).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+        gathered = torch.empty(T_loc * world, K, device=dev, dtype=torch.bfloat16)
+
+        def plain_ag(x_loc=x_loc, w=w, gathered=gathered):
+            dist.all_gather_into_tensor(gathered, x_loc)
+            return cuda.gemm(gathered, w)
+        # timed further down, once the timing helper exists
+        globals().setdefault("_AG_CASES", []).append((x_loc, w, gathered, plain_ag, T_loc, N, K))
+
     # device time of the fused kernel next to GEMM + NCCL all-reduce (information only)
     def timed(fn, iters=20):
         for _ in range(5):
@@ -139,6 +167,14 @@ def main():
         if rank == 0:
             print(f"TIMING T={T} N={N} K={K} world={world}: fused {t_fused:.1f} us, gemm+nccl {t_nccl:.1f} us, "
                   f"gemm alone {t_gemm:.1f} us, status {cuda.check_status()}", flush=True)
+    for (x_loc, w, gathered, plain_ag, T_loc, N, K) in globals().get("_AG_CASES", []):
+        t_fused = timed(lambda: cuda.gemm_all_gather(x_loc, w, heap))
+        t_plain = timed(plain_ag)
+        t_gemm = timed(lambda: cuda.gemm(gathered, w))
+        if rank == 0:
+            print(f"TIMING all-gather->GEMM T_loc={T_loc} N={N} K={K} world={world}: fused {t_fused:.1f} us, "
+                  f"nccl all-gather + gemm {t_plain:.1f} us, gemm alone {t_gemm:.1f} us, "
+                  f"status {cuda.check_status()}", flush=True)
     if cuda.check_status() != 0:
         ok = False
     # stand-alone peer all-reduce

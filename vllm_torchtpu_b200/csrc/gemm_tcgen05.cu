@@ -85,6 +85,19 @@ struct GemmParams {
   // int[world] "returned" flags that the last CTA raises at every rank
   const int2* row_route;
   unsigned long long route_ret_off;
+  // ---- all-gather of the activations fused in front of the GEMM (ar_mode 5): the activation rows are
+  // sharded over the ranks; the extra warps of every CTA push this rank's shard (ag_src, ag_rows
+  // rows of ag_ld elements) into the full matrix [world * ag_rows, K] that every rank keeps at heap
+  // offset ag_dst_off (the TMA operand), raising flags[src][block * ag_parts + part] per BN-row
+  // block and K slice; the TMA producer waits for the flags of a block before loading from it
+  const __nv_bfloat16* ag_src;
+  unsigned long long ag_dst_off;
+  int ag_rows, ag_ld, ag_tps, ag_parts;  // ag_tps: BN-row blocks per shard
+  // back-pressure: a rank finishes reading its gather buffer `ag_flip` when its launch ends and then
+  // writes the launch's epoch to ag_done[ag_flip][rank] at every rank; nobody pushes into a buffer
+  // before its owner has finished the previous launch that used it (epoch kept in ctrl[2 + flip])
+  unsigned long long ag_done_off;
+  int ag_flip;
   int* epoch_ptr;                        // local: epoch of the last completed fused launch
   int* cta_done;                         // local: CTA exit counter
   unsigned int spin_limit;
@@ -126,6 +139,10 @@ __device__ __forceinline__ Work get_work(int w, const GemmParams& p, const int* 
   if (p.group_off == nullptr) {
     int n_tile, t_tile;
     decode_work(w, p, n_tile, t_tile, k.split, k.tile);
+    if (p.ar_mode == 5) {          // start with the token blocks of this rank's own shard
+      t_tile += p.rank * p.ag_tps;
+      if (t_tile >= p.t_tiles) t_tile -= p.t_tiles;
+    }
     k.w_row = n_tile * BM;
     k.n0 = n_tile * BM;
     k.t_row = t_tile * BN;
@@ -166,7 +183,7 @@ struct TileDst {
 template <int BN>
 __device__ __forceinline__ TileDst tile_dst(const GemmParams& p, const Work& wk, int d) {
   TileDst t;
-  if (p.world == 1) {
+  if (p.world == 1 || p.ar_mode == 5) {
     t.base = p.Y + (size_t)wk.t_row * p.ldy + wk.n0;
     t.cs = p.ldy;
   } else if (p.ar_mode >= 2) {
@@ -279,7 +296,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   int* s_prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES);
   const bool fused = p.world > 1;
   __nv_bfloat16* const dst_base = p.Y;       // SwiGLU and grouped launches (never fused)
-  const int ndst = (fused && p.ar_mode >= 2) ? p.world : 1;
+  const bool push_out = fused && p.ar_mode <= 3;       // the epilogue feeds a cross-rank reduction
+  const int ndst = (push_out && p.ar_mode >= 2) ? p.world : 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -355,9 +373,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
       }
       if (dense) pdl_wait();
+      const int ag_epoch = p.ar_mode == 5 ? *reinterpret_cast<volatile int*>(p.epoch_ptr) + 1 : 0;
+      uint32_t ag_seen[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};   // blocks known to have arrived, per source
       int issued = 0;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const Work k = get_work<BN>(w, p, s_prefix);
+        if (p.ar_mode == 5) {
+          const int blk = k.t_row / BN, src = blk / p.ag_tps, j = blk - src * p.ag_tps;
+          if (!((ag_seen[src] >> j) & 1u)) {
+            const int* f = reinterpret_cast<const int*>(p.peer[p.rank] + p.tile_flag_off) +
+                           (size_t)src * p.max_tiles + j * p.ag_parts;
+            for (int part = 0; part < p.ag_parts && ok; ++part)
+              if (!wait_flag_ge(f + part, ag_epoch, p.status, p.spin_limit)) { *abort_flag = 1; ok = false; }
+            if (!ok) break;
+            // the rows were written by other GPUs and are read by the async proxy (TMA) from here on
+            asm volatile("fence.proxy.async;" ::: "memory");
+            ag_seen[src] |= 1u << j;
+          }
+        }
         for (int kb = k.kb0; kb < k.kb1; ++kb, ++issued) {
           uint8_t* a = smem + s * Cfg::STAGE_BYTES;
           if (issued < npre) {
@@ -543,7 +576,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
-        if (fused) {
+        if (push_out) {
           // the partial tile has been pushed: make it visible system-wide, then raise its flag(s)
           __threadfence_system();
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -640,7 +673,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             }
           }
           if (threadIdx.x == 64) p.counters[tile] = 0;
-          if (fused) {
+          if (push_out) {
             __threadfence_system();
             asm volatile("bar.sync 1, 128;" ::: "memory");
             publish_tile(p, tile, epoch, (int)threadIdx.x - 64);
@@ -648,6 +681,51 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is rewritten next iteration
       }
+    }
+  }
+
+  else if (fused && p.ar_mode == 5) {
+    // ------------------------------------------- gather warps (threads 192..319), all-gather -> GEMM
+    // unit = (destination, BN-row block of this rank's shard, K slice); destinations start with this
+    // rank itself and go round, so that every link is busy and the local blocks are ready first
+    const int rt = threadIdx.x - NUM_THREADS;
+    const int kv = p.K >> 3;                                   // 16-byte vectors per row
+    const int vpp = (kv + p.ag_parts - 1) / p.ag_parts;
+    const int units = p.world * p.ag_tps * p.ag_parts;
+    const int prev_use = *reinterpret_cast<volatile int*>(p.epoch_ptr + 2 + p.ag_flip);
+    const int* ag_done = reinterpret_cast<const int*>(p.peer[p.rank] + p.ag_done_off) + p.ag_flip * p.world;
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const int part = u % p.ag_parts;
+      const int j = (u / p.ag_parts) % p.ag_tps;
+      const int d = (p.rank + u / (p.ag_parts * p.ag_tps)) % p.world;
+      if (rt == 0 && !wait_flag_ge(ag_done + d, prev_use, p.status, p.spin_limit)) *red_ok = 0;
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (!*red_ok) break;
+      const int row0 = j * BN, rows = min(BN, p.ag_rows - row0);
+      const int v0 = part * vpp, nv = min(vpp, kv - v0);
+      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src + (size_t)row0 * p.ag_ld) + v0;
+      uint4* dst = reinterpret_cast<uint4*>(p.peer[d] + p.ag_dst_off) +
+                   ((size_t)p.rank * p.ag_rows + row0) * kv + v0;
+      const int src_ldv = p.ag_ld >> 3;
+      const int total = rows * nv;
+      for (int base = rt; base < total; base += 128 * 4) {
+        uint4 val[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int idx = base + q * 128;
+          if (idx < total) val[q] = src[(size_t)(idx / nv) * src_ldv + idx % nv];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int idx = base + q * 128;
+          if (idx < total) dst[(size_t)(idx / nv) * kv + idx % nv] = val[q];
+        }
+      }
+      __threadfence_system();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (rt == 0)
+        st_release_sys(reinterpret_cast<int*>(p.peer[d] + p.tile_flag_off) + (size_t)p.rank * p.max_tiles +
+                           j * p.ag_parts + part, epoch);
     }
   }
 
@@ -789,12 +867,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           }
         }
       }
-      if (fused) __threadfence_system();
+      if (push_out) __threadfence_system();
     }
     __syncwarp();
     cluster_arrive_release();          // nobody leaves while its partial may still be read
     cluster_wait_acquire();
-    if (fused && cluster_ctarank() == 0 && warp == 2 && blockIdx.x < total_work) {
+    if (push_out && cluster_ctarank() == 0 && warp == 2 && blockIdx.x < total_work) {
       const Work wk = get_work<BN>(blockIdx.x, p, s_prefix);
       publish_tile(p, wk.tile, epoch, lane);
     }
@@ -818,6 +896,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         for (int r = 0; r < p.world; ++r)
           st_release_sys(reinterpret_cast<int*>(p.peer[r] + p.done_flag_off) + p.rank, ep_epoch);
       } else {
+        if (p.ar_mode == 5) {
+          // this rank no longer reads its gather buffer: peers may overwrite it
+          for (int r = 0; r < p.world; ++r)
+            st_release_sys(reinterpret_cast<int*>(p.peer[r] + p.ag_done_off) + p.ag_flip * p.world + p.rank,
+                           epoch);
+          p.epoch_ptr[2 + p.ag_flip] = epoch;
+        }
         *p.epoch_ptr = epoch;       // every CTA of this launch has read the old value by now
       }
       __threadfence();
@@ -970,7 +1055,7 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gem
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     attr_set = true;
   }
-  const int threads = (p.world > 1 && p.ar_mode < 3) ? NUM_THREADS_FUSED : NUM_THREADS;
+  const int threads = (p.world > 1 && (p.ar_mode < 3 || p.ar_mode == 5)) ? NUM_THREADS_FUSED : NUM_THREADS;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(threads);
@@ -1304,3 +1389,76 @@ extern "C" int b200_grouped_gemm_bf16_routed(const void* X, const void* W, const
   }
 }
 
+
+// All-gather fused in front of a column-parallel GEMM: the activation rows are sharded over the
+// ranks (T_loc rows each, row stride ldx), Y[world * T_loc, N] = gather(X) * W^T (+bias) lands in
+// local memory.  Every rank pushes its shard into the [world * T_loc, K] buffer that each rank keeps
+// at heap offset xfull_off, block by block, while the tensor cores already work on the blocks that
+// have arrived (this rank's own first).  T_loc must be a multiple of 32.  Callers alternate between
+// two gather buffers (flip 0 / 1, each with its xfull_off); ag_done_off names int[2][world] in the heap;
+// ctrl is int[4]: epoch, CTA counter, epoch of the last launch that used buffer 0 / 1.
+extern "C" int b200_gemm_bf16_allgather(const void* X_loc, const void* W, void* Y, const void* bias, int T_loc,
+                                        int N, int K, int ldx, int ldw, int ldy, void* const* peers, int rank,
+                                        int world, unsigned long long xfull_off, unsigned long long xfull_bytes,
+                                        unsigned long long tile_flag_off, int max_tiles,
+                                        unsigned long long ag_done_off, int flip, int* ctrl, int* status,
+                                        int num_sms, unsigned int spin_limit, cudaStream_t stream) {
+  using namespace b200;
+  if (T_loc <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % 8 || ldx % 8 || ldw % 8 || T_loc % 32 || world < 2 || world > 8) {
+    b200_set_last_error("gemm_allgather: K, strides multiples of 8, T_loc multiple of 32, 2 <= world <= 8",
+                        __FILE__, __LINE__);
+    return -3;
+  }
+  const int T = T_loc * world;
+  int bn = 256;
+  while (bn > 32 && (T_loc % bn || bn > T)) bn >>= 1;
+  if ((unsigned long long)T * K * 2ull > xfull_bytes) {
+    b200_set_last_error("gemm_allgather: gather buffer too small", __FILE__, __LINE__);
+    return -5;
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.Y = reinterpret_cast<__nv_bfloat16*>(Y);
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.status = status;
+  p.T = T; p.N = N; p.K = K; p.ldy = ldy;
+  p.n_tiles = (N + BM - 1) / BM;
+  p.t_tiles = T / bn;
+  p.kb_total = (K + BK - 1) / BK;
+  p.splits = 1;
+  p.kb_per_split = p.kb_total;
+  p.world = world; p.rank = rank; p.ar_mode = 5;
+  for (int i = 0; i < 8; ++i) p.peer[i] = i < world ? (uint8_t*)peers[i] : nullptr;
+  p.tile_flag_off = tile_flag_off;
+  p.max_tiles = max_tiles;
+  p.epoch_ptr = ctrl; p.cta_done = ctrl + 1;
+  p.spin_limit = spin_limit;
+  p.ag_src = reinterpret_cast<const __nv_bfloat16*>(X_loc);
+  p.ag_dst_off = xfull_off;
+  p.ag_rows = T_loc; p.ag_ld = ldx;
+  p.ag_done_off = ag_done_off; p.ag_flip = flip & 1;
+  p.ag_tps = T_loc / bn;
+  int parts = (2 * num_sms + world * p.ag_tps - 1) / (world * p.ag_tps);
+  if (parts > 8) parts = 8;
+  if (parts < 1) parts = 1;
+  p.ag_parts = parts;
+  if (p.ag_tps > 32 || p.ag_tps * parts > max_tiles) {
+    b200_set_last_error("gemm_allgather: too many row blocks per shard", __FILE__, __LINE__);
+    return -4;
+  }
+  CUtensorMap tmW, tmX;
+  int rc = cached_tmap(&tmW, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, BM);
+  if (rc) return rc;
+  rc = cached_tmap(&tmX, (const uint8_t*)peers[rank] + xfull_off, (uint64_t)T, (uint64_t)K, (uint64_t)K * 2,
+                   (uint32_t)bn);
+  if (rc) return rc;
+  const int total = p.n_tiles * p.t_tiles;
+  const int grid = total < num_sms ? total : num_sms;
+  switch (bn) {
+    case 32: return launch_gemm<32>(tmW, tmX, p, grid, stream);
+    case 64: return launch_gemm<64>(tmW, tmX, p, grid, stream);
+    case 128: return launch_gemm<128>(tmW, tmX, p, grid, stream);
+    default: return launch_gemm<256>(tmW, tmX, p, grid, stream);
+  }
+}

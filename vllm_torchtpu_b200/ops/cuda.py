@@ -375,6 +375,10 @@ class FusedTP:
         self.outs = [heap.alloc("tp_out0", self.max_elems * 2), heap.alloc("tp_out1", self.max_elems * 2)]
         self.tile_flags = heap.alloc("tp_tile_flags", heap.world * self.MAX_TILES * 4)
         self.done_flags = heap.alloc("tp_done_flags", self.MAX_TILES * 4)
+        # all-gather -> GEMM: two full activation matrices [max_tokens, max_n] and their done flags
+        self.xfull = [heap.alloc("tp_xfull0", self.max_elems * 2), heap.alloc("tp_xfull1", self.max_elems * 2)]
+        self.ag_done = heap.alloc("tp_ag_done", 2 * heap.world * 4)
+        self.ag_flip = 0
         self.ctrl = torch.zeros(4, dtype=torch.int32, device=heap.device)
         self.flip = 0
 
@@ -394,7 +398,7 @@ class FusedTP:
     @staticmethod
     def heap_bytes(max_tokens: int, max_n: int, world: int) -> int:
         region = FusedTP.region_bytes(max_tokens, max_n, world, envs.B200_TP_ONE_SHOT_BYTES)
-        return (2 * region + 2 * max_tokens * max_n * 2 + world * FusedTP.MAX_TILES * 4 +
+        return (2 * region + 4 * max_tokens * max_n * 2 + world * FusedTP.MAX_TILES * 4 +
                 FusedTP.MAX_TILES * 4 + (1 << 20))
 
 
@@ -423,6 +427,34 @@ def gemm_all_reduce(x, w, heap, mode: int = 0):
         c_int(_sms), ctypes.c_uint(min(heap.spin_limit, 2**31 - 1)), _stream()), "gemm_fused_reduce")
     count_launch()
     return heap.tensor(out, (T, N), torch.bfloat16)
+
+
+def gemm_all_gather(x_local, w, heap, bias=None):
+    """Column-parallel ``gather(x) @ w.T`` where the rows of ``x`` are sharded over the ranks of
+    ``heap`` (equal shards, a multiple of 32 rows): the all-gather runs inside the GEMM kernel as
+    NVLink pushes that overlap the tensor-core work.  Returns [world * T_loc, N] in local memory."""
+    _require_bf16(x_local, w, bias)
+    st = heap.fused_tp
+    if x_local.stride(-1) != 1:
+        x_local = x_local.contiguous()
+    T_loc, K = x_local.shape
+    N = w.shape[0]
+    T = T_loc * heap.world
+    if T * K > st.max_elems:
+        raise RuntimeError(f"gather buffers hold {st.max_elems} elements, need {T * K}")
+    flip = st.ag_flip
+    st.ag_flip ^= 1
+    y = torch.empty((T, N), dtype=torch.bfloat16, device=x_local.device)
+    ws = Workspace.get(x_local.device)
+    _check(lib().b200_gemm_bf16_allgather(
+        _p(x_local), _p(w), _p(y), _p(bias), c_int(T_loc), c_int(N), c_int(K), c_int(x_local.stride(0)),
+        c_int(w.stride(0)), c_int(y.stride(0)), heap.peers_c, c_int(heap.rank), c_int(heap.world),
+        c_ulonglong(st.xfull[flip].offset), c_ulonglong(st.xfull[flip].nbytes),
+        c_ulonglong(st.tile_flags.offset), c_int(FusedTP.MAX_TILES), c_ulonglong(st.ag_done.offset), c_int(flip),
+        _p(st.ctrl), _p(ws.status), c_int(_sms), ctypes.c_uint(min(heap.spin_limit, 2**31 - 1)), _stream()),
+        "gemm_all_gather")
+    count_launch()
+    return y
 
 
 class PendingReduce:
