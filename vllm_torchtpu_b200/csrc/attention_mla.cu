@@ -1,0 +1,316 @@
+// Multi-head latent attention over the paged latent cache (absorbed-query form, MQA over one latent
+// "head"), dense or sparse (top-k indexed), for decode, spec-verify, chunked prefill and mixed batches.
+//
+//   q_latent [T, H, Dq]  Dq = kv_lora + rope (576 for DeepSeek-V3), already multiplied by W_UK
+//   cache    [blocks, block_size, Dq] bf16; the value of a row is its first L = kv_lora dims
+//   out      [T, H, L]
+//
+// One CTA per (token, group of 16 heads): all 16 rows of the MMA tile share the query position, so
+// the causal limit and (sparse) the token's top-k list are uniform over the tile.  KV rows stream
+// in 16-row chunks through a 2-stage cp.async ring (rows are gathered by pointer, so the dense and
+// the top-k case share the loop).  The four warps split the Dq contraction of Q K^T (partials summed
+// through shared memory) and each owns a quarter of the L value columns for P V, which keeps the
+// 16 x 512 fp32 output in registers.  bf16 mma.sync m16n8k16, fp32 online softmax in the log2 domain.
+//
+// Semantics of the reference's dense / sparse MLA kernels and latent cache write
+// (reference: src/vllm_torchtpu/kernels/mla/v2/, kernels/mla/sparse/, layers/adapter/attention.py:2659-2879).
+#include "common.cuh"
+
+namespace b200 {
+namespace mla {
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, const uint32_t* b) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void ldsm4(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp16(uint32_t smem, const void* g) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+constexpr int KS_MAX = 9;             // k-steps of 16 per warp: Dq <= 4 * 9 * 16 = 576
+
+struct Params {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* cache;
+  __nv_bfloat16* out;
+  float* lse;
+  const int* block_tables;
+  const int* seq_lens;
+  const int* qsl;
+  const int* topk;                    // optional [T, topk_k] context positions, -1 = unused
+  int topk_k, T, H, Dq, L, num_reqs, max_blocks, block_size;
+  long long num_blocks;
+  float scale_log2;
+};
+
+// LW = value columns per warp (L / 4).
+template <int LW>
+__global__ void __launch_bounds__(128) mla_attn_kernel(const Params p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ const __nv_bfloat16* s_ptr[2][16];
+  __shared__ int s_valid[2][16];
+  __shared__ float s_part[4][16][17];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int groups = (p.H + 15) >> 4;
+  const int t = blockIdx.x / groups, g = blockIdx.x - t * groups;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // request of this token: largest r with qsl[r] <= t
+  int lo = 0, hi = p.num_reqs;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (p.qsl[mid] <= t) lo = mid; else hi = mid;
+  }
+  const int r = lo;
+  const int qs = p.qsl[r], q_len = p.qsl[r + 1] - qs, kv_len = p.seq_lens[r];
+  if (t >= p.qsl[p.num_reqs] || q_len <= 0 || kv_len <= 0) return;       // padded token
+  const int qpos = kv_len - q_len + (t - qs);
+  const int n_kv = p.topk ? p.topk_k : qpos + 1;
+  const int chunks = (n_kv + 15) >> 4;
+  const int rows_valid = min(16, p.H - g * 16);
+  const int ksteps = p.Dq >> 4;                    // Dq % 16 == 0
+  const int nch = p.Dq >> 3;                       // 16-byte chunks per row
+  const int RS = ((nch + 7) & ~7) << 4;            // row stride in shared memory (swizzle groups of 8)
+  const int STAGE = 16 * RS;
+  const uint32_t sbase = smem_u32(smem);
+
+  // Q fragments of this warp's k-steps (ks = warp, warp + 4, ...)
+  uint32_t qf[KS_MAX][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, cb = 2 * (lane & 3);
+    const __nv_bfloat16* q0 = r0 < rows_valid ? p.q + ((size_t)t * p.H + g * 16 + r0) * p.Dq : nullptr;
+    const __nv_bfloat16* q1 = r1 < rows_valid ? p.q + ((size_t)t * p.H + g * 16 + r1) * p.Dq : nullptr;
+#pragma unroll
+    for (int i = 0; i < KS_MAX; ++i) {
+      const int ks = warp + 4 * i;
+      const bool in = ks < ksteps;
+      qf[i][0] = (in && q0) ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + cb) : 0u;
+      qf[i][1] = (in && q1) ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + cb) : 0u;
+      qf[i][2] = (in && q0) ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + cb) : 0u;
+      qf[i][3] = (in && q1) ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + cb) : 0u;
+    }
+  }
+  const int* bt = p.block_tables + (size_t)r * p.max_blocks;
+
+  auto prefetch = [&](int c, int stage) {
+    if (threadIdx.x < 16) {
+      const int i = (c << 4) + threadIdx.x;
+      int pos = -1;
+      if (i < n_kv) pos = p.topk ? p.topk[(size_t)t * p.topk_k + i] : i;
+      const bool ok = pos >= 0 && pos <= qpos && pos < kv_len;
+      long long blk = 0;
+      int off = 0;
+      if (ok) {
+        blk = bt[pos / p.block_size];
+        off = pos % p.block_size;
+        if (blk < 0 || blk >= p.num_blocks) blk = 0;
+      }
+      s_ptr[stage][threadIdx.x] = p.cache + ((size_t)blk * p.block_size + off) * p.Dq;
+      s_valid[stage][threadIdx.x] = ok ? 1 : 0;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * nch; idx += 128) {
+      const int row = idx / nch, ch = idx - row * nch;
+      cp16(sbase + stage * STAGE + row * RS + ((ch ^ (row & 7)) << 4), s_ptr[stage][row] + ch * 8);
+    }
+  };
+
+  float o[LW / 8][4];
+#pragma unroll
+  for (int i = 0; i < LW / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int mi = lane >> 3, rr = lane & 7;
+
+  if (chunks > 0) prefetch(0, 0);
+  cp_commit();
+  for (int c = 0; c < chunks; ++c) {
+    const int stage = c & 1;
+    if (c + 1 < chunks) prefetch(c + 1, stage ^ 1);
+    cp_commit();
+    cp_wait<1>();
+    __syncthreads();
+    const uint32_t sb = sbase + stage * STAGE;
+    // ---- partial scores over this warp's part of Dq
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      const int tok = (mi >> 1) * 8 + rr;
+#pragma unroll
+      for (int i = 0; i < KS_MAX; ++i) {
+        const int ks = warp + 4 * i;
+        if (ks < ksteps) {
+          const int ch = 2 * ks + (mi & 1);
+          uint32_t b[4];
+          ldsm4(b, sb + (uint32_t)(tok * RS + ((ch ^ (tok & 7)) << 4)));
+          mma16816(s[0], qf[i], &b[0]);
+          mma16816(s[1], qf[i], &b[2]);
+        }
+      }
+    }
+    const int row0 = lane >> 2, row1 = row0 + 8, col = 2 * (lane & 3);
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      s_part[warp][row0][nb * 8 + col] = s[nb][0];
+      s_part[warp][row0][nb * 8 + col + 1] = s[nb][1];
+      s_part[warp][row1][nb * 8 + col] = s[nb][2];
+      s_part[warp][row1][nb * 8 + col + 1] = s[nb][3];
+    }
+    __syncthreads();
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int rrow = (e < 2) ? row0 : row1, cc = nb * 8 + col + (e & 1);
+        float v = s_part[0][rrow][cc] + s_part[1][rrow][cc] + s_part[2][rrow][cc] + s_part[3][rrow][cc];
+        v = s_valid[stage][cc] ? v * p.scale_log2 : -INFINITY;
+        s[nb][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+    const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+    const float a0 = ex2(m[0] - base0), a1 = ex2(m[1] - base1);
+    m[0] = mn0; m[1] = mn1;
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      s[nb][0] = ex2(s[nb][0] - base0); s[nb][1] = ex2(s[nb][1] - base0);
+      s[nb][2] = ex2(s[nb][2] - base1); s[nb][3] = ex2(s[nb][3] - base1);
+      ps0 += s[nb][0] + s[nb][1];
+      ps1 += s[nb][2] + s[nb][3];
+    }
+    l[0] = l[0] * a0 + ps0;
+    l[1] = l[1] * a1 + ps1;
+#pragma unroll
+    for (int i = 0; i < LW / 8; ++i) {
+      o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1;
+    }
+    const uint32_t pa[4] = {pack2(s[0][0], s[0][1]), pack2(s[0][2], s[0][3]), pack2(s[1][0], s[1][1]),
+                            pack2(s[1][2], s[1][3])};
+    // ---- P V on this warp's value columns [warp * LW, (warp + 1) * LW)
+    {
+      const int tok = (mi & 1) * 8 + rr;
+#pragma unroll
+      for (int np = 0; np < LW / 16; ++np) {
+        const int ch = (warp * LW >> 3) + 2 * np + (mi >> 1);
+        uint32_t b[4];
+        ldsm4t(b, sb + (uint32_t)(tok * RS + ((ch ^ (tok & 7)) << 4)));
+        mma16816(o[2 * np], pa, &b[0]);
+        mma16816(o[2 * np + 1], pa, &b[2]);
+      }
+    }
+    __syncthreads();                 // the stage and s_part are rewritten by the next iteration
+  }
+  cp_wait<0>();
+  l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1); l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+  l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+  const int row0 = lane >> 2, row1 = row0 + 8;
+  const float inv0 = l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
+#pragma unroll
+  for (int i = 0; i < LW / 8; ++i) {
+    const int colv = warp * LW + i * 8 + 2 * (lane & 3);
+    if (row0 < rows_valid)
+      *reinterpret_cast<uint32_t*>(p.out + ((size_t)t * p.H + g * 16 + row0) * p.L + colv) =
+          pack2(o[i][0] * inv0, o[i][1] * inv0);
+    if (row1 < rows_valid)
+      *reinterpret_cast<uint32_t*>(p.out + ((size_t)t * p.H + g * 16 + row1) * p.L + colv) =
+          pack2(o[i][2] * inv1, o[i][3] * inv1);
+  }
+  if (p.lse != nullptr && warp == 0 && (lane & 3) == 0) {
+    if (row0 < rows_valid)
+      p.lse[(size_t)t * p.H + g * 16 + row0] = l[0] > 0.f ? (m[0] + log2f(l[0])) * 0.6931471805599453f : -INFINITY;
+    if (row1 < rows_valid)
+      p.lse[(size_t)t * p.H + g * 16 + row1] = l[1] > 0.f ? (m[1] + log2f(l[1])) * 0.6931471805599453f : -INFINITY;
+  }
+}
+
+// cache row of slot s = kv_c[t] (L values) followed by k_pe[t] (R values); slot < 0: skipped
+__global__ void mla_write_cache_kernel(__nv_bfloat16* __restrict__ cache, const __nv_bfloat16* __restrict__ kv_c,
+                                       const __nv_bfloat16* __restrict__ k_pe, const int* __restrict__ slots,
+                                       int L, int R, int ld_c, int ld_pe, long long num_slots) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const long long slot = slots[t];
+  if (slot < 0 || slot >= num_slots) return;
+  __nv_bfloat16* dst = cache + (size_t)slot * (L + R);
+  for (int i = threadIdx.x; i < L + R; i += blockDim.x)
+    dst[i] = i < L ? kv_c[(size_t)t * ld_c + i] : k_pe[(size_t)t * ld_pe + (i - L)];
+}
+
+}  // namespace mla
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_mla_write_cache(void* cache, const void* kv_c, const void* k_pe, const int* slots, int T, int L,
+                                    int R, int ld_c, int ld_pe, long long num_slots, cudaStream_t stream) {
+  if (T == 0) return 0;
+  B200_CUDA_CHECK(launch_pdl(mla::mla_write_cache_kernel, dim3(T), dim3(128), 0, stream, (__nv_bfloat16*)cache,
+                             (const __nv_bfloat16*)kv_c, (const __nv_bfloat16*)k_pe, slots, L, R, ld_c, ld_pe,
+                             num_slots));
+  return 0;
+}
+
+// q [T, H, Dq], cache [num_blocks, block_size, Dq], out [T, H, L], lse [T, H] or null,
+// topk [T, topk_k] or null.  Dq % 16 == 0, Dq <= 576, L in {64, 128, 256, 512}.
+extern "C" int b200_mla_attention(const void* q, const void* cache, void* out, float* lse, const int* block_tables,
+                                  const int* seq_lens, const int* qsl, const int* topk, int topk_k, int T,
+                                  int num_reqs, int H, int Dq, int L, int max_blocks, int block_size,
+                                  long long num_blocks, float scale, cudaStream_t stream) {
+  if (T <= 0 || num_reqs <= 0) return 0;
+  if (Dq % 16 || Dq > 4 * mla::KS_MAX * 16 || L > Dq || (L != 64 && L != 128 && L != 256 && L != 512)) {
+    b200_set_last_error("mla_attention: Dq % 16 == 0, Dq <= 576 and kv_lora in {64,128,256,512} required",
+                        __FILE__, __LINE__);
+    return -1;
+  }
+  mla::Params p;
+  p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache; p.out = (__nv_bfloat16*)out;
+  p.lse = lse; p.block_tables = block_tables; p.seq_lens = seq_lens; p.qsl = qsl;
+  p.topk = topk; p.topk_k = topk_k;
+  p.T = T; p.H = H; p.Dq = Dq; p.L = L; p.num_reqs = num_reqs; p.max_blocks = max_blocks;
+  p.block_size = block_size; p.num_blocks = num_blocks;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const int nch = Dq / 8;
+  const int smem = 2 * 16 * (((nch + 7) & ~7) << 4);
+  const dim3 grid(T * ((H + 15) / 16));
+#define MLA_LAUNCH(LWV)                                                                                      \
+  do {                                                                                                       \
+    B200_CUDA_CHECK(cudaFuncSetAttribute(mla::mla_attn_kernel<LWV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         smem));                                                             \
+    B200_CUDA_CHECK(launch_pdl(mla::mla_attn_kernel<LWV>, grid, dim3(128), (size_t)smem, stream, p));         \
+  } while (0)
+  if (L == 512) MLA_LAUNCH(128);
+  else if (L == 256) MLA_LAUNCH(64);
+  else if (L == 128) MLA_LAUNCH(32);
+  else MLA_LAUNCH(16);
+#undef MLA_LAUNCH
+  return 0;
+}

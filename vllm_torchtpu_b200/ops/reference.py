@@ -335,7 +335,8 @@ def mla_paged_attention(q_latent, cache, block_tables, seq_lens, query_start_loc
             sel = torch.zeros(q_len, kv_len, dtype=torch.bool, device=s.device)
             idx = topk_indices[qs:qe].long()
             ok = (idx >= 0) & (idx < kv_len)
-            sel.scatter_(1, idx.clamp(0, kv_len - 1), ok)
+            qrow = torch.arange(q_len, device=s.device)[:, None].expand_as(idx)
+            sel[qrow[ok], idx[ok]] = True           # unused (-1) and out-of-range entries select nothing
             mask = mask & sel
         s = s.masked_fill(~mask[None], float("-inf"))
         l = torch.logsumexp(s, dim=-1)
