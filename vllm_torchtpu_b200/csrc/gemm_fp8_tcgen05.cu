@@ -281,11 +281,14 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       }
       const uint32_t part_local = smem_u32(smem);
       for (int c = (int)rank + S * q; c < k.t_valid; c += 4 * S) {
+        float4 v[8];                     // all partials of the column are requested before the first is used
+#pragma unroll
+        for (int r2 = 0; r2 < 8; ++r2)
+          if (r2 < S) v[r2] = ld_dsmem_v4(mapa_shared(part_local + (uint32_t)((c * BM + 4 * lane) * 4), r2));
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r2 = 0; r2 < S; ++r2) {
-          const float4 v = ld_dsmem_v4(mapa_shared(part_local + (uint32_t)((c * BM + 4 * lane) * 4), r2));
-          a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
-        }
+#pragma unroll
+        for (int r2 = 0; r2 < 8; ++r2)
+          if (r2 < S) { a.x += v[r2].x; a.y += v[r2].y; a.z += v[r2].z; a.w += v[r2].w; }
         const float vals[4] = {a.x, a.y, a.z, a.w};
         __nv_bfloat16* yp = p.Y + (size_t)(k.t_row + c) * p.ldy + n4;
 #pragma unroll

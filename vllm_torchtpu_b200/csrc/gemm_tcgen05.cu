@@ -98,6 +98,7 @@ struct GemmParams {
   // before its owner has finished the previous launch that used it (epoch kept in ctrl[2 + flip])
   unsigned long long ag_done_off;
   int ag_flip;
+  unsigned long long* dbg;               // optional: per-CTA phase timestamps (ns), 16 slots per CTA
   int* epoch_ptr;                        // local: epoch of the last completed fused launch
   int* cta_done;                         // local: CTA exit counter
   unsigned int spin_limit;
@@ -133,13 +134,13 @@ struct Work {
 };
 
 // dense: tiles rastered in groups of GROUP_N weight tiles; grouped: work = (token tile of an expert, n tile)
-template <int BN>
+template <int BN, bool FULL = true>
 __device__ __forceinline__ Work get_work(int w, const GemmParams& p, const int* s_prefix) {
   Work k;
-  if (p.group_off == nullptr) {
+  if (!FULL || p.group_off == nullptr) {
     int n_tile, t_tile;
     decode_work(w, p, n_tile, t_tile, k.split, k.tile);
-    if (p.ar_mode == 5) {          // start with the token blocks of this rank's own shard
+    if (FULL && p.ar_mode == 5) {  // start with the token blocks of this rank's own shard
       t_tile += p.rank * p.ag_tps;
       if (t_tile >= p.t_tiles) t_tile -= p.t_tiles;
     }
@@ -180,10 +181,10 @@ struct TileDst {
   __nv_bfloat16* base;
   int cs;
 };
-template <int BN>
+template <int BN, bool FULL = true>
 __device__ __forceinline__ TileDst tile_dst(const GemmParams& p, const Work& wk, int d) {
   TileDst t;
-  if (p.world == 1 || p.ar_mode == 5) {
+  if (!FULL || p.world == 1 || p.ar_mode == 5) {
     t.base = p.Y + (size_t)wk.t_row * p.ldy + wk.n0;
     t.cs = p.ldy;
   } else if (p.ar_mode >= 2) {
@@ -275,8 +276,76 @@ __device__ __forceinline__ void sum_slabs4(const uint8_t* slab, size_t stride, i
   }
 }
 
-template <int BN, int NACC>
-__global__ void __launch_bounds__(NUM_THREADS_FUSED, 1)
+// Split-K reduction over distributed shared memory, the share of cluster CTA `rank`, warp `q`:
+// columns c = rank + S*q + 4*S*i of the fp32 partials [column][row] that every CTA of the cluster
+// keeps at shared offset part_local are summed over the S CTAs in rank order and stored as bf16.
+template <int BN, int SMAX, bool FULL>
+__device__ __forceinline__ void cluster_reduce_cols(const GemmParams& p, const Work& wk, uint32_t part_local,
+                                                    int rank, int q, int lane, int ndst, const float (&b4)[4]) {
+  constexpr int CPC = 16 / SMAX;                 // whole columns per batch of loads
+  const int S = p.splits;
+  const int n4 = wk.n0 + 4 * lane;
+  for (int i0 = 0; rank + S * q + 4 * S * i0 < wk.t_valid; i0 += CPC) {
+    float4 v[CPC][SMAX];
+#pragma unroll
+    for (int ci = 0; ci < CPC; ++ci) {
+      const int c = rank + S * q + 4 * S * (i0 + ci);
+#pragma unroll
+      for (int r2 = 0; r2 < SMAX; ++r2)
+        if (r2 < S && c < wk.t_valid) {
+          v[ci][r2] = ld_dsmem_v4(mapa_shared(part_local + (uint32_t)((c * BM + 4 * lane) * 4), r2));
+        }
+    }
+#pragma unroll
+    for (int ci = 0; ci < CPC; ++ci) {
+      const int c = rank + S * q + 4 * S * (i0 + ci);
+      if (c < wk.t_valid) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r2 = 0; r2 < SMAX; ++r2)
+          if (r2 < S) { a.x += v[ci][r2].x; a.y += v[ci][r2].y; a.z += v[ci][r2].z; a.w += v[ci][r2].w; }
+        for (int d = 0; d < ndst; ++d) {
+          const TileDst td = tile_dst<BN, FULL>(p, wk, d);
+          __nv_bfloat16* yp = td.base + (size_t)c * td.cs + 4 * lane;
+          const bool vec_ok = (n4 + 3 < p.N) && ((td.cs & 3) == 0) &&
+                              ((reinterpret_cast<uintptr_t>(td.base) & 7) == 0);
+          if (vec_ok) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(a.x + b4[0], a.y + b4[1]);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(a.z + b4[2], a.w + b4[3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(yp) = pk;
+          } else {
+            const float vals[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+          }
+        }
+      }
+    }
+  }
+}
+
+// Phase timestamps are compiled in only with -DB200_GEMM_TIMESTAMPS (they lengthen the hot path).
+__device__ __forceinline__ void dbg_stamp(const GemmParams& p, int slot) {
+#ifdef B200_GEMM_TIMESTAMPS
+  if (p.dbg != nullptr) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.dbg[(size_t)blockIdx.x * 16 + slot] = t;
+  }
+#else
+  (void)p; (void)slot;
+#endif
+}
+
+// FULL = false is the compact instantiation for the common single-rank dense case (no grouped mode, no
+// cross-rank roles, no global-scratch split-K): the cold paths it leaves out cost instruction-cache
+// misses in the short decode GEMMs even when they are never taken.
+template <int BN, int NACC, bool FULL>
+__global__ void __launch_bounds__(FULL ? NUM_THREADS_FUSED : NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  const GemmParams p) {
   using Cfg = GemmCfg<BN, NACC>;
@@ -294,7 +363,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
   volatile int* red_ok = reinterpret_cast<volatile int*>(tmem_slot + 3);
   int* s_prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES);
-  const bool fused = p.world > 1;
+  const bool fused = FULL && p.world > 1;
   __nv_bfloat16* const dst_base = p.Y;       // SwiGLU and grouped launches (never fused)
   const bool push_out = fused && p.ar_mode <= 3;       // the epilogue feeds a cross-rank reduction
   const int ndst = (push_out && p.ar_mode >= 2) ? p.world : 1;
@@ -302,6 +371,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  if (threadIdx.x == 0) dbg_stamp(p, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -327,14 +397,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   // Weights do not depend on the previous kernel, so in dense mode the producer prefetches weight
   // tiles before it waits; every other thread waits here.  Grouped mode reads the expert offsets
   // the previous kernel wrote, so all of it waits first.
-  const bool dense = p.group_off == nullptr;
+  const bool dense = !FULL || p.group_off == nullptr;
   pdl_launch_dependents();
   if (!(dense && warp == 0)) pdl_wait();
   // The epoch is bumped by the last CTA of a fused launch to exit, so it must be read after the wait
   // above (the previous launch may be a fused one that is still running) and is read by every thread
   // before any CTA of this launch can bump it.  Warp 0 never uses it.
   const int epoch = (fused && warp != 0) ? (*reinterpret_cast<volatile int*>(p.epoch_ptr) + 1) : 0;
-  if (p.group_off != nullptr) {
+  if (FULL && p.group_off != nullptr) {
     // token tiles per expert -> exclusive prefix (serial scan: at most MAX_GROUPS short steps)
     for (int e = threadIdx.x; e < p.num_groups; e += blockDim.x)
       s_prefix[e + 1] = (p.group_off[e + 1] - p.group_off[e] + BN - 1) / BN;
@@ -348,8 +418,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total_work = p.group_off != nullptr ? s_prefix[p.num_groups] * p.n_tiles
+  const int total_work = (FULL && p.group_off != nullptr) ? s_prefix[p.num_groups] * p.n_tiles
                                                 : p.n_tiles * p.t_tiles * p.splits;
+  if (threadIdx.x == 0) dbg_stamp(p, 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -360,7 +431,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       bool ok = true;
       int npre = 0;             // weight tiles of the first work item already in flight (dense mode)
       if (dense && (int)blockIdx.x < total_work) {
-        const Work k0 = get_work<BN>(blockIdx.x, p, s_prefix);
+        const Work k0 = get_work<BN, FULL>(blockIdx.x, p, s_prefix);
         npre = min(STAGES, k0.kb1 - k0.kb0);
         for (int i = 0; i < npre; ++i) {
           uint8_t* a = smem + i * Cfg::STAGE_BYTES;
@@ -373,12 +444,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
       }
       if (dense) pdl_wait();
-      const int ag_epoch = p.ar_mode == 5 ? *reinterpret_cast<volatile int*>(p.epoch_ptr) + 1 : 0;
+      const int ag_epoch = (FULL && p.ar_mode == 5) ? *reinterpret_cast<volatile int*>(p.epoch_ptr) + 1 : 0;
       uint32_t ag_seen[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};   // blocks known to have arrived, per source
       int issued = 0;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const Work k = get_work<BN>(w, p, s_prefix);
-        if (p.ar_mode == 5) {
+        const Work k = get_work<BN, FULL>(w, p, s_prefix);
+        if (FULL && p.ar_mode == 5) {
           const int blk = k.t_row / BN, src = blk / p.ag_tps, j = blk - src * p.ag_tps;
           if (!((ag_seen[src] >> j) & 1u)) {
             const int* f = reinterpret_cast<const int*>(p.peer[p.rank] + p.tile_flag_off) +
@@ -430,7 +501,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       int iter = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
-        const Work wk = get_work<BN>(w, p, s_prefix);
+        const Work wk = get_work<BN, FULL>(w, p, s_prefix);
         const int kb0 = wk.kb0, kb1 = wk.kb1;
         const int acc = iter & 1;
         const uint32_t acc_ph = (iter >> 1) & 1;
@@ -439,6 +510,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          if (iter == 0 && kb == kb0) dbg_stamp(p, 2);
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
           const uint64_t adesc = umma_desc_k_sw128(a_addr);
@@ -455,6 +527,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (ok) umma_commit(&tfull[acc]);
+        dbg_stamp(p, 3);
       }
     }
   } else if (warp < 6) {
@@ -464,11 +537,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     int iter = 0;
     uint32_t push_count = 0;                      // bulk copies issued so far (selects the staging buffer)
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++iter) {
-      const Work wk = get_work<BN>(w, p, s_prefix);
+      const Work wk = get_work<BN, FULL>(w, p, s_prefix);
       const int tile = wk.tile, split = wk.split;
       const int acc = iter & 1;
       const uint32_t acc_ph = (iter >> 1) & 1;
       if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
+      if (threadIdx.x == 64) dbg_stamp(p, 4);
       tc_fence_after();
       const int n = wk.n0 + row;
       const int t0 = wk.t_row;
@@ -497,7 +571,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
-      } else if (p.row_route != nullptr) {
+      } else if (FULL && p.row_route != nullptr) {
         // expert-parallel combine: every output row is stored into the return slot of the rank that
         // sent the token (a peer's heap or this rank's own)
 #pragma unroll 1
@@ -524,7 +598,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         __threadfence_system();
       } else if (p.splits == 1 && fused && p.ar_mode < 2) {
         // partial tile -> the owner's slab [BN][BM] bf16, 32 columns (8 KB) per bulk copy
-        uint8_t* slab = reinterpret_cast<uint8_t*>(tile_dst<BN>(p, wk, 0).base);
+        uint8_t* slab = reinterpret_cast<uint8_t*>(tile_dst<BN, FULL>(p, wk, 0).base);
         __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + Cfg::PUSH_OFF);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -564,7 +638,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           tmem_ld_wait();
           if (n < p.N) {
             for (int d = 0; d < ndst; ++d) {
-              const TileDst td = tile_dst<BN>(p, wk, d);
+              const TileDst td = tile_dst<BN, FULL>(p, wk, d);
               __nv_bfloat16* yp = td.base + (size_t)c0 * td.cs + row;
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -599,7 +673,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
-      } else {
+      } else if (FULL) {
         float* wsp = p.ws + ((size_t)tile * p.splits + split) * (size_t)(BM * BN);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -652,7 +726,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
               const int c = c0 + 4 * u;
               if (c >= t_valid) continue;
               for (int d = 0; d < ndst; ++d) {
-                const TileDst td = tile_dst<BN>(p, wk, d);
+                const TileDst td = tile_dst<BN, FULL>(p, wk, d);
                 __nv_bfloat16* yp = td.base + (size_t)c * td.cs + 4 * lane;
                 const bool vec_ok = (n4 + 3 < p.N) && ((td.cs & 3) == 0) &&
                                     ((reinterpret_cast<uintptr_t>(td.base) & 7) == 0);
@@ -828,8 +902,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     __syncwarp();
     cluster_arrive_release();
     cluster_wait_acquire();
+    if (threadIdx.x == 64) dbg_stamp(p, 5);
     if (warp >= 2 && warp < 6 && !*abort_flag && blockIdx.x < total_work) {
-      const Work wk = get_work<BN>(blockIdx.x, p, s_prefix);
+      const Work wk = get_work<BN, FULL>(blockIdx.x, p, s_prefix);
+      if (threadIdx.x == 64) dbg_stamp(p, 9);
       const int q = warp & 3;
       const uint32_t rank = cluster_ctarank();
       const int S = p.splits;
@@ -841,43 +917,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           if (n4 + j < p.N) b4[j] = __bfloat162float(p.bias[n4 + j]);
       }
       const uint32_t part_local = smem_u32(smem);
-      for (int c = (int)rank + S * q; c < wk.t_valid; c += 4 * S) {
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r2 = 0; r2 < S; ++r2) {
-          const float4 v = ld_dsmem_v4(mapa_shared(part_local + (uint32_t)((c * BM + 4 * lane) * 4), r2));
-          a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
-        }
-        for (int d = 0; d < ndst; ++d) {
-          const TileDst td = tile_dst<BN>(p, wk, d);
-          __nv_bfloat16* yp = td.base + (size_t)c * td.cs + 4 * lane;
-          const bool vec_ok = (n4 + 3 < p.N) && ((td.cs & 3) == 0) &&
-                              ((reinterpret_cast<uintptr_t>(td.base) & 7) == 0);
-          if (vec_ok) {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(a.x + b4[0], a.y + b4[1]);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(a.z + b4[2], a.w + b4[3]);
-            uint2 pk;
-            pk.x = *reinterpret_cast<uint32_t*>(&lo);
-            pk.y = *reinterpret_cast<uint32_t*>(&hi);
-            *reinterpret_cast<uint2*>(yp) = pk;
-          } else {
-            const float vals[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
-          }
-        }
-      }
+      // Distributed-shared-memory loads have a long latency (several hundred ns each round trip): the
+      // partials of as many whole columns as fit in 16 vector registers are requested together.
+      if (S <= 2) cluster_reduce_cols<BN, 2, FULL>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
+      else if (S <= 4) cluster_reduce_cols<BN, 4, FULL>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
+      else cluster_reduce_cols<BN, 8, FULL>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
       if (push_out) __threadfence_system();
     }
+    if (threadIdx.x == 64) dbg_stamp(p, 6);
     __syncwarp();
     cluster_arrive_release();          // nobody leaves while its partial may still be read
     cluster_wait_acquire();
     if (push_out && cluster_ctarank() == 0 && warp == 2 && blockIdx.x < total_work) {
-      const Work wk = get_work<BN>(blockIdx.x, p, s_prefix);
+      const Work wk = get_work<BN, FULL>(blockIdx.x, p, s_prefix);
       publish_tile(p, wk.tile, epoch, lane);
     }
   }
 
+  if (threadIdx.x == 64) dbg_stamp(p, 7);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -1001,7 +1058,8 @@ static int cached_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_
 template <int BN>
 static int max_active_clusters_t(int splits, int threads) {
   using Cfg = GemmCfg<BN, 1>;
-  cudaFuncSetAttribute(gemm_bf16_kernel<BN, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+  auto kern = threads > NUM_THREADS ? gemm_bf16_kernel<BN, 1, true> : gemm_bf16_kernel<BN, 1, false>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits * 64);
   cfg.blockDim = dim3(threads);
@@ -1014,7 +1072,7 @@ static int max_active_clusters_t(int splits, int threads) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<BN, 1>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
@@ -1045,13 +1103,30 @@ static int fit_cluster_splits(int want, int tiles, int bn, int threads) {
   return s;
 }
 
+// the compact kernel serves dense single-rank launches without split-K or with cluster split-K
+static bool plain_eligible(const GemmParams& p) {
+  return p.world == 1 && p.group_off == nullptr && p.row_route == nullptr &&
+         (p.splits == 1 || p.cluster_splitk);
+}
+
+template <int BN, int NACC, bool FULL>
+static int launch_gemm_v(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int grid,
+                         cudaStream_t stream);
+
 template <int BN, int NACC = 1>
 static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int grid,
                        cudaStream_t stream) {
+  if (plain_eligible(p)) return launch_gemm_v<BN, NACC, false>(tmW, tmX, p, grid, stream);
+  return launch_gemm_v<BN, NACC, true>(tmW, tmX, p, grid, stream);
+}
+
+template <int BN, int NACC, bool FULL>
+static int launch_gemm_v(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int grid,
+                         cudaStream_t stream) {
   using Cfg = GemmCfg<BN, NACC>;
   static bool attr_set = false;
   if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN, NACC>,
+    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN, NACC, FULL>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     attr_set = true;
   }
@@ -1078,13 +1153,20 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const Gem
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, NACC>, tmW, tmX, p));
+  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, NACC, FULL>, tmW, tmX, p));
   return 0;
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
 
 }  // namespace b200
+
+namespace b200 { static unsigned long long* g_gemm_dbg = nullptr; }
+// Debug aid (builds with -DB200_GEMM_TIMESTAMPS): plain GEMM launches record phase timestamps (ns),
+// 16 slots per CTA, into `buf`
+// (start, set-up done, first stage landed, last MMA issued, accumulator ready, split-K partials
+// visible, reduced and stored, cluster released).
+extern "C" void b200_gemm_set_debug(unsigned long long* buf) { b200::g_gemm_dbg = buf; }
 
 extern "C" int b200_gemm_plan(int T, int N, int K, int num_sms, int* bn_out, int* splits_out,
                               size_t* ws_bytes, int* counters_needed) {
@@ -1152,6 +1234,7 @@ extern "C" int b200_gemm_bf16(const void* X, const void* W, void* Y, const void*
   }
   p.w_evict_first = (p.t_tiles == 1) ? 1 : 0;
   p.cluster_splitk = (p.splits > 1 && p.splits <= 8) ? 1 : 0;
+  p.dbg = g_gemm_dbg;
   CUtensorMap tmW, tmX;
   int rc = cached_tmap(&tmW, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, BM);
   if (rc) return rc;
