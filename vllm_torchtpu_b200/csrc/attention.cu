@@ -365,7 +365,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
 
 // ----------------------------------------------------------------------- prefill
 template <int D>
-__global__ void __launch_bounds__(128, 2) attn_prefill_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p) {
   constexpr int BQ = 64, BKV = 64, STAGES = 2;
   constexpr int TILE_BYTES = BKV * D * 2;          // K (or V) chunk
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;

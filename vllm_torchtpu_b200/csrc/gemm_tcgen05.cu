@@ -1015,6 +1015,33 @@ extern "C" int b200_make_tmap_2d(void* out_map, const void* ptr, int elem_bytes,
   return 0;
 }
 
+// bf16 3D tensor map: dims (x fastest, y, z), byte strides of y and z, box (bx, by, bz), SWIZZLE_128B.
+extern "C" int b200_make_tmap_3d_bf16(void* out_map, const void* ptr, uint64_t dx, uint64_t dy, uint64_t dz,
+                                      uint64_t stride_y_bytes, uint64_t stride_z_bytes, uint32_t bx, uint32_t by,
+                                      uint32_t bz) {
+  auto fn = b200::get_encode_fn();
+  if (!fn) {
+    b200_set_last_error("cuTensorMapEncodeTiled not available", __FILE__, __LINE__);
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (stride_y_bytes & 15) || (stride_z_bytes & 15)) {
+    b200_set_last_error("TMA operand must be 16-byte aligned with 16-byte multiple strides", __FILE__, __LINE__);
+    return -2;
+  }
+  cuuint64_t gdim[3] = {dx, dy, dz};
+  cuuint64_t gstride[2] = {stride_y_bytes, stride_z_bytes};
+  cuuint32_t box[3] = {bx, by, bz};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                  const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    b200_set_last_error("cuTensorMapEncodeTiled (3D) failed", __FILE__, __LINE__);
+    return (int)r;
+  }
+  return 0;
+}
+
 namespace b200 {
 
 struct TmapKey {

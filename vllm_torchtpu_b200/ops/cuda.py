@@ -287,11 +287,19 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
             tiles = int(((ql + 63) // 64).sum())
         else:
             tiles = (T + 63) // 64 + (R - nd)
-        _check(L.b200_attn_prefill(
-            _p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
-            _p(meta.query_start_loc), c_int(nd), c_int(R), c_int(tiles), c_int(max_blocks), c_int(bs),
-            c_longlong(nb), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale), c_int(window), c_float(cap),
-            _p(sinks), _stream()), "attn_prefill")
+        if D == 128 and G in (1, 2, 4, 8) and envs.B200_ATTN_PREFILL_IMPL == "tc":
+            # tcgen05 kernel: one CTA per (kv head, 128 / G positions), K/V shared by the GQA group
+            _check(L.b200_attn_prefill_tc(
+                _p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
+                _p(meta.query_start_loc), c_int(nd), c_int(R), c_int(tiles), c_int(T), c_int(max_blocks),
+                c_int(bs), c_longlong(nb), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale), c_int(window),
+                c_float(cap), _p(sinks), _p(ws.status), _stream()), "attn_prefill_tc")
+        else:
+            _check(L.b200_attn_prefill(
+                _p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
+                _p(meta.query_start_loc), c_int(nd), c_int(R), c_int(tiles), c_int(max_blocks), c_int(bs),
+                c_longlong(nb), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale), c_int(window), c_float(cap),
+                _p(sinks), _stream()), "attn_prefill")
         count_launch()
     if return_lse:
         return out, lse
