@@ -1,0 +1,54 @@
+"""Multi-rank engine paths on CPU (gloo, two processes): tensor, pipeline and expert parallelism
+must generate the tokens of the single-process engine."""
+import json
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(nproc, *args, timeout=240):
+    worker = os.path.join(HERE, "workers", "cpu_parallel_worker.py")
+    if nproc == 1:
+        cmd = [sys.executable, worker, *args]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+               "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), worker, *args]
+    env = dict(os.environ)
+    env.update({"OMP_NUM_THREADS": "2", "CUDA_VISIBLE_DEVICES": ""})
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    for line in r.stdout.splitlines():
+        if line.startswith("RESULT "):
+            return json.loads(line[7:])["tokens"]
+    raise AssertionError(r.stdout[-2000:] + r.stderr[-3000:])
+
+
+@pytest.fixture(scope="module")
+def single():
+    return _run(1, "tp", "tiny-llama")
+
+
+def test_tp2_matches_single_process(single):
+    assert _run(2, "tp", "tiny-llama") == single
+
+
+def test_pp2_matches_single_process(single):
+    assert _run(2, "pp", "tiny-llama") == single
+
+
+def test_pp2_async_scheduling_matches_single_process(single):
+    assert _run(2, "pp", "tiny-llama", "--async") == single
+
+
+def test_ep2_moe_matches_single_process():
+    assert _run(2, "ep", "tiny-moe") == _run(1, "tp", "tiny-moe")

@@ -1,0 +1,44 @@
+"""Child process of the CPU multi-rank tests (gloo, launched by torch.distributed.run): the same
+prompts through an engine with tensor or pipeline parallelism; rank 0 prints the tokens as JSON."""
+import json
+import os
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def main():
+    import faulthandler
+    faulthandler.dump_traceback_later(150, exit=True)
+    from vllm_torchtpu_b200 import SamplingParams
+    from vllm_torchtpu_b200.engine.llm import LLM
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    mode = sys.argv[1] if len(sys.argv) > 1 else "tp"
+    model = sys.argv[2] if len(sys.argv) > 2 else "tiny-llama"
+    kw = {}
+    if mode == "tp":
+        kw["tensor_parallel_size"] = world
+    elif mode == "pp":
+        kw["pipeline_parallel_size"] = world
+    elif mode == "ep":
+        kw["tensor_parallel_size"] = world
+        kw["enable_expert_parallel"] = True
+    llm = LLM(model, device="cpu", max_num_seqs=8, max_num_batched_tokens=64, block_size=16,
+              num_gpu_blocks_override=64, async_scheduling="--async" in sys.argv, **kw)
+    rng = np.random.RandomState(0)
+    vocab = llm.engine.cfg.model.vocab_size
+    prompts = [rng.randint(0, vocab, size=n).tolist() for n in (5, 23, 70)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    if int(os.environ.get("RANK", "0")) == 0:
+        print("RESULT " + json.dumps({"tokens": [o.outputs[0].token_ids for o in outs]}), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()

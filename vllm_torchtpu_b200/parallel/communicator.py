@@ -53,8 +53,10 @@ class DeviceCommunicator:
         if self.size == 1:
             return x
         dim = dim % x.dim()
-        out = torch.empty((self.size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group.device_group)
+        # the concatenated output form is accepted by NCCL and gloo alike
+        flat = torch.empty((self.size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(flat, x.contiguous(), group=self.group.device_group)
+        out = flat.view((self.size,) + tuple(x.shape))
         if dim == 0:
             return out.reshape((self.size * x.shape[0],) + tuple(x.shape[1:]))
         out = out.movedim(0, dim)
@@ -67,6 +69,11 @@ class DeviceCommunicator:
             return x
         x = x.movedim(dim, 0).contiguous()
         assert x.shape[0] % self.size == 0
+        if not x.is_cuda:
+            # gloo has no reduce-scatter: reduce everything, keep this rank's slice
+            dist.all_reduce(x, group=self.group.device_group)
+            n = x.shape[0] // self.size
+            return x[self.rank * n:(self.rank + 1) * n].movedim(0, dim)
         out = torch.empty((x.shape[0] // self.size,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         dist.reduce_scatter_tensor(out, x, group=self.group.device_group)
         return out.movedim(0, dim)
@@ -78,6 +85,13 @@ class DeviceCommunicator:
         if self.size == 1:
             return x
         pieces = [p.contiguous() for p in x.chunk(self.size, dim=split_dim)]
+        if not x.is_cuda:
+            # gloo: gather everybody's pieces, keep the ones addressed to this rank
+            stacked = torch.stack(pieces, 0)
+            every = torch.empty((self.size * self.size,) + tuple(pieces[0].shape), dtype=x.dtype)
+            dist.all_gather_into_tensor(every, stacked, group=self.group.device_group)
+            every = every.view((self.size, self.size) + tuple(pieces[0].shape))
+            return torch.cat([every[src, self.rank] for src in range(self.size)], dim=concat_dim)
         outs = [torch.empty_like(pieces[0]) for _ in range(self.size)]
         dist.all_to_all(outs, pieces, group=self.group.device_group)
         return torch.cat(outs, dim=concat_dim)

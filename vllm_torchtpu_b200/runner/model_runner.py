@@ -282,6 +282,9 @@ class ModelRunner:
         n_req_pad, verify = R, L is not None
         R = L if verify else R
         ids = dv("input_ids", T)
+        st = get_state()
+        if st.pp.size > 1:
+            return self._forward_and_sample_pp(bufs, meta, T, R, n_req_pad, all_greedy, verify)
         hidden0 = self._embed(ids, dv("token_src", T))
         hidden, residual = self.model.forward(ids, meta, self.kv_caches, hidden=hidden0)
         rows = self._select_rows(hidden, residual, meta.logits_indices)
@@ -314,6 +317,61 @@ class ModelRunner:
                 uniform = torch.rand(logits.shape, generator=self._gen, dtype=torch.float32)
             tokens = ops.sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
                                 dv("top_p", R, torch.float32), uniform, all_greedy).to(torch.int32)
+        if not verify:
+            self._store_last_tokens(tokens, dv("batch_slots", n_req_pad))
+        return tokens, logits
+
+    def _pp_handoff(self):
+        if getattr(self, "_pp", None) is None:
+            from ..parallel.pp import NcclTransport, PPHandoff
+            st = get_state()
+            self._pp = PPHandoff(NcclTransport(), prev_rank=None if st.pp.is_first else st.pp.prev_rank,
+                                 next_rank=None if st.pp.is_last else st.pp.next_rank,
+                                 hidden_size=self.mcfg.hidden_size, dtype=self.mcfg.dtype, device=self.device,
+                                 my_rank=st.rank)
+        return self._pp
+
+    def _forward_and_sample_pp(self, bufs, meta, T, R, n_req_pad, all_greedy, verify):
+        """One step on one pipeline stage.  Every stage schedules the same batch (the schedulers run in
+        lockstep); a stage receives hidden + residual as one tensor from its predecessor, runs its
+        layers and hands the sum on; the last stage samples and broadcasts the tokens to the others
+        (reference: src/vllm_torchtpu/distributed/pp_buffered.py:14-85, runner/tpu_runner.py:8953-9034)."""
+        import torch.distributed as dist
+        dv = bufs.dev_view
+        st = get_state()
+        pp = self._pp_handoff()
+        ids = dv("input_ids", T)
+        if st.pp.is_first:
+            hidden, residual = self._embed(ids, dv("token_src", T)), None
+        else:
+            hidden, residual, _ = pp.start_forward(T)
+        hidden, residual = self.model.forward(ids, meta, self.kv_caches, hidden=hidden, residual=residual)
+        last_global = st.pp.ranks[-1]
+        if st.pp.is_last:
+            rows = self._select_rows(hidden, residual, meta.logits_indices)
+            h = self.model.finalize(*rows)
+            logits = self.model.compute_logits(h)
+            if self._step_bitmask is not None:
+                from ..structured import apply_token_bitmask
+                bm, brows = self._step_bitmask
+                apply_token_bitmask(logits, bm.to(logits.device), brows.to(logits.device))
+            uniform = None
+            if not all_greedy and not self.is_cuda:
+                uniform = torch.rand(logits.shape, generator=self._gen, dtype=torch.float32)
+            if self.is_cuda:
+                tokens = ops.cuda_ops().sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
+                                               dv("top_p", R, torch.float32), None, all_greedy,
+                                               seed=self.mcfg.seed, step_tensor=dv("rng_step").view(torch.int64))
+            else:
+                tokens = ops.sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
+                                    dv("top_p", R, torch.float32), uniform, all_greedy).to(torch.int32)
+            pp.end_forward(hidden, residual)           # counts the transfer; nothing is sent
+        else:
+            pp.end_forward(hidden, residual)
+            tokens = torch.empty(R, dtype=torch.int32, device=self.device)
+            logits = None
+        tokens = tokens.contiguous()
+        dist.broadcast(tokens, src=last_global, group=st.pp.device_group)
         if not verify:
             self._store_last_tokens(tokens, dv("batch_slots", n_req_pad))
         return tokens, logits
@@ -360,7 +418,8 @@ class ModelRunner:
             if bm is not None:
                 self._step_bitmask = (bm, rows)
         use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
-                     and envs.B200_CUDA_GRAPHS and self._step_bitmask is None)
+                     and envs.B200_CUDA_GRAPHS and self._step_bitmask is None
+                     and get_state().pp.size == 1)          # pipeline stages hand off through host threads
         if use_graph:
             key = (R, p["all_greedy"])
             g = self.graphs.get(key)
@@ -432,7 +491,7 @@ class ModelRunner:
 
     def capture_model(self) -> None:
         """Capture every decode request bucket (greedy variant) ahead of serving."""
-        if not (self.is_cuda and envs.B200_CUDA_GRAPHS) or self.cfg.enforce_eager:
+        if not (self.is_cuda and envs.B200_CUDA_GRAPHS) or self.cfg.enforce_eager or get_state().pp.size > 1:
             return
         t0 = time.time()
         for R in reversed(self.cfg.request_buckets):
