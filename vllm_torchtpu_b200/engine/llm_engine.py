@@ -99,6 +99,31 @@ class LLMEngine:
                                            kv_transfer_params=kv_transfer_params))
         return rid
 
+    # ---- LoRA adapters (reference: src/vllm_torchtpu/worker/tpu_worker.py:898-908) -----------------
+    def _lora(self):
+        if getattr(self, "lora_manager", None) is None:
+            from ..lora import LoRAManager, wiring
+            add = self.cfg.additional or {}
+            self.lora_manager = LoRAManager(int(add.get("max_loras", 4)), int(add.get("max_lora_rank", 64)),
+                                            dtype=self.cfg.model.dtype, device=self.runner.device)
+            wiring.attach(self.runner.model, self.lora_manager)
+            self.runner.lora_manager = self.lora_manager
+        return self.lora_manager
+
+    def add_lora(self, name: str, rank: int, alpha: float, weights: dict) -> bool:
+        """weights: {"model.layers.N.self_attn.q_proj": (A [r, in], B [out, r]), ...}."""
+        from ..lora import LoRAAdapter
+        return self._lora().add_adapter(LoRAAdapter(name, rank, alpha, weights))
+
+    def remove_lora(self, name: str) -> bool:
+        return self._lora().remove_adapter(name)
+
+    def pin_lora(self, name: str) -> bool:
+        return self._lora().pin_adapter(name)
+
+    def list_loras(self) -> list:
+        return self._lora().list_adapters()
+
     def abort_request(self, request_id: str) -> None:
         self.scheduler.abort_request(request_id)
 

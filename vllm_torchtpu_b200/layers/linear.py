@@ -62,8 +62,15 @@ class LinearBase:
     def weight_bytes(self) -> int:
         return self.method.weight_bytes(self)
 
+    lora_targets = None          # set by lora.wiring.attach: [(adapter target name, column offset)]
+
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        return self.forward(x)
+        y = self.forward(x)
+        if self.lora_targets:
+            from ..lora import wiring
+            if wiring.active():
+                y = wiring.apply(self, x, y)
+        return y
 
 
 class ReplicatedLinear(LinearBase):
@@ -126,7 +133,8 @@ class RowParallelLinear(LinearBase):
         if (x.is_cuda and comm.heap is not None and comm.heap.fused_tp is not None
                 and self.method.supports_fused_reduce):
             ft = comm.heap.fused_tp
-            if (self.defer_reduce and self.bias is None and hasattr(self.method, "apply_push")
+            if (self.defer_reduce and self.bias is None and not self.lora_targets
+                    and hasattr(self.method, "apply_push")
                     and ft.can_push(x.numel() // x.shape[-1], self.out_features)):
                 return self.method.apply_push(self, x, comm)
             y = self.method.apply_fused_all_reduce(self, x, comm)

@@ -70,7 +70,8 @@ class LlamaMLP:
 
     def forward(self, x):
         gu = self.gate_up
-        if x.is_cuda and gu.bias is None and getattr(gu.method, "supports_fused_reduce", False):
+        if (x.is_cuda and gu.bias is None and getattr(gu.method, "supports_fused_reduce", False)
+                and not gu.lora_targets):
             # gate and up tiles share the activation tile; SiLU*mul happens in the GEMM epilogue
             return self.down(ops.cuda_ops().gemm_swiglu(x, gu.weight))
         return self.down(ops.silu_and_mul(self.gate_up(x)))

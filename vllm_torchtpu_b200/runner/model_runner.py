@@ -412,13 +412,22 @@ class ModelRunner:
         if self.timing_events is not None and self.is_cuda:
             ev0 = torch.cuda.Event(enable_timing=True)
             ev0.record()
+        lora_idx = None
+        if getattr(self, "lora_manager", None) is not None:
+            names = [s.request.sampling_params.lora_name for s in p["scheds"]]
+            lora_idx = self.lora_manager.token_indices(names, [s.num_new_tokens for s in p["scheds"]])
+            if lora_idx is not None and lora_idx.numel() < T:
+                pad = torch.full((T - lora_idx.numel(),), -1, dtype=lora_idx.dtype, device=lora_idx.device)
+                lora_idx = torch.cat([lora_idx, pad])
+            from ..lora import wiring
+            wiring.set_step(lora_idx)
         self._step_bitmask = None
         if self.structured is not None and self.structured.grammars:
             bm, rows = self.structured.build_bitmask([s.request.request_id for s in p["scheds"]])
             if bm is not None:
                 self._step_bitmask = (bm, rows)
         use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
-                     and envs.B200_CUDA_GRAPHS and self._step_bitmask is None
+                     and envs.B200_CUDA_GRAPHS and self._step_bitmask is None and lora_idx is None
                      and get_state().pp.size == 1)          # pipeline stages hand off through host threads
         if use_graph:
             key = (R, p["all_greedy"])
