@@ -199,12 +199,52 @@ def bench_decode_layer(reqs, ctx, layers=8, parts="all", iters=10, H=4096, I=143
             "status": cuda.check_status()}
 
 
+def bench_gemm_sustained(T, N, K, seconds=3.0, impl="tcgen05") -> dict:
+    """The same GEMM launched back to back for ``seconds`` (under the board power cap the clocks
+    settle below the burst value): average TFLOP/s over the whole run, with distinct weights cycled
+    so that operands stream from HBM."""
+    import subprocess
+    import time
+    from . import cuda
+    pk, tag = peaks()
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    ws = [(torch.randn(N, K, device="cuda") * 0.05).bfloat16() for _ in range(4)]
+    y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    fn = (lambda w: cuda.gemm(x, w, out=y)) if impl == "tcgen05" else (lambda w: torch.matmul(x, w.t(), out=y))
+    g = torch.cuda.CUDAGraph()
+    for w in ws:
+        fn(w)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(g):
+        for _ in range(8):
+            for w in ws:
+                fn(w)
+    per_replay = 32
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_end = time.time() + seconds
+    n = 0
+    a.record()
+    while time.time() < t_end:
+        g.replay()
+        n += per_replay
+        if n % (per_replay * 16) == 0:
+            torch.cuda.synchronize()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    clk = subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm,power.draw", "--format=csv,noheader,nounits", "-i",
+                          str(torch.cuda.current_device())], capture_output=True, text=True).stdout.strip()
+    tf = 2.0 * T * N * K * n / ms / 1e9
+    return {"op": "gemm_sustained", "impl": impl, "T": T, "N": N, "K": K, "seconds": round(ms / 1e3, 2),
+            "tflops": round(tf, 1), "launches": n, "clock_power_after": clk, "peaks": tag}
+
+
 LLAMA8B_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128256, 4096)]
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm-sweep", "attn-decode", "attn-prefill", "decode-layer", "all"])
+    ap.add_argument("what", choices=["gemm", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill", "decode-layer", "all"])
     ap.add_argument("--T", type=int, default=64)
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
@@ -225,6 +265,9 @@ def main():
                     continue
                 for impl in ("tcgen05", "cublas"):
                     print(json.dumps(bench_gemm(T, N, K, max(5, a.iters // 2), impl, check=(T <= 1024))))
+    if a.what == "gemm-sustained":
+        for impl in ("tcgen05", "cublas"):
+            print(json.dumps(bench_gemm_sustained(a.T, a.N, a.K, 3.0, impl)))
     if a.what == "decode-layer":
         for parts in a.parts.split(","):
             print(json.dumps(bench_decode_layer(a.reqs, a.ctx, a.layers, parts, a.iters)))
