@@ -52,3 +52,9 @@ def test_pp2_async_scheduling_matches_single_process(single):
 
 def test_ep2_moe_matches_single_process():
     assert _run(2, "ep", "tiny-moe") == _run(1, "tp", "tiny-moe")
+
+
+def test_dp2_with_expert_parallel_lockstep_matches_single_process():
+    """Two replicas with different (and different numbers of) requests, experts sharded over both:
+    steps run in lockstep with padded rows, an idle replica runs placeholder batches."""
+    assert _run(2, "dpep", "tiny-moe") == _run(1, "tp", "tiny-moe")

@@ -25,14 +25,32 @@ def main():
     elif mode == "ep":
         kw["tensor_parallel_size"] = world
         kw["enable_expert_parallel"] = True
+    elif mode == "dpep":
+        kw["data_parallel_size"] = world
+        kw["enable_expert_parallel"] = True
     llm = LLM(model, device="cpu", max_num_seqs=8, max_num_batched_tokens=64, block_size=16,
               num_gpu_blocks_override=64, async_scheduling="--async" in sys.argv, **kw)
     rng = np.random.RandomState(0)
     vocab = llm.engine.cfg.model.vocab_size
     prompts = [rng.randint(0, vocab, size=n).tolist() for n in (5, 23, 70)]
-    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
-    if int(os.environ.get("RANK", "0")) == 0:
-        print("RESULT " + json.dumps({"tokens": [o.outputs[0].token_ids for o in outs]}), flush=True)
+    rank = int(os.environ.get("RANK", "0"))
+    mine = prompts
+    if mode == "dpep":
+        # every replica serves its own requests: rank 0 gets two prompts, rank 1 one (uneven on purpose)
+        mine = [p for i, p in enumerate(prompts) if i % world == rank]
+    outs = llm.generate(mine, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    toks = [o.outputs[0].token_ids for o in outs]
+    if mode == "dpep":
+        import torch.distributed as dist
+        every = [None] * world
+        dist.all_gather_object(every, toks)
+        merged = [None] * len(prompts)
+        for r, part in enumerate(every):
+            for j, t in enumerate(part):
+                merged[r + j * world] = t
+        toks = merged
+    if rank == 0:
+        print("RESULT " + json.dumps({"tokens": toks}), flush=True)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()

@@ -71,6 +71,11 @@ class LLMEngine:
         self.scheduler = make_scheduler(self.cfg, num_blocks,
                                         self.connector.scheduler if self.connector else None, num_spec)
         self.runner.capture_model()
+        # Data-parallel replicas coupled by expert parallelism run their steps in lockstep: the MoE
+        # collectives of a step need every rank, with equal padded row counts on the gather plane
+        # (reference: src/vllm_torchtpu/runner/tpu_runner.py:4132-4180, worker/tpu_worker.py:696-713).
+        self._dp_lockstep = st.dp.size > 1 and st.expert_parallel
+        self._dp_group_busy = True
         self._inflight: deque = deque()
         self._next_id = 0
         self.eos_token_id: Optional[int] = None
@@ -128,14 +133,33 @@ class LLMEngine:
         self.scheduler.abort_request(request_id)
 
     def has_unfinished(self) -> bool:
+        if self._dp_lockstep:
+            # a rank without requests keeps stepping (dummy batches) while any replica has work
+            return self._dp_group_busy or self.scheduler.has_unfinished() or bool(self._inflight)
         return self.scheduler.has_unfinished() or bool(self._inflight)
 
     # ---- stepping ---------------------------------------------------------------
     def _launch(self):
         out = self.scheduler.schedule()
+        min_tokens = 0
+        if self._dp_lockstep:
+            from ..parallel.communicator import DeviceCommunicator
+            st = get_state()
+            t_pad, eager = self.runner.step_shape(out)
+            busy = 1 if (out.scheduled or self.scheduler.has_unfinished()) else 0
+            agreed = DeviceCommunicator(st.dp, None).cpu_all_reduce_max([t_pad, eager, busy])
+            self._dp_group_busy = bool(agreed[2])
+            if not self._dp_group_busy:
+                return out, self.runner.execute_model(out)           # nothing anywhere: empty result
+            if not out.scheduled:
+                self.runner.execute_dummy_batch(max(1, agreed[0]))
+                return out, self.runner.execute_model(out)
+            min_tokens = agreed[0]
+            if agreed[1]:
+                min_tokens = -agreed[0]       # some replica runs a prefill: everybody runs this step eagerly
         if self.connector is not None:
             self.connector.worker.start_load_kv(out.kv_connector_metadata)
-        res = self.runner.execute_model(out)
+        res = self.runner.execute_model(out, min_tokens=min_tokens)
         if self.connector is not None:
             self.connector.worker.save_kv(out.kv_connector_metadata)
         return out, res
@@ -168,7 +192,7 @@ class LLMEngine:
             out, res = self._launch()
             return self._retire(out, res)
         finished = []
-        if self.scheduler.has_unfinished():
+        if self.scheduler.has_unfinished() or self._dp_lockstep:
             self._inflight.append(self._launch())
         if len(self._inflight) > 1 or (self._inflight and not self.scheduler.has_unfinished()):
             out, res = self._inflight.popleft()
@@ -188,6 +212,8 @@ class LLMEngine:
     def run_until_done(self) -> list:
         done = []
         idle = 0
+        if self._dp_lockstep:
+            self._dp_group_busy = True          # step at least once: another replica may have requests
         while self.has_unfinished():
             f = self.step()
             done += f

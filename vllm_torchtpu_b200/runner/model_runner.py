@@ -188,7 +188,7 @@ class ModelRunner:
             else:
                 self.batch.append_blocks(self.batch.slot_of[s.request.request_id], s.new_block_ids)
 
-    def _prepare_inputs(self, out):
+    def _prepare_inputs(self, out, min_tokens: int = 0):
         scheds = out.scheduled
         n = len(scheds)
         b = self.batch
@@ -207,6 +207,15 @@ class ModelRunner:
             T_pad = R_pad
         else:
             R_pad, T_pad = n, T
+        if min_tokens > T_pad:
+            # lockstep with other replicas: more rows than this rank needs (padded rows: no request)
+            if decode_only and T_pad == R_pad and min_tokens in self.cfg.request_buckets and self.is_cuda \
+                    and not self.cfg.enforce_eager:
+                R_pad = T_pad = min_tokens              # still a captured decode bucket
+            else:
+                T_pad = min_tokens
+                if decode_only:
+                    bufs = self.bufs_prefill            # the decode buffers hold one row per request
         qsl = np.zeros(n + 1, dtype=np.int64)
         np.cumsum(num_new, out=qsl[1:])
         if decode_only:
@@ -398,12 +407,52 @@ class ModelRunner:
             valid = batch_slots >= 0
             self.last_tokens[batch_slots[valid].long()] = tokens[valid]
 
-    def execute_model(self, out) -> StepResult:
+    def step_shape(self, out) -> tuple:
+        """(padded token rows, 1 if the step cannot use a decode graph) of a scheduled step, for the
+        data-parallel lockstep agreement."""
+        scheds = out.scheduled
+        if not scheds:
+            return 0, 0
+        T = sum(s.num_new_tokens for s in scheds)
+        decode_only = all(s.num_new_tokens == 1 and s.start > 0 for s in scheds)
+        if decode_only and not self.cfg.enforce_eager and self.is_cuda:
+            return pad_to_bucket(len(scheds), self.cfg.request_buckets), 0
+        return T, 0 if decode_only else 1
+
+    def execute_dummy_batch(self, T: int) -> None:
+        """A step without requests for a replica that must take part in the group's collectives:
+        one placeholder request (no KV writes, output ignored) padded to ``T`` rows
+        (reference: src/vllm_torchtpu/worker/tpu_worker.py:696-713)."""
+        bufs = self.bufs_prefill
+        per = max(1, min(T, self.mcfg.max_model_len, self.block_size * self.batch.max_blocks))
+        hv = bufs.host_view
+        hv("input_ids", T)[:] = 0
+        v = hv("positions", T); v[:] = 0; v[:per] = np.arange(per)
+        hv("slot_mapping", T)[:] = -1
+        hv("token_src", T)[:] = -1
+        hv("query_start_loc", 2)[:] = [0, per]
+        hv("seq_lens", 1)[:] = per
+        hv("logits_indices", 1)[:] = per - 1
+        hv("top_k", 1)[:] = 0
+        hv("batch_slots", 1)[:] = -1
+        hv("temperature", 1, np.float32)[:] = 0
+        hv("top_p", 1, np.float32)[:] = 1
+        bufs.np_bt[:1] = 0
+        bufs.upload(1)
+        p = dict(bufs=bufs, n=1, T=per, R_pad=1, T_pad=T, num_decode=0, max_q=per, max_seq=per,
+                 seq_lens_np=np.full(1, per, dtype=np.int64), qsl_np=np.array([0, per], dtype=np.int64))
+        self._forward_and_sample(bufs, self._make_meta(p), T, 1, True)
+
+    def execute_model(self, out, min_tokens: int = 0) -> StepResult:
+        """``min_tokens`` > 0 pads the step to at least that many token rows (data-parallel lockstep);
+        a negative value additionally forces the eager path for this step."""
         if not out.scheduled:
             self._update_batch(out)
             return StepResult([], [], None, None, 0)
         self._update_batch(out)
-        p = self._prepare_inputs(out)
+        p = self._prepare_inputs(out, min_tokens=abs(min_tokens))
+        if min_tokens < 0:
+            p["decode_only"] = False
         bufs, n, R, T = p["bufs"], p["n"], p["R_pad"], p["T_pad"]
         self.stats["h2d_bytes"] += bufs.upload(R)
         meta = self._make_meta(p)
@@ -427,7 +476,7 @@ class ModelRunner:
             if bm is not None:
                 self._step_bitmask = (bm, rows)
         use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
-                     and envs.B200_CUDA_GRAPHS and self._step_bitmask is None and lora_idx is None
+                     and p["T_pad"] == p["R_pad"] and envs.B200_CUDA_GRAPHS and self._step_bitmask is None and lora_idx is None
                      and get_state().pp.size == 1)          # pipeline stages hand off through host threads
         if use_graph:
             key = (R, p["all_greedy"])
