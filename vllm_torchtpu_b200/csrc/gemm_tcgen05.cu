@@ -279,14 +279,15 @@ __device__ __forceinline__ void sum_slabs4(const uint8_t* slab, size_t stride, i
 // Split-K reduction over distributed shared memory, the share of cluster CTA `rank`, warp `q`:
 // columns c = rank + S*q + 4*S*i of the fp32 partials [column][row] that every CTA of the cluster
 // keeps at shared offset part_local are summed over the S CTAs in rank order and stored as bf16.
-template <int BN, int SMAX, bool FULL>
+template <int BN, int SMAX, bool FULL, int NACC = 1>
 __device__ __forceinline__ void cluster_reduce_cols(const GemmParams& p, const Work& wk, uint32_t part_local,
                                                     int rank, int q, int lane, int ndst, const float (&b4)[4]) {
-  constexpr int CPC = 16 / SMAX;                 // whole columns per batch of loads
+  constexpr int CPC = 16 / (SMAX * NACC) > 0 ? 16 / (SMAX * NACC) : 1;   // whole columns per batch of loads
   const int S = p.splits;
   const int n4 = wk.n0 + 4 * lane;
   for (int i0 = 0; rank + S * q + 4 * S * i0 < wk.t_valid; i0 += CPC) {
     float4 v[CPC][SMAX];
+    float4 vu[NACC == 2 ? CPC : 1][NACC == 2 ? SMAX : 1];     // up-projection partials (SwiGLU)
 #pragma unroll
     for (int ci = 0; ci < CPC; ++ci) {
       const int c = rank + S * q + 4 * S * (i0 + ci);
@@ -294,6 +295,8 @@ __device__ __forceinline__ void cluster_reduce_cols(const GemmParams& p, const W
       for (int r2 = 0; r2 < SMAX; ++r2)
         if (r2 < S && c < wk.t_valid) {
           v[ci][r2] = ld_dsmem_v4(mapa_shared(part_local + (uint32_t)((c * BM + 4 * lane) * 4), r2));
+          if (NACC == 2)
+            vu[ci][r2] = ld_dsmem_v4(mapa_shared(part_local + (uint32_t)(((BN + c) * BM + 4 * lane) * 4), r2));
         }
     }
 #pragma unroll
@@ -304,6 +307,16 @@ __device__ __forceinline__ void cluster_reduce_cols(const GemmParams& p, const W
 #pragma unroll
         for (int r2 = 0; r2 < SMAX; ++r2)
           if (r2 < S) { a.x += v[ci][r2].x; a.y += v[ci][r2].y; a.z += v[ci][r2].z; a.w += v[ci][r2].w; }
+        if (NACC == 2) {
+          float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int r2 = 0; r2 < SMAX; ++r2)
+            if (r2 < S) { u.x += vu[ci][r2].x; u.y += vu[ci][r2].y; u.z += vu[ci][r2].z; u.w += vu[ci][r2].w; }
+          a.x = a.x / (1.f + __expf(-a.x)) * u.x;
+          a.y = a.y / (1.f + __expf(-a.y)) * u.y;
+          a.z = a.z / (1.f + __expf(-a.z)) * u.z;
+          a.w = a.w / (1.f + __expf(-a.w)) * u.w;
+        }
         for (int d = 0; d < ndst; ++d) {
           const TileDst td = tile_dst<BN, FULL>(p, wk, d);
           __nv_bfloat16* yp = td.base + (size_t)c * td.cs + 4 * lane;
@@ -548,7 +561,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const int t0 = wk.t_row;
       const int t_valid = wk.t_valid;
       const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
-      if (NACC == 2) {
+      if (NACC == 2 && p.splits == 1) {
         // SwiGLU: accumulator 0 holds the gate tile, accumulator 1 the up tile of the same columns
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -669,6 +682,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) part[(c0 + j) * BM + row] = __uint_as_float(r[j]);
+          if (NACC == 2) {       // the up accumulator goes behind the gate accumulator's BN columns
+            tmem_ld_32x32(taddr + BN + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) part[(BN + c0 + j) * BM + row] = __uint_as_float(r[j]);
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -919,9 +938,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const uint32_t part_local = smem_u32(smem);
       // Distributed-shared-memory loads have a long latency (several hundred ns each round trip): the
       // partials of as many whole columns as fit in 16 vector registers are requested together.
-      if (S <= 2) cluster_reduce_cols<BN, 2, FULL>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
-      else if (S <= 4) cluster_reduce_cols<BN, 4, FULL>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
-      else cluster_reduce_cols<BN, 8, FULL>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
+      if (S <= 2) cluster_reduce_cols<BN, 2, FULL, NACC>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
+      else if (S <= 4) cluster_reduce_cols<BN, 4, FULL, NACC>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
+      else cluster_reduce_cols<BN, 8, FULL, NACC>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
       if (push_out) __threadfence_system();
     }
     if (threadIdx.x == 64) dbg_stamp(p, 6);
@@ -1400,13 +1419,33 @@ extern "C" int b200_gemm_bf16_swiglu(const void* X, const void* W, void* Y, int 
   init_params(p, Y, T, I, K, ldy, bn, status);
   p.up_row_off = I;
   p.w_evict_first = (p.t_tiles == 1) ? 1 : 0;
+  {
+    // few output tiles (small I per rank under tensor parallelism): split K over a cluster so that
+    // every SM streams weights; the gate and up partials are reduced over DSMEM before the activation
+    const int tiles = p.n_tiles * p.t_tiles;
+    int splits = 1;
+    if (tiles * 2 <= num_sms && bn <= 64) {
+      splits = num_sms / tiles;
+      const int max_by_k = p.kb_total / 8 > 0 ? p.kb_total / 8 : 1;
+      if (splits > max_by_k) splits = max_by_k;
+      if (splits > 8) splits = 8;
+      if (splits > 1) splits = fit_cluster_splits(splits, tiles, bn, NUM_THREADS);
+    }
+    p.splits = splits;
+    p.kb_per_split = (p.kb_total + splits - 1) / splits;
+    while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= p.kb_total) {
+      --p.splits;
+      p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+    }
+    p.cluster_splitk = p.splits > 1 ? 1 : 0;
+  }
   CUtensorMap tmW, tmX;
   int rc = cached_tmap(&tmW, W, (uint64_t)2 * I, (uint64_t)K, (uint64_t)ldw * 2, BM);
   if (rc) return rc;
   rc = cached_tmap(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn);
   if (rc) return rc;
-  const int total = p.n_tiles * p.t_tiles;
-  const int grid = total < num_sms ? total : num_sms;
+  const int total = p.n_tiles * p.t_tiles * p.splits;
+  const int grid = p.cluster_splitk ? total : (total < num_sms ? total : num_sms);
   switch (bn) {
     case 32: return launch_gemm<32, 2>(tmW, tmX, p, grid, stream);
     case 64: return launch_gemm<64, 2>(tmW, tmX, p, grid, stream);
