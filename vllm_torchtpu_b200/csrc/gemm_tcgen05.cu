@@ -134,8 +134,9 @@ struct Work {
 };
 
 // dense: tiles rastered in groups of GROUP_N weight tiles; grouped: work = (token tile of an expert, n tile)
-template <int BN, bool FULL = true>
+template <int BN, int MODE = 2>
 __device__ __forceinline__ Work get_work(int w, const GemmParams& p, const int* s_prefix) {
+  constexpr bool FULL = MODE == 2;
   Work k;
   if (!FULL || p.group_off == nullptr) {
     int n_tile, t_tile;
@@ -181,10 +182,15 @@ struct TileDst {
   __nv_bfloat16* base;
   int cs;
 };
-template <int BN, bool FULL = true>
+template <int BN, int MODE = 2>
 __device__ __forceinline__ TileDst tile_dst(const GemmParams& p, const Work& wk, int d) {
+  constexpr bool FULL = MODE == 2;
   TileDst t;
-  if (!FULL || p.world == 1 || p.ar_mode == 5) {
+  if (MODE == 1) {
+    t.base = reinterpret_cast<__nv_bfloat16*>(p.peer[d] + p.part_off + (size_t)p.rank * p.part_src_stride) +
+             (size_t)wk.t_row * p.N + wk.n0;
+    t.cs = p.N;
+  } else if (!FULL || p.world == 1 || p.ar_mode == 5) {
     t.base = p.Y + (size_t)wk.t_row * p.ldy + wk.n0;
     t.cs = p.ldy;
   } else if (p.ar_mode >= 2) {
@@ -202,8 +208,9 @@ __device__ __forceinline__ TileDst tile_dst(const GemmParams& p, const Work& wk,
 
 // Tell the consumers of this rank's partial of `tile` that it has landed (t = index of the calling
 // thread inside its group; the group has fenced system-wide and synchronised before the call).
+template <int MODE = 2>
 __device__ __forceinline__ void publish_tile(const GemmParams& p, int tile, int epoch, int t) {
-  if (p.ar_mode >= 2) {
+  if (MODE == 1 || p.ar_mode >= 2) {
     if (t < p.world)
       st_release_sys(reinterpret_cast<int*>(p.peer[t] + p.tile_flag_off) + (size_t)p.rank * p.max_tiles + tile,
                      epoch);
@@ -279,7 +286,7 @@ __device__ __forceinline__ void sum_slabs4(const uint8_t* slab, size_t stride, i
 // Split-K reduction over distributed shared memory, the share of cluster CTA `rank`, warp `q`:
 // columns c = rank + S*q + 4*S*i of the fp32 partials [column][row] that every CTA of the cluster
 // keeps at shared offset part_local are summed over the S CTAs in rank order and stored as bf16.
-template <int BN, int SMAX, bool FULL, int NACC = 1>
+template <int BN, int SMAX, int MODE, int NACC = 1>
 __device__ __forceinline__ void cluster_reduce_cols(const GemmParams& p, const Work& wk, uint32_t part_local,
                                                     int rank, int q, int lane, int ndst, const float (&b4)[4]) {
   constexpr int CPC = 16 / (SMAX * NACC) > 0 ? 16 / (SMAX * NACC) : 1;   // whole columns per batch of loads
@@ -318,7 +325,7 @@ __device__ __forceinline__ void cluster_reduce_cols(const GemmParams& p, const W
           a.w = a.w / (1.f + __expf(-a.w)) * u.w;
         }
         for (int d = 0; d < ndst; ++d) {
-          const TileDst td = tile_dst<BN, FULL>(p, wk, d);
+          const TileDst td = tile_dst<BN, MODE>(p, wk, d);
           __nv_bfloat16* yp = td.base + (size_t)c * td.cs + 4 * lane;
           const bool vec_ok = (n4 + 3 < p.N) && ((td.cs & 3) == 0) &&
                               ((reinterpret_cast<uintptr_t>(td.base) & 7) == 0);
@@ -354,11 +361,13 @@ __device__ __forceinline__ void dbg_stamp(const GemmParams& p, int slot) {
 #endif
 }
 
-// FULL = false is the compact instantiation for the common single-rank dense case (no grouped mode, no
+// MODE 0 is the compact instantiation for the common single-rank dense case (no grouped mode, no
 // cross-rank roles, no global-scratch split-K): the cold paths it leaves out cost instruction-cache
 // misses in the short decode GEMMs even when they are never taken.
-template <int BN, int NACC, bool FULL>
-__global__ void __launch_bounds__(FULL ? NUM_THREADS_FUSED : NUM_THREADS, 1)
+// MODE 1 is the equally compact instantiation of the decode push plane (ar_mode 3): a dense GEMM whose
+// output rows go to every rank's receive slab, flags raised per tile, nothing else.
+template <int BN, int NACC, int MODE>
+__global__ void __launch_bounds__(MODE == 2 ? NUM_THREADS_FUSED : NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                  const GemmParams p) {
   using Cfg = GemmCfg<BN, NACC>;
@@ -376,10 +385,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
   volatile int* red_ok = reinterpret_cast<volatile int*>(tmem_slot + 3);
   int* s_prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES);
-  const bool fused = FULL && p.world > 1;
+  constexpr bool FULL = MODE == 2;
+  constexpr bool PUSH = MODE == 1;
+  const bool fused = PUSH || (FULL && p.world > 1);
   __nv_bfloat16* const dst_base = p.Y;       // SwiGLU and grouped launches (never fused)
-  const bool push_out = fused && p.ar_mode <= 3;       // the epilogue feeds a cross-rank reduction
-  const int ndst = (push_out && p.ar_mode >= 2) ? p.world : 1;
+  const bool push_out = PUSH || (fused && p.ar_mode <= 3);   // the epilogue feeds a cross-rank reduction
+  const int ndst = PUSH ? p.world : ((push_out && p.ar_mode >= 2) ? p.world : 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -444,7 +455,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       bool ok = true;
       int npre = 0;             // weight tiles of the first work item already in flight (dense mode)
       if (dense && (int)blockIdx.x < total_work) {
-        const Work k0 = get_work<BN, FULL>(blockIdx.x, p, s_prefix);
+        const Work k0 = get_work<BN, MODE>(blockIdx.x, p, s_prefix);
         npre = min(STAGES, k0.kb1 - k0.kb0);
         for (int i = 0; i < npre; ++i) {
           uint8_t* a = smem + i * Cfg::STAGE_BYTES;
@@ -461,7 +472,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       uint32_t ag_seen[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};   // blocks known to have arrived, per source
       int issued = 0;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const Work k = get_work<BN, FULL>(w, p, s_prefix);
+        const Work k = get_work<BN, MODE>(w, p, s_prefix);
         if (FULL && p.ar_mode == 5) {
           const int blk = k.t_row / BN, src = blk / p.ag_tps, j = blk - src * p.ag_tps;
           if (!((ag_seen[src] >> j) & 1u)) {
@@ -514,7 +525,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       int iter = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++iter) {
-        const Work wk = get_work<BN, FULL>(w, p, s_prefix);
+        const Work wk = get_work<BN, MODE>(w, p, s_prefix);
         const int kb0 = wk.kb0, kb1 = wk.kb1;
         const int acc = iter & 1;
         const uint32_t acc_ph = (iter >> 1) & 1;
@@ -550,7 +561,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     int iter = 0;
     uint32_t push_count = 0;                      // bulk copies issued so far (selects the staging buffer)
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++iter) {
-      const Work wk = get_work<BN, FULL>(w, p, s_prefix);
+      const Work wk = get_work<BN, MODE>(w, p, s_prefix);
       const int tile = wk.tile, split = wk.split;
       const int acc = iter & 1;
       const uint32_t acc_ph = (iter >> 1) & 1;
@@ -609,9 +620,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
         __threadfence_system();
-      } else if (p.splits == 1 && fused && p.ar_mode < 2) {
+      } else if (FULL && p.splits == 1 && fused && p.ar_mode < 2) {
         // partial tile -> the owner's slab [BN][BM] bf16, 32 columns (8 KB) per bulk copy
-        uint8_t* slab = reinterpret_cast<uint8_t*>(tile_dst<BN, FULL>(p, wk, 0).base);
+        uint8_t* slab = reinterpret_cast<uint8_t*>(tile_dst<BN, MODE>(p, wk, 0).base);
         __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + Cfg::PUSH_OFF);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -639,7 +650,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         if (threadIdx.x == 64) {
           bulk_wait_group<0>();                   // every chunk of this tile has been written
           __threadfence_system();
-          publish_tile(p, tile, epoch, 0);
+          publish_tile<MODE>(p, tile, epoch, 0);
         }
       } else if (p.splits == 1) {
         const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
@@ -651,7 +662,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           tmem_ld_wait();
           if (n < p.N) {
             for (int d = 0; d < ndst; ++d) {
-              const TileDst td = tile_dst<BN, FULL>(p, wk, d);
+              const TileDst td = tile_dst<BN, MODE>(p, wk, d);
               __nv_bfloat16* yp = td.base + (size_t)c0 * td.cs + row;
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -664,10 +675,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
         if (push_out) {
-          // the partial tile has been pushed: make it visible system-wide, then raise its flag(s)
-          __threadfence_system();
+          // the partial tile has been pushed; the flag stores below are release operations at system
+          // scope and the barrier orders every epilogue thread's stores before them
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          publish_tile(p, tile, epoch, (int)threadIdx.x - 64);
+          publish_tile<MODE>(p, tile, epoch, (int)threadIdx.x - 64);
         }
       } else if (p.cluster_splitk) {
         // split-K inside a thread-block cluster: the partial stays on chip.  This CTA has exactly one
@@ -745,7 +756,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
               const int c = c0 + 4 * u;
               if (c >= t_valid) continue;
               for (int d = 0; d < ndst; ++d) {
-                const TileDst td = tile_dst<BN, FULL>(p, wk, d);
+                const TileDst td = tile_dst<BN, MODE>(p, wk, d);
                 __nv_bfloat16* yp = td.base + (size_t)c * td.cs + 4 * lane;
                 const bool vec_ok = (n4 + 3 < p.N) && ((td.cs & 3) == 0) &&
                                     ((reinterpret_cast<uintptr_t>(td.base) & 7) == 0);
@@ -769,7 +780,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           if (push_out) {
             __threadfence_system();
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            publish_tile(p, tile, epoch, (int)threadIdx.x - 64);
+            publish_tile<MODE>(p, tile, epoch, (int)threadIdx.x - 64);
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is rewritten next iteration
@@ -777,7 +788,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
   }
 
-  else if (fused && p.ar_mode == 5) {
+  else if (FULL && fused && p.ar_mode == 5) {
     // ------------------------------------------- gather warps (threads 192..319), all-gather -> GEMM
     // unit = (destination, BN-row block of this rank's shard, K slice); destinations start with this
     // rank itself and go round, so that every link is busy and the local blocks are ready first
@@ -822,7 +833,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
   }
 
-  else if (fused) {      // (absent in ar_mode 3 launches, which have no reducer warps)
+  else if (FULL && fused) {      // (absent in ar_mode 3 launches, which have no reducer warps)
     // ------------------------------------------- reducer warps (threads 192..319)
     // All cross-rank traffic is stores: partials were pushed into this rank's receive slabs, so the
     // sums below read local memory only (written by peers: L1 is bypassed).
@@ -923,7 +934,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     cluster_wait_acquire();
     if (threadIdx.x == 64) dbg_stamp(p, 5);
     if (warp >= 2 && warp < 6 && !*abort_flag && blockIdx.x < total_work) {
-      const Work wk = get_work<BN, FULL>(blockIdx.x, p, s_prefix);
+      const Work wk = get_work<BN, MODE>(blockIdx.x, p, s_prefix);
       if (threadIdx.x == 64) dbg_stamp(p, 9);
       const int q = warp & 3;
       const uint32_t rank = cluster_ctarank();
@@ -938,18 +949,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const uint32_t part_local = smem_u32(smem);
       // Distributed-shared-memory loads have a long latency (several hundred ns each round trip): the
       // partials of as many whole columns as fit in 16 vector registers are requested together.
-      if (S <= 2) cluster_reduce_cols<BN, 2, FULL, NACC>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
-      else if (S <= 4) cluster_reduce_cols<BN, 4, FULL, NACC>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
-      else cluster_reduce_cols<BN, 8, FULL, NACC>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
-      if (push_out) __threadfence_system();
+      if (S <= 2) cluster_reduce_cols<BN, 2, MODE, NACC>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
+      else if (S <= 4) cluster_reduce_cols<BN, 4, MODE, NACC>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
+      else cluster_reduce_cols<BN, 8, MODE, NACC>(p, wk, part_local, (int)rank, q, lane, ndst, b4);
     }
     if (threadIdx.x == 64) dbg_stamp(p, 6);
     __syncwarp();
     cluster_arrive_release();          // nobody leaves while its partial may still be read
     cluster_wait_acquire();
     if (push_out && cluster_ctarank() == 0 && warp == 2 && blockIdx.x < total_work) {
-      const Work wk = get_work<BN, FULL>(blockIdx.x, p, s_prefix);
-      publish_tile(p, wk.tile, epoch, lane);
+      const Work wk = get_work<BN, MODE>(blockIdx.x, p, s_prefix);
+      publish_tile<MODE>(p, wk.tile, epoch, lane);
     }
   }
 
@@ -1104,7 +1114,7 @@ static int cached_tmap(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_
 template <int BN>
 static int max_active_clusters_t(int splits, int threads) {
   using Cfg = GemmCfg<BN, 1>;
-  auto kern = threads > NUM_THREADS ? gemm_bf16_kernel<BN, 1, true> : gemm_bf16_kernel<BN, 1, false>;
+  auto kern = threads > NUM_THREADS ? gemm_bf16_kernel<BN, 1, 2> : gemm_bf16_kernel<BN, 1, 0>;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits * 64);
@@ -1149,30 +1159,35 @@ static int fit_cluster_splits(int want, int tiles, int bn, int threads) {
   return s;
 }
 
-// the compact kernel serves dense single-rank launches without split-K or with cluster split-K
-static bool plain_eligible(const GemmParams& p) {
-  return p.world == 1 && p.group_off == nullptr && p.row_route == nullptr &&
-         (p.splits == 1 || p.cluster_splitk);
+// 0: compact kernel (dense single-rank launches without split-K or with cluster split-K),
+// 1: compact push kernel (ar_mode 3), 2: the full kernel
+static int kernel_mode(const GemmParams& p) {
+  const bool simple = p.group_off == nullptr && p.row_route == nullptr && (p.splits == 1 || p.cluster_splitk);
+  if (simple && p.world == 1) return 0;
+  if (simple && p.world > 1 && p.ar_mode == 3) return 1;
+  return 2;
 }
 
-template <int BN, int NACC, bool FULL>
+template <int BN, int NACC, int MODE>
 static int launch_gemm_v(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int grid,
                          cudaStream_t stream);
 
 template <int BN, int NACC = 1>
 static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int grid,
                        cudaStream_t stream) {
-  if (plain_eligible(p)) return launch_gemm_v<BN, NACC, false>(tmW, tmX, p, grid, stream);
-  return launch_gemm_v<BN, NACC, true>(tmW, tmX, p, grid, stream);
+  const int mode = kernel_mode(p);
+  if (mode == 0) return launch_gemm_v<BN, NACC, 0>(tmW, tmX, p, grid, stream);
+  if (mode == 1 && NACC == 1) return launch_gemm_v<BN, 1, 1>(tmW, tmX, p, grid, stream);
+  return launch_gemm_v<BN, NACC, 2>(tmW, tmX, p, grid, stream);
 }
 
-template <int BN, int NACC, bool FULL>
+template <int BN, int NACC, int MODE>
 static int launch_gemm_v(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int grid,
                          cudaStream_t stream) {
   using Cfg = GemmCfg<BN, NACC>;
   static bool attr_set = false;
   if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN, NACC, FULL>,
+    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN, NACC, MODE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     attr_set = true;
   }
@@ -1199,7 +1214,7 @@ static int launch_gemm_v(const CUtensorMap& tmW, const CUtensorMap& tmX, const G
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, NACC, FULL>, tmW, tmX, p));
+  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, NACC, MODE>, tmW, tmX, p));
   return 0;
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;

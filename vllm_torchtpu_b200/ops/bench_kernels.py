@@ -138,7 +138,8 @@ def bench_attn_prefill(reqs, qlen, Hq=32, Hkv=8, D=128, iters=10) -> dict:
             "frac_of_bf16_peak": round(flops / ms / 1e9 / pk["bf16_tflops"], 3), "peaks": tag}
 
 
-def bench_decode_layer(reqs, ctx, layers=8, parts="all", iters=10, H=4096, I=14336, Hq=32, Hkv=8, D=128) -> dict:
+def bench_decode_layer(reqs, ctx, layers=8, parts="all", iters=10, H=4096, I=14336, Hq=32, Hkv=8, D=128,
+                       tp=1) -> dict:
     """One CUDA graph of ``layers`` Llama-8B-shaped decoder layers (distinct weights and KV, so every
     layer streams from HBM) on a batch of ``reqs`` decode tokens at context ``ctx``; reports device
     time per layer.  ``parts`` keeps a subset: gemm | attn | elem | all."""
@@ -146,6 +147,8 @@ def bench_decode_layer(reqs, ctx, layers=8, parts="all", iters=10, H=4096, I=143
     from . import cuda
     from . import reference as ref
     pk, tag = peaks()
+    # the per-rank shapes of a tensor-parallel layout, run on one GPU without the collectives
+    I, Hq, Hkv = I // tp, Hq // tp, max(1, Hkv // tp)
     bs = 16
     nblk_per = -(-(ctx + 1) // bs)
     nb = reqs * nblk_per + 1
@@ -193,7 +196,7 @@ def bench_decode_layer(reqs, ctx, layers=8, parts="all", iters=10, H=4096, I=143
     byts = (w_bytes if g else 0) + (kv_bytes if a else 0)
     us = ms * 1e3 / layers
     roof_us = byts / (pk["hbm_gbs"] * 1e9) * 1e6
-    return {"op": "decode_layer", "parts": parts, "reqs": reqs, "ctx": ctx, "layers": layers,
+    return {"op": "decode_layer", "parts": parts, "reqs": reqs, "ctx": ctx, "layers": layers, "tp_shapes": tp,
             "us_per_layer": round(us, 2), "hbm_roofline_us": round(roof_us, 2),
             "frac_of_hbm": round(roof_us / us, 3) if us > 0 else None, "peaks": tag,
             "status": cuda.check_status()}
@@ -254,6 +257,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--impl", default="tcgen05", choices=["tcgen05", "cublas"])
     ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--tp", type=int, default=1, help="decode-layer: use the per-rank shapes of this TP degree")
     ap.add_argument("--parts", default="all,gemm,attn,elem")
     a = ap.parse_args()
     if a.what == "gemm":
@@ -270,7 +274,7 @@ def main():
             print(json.dumps(bench_gemm_sustained(a.T, a.N, a.K, 3.0, impl)))
     if a.what == "decode-layer":
         for parts in a.parts.split(","):
-            print(json.dumps(bench_decode_layer(a.reqs, a.ctx, a.layers, parts, a.iters)))
+            print(json.dumps(bench_decode_layer(a.reqs, a.ctx, a.layers, parts, a.iters, tp=a.tp)))
     if a.what in ("attn-decode", "all"):
         for reqs, ctx in ((a.reqs, a.ctx),) if a.what == "attn-decode" else ((64, 1100), (256, 2048), (8, 8000)):
             print(json.dumps(bench_attn_decode(reqs, ctx, iters=a.iters)))
