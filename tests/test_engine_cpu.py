@@ -64,3 +64,27 @@ def test_tiny_moe_matches_dense_reference():
     for p, o in zip(_prompts()[:3], outs):
         want, _ = dense_greedy_generate(model, p, 8)
         assert o.outputs[0].token_ids == want
+
+
+def test_embedding_pooling_matches_dense_hidden_states():
+    """LLM.embed: last-token and mean pooling of the final-norm hidden states, also when the prompt is
+    prefilled in several chunks."""
+    import numpy as np
+    import torch
+
+    from vllm_torchtpu_b200.engine.llm import LLM
+    from vllm_torchtpu_b200.models.reference_forward import dense_llama_hidden
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, max_num_batched_tokens=32, block_size=16,
+              num_gpu_blocks_override=32)
+    rng = np.random.RandomState(3)
+    vocab = llm.engine.cfg.model.vocab_size
+    prompts = [rng.randint(0, vocab, size=n).tolist() for n in (7, 50)]        # 50 > 32: two chunks
+    model = llm.engine.runner.model
+    for mode in ("last", "mean"):
+        got = llm.embed(prompts, pooling=mode, normalize=False)
+        for p, g in zip(prompts, got):
+            h = dense_llama_hidden(model, p)                                    # [len, H] after the final norm
+            want = h[-1] if mode == "last" else h.mean(0)
+            torch.testing.assert_close(torch.tensor(g), want.float(), rtol=2e-3, atol=2e-3)
+    unit = llm.embed(prompts[:1])[0]
+    assert abs(sum(a * a for a in unit) - 1.0) < 1e-4

@@ -85,6 +85,22 @@ class LLM:
             return list(prompt["prompt_token_ids"])
         return list(prompt)
 
+    def embed(self, prompts: Sequence, pooling: str = "last", normalize: bool = True) -> list:
+        """Pooled final hidden state per prompt (``last`` token or ``mean`` over the prompt), optionally
+        L2-normalised: the embedding-model path (reference: src/vllm_torchtpu/runner/tpu_pooling.py)."""
+        if pooling not in ("last", "mean"):
+            raise ValueError("pooling must be 'last' or 'mean'")
+        sp = SamplingParams(temperature=0.0, max_tokens=1, pooling=pooling)
+        outs = self.generate(prompts, sp)
+        vecs = []
+        for o in outs:
+            v = o.pooled
+            if normalize and v is not None:
+                n = sum(a * a for a in v) ** 0.5 or 1.0
+                v = [a / n for a in v]
+            vecs.append(v)
+        return vecs
+
     def generate(self, prompts: Sequence, sampling_params: Union[SamplingParams, Sequence, None] = None,
                  ) -> list:
         if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):

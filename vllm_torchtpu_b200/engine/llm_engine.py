@@ -141,7 +141,7 @@ class LLMEngine:
     # ---- stepping ---------------------------------------------------------------
     def _launch(self):
         out = self.scheduler.schedule()
-        min_tokens = 0
+        pad_to = 0
         if self._dp_lockstep:
             from ..parallel.communicator import DeviceCommunicator
             st = get_state()
@@ -154,12 +154,12 @@ class LLMEngine:
             if not out.scheduled:
                 self.runner.execute_dummy_batch(max(1, agreed[0]))
                 return out, self.runner.execute_model(out)
-            min_tokens = agreed[0]
+            pad_to = agreed[0]
             if agreed[1]:
-                min_tokens = -agreed[0]       # some replica runs a prefill: everybody runs this step eagerly
+                pad_to = -agreed[0]           # some replica runs a prefill: everybody runs this step eagerly
         if self.connector is not None:
             self.connector.worker.start_load_kv(out.kv_connector_metadata)
-        res = self.runner.execute_model(out, min_tokens=min_tokens)
+        res = self.runner.execute_model(out, pad_tokens_to=pad_to)
         if self.connector is not None:
             self.connector.worker.save_kv(out.kv_connector_metadata)
         return out, res
@@ -173,6 +173,9 @@ class LLMEngine:
         if self.spec is not None and sampled:
             spec_next = self.spec.propose(out, sampled)
         finished = self.scheduler.update_from_output(out, sampled, spec_next)
+        for r in finished:
+            if r.sampling_params.pooling:
+                r.pooled = self.runner.take_pooled(r.request_id)
         if self.runner.structured is not None:
             for r in finished:
                 self.runner.structured.remove_request(r.request_id)

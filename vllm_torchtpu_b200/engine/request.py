@@ -43,6 +43,7 @@ class Request:
     first_token_time: Optional[float] = None
     finish_time: Optional[float] = None
     error: Optional[str] = None
+    pooled: Optional[list] = None          # pooled final hidden state (pooling requests)
     logprobs: list = field(default_factory=list)
     num_preemptions: int = 0
     # tokens sampled on the device that the host has not seen yet (async scheduling)

@@ -15,7 +15,12 @@ def _rms(x, w, eps):
 
 
 @torch.no_grad()
-def dense_llama_logits(model, token_ids: list) -> torch.Tensor:
+def dense_llama_hidden(model, token_ids: list) -> torch.Tensor:
+    """Final-norm hidden states [S, H] of one sequence (fp32 math)."""
+    return dense_llama_logits(model, token_ids, return_hidden=True)
+
+
+def dense_llama_logits(model, token_ids: list, return_hidden: bool = False) -> torch.Tensor:
     """Logits [S, V] of one sequence for a single-rank LlamaForCausalLM (fp32 math)."""
     cfg = model.cfg
     ids = torch.tensor(token_ids, dtype=torch.long, device=model.embed.device)
@@ -51,6 +56,8 @@ def dense_llama_logits(model, token_ids: list) -> torch.Tensor:
         else:
             x = x + layer.mlp.forward(h.to(cfg.dtype)).float()
     x = _rms(x, model.norm, cfg.rms_norm_eps)
+    if return_hidden:
+        return x
     return x @ model.lm_head.float().t()
 
 

@@ -25,6 +25,7 @@ class RequestOutput:
     latency_s: Optional[float] = None
     kv_transfer_params: Optional[dict] = None
     error: Optional[str] = None
+    pooled: Optional[list] = None          # embedding of the prompt for pooling requests
 
     @staticmethod
     def from_request(req, detokenize=None) -> "RequestOutput":
@@ -35,4 +36,5 @@ class RequestOutput:
             req.request_id, req.prompt_token_ids,
             [CompletionOutput(0, list(req.output_token_ids), text, req.status.value,
                               req.logprobs or None)],
-            req.status.finished, req.num_cached_tokens, ttft, lat, req.kv_transfer_params, req.error)
+            req.status.finished, req.num_cached_tokens, ttft, lat, req.kv_transfer_params, req.error,
+            getattr(req, "pooled", None))

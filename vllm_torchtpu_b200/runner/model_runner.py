@@ -96,6 +96,8 @@ class ModelRunner:
         self.structured = None           # StructuredDecodingManager when a request asks for it
         self._step_bitmask = None
         self.timing_events = None        # (start event, end event, decode-only?, tokens) per step when enabled
+        self._pool_plan = None           # pooling requests of the current step: (id, row lo, row hi, mode, last chunk)
+        self._pool_acc: dict = {}        # request id -> [sum or last row, count]
         if envs.B200_STAGE_TIMING and self.is_cuda:
             from ..tracing.stage_timing import RunnerStageTiming
             self._stage_timers = RunnerStageTiming()
@@ -188,7 +190,7 @@ class ModelRunner:
             else:
                 self.batch.append_blocks(self.batch.slot_of[s.request.request_id], s.new_block_ids)
 
-    def _prepare_inputs(self, out, min_tokens: int = 0):
+    def _prepare_inputs(self, out, pad_tokens_to: int = 0):
         scheds = out.scheduled
         n = len(scheds)
         b = self.batch
@@ -207,13 +209,13 @@ class ModelRunner:
             T_pad = R_pad
         else:
             R_pad, T_pad = n, T
-        if min_tokens > T_pad:
+        if pad_tokens_to > T_pad:
             # lockstep with other replicas: more rows than this rank needs (padded rows: no request)
-            if decode_only and T_pad == R_pad and min_tokens in self.cfg.request_buckets and self.is_cuda \
+            if decode_only and T_pad == R_pad and pad_tokens_to in self.cfg.request_buckets and self.is_cuda \
                     and not self.cfg.enforce_eager:
-                R_pad = T_pad = min_tokens              # still a captured decode bucket
+                R_pad = T_pad = pad_tokens_to           # still a captured decode bucket
             else:
-                T_pad = min_tokens
+                T_pad = pad_tokens_to
                 if decode_only:
                     bufs = self.bufs_prefill            # the decode buffers hold one row per request
         qsl = np.zeros(n + 1, dtype=np.int64)
@@ -296,6 +298,8 @@ class ModelRunner:
             return self._forward_and_sample_pp(bufs, meta, T, R, n_req_pad, all_greedy, verify)
         hidden0 = self._embed(ids, dv("token_src", T))
         hidden, residual = self.model.forward(ids, meta, self.kv_caches, hidden=hidden0)
+        if self._pool_plan:
+            self._pool(hidden, residual)
         rows = self._select_rows(hidden, residual, meta.logits_indices)
         h = self.model.finalize(*rows)
         st = get_state()
@@ -385,6 +389,27 @@ class ModelRunner:
             self._store_last_tokens(tokens, dv("batch_slots", n_req_pad))
         return tokens, logits
 
+    def _pool(self, hidden, residual) -> None:
+        """Embedding requests: the final-norm hidden states of the prompt rows of this step are summed
+        (mean pooling, accumulated over prefill chunks) or the last row is kept (static shapes: the
+        whole step is normalised once; reference: src/vllm_torchtpu/runner/tpu_pooling.py)."""
+        hn = self.model.finalize(hidden, residual).float()
+        for rid, lo, hi, mode, last_chunk in self._pool_plan:
+            acc = self._pool_acc.setdefault(rid, [None, 0])
+            if mode == "mean":
+                part = hn[lo:hi].sum(0)
+                acc[0] = part if acc[0] is None else acc[0] + part
+                acc[1] += hi - lo
+            elif last_chunk:
+                acc[0], acc[1] = hn[hi - 1].clone(), 1
+        self._pool_plan = None
+
+    def take_pooled(self, rid: str):
+        acc = self._pool_acc.pop(rid, None)
+        if acc is None or acc[0] is None:
+            return None
+        return (acc[0] / max(1, acc[1])).cpu().tolist()
+
     def _embed(self, ids, token_src):
         if self.model.embed is None:
             return None
@@ -443,15 +468,15 @@ class ModelRunner:
                  seq_lens_np=np.full(1, per, dtype=np.int64), qsl_np=np.array([0, per], dtype=np.int64))
         self._forward_and_sample(bufs, self._make_meta(p), T, 1, True)
 
-    def execute_model(self, out, min_tokens: int = 0) -> StepResult:
-        """``min_tokens`` > 0 pads the step to at least that many token rows (data-parallel lockstep);
+    def execute_model(self, out, pad_tokens_to: int = 0) -> StepResult:
+        """``pad_tokens_to`` > 0 pads the step to at least that many token rows (data-parallel lockstep);
         a negative value additionally forces the eager path for this step."""
         if not out.scheduled:
             self._update_batch(out)
             return StepResult([], [], None, None, 0)
         self._update_batch(out)
-        p = self._prepare_inputs(out, min_tokens=abs(min_tokens))
-        if min_tokens < 0:
+        p = self._prepare_inputs(out, pad_tokens_to=abs(pad_tokens_to))
+        if pad_tokens_to < 0:
             p["decode_only"] = False
         bufs, n, R, T = p["bufs"], p["n"], p["R_pad"], p["T_pad"]
         self.stats["h2d_bytes"] += bufs.upload(R)
@@ -470,6 +495,15 @@ class ModelRunner:
                 lora_idx = torch.cat([lora_idx, pad])
             from ..lora import wiring
             wiring.set_step(lora_idx)
+        self._pool_plan = None
+        if any(s.request.sampling_params.pooling for s in p["scheds"]):
+            plan, qsl_np = [], p["qsl_np"]
+            for i, s in enumerate(p["scheds"]):
+                mode = s.request.sampling_params.pooling
+                if mode and s.start < s.request.num_prompt_tokens:
+                    last = s.start + s.num_new_tokens >= s.request.num_prompt_tokens
+                    plan.append((s.request.request_id, int(qsl_np[i]), int(qsl_np[i + 1]), mode, last))
+            self._pool_plan = plan or None
         self._step_bitmask = None
         if self.structured is not None and self.structured.grammars:
             bm, rows = self.structured.build_bitmask([s.request.request_id for s in p["scheds"]])
