@@ -59,3 +59,29 @@ def test_random_sampling_runs_and_is_seeded():
     a = [o.outputs[0].token_ids for o in _llm().generate(_prompts()[:2], sp)]
     b = [o.outputs[0].token_ids for o in _llm().generate(_prompts()[:2], sp)]
     assert a == b
+
+
+def test_lora_request_and_embedding_on_gpu():
+    """Adapter requests run through the bgmv kernels next to base requests (which keep their tokens),
+    and LLM.embed returns unit vectors."""
+    import numpy as np
+    llm = _llm(enforce_eager=True)
+    prompts = _prompts()[:2]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    base = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    g = torch.Generator().manual_seed(0)
+    weights = {}
+    for lin in llm.engine.runner.model.named_linears():
+        prefix, leaf = lin.name.rsplit(".", 1)
+        if leaf == "down_proj":
+            weights[lin.name] = (torch.randn(8, lin.in_features, generator=g) * 0.5,
+                                 torch.randn(lin.out_features, 8, generator=g) * 0.5)
+    assert llm.engine.add_lora("ad", 8, 64.0, weights)
+    sp_l = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, lora_name="ad")
+    outs = llm.generate(prompts, [sp_l, sp])
+    assert outs[1].outputs[0].token_ids == base[1]
+    assert outs[0].outputs[0].token_ids != base[0]
+    v = llm.embed(prompts[:1])[0]
+    assert abs(float(np.square(v).sum()) - 1.0) < 1e-2
+    from vllm_torchtpu_b200.ops import cuda
+    assert cuda.check_status() == 0
