@@ -12,7 +12,7 @@
 //                    their fp32 register accumulators (acc = acc * alpha + O_chunk), so TMEM is
 //                    never rescaled in place.
 // Warp roles: warp 0 TMA producer (Q tile once, K and V rings, one 16-token page per copy), warp 1
-// MMA issuer, warps 2-5 softmax + output.  S(j+1) is issued before P V(j), so the tensor core works
+// MMA issuer, warps 2-9 softmax + output (two threads per row, one per half of the key columns).  S(j+1) is issued before P V(j), so the tensor core works
 // on the next scores while the softmax of the current chunk runs.  512 TMEM columns, 192 KB of
 // shared memory.  Every mbarrier wait is bounded (status word + abort flag + TMEM freed on exit).
 //
@@ -38,8 +38,9 @@ constexpr int SMEM_K = SMEM_Q + TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;
 constexpr int SMEM_P = SMEM_V + KV_STAGES * TILE_BYTES;
 constexpr int SMEM_BAR = SMEM_P + TILE_BYTES;
-constexpr int SMEM_TOTAL = SMEM_BAR + 256 + 1024;     // + alignment slack
-constexpr int NUM_THREADS = 192;
+constexpr int SMEM_XCH = SMEM_BAR + 256;                // row-max and row-sum exchange between the two column halves
+constexpr int SMEM_TOTAL = SMEM_XCH + 3 * 2 * 128 * 4 + 1024;     // + alignment slack
+constexpr int NUM_THREADS = 64 + 256;                   // TMA warp, MMA warp, 8 softmax warps
 
 struct Params {
   __nv_bfloat16* out;
@@ -92,7 +93,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint64_t* o_empty = bars + 15;           // [2]
   uint64_t* p_full = bars + 17;            // 1
   uint64_t* p_empty = bars + 18;           // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  uint64_t* mx_bar = bars + 19;            // [2] row-max exchange, 256 arrivals
+  uint64_t* l_bar = bars + 21;             // 1   row-sum exchange, 256 arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -101,10 +104,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
-      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 4);
+      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 8);
+      mbar_init(&o_full[i], 1); mbar_init(&o_empty[i], 8);
+      mbar_init(&mx_bar[i], 256);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
+    mbar_init(l_bar, 256);
     mbar_init(p_empty, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -246,36 +251,44 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
     }
   } else {
-    // ------------------------------------------------------- softmax + output (one thread per row)
+    // ------------------------------------------------ softmax + output: two threads per row
+    // Warps 2-5 own key columns [0, 64) of every chunk and output dims [0, 64), warps 6-9 the other
+    // halves (a warp may only touch the TMEM lanes of its quarter, so the pair of a row sits in two
+    // warps).  The pair agrees on the chunk's row maximum through shared memory and an mbarrier
+    // (bounded wait, like every other wait here); row sums are combined once at the end.
     const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;                     // 0: columns 0-63, 1: columns 64-127
     const int row = qd * 32 + lane;                       // TMEM lane = tile row
     const int pos_local = row / p.G, head = h * p.G + row % p.G;
     const bool row_ok = active && (q0 + pos_local) < q_len;
     const int lim = ctx + q0 + pos_local;                 // last visible key of this row
-    float acc[D];
+    constexpr int HC = BKV / 2, HD = D / 2;
+    float acc[HD];
 #pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.f;
+    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
     const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
-    uint8_t* p_row = smem + SMEM_P + row * 128;
+    uint8_t* p_row = smem + SMEM_P + half * HALF_BYTES + row * 128;      // this thread's 64 keys of P
+    float* mx_sh = reinterpret_cast<float*>(smem + SMEM_XCH);           // [2 parity][2 half][128]
+    float* l_sh = mx_sh + 2 * 2 * 128;                                  // [2 half][128]
     bool ok = true;
     for (int j = 0; j < nchunks && ok; ++j) {
       const int st = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      const int tok0 = kv_begin + j * BKV;
+      const int tok0 = kv_begin + j * BKV + half * HC;
       if (!mbar_wait(&s_full[st], ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t s_addr = tmem_base + st * BKV + lane_addr;
-      // columns [c_lo, c_hi) of this chunk are visible to the row (causal limit, end of the
+      const uint32_t s_addr = tmem_base + st * BKV + half * HC + lane_addr;
+      // columns [c_lo, c_hi) of this thread's 64 are visible to the row (causal limit, end of the
       // sequence, sliding window); most chunks are fully visible
-      const int c_hi = min(BKV, min(lim, kv_end - 1) - tok0 + 1);
+      const int c_hi = min(HC, min(lim, kv_end - 1) - tok0 + 1);
       const int c_lo = p.window > 0 ? max(0, lim - p.window + 1 - tok0) : 0;
-      const bool full = c_lo <= 0 && c_hi >= BKV;
+      const bool full = c_lo <= 0 && c_hi >= HC;
       const bool capped = p.softcap > 0.f;
       // pass 1: row maximum (raw scores; the scale is positive, the soft-cap monotonic)
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
+      for (int c0 = 0; c0 < HC; c0 += 32) {
         uint32_t rv[32];
         tmem_ld_32x32(s_addr + c0, rv);
         tmem_ld_wait();
@@ -288,6 +301,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             if (c0 + i >= c_lo && c0 + i < c_hi) mx = fmaxf(mx, __uint_as_float(rv[i]));
         }
       }
+      mx_sh[(st * 2 + half) * 128 + row] = mx;
+      mbar_arrive(&mx_bar[st]);
+      if (!mbar_wait(&mx_bar[st], ph, abort_flag, p.status, ST_TIMEOUT_FLAG)) { ok = false; break; }
+      mx = fmaxf(mx, mx_sh[(st * 2 + (half ^ 1)) * 128 + row]);
       if (mx != -INFINITY) {
         mx *= p.scale_log2;
         if (capped) mx = p.softcap * tanhf(mx / p.softcap);
@@ -301,7 +318,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       // pass 2: probabilities, row sum, P (bf16) into shared memory, K-major swizzled
       float ps = 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BKV; c0 += 32) {
+      for (int c0 = 0; c0 < HC; c0 += 32) {
         uint32_t rv[32];
         tmem_ld_32x32(s_addr + c0, rv);
         tmem_ld_wait();
@@ -326,12 +343,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           __nv_bfloat162 b2 = __floats2bfloat162_rn(e[i], e[i + 1]);
           pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
         }
-        // 32 keys = 4 chunks of 16 bytes; key k of the chunk lives in half k / 64
-        uint8_t* half = p_row + (c0 >> 6) * HALF_BYTES;
+        // 32 keys = 4 chunks of 16 bytes inside this thread's 128-byte row of the half
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
-          const int chunk = ((c0 & 63) >> 3) + cc;
-          *reinterpret_cast<uint4*>(half + ((chunk ^ (row & 7)) << 4)) =
+          const int chunk = (c0 >> 3) + cc;
+          *reinterpret_cast<uint4*>(p_row + ((chunk ^ (row & 7)) << 4)) =
               make_uint4(pk[4 * cc], pk[4 * cc + 1], pk[4 * cc + 2], pk[4 * cc + 3]);
         }
       }
@@ -349,9 +365,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const int so = (j - 1) & 1;
         if (!mbar_wait(&o_full[so], ((j - 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t o_addr = tmem_base + 2 * BKV + so * D + lane_addr;
+        const uint32_t o_addr = tmem_base + 2 * BKV + so * D + half * HD + lane_addr;
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t rv[32];
           tmem_ld_32x32(o_addr + c0, rv);
           tmem_ld_wait();
@@ -368,9 +384,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const int so = (nchunks - 1) & 1;
       if (mbar_wait(&o_full[so], ((nchunks - 1) >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) {
         tc_fence_after();
-        const uint32_t o_addr = tmem_base + 2 * BKV + so * D + lane_addr;
+        const uint32_t o_addr = tmem_base + 2 * BKV + so * D + half * HD + lane_addr;
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t rv[32];
           tmem_ld_32x32(o_addr + c0, rv);
           tmem_ld_wait();
@@ -382,6 +398,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         ok = false;
       }
     }
+    // row sum of the pair (each thread summed its 64 columns of every chunk)
+    if (nchunks > 0) {
+      l_sh[half * 128 + row] = l;
+      mbar_arrive(l_bar);
+      if (ok && !mbar_wait(l_bar, 0, abort_flag, p.status, ST_TIMEOUT_FLAG)) ok = false;
+      if (ok) l += l_sh[(half ^ 1) * 128 + row];
+    }
     if (ok && row_ok) {
       float sc = 1.f;
       if (p.sinks != nullptr) {
@@ -392,16 +415,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         m = n;
       }
       const float inv = l > 0.f ? sc / l : 0.f;
-      __nv_bfloat16* dst = p.out + ((size_t)(qs + q0 + pos_local) * p.Hq + head) * D;
+      __nv_bfloat16* dst = p.out + ((size_t)(qs + q0 + pos_local) * p.Hq + head) * D + half * HD;
 #pragma unroll
-      for (int i = 0; i < D; i += 8) {
+      for (int i = 0; i < HD; i += 8) {
         uint4 o;
         __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
         for (int u = 0; u < 4; ++u) oh[u] = __floats2bfloat162_rn(acc[i + 2 * u] * inv, acc[i + 2 * u + 1] * inv);
         *reinterpret_cast<uint4*>(dst + i) = o;
       }
-      if (p.lse != nullptr)
+      if (p.lse != nullptr && half == 0)
         p.lse[(size_t)(qs + q0 + pos_local) * p.Hq + head] =
             l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
