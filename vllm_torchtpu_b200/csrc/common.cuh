@@ -30,8 +30,8 @@ enum : int {
   ST_TIMEOUT_DRAIN = 7,
 };
 
-#ifndef B200_WAIT_LIMIT
-#define B200_WAIT_LIMIT (1u << 24)
+#ifndef B200_WAIT_LIMIT_NS
+#define B200_WAIT_LIMIT_NS 1000000000ull     // one second
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -78,13 +78,44 @@ __device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity) {
   return ok;
 }
 
-// Bounded wait.  Returns true when the phase completed, false on timeout or when
-// another role of the CTA already aborted.
+// try_wait with a suspend-time hint: the thread may be parked by the hardware for up to `ns`
+// nanoseconds instead of burning issue slots (and power) in a polling loop.
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns true when the phase completed, false on timeout or when another role of
+// the CTA already aborted.  A few immediate polls cover the common case of a barrier that is
+// (almost) ready; after that the thread parks in try_wait and the bound is wall time
+// (B200_WAIT_LIMIT_NS), checked every few wake-ups together with the CTA's abort flag.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-  for (uint32_t it = 0; it < B200_WAIT_LIMIT; ++it) {
+#pragma unroll 1
+  for (int it = 0; it < 32; ++it)
     if (mbar_test(bar, parity)) return true;
-    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  const unsigned long long t0 = global_timer_ns();
+#pragma unroll 1
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity, 2000u)) return true;
+    if ((it & 7u) == 7u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > B200_WAIT_LIMIT_NS) break;
+    }
   }
   *abort_flag = 1;
   if (status) atomicCAS(status, ST_OK, code);
