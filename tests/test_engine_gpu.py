@@ -85,3 +85,28 @@ def test_lora_request_and_embedding_on_gpu():
     assert abs(float(np.square(v).sum()) - 1.0) < 1e-2
     from vllm_torchtpu_b200.ops import cuda
     assert cuda.check_status() == 0
+
+
+def test_fp8_kv_cache_engine():
+    """An e4m3 KV cache (written by the rope kernel, expanded inside the attention kernels) keeps the
+    prefill logits close to the dense forward and decodes through CUDA graphs."""
+    from vllm_torchtpu_b200.models.reference_forward import dense_llama_logits
+    llm = _llm(kv_cache_dtype="fp8")
+    eng = llm.engine
+    r = eng.runner
+    assert r.kv_caches[0].dtype == torch.float8_e4m3fn
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    outs = llm.generate(_prompts(), sp)
+    assert all(len(o.outputs[0].token_ids) == 12 for o in outs)
+    p = _prompts()[3]
+    eng.add_request(p, SamplingParams(max_tokens=1))
+    out = eng.scheduler.schedule()
+    r._update_batch(out)
+    prep = r._prepare_inputs(out)
+    prep["bufs"].upload(prep["R_pad"])
+    _, logits = r._forward_and_sample(prep["bufs"], r._make_meta(prep), prep["T_pad"], prep["R_pad"], True)
+    want = dense_llama_logits(r.model, p)[-1]
+    err = (logits[0].float() - want).abs().max().item()
+    assert err < 0.12 * want.abs().max().item() + 0.05, err
+    from vllm_torchtpu_b200.ops import cuda
+    assert cuda.check_status() == 0

@@ -75,13 +75,20 @@ def test_rope_and_cache(D, interleaved, qk_norm):
     _close(c1, c2, 2e-2, 2e-2)
 
 
-def _attn_case(q_lens, ctx_lens, Hq, Hkv, D, bs=16, window=None, softcap=None, sinks=False, num_decode=0):
+def _attn_case(q_lens, ctx_lens, Hq, Hkv, D, bs=16, window=None, softcap=None, sinks=False, num_decode=0,
+               kv_fp8=False):
     g = torch.Generator(device=DEV).manual_seed(2)
     R = len(q_lens)
     seq = [q + c for q, c in zip(q_lens, ctx_lens)]
     maxb = max(-(-s // bs) for s in seq) + 1
     nb = sum(-(-s // bs) for s in seq) + 2
     cache = (torch.randn(nb, 2, Hkv, bs, D, device=DEV, generator=g) * 0.5).bfloat16()
+    k_scale, v_scale = 1.0, 1.0
+    if kv_fp8:
+        # e4m3 cache with per-tensor scales: the oracle dequantises the same bytes in fp32
+        k_scale, v_scale = 0.02, 0.03
+        cache = torch.stack([cache[:, 0].float() / k_scale, cache[:, 1].float() / v_scale],
+                            1).to(torch.float8_e4m3fn)
     perm = (torch.randperm(nb - 1, device=DEV) + 1).to(torch.int32)
     bt = torch.zeros(R, maxb, dtype=torch.int32, device=DEV)
     off = 0
@@ -101,9 +108,10 @@ def _attn_case(q_lens, ctx_lens, Hq, Hkv, D, bs=16, window=None, softcap=None, s
     sk = torch.randn(Hq, device=DEV) if sinks else None
     scale = D ** -0.5
     got, got_lse = cu().paged_attention(q, cache, meta, scale, sliding_window=window, softcap=softcap,
-                                        sinks=sk, return_lse=True)
+                                        sinks=sk, k_scale=k_scale, v_scale=v_scale, return_lse=True)
     want, want_lse = ref.paged_attention(q, cache, bt, sl, qsl, scale, num_reqs=R, sliding_window=window,
-                                         softcap=softcap, sinks=sk, return_lse=True)
+                                         softcap=softcap, sinks=sk, k_scale=k_scale, v_scale=v_scale,
+                                         return_lse=True)
     _close(got, want, 2e-2, 2e-2)
     fin = torch.isfinite(want_lse)
     _close(got_lse[fin], want_lse[fin], 1e-2, 1e-2)
@@ -130,6 +138,15 @@ def test_attention_spec_verify_rows():
 @pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (4, 2, 64)])
 def test_attention_prefill_and_mixed(Hq, Hkv, D):
     _attn_case([1, 1, 200, 64, 65, 1, 333], [40, 900, 0, 128, 37, 0, 1000], Hq, Hkv, D, num_decode=2)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (4, 2, 64)])
+def test_attention_fp8_kv_cache(Hq, Hkv, D):
+    ctx = [0, 15, 16, 100, 1023, 2500, 7]
+    _attn_case([1] * len(ctx), ctx, Hq, Hkv, D, num_decode=len(ctx), kv_fp8=True)
+    _attn_case([1, 1, 200, 64, 65, 1, 333], [40, 900, 0, 128, 37, 0, 1000], Hq, Hkv, D, num_decode=2,
+               kv_fp8=True)
+    _attn_case([1, 130, 17], [500, 300, 0], Hq, Hkv, D, window=128, sinks=True, num_decode=1, kv_fp8=True)
 
 
 def test_attention_window_softcap_sinks():

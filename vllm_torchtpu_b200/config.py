@@ -84,7 +84,7 @@ class ModelConfig:
     # quantisation
     quantization: Optional[str] = None   # None | fp8 | fp8_block | int8 | mxfp4 | nvfp4 | online_fp8
     weight_block_size: tuple = (128, 128)
-    kv_cache_dtype: str = "auto"         # auto | bfloat16 | fp8 | fp8_e4m3 | fp8_e5m2
+    kv_cache_dtype: str = "auto"         # auto | bfloat16 | fp8 | fp8_e4m3
     seed: int = 0
     init_std: float = 0.02
 

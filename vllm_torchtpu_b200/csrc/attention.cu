@@ -75,6 +75,7 @@ struct AttnParams {
   int max_blocks, block_size, Hq, Hkv, req_begin, req_end, num_splits, window;
   long long num_blocks;
   float scale_log2, softcap;
+  float v_scale;                 // fp8 cache: dequantisation factor of V (K's is folded into scale_log2)
 };
 
 // Copy `rows` tokens x D of one K or V page region into swizzled shared memory.
@@ -86,6 +87,125 @@ __device__ __forceinline__ void load_rows_async(uint32_t smem_base, const __nv_b
   for (int idx = tid; idx < rows * CPR; idx += NTHREADS) {
     const int r = idx / CPR, c = idx % CPR;
     cp_async16(smem_base + (uint32_t)(r * D * 2 + ((c ^ (r & 7)) << 4)), g + (size_t)r * D + c * 8);
+  }
+}
+
+// ---- fp8 (e4m3) cache path --------------------------------------------------------------------
+// The raw bytes go to shared memory (16-byte chunk c of token row r at a swizzled position) and are
+// widened to fp16 in registers right after ldmatrix (e4m3 is a subset of fp16, so this is exact).
+// Q and P are fed as fp16 to the fp16 MMA.
+//  * QK: an 8x8 b16 ldmatrix tile is 8 tokens x 16 e4m3 values, so a thread receives k = 4c..4c+3 of a
+//    16-wide k block (c = lane & 3) instead of the MMA's {2c, 2c+1, 2c+8, 2c+9}; the Q fragments are
+//    loaded with the same permutation of k, which leaves the dot product unchanged.
+//  * PV: the transposed tile hands a thread V[tokens 2c, 2c+1][dims 2j, 2j+1] (j = lane >> 2); even and
+//    odd dims go to two MMAs, so accumulator o[2 * dc + par][e] holds dim 16 * dc + 4c + par + 2 * (e & 1).
+template <int D>
+__device__ __forceinline__ int swz_fp8(int r, int c) {
+  return D == 128 ? (c ^ (r & 7)) : (c ^ ((r >> 1) & 3));
+}
+template <int D, int NTHREADS>
+__device__ __forceinline__ void load_rows_async_fp8(uint32_t smem_base, const uint8_t* g, int rows, int tid) {
+  constexpr int CPR = D / 16;
+  for (int idx = tid; idx < rows * CPR; idx += NTHREADS) {
+    const int r = idx / CPR, c = idx % CPR;
+    cp_async16(smem_base + (uint32_t)(r * D + (swz_fp8<D>(r, c) << 4)), g + ((size_t)idx << 4));
+  }
+}
+// How e4m3 pairs become f16x2: bit 0 (K) / bit 1 (V) set = cvt.rn.f16x2.e4m3x2, clear = the integer
+// widening below.  Measured on B200 (256 requests x 2048 context): 0.358 ms with 0, 0.334 with 1 or 2,
+// 0.307 with 3; the bf16 cache takes 0.338 ms.
+#ifndef B200_FP8_WIDEN
+#define B200_FP8_WIDEN 3
+#endif
+// Two e4m3 bytes of x, picked by the byte permutation SEL = 0x{hi}4{lo}4, to f16x2 (low half first).
+// Integer widening: the 7 magnitude bits of a byte placed at bit 7 of a half give exactly value / 256,
+// sub-normals included, so that variant carries a factor that the host folds into the scales.
+template <int HW, uint32_t SEL>
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2_scaled(uint32_t x) {
+  if constexpr (HW) {
+    constexpr uint32_t LO = (SEL >> 4) & 0xfu, HI = (SEL >> 12) & 0xfu;
+    uint32_t h2;
+    if constexpr (LO == 0 && HI == 1) {
+      asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo; }" : "=r"(h2) : "r"(x));
+    } else if constexpr (LO == 2 && HI == 3) {
+      asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, hi; }" : "=r"(h2) : "r"(x));
+    } else {
+      uint32_t u;
+      asm("prmt.b32 %0, %1, 0, %2;" : "=r"(u) : "r"(x), "n"(0x4400u | (HI << 4) | LO));
+      asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo; }" : "=r"(h2) : "r"(u));
+    }
+    return h2;
+  }
+  uint32_t t;
+  asm("prmt.b32 %0, %1, 0, %2;" : "=r"(t) : "r"(x), "n"(SEL));       // (b_lo << 8) | (b_hi << 24)
+  return (t & 0x80008000u) | ((t >> 1) & 0x3f803f80u);
+}
+constexpr bool kHwK = (B200_FP8_WIDEN & 1) != 0, kHwV = (B200_FP8_WIDEN & 2) != 0;
+__device__ __forceinline__ void mma_f16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_f16(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+  return pack_f16(f.x, f.y);
+}
+// Q fragments for the fp8 path: fp16, k permuted as described above.  q0 / q1 may be null (zero rows).
+template <int D>
+__device__ __forceinline__ void load_q_frags_fp8(uint32_t (*qf)[4], const __nv_bfloat16* q0,
+                                                 const __nv_bfloat16* q1, int lane) {
+  const int c4 = 4 * (lane & 3);
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    uint2 a = make_uint2(0u, 0u), b = make_uint2(0u, 0u);
+    if (q0) a = *reinterpret_cast<const uint2*>(q0 + ks * 16 + c4);
+    if (q1) b = *reinterpret_cast<const uint2*>(q1 + ks * 16 + c4);
+    qf[ks][0] = bf16x2_to_f16x2(a.x); qf[ks][1] = bf16x2_to_f16x2(b.x);
+    qf[ks][2] = bf16x2_to_f16x2(a.y); qf[ks][3] = bf16x2_to_f16x2(b.y);
+  }
+}
+template <int D>
+__device__ __forceinline__ void qk_16_fp8(float s[2][4], const uint32_t (*qf)[4], uint32_t kbase, int lane) {
+  const int mi = lane >> 3, rr = lane & 7;
+  const int tok = (mi & 1) * 8 + rr;
+#pragma unroll
+  for (int k2 = 0; k2 < D / 32; ++k2) {
+    const int c = 2 * k2 + (mi >> 1);
+    uint32_t b[4];     // (tokens 0-7, chunk 2k2) (8-15, 2k2) (0-7, 2k2+1) (8-15, 2k2+1)
+    ldsm_x4(b, kbase + (uint32_t)(tok * D + (swz_fp8<D>(tok, c) << 4)));
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mma_f16_16816(s[0], qf[2 * k2 + h], e4m3x2_to_f16x2_scaled<kHwK, 0x1404u>(b[2 * h]),
+                    e4m3x2_to_f16x2_scaled<kHwK, 0x3424u>(b[2 * h]));
+      mma_f16_16816(s[1], qf[2 * k2 + h], e4m3x2_to_f16x2_scaled<kHwK, 0x1404u>(b[2 * h + 1]),
+                    e4m3x2_to_f16x2_scaled<kHwK, 0x3424u>(b[2 * h + 1]));
+    }
+  }
+}
+template <int D>
+__device__ __forceinline__ void pv_16_fp8(float (*o)[4], const uint32_t* pa, uint32_t vbase, int lane) {
+  const int mi = lane >> 3, rr = lane & 7;
+  const int tok = (mi & 1) * 8 + rr;
+#pragma unroll
+  for (int d2 = 0; d2 < D / 32; ++d2) {
+    const int c = 2 * d2 + (mi >> 1);
+    uint32_t b[4];     // (tokens 0-7, chunk 2d2) (8-15, 2d2) (0-7, 2d2+1) (8-15, 2d2+1)
+    ldsm_x4_t(b, vbase + (uint32_t)(tok * D + (swz_fp8<D>(tok, c) << 4)));
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      // bytes of b[2h]: V[2c][2j], V[2c][2j+1], V[2c+1][2j], V[2c+1][2j+1]; b[2h+1]: tokens + 8
+      const uint32_t lo = b[2 * h], hi = b[2 * h + 1];
+      mma_f16_16816(o[4 * d2 + 2 * h], pa, e4m3x2_to_f16x2_scaled<kHwV, 0x2404u>(lo),
+                    e4m3x2_to_f16x2_scaled<kHwV, 0x2404u>(hi));
+      mma_f16_16816(o[4 * d2 + 2 * h + 1], pa, e4m3x2_to_f16x2_scaled<kHwV, 0x3414u>(lo),
+                    e4m3x2_to_f16x2_scaled<kHwV, 0x3414u>(hi));
+    }
   }
 }
 
@@ -119,12 +239,25 @@ __device__ __forceinline__ void pv_16(float (*o)[4], const uint32_t* pa, uint32_
 }
 
 // ------------------------------------------------------------------------ decode
-template <int D>
+// FP8: the cache holds e4m3 bytes; the ring keeps the same number of bytes in flight with twice the stages.
+template <int D, bool FP8>
+struct DecodeSmem {
+  static constexpr int STAGES = FP8 ? 6 : 3;
+  static constexpr int PAGE_BYTES = 16 * D * (FP8 ? 1 : 2);           // 16 tokens of K (or V) as stored
+  static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int MERGE_BYTES = 16 * D * 4;                      // [16][D] fp32 per warp at the end
+  static constexpr int WARP_BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
+  static constexpr int TOTAL = 4 * WARP_BYTES;
+};
+
+template <int D, bool FP8 = false>
 __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p) {
-  constexpr int STAGES = 3;
-  constexpr int PAGE_BYTES = 16 * D * 2;          // 16 tokens of K (or V)
-  constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
-  constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
+  using SM = DecodeSmem<D, FP8>;
+  constexpr int STAGES = SM::STAGES;
+  constexpr int PAGE_BYTES = SM::PAGE_BYTES;
+  constexpr int STAGE_BYTES = SM::STAGE_BYTES;
+  constexpr int WARP_BYTES = SM::WARP_BYTES;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float s_ml[4][16][2];
   __shared__ int s_last;
@@ -148,12 +281,16 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
     const __nv_bfloat16* q1 = nullptr;
     if (r0 < rows_valid) q0 = p.q + ((size_t)(qs + r0 / G) * p.Hq + h * G + r0 % G) * D;
     if (r1 < rows_valid) q1 = p.q + ((size_t)(qs + r1 / G) * p.Hq + h * G + r1 % G) * D;
+    if constexpr (FP8) {
+      load_q_frags_fp8<D>(qf, q0, q1, lane);
+    } else {
 #pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + cb) : 0u;
-      qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + cb) : 0u;
-      qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + cb) : 0u;
-      qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + cb) : 0u;
+      for (int ks = 0; ks < D / 16; ++ks) {
+        qf[ks][0] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + cb) : 0u;
+        qf[ks][1] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + cb) : 0u;
+        qf[ks][2] = q0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + cb) : 0u;
+        qf[ks][3] = q1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + cb) : 0u;
+      }
     }
   }
 
@@ -186,11 +323,17 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
     }
     long long blk = __shfl_sync(0xffffffffu, bt_reg, page - bt_base);
     if (blk < 0 || blk >= p.num_blocks) blk = 0;
-    const __nv_bfloat16* kp = p.kv + (((size_t)blk * 2 + 0) * p.Hkv + h) * head_stride + (size_t)off * D;
-    const __nv_bfloat16* vp = p.kv + (((size_t)blk * 2 + 1) * p.Hkv + h) * head_stride + (size_t)off * D;
+    const size_t ko = (((size_t)blk * 2 + 0) * p.Hkv + h) * head_stride + (size_t)off * D;
+    const size_t vo = (((size_t)blk * 2 + 1) * p.Hkv + h) * head_stride + (size_t)off * D;
     const uint32_t sb = wbase + stage * STAGE_BYTES;
-    load_rows_async<D, 32>(sb, kp, 16, lane);
-    load_rows_async<D, 32>(sb + PAGE_BYTES, vp, 16, lane);
+    if constexpr (FP8) {
+      const uint8_t* kv8 = reinterpret_cast<const uint8_t*>(p.kv);
+      load_rows_async_fp8<D, 32>(sb, kv8 + ko, 16, lane);
+      load_rows_async_fp8<D, 32>(sb + PAGE_BYTES, kv8 + vo, 16, lane);
+    } else {
+      load_rows_async<D, 32>(sb, p.kv + ko, 16, lane);
+      load_rows_async<D, 32>(sb + PAGE_BYTES, p.kv + vo, 16, lane);
+    }
   };
 
   float o[D / 8][4];
@@ -214,7 +357,8 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
 
     const uint32_t sb = wbase + stage * STAGE_BYTES;
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    qk_16<D>(s, qf, sb, lane);
+    if constexpr (FP8) qk_16_fp8<D>(s, qf, sb, lane);
+    else qk_16<D>(s, qf, sb, lane);
     const int tk = (c << 4) + 2 * (lane & 3);
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -255,9 +399,15 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
         o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1;
       }
     }
-    uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
-                      pack_bf16(s[1][2], s[1][3])};
-    pv_16<D>(o, pa, sb + PAGE_BYTES, lane);
+    if constexpr (FP8) {
+      uint32_t pa[4] = {pack_f16(s[0][0], s[0][1]), pack_f16(s[0][2], s[0][3]), pack_f16(s[1][0], s[1][1]),
+                        pack_f16(s[1][2], s[1][3])};
+      pv_16_fp8<D>(o, pa, sb + PAGE_BYTES, lane);
+    } else {
+      uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
+                        pack_bf16(s[1][2], s[1][3])};
+      pv_16<D>(o, pa, sb + PAGE_BYTES, lane);
+    }
   }
   cp_async_wait<0>();
   // row sums over the 4 lanes that share a row
@@ -267,11 +417,22 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
 
   // ---- merge the 4 warps in shared memory (each warp reuses its own ring)
   float* wo = reinterpret_cast<float*>(smem + warp * WARP_BYTES);        // [16][D] fp32 (<= 8 KB)
+  if constexpr (FP8) {
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) {
-    const int col = i * 8 + 2 * (lane & 3);
-    *reinterpret_cast<float2*>(wo + row0 * D + col) = make_float2(o[i][0], o[i][1]);
-    *reinterpret_cast<float2*>(wo + row1 * D + col) = make_float2(o[i][2], o[i][3]);
+    for (int dc = 0; dc < D / 16; ++dc) {             // permuted accumulator layout of pv_16_fp8
+      const int col = dc * 16 + 4 * (lane & 3);
+      *reinterpret_cast<float4*>(wo + row0 * D + col) =
+          make_float4(o[2 * dc][0], o[2 * dc + 1][0], o[2 * dc][1], o[2 * dc + 1][1]);
+      *reinterpret_cast<float4*>(wo + row1 * D + col) =
+          make_float4(o[2 * dc][2], o[2 * dc + 1][2], o[2 * dc][3], o[2 * dc + 1][3]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int col = i * 8 + 2 * (lane & 3);
+      *reinterpret_cast<float2*>(wo + row0 * D + col) = make_float2(o[i][0], o[i][1]);
+      *reinterpret_cast<float2*>(wo + row1 * D + col) = make_float2(o[i][2], o[i][3]);
+    }
   }
   if ((lane & 3) == 0) {
     s_ml[warp][row0][0] = m[0]; s_ml[warp][row0][1] = l[0];
@@ -308,12 +469,12 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
       const float sc = (mfin == -INFINITY) ? 0.f : ex2(mfin - mnew);
       Lfin = Lfin * sc + ex2(sk - mnew);
       mfin = mnew;
-      const float inv = 1.f / Lfin;
+      const float inv = (FP8 ? p.v_scale : 1.f) / Lfin;
       __nv_bfloat16* dst = p.out + ((size_t)tok_row * p.Hq + head) * D + seg * SEG;
 #pragma unroll
       for (int d = 0; d < SEG; ++d) dst[d] = __float2bfloat16(a[d] * sc * inv);
     } else {
-      const float inv = Lfin > 0.f ? 1.f / Lfin : 0.f;
+      const float inv = Lfin > 0.f ? (FP8 ? p.v_scale : 1.f) / Lfin : 0.f;
       __nv_bfloat16* dst = p.out + ((size_t)tok_row * p.Hq + head) * D + seg * SEG;
 #pragma unroll
       for (int d = 0; d < SEG; ++d) dst[d] = __float2bfloat16(a[d] * inv);
@@ -364,10 +525,13 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
 }
 
 // ----------------------------------------------------------------------- prefill
-template <int D>
+// FP8: the stages hold raw e4m3 tiles, widened in registers (see the fp8 cache path above).
+template <int D, bool FP8 = false>
 __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p) {
-  constexpr int BQ = 64, BKV = 64, STAGES = 2;
-  constexpr int TILE_BYTES = BKV * D * 2;          // K (or V) chunk
+  constexpr int BQ = 64, BKV = 64;
+  constexpr int EB = FP8 ? 1 : 2;                  // bytes per cache element
+  constexpr int TILE_BYTES = BKV * D * EB;         // K (or V) chunk as stored
+  constexpr int GROUP_BYTES = 16 * D * EB;         // one 16-token group
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
@@ -398,12 +562,16 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
     const int cb = 2 * (lane & 3);
     const __nv_bfloat16* qa = row0 < q_len ? p.q + ((size_t)(qs + row0) * p.Hq + hq) * D : nullptr;
     const __nv_bfloat16* qb = row1 < q_len ? p.q + ((size_t)(qs + row1) * p.Hq + hq) * D : nullptr;
+    if constexpr (FP8) {
+      load_q_frags_fp8<D>(qf, qa, qb, lane);
+    } else {
 #pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      qf[ks][0] = qa ? *reinterpret_cast<const uint32_t*>(qa + ks * 16 + cb) : 0u;
-      qf[ks][1] = qb ? *reinterpret_cast<const uint32_t*>(qb + ks * 16 + cb) : 0u;
-      qf[ks][2] = qa ? *reinterpret_cast<const uint32_t*>(qa + ks * 16 + 8 + cb) : 0u;
-      qf[ks][3] = qb ? *reinterpret_cast<const uint32_t*>(qb + ks * 16 + 8 + cb) : 0u;
+      for (int ks = 0; ks < D / 16; ++ks) {
+        qf[ks][0] = qa ? *reinterpret_cast<const uint32_t*>(qa + ks * 16 + cb) : 0u;
+        qf[ks][1] = qb ? *reinterpret_cast<const uint32_t*>(qb + ks * 16 + cb) : 0u;
+        qf[ks][2] = qa ? *reinterpret_cast<const uint32_t*>(qa + ks * 16 + 8 + cb) : 0u;
+        qf[ks][3] = qb ? *reinterpret_cast<const uint32_t*>(qb + ks * 16 + 8 + cb) : 0u;
+      }
     }
   }
   const int kv_end = min(seq_len, ctx + q0 + BQ);               // causal bound of the tile
@@ -425,10 +593,16 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
       const int page = tok / p.block_size, off = tok - page * p.block_size;
       long long blk = bt[page];
       if (blk < 0 || blk >= p.num_blocks) blk = 0;
-      const __nv_bfloat16* kp = p.kv + (((size_t)blk * 2 + 0) * p.Hkv + h) * head_stride + (size_t)off * D;
-      const __nv_bfloat16* vp = p.kv + (((size_t)blk * 2 + 1) * p.Hkv + h) * head_stride + (size_t)off * D;
-      load_rows_async<D, 128>(sb + g * 16 * D * 2, kp, 16, threadIdx.x);
-      load_rows_async<D, 128>(sb + TILE_BYTES + g * 16 * D * 2, vp, 16, threadIdx.x);
+      const size_t ko = (((size_t)blk * 2 + 0) * p.Hkv + h) * head_stride + (size_t)off * D;
+      const size_t vo = (((size_t)blk * 2 + 1) * p.Hkv + h) * head_stride + (size_t)off * D;
+      if constexpr (FP8) {
+        const uint8_t* kv8 = reinterpret_cast<const uint8_t*>(p.kv);
+        load_rows_async_fp8<D, 128>(sb + g * GROUP_BYTES, kv8 + ko, 16, threadIdx.x);
+        load_rows_async_fp8<D, 128>(sb + TILE_BYTES + g * GROUP_BYTES, kv8 + vo, 16, threadIdx.x);
+      } else {
+        load_rows_async<D, 128>(sb + g * GROUP_BYTES, p.kv + ko, 16, threadIdx.x);
+        load_rows_async<D, 128>(sb + TILE_BYTES + g * GROUP_BYTES, p.kv + vo, 16, threadIdx.x);
+      }
     }
   };
 
@@ -455,8 +629,10 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
     for (int i = 0; i < BKV / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
 #pragma unroll
     for (int g = 0; g < BKV / 16; ++g) {
-      if (tok0 + g * 16 <= warp_max_key && tok0 + g * 16 < kv_end)
-        qk_16<D>(reinterpret_cast<float(*)[4]>(&s[2 * g][0]), qf, sb + g * 16 * D * 2, lane);
+      if (tok0 + g * 16 <= warp_max_key && tok0 + g * 16 < kv_end) {
+        if constexpr (FP8) qk_16_fp8<D>(reinterpret_cast<float(*)[4]>(&s[2 * g][0]), qf, sb + g * GROUP_BYTES, lane);
+        else qk_16<D>(reinterpret_cast<float(*)[4]>(&s[2 * g][0]), qf, sb + g * GROUP_BYTES, lane);
+      }
     }
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -498,10 +674,17 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
 #pragma unroll
     for (int g = 0; g < BKV / 16; ++g) {
       if (tok0 + g * 16 <= warp_max_key && tok0 + g * 16 < kv_end) {
-        uint32_t pa[4] = {pack_bf16(s[2 * g][0], s[2 * g][1]), pack_bf16(s[2 * g][2], s[2 * g][3]),
-                          pack_bf16(s[2 * g + 1][0], s[2 * g + 1][1]),
-                          pack_bf16(s[2 * g + 1][2], s[2 * g + 1][3])};
-        pv_16<D>(o, pa, sb + TILE_BYTES + g * 16 * D * 2, lane);
+        if constexpr (FP8) {
+          uint32_t pa[4] = {pack_f16(s[2 * g][0], s[2 * g][1]), pack_f16(s[2 * g][2], s[2 * g][3]),
+                            pack_f16(s[2 * g + 1][0], s[2 * g + 1][1]),
+                            pack_f16(s[2 * g + 1][2], s[2 * g + 1][3])};
+          pv_16_fp8<D>(o, pa, sb + TILE_BYTES + g * GROUP_BYTES, lane);
+        } else {
+          uint32_t pa[4] = {pack_bf16(s[2 * g][0], s[2 * g][1]), pack_bf16(s[2 * g][2], s[2 * g][3]),
+                            pack_bf16(s[2 * g + 1][0], s[2 * g + 1][1]),
+                            pack_bf16(s[2 * g + 1][2], s[2 * g + 1][3])};
+          pv_16<D>(o, pa, sb + TILE_BYTES + g * GROUP_BYTES, lane);
+        }
       }
     }
     __syncthreads();
@@ -520,21 +703,38 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
     l[1] = l[1] * sc1 + ex2(sk - n1);
     m[0] = n0; m[1] = n1;
   }
+  if constexpr (FP8) { sc0 *= p.v_scale; sc1 *= p.v_scale; }
   const float inv0 = l[0] > 0.f ? sc0 / l[0] : 0.f, inv1 = l[1] > 0.f ? sc1 / l[1] : 0.f;
   if (row0 < q_len) {
-    __nv_bfloat16* dst = p.out + ((size_t)(qs + row0) * p.Hq + hq) * D + 2 * (lane & 3);
+    __nv_bfloat16* dst = p.out + ((size_t)(qs + row0) * p.Hq + hq) * D + (FP8 ? 4 : 2) * (lane & 3);
+    if constexpr (FP8) {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i)
-      *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+      for (int dc = 0; dc < D / 16; ++dc)
+        *reinterpret_cast<uint2*>(dst + dc * 16) =
+            make_uint2(pack_bf16(o[2 * dc][0] * inv0, o[2 * dc + 1][0] * inv0),
+                       pack_bf16(o[2 * dc][1] * inv0, o[2 * dc + 1][1] * inv0));
+    } else {
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+    }
     if (p.lse != nullptr && (lane & 3) == 0)
       p.lse[(size_t)(qs + row0) * p.Hq + hq] =
           l[0] > 0.f ? (m[0] + log2f(l[0])) * 0.6931471805599453f : -INFINITY;
   }
   if (row1 < q_len) {
-    __nv_bfloat16* dst = p.out + ((size_t)(qs + row1) * p.Hq + hq) * D + 2 * (lane & 3);
+    __nv_bfloat16* dst = p.out + ((size_t)(qs + row1) * p.Hq + hq) * D + (FP8 ? 4 : 2) * (lane & 3);
+    if constexpr (FP8) {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i)
-      *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+      for (int dc = 0; dc < D / 16; ++dc)
+        *reinterpret_cast<uint2*>(dst + dc * 16) =
+            make_uint2(pack_bf16(o[2 * dc][2] * inv1, o[2 * dc + 1][2] * inv1),
+                       pack_bf16(o[2 * dc][3] * inv1, o[2 * dc + 1][3] * inv1));
+    } else {
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+    }
     if (p.lse != nullptr && (lane & 3) == 0)
       p.lse[(size_t)(qs + row1) * p.Hq + hq] =
           l[1] > 0.f ? (m[1] + log2f(l[1])) * 0.6931471805599453f : -INFINITY;
@@ -565,7 +765,42 @@ static void fill_params(AttnParams& p, const void* q, const void* kv, void* out,
   p.scale_log2 = scale * 1.4426950408889634f;
   p.softcap = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   p.sinks = sinks;
+  p.v_scale = 1.f;
   (void)D;
+}
+
+// fp8 (e4m3) cache: K's dequantisation factor joins the logit scale, V's the output normalisation.
+// The integer widening variant yields value / 256 (see e4m3x2_to_f16x2_scaled), hence the factors.
+static void set_fp8_scales(AttnParams& p, float k_scale, float v_scale) {
+  p.scale_log2 *= k_scale * (kHwK ? 1.f : 256.f);
+  p.v_scale = v_scale * (kHwV ? 1.f : 256.f);
+}
+
+template <int D, bool FP8>
+static cudaError_t launch_decode(dim3 grid, cudaStream_t stream, const AttnParams& p) {
+  constexpr int smem = DecodeSmem<D, FP8>::TOTAL;
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         smem);
+    if (e != cudaSuccess) return e;
+    set = true;
+  }
+  return launch_pdl(attn_decode_kernel<D, FP8>, grid, dim3(128), smem, stream, p);
+}
+
+template <int D, bool FP8>
+static cudaError_t launch_prefill(dim3 grid, cudaStream_t stream, const AttnParams& p) {
+  constexpr int smem = 2 * 2 * 64 * D * (FP8 ? 1 : 2);
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D, FP8>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    set = true;
+  }
+  attn_prefill_kernel<D, FP8><<<grid, 128, smem, stream>>>(p);
+  return cudaGetLastError();
 }
 
 // Scratch sizes of the decode kernel for (num_reqs, Hkv, splits, D).
@@ -576,11 +811,12 @@ extern "C" size_t b200_attn_decode_scratch_bytes(int num_reqs, int Hkv, int spli
 
 // Requests [req_begin, req_end) must have q_len * (Hq/Hkv) <= 16.  scratch holds part_o then
 // part_ml; counters: [num_reqs * Hkv] ints, zero before first use (re-armed by the kernel).
-extern "C" int b200_attn_decode(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
-                                const int* seq_lens, const int* qsl, int req_begin, int req_end,
-                                int max_blocks, int block_size, long long num_blocks, int Hq, int Hkv, int D,
-                                float scale, int window, float softcap, const float* sinks, int num_splits,
-                                void* scratch, int* counters, cudaStream_t stream) {
+static int attn_decode_impl(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                            const int* seq_lens, const int* qsl, int req_begin, int req_end,
+                            int max_blocks, int block_size, long long num_blocks, int Hq, int Hkv, int D,
+                            float scale, int window, float softcap, const float* sinks, int num_splits,
+                            void* scratch, int* counters, int kv_fp8, float k_scale, float v_scale,
+                            cudaStream_t stream) {
   const int R = req_end - req_begin;
   if (R <= 0) return 0;
   if (block_size % 16 || (Hq % Hkv) || Hq / Hkv > 16) {
@@ -600,25 +836,12 @@ extern "C" int b200_attn_decode(const void* q, const void* kv, void* out, float*
   p.part_ml = p.part_o + (size_t)R * Hkv * num_splits * 16 * D;
   p.counters = counters;
   dim3 grid(Hkv, R, num_splits);
-  if (D == 128) {
-    const int smem = 4 * 3 * 2 * 16 * 128 * 2;
-    static bool set = false;
-    if (!set) {
-      B200_CUDA_CHECK(cudaFuncSetAttribute(attn_decode_kernel<128>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      set = true;
-    }
-    B200_CUDA_CHECK(launch_pdl(attn_decode_kernel<128>, grid, dim3(128), smem, stream, p));
-  } else if (D == 64) {
-    const int smem = 4 * 3 * 2 * 16 * 64 * 2 < 4 * 16 * 64 * 4 ? 4 * 16 * 64 * 4 : 4 * 3 * 2 * 16 * 64 * 2;
-    static bool set = false;
-    if (!set) {
-      B200_CUDA_CHECK(cudaFuncSetAttribute(attn_decode_kernel<64>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      set = true;
-    }
-    B200_CUDA_CHECK(launch_pdl(attn_decode_kernel<64>, grid, dim3(128), smem, stream, p));
-  } else {
+  if (kv_fp8) set_fp8_scales(p, k_scale, v_scale);
+  if (D == 128 && kv_fp8) B200_CUDA_CHECK((launch_decode<128, true>(grid, stream, p)));
+  else if (D == 128) B200_CUDA_CHECK((launch_decode<128, false>(grid, stream, p)));
+  else if (D == 64 && kv_fp8) B200_CUDA_CHECK((launch_decode<64, true>(grid, stream, p)));
+  else if (D == 64) B200_CUDA_CHECK((launch_decode<64, false>(grid, stream, p)));
+  else {
     b200_set_last_error("attn_decode: head_dim must be 64 or 128", __FILE__, __LINE__);
     return -1;
   }
@@ -626,12 +849,33 @@ extern "C" int b200_attn_decode(const void* q, const void* kv, void* out, float*
   return 0;
 }
 
+extern "C" int b200_attn_decode(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                                const int* seq_lens, const int* qsl, int req_begin, int req_end,
+                                int max_blocks, int block_size, long long num_blocks, int Hq, int Hkv, int D,
+                                float scale, int window, float softcap, const float* sinks, int num_splits,
+                                void* scratch, int* counters, cudaStream_t stream) {
+  return attn_decode_impl(q, kv, out, lse, block_tables, seq_lens, qsl, req_begin, req_end, max_blocks,
+                          block_size, num_blocks, Hq, Hkv, D, scale, window, softcap, sinks, num_splits, scratch,
+                          counters, 0, 1.f, 1.f, stream);
+}
+// The cache holds e4m3 bytes: stored value * k_scale (v_scale) is the key (value).
+extern "C" int b200_attn_decode_fp8kv(const void* q, const void* kv, void* out, float* lse,
+                                      const int* block_tables, const int* seq_lens, const int* qsl,
+                                      int req_begin, int req_end, int max_blocks, int block_size,
+                                      long long num_blocks, int Hq, int Hkv, int D, float scale, int window,
+                                      float softcap, const float* sinks, int num_splits, void* scratch,
+                                      int* counters, float k_scale, float v_scale, cudaStream_t stream) {
+  return attn_decode_impl(q, kv, out, lse, block_tables, seq_lens, qsl, req_begin, req_end, max_blocks,
+                          block_size, num_blocks, Hq, Hkv, D, scale, window, softcap, sinks, num_splits, scratch,
+                          counters, 1, k_scale, v_scale, stream);
+}
+
 // num_tiles = sum over requests of ceil(q_len / 64) (computed by the caller from host metadata).
-extern "C" int b200_attn_prefill(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
-                                 const int* seq_lens, const int* qsl, int req_begin, int req_end,
-                                 int num_tiles, int max_blocks, int block_size, long long num_blocks, int Hq,
-                                 int Hkv, int D, float scale, int window, float softcap, const float* sinks,
-                                 cudaStream_t stream) {
+static int attn_prefill_impl(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                             const int* seq_lens, const int* qsl, int req_begin, int req_end,
+                             int num_tiles, int max_blocks, int block_size, long long num_blocks, int Hq,
+                             int Hkv, int D, float scale, int window, float softcap, const float* sinks,
+                             int kv_fp8, float k_scale, float v_scale, cudaStream_t stream) {
   if (req_end <= req_begin || num_tiles <= 0) return 0;
   if (block_size % 16 || (Hq % Hkv)) {
     b200_set_last_error("attn_prefill: block_size % 16 == 0 required", __FILE__, __LINE__);
@@ -645,24 +889,37 @@ extern "C" int b200_attn_prefill(const void* q, const void* kv, void* out, float
   p.num_splits = 1;
   p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr;
   dim3 grid(Hq, num_tiles);
-  if (D == 128) {
-    const int smem = 2 * 2 * 64 * 128 * 2;
-    static bool set = false;
-    if (!set) {
-      B200_CUDA_CHECK(cudaFuncSetAttribute(attn_prefill_kernel<128>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      set = true;
-    }
-    attn_prefill_kernel<128><<<grid, 128, smem, stream>>>(p);
-  } else if (D == 64) {
-    const int smem = 2 * 2 * 64 * 64 * 2;
-    attn_prefill_kernel<64><<<grid, 128, smem, stream>>>(p);
-  } else {
+  if (kv_fp8) set_fp8_scales(p, k_scale, v_scale);
+  if (D == 128 && kv_fp8) B200_CUDA_CHECK((launch_prefill<128, true>(grid, stream, p)));
+  else if (D == 128) B200_CUDA_CHECK((launch_prefill<128, false>(grid, stream, p)));
+  else if (D == 64 && kv_fp8) B200_CUDA_CHECK((launch_prefill<64, true>(grid, stream, p)));
+  else if (D == 64) B200_CUDA_CHECK((launch_prefill<64, false>(grid, stream, p)));
+  else {
     b200_set_last_error("attn_prefill: head_dim must be 64 or 128", __FILE__, __LINE__);
     return -1;
   }
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
+}
+
+extern "C" int b200_attn_prefill(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                                 const int* seq_lens, const int* qsl, int req_begin, int req_end,
+                                 int num_tiles, int max_blocks, int block_size, long long num_blocks, int Hq,
+                                 int Hkv, int D, float scale, int window, float softcap, const float* sinks,
+                                 cudaStream_t stream) {
+  return attn_prefill_impl(q, kv, out, lse, block_tables, seq_lens, qsl, req_begin, req_end, num_tiles,
+                           max_blocks, block_size, num_blocks, Hq, Hkv, D, scale, window, softcap, sinks, 0, 1.f,
+                           1.f, stream);
+}
+extern "C" int b200_attn_prefill_fp8kv(const void* q, const void* kv, void* out, float* lse,
+                                       const int* block_tables, const int* seq_lens, const int* qsl,
+                                       int req_begin, int req_end, int num_tiles, int max_blocks,
+                                       int block_size, long long num_blocks, int Hq, int Hkv, int D, float scale,
+                                       int window, float softcap, const float* sinks, float k_scale,
+                                       float v_scale, cudaStream_t stream) {
+  return attn_prefill_impl(q, kv, out, lse, block_tables, seq_lens, qsl, req_begin, req_end, num_tiles,
+                           max_blocks, block_size, num_blocks, Hq, Hkv, D, scale, window, softcap, sinks, 1,
+                           k_scale, v_scale, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -679,8 +936,8 @@ static __device__ __align__(256) unsigned char g_attn_static_scratch[B200_ATTN_S
 
 namespace {
 constexpr int kMaxDevices = 64;
-constexpr int kDecodeSmem128 = 4 * 3 * 2 * 16 * 128 * 2;
-constexpr int kDecodeSmem64 = 4 * 3 * 2 * 16 * 64 * 2;
+constexpr int kDecodeSmem128 = b200::DecodeSmem<128, false>::TOTAL;
+constexpr int kDecodeSmem64 = b200::DecodeSmem<64, false>::TOTAL;
 std::mutex g_static_mu;
 unsigned char* g_static_ptr[kMaxDevices] = {};   // device address of the array, per device
 }  // namespace

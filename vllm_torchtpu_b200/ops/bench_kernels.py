@@ -91,7 +91,7 @@ def bench_gemm(T, N, K, iters=20, impl="tcgen05", check=True) -> dict:
             "peaks": tag, "bn": bn, "splits": splits, "rel_err": err, "status": cuda.check_status()}
 
 
-def bench_attn_decode(reqs, ctx, Hq=32, Hkv=8, D=128, iters=20) -> dict:
+def bench_attn_decode(reqs, ctx, Hq=32, Hkv=8, D=128, iters=20, kv_fp8=False) -> dict:
     from ..runner.attn_metadata import AttentionMetadata
     from . import cuda
     pk, tag = peaks()
@@ -99,6 +99,8 @@ def bench_attn_decode(reqs, ctx, Hq=32, Hkv=8, D=128, iters=20) -> dict:
     nblk_per = -(-ctx // bs)
     nb = reqs * nblk_per + 1
     cache = (torch.randn(nb, 2, Hkv, bs, D, device="cuda") * 0.5).bfloat16()
+    if kv_fp8:
+        cache = cache.to(torch.float8_e4m3fn)
     bt = (torch.randperm(nb - 1, device="cuda") + 1).to(torch.int32).view(reqs, nblk_per).contiguous()
     q = torch.randn(reqs, Hq, D, device="cuda").bfloat16()
     qsl = torch.arange(reqs + 1, device="cuda", dtype=torch.int32)
@@ -107,9 +109,9 @@ def bench_attn_decode(reqs, ctx, Hq=32, Hkv=8, D=128, iters=20) -> dict:
                              padded_num_reqs=reqs, padded_num_tokens=reqs)
     fn = lambda: cuda.paged_attention(q, cache, meta, D ** -0.5)
     ms = time_fn(fn, iters)
-    byts = reqs * ctx * 2 * Hkv * D * 2.0
+    byts = reqs * ctx * 2 * Hkv * D * float(cache.element_size())
     gbs = byts / ms / 1e6
-    return {"op": "attn_decode", "reqs": reqs, "ctx": ctx, "Hq": Hq, "Hkv": Hkv, "ms": round(ms, 4),
+    return {"op": "attn_decode", "kv": "e4m3" if kv_fp8 else "bf16", "reqs": reqs, "ctx": ctx, "Hq": Hq, "Hkv": Hkv, "ms": round(ms, 4),
             "kv_gbs": round(gbs, 1), "frac_of_hbm": round(gbs / pk["hbm_gbs"], 3), "peaks": tag,
             "splits": cuda.decode_splits(reqs, Hkv)}
 
@@ -259,6 +261,7 @@ def main():
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--tp", type=int, default=1, help="decode-layer: use the per-rank shapes of this TP degree")
     ap.add_argument("--parts", default="all,gemm,attn,elem")
+    ap.add_argument("--kv-fp8", action="store_true", help="attn-decode: e4m3 KV cache")
     a = ap.parse_args()
     if a.what == "gemm":
         print(json.dumps(bench_gemm(a.T, a.N, a.K, a.iters, a.impl)))
@@ -277,7 +280,7 @@ def main():
             print(json.dumps(bench_decode_layer(a.reqs, a.ctx, a.layers, parts, a.iters, tp=a.tp)))
     if a.what in ("attn-decode", "all"):
         for reqs, ctx in ((a.reqs, a.ctx),) if a.what == "attn-decode" else ((64, 1100), (256, 2048), (8, 8000)):
-            print(json.dumps(bench_attn_decode(reqs, ctx, iters=a.iters)))
+            print(json.dumps(bench_attn_decode(reqs, ctx, iters=a.iters, kv_fp8=a.kv_fp8)))
     if a.what in ("attn-prefill", "all"):
         for reqs, q in ((a.reqs, a.q),) if a.what == "attn-prefill" else ((8, 1024), (2, 4096)):
             print(json.dumps(bench_attn_prefill(reqs, q, iters=max(5, a.iters // 2))))

@@ -244,8 +244,11 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
                     k_scale=1.0, v_scale=1.0, return_lse=False):
     """Ragged paged attention over [decode | prefill/mixed] request ranges of the batch."""
     _require_bf16(q)
-    if kv_cache.dtype != torch.bfloat16:
-        raise NotImplementedError("fp8 KV cache attention kernel")
+    # an e4m3 cache is expanded to bf16 in shared memory by the mma.sync kernels; k_scale joins the
+    # logit scale and v_scale the output normalisation (reference: layers/adapter/quantization.py:91)
+    kv_fp8 = 1 if kv_cache.dtype == torch.float8_e4m3fn else 0
+    if not kv_fp8 and kv_cache.dtype != torch.bfloat16:
+        raise NotImplementedError(f"KV cache dtype {kv_cache.dtype}: bf16 or float8_e4m3fn")
     T, Hq, D = q.shape
     nb, _, Hkv, bs, _ = kv_cache.shape
     ws = Workspace.get(q.device)
@@ -272,11 +275,15 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
         need = L.b200_attn_decode_scratch_bytes(c_int(n_dec), c_int(Hkv), c_int(splits), c_int(D))
         if need > ws.attn_scratch.numel() or n_dec * Hkv > ws.attn_counters.numel():
             splits = 1
-        _check(L.b200_attn_decode(
-            _p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
-            _p(meta.query_start_loc), c_int(0), c_int(n_dec), c_int(max_blocks), c_int(bs), c_longlong(nb),
-            c_int(Hq), c_int(Hkv), c_int(D), c_float(scale), c_int(window), c_float(cap), _p(sinks),
-            c_int(splits), _p(ws.attn_scratch), _p(ws.attn_counters), _stream()), "attn_decode")
+        args = (_p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
+                _p(meta.query_start_loc), c_int(0), c_int(n_dec), c_int(max_blocks), c_int(bs), c_longlong(nb),
+                c_int(Hq), c_int(Hkv), c_int(D), c_float(scale), c_int(window), c_float(cap), _p(sinks),
+                c_int(splits), _p(ws.attn_scratch), _p(ws.attn_counters))
+        if kv_fp8:
+            _check(L.b200_attn_decode_fp8kv(*args, c_float(k_scale), c_float(v_scale), _stream()),
+                   "attn_decode_fp8kv")
+        else:
+            _check(L.b200_attn_decode(*args, _stream()), "attn_decode")
         count_launch()
     else:
         nd = 0
@@ -287,7 +294,7 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
             tiles = int(((ql + 63) // 64).sum())
         else:
             tiles = (T + 63) // 64 + (R - nd)
-        if D == 128 and G in (1, 2, 4, 8) and envs.B200_ATTN_PREFILL_IMPL == "tc":
+        if D == 128 and G in (1, 2, 4, 8) and envs.B200_ATTN_PREFILL_IMPL == "tc" and not kv_fp8:
             # tcgen05 kernel: one CTA per (kv head, 128 / G positions), K/V shared by the GQA group
             _check(L.b200_attn_prefill_tc(
                 _p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
@@ -295,11 +302,15 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
                 c_int(bs), c_longlong(nb), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale), c_int(window),
                 c_float(cap), _p(sinks), _p(ws.status), _stream()), "attn_prefill_tc")
         else:
-            _check(L.b200_attn_prefill(
-                _p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
-                _p(meta.query_start_loc), c_int(nd), c_int(R), c_int(tiles), c_int(max_blocks), c_int(bs),
-                c_longlong(nb), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale), c_int(window), c_float(cap),
-                _p(sinks), _stream()), "attn_prefill")
+            args = (_p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
+                    _p(meta.query_start_loc), c_int(nd), c_int(R), c_int(tiles), c_int(max_blocks), c_int(bs),
+                    c_longlong(nb), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale), c_int(window),
+                    c_float(cap), _p(sinks))
+            if kv_fp8:
+                _check(L.b200_attn_prefill_fp8kv(*args, c_float(k_scale), c_float(v_scale), _stream()),
+                       "attn_prefill_fp8kv")
+            else:
+                _check(L.b200_attn_prefill(*args, _stream()), "attn_prefill")
         count_launch()
     if return_lse:
         return out, lse

@@ -96,7 +96,7 @@ class B200Platform:
     cpu_dist_backend = "gloo"
     supported_quantization = ("fp8", "fp8_block", "online_fp8", "int8", "mxfp4", "nvfp4",
                               "compressed-tensors", "awq", "gptq")
-    supported_kv_cache_dtypes = ("auto", "bfloat16", "fp8", "fp8_e4m3", "fp8_e5m2")
+    supported_kv_cache_dtypes = ("auto", "bfloat16", "fp8", "fp8_e4m3")
     supported_connectors = ("B200P2PConnector", "B200HostConnector", "B200MultiConnector",
                             "B200OffloadingConnector", "DecodeBenchConnector")
     supported_spec_methods = ("ngram", "suffix", "eagle3", "mtp", "dflash", "dspark")
@@ -135,8 +135,6 @@ class B200Platform:
             return torch.bfloat16
         if name in ("fp8", "fp8_e4m3"):
             return torch.float8_e4m3fn
-        if name == "fp8_e5m2":
-            return torch.float8_e5m2
         raise ValueError(f"unsupported kv cache dtype {name}")
 
     # ---- requests ---------------------------------------------------------
