@@ -53,3 +53,29 @@ def test_gemm_strided_views():
     y = cuda.gemm(x, w)
     want = x.float() @ w.float().t()
     torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("T,N,K,bias", [(256, 256, 64, False), (1024, 4096, 4096, False), (300, 392, 520, True),
+                                        (8192, 1024, 1024, True), (2049, 6144, 4096, False)])
+def test_gemm_two_sm(T, N, K, bias, monkeypatch):
+    """cta_group::2 kernel (SM pairs, 256 x 256 tiles) against the fp32 product, ragged edges included."""
+    from vllm_torchtpu_b200 import envs
+    from vllm_torchtpu_b200.ops import cuda
+    monkeypatch.setenv("B200_GEMM_2SM_MIN_T", "1")
+    envs.reset()
+    try:
+        g = torch.Generator(device="cuda").manual_seed(T + N)
+        x = torch.randn(T, K, device="cuda", generator=g).bfloat16()
+        w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+        b = torch.randn(N, device="cuda", generator=g).bfloat16() if bias else None
+        y = cuda.gemm(x, w, b)
+        want = x.float() @ w.float().t()
+        if bias:
+            want = want + b.float()
+        torch.cuda.synchronize()
+        assert cuda.check_status() == 0
+        err = (y.float() - want).abs().max().item()
+        assert err <= 2e-2 * want.abs().max().item() + 1e-2, err
+    finally:
+        monkeypatch.delenv("B200_GEMM_2SM_MIN_T")
+        envs.reset()

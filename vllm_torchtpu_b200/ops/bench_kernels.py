@@ -65,19 +65,28 @@ def time_fn(fn, iters: int = 20, warmup: int = 3, flush: bool = True, use_graph:
     return statistics.median(ts)
 
 
+def _select_gemm_impl(impl: str) -> None:
+    """'2sm' routes every dense GEMM of this process to the two-SM kernel, 'tcgen05' to the one-SM one."""
+    import os
+    from .. import envs
+    os.environ["B200_GEMM_2SM_MIN_T"] = "1" if impl == "2sm" else "0"
+    envs.reset()
+
+
 def bench_gemm(T, N, K, iters=20, impl="tcgen05", check=True) -> dict:
     from . import cuda
     pk, tag = peaks()
+    _select_gemm_impl(impl)
     x = torch.randn(T, K, device="cuda").bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
     y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
-    if impl == "tcgen05":
+    if impl in ("tcgen05", "2sm"):
         fn = lambda: cuda.gemm(x, w, out=y)
     else:
         fn = lambda: torch.matmul(x, w.t(), out=y)
     ms = time_fn(fn, iters)
     err = None
-    if check and impl == "tcgen05":
+    if check and impl in ("tcgen05", "2sm"):
         want = x.float() @ w.float().t()
         err = float((y.float() - want).abs().max() / want.abs().max())
     flops = 2.0 * T * N * K
@@ -215,7 +224,9 @@ def bench_gemm_sustained(T, N, K, seconds=3.0, impl="tcgen05") -> dict:
     x = torch.randn(T, K, device="cuda").bfloat16()
     ws = [(torch.randn(N, K, device="cuda") * 0.05).bfloat16() for _ in range(4)]
     y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
-    fn = (lambda w: cuda.gemm(x, w, out=y)) if impl == "tcgen05" else (lambda w: torch.matmul(x, w.t(), out=y))
+    _select_gemm_impl(impl)
+    fn = ((lambda w: cuda.gemm(x, w, out=y)) if impl in ("tcgen05", "2sm")
+          else (lambda w: torch.matmul(x, w.t(), out=y)))
     g = torch.cuda.CUDAGraph()
     for w in ws:
         fn(w)
@@ -257,7 +268,8 @@ def main():
     ap.add_argument("--ctx", type=int, default=1100)
     ap.add_argument("--q", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--impl", default="tcgen05", choices=["tcgen05", "cublas"])
+    ap.add_argument("--impl", default="tcgen05", choices=["tcgen05", "2sm", "cublas"])
+    ap.add_argument("--impls", default="tcgen05,cublas", help="gemm-sustained: implementations to run")
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--tp", type=int, default=1, help="decode-layer: use the per-rank shapes of this TP degree")
     ap.add_argument("--parts", default="all,gemm,attn,elem")
@@ -273,7 +285,7 @@ def main():
                 for impl in ("tcgen05", "cublas"):
                     print(json.dumps(bench_gemm(T, N, K, max(5, a.iters // 2), impl, check=(T <= 1024))))
     if a.what == "gemm-sustained":
-        for impl in ("tcgen05", "cublas"):
+        for impl in a.impls.split(","):
             print(json.dumps(bench_gemm_sustained(a.T, a.N, a.K, 3.0, impl)))
     if a.what == "decode-layer":
         for parts in a.parts.split(","):

@@ -212,6 +212,12 @@ def gemm(x, w, bias=None, out=None, force_splits: int = 0):
     if T == 0:
         return y.reshape(*lead, N)
     ws = Workspace.get(x.device)
+    if force_splits == 0 and 0 < envs.B200_GEMM_2SM_MIN_T <= T:
+        _check(lib().b200_gemm_bf16_2sm(
+            _p(x2), _p(w), _p(y), _p(bias), c_int(T), c_int(N), c_int(K), c_int(x2.stride(0)),
+            c_int(w.stride(0)), c_int(y.stride(0)), _p(ws.status), c_int(_sms), _stream()), "gemm_2sm")
+        count_launch()
+        return y.reshape(*lead, N)
     _check(lib().b200_gemm_bf16(
         _p(x2), _p(w), _p(y), _p(bias), c_int(T), c_int(N), c_int(K), c_int(x2.stride(0)), c_int(w.stride(0)),
         c_int(y.stride(0)), _p(ws.gemm_ws), c_size_t(ws.gemm_ws.numel()), _p(ws.gemm_counters),
