@@ -79,3 +79,26 @@ def test_gemm_two_sm(T, N, K, bias, monkeypatch):
     finally:
         monkeypatch.delenv("B200_GEMM_2SM_MIN_T")
         envs.reset()
+
+
+@pytest.mark.parametrize("T,I,K", [(256, 128, 64), (1024, 1024, 512), (300, 200, 520), (4096, 3584, 1024)])
+def test_gemm_swiglu_two_sm(T, I, K, monkeypatch):
+    """SwiGLU form of the cta_group::2 kernel: gate and up rows share a CTA's accumulator lanes."""
+    from vllm_torchtpu_b200 import envs
+    from vllm_torchtpu_b200.ops import cuda
+    monkeypatch.setenv("B200_GEMM_2SM_MIN_T", "1")
+    envs.reset()
+    try:
+        g = torch.Generator(device="cuda").manual_seed(T + I)
+        x = torch.randn(T, K, device="cuda", generator=g).bfloat16()
+        w = (torch.randn(2 * I, K, device="cuda", generator=g) * 0.05).bfloat16()
+        y = cuda.gemm_swiglu(x, w)
+        gu = x.float() @ w.float().t()
+        want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+        torch.cuda.synchronize()
+        assert cuda.check_status() == 0
+        err = (y.float() - want).abs().max().item()
+        assert err <= 2e-2 * want.abs().max().item() + 1e-2, err
+    finally:
+        monkeypatch.delenv("B200_GEMM_2SM_MIN_T")
+        envs.reset()

@@ -17,6 +17,12 @@
 //   * tempty[a] lives in the leader; the four epilogue warps of both CTAs arrive on it.
 // Every wait is time bounded (mbar_wait): on a timeout the CTA records a status code, leaves its
 // loops, and still reaches the closing cluster barrier and the TMEM release.
+//
+// SwiGLU form (W = [2I, K], gate rows then up rows, Y[T, I] = silu(gate) * up): the 128 operand-A rows
+// of a CTA are 64 gate rows followed by the 64 up rows of the same outputs, so the main loop and the
+// double-buffered 256-column accumulator are those of the plain form.  TMEM lanes 0-63 then hold gate,
+// lanes 64-127 up; the epilogue warps of a gate quarter and of the matching up quarter exchange half of
+// their values through shared memory, 32 token columns at a time, and each finishes 16 of the columns.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -41,7 +47,8 @@ constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = (BNT / 2) * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int BAR_BYTES = 256;
-constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+constexpr int XCHG_BYTES = 2 * 2 * 32 * 32 * 4;   // SwiGLU: two warp pairs x two buffers x [32 columns][32 rows] fp32
+constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + XCHG_BYTES + 1024;
 constexpr int TMEM_COLS = 512;
 constexpr int THREADS = 192;
 constexpr int GROUP_N = 8;         // raster: 8 weight tile pairs share the activations in L2
@@ -52,6 +59,7 @@ struct Params {
   int* status;
   int T, N, K, ldy;
   int n_pairs, t_tiles, kb_total;
+  int up_row_off;                  // SwiGLU: first up row of W (= I)
 };
 
 __device__ __forceinline__ void tmem_alloc_2sm(uint32_t* smem_dst, uint32_t ncols) {
@@ -111,6 +119,7 @@ __device__ __forceinline__ void decode_work(int w, const Params& p, int& n_pair,
   n_pair = first + rem - t_tile * gsize;
 }
 
+template <bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                      const Params p) {
@@ -167,14 +176,20 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_const
       for (int w = pair; w < total_work && ok; w += npairs) {
         int n_pair, t_tile;
         decode_work(w, p, n_pair, t_tile);
-        const int w_row = n_pair * (2 * BM) + (int)rank * BM;
+        // output rows (weight rows, or gate rows in the SwiGLU form) of this CTA's part of the tile
+        const int w_row = SWIGLU ? (n_pair * 2 + (int)rank) * (BM / 2) : n_pair * (2 * BM) + (int)rank * BM;
         const int t_row = t_tile * BNT + (int)rank * (BNT / 2);
         for (int kb = 0; kb < p.kb_total; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* a = smem + s * STAGE_BYTES;
           if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
           const uint32_t bar = mapa_shared(smem_u32(&full[s]), 0);
-          tma_load_2d_pair(a, &tmW, bar, kb * BK, w_row);
+          if (SWIGLU) {      // tmW has a 64-row box here
+            tma_load_2d_pair(a, &tmW, bar, kb * BK, w_row);
+            tma_load_2d_pair(a + A_BYTES / 2, &tmW, bar, kb * BK, p.up_row_off + w_row);
+          } else {
+            tma_load_2d_pair(a, &tmW, bar, kb * BK, w_row);
+          }
           tma_load_2d_pair(a + A_BYTES, &tmX, bar, kb * BK, t_row);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -225,10 +240,62 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_const
       const uint32_t acc_ph = (iter >> 1) & 1;
       if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) break;
       tc_fence_after();
-      const int n = n_pair * (2 * BM) + (int)rank * BM + row;
       const int t0 = t_tile * BNT;
       const int t_valid = min(BNT, p.T - t0);
       const uint32_t taddr = tmem_base + acc * BNT + ((uint32_t)(q * 32) << 16);
+      if constexpr (SWIGLU) {
+        // quarters 0, 1 hold gate rows, quarters 2, 3 the up rows of the same outputs
+        const int hp = q & 1;                       // warp pair
+        const int n = (n_pair * 2 + (int)rank) * (BM / 2) + hp * 32 + lane;
+        float* xb = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + BAR_BYTES) + hp * (2 * 32 * 32);
+        int chunk = 0;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BNT; c0 += 32, ++chunk) {
+          if (c0 >= t_valid) break;                 // uniform over the four warps
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c0, r);
+          tmem_ld_wait();
+          float* buf = xb + (chunk & 1) * (32 * 32);
+          // The gate warp finishes token columns 0-15 of the chunk and the up warp columns 16-31, so
+          // each hands the other the 16 values it does not finish itself.
+          if (q >= 2) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) buf[j * 32 + lane] = __uint_as_float(r[j]);
+          } else {
+#pragma unroll
+            for (int j = 16; j < 32; ++j) buf[j * 32 + lane] = __uint_as_float(r[j]);
+          }
+          // pair barrier (ids 1 and 2): this chunk's values are visible to the partner warp, and the
+          // partner has finished reading the buffer written two chunks ago
+          asm volatile("bar.sync %0, 64;" ::"r"(1 + hp) : "memory");
+          if (n < p.N) {
+            if (q >= 2) {        // up warp: columns 16-31, gate values from the partner
+              __nv_bfloat16* yp = p.Y + (size_t)(t0 + c0 + 16) * p.ldy + n;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (c0 + 16 + j < t_valid) {
+                  const float gv = buf[(16 + j) * 32 + lane], uv = __uint_as_float(r[16 + j]);
+                  yp[(size_t)j * p.ldy] = __float2bfloat16(__fdividef(gv, 1.f + __expf(-gv)) * uv);
+                }
+              }
+            } else {             // gate warp: columns 0-15, up values from the partner
+              __nv_bfloat16* yp = p.Y + (size_t)(t0 + c0) * p.ldy + n;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (c0 + j < t_valid) {
+                  const float gv = __uint_as_float(r[j]), uv = buf[j * 32 + lane];
+                  yp[(size_t)j * p.ldy] = __float2bfloat16(__fdividef(gv, 1.f + __expf(-gv)) * uv);
+                }
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0));
+        continue;
+      }
+      const int n = n_pair * (2 * BM) + (int)rank * BM + row;
       const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < BNT; c0 += 32) {
@@ -286,21 +353,52 @@ struct MapHash {
   }
 };
 
-// tensor map of a row-major bf16 matrix with a 128-row x 64-column box (both operands use it)
-static int operand_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride_bytes) {
+// tensor map of a row-major bf16 matrix with a box_rows x 64-column box
+static int operand_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t stride_bytes,
+                       uint32_t box_rows = BM) {
   static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
   static std::mutex mu;
-  MapKey key{ptr, rows, cols, stride_bytes};
+  MapKey key{ptr, rows, cols | ((uint64_t)box_rows << 48), stride_bytes};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
     *out = it->second;
     return 0;
   }
-  int rc = b200_make_tmap_2d(out, ptr, 2, rows, cols, stride_bytes, BM, BK);
+  int rc = b200_make_tmap_2d(out, ptr, 2, rows, cols, stride_bytes, box_rows, BK);
   if (rc != 0) return rc;
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, *out);
+  return 0;
+}
+
+// persistent grid: exactly as many SM pairs as can be resident at once (a cluster needs both SMs of a
+// pair, so this can be fewer than num_sms / 2)
+template <bool SWIGLU>
+static int launch_pairs(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int num_sms,
+                        cudaStream_t stream) {
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_2sm_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (num_sms / 2));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_2sm_kernel<SWIGLU>, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = num_sms / 2;
+    }
+    max_pairs = n;
+  }
+  const int total = p.n_pairs * p.t_tiles;
+  int pairs = max_pairs < num_sms / 2 ? max_pairs : num_sms / 2;
+  if (pairs > total) pairs = total;
+  if (pairs < 1) pairs = 1;
+  B200_CUDA_CHECK(launch_pdl(gemm_bf16_2sm_kernel<SWIGLU>, dim3(2 * pairs), dim3(THREADS), SMEM, stream, tmW, tmX,
+                             p));
+  B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
 
@@ -332,31 +430,32 @@ extern "C" int b200_gemm_bf16_2sm(const void* X, const void* W, void* Y, const v
   if (rc) return rc;
   rc = operand_map(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx * 2);
   if (rc) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    attr_set = true;
+  return launch_pairs<false>(tmW, tmX, p, num_sms, stream);
+}
+
+// Y[T, I] = silu(X * W[0:I]^T) * (X * W[I:2I]^T); W [2I, K] row stride ldw.
+extern "C" int b200_gemm_bf16_swiglu_2sm(const void* X, const void* W, void* Y, int T, int I, int K, int ldx,
+                                         int ldw, int ldy, int* status, int num_sms, cudaStream_t stream) {
+  using namespace b200;
+  using namespace b200::g2;
+  if (T <= 0 || I <= 0 || K <= 0) return 0;
+  if (K % 8 || ldx % 8 || ldw % 8) {
+    b200_set_last_error("gemm_swiglu_2sm: K and row strides must be multiples of 8 elements", __FILE__, __LINE__);
+    return -3;
   }
-  const int total = p.n_pairs * p.t_tiles;
-  // persistent grid: exactly as many SM pairs as can be resident at once (a cluster needs both SMs of
-  // a pair, so this can be fewer than num_sms / 2)
-  static int max_pairs = 0;
-  if (max_pairs == 0) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * (num_sms / 2));
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = SMEM;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_2sm_kernel, &cfg) != cudaSuccess || n < 1) {
-      cudaGetLastError();
-      n = num_sms / 2;
-    }
-    max_pairs = n;
-  }
-  int pairs = max_pairs < num_sms / 2 ? max_pairs : num_sms / 2;
-  if (pairs > total) pairs = total;
-  if (pairs < 1) pairs = 1;
-  B200_CUDA_CHECK(launch_pdl(gemm_bf16_2sm_kernel, dim3(2 * pairs), dim3(THREADS), SMEM, stream, tmW, tmX, p));
-  B200_CUDA_CHECK(cudaGetLastError());
-  return 0;
+  Params p;
+  memset(&p, 0, sizeof(p));
+  p.Y = reinterpret_cast<__nv_bfloat16*>(Y);
+  p.status = status;
+  p.T = T; p.N = I; p.K = K; p.ldy = ldy;
+  p.n_pairs = (I + BM - 1) / BM;                 // a pair produces 2 x 64 output rows
+  p.t_tiles = (T + BNT - 1) / BNT;
+  p.kb_total = (K + BK - 1) / BK;
+  p.up_row_off = I;
+  CUtensorMap tmW, tmX;
+  int rc = operand_map(&tmW, W, (uint64_t)2 * I, (uint64_t)K, (uint64_t)ldw * 2, BM / 2);
+  if (rc) return rc;
+  rc = operand_map(&tmX, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx * 2);
+  if (rc) return rc;
+  return launch_pairs<true>(tmW, tmX, p, num_sms, stream);
 }

@@ -72,8 +72,8 @@ _decl("B200_TOKEN_BUCKET_LINEAR", int, 0, "if >0, add linear token buckets with 
 _decl("B200_MIN_NUM_SEQS", int, 8, "smallest request bucket")
 _decl("B200_GEMM_IMPL", str, "tcgen05", "dense GEMM implementation",
       choices=("tcgen05", "cublas"))
-_decl("B200_GEMM_2SM_MIN_T", int, 0,
-      "token count from which the dense GEMM runs on the two-SM (cta_group::2) kernel; 0 = never")
+_decl("B200_GEMM_2SM_MIN_T", int, 1024,
+      "token count from which the dense and SwiGLU GEMMs run on the two-SM (cta_group::2) kernel; 0 = never")
 _decl("B200_ATTN_PREFILL_IMPL", str, "tc", "prefill attention kernel: tcgen05 (head_dim 128) or legacy mma.sync",
       choices=("tc", "mma"))
 _decl("B200_ATTN_SPLIT_KV", int, 0, "force the decode split-KV factor (0 = heuristic)")

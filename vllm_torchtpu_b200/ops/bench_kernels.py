@@ -213,6 +213,30 @@ def bench_decode_layer(reqs, ctx, layers=8, parts="all", iters=10, H=4096, I=143
             "status": cuda.check_status()}
 
 
+def bench_gemm_swiglu(T, I, K, iters=20, impl="tcgen05") -> dict:
+    """silu(x Wg^T) * (x Wu^T) with W = [2I, K]; 'cublas' is torch.matmul followed by an eager activation."""
+    from . import cuda
+    pk, tag = peaks()
+    _select_gemm_impl(impl)
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    w = (torch.randn(2 * I, K, device="cuda") * 0.05).bfloat16()
+    y = torch.empty(T, I, device="cuda", dtype=torch.bfloat16)
+    if impl in ("tcgen05", "2sm"):
+        fn = lambda: cuda.gemm_swiglu(x, w, out=y)
+    else:
+        def fn():
+            gu = torch.matmul(x, w.t())
+            torch.mul(torch.nn.functional.silu(gu[:, :I]), gu[:, I:], out=y)
+    ms = time_fn(fn, iters)
+    gu = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    err = float((y.float() - want).abs().max() / want.abs().max())
+    tf = 4.0 * T * I * K / ms / 1e9
+    return {"op": "gemm_swiglu", "impl": impl, "T": T, "I": I, "K": K, "ms": round(ms, 4), "tflops": round(tf, 1),
+            "frac_of_bf16_peak": round(tf / pk["bf16_tflops"], 3), "peaks": tag, "rel_err": err,
+            "status": cuda.check_status()}
+
+
 def bench_gemm_sustained(T, N, K, seconds=3.0, impl="tcgen05") -> dict:
     """The same GEMM launched back to back for ``seconds`` (under the board power cap the clocks
     settle below the burst value): average TFLOP/s over the whole run, with distinct weights cycled
@@ -260,7 +284,7 @@ LLAMA8B_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill", "decode-layer", "all"])
+    ap.add_argument("what", choices=["gemm", "gemm-swiglu", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill", "decode-layer", "all"])
     ap.add_argument("--T", type=int, default=64)
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
@@ -284,6 +308,8 @@ def main():
                     continue
                 for impl in ("tcgen05", "cublas"):
                     print(json.dumps(bench_gemm(T, N, K, max(5, a.iters // 2), impl, check=(T <= 1024))))
+    if a.what == "gemm-swiglu":
+        print(json.dumps(bench_gemm_swiglu(a.T, a.N, a.K, a.iters, a.impl)))
     if a.what == "gemm-sustained":
         for impl in a.impls.split(","):
             print(json.dumps(bench_gemm_sustained(a.T, a.N, a.K, 3.0, impl)))

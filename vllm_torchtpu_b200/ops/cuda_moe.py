@@ -5,6 +5,7 @@ from ctypes import c_float, c_int, c_void_p
 
 import torch
 
+from .. import envs
 from . import count_launch
 from . import cuda as _c
 
@@ -21,6 +22,12 @@ def gemm_swiglu(x, w, out=None):
     if T == 0:
         return y
     ws = _c.Workspace.get(x.device)
+    if 0 < envs.B200_GEMM_2SM_MIN_T <= T:
+        _c._check(_c.lib().b200_gemm_bf16_swiglu_2sm(
+            _c._p(x2), _c._p(w), _c._p(y), c_int(T), c_int(I), c_int(K), c_int(x2.stride(0)), c_int(w.stride(0)),
+            c_int(y.stride(0)), _c._p(ws.status), c_int(_c._sms), _c._stream()), "gemm_swiglu_2sm")
+        count_launch()
+        return y
     _c._check(_c.lib().b200_gemm_bf16_swiglu(
         _c._p(x2), _c._p(w), _c._p(y), c_int(T), c_int(I), c_int(K), c_int(x2.stride(0)), c_int(w.stride(0)),
         c_int(y.stride(0)), _c._p(ws.status), c_int(_c._sms), _c._stream()), "gemm_swiglu")
