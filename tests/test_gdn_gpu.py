@@ -37,3 +37,26 @@ def test_gdn_forward_two_steps(Hk, Hv, dk, dv):
         err = (got.float() - want.float()).abs().max().item()
         assert err <= 3e-2 * want.float().abs().max().item() + 1e-2, err
     torch.testing.assert_close(pools[0][1], pools[1][1], rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("Hk,Hv,dk,dv,lb", [(2, 2, 128, 128, None), (2, 4, 64, 64, -5.0), (1, 2, 32, 128, None)])
+def test_kda_forward_two_steps(Hk, Hv, dk, dv, lb):
+    """Per-channel decay (Kimi Delta Attention): both gate forms, state carried across two steps."""
+    from vllm_torchtpu_b200.ops import cuda
+    torch.manual_seed(1)
+    A_log = torch.randn(Hv, device=DEV) * 0.3
+    dt_bias = torch.randn(Hv, dk, device=DEV) * 0.3
+    pools = [torch.zeros(5, Hv, dk, dv, device=DEV) for _ in range(2)]
+    for q_lens, ctx in (([17, 1, 40], [0, 0, 0]), ([1, 1, 5], [17, 1, 40])):
+        T = sum(q_lens)
+        q = torch.randn(T, Hk, dk, device=DEV).bfloat16()
+        k = torch.randn(T, Hk, dk, device=DEV).bfloat16()
+        v = torch.randn(T, Hv, dv, device=DEV).bfloat16()
+        a = torch.randn(T, Hv, dk, device=DEV).bfloat16()
+        b = torch.randn(T, Hv, device=DEV).bfloat16()
+        meta = _meta(q_lens, ctx, [3, 0, 2])
+        got = cuda.kda_forward(q, k, v, a, b, meta, pools[0], A_log, dt_bias, lb)
+        want = g.kda_forward(q, k, v, a, b, meta, pools[1], A_log, dt_bias, lb)
+        err = (got.float() - want.float()).abs().max().item()
+        assert err <= 3e-2 * want.float().abs().max().item() + 1e-2, err
+    torch.testing.assert_close(pools[0], pools[1], rtol=3e-2, atol=3e-2)

@@ -87,3 +87,41 @@ def test_gdn_recurrence_is_chunk_invariant_and_engine_runs_hybrid():
     many = LLM("tiny-gdn", device="cpu", max_num_seqs=4, max_num_batched_tokens=16, block_size=16, init_dist=False)
     got = [o.outputs[0].token_ids for o in many.generate(_prompts(), sp)]
     assert got == want
+
+
+def test_kda_recurrence_reduces_to_gdn_and_is_chunk_invariant():
+    """Kimi Delta Attention with the same log-decay on every key channel is the gated delta rule, and
+    running a sequence in two pieces with the carried state equals running it whole."""
+    from vllm_torchtpu_b200.ops import gdn_reference as g
+    torch.manual_seed(0)
+    T, Hk, Hv, dk, dv = 12, 2, 4, 16, 8
+    q, k = torch.randn(T, Hk, dk), torch.randn(T, Hk, dk)
+    v = torch.randn(T, Hv, dv)
+    gl = -torch.rand(T, Hv)
+    beta = torch.rand(T, Hv)
+    s1, s2 = torch.zeros(Hv, dk, dv), torch.zeros(Hv, dk, dv)
+    o_gdn = g.gated_delta_rule(q, k, v, gl, beta, s1)
+    o_kda = g.kda_rule(q, k, v, gl[:, :, None].expand(T, Hv, dk).contiguous(), beta, s2)
+    torch.testing.assert_close(o_kda, o_gdn, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(s1, s2, rtol=1e-4, atol=1e-4)
+    gk = -torch.rand(T, Hv, dk)
+    whole = torch.zeros(Hv, dk, dv)
+    o_whole = g.kda_rule(q, k, v, gk, beta, whole)
+    part = torch.zeros(Hv, dk, dv)
+    o_a = g.kda_rule(q[:5], k[:5], v[:5], gk[:5], beta[:5], part)
+    o_b = g.kda_rule(q[5:], k[5:], v[5:], gk[5:], beta[5:], part)
+    torch.testing.assert_close(torch.cat([o_a, o_b]), o_whole, rtol=1e-5, atol=1e-5)
+    # bounded gate form stays inside [lower_bound, 0]
+    gb = g.kda_gate(torch.randn(T, Hv, dk), torch.zeros(Hv), torch.zeros(Hv, dk), lower_bound=-5.0)
+    assert float(gb.min()) >= -5.0 and float(gb.max()) <= 0.0
+
+
+def test_kimi_linear_hybrid_engine_is_chunk_and_batch_invariant():
+    """KDA layers (conv window + per-channel-decay state in slot pools) next to full attention: chunked
+    prefill and batching leave the greedy tokens unchanged."""
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    one = LLM("tiny-kda", device="cpu", max_num_seqs=4, max_num_batched_tokens=256, block_size=16, init_dist=False)
+    want = [one.generate([p], sp)[0].outputs[0].token_ids for p in _prompts()]
+    many = LLM("tiny-kda", device="cpu", max_num_seqs=4, max_num_batched_tokens=16, block_size=16, init_dist=False)
+    got = [o.outputs[0].token_ids for o in many.generate(_prompts(), sp)]
+    assert got == want

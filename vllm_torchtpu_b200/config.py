@@ -81,6 +81,8 @@ class ModelConfig:
     gdn_head_k_dim: int = 0
     gdn_head_v_dim: int = 0
     gdn_conv_kernel: int = 4
+    kda_gate_rank: int = 0               # Kimi Delta Attention: rank of the gate projections (0 = head dim)
+    kda_gate_lower_bound: Optional[float] = None   # floor of the per-channel log-decay (None = unbounded)
     # quantisation
     quantization: Optional[str] = None   # None | fp8 | fp8_block | int8 | mxfp4 | nvfp4 | online_fp8
     weight_block_size: tuple = (128, 128)
@@ -176,6 +178,21 @@ class ModelConfig:
             mc.gdn_head_k_dim = cfg.get("linear_key_head_dim", 128)
             mc.gdn_head_v_dim = cfg.get("linear_value_head_dim", 128)
             mc.gdn_conv_kernel = cfg.get("linear_conv_kernel_dim", 4)
+        elif arch.startswith("KimiLinear"):
+            la = cfg.get("linear_attn_config") or {}
+            mc.architecture = "kimi_linear"
+            kda_layers = la.get("kda_layers") or []
+            full_layers = la.get("full_attn_layers") or []
+            mc.full_attention_interval = (full_layers[0] if full_layers else 4)
+            mc.gdn_num_k_heads = mc.gdn_num_v_heads = la.get("num_heads", mc.num_q_heads)
+            mc.gdn_head_k_dim = mc.gdn_head_v_dim = la.get("head_dim", 128)
+            mc.gdn_conv_kernel = la.get("short_conv_kernel_size", 4)
+            mc.kda_gate_rank = la.get("head_dim", 128)
+            mc.num_experts = cfg.get("num_experts", 0)
+            mc.num_experts_per_tok = cfg.get("num_experts_per_token", cfg.get("num_experts_per_tok", 0))
+            mc.moe_intermediate_size = cfg.get("moe_intermediate_size", 0)
+            mc.num_shared_experts = cfg.get("num_shared_experts", 0)
+            del kda_layers
         elif arch.startswith("Qwen3"):
             mc.architecture, mc.qk_norm = "llama", True
         elif arch.startswith(("DeepseekV3", "DeepseekV2", "DeepseekV32")):
@@ -240,6 +257,10 @@ def model_preset(name: str) -> ModelConfig:
                        moe_n_group=2, moe_topk_group=1, moe_routed_scaling=2.5,
                        q_lora_rank=96, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16,
                        v_head_dim=32, rope_interleaved=True, max_model_len=256)
+    if n in ("tiny-kda",):
+        return _preset(name="tiny-kda", architecture="kimi_linear", dtype=torch.float32,
+                       num_layers=4, full_attention_interval=4, gdn_num_k_heads=4, gdn_num_v_heads=4,
+                       gdn_head_k_dim=32, gdn_head_v_dim=32, kda_gate_rank=16, max_model_len=256)
     if n in ("tiny-gdn",):
         return _preset(name="tiny-gdn", architecture="qwen3_next", qk_norm=True, dtype=torch.float32,
                        num_layers=4, full_attention_interval=2, gdn_num_k_heads=2, gdn_num_v_heads=4,

@@ -18,8 +18,11 @@ def get_model_class(cfg: ModelConfig):
     if a == "qwen3_next":
         from .qwen3_next import Qwen3NextForCausalLM
         return Qwen3NextForCausalLM
+    if a == "kimi_linear":
+        from .kimi_linear import KimiLinearForCausalLM
+        return KimiLinearForCausalLM
     raise ValueError(f"no model class for architecture {a!r}")
 
 
 def supported_architectures() -> list[str]:
-    return ["llama", "qwen3_moe", "deepseek_v3", "qwen3_next"]
+    return ["llama", "qwen3_moe", "deepseek_v3", "qwen3_next", "kimi_linear"]

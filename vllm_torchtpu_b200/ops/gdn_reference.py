@@ -80,3 +80,55 @@ def gdn_forward(mixed_qkv, a, b, z_unused, meta, conv_pool, rec_pool, conv_w, A_
         out[qs:qe] = gated_delta_rule(qh.reshape(-1, Hk, dk), kh.reshape(-1, Hk, dk), vh.reshape(-1, Hv, dv),
                                       g[qs:qe], beta[qs:qe], rec_pool[slot])
     return out
+
+
+def kda_gate(a, A_log, dt_bias, lower_bound=None):
+    """Raw gate a [T, Hv, dk] -> per-channel log-decay (<= 0); A_log [Hv], dt_bias [Hv, dk]
+    (reference: src/vllm_torchtpu/kernels/gdn/v3/compute_kda.py:42-63)."""
+    af = a.float() + dt_bias.float()[None]
+    ea = torch.exp(A_log.float())[None, :, None]
+    if lower_bound is None:
+        return -ea * F.softplus(af)
+    return lower_bound * torch.sigmoid(ea * af)
+
+
+def kda_rule(q, k, v, g, beta, state):
+    """Kimi Delta Attention recurrence: as gated_delta_rule, but g [T, Hv, dk] decays every key channel
+    of the state on its own (reference: compute_kda.py:362-423).  state [Hv, dk, dv] fp32, in place."""
+    T, Hk, dk = q.shape
+    Hv, dv = v.shape[1], v.shape[2]
+    rep = Hv // Hk
+    qf = q.float()
+    kf = k.float()
+    qf = (qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + 1e-6)).repeat_interleave(rep, dim=1) * (dk ** -0.5)
+    kf = (kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)).repeat_interleave(rep, dim=1)
+    vf, gf, bf = v.float(), g.float(), beta.float()
+    out = torch.empty(T, Hv, dv, dtype=torch.float32, device=q.device)
+    S = state
+    for t in range(T):
+        S.mul_(torch.exp(gf[t])[:, :, None])
+        kv_mem = torch.einsum("hkv,hk->hv", S, kf[t])
+        u = (vf[t] - kv_mem) * bf[t][:, None]
+        S.add_(kf[t][:, :, None] * u[:, None, :])
+        out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
+    return out.to(q.dtype)
+
+
+def kda_forward(q, k, v, a, b, meta, rec_pool, A_log, dt_bias, lower_bound=None):
+    """Whole-batch driver of the KDA recurrence over a ragged batch; rec_pool [slots, Hv, dk, dv] fp32."""
+    T, Hv, dv = v.shape
+    out = torch.zeros(T, Hv, dv, dtype=v.dtype, device=v.device)
+    qsl = meta.query_start_loc.tolist()
+    sl = meta.seq_lens.tolist()
+    slots = meta.state_slots.tolist()
+    g = kda_gate(a, A_log, dt_bias, lower_bound)
+    beta = torch.sigmoid(b.float())
+    for r in range(meta.num_reqs):
+        qs, qe = qsl[r], qsl[r + 1]
+        if qe <= qs:
+            continue
+        slot = slots[r]
+        if sl[r] - (qe - qs) == 0:
+            rec_pool[slot].zero_()
+        out[qs:qe] = kda_rule(q[qs:qe], k[qs:qe], v[qs:qe], g[qs:qe], beta[qs:qe], rec_pool[slot])
+    return out
