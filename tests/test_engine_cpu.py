@@ -88,3 +88,37 @@ def test_embedding_pooling_matches_dense_hidden_states():
             torch.testing.assert_close(torch.tensor(g), want.float(), rtol=2e-3, atol=2e-3)
     unit = llm.embed(prompts[:1])[0]
     assert abs(sum(a * a for a in unit) - 1.0) < 1e-4
+
+
+@pytest.mark.parametrize("async_sched", [False, True])
+def test_sample_logprobs_min_tokens_and_prompt_logprobs(async_sched):
+    """Logprobs of sampled tokens, the on-device min_tokens mask and chunked prompt logprobs, against the
+    dense fp32 forward of the same model."""
+    from vllm_torchtpu_b200.models.reference_forward import dense_llama_logits
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, max_num_batched_tokens=16, block_size=16,
+              init_dist=False, async_scheduling=async_sched)
+    prompt = _prompts()[2]
+    base = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))[0]
+    toks = base.outputs[0].token_ids
+    # sampled-token logprobs: greedy tokens are rank 1 and head the top-k list
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True, logprobs=3))[0]
+    lps = out.outputs[0].logprobs
+    assert out.outputs[0].token_ids == toks and len(lps) == 5
+    for t, e in zip(toks, lps):
+        assert e["token_id"] == t and e["rank"] == 1 and e["top"][0][0] == t and len(e["top"]) == 3
+        assert e["logprob"] <= 0.0 and abs(e["top"][0][1] - e["logprob"]) < 1e-5
+    # stop token = the first greedy token: one token without min_tokens, masked until min_tokens with it
+    stop = SamplingParams(temperature=0.0, max_tokens=8, stop_token_ids=[toks[0]])
+    assert llm.generate([prompt], stop)[0].outputs[0].token_ids == [toks[0]]
+    held = SamplingParams(temperature=0.0, max_tokens=8, stop_token_ids=[toks[0]], min_tokens=3)
+    got = llm.generate([prompt], held)[0].outputs[0].token_ids
+    assert len(got) >= 3 and toks[0] not in got[:3]
+    # prompt logprobs over a prefill that takes several chunks (16 tokens per step)
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=1, prompt_logprobs=2))[0]
+    plp = out.prompt_logprobs
+    assert len(plp) == len(prompt) and plp[0] is None
+    want = torch.log_softmax(dense_llama_logits(llm.engine.runner.model, prompt).float(), dim=-1)
+    for i in range(1, len(prompt)):
+        assert plp[i]["token_id"] == prompt[i]
+        assert abs(plp[i]["logprob"] - float(want[i - 1, prompt[i]])) < 2e-3, i
+        assert len(plp[i]["top"]) == 2

@@ -134,3 +134,29 @@ def test_hybrid_linear_attention_models_on_gpu(arch, extra):
     assert same >= len(prompts) - 1, (got, want)      # bf16 ties may flip one continuation
     from vllm_torchtpu_b200.ops import cuda
     assert cuda.check_status() == 0
+
+
+def test_logprobs_min_tokens_prompt_logprobs_on_gpu():
+    """The logprob kernel, the min_tokens mask and chunked prompt logprobs on the device path (these
+    steps leave the CUDA graphs), against the dense fp32 forward."""
+    from vllm_torchtpu_b200.models.reference_forward import dense_llama_logits
+    llm = LLM(_cfg(), device="cuda", max_num_seqs=8, max_num_batched_tokens=64, num_gpu_blocks_override=512,
+              init_dist=False)
+    prompt = _prompts()[4]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    toks = llm.generate([prompt], sp)[0].outputs[0].token_ids
+    out = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=4,
+                                                prompt_logprobs=1))[0]
+    assert out.outputs[0].token_ids == toks
+    for t, e in zip(toks, out.outputs[0].logprobs):
+        assert e["token_id"] == t and e["rank"] == 1 and e["top"][0][0] == t and e["logprob"] <= 0.0
+    want = torch.log_softmax(dense_llama_logits(llm.engine.runner.model, prompt).float(), dim=-1)
+    plp = out.prompt_logprobs
+    assert len(plp) == len(prompt) and plp[0] is None
+    err = max(abs(plp[i]["logprob"] - float(want[i - 1, prompt[i]])) for i in range(1, len(prompt)))
+    assert err < 0.08, err
+    held = SamplingParams(temperature=0.0, max_tokens=8, stop_token_ids=[toks[0]], min_tokens=3)
+    got = llm.generate([prompt], held)[0].outputs[0].token_ids
+    assert len(got) >= 3 and toks[0] not in got[:3]
+    from vllm_torchtpu_b200.ops import cuda
+    assert cuda.check_status() == 0

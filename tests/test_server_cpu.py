@@ -41,3 +41,15 @@ def test_streaming_and_chat(client):
 def test_bad_requests(client):
     assert client.post("/v1/completions", json={"prompt": [1, 2], "seed": 3}).status_code == 400
     assert client.post("/v1/completions", json={"prompt": [1] * 5000, "max_tokens": 4}).status_code == 500
+
+
+def test_completion_logprobs_and_prompt_logprobs(client):
+    r = client.post("/v1/completions", json={"prompt": [1, 2, 3, 4, 5, 6], "max_tokens": 3, "temperature": 0,
+                                             "ignore_eos": True, "logprobs": 2, "prompt_logprobs": 1})
+    assert r.status_code == 200
+    ch = r.json()["choices"][0]
+    lp = ch["logprobs"]
+    assert lp["token_ids"] == ch["token_ids"] and len(lp["token_logprobs"]) == 3
+    assert all(len(t) == 2 for t in lp["top_logprobs"]) and all(v <= 0 for v in lp["token_logprobs"])
+    plp = ch["prompt_logprobs"]
+    assert len(plp) == 6 and plp[0] is None and [e["token_id"] for e in plp[1:]] == [2, 3, 4, 5, 6]

@@ -172,7 +172,16 @@ class LLMEngine:
         spec_next = None
         if self.spec is not None and sampled:
             spec_next = self.spec.propose(out, sampled)
-        finished = self.scheduler.update_from_output(out, sampled, spec_next)
+        sample_lp, prompt_lp = res.take_logprobs()
+        if prompt_lp:
+            by_id = {s.request.request_id: s.request for s in out.scheduled}
+            for rid, ents in prompt_lp.items():
+                req = by_id.get(rid)
+                if req is not None:
+                    if not req.prompt_logprobs:
+                        req.prompt_logprobs = [None]          # the first prompt token has no prefix
+                    req.prompt_logprobs.extend(ents)
+        finished = self.scheduler.update_from_output(out, sampled, spec_next, logprobs=sample_lp)
         for r in finished:
             if r.sampling_params.pooling:
                 r.pooled = self.runner.take_pooled(r.request_id)

@@ -45,6 +45,7 @@ class Request:
     error: Optional[str] = None
     pooled: Optional[list] = None          # pooled final hidden state (pooling requests)
     logprobs: list = field(default_factory=list)
+    prompt_logprobs: list = field(default_factory=list)
     num_preemptions: int = 0
     # tokens sampled on the device that the host has not seen yet (async scheduling)
     num_output_placeholders: int = 0

@@ -26,6 +26,8 @@ class StreamItem:
     error: Optional[str] = None
     num_prompt_tokens: int = 0
     num_cached_tokens: int = 0
+    logprobs: Optional[list] = None          # entries of new_token_ids when the request asked for them
+    prompt_logprobs: Optional[list] = None   # with the final item
 
 
 class AsyncEngine:
@@ -76,9 +78,11 @@ class AsyncEngine:
                         self.metrics["ttft_sum"] += req.first_token_time - req.arrival_time
                         self.metrics["ttft_n"] += 1
                     self.metrics["output_tokens"] += len(new)
+                    lps = req.logprobs[sent:sent + len(new)] if req.logprobs else None
                     self._emit(StreamItem(rid, list(new), done, req.status.value if done else None,
                                           req.kv_transfer_params if done else None, req.error,
-                                          req.num_prompt_tokens, req.num_cached_tokens))
+                                          req.num_prompt_tokens, req.num_cached_tokens, lps,
+                                          (req.prompt_logprobs or None) if done else None))
                     if done:
                         eng.scheduler.requests.pop(rid, None)
             del finished

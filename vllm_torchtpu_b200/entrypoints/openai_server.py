@@ -18,13 +18,29 @@ from ..sampling_params import SamplingParams
 from .async_engine import AsyncEngine
 
 
+def _logprobs_from_body(body: dict):
+    """Completions: ``logprobs`` = number of alternatives.  Chat: ``logprobs`` is a flag and
+    ``top_logprobs`` the number."""
+    lp = body.get("logprobs")
+    if isinstance(lp, bool):
+        return int(body.get("top_logprobs") or 0) if lp else None
+    return lp
+
+
+def _logprobs_payload(token_ids: list, entries: list, decode) -> dict:
+    return {"tokens": [decode([t]) for t in token_ids], "token_ids": list(token_ids),
+            "token_logprobs": [e["logprob"] for e in entries],
+            "top_logprobs": [{str(i): v for i, v in e["top"]} for e in entries]}
+
+
 def _sampling_from_body(body: dict) -> SamplingParams:
     return SamplingParams(
         temperature=float(body.get("temperature", 1.0) if body.get("temperature") is not None else 1.0),
         top_k=int(body.get("top_k", 0) or 0), top_p=float(body.get("top_p", 1.0) or 1.0),
         max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
         min_tokens=int(body.get("min_tokens", 0) or 0), ignore_eos=bool(body.get("ignore_eos", False)),
-        stop_token_ids=list(body.get("stop_token_ids") or []), logprobs=body.get("logprobs"),
+        stop_token_ids=list(body.get("stop_token_ids") or []), logprobs=_logprobs_from_body(body),
+        prompt_logprobs=body.get("prompt_logprobs"),
         seed=body.get("seed"), structured=body.get("structured_outputs") or body.get("guided") or None)
 
 
@@ -96,18 +112,28 @@ def build_app(engine, model_name: str, tokenizer=None):
                         break
                     payload = chunk_payload(decode(item.new_token_ids), item.finish_reason,
                                             item if item.finished else None)
+                    if item.logprobs:
+                        payload["choices"][0]["logprobs"] = _logprobs_payload(item.new_token_ids, item.logprobs,
+                                                                              decode)
                     yield f"data: {json.dumps(payload)}\n\n"
                 yield "data: [DONE]\n\n"
             return StreamingResponse(sse(), media_type="text/event-stream")
-        toks, last = [], None
+        toks, lps, last = [], [], None
         async for item in aeng.generate(rid, prompt_ids, sp, kvp):
             toks += item.new_token_ids
+            lps += item.logprobs or []
             last = item
         if last is not None and last.error:
             raise HTTPException(500, last.error)
         final_item_tokens[0] = len(toks)
         payload = chunk_payload(decode(toks), last.finish_reason if last else None, last)
         payload["choices"][0]["token_ids"] = toks
+        if lps:
+            payload["choices"][0]["logprobs"] = _logprobs_payload(toks, lps, decode)
+        if last is not None and last.prompt_logprobs:
+            payload["choices"][0]["prompt_logprobs"] = [
+                None if e is None else {"token_id": e["token_id"], "logprob": e["logprob"], "rank": e["rank"]}
+                for e in last.prompt_logprobs]
         return JSONResponse(payload)
 
     @app.post("/v1/completions")

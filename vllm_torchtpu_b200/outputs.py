@@ -26,6 +26,7 @@ class RequestOutput:
     kv_transfer_params: Optional[dict] = None
     error: Optional[str] = None
     pooled: Optional[list] = None          # embedding of the prompt for pooling requests
+    prompt_logprobs: Optional[list] = None  # [None, entry, ...] per prompt token when requested
 
     @staticmethod
     def from_request(req, detokenize=None) -> "RequestOutput":
@@ -37,4 +38,4 @@ class RequestOutput:
             [CompletionOutput(0, list(req.output_token_ids), text, req.status.value,
                               req.logprobs or None)],
             req.status.finished, req.num_cached_tokens, ttft, lat, req.kv_transfer_params, req.error,
-            getattr(req, "pooled", None))
+            getattr(req, "pooled", None), getattr(req, "prompt_logprobs", None) or None)

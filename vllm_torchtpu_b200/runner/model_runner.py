@@ -46,6 +46,30 @@ class StepResult:
     num_reqs: int
     d2h_bytes: int = 0
     extra: dict = field(default_factory=dict)
+    lp: Optional[dict] = None       # sample / prompt logprob tensors of the step (device or host)
+
+    def take_logprobs(self):
+        """After ``get()``: ({request_id: entry}, {request_id: [entry per prompt position]}).  An entry is
+        {"token_id", "logprob", "rank", "top": [(token_id, logprob), ...]}."""
+        if not self.lp:
+            return None, None
+
+        def entries(tok, pack, k):
+            tok_lp, top_lp, top_id, rank = (t.cpu().tolist() for t in pack)
+            return [{"token_id": int(t), "logprob": float(lp), "rank": int(r),
+                     "top": [(int(i), float(v)) for i, v in zip(ids[:k], vals[:k])]}
+                    for t, lp, vals, ids, r in zip(tok, tok_lp, top_lp, top_id, rank)]
+        sample, prompt = {}, {}
+        if self.lp.get("sample") is not None:
+            rows, ks, pack = self.lp["sample"]
+            toks = self.tokens_host[: self.num_reqs].tolist()
+            ent = entries([toks[i] for i in rows], pack, max(ks))
+            for i, k, e in zip(rows, ks, ent):
+                e["top"] = e["top"][:k]
+                sample[self.req_ids[i]] = e
+        for rid, targets, k, pack in self.lp.get("prompt", []):
+            prompt[rid] = entries(targets, pack, k)
+        return sample, prompt
 
     def get(self) -> dict:
         if self.event is not None:
@@ -96,6 +120,7 @@ class ModelRunner:
         self.structured = None           # StructuredDecodingManager when a request asks for it
         self._step_bitmask = None
         self.timing_events = None        # (start event, end event, decode-only?, tokens) per step when enabled
+        self._step_extras = None         # logprob / min_tokens work of the current step (see _plan_extras)
         self._pool_plan = None           # pooling requests of the current step: (id, row lo, row hi, mode, last chunk)
         self._pool_acc: dict = {}        # request id -> [sum or last row, count]
         if envs.B200_STAGE_TIMING and self.is_cuda:
@@ -300,11 +325,14 @@ class ModelRunner:
         hidden, residual = self.model.forward(ids, meta, self.kv_caches, hidden=hidden0)
         if self._pool_plan:
             self._pool(hidden, residual)
+        ex = self._step_extras
+        if ex is not None and ex["prompt"]:
+            self._prompt_logprobs(hidden, residual, ex)
         rows = self._select_rows(hidden, residual, meta.logits_indices)
         h = self.model.finalize(*rows)
         st = get_state()
         if (self.is_cuda and all_greedy and st.tp.size > 1 and envs.B200_GREEDY_TOP_TOKENS
-                and self.model.vocab_shard is not None):
+                and self.model.vocab_shard is not None and ex is None):
             # vocab-parallel arg-max: exchange (value, index) pairs instead of gathering the logits
             from ..ops import cuda_tp
             from ..parallel.communicator import get_tp_comm
@@ -319,6 +347,12 @@ class ModelRunner:
             from ..structured import apply_token_bitmask
             bm, rows = self._step_bitmask
             apply_token_bitmask(logits, bm.to(logits.device), rows.to(logits.device))
+        if ex is not None and ex["mask_rows"]:
+            # min_tokens: end-of-sequence and stop tokens cannot be sampled yet
+            # (reference: src/vllm_torchtpu/runner/min_tokens.py)
+            r_i = torch.tensor(ex["mask_rows"], dtype=torch.long, device=logits.device)
+            t_i = torch.tensor(ex["mask_ids"], dtype=torch.long, device=logits.device)
+            logits[r_i, t_i] = float("-inf")
         if self.is_cuda:
             # noise comes from Philox inside the kernel, keyed by (seed, step counter in device memory)
             tokens = ops.cuda_ops().sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
@@ -332,7 +366,69 @@ class ModelRunner:
                                 dv("top_p", R, torch.float32), uniform, all_greedy).to(torch.int32)
         if not verify:
             self._store_last_tokens(tokens, dv("batch_slots", n_req_pad))
+        if ex is not None and ex["lp_rows"]:
+            idx = torch.tensor(ex["lp_rows"], dtype=torch.long, device=logits.device)
+            ex["out"]["sample"] = (ex["lp_rows"], ex["lp_ks"],
+                                   self._gather_logprobs(logits[idx], tokens[idx], max(1, max(ex["lp_ks"]))))
         return tokens, logits
+
+    def _gather_logprobs(self, logits, token_ids, k: int):
+        if self.is_cuda:
+            return ops.cuda_ops().gather_logprobs(logits.contiguous(), token_ids.contiguous(), k)
+        from ..ops import reference
+        return reference.gather_logprobs(logits, token_ids.long(), k)
+
+    def _prompt_logprobs(self, hidden, residual, ex, chunk: int = 1024) -> None:
+        """Log-probability of every prompt token given its prefix, for the prompt rows of this step, in
+        row chunks so that the [rows, vocab] logits stay bounded
+        (reference: src/vllm_torchtpu/runner/prompt_logprobs.py)."""
+        for rid, lo, hi, targets, k in ex["prompt"]:
+            packs = []
+            for a in range(lo, hi, chunk):
+                b = min(hi, a + chunk)
+                idx = torch.arange(a, b, dtype=torch.int32, device=hidden.device)
+                h = self.model.finalize(*self._select_rows(hidden, residual, idx))
+                logits = self.model.compute_logits(h)
+                tg = torch.tensor(targets[a - lo:b - lo], dtype=torch.int32, device=hidden.device)
+                packs.append(self._gather_logprobs(logits, tg, max(1, k)))
+            pack = tuple(torch.cat([p[j] for p in packs]) for j in range(4))
+            ex["out"].setdefault("prompt", []).append((rid, targets, k, pack))
+
+    def _plan_extras(self, p):
+        """Per-step work outside the plain sample: logprobs of the sampled tokens, the min_tokens mask and
+        prompt logprobs.  Steps that need any of it run eagerly."""
+        if p.get("has_spec") or get_state().pp.size > 1:
+            return None
+        lp_rows, lp_ks, mask_rows, mask_ids, prompt = [], [], [], [], []
+        qsl = p["qsl_np"]
+        for i, s in enumerate(p["scheds"]):
+            req = s.request
+            sp = req.sampling_params
+            if s.samples:
+                if sp.logprobs is not None:
+                    lp_rows.append(i)
+                    lp_ks.append(int(sp.logprobs))
+                # tokens produced before this step's sample (placeholders count steps still in flight,
+                # this one included)
+                n_out = len(req.output_token_ids) + max(0, req.num_output_placeholders - 1)
+                if sp.min_tokens and n_out < sp.min_tokens:
+                    ids = list(sp.stop_token_ids)
+                    if req.eos_token_id is not None and not sp.ignore_eos:
+                        ids.append(req.eos_token_id)
+                    for t in ids:
+                        if 0 <= t < self.mcfg.vocab_size:
+                            mask_rows.append(i)
+                            mask_ids.append(int(t))
+            if sp.prompt_logprobs is not None and s.start < req.num_prompt_tokens:
+                lo = int(qsl[i])
+                n_rows = min(int(qsl[i + 1]) - lo, req.num_prompt_tokens - s.start)
+                targets = list(req.prompt_token_ids[s.start + 1: s.start + n_rows + 1])
+                if targets:
+                    prompt.append((req.request_id, lo, lo + len(targets), targets, int(sp.prompt_logprobs)))
+        if not (lp_rows or mask_rows or prompt):
+            return None
+        return {"lp_rows": lp_rows, "lp_ks": lp_ks, "mask_rows": mask_rows, "mask_ids": mask_ids,
+                "prompt": prompt, "out": {}}
 
     def _pp_handoff(self):
         if getattr(self, "_pp", None) is None:
@@ -509,8 +605,10 @@ class ModelRunner:
             bm, rows = self.structured.build_bitmask([s.request.request_id for s in p["scheds"]])
             if bm is not None:
                 self._step_bitmask = (bm, rows)
+        self._step_extras = self._plan_extras(p)
         use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
                      and p["T_pad"] == p["R_pad"] and envs.B200_CUDA_GRAPHS and self._step_bitmask is None and lora_idx is None
+                     and self._step_extras is None
                      and get_state().pp.size == 1)          # pipeline stages hand off through host threads
         if use_graph:
             key = (R, p["all_greedy"])
@@ -547,6 +645,9 @@ class ModelRunner:
         self.stats["d2h_bytes"] += rows * 4
         res = StepResult([s.request.request_id for s in p["scheds"]], [s.samples for s in p["scheds"]],
                          host, ev, n, rows * 4)
+        if self._step_extras is not None:
+            res.lp = self._step_extras["out"]
+            self._step_extras = None
         if p.get("has_spec"):
             res.extra = {"spec_k": p["spec_k"], "drafts": [list(s.spec_token_ids) for s in p["scheds"]],
                          "stats": self.stats}
