@@ -10,8 +10,9 @@
 //
 // Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation and (leader CTA
 // only) the MMA issuer, warps 2-5 = epilogue.  Synchronisation across the pair:
-//   * full[s]   lives in the leader (cluster rank 0); both producers' TMA loads complete their
-//               bytes on it (cp.async.bulk.tensor ... .cta_group::2, no cluster multicast);
+//   * full[s]   lives in the leader (cluster rank 0); both producers' tensor loads complete their
+//               bytes on it (the .cta_group::2 form lets a load signal the peer CTA's barrier; every
+//               CTA fetches only its own operand halves, nothing is broadcast);
 //   * empty[s]  lives in each CTA; the leader's tcgen05.commit arrives on both (commit multicast);
 //   * tfull[a]  lives in each CTA, same commit multicast;
 //   * tempty[a] lives in the leader; the four epilogue warps of both CTAs arrive on it.
@@ -74,7 +75,7 @@ __device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols)
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 // 2D tiled load into this CTA's shared memory whose byte count completes on a barrier given by its
-// shared::cluster address (the leader's); no multicast: each CTA fetches only its own operand halves
+// shared::cluster address (the leader's); each CTA fetches only its own operand halves
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr,
                                                  int x, int y) {
   asm volatile(
