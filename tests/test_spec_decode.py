@@ -1,5 +1,6 @@
 """Speculative decoding pieces on CPU: drafter, rejection sampling laws, engine equivalence."""
 import numpy as np
+import pytest
 import torch
 
 from vllm_torchtpu_b200 import SamplingParams
@@ -47,3 +48,51 @@ def test_engine_with_ngram_drafts_matches_plain_greedy():
     assert got == want
     assert spec.engine.spec.stats["proposed"] > 0
     assert spec.engine.runner.stats.get("spec_accepted", 0) >= 0
+
+
+def test_adaptive_verification_budget_and_prefixes():
+    """The budget maximises expected tokens per millisecond under the cost table; every request keeps a
+    prefix of its drafts; cheap rows admit more drafts than expensive rows; padding is refilled."""
+    from vllm_torchtpu_b200.spec_decode.adaptive_verification import AdaptiveVerificationManager, StepCostTable
+    conf = {"a": [0.9, 0.9, 0.9], "b": [0.5, 0.2, 0.9], "c": [0.05, 0.9, 0.9]}
+    flat = AdaptiveVerificationManager(StepCostTable([(1, 1.0), (64, 1.0)]), 3)
+    assert flat.select(conf) == {"a": 3, "b": 3, "c": 3}          # rows are free: verify everything
+    steep = AdaptiveVerificationManager(StepCostTable([(3, 1.0), (12, 10.0)]), 3)
+    keep = steep.select(conf)
+    assert keep["a"] >= keep["b"] >= keep["c"] and keep["c"] == 0 and sum(keep.values()) < 9
+    # exhaustive check of the optimum over budgets
+    surv = sorted((s for c in conf.values() for s in steep.survival(c)), reverse=True)
+    rates = [(3 + sum(surv[:b])) / steep.cost_table.cost(3 + b) for b in range(10)]
+    assert sum(keep.values()) == max(range(10), key=lambda b: rates[b])
+    grown = steep.expand(keep, conf, extra_rows=2)
+    assert sum(grown.values()) == sum(keep.values()) + 2 and all(grown[r] >= keep[r] for r in keep)
+    expect = steep.select({"a": conf["a"], "b": conf["b"]}, base_rows=3)
+    trimmed = steep.trim({"a": [1, 2, 3], "b": [4, 5, 6], "z": [7]}, conf, base_rows=3)
+    assert trimmed.get("a", []) == [1, 2, 3][: expect["a"]] and trimmed.get("b", []) == [4, 5, 6][: expect["b"]]
+    assert trimmed["z"] == [7] and "c" not in trimmed          # no confidences: drafts kept whole
+    # overhead calibration ignores stalls
+    steep.observe(3, 1.5)
+    assert 0 < steep.overhead_ms < 0.1
+    before = steep.overhead_ms
+    steep.observe(3, 100.0)
+    assert steep.overhead_ms == before
+    t = StepCostTable([(8, 1.0), (16, 2.0), (32, 6.0)])
+    assert t.cost(12) == 1.5 and t.cost(24) == 4.0 and t.cost(64) == 14.0 and t.cost(1) >= 0.0
+
+
+def test_engine_with_draft_head_and_adaptive_verification_is_lossless():
+    prompts = [np.random.RandomState(7).randint(0, 1024, size=n).tolist() for n in (9, 21)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    plain = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    want = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    spec = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False,
+               speculative_config={"method": "mtp", "num_speculative_tokens": 3,
+                                   "enable_adaptive_verification": True,
+                                   "step_cost_samples": [(1, 1.0), (4, 1.2), (16, 4.0)]})
+    got = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]
+    assert got == want
+    st = spec.engine.adaptive.stats
+    assert st["steps"] > 0 and st["verified"] <= st["proposed"]
+    with pytest.raises(ValueError):
+        LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False,
+            speculative_config={"method": "ngram", "enable_adaptive_verification": True})

@@ -68,6 +68,13 @@ class LLMEngine:
             from ..spec_decode import create_proposer
             self.spec = create_proposer(cfg, self.runner)
             num_spec = self.spec.num_speculative_tokens
+        self.adaptive = None
+        if cfg.speculative and cfg.speculative.get("enable_adaptive_verification"):
+            from ..spec_decode.adaptive_verification import (AdaptiveVerificationManager, StepCostTable,
+                                                             validate_adaptive_verification_config)
+            validate_adaptive_verification_config(cfg)
+            samples = cfg.speculative.get("step_cost_samples") or self._profile_step_costs()
+            self.adaptive = AdaptiveVerificationManager(StepCostTable(samples), num_spec)
         self.scheduler = make_scheduler(self.cfg, num_blocks,
                                         self.connector.scheduler if self.connector else None, num_spec)
         self.runner.capture_model()
@@ -129,6 +136,27 @@ class LLMEngine:
     def list_loras(self) -> list:
         return self._lora().list_adapters()
 
+    def _profile_step_costs(self) -> list:
+        """(rows, ms) of placeholder steps of a few sizes, for the adaptive verification cost table."""
+        import time
+        import torch
+        out = []
+        cap = max(8, min(self.cfg.scheduler.max_num_batched_tokens, 512))
+        for rows in sorted({8, 32, 64, 128, 256, cap}):
+            if rows > cap:
+                continue
+            times = []
+            for _ in range(3):
+                if self.runner.is_cuda:
+                    torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                self.runner.execute_dummy_batch(rows)
+                if self.runner.is_cuda:
+                    torch.cuda.synchronize()
+                times.append((time.perf_counter() - t0) * 1e3)
+            out.append((rows, sorted(times)[1]))
+        return out
+
     def abort_request(self, request_id: str) -> None:
         self.scheduler.abort_request(request_id)
 
@@ -171,7 +199,13 @@ class LLMEngine:
             self.runner.structured.accept_tokens(sampled)
         spec_next = None
         if self.spec is not None and sampled:
+            if hasattr(self.spec, "note_step"):
+                self.spec.note_step(out, res, sampled)
             spec_next = self.spec.propose(out, sampled)
+            if self.adaptive is not None and spec_next:
+                # verify only the draft prefixes that are worth their rows in the next step
+                spec_next = self.adaptive.trim(spec_next, getattr(self.spec, "last_confidences", {}),
+                                               base_rows=len(self.scheduler.running))
         sample_lp, prompt_lp = res.take_logprobs()
         if prompt_lp:
             by_id = {s.request.request_id: s.request for s in out.scheduled}

@@ -47,6 +47,7 @@ class StepResult:
     d2h_bytes: int = 0
     extra: dict = field(default_factory=dict)
     lp: Optional[dict] = None       # sample / prompt logprob tensors of the step (device or host)
+    hidden: Optional[torch.Tensor] = None   # final-norm hidden state of every sampled row (draft heads)
 
     def take_logprobs(self):
         """After ``get()``: ({request_id: entry}, {request_id: [entry per prompt position]}).  An entry is
@@ -121,6 +122,8 @@ class ModelRunner:
         self._step_bitmask = None
         self.timing_events = None        # (start event, end event, decode-only?, tokens) per step when enabled
         self._step_extras = None         # logprob / min_tokens work of the current step (see _plan_extras)
+        self.keep_hidden = False         # a draft head wants the hidden state of the sampled rows
+        self._last_h = None
         self._pool_plan = None           # pooling requests of the current step: (id, row lo, row hi, mode, last chunk)
         self._pool_acc: dict = {}        # request id -> [sum or last row, count]
         if envs.B200_STAGE_TIMING and self.is_cuda:
@@ -330,6 +333,8 @@ class ModelRunner:
             self._prompt_logprobs(hidden, residual, ex)
         rows = self._select_rows(hidden, residual, meta.logits_indices)
         h = self.model.finalize(*rows)
+        if self.keep_hidden:
+            self._last_h = h
         st = get_state()
         if (self.is_cuda and all_greedy and st.tp.size > 1 and envs.B200_GREEDY_TOP_TOKENS
                 and self.model.vocab_shard is not None and ex is None):
@@ -608,7 +613,7 @@ class ModelRunner:
         self._step_extras = self._plan_extras(p)
         use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
                      and p["T_pad"] == p["R_pad"] and envs.B200_CUDA_GRAPHS and self._step_bitmask is None and lora_idx is None
-                     and self._step_extras is None
+                     and self._step_extras is None and not self.keep_hidden
                      and get_state().pp.size == 1)          # pipeline stages hand off through host threads
         if use_graph:
             key = (R, p["all_greedy"])
@@ -645,6 +650,8 @@ class ModelRunner:
         self.stats["d2h_bytes"] += rows * 4
         res = StepResult([s.request.request_id for s in p["scheds"]], [s.samples for s in p["scheds"]],
                          host, ev, n, rows * 4)
+        if self.keep_hidden:
+            res.hidden, self._last_h = self._last_h, None
         if self._step_extras is not None:
             res.lp = self._step_extras["out"]
             self._step_extras = None
