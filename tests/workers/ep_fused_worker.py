@@ -41,6 +41,10 @@ def main():
         topk_ids = topk_ids.to(torch.int32).contiguous()
         topk_w = topk_w.float().contiguous()
         for rep in range(2):
+            # the bounded flag waits of the plane are short in tests: start every call together, so that
+            # one rank's lazy set-up (tensor maps, kernel attributes) does not run into the peers' limit
+            torch.cuda.synchronize()
+            dist.barrier()
             y = cuda.moe_experts_ep(x, w13_l, w2_l, topk_ids, topk_w, heap, E)
         torch.cuda.synchronize()
         status = cuda.check_status()
