@@ -98,3 +98,33 @@ def test_plugin_entry_points_are_declared_and_safe_without_a_gpu():
     mod, cls = plugin.PLATFORM_CLASS.rsplit(".", 1)
     import importlib
     assert hasattr(importlib.import_module(mod), cls)
+
+
+def test_export_serving_dir_roundtrip_and_validation(tmp_path):
+    """Export -> validate -> load gives the same greedy tokens; a corrupted file and a wrong format
+    version are reported."""
+    import json
+    import os
+    import numpy as np
+    from vllm_torchtpu_b200 import SamplingParams
+    from vllm_torchtpu_b200.engine.llm import LLM
+    from vllm_torchtpu_b200.entrypoints.cli import main
+    from vllm_torchtpu_b200.export import export_serving_dir, load_serving_dir, validate_serving_dir
+    src = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    prompts = [np.random.RandomState(3).randint(0, 1024, size=n).tolist() for n in (5, 19)]
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    want = [o.outputs[0].token_ids for o in src.generate(prompts, sp)]
+    d = str(tmp_path / "serving")
+    meta = export_serving_dir(src, d)
+    assert meta["plan"]["request_buckets"] and "serving_checkpoint/model.safetensors" in meta["manifest"]
+    assert validate_serving_dir(d) == [] and main(["validate-export", d]) == 0
+    dst = load_serving_dir(d, device="cpu", init_dist=False)
+    assert [o.outputs[0].token_ids for o in dst.generate(prompts, sp)] == want
+    with open(os.path.join(d, "serving_checkpoint", "config.json"), "a") as f:
+        f.write(" ")
+    assert any("config.json" in p for p in validate_serving_dir(d))
+    m = json.load(open(os.path.join(d, "metadata.json")))
+    m["format_version"] = 99
+    json.dump(m, open(os.path.join(d, "metadata.json"), "w"))
+    assert any("format_version" in p for p in validate_serving_dir(d))
+    assert main(["validate-export", d]) == 1

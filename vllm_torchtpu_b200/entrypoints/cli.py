@@ -74,6 +74,11 @@ def main(argv=None) -> int:
     p.add_argument("--host", default="0.0.0.0")
     p.add_argument("--port", type=int, default=8000)
     e = sub.add_parser("envs", help="list the environment knobs")
+    x = sub.add_parser("export", help="write a serving directory (weights, configuration, shape plan, manifest)")
+    add_engine_args(x)
+    x.add_argument("--output", required=True)
+    v = sub.add_parser("validate-export", help="check a serving directory against its manifest")
+    v.add_argument("path")
     a = ap.parse_args(argv)
 
     from .. import env_validation
@@ -86,6 +91,18 @@ def main(argv=None) -> int:
         from .. import envs
         for name, var in sorted(envs.declared().items()):
             print(f"{name:40s} {var.type.__name__:6s} default={var.default!r}  {var.doc}")
+        return 0
+    if a.cmd == "validate-export":
+        from ..export import validate_serving_dir
+        problems = validate_serving_dir(a.path)
+        for p in problems:
+            print(p)
+        print("valid" if not problems else f"{len(problems)} problem(s)")
+        return 0 if not problems else 1
+    if a.cmd == "export":
+        from ..export import export_serving_dir
+        meta = export_serving_dir(make_llm(a), a.output)
+        print(json.dumps({"output": a.output, "files": sorted(meta["manifest"])}))
         return 0
     if a.cmd == "proxy":
         from ..kv_transfer.proxy import run_proxy
