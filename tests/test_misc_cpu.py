@@ -128,3 +128,25 @@ def test_export_serving_dir_roundtrip_and_validation(tmp_path):
     json.dump(m, open(os.path.join(d, "metadata.json"), "w"))
     assert any("format_version" in p for p in validate_serving_dir(d))
     assert main(["validate-export", d]) == 1
+
+
+def test_merge_rank_traces(tmp_path):
+    import json
+    import os
+    from vllm_torchtpu_b200.tracing.merge_traces import main, merge_dir
+    for rank, skew in ((0, 0), (1, 500)):
+        d = tmp_path / f"rank_{rank}"
+        d.mkdir()
+        ev = [{"ph": "M", "name": "process_name", "pid": 7, "tid": 0, "args": {"name": "python"}},
+              {"ph": "X", "name": "barrier", "pid": 7, "tid": 1, "ts": 1000 + skew, "dur": 5},
+              {"ph": "X", "name": "step", "pid": 7, "tid": 1, "ts": 1100 + skew, "dur": 50}]
+        (d / "trace_1.json").write_text(json.dumps({"traceEvents": ev}))
+    out = str(tmp_path / "m.json")
+    info = merge_dir(str(tmp_path), out, "barrier")
+    assert info["ranks"] == [0, 1]
+    ev = json.load(open(out))["traceEvents"]
+    steps = sorted((e["pid"], e["ts"]) for e in ev if e.get("name") == "step")
+    assert steps[0][0] != steps[1][0] and steps[0][1] == steps[1][1] == 1100      # skew removed
+    names = [e["args"]["name"] for e in ev if e.get("name") == "process_name"]
+    assert names == ["rank 0: python", "rank 1: python"]
+    assert main([str(tmp_path), "-o", out]) == 0 and os.path.getsize(out) > 0
