@@ -636,7 +636,7 @@ class ModelRunner:
         if ev0 is not None:
             ev1 = torch.cuda.Event(enable_timing=True)
             ev1.record()
-            self.timing_events.append((ev0, ev1, bool(p["decode_only"]), n))
+            self.timing_events.append((ev0, ev1, bool(p["decode_only"]), int(p["T"])))   # T = token rows of the step
         host = self.tokens_host[self._tok_ring]
         self._tok_ring = (self._tok_ring + 1) % len(self.tokens_host)
         ev = None
