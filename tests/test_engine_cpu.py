@@ -122,3 +122,55 @@ def test_sample_logprobs_min_tokens_and_prompt_logprobs(async_sched):
         assert plp[i]["token_id"] == prompt[i]
         assert abs(plp[i]["logprob"] - float(want[i - 1, prompt[i]])) < 2e-3, i
         assert len(plp[i]["top"]) == 2
+
+
+def test_multimodal_embeddings_through_vision_encoder():
+    """Image patches -> vision encoder (bidirectional varlen attention, batched under a patch budget,
+    padded to a bucket) -> rows that replace the placeholder tokens; chunked prefill across an image
+    and batching with a text-only request leave the tokens unchanged."""
+    from vllm_torchtpu_b200.layers.vision import VisionConfig, VisionEncoder
+    from vllm_torchtpu_b200.runner.mm_encoder import MMEncoderManager, MMItem, chunk_video, patch_buckets
+    assert chunk_video(10, 64, 256, temporal_patch=2) == [(0, 8), (8, 2)]
+    assert chunk_video(3, 100, 100, temporal_patch=1) == [(0, 1), (1, 1), (2, 1)]
+    assert patch_buckets(1000, 256) == [256, 512, 1000]
+    with pytest.raises(ValueError):
+        chunk_video(4, 300, 256)
+    # the encoder treats every item as its own attention segment: batching does not change an item
+    vc = VisionConfig(patch_dim=48, hidden_size=64, num_heads=2, depth=2, merge=4, out_hidden_size=256)
+    enc = VisionEncoder(vc, "cpu")
+    g = torch.Generator().manual_seed(0)
+    a, b = torch.randn(16, 48, generator=g), torch.randn(40, 48, generator=g)
+    alone = enc.forward(a, [16])[0]
+    both = enc.forward(torch.cat([a, b]), [16, 40])
+    torch.testing.assert_close(both[0], alone, rtol=1e-5, atol=1e-5)
+    assert both[1].shape == (10, 256)
+    mgr = MMEncoderManager(enc, max_patches_per_batch=48, buckets=[32, 48])
+    mgr.add_request("r", [MMItem("r", 0, a, 3), MMItem("r", 1, b, 20)])
+    rows = mgr.gather("r", 0, 8)                       # first chunk covers part of item 0 only
+    assert len(rows) == 1 and rows[0][0] == 3 and rows[0][1].shape[0] == 4 and mgr.stats["batches"] == 1
+    torch.testing.assert_close(rows[0][1], alone, rtol=1e-5, atol=1e-5)
+    rows = mgr.gather("r", 22, 40)
+    assert rows[0][0] == 0 and rows[0][1].shape[0] == 8 and mgr.stats["batches"] == 2
+    assert mgr.stats["padded_patches"] == 32 + 48
+    # engine: greedy tokens with image embeddings, whole prompt vs 16-token chunks + a text neighbour
+    prompt = _prompts()[3][:48]
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+
+    def run(max_batched, extra):
+        llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, max_num_batched_tokens=max_batched, block_size=16,
+                  init_dist=False)
+        llm.engine.enable_vision(vc, max_patches_per_batch=64)
+        eng = llm.engine
+        rid = eng.add_request(prompt, sp, mm_items=[(a, 5), (b, 30)])
+        for p in extra:
+            eng.add_request(p, sp)
+        done = {r.request_id: r.output_token_ids for r in eng.run_until_done()}
+        return done[rid]
+
+    whole = run(256, [])
+    chunked = run(16, [_prompts()[1]])
+    assert whole == chunked
+    plain = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    assert plain.generate([prompt], sp)[0].outputs[0].token_ids != whole      # the image changes the output
+    with pytest.raises(ValueError):
+        plain.engine.add_request(prompt, sp, mm_items=[(a, 5)])

@@ -160,3 +160,26 @@ def test_logprobs_min_tokens_prompt_logprobs_on_gpu():
     assert len(got) >= 3 and toks[0] not in got[:3]
     from vllm_torchtpu_b200.ops import cuda
     assert cuda.check_status() == 0
+
+
+def test_vision_encoder_on_gpu_matches_cpu():
+    """ViT blocks on the tcgen05 GEMM and the bidirectional attention kernel against the fp32 CPU stack."""
+    from vllm_torchtpu_b200.layers.vision import VisionConfig, VisionEncoder
+    kw = dict(patch_dim=96, hidden_size=256, num_heads=4, depth=2, merge=4, out_hidden_size=512)
+    cpu = VisionEncoder(VisionConfig(dtype=torch.float32, **kw), "cpu")
+    gpu = VisionEncoder(VisionConfig(dtype=torch.bfloat16, **kw), "cuda")
+    # random-init draws differ between devices: give the GPU stack the CPU stack's weights
+    for name in ("patch_w", "merge_w"):
+        setattr(gpu, name, getattr(cpu, name).to("cuda", torch.bfloat16))
+    for bc, bg in zip(cpu.blocks, gpu.blocks):
+        for name in ("qkv_w", "proj_w", "fc1_w", "fc2_w"):
+            setattr(bg, name, getattr(bc, name).to("cuda", torch.bfloat16))
+    g = torch.Generator().manual_seed(0)
+    counts = [64, 200, 16]
+    patches = torch.randn(sum(counts), 96, generator=g)
+    want = cpu.forward(patches, counts)
+    got = gpu.forward(patches.cuda(), counts)
+    for a, b in zip(got, want):
+        assert a.shape == b.shape
+        err = (a.float().cpu() - b).abs().max().item()
+        assert err < 0.05 * b.abs().max().item() + 0.02, err

@@ -185,3 +185,20 @@ def test_logprobs():
     lf = logits.float()
     assert torch.equal(lf.gather(1, a[2].long()), lf.gather(1, b[2]))
     assert torch.equal(a[3].long(), b[3])
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(16, 16, 64), (8, 2, 128)])
+def test_encoder_attention_bidirectional(Hq, Hkv, D):
+    """Non-causal varlen attention (vision encoder): every token sees its whole sequence."""
+    g = torch.Generator(device=DEV).manual_seed(5)
+    lens = [1, 63, 64, 200, 577]
+    offs = [0]
+    for n in lens:
+        offs.append(offs[-1] + n)
+    T = offs[-1]
+    q = torch.randn(T, Hq, D, device=DEV, generator=g).bfloat16()
+    k = torch.randn(T, Hkv, D, device=DEV, generator=g).bfloat16()
+    v = torch.randn(T, Hkv, D, device=DEV, generator=g).bfloat16()
+    got = cu().encoder_attention(q, k, v, offs)
+    want = ref.encoder_attention(q, k, v, offs)
+    _close(got, want, 2e-2, 2e-2)

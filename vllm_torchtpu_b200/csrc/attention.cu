@@ -73,6 +73,7 @@ struct AttnParams {
   int* counters;                 // decode scratch [R * Hkv]
   const float* sinks;            // optional [Hq]
   int max_blocks, block_size, Hq, Hkv, req_begin, req_end, num_splits, window;
+  int non_causal;                // prefill kernel: every query sees all seq_len keys (encoder attention)
   long long num_blocks;
   float scale_log2, softcap;
   float v_scale;                 // fp8 cache: dequantisation factor of V (K's is folded into scale_log2)
@@ -574,7 +575,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
       }
     }
   }
-  const int kv_end = min(seq_len, ctx + q0 + BQ);               // causal bound of the tile
+  const int kv_end = p.non_causal ? seq_len : min(seq_len, ctx + q0 + BQ);   // causal bound of the tile
   int kv_begin = 0;
   if (p.window > 0) kv_begin = max(0, ctx + q0 - p.window + 1) / BKV * BKV;
   const int nchunks = (kv_end - kv_begin + BKV - 1) / BKV;
@@ -610,7 +611,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  const int lim0 = ctx + row0, lim1 = ctx + row1;
+  const int lim0 = p.non_causal ? 0x3fffffff : ctx + row0, lim1 = p.non_causal ? 0x3fffffff : ctx + row1;
 
   if (nchunks > 0) issue(0, 0);
   cp_async_commit();
@@ -623,7 +624,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
     const uint32_t sb = sbase + stage * STAGE_BYTES;
     const int tok0 = kv_begin + c * BKV;
     // skip groups entirely above this warp's diagonal
-    const int warp_max_key = ctx + q0 + warp * 16 + 15;
+    const int warp_max_key = p.non_causal ? 0x3fffffff : ctx + q0 + warp * 16 + 15;
     float s[BKV / 8][4];
 #pragma unroll
     for (int i = 0; i < BKV / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -766,6 +767,7 @@ static void fill_params(AttnParams& p, const void* q, const void* kv, void* out,
   p.softcap = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   p.sinks = sinks;
   p.v_scale = 1.f;
+  p.non_causal = 0;
   (void)D;
 }
 
@@ -910,6 +912,34 @@ extern "C" int b200_attn_prefill(const void* q, const void* kv, void* out, float
   return attn_prefill_impl(q, kv, out, lse, block_tables, seq_lens, qsl, req_begin, req_end, num_tiles,
                            max_blocks, block_size, num_blocks, Hq, Hkv, D, scale, window, softcap, sinks, 0, 1.f,
                            1.f, stream);
+}
+// Bidirectional attention over a ragged batch whose keys and values sit in the paged layout (vision
+// encoders: each request's q_len equals its seq_len).  Same arguments as b200_attn_prefill.
+extern "C" int b200_attn_encoder(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                                 const int* seq_lens, const int* qsl, int req_begin, int req_end, int num_tiles,
+                                 int max_blocks, int block_size, long long num_blocks, int Hq, int Hkv, int D,
+                                 float scale, cudaStream_t stream) {
+  if (req_end <= req_begin || num_tiles <= 0) return 0;
+  if (block_size % 16 || (Hq % Hkv)) {
+    b200_set_last_error("attn_encoder: block_size % 16 == 0 required", __FILE__, __LINE__);
+    return -1;
+  }
+  AttnParams p;
+  fill_params(p, q, kv, out, lse, block_tables, seq_lens, qsl, max_blocks, block_size, num_blocks, Hq, Hkv, D,
+              scale, 0, 0.f, nullptr);
+  p.req_begin = req_begin;
+  p.req_end = req_end;
+  p.num_splits = 1;
+  p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr;
+  p.non_causal = 1;
+  dim3 grid(Hq, num_tiles);
+  if (D == 128) B200_CUDA_CHECK((launch_prefill<128, false>(grid, stream, p)));
+  else if (D == 64) B200_CUDA_CHECK((launch_prefill<64, false>(grid, stream, p)));
+  else {
+    b200_set_last_error("attn_encoder: head_dim must be 64 or 128", __FILE__, __LINE__);
+    return -1;
+  }
+  return 0;
 }
 extern "C" int b200_attn_prefill_fp8kv(const void* q, const void* kv, void* out, float* lse,
                                        const int* block_tables, const int* seq_lens, const int* qsl,

@@ -90,7 +90,11 @@ class LLMEngine:
 
     # ---- requests ---------------------------------------------------------------
     def add_request(self, prompt_token_ids: list, sampling_params: Optional[SamplingParams] = None,
-                    request_id: Optional[str] = None, kv_transfer_params: Optional[dict] = None) -> str:
+                    request_id: Optional[str] = None, kv_transfer_params: Optional[dict] = None,
+                    mm_items: Optional[list] = None) -> str:
+        """``mm_items``: [(patches [num_patches, patch_dim], prompt_offset), ...] — images or video chunks
+        whose embeddings replace the placeholder tokens starting at ``prompt_offset`` (needs
+        ``enable_vision`` first)."""
         sp = sampling_params or SamplingParams()
         B200Platform.validate_request(sp)
         if len(prompt_token_ids) + sp.max_tokens > self.cfg.model.max_model_len:
@@ -107,9 +111,32 @@ class LLMEngine:
                                                                    getattr(self, "vocab_strings", None),
                                                                    self.eos_token_id)
             self.runner.structured.add_request(rid, sp.structured)
+        if mm_items:
+            if self.runner.mm_manager is None:
+                raise ValueError("multimodal items need a vision encoder: call enable_vision first")
+            from ..runner.mm_encoder import MMItem
+            items = [MMItem(rid, i, p, int(off)) for i, (p, off) in enumerate(mm_items)]
+            self.runner.mm_manager.add_request(rid, items)
+            for it in items:
+                if it.prompt_offset + it.num_tokens > len(prompt_token_ids):
+                    self.runner.mm_manager.remove_request(rid)
+                    raise ValueError("a multimodal item's placeholder range runs past the prompt")
         self.scheduler.add_request(Request(rid, list(prompt_token_ids), sp, self.eos_token_id,
                                            kv_transfer_params=kv_transfer_params))
         return rid
+
+    def enable_vision(self, vision_cfg, max_patches_per_batch: int = 8192):
+        """Attach a vision encoder whose output width is the model's hidden size.  Prefix caching is
+        keyed by token ids only, so requests with multimodal items must not share cached blocks."""
+        from ..layers.vision import VisionEncoder
+        from ..runner.mm_encoder import MMEncoderManager
+        if vision_cfg.out_hidden_size != self.cfg.model.hidden_size:
+            raise ValueError("vision out_hidden_size must equal the model's hidden size")
+        if self.cfg.cache.enable_prefix_caching:
+            raise ValueError("multimodal requests need enable_prefix_caching=False")
+        enc = VisionEncoder(vision_cfg, self.runner.device)
+        self.runner.mm_manager = MMEncoderManager(enc, max_patches_per_batch)
+        return self.runner.mm_manager
 
     # ---- LoRA adapters (reference: src/vllm_torchtpu/worker/tpu_worker.py:898-908) -----------------
     def _lora(self):
@@ -219,6 +246,8 @@ class LLMEngine:
         for r in finished:
             if r.sampling_params.pooling:
                 r.pooled = self.runner.take_pooled(r.request_id)
+            if self.runner.mm_manager is not None:
+                self.runner.mm_manager.remove_request(r.request_id)
         if self.runner.structured is not None:
             for r in finished:
                 self.runner.structured.remove_request(r.request_id)

@@ -323,6 +323,48 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
     return out
 
 
+def encoder_attention(q, k, v, cu_seqlens, scale=None):
+    """Bidirectional attention over a ragged batch of sequences (vision encoders).  q [T, Hq, D], k / v
+    [T, Hkv, D] bf16, ``cu_seqlens`` = list of R + 1 token offsets.  Keys and values are packed into the
+    paged layout of the attention kernels and the prefill kernel runs with the causal mask off
+    (reference: src/vllm_torchtpu/kernels/flash_attention/ — segment-id flash attention)."""
+    _require_bf16(q, k, v)
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    bs = 16
+    lens = [int(cu_seqlens[i + 1]) - int(cu_seqlens[i]) for i in range(len(cu_seqlens) - 1)]
+    R = len(lens)
+    nblk = [-(-n // bs) for n in lens]
+    max_blocks = max(1, max(nblk) if nblk else 1)
+    NB = max(1, sum(nblk))
+    dev = q.device
+    bt = torch.zeros((R, max_blocks), dtype=torch.int32)
+    slots = torch.empty(T, dtype=torch.long)
+    off = 0
+    for r, n in enumerate(lens):
+        bt[r, :nblk[r]] = torch.arange(off, off + nblk[r], dtype=torch.int32)
+        slots[int(cu_seqlens[r]):int(cu_seqlens[r + 1])] = off * bs + torch.arange(n)
+        off += nblk[r]
+    flat = torch.zeros((NB * bs, 2, Hkv, D), dtype=q.dtype, device=dev)
+    slots = slots.to(dev)
+    flat[slots, 0] = k
+    flat[slots, 1] = v
+    cache = flat.view(NB, bs, 2, Hkv, D).permute(0, 2, 3, 1, 4).contiguous()
+    bt_d = bt.to(dev)
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+    qsl = torch.tensor([int(c) for c in cu_seqlens], dtype=torch.int32, device=dev)
+    out = torch.zeros_like(q)
+    tiles = sum(-(-n // 64) for n in lens)
+    sc = float(scale) if scale is not None else D ** -0.5
+    qc = q.contiguous()
+    _check(lib().b200_attn_encoder(
+        _p(qc), _p(cache), _p(out), c_void_p(0), _p(bt_d), _p(sl), _p(qsl), c_int(0), c_int(R), c_int(tiles),
+        c_int(max_blocks), c_int(bs), c_longlong(NB), c_int(Hq), c_int(Hkv), c_int(D), c_float(sc), _stream()),
+        "attn_encoder")
+    count_launch()
+    return out
+
+
 # -------------------------------------------------------------------- sampling
 def _logit_dtype(t):
     if t.dtype == torch.bfloat16:

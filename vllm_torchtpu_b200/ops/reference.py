@@ -348,3 +348,23 @@ def mla_paged_attention(q_latent, cache, block_tables, seq_lens, query_start_loc
     if return_lse:
         return out, lse
     return out
+
+
+def encoder_attention(q, k, v, cu_seqlens, scale=None):
+    """Bidirectional attention inside each sequence of a ragged batch (fp32 oracle).
+    q [T, Hq, D]; k, v [T, Hkv, D]; cu_seqlens: R + 1 offsets."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    G = Hq // Hkv
+    sc = float(scale) if scale is not None else D ** -0.5
+    out = torch.zeros_like(q)
+    for r in range(len(cu_seqlens) - 1):
+        a, b = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
+        if b <= a:
+            continue
+        qr = q[a:b].float().permute(1, 0, 2).reshape(Hkv, G, b - a, D)
+        kr, vr = k[a:b].float().permute(1, 0, 2), v[a:b].float().permute(1, 0, 2)
+        p = torch.softmax(torch.einsum("hgqd,hkd->hgqk", qr, kr) * sc, dim=-1)
+        o = torch.einsum("hgqk,hkd->hgqd", p, vr).reshape(Hq, b - a, D).permute(1, 0, 2)
+        out[a:b] = o.to(q.dtype)
+    return out

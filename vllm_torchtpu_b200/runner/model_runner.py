@@ -123,6 +123,8 @@ class ModelRunner:
         self.timing_events = None        # (start event, end event, decode-only?, tokens) per step when enabled
         self._step_extras = None         # logprob / min_tokens work of the current step (see _plan_extras)
         self.keep_hidden = False         # a draft head wants the hidden state of the sampled rows
+        self.mm_manager = None           # multimodal encoder manager (runner/mm_encoder.py)
+        self._mm_plan = None             # (request id, first prompt token, first row, rows) of this step
         self._last_h = None
         self._pool_plan = None           # pooling requests of the current step: (id, row lo, row hi, mode, last chunk)
         self._pool_acc: dict = {}        # request id -> [sum or last row, count]
@@ -325,6 +327,10 @@ class ModelRunner:
         if st.pp.size > 1:
             return self._forward_and_sample_pp(bufs, meta, T, R, n_req_pad, all_greedy, verify)
         hidden0 = self._embed(ids, dv("token_src", T))
+        if self._mm_plan and hidden0 is not None:
+            # image / video embeddings replace the placeholder-token rows of the prompt
+            for rid, start, row0, nrows in self._mm_plan:
+                self.mm_manager.merge_into(hidden0, rid, start, row0, nrows)
         hidden, residual = self.model.forward(ids, meta, self.kv_caches, hidden=hidden0)
         if self._pool_plan:
             self._pool(hidden, residual)
@@ -611,6 +617,13 @@ class ModelRunner:
             if bm is not None:
                 self._step_bitmask = (bm, rows)
         self._step_extras = self._plan_extras(p)
+        self._mm_plan = None
+        if self.mm_manager is not None and self.mm_manager.items:
+            qsl_np = p["qsl_np"]
+            self._mm_plan = [(s.request.request_id, s.start, int(qsl_np[i]), int(qsl_np[i + 1] - qsl_np[i]))
+                             for i, s in enumerate(p["scheds"])
+                             if s.request.request_id in self.mm_manager.items
+                             and s.start < s.request.num_prompt_tokens] or None
         use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
                      and p["T_pad"] == p["R_pad"] and envs.B200_CUDA_GRAPHS and self._step_bitmask is None and lora_idx is None
                      and self._step_extras is None and not self.keep_hidden
