@@ -58,3 +58,11 @@ def test_dp2_with_expert_parallel_lockstep_matches_single_process():
     """Two replicas with different (and different numbers of) requests, experts sharded over both:
     steps run in lockstep with padded rows, an idle replica runs placeholder batches."""
     assert _run(2, "dpep", "tiny-moe") == _run(1, "tp", "tiny-moe")
+
+
+def test_tp2_lora_matches_single_process(single):
+    """Adapters sharded like the base weights (B rows of column-parallel targets, A columns of row-parallel
+    targets with the partial update added before the all-reduce) reproduce the one-process tokens."""
+    one = _run(1, "tplora", "tiny-llama")
+    assert _run(2, "tplora", "tiny-llama") == one
+    assert one[1] == single[1] and one[0] != single[0]          # request 1 runs without the adapter

@@ -18,7 +18,7 @@ def main():
     mode = sys.argv[1] if len(sys.argv) > 1 else "tp"
     model = sys.argv[2] if len(sys.argv) > 2 else "tiny-llama"
     kw = {}
-    if mode == "tp":
+    if mode in ("tp", "tplora"):
         kw["tensor_parallel_size"] = world
     elif mode == "pp":
         kw["pipeline_parallel_size"] = world
@@ -38,7 +38,26 @@ def main():
     if mode == "dpep":
         # every replica serves its own requests: rank 0 gets two prompts, rank 1 one (uneven on purpose)
         mine = [p for i, p in enumerate(prompts) if i % world == rank]
-    outs = llm.generate(mine, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    if mode == "tplora":
+        # one adapter on a fused column-parallel target, a plain column-parallel sub-projection and a
+        # row-parallel target; full-size matrices, identical on every rank, sharded by the wiring
+        import torch
+        mc = llm.engine.cfg.model
+        g = torch.Generator().manual_seed(11)
+        weights = {}
+        for li in range(mc.num_layers):
+            pre = f"model.layers.{li}."
+            weights[pre + "self_attn.q_proj"] = (torch.randn(4, mc.hidden_size, generator=g) * 0.3,
+                                                 torch.randn(mc.num_q_heads * mc.head_dim, 4, generator=g) * 0.3)
+            weights[pre + "mlp.up_proj"] = (torch.randn(4, mc.hidden_size, generator=g) * 0.3,
+                                            torch.randn(mc.intermediate_size, 4, generator=g) * 0.3)
+            weights[pre + "mlp.down_proj"] = (torch.randn(4, mc.intermediate_size, generator=g) * 0.3,
+                                              torch.randn(mc.hidden_size, 4, generator=g) * 0.3)
+        assert llm.engine.add_lora("ad", 4, 16.0, weights)
+        sp = [SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True, lora_name="ad" if i != 1 else None)
+              for i in range(len(mine))]
+    outs = llm.generate(mine, sp)
     toks = [o.outputs[0].token_ids for o in outs]
     if mode == "dpep":
         import torch.distributed as dist

@@ -64,9 +64,11 @@ class LinearBase:
 
     lora_targets = None          # set by lora.wiring.attach: [(adapter target name, column offset)]
 
+    lora_in_forward = False      # row-parallel layers under TP add the update before their all-reduce
+
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         y = self.forward(x)
-        if self.lora_targets:
+        if self.lora_targets and not self.lora_in_forward:
             from ..lora import wiring
             if wiring.active():
                 y = wiring.apply(self, x, y)
@@ -119,6 +121,7 @@ class RowParallelLinear(LinearBase):
         # set by a decoder layer whose next op is add + RMSNorm: small outputs may then be returned
         # as a pending reduction that the norm kernel completes
         self.defer_reduce = False
+        self.lora_in_forward = self.tp_size > 1 and reduce_results
         self.full_in, self.full_out = in_features, out_features
         super().__init__(name, in_features // self.tp_size, out_features, **kw)
 
@@ -130,6 +133,13 @@ class RowParallelLinear(LinearBase):
         if self.tp_size == 1 or not self.reduce_results:
             return self.method.apply(self, x, self.bias)
         comm = get_tp_comm()
+        if self.lora_targets:
+            from ..lora import wiring
+            if wiring.active():
+                # the low-rank update of this rank's input shard is a partial sum like the base product
+                y = wiring.apply(self, x, self.method.apply(self, x, None))
+                y = comm.all_reduce(y)
+                return y + self.bias if self.bias is not None else y
         if (x.is_cuda and comm.heap is not None and comm.heap.fused_tp is not None
                 and self.method.supports_fused_reduce):
             ft = comm.heap.fused_tp

@@ -33,6 +33,8 @@ class LoRAManager:
         self.scales = torch.zeros(max_loras, dtype=torch.float32, device=device)
 
     def register_layer(self, name: str, in_features: int, out_features: int) -> None:
+        if not hasattr(self, "shard_fns"):
+            self.shard_fns = {}
         self.layers[name] = (torch.zeros(self.max_loras, self.max_rank, in_features, dtype=self.dtype, device=self.device),
                              torch.zeros(self.max_loras, out_features, self.max_rank, dtype=self.dtype, device=self.device))
 
@@ -82,6 +84,8 @@ class LoRAManager:
             B[slot].zero_()
             if lname in ad.weights:
                 a, b = ad.weights[lname]
+                if lname in self.shard_fns:          # tensor parallelism: this rank's part
+                    a, b = self.shard_fns[lname](a, b)
                 A[slot, :a.shape[0], :] = a.to(self.dtype)
                 B[slot, :, :b.shape[1]] = b.to(self.dtype)
         self.scales[slot] = ad.scale

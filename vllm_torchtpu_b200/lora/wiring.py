@@ -20,25 +20,60 @@ _step_idx: Optional[torch.Tensor] = None         # [T_pad] slot per token row, -
 _manager: Optional[LoRAManager] = None
 
 
+def _column_shard_fn(lin, sub_index: int):
+    """Adapter weights of one logical sub-projection of a column-parallel linear -> this rank's part.
+    A (rank x in) is kept whole; B (out x rank) is cut exactly like the base weight's rows, by running
+    the linear's own sharding over a full-height matrix that holds B at the sub-projection's rows."""
+    full_sizes = list(lin.output_sizes)
+    local_sizes = list(getattr(lin, "shard_sizes", None) or lin.output_sizes)
+    off_full, off_local = sum(full_sizes[:sub_index]), sum(local_sizes[:sub_index])
+
+    def fn(a, b):
+        if b.shape[0] == local_sizes[sub_index] and lin.tp_size == 1:
+            return a, b
+        full = torch.zeros((sum(full_sizes), b.shape[1]), dtype=b.dtype)
+        full[off_full:off_full + full_sizes[sub_index]] = b
+        local = lin.shard_of(full)
+        return a, local[off_local:off_local + local_sizes[sub_index]]
+    return fn
+
+
+def _row_shard_fn(lin):
+    """Row-parallel linear: A (rank x in) is cut along the input features like the base weight, B is
+    kept whole; every rank's update is a partial sum that the layer's all-reduce completes."""
+    def fn(a, b):
+        return lin.shard_of(a), b
+    return fn
+
+
 def attach(model, manager: LoRAManager) -> None:
-    from ..parallel.state import get_state
-    if get_state().tp.size > 1:
-        raise NotImplementedError("LoRA adapters are wired for tensor_parallel_size == 1")
+    """Under tensor parallelism the adapter matrices are sharded like the base weights: column-parallel
+    layers cut B by output rows, row-parallel layers cut A by input columns and add their partial
+    update before the all-reduce."""
     global _manager
     _manager = manager
     for lin in model.named_linears():
         prefix, leaf = lin.name.rsplit(".", 1)
         targets = []
+        tp = getattr(lin, "tp_size", 1)
+        row_parallel = hasattr(lin, "reduce_results")
         if leaf in FUSED_TARGETS:
             sizes = getattr(lin, "shard_sizes", None) or lin.output_sizes
             off = 0
-            for sub, size in zip(FUSED_TARGETS[leaf], sizes):
+            for i, (sub, size) in enumerate(zip(FUSED_TARGETS[leaf], sizes)):
                 key = f"{prefix}.{sub}"
                 manager.register_layer(key, lin.in_features, size)
+                if tp > 1:
+                    manager.shard_fns[key] = _column_shard_fn(lin, i)
                 targets.append((key, off))
                 off += size
         else:
             manager.register_layer(lin.name, lin.in_features, lin.out_features)
+            if tp > 1:
+                if row_parallel:
+                    manager.shard_fns[lin.name] = _row_shard_fn(lin)
+                elif hasattr(lin, "output_sizes"):
+                    manager.shard_fns[lin.name] = _column_shard_fn(lin, 0)
             targets.append((lin.name, 0))
         lin.lora_targets = targets
 
