@@ -53,3 +53,26 @@ def test_completion_logprobs_and_prompt_logprobs(client):
     assert all(len(t) == 2 for t in lp["top_logprobs"]) and all(v <= 0 for v in lp["token_logprobs"])
     plp = ch["prompt_logprobs"]
     assert len(plp) == 6 and plp[0] is None and [e["token_id"] for e in plp[1:]] == [2, 3, 4, 5, 6]
+
+
+def test_multimodal_items_over_http():
+    """Image patches in the request body reach the vision encoder; without one the request fails cleanly."""
+    from vllm_torchtpu_b200.layers.vision import VisionConfig
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    hidden = llm.engine.cfg.model.hidden_size
+    llm.engine.enable_vision(VisionConfig(patch_dim=12, hidden_size=32, num_heads=2, depth=1, merge=4,
+                                          out_hidden_size=hidden))
+    app = build_app(llm.engine, "tiny-llama", None)
+    rng = np.random.RandomState(0)
+    prompt = list(range(1, 25))
+    body = {"prompt": prompt, "max_tokens": 3, "temperature": 0, "ignore_eos": True}
+    with TestClient(app) as c:
+        plain = c.post("/v1/completions", json=body).json()["choices"][0]["token_ids"]
+        item = {"patches": rng.randn(16, 12).tolist(), "offset": 4}
+        r = c.post("/v1/completions", json=dict(body, mm_items=[item]))
+        assert r.status_code == 200 and len(r.json()["choices"][0]["token_ids"]) == 3
+        assert r.json()["choices"][0]["token_ids"] != plain
+        assert c.post("/v1/completions", json=dict(body, mm_items=[{"offset": 1}])).status_code == 400
+        bad = dict(body, mm_items=[dict(item, offset=23)])          # runs past the prompt
+        assert c.post("/v1/completions", json=bad).status_code == 500
+    app.state.async_engine.shutdown()

@@ -83,6 +83,15 @@ def build_app(engine, model_name: str, tokenizer=None):
         rid = f"{'chatcmpl' if chat else 'cmpl'}-{uuid.uuid4().hex}"
         created = int(time.time())
         kvp = body.get("kv_transfer_params")
+        mm = None
+        if body.get("mm_items"):
+            # [{"patches": [[...], ...], "offset": first placeholder token}, ...]; the engine needs a
+            # vision encoder (LLMEngine.enable_vision) for these
+            import torch
+            try:
+                mm = [(torch.tensor(it["patches"], dtype=torch.float32), int(it["offset"])) for it in body["mm_items"]]
+            except (KeyError, TypeError, ValueError) as e:
+                raise HTTPException(400, f"bad mm_items: {e}")
         obj = "chat.completion" if chat else "text_completion"
 
         def chunk_payload(text, finish, final_item=None):
@@ -105,7 +114,7 @@ def build_app(engine, model_name: str, tokenizer=None):
         final_item_tokens = [0]
         if body.get("stream"):
             async def sse():
-                async for item in aeng.generate(rid, prompt_ids, sp, kvp):
+                async for item in aeng.generate(rid, prompt_ids, sp, kvp, mm):
                     final_item_tokens[0] += len(item.new_token_ids)
                     if item.error:
                         yield f"data: {json.dumps({'error': item.error})}\n\n"
@@ -119,7 +128,7 @@ def build_app(engine, model_name: str, tokenizer=None):
                 yield "data: [DONE]\n\n"
             return StreamingResponse(sse(), media_type="text/event-stream")
         toks, lps, last = [], [], None
-        async for item in aeng.generate(rid, prompt_ids, sp, kvp):
+        async for item in aeng.generate(rid, prompt_ids, sp, kvp, mm):
             toks += item.new_token_ids
             lps += item.logprobs or []
             last = item
