@@ -174,3 +174,22 @@ def test_multimodal_embeddings_through_vision_encoder():
     assert plain.generate([prompt], sp)[0].outputs[0].token_ids != whole      # the image changes the output
     with pytest.raises(ValueError):
         plain.engine.add_request(prompt, sp, mm_items=[(a, 5)])
+
+
+def test_device_wait_timeout_fails_the_step_not_the_engine():
+    """A non-zero device status word (what a bounded wait inside a kernel leaves when it gives up) turns
+    into failed requests for that step; the word is cleared and the engine keeps serving."""
+    from vllm_torchtpu_b200.runner.model_runner import DeviceWaitTimeout, StepResult
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False, async_scheduling=False)
+    eng = llm.engine
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    rid = eng.add_request(_prompts()[0], sp)
+    eng.runner.status_dev[0] = 5                       # as if a peer flag never arrived
+    done = eng.step()
+    assert [r.request_id for r in done] == [rid] and done[0].error.startswith("device_wait_timeout")
+    assert done[0].status.value == "error" and int(eng.runner.status_dev[0]) == 0 and eng.device_errors == 1
+    out = llm.generate([_prompts()[1]], sp)[0]          # the engine still serves
+    assert len(out.outputs[0].token_ids) == 4 and out.error is None
+    with pytest.raises(DeviceWaitTimeout) as ei:
+        StepResult([], [], None, None, 0, status_host=torch.tensor([3], dtype=torch.int32)).get()
+    assert ei.value.code == 3 and "accumulator" in str(ei.value)

@@ -220,7 +220,13 @@ class LLMEngine:
         return out, res
 
     def _retire(self, out, res) -> list:
-        sampled = res.get()
+        try:
+            sampled = res.get()
+        except Exception as e:          # noqa: BLE001 - a device wait timed out: fail this step's requests
+            from ..runner.model_runner import DeviceWaitTimeout
+            if not isinstance(e, DeviceWaitTimeout):
+                raise
+            return self._fail_step(out, e)
         self.runner.note_sampled(sampled)
         if self.runner.structured is not None:
             self.runner.structured.accept_tokens(sampled)
@@ -259,6 +265,26 @@ class LLMEngine:
             for rid in self.connector.worker.get_finished_sending():
                 self.scheduler.free_delayed(rid)
         return finished
+
+    def _fail_step(self, out, err) -> list:
+        """The device reported that a bounded wait gave up during this step: its requests end with an
+        error (their KV content is not trustworthy), the status word is cleared and serving continues
+        (reference: src/vllm_torchtpu/distributed/pp_buffered.py:354-369 — helper-thread errors are
+        re-raised on the worker; here the failing unit is the step)."""
+        from ..engine.request import RequestStatus
+        logger.error("step failed: %s", err)
+        self.runner.status_dev.zero_()
+        self.device_errors = getattr(self, "device_errors", 0) + 1
+        failed = []
+        for s in out.scheduled:
+            req = s.request
+            if req.status.finished:
+                continue
+            req.error = f"device_wait_timeout: {err}"
+            self.scheduler._finish(req, RequestStatus.FINISHED_ERROR)
+            failed.append(req)
+        self.runner.note_sampled({})
+        return failed
 
     def step(self) -> list:
         """Advance the engine; returns requests that finished."""

@@ -36,6 +36,23 @@ from .input_batch import InputBatch, StepBuffers
 logger = init_logger(__name__)
 
 
+DEVICE_STATUS_NAMES = {1: "a GEMM consumer waited for a TMA stage", 2: "a TMA producer waited for a free stage",
+                       3: "an epilogue waited for its accumulator", 4: "an MMA issuer waited for a free accumulator",
+                       5: "a kernel waited for a flag of a peer GPU or of another CTA",
+                       6: "an index was out of range (bounds-checked build)",
+                       7: "a kernel waited for its copies in flight"}
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded wait inside a kernel gave up (the kernel returned early and left this status code):
+    the step's results are not valid."""
+
+    def __init__(self, code: int):
+        self.code = code
+        super().__init__(f"device status {code}: {DEVICE_STATUS_NAMES.get(code, 'unknown code')}; "
+                         "the step did not complete")
+
+
 @dataclass
 class StepResult:
     """Handle on a launched step; ``get()`` waits for the token copy."""
@@ -48,6 +65,7 @@ class StepResult:
     extra: dict = field(default_factory=dict)
     lp: Optional[dict] = None       # sample / prompt logprob tensors of the step (device or host)
     hidden: Optional[torch.Tensor] = None   # final-norm hidden state of every sampled row (draft heads)
+    status_host: Optional[torch.Tensor] = None   # copy of the device status word taken after the step
 
     def take_logprobs(self):
         """After ``get()``: ({request_id: entry}, {request_id: [entry per prompt position]}).  An entry is
@@ -75,6 +93,10 @@ class StepResult:
     def get(self) -> dict:
         if self.event is not None:
             self.event.synchronize()
+        if self.status_host is not None:
+            code = int(self.status_host[0])
+            if code:
+                raise DeviceWaitTimeout(code)
         if self.tokens_host is None:
             return {}
         if not self.extra:
@@ -166,6 +188,12 @@ class ModelRunner:
         self.last_tokens = torch.zeros(self.max_reqs, dtype=torch.int32, device=self.device)
         self.tokens_host = [torch.zeros(self.max_reqs * 9, dtype=torch.int32, pin_memory=self.is_cuda)
                             for _ in range(4)]
+        self.status_host = [torch.zeros(1, dtype=torch.int32, pin_memory=self.is_cuda) for _ in range(4)]
+        if self.is_cuda:
+            from ..ops import cuda as _cuda
+            self.status_dev = _cuda.Workspace.get(self.device).status       # written by bounded device waits
+        else:
+            self.status_dev = torch.zeros(1, dtype=torch.int32)
         self._tok_ring = 0
 
     def determine_num_blocks(self) -> int:
@@ -651,18 +679,23 @@ class ModelRunner:
             ev1.record()
             self.timing_events.append((ev0, ev1, bool(p["decode_only"]), int(p["T"])))   # T = token rows of the step
         host = self.tokens_host[self._tok_ring]
+        st_host = self.status_host[self._tok_ring]
         self._tok_ring = (self._tok_ring + 1) % len(self.tokens_host)
         ev = None
         rows = p["L_pad"] if p.get("has_spec") else R
         if self.is_cuda:
             host[:rows].copy_(tokens[:rows], non_blocking=True)
+            # the status word of the bounded device waits travels with the tokens: a kernel that gave
+            # up turns into an exception when the host reads this step's result
+            st_host.copy_(self.status_dev, non_blocking=True)
             ev = torch.cuda.Event()
             ev.record()
         else:
             host[:rows] = tokens[:rows]
-        self.stats["d2h_bytes"] += rows * 4
+            st_host.copy_(self.status_dev)
+        self.stats["d2h_bytes"] += rows * 4 + 4
         res = StepResult([s.request.request_id for s in p["scheds"]], [s.samples for s in p["scheds"]],
-                         host, ev, n, rows * 4)
+                         host, ev, n, rows * 4 + 4, status_host=st_host)
         if self.keep_hidden:
             res.hidden, self._last_h = self._last_h, None
         if self._step_extras is not None:
