@@ -66,3 +66,9 @@ def test_tp2_lora_matches_single_process(single):
     one = _run(1, "tplora", "tiny-llama")
     assert _run(2, "tplora", "tiny-llama") == one
     assert one[1] == single[1] and one[0] != single[0]          # request 1 runs without the adapter
+
+
+def test_tp2_pads_query_heads_that_do_not_divide():
+    """3 query heads on 2 ranks: every KV group is zero-padded to 4 heads (q_proj rows and o_proj columns),
+    the KV head is replicated, and the tokens equal the one-process run."""
+    assert _run(2, "tp", "tiny-odd-heads") == _run(1, "tp", "tiny-odd-heads")

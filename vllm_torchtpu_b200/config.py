@@ -76,6 +76,7 @@ class ModelConfig:
     index_head_dim: int = 0
     # Gated DeltaNet hybrid (every `full_attention_interval`-th layer is softmax attention)
     full_attention_interval: int = 0
+    num_q_heads_unpadded: int = 0        # checkpoint's query heads when num_q_heads was zero-padded for TP
     gdn_num_k_heads: int = 0
     gdn_num_v_heads: int = 0
     gdn_head_k_dim: int = 0
@@ -257,6 +258,9 @@ def model_preset(name: str) -> ModelConfig:
                        moe_n_group=2, moe_topk_group=1, moe_routed_scaling=2.5,
                        q_lora_rank=96, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16,
                        v_head_dim=32, rope_interleaved=True, max_model_len=256)
+    if n in ("tiny-odd-heads",):
+        return _preset(name="tiny-odd-heads", dtype=torch.float32, num_q_heads=3, num_kv_heads=1, head_dim=64,
+                       hidden_size=256, max_model_len=256)
     if n in ("tiny-kda",):
         return _preset(name="tiny-kda", architecture="kimi_linear", dtype=torch.float32,
                        num_layers=4, full_attention_interval=4, gdn_num_k_heads=4, gdn_num_v_heads=4,

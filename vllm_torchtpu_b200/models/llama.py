@@ -19,13 +19,27 @@ from ..parallel.state import get_state
 from ..quantization import QuantConfig
 
 
-class QKVParallelLinear(ColumnParallelLinear):
-    """q/k/v packed; KV heads are replicated when there are fewer than TP ranks."""
+def pad_q_heads(t: torch.Tensor, dim: int, num_kv_heads: int, g: int, g_padded: int, head_dim: int):
+    """Zero-pad the query heads of every KV group from ``g`` to ``g_padded`` along ``dim`` of a weight
+    whose extent there is ``num_kv_heads * g * head_dim``; the head -> KV-head mapping is unchanged
+    (reference: src/vllm_torchtpu/gqa_head_padding.py — zero-pad Q heads when heads % tp != 0)."""
+    t = t.movedim(dim, 0)
+    rest = t.shape[1:]
+    t = t.reshape(num_kv_heads, g, head_dim, -1)
+    out = t.new_zeros((num_kv_heads, g_padded, head_dim, t.shape[-1]))
+    out[:, :g] = t
+    return out.reshape((num_kv_heads * g_padded * head_dim,) + tuple(rest)).movedim(0, dim)
 
-    def __init__(self, name, hidden, num_q_heads, num_kv_heads, head_dim, **kw):
+
+class QKVParallelLinear(ColumnParallelLinear):
+    """q/k/v packed; KV heads are replicated when there are fewer than TP ranks.  ``unpadded_q`` > 0:
+    checkpoints hold that many query heads and ``num_q_heads`` is the zero-padded count."""
+
+    def __init__(self, name, hidden, num_q_heads, num_kv_heads, head_dim, unpadded_q: int = 0, **kw):
         st = get_state()
         tp, r = st.tp.size, st.tp.rank_in_group
         self.total_q, self.total_kv, self.hd = num_q_heads, num_kv_heads, head_dim
+        self.unpadded_q = unpadded_q if unpadded_q and unpadded_q != num_q_heads else 0
         self.q_per_rank = num_q_heads // tp
         self.kv_per_rank = max(1, num_kv_heads // tp)
         self.kv_replicas = max(1, tp // num_kv_heads)
@@ -36,9 +50,16 @@ class QKVParallelLinear(ColumnParallelLinear):
         if self.out_features != sum(self.shard_sizes):
             self.out_features = sum(self.shard_sizes)
         self._r = r
+        if self.unpadded_q:
+            # random-init and checkpoint weights both come with the checkpoint's head count
+            self.full_out = (self.unpadded_q + 2 * num_kv_heads) * head_dim
 
     def shard_of(self, full_weight):
         hd = self.hd
+        if self.unpadded_q and full_weight.shape[0] == (self.unpadded_q + 2 * self.total_kv) * hd:
+            q = pad_q_heads(full_weight[: self.unpadded_q * hd], 0, self.total_kv,
+                            self.unpadded_q // self.total_kv, self.total_q // self.total_kv, hd)
+            full_weight = torch.cat([q, full_weight[self.unpadded_q * hd:]], 0)
         q = full_weight[: self.total_q * hd]
         k = full_weight[self.total_q * hd:(self.total_q + self.total_kv) * hd]
         v = full_weight[(self.total_q + self.total_kv) * hd:]
@@ -48,6 +69,23 @@ class QKVParallelLinear(ColumnParallelLinear):
         ks = k[kv_idx * self.kv_per_rank * hd:(kv_idx + 1) * self.kv_per_rank * hd]
         vs = v[kv_idx * self.kv_per_rank * hd:(kv_idx + 1) * self.kv_per_rank * hd]
         return torch.cat([qs, ks, vs], 0)
+
+
+class OProjParallelLinear(RowParallelLinear):
+    """Row-parallel output projection whose input features are query heads; pads the checkpoint's
+    columns when the query heads were zero-padded for tensor parallelism."""
+
+    def __init__(self, name, num_q_heads, num_kv_heads, head_dim, hidden, unpadded_q: int = 0, **kw):
+        super().__init__(name, num_q_heads * head_dim, hidden, **kw)
+        self.q_pad = None
+        if unpadded_q and unpadded_q != num_q_heads:
+            self.q_pad = (num_kv_heads, unpadded_q // num_kv_heads, num_q_heads // num_kv_heads, head_dim)
+            self.full_in = unpadded_q * head_dim
+
+    def shard_of(self, full_weight):
+        if self.q_pad is not None and full_weight.shape[1] == self.q_pad[0] * self.q_pad[1] * self.q_pad[3]:
+            full_weight = pad_q_heads(full_weight, 1, *self.q_pad)
+        return super().shard_of(full_weight)
 
 
 class LlamaMLP:
@@ -81,8 +119,10 @@ class LlamaAttention:
     def __init__(self, name, cfg: ModelConfig, device, quant):
         kw = dict(dtype=cfg.dtype, device=device, quant_config=quant)
         self.qkv = QKVParallelLinear(f"{name}.qkv_proj", cfg.hidden_size, cfg.num_q_heads,
-                                     cfg.num_kv_heads, cfg.head_dim, bias=cfg.attention_bias, **kw)
-        self.o = RowParallelLinear(f"{name}.o_proj", cfg.num_q_heads * cfg.head_dim, cfg.hidden_size, **kw)
+                                     cfg.num_kv_heads, cfg.head_dim, unpadded_q=cfg.num_q_heads_unpadded,
+                                     bias=cfg.attention_bias, **kw)
+        self.o = OProjParallelLinear(f"{name}.o_proj", cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim,
+                                     cfg.hidden_size, unpadded_q=cfg.num_q_heads_unpadded, **kw)
         self.q_norm_w = self.k_norm_w = None
         if cfg.qk_norm:
             self.q_norm_w = torch.ones(cfg.head_dim, dtype=cfg.dtype, device=device)

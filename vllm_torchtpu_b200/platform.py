@@ -164,10 +164,20 @@ class B200Platform:
         if c.block_size not in (16, 32, 64, 128, 256):
             raise ValueError("block_size must be one of 16/32/64/128/256")
         tp = p.tensor_parallel_size
-        if m.num_q_heads % tp:
-            raise ValueError(f"{m.num_q_heads} query heads do not divide over tp={tp}")
         if not m.is_mla and m.num_kv_heads % tp and tp % m.num_kv_heads:
             raise ValueError(f"{m.num_kv_heads} kv heads cannot be sharded or replicated over tp={tp}")
+        if m.num_q_heads % tp:
+            if m.is_mla or m.num_q_heads % m.num_kv_heads or m.architecture not in ("llama", "qwen3_moe"):
+                raise ValueError(f"{m.num_q_heads} query heads do not divide over tp={tp}")
+            # zero-pad the query heads of every KV group until they divide over the ranks; the padded
+            # heads have zero q_proj rows and zero o_proj columns, so the function is unchanged
+            g = m.num_q_heads // m.num_kv_heads
+            gp = g
+            while (m.num_kv_heads * gp) % tp:
+                gp += 1
+            m.num_q_heads_unpadded = m.num_q_heads
+            m.num_q_heads = m.num_kv_heads * gp
+            logger.info("query heads padded %d -> %d for tp=%d", m.num_q_heads_unpadded, m.num_q_heads, tp)
         if p.enable_expert_parallel and not m.is_moe:
             logger.warning("--enable-expert-parallel ignored: %s has no experts", m.name)
             p.enable_expert_parallel = False
