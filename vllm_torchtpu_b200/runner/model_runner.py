@@ -191,7 +191,7 @@ class ModelRunner:
         self.status_host = [torch.zeros(1, dtype=torch.int32, pin_memory=self.is_cuda) for _ in range(4)]
         if self.is_cuda:
             from ..ops import cuda as _cuda
-            self.status_dev = _cuda.Workspace.get(self.device).status       # written by bounded device waits
+            self.status_dev = _cuda.Workspace.get(self.device).status[:1]   # code written by bounded device waits
         else:
             self.status_dev = torch.zeros(1, dtype=torch.int32)
         self._tok_ring = 0
