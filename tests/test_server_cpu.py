@@ -76,3 +76,31 @@ def test_multimodal_items_over_http():
         bad = dict(body, mm_items=[dict(item, offset=23)])          # runs past the prompt
         assert c.post("/v1/completions", json=bad).status_code == 500
     app.state.async_engine.shutdown()
+
+
+def test_embeddings_and_lora_adapter_routes(client, tmp_path):
+    import torch
+    from safetensors.torch import save_file
+    r = client.post("/v1/embeddings", json={"input": [[1, 2, 3, 4], [9, 8, 7]], "pooling": "mean"})
+    assert r.status_code == 200
+    data = r.json()["data"]
+    assert len(data) == 2 and abs(sum(a * a for a in data[0]["embedding"]) - 1.0) < 1e-3
+    assert r.json()["usage"]["prompt_tokens"] == 7
+    assert client.post("/v1/embeddings", json={"input": [1, 2], "pooling": "max"}).status_code == 400
+    body = {"prompt": [3, 1, 4, 1, 5, 9, 2, 6], "max_tokens": 4, "temperature": 0, "ignore_eos": True}
+    base = client.post("/v1/completions", json=body).json()["choices"][0]["token_ids"]
+    g = torch.Generator().manual_seed(0)
+    tensors = {}
+    for li in range(2):
+        k = f"model.layers.{li}.mlp.down_proj"
+        tensors[k + ".lora_A.weight"] = torch.randn(4, 512, generator=g) * 0.5
+        tensors[k + ".lora_B.weight"] = torch.randn(256, 4, generator=g) * 0.5
+    path = str(tmp_path / "ad.safetensors")
+    save_file(tensors, path)
+    r = client.post("/v1/load_lora_adapter", json={"lora_name": "ad", "lora_path": path, "alpha": 32})
+    assert r.status_code == 200 and r.json()["loaded"]
+    with_ad = client.post("/v1/completions", json=dict(body, lora_name="ad")).json()["choices"][0]["token_ids"]
+    assert with_ad != base
+    assert client.post("/v1/completions", json=body).json()["choices"][0]["token_ids"] == base
+    assert client.post("/v1/unload_lora_adapter", json={"lora_name": "ad"}).json()["unloaded"]
+    assert client.post("/v1/load_lora_adapter", json={"lora_name": "x", "lora_path": "/nonexistent"}).status_code == 400

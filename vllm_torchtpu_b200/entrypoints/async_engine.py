@@ -28,6 +28,16 @@ class StreamItem:
     num_cached_tokens: int = 0
     logprobs: Optional[list] = None          # entries of new_token_ids when the request asked for them
     prompt_logprobs: Optional[list] = None   # with the final item
+    pooled: Optional[list] = None            # embedding of a pooling request, with the final item
+
+
+def _settle(fut, res, exc) -> None:
+    if fut.cancelled():
+        return
+    if exc is not None:
+        fut.set_exception(exc)
+    else:
+        fut.set_result(res)
 
 
 class AsyncEngine:
@@ -58,6 +68,15 @@ class AsyncEngine:
                             self._emit(StreamItem(rid, [], True, "error", error=str(e)))
                     elif kind == "abort":
                         eng.abort_request(payload)
+                    elif kind == "call":
+                        # engine-thread work on behalf of a route (adapter loading): no step is in
+                        # progress while it runs
+                        fn, fut, loop = payload
+                        try:
+                            res, exc = fn(eng), None
+                        except Exception as e:       # noqa: BLE001 - handed to the awaiting route
+                            res, exc = None, e
+                        loop.call_soon_threadsafe(_settle, fut, res, exc)
             except queue.Empty:
                 pass
             if not eng.has_unfinished():
@@ -82,7 +101,8 @@ class AsyncEngine:
                     self._emit(StreamItem(rid, list(new), done, req.status.value if done else None,
                                           req.kv_transfer_params if done else None, req.error,
                                           req.num_prompt_tokens, req.num_cached_tokens, lps,
-                                          (req.prompt_logprobs or None) if done else None))
+                                          (req.prompt_logprobs or None) if done else None,
+                                          getattr(req, "pooled", None) if done else None))
                     if done:
                         eng.scheduler.requests.pop(rid, None)
             del finished
@@ -98,6 +118,13 @@ class AsyncEngine:
             self._sent.pop(item.request_id, None)
 
     # ---- caller side -----------------------------------------------------------------
+    async def call(self, fn):
+        """Run ``fn(engine)`` on the engine thread, between steps, and return its result."""
+        loop = asyncio.get_running_loop()
+        fut = loop.create_future()
+        self._inbox.put(("call", (fn, fut, loop)))
+        return await fut
+
     async def generate(self, request_id: str, prompt_token_ids: list, sp: SamplingParams,
                        kv_transfer_params: Optional[dict] = None,
                        mm_items: Optional[list] = None) -> AsyncIterator[StreamItem]:

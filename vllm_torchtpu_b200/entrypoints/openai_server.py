@@ -40,7 +40,7 @@ def _sampling_from_body(body: dict) -> SamplingParams:
         max_tokens=int(body.get("max_tokens") or body.get("max_completion_tokens") or 16),
         min_tokens=int(body.get("min_tokens", 0) or 0), ignore_eos=bool(body.get("ignore_eos", False)),
         stop_token_ids=list(body.get("stop_token_ids") or []), logprobs=_logprobs_from_body(body),
-        prompt_logprobs=body.get("prompt_logprobs"),
+        prompt_logprobs=body.get("prompt_logprobs"), lora_name=body.get("lora_name"),
         seed=body.get("seed"), structured=body.get("structured_outputs") or body.get("guided") or None)
 
 
@@ -154,6 +154,63 @@ def build_app(engine, model_name: str, tokenizer=None):
     async def chat_completions(request: Request):
         body = await request.json()
         return await run(body, chat_prompt(body.get("messages", [])), chat=True)
+
+    @app.post("/v1/embeddings")
+    async def embeddings(request: Request):
+        """``input``: one prompt or a list (token-id lists, or text with a tokenizer); ``pooling``: last | mean."""
+        body = await request.json()
+        inp = body.get("input")
+        if inp is None:
+            raise HTTPException(400, "missing input")
+        many = isinstance(inp, list) and inp and not isinstance(inp[0], int)
+        prompts = inp if many else [inp]
+        pooling = body.get("pooling", "last")
+        if pooling not in ("last", "mean"):
+            raise HTTPException(400, "pooling must be 'last' or 'mean'")
+        data, used = [], 0
+        for i, pr in enumerate(prompts):
+            ids = encode(pr)
+            sp = SamplingParams(temperature=0.0, max_tokens=1, pooling=pooling)
+            rid = f"embd-{uuid.uuid4().hex}"
+            last = None
+            async for item in aeng.generate(rid, ids, sp, None):
+                last = item
+            if last is None or last.error or last.pooled is None:
+                raise HTTPException(500, (last.error if last else None) or "no embedding produced")
+            vec = last.pooled
+            if body.get("normalize", True):
+                n = sum(a * a for a in vec) ** 0.5 or 1.0
+                vec = [a / n for a in vec]
+            data.append({"object": "embedding", "index": i, "embedding": vec})
+            used += len(ids)
+        return JSONResponse({"object": "list", "model": model_name, "data": data,
+                             "usage": {"prompt_tokens": used, "total_tokens": used}})
+
+    @app.post("/v1/load_lora_adapter")
+    async def load_lora(request: Request):
+        """``lora_name`` + ``lora_path`` (a safetensors file of ``<layer>.lora_A.weight`` / ``lora_B.weight``
+        pairs), with ``rank`` and ``alpha``."""
+        body = await request.json()
+        try:
+            from safetensors.torch import load_file
+            tensors = load_file(body["lora_path"])
+            weights = {}
+            for k, a in tensors.items():
+                if k.endswith(".lora_A.weight"):
+                    base = k[: -len(".lora_A.weight")]
+                    weights[base] = (a, tensors[base + ".lora_B.weight"])
+            rank = int(body.get("rank") or next(iter(weights.values()))[0].shape[0])
+            ok = await aeng.call(lambda eng: eng.add_lora(body["lora_name"], rank, float(body.get("alpha", rank)),
+                                                        weights))
+        except (KeyError, OSError, StopIteration, ValueError) as e:
+            raise HTTPException(400, f"cannot load adapter: {e}")
+        return JSONResponse({"loaded": bool(ok), "lora_name": body["lora_name"]})
+
+    @app.post("/v1/unload_lora_adapter")
+    async def unload_lora(request: Request):
+        body = await request.json()
+        ok = await aeng.call(lambda eng: eng.remove_lora(body.get("lora_name", "")))
+        return JSONResponse({"unloaded": bool(ok)})
 
     @app.get("/v1/models")
     async def models():
