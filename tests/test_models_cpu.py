@@ -125,3 +125,9 @@ def test_kimi_linear_hybrid_engine_is_chunk_and_batch_invariant():
     many = LLM("tiny-kda", device="cpu", max_num_seqs=4, max_num_batched_tokens=16, block_size=16, init_dist=False)
     got = [o.outputs[0].token_ids for o in many.generate(_prompts(), sp)]
     assert got == want
+
+
+def test_hybrid_models_reject_speculative_decoding():
+    with pytest.raises(ValueError, match="state checkpoints"):
+        LLM("tiny-kda", device="cpu", max_num_seqs=4, block_size=16, init_dist=False,
+            speculative_config={"method": "ngram", "num_speculative_tokens": 2})
