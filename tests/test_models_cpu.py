@@ -1,5 +1,6 @@
 """Model families on the CPU path vs dense references."""
 import numpy as np
+import pytest
 import torch
 
 from vllm_torchtpu_b200 import SamplingParams
