@@ -161,6 +161,9 @@ class B200Platform:
         if not cls.is_kv_cache_dtype_supported(kvd):
             raise ValueError(f"kv cache dtype {kvd!r} is not supported")
         c.kv_cache_dtype = kvd
+        if kvd in ("fp8", "fp8_e4m3") and m.is_mla:
+            raise ValueError("an fp8 KV cache is implemented for GQA attention only; the latent (MLA) cache "
+                             "kernels read bf16")
         if c.block_size not in (16, 32, 64, 128, 256):
             raise ValueError("block_size must be one of 16/32/64/128/256")
         tp = p.tensor_parallel_size
