@@ -224,7 +224,7 @@ class LLMEngine:
             sampled = res.get()
         except Exception as e:          # noqa: BLE001 - a device wait timed out: fail this step's requests
             from ..runner.model_runner import DeviceWaitTimeout
-            if not isinstance(e, DeviceWaitTimeout) or self.cfg.parallel.world_size > 1:
+            if not isinstance(e, DeviceWaitTimeout) or get_state().world_size > 1:
                 # with several ranks the failure is not symmetric (one rank's wait gave up): failing
                 # requests locally would let the ranks' schedules diverge, so the process ends and the
                 # launcher takes the group down
