@@ -150,3 +150,19 @@ def test_merge_rank_traces(tmp_path):
     names = [e["args"]["name"] for e in ev if e.get("name") == "process_name"]
     assert names == ["rank 0: python", "rank 1: python"]
     assert main([str(tmp_path), "-o", out]) == 0 and os.path.getsize(out) > 0
+
+
+def test_pad_q_heads_keeps_the_kv_group_mapping():
+    import torch
+    from vllm_torchtpu_b200.models.llama import pad_q_heads
+    Hkv, G, Gp, D, H = 2, 3, 4, 8, 5
+    w = torch.arange(Hkv * G * D * H, dtype=torch.float32).reshape(Hkv * G * D, H)
+    p = pad_q_heads(w, 0, Hkv, G, Gp, D)
+    assert p.shape == (Hkv * Gp * D, H)
+    p4 = p.reshape(Hkv, Gp, D, H)
+    torch.testing.assert_close(p4[:, :G].reshape(-1, H), w)          # real heads keep their group and order
+    assert float(p4[:, G:].abs().sum()) == 0.0                       # padded heads are zero
+    o = torch.arange(H * Hkv * G * D, dtype=torch.float32).reshape(H, Hkv * G * D)
+    po = pad_q_heads(o, 1, Hkv, G, Gp, D)
+    assert po.shape == (H, Hkv * Gp * D)
+    torch.testing.assert_close(po.reshape(H, Hkv, Gp, D)[:, :, :G].reshape(H, -1), o)
