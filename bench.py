@@ -48,6 +48,7 @@ def parse_args():
     ap.add_argument("--output-len", type=int, default=128)
     ap.add_argument("--concurrency", type=int, default=64)
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--kv-cache-dtype", default="auto", help="auto (= model dtype) or fp8 (e4m3 cache; not the headline config)")
     ap.add_argument("--sync-scheduling", action="store_true")
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--warmup-requests", type=int, default=0,
@@ -154,6 +155,7 @@ def main():
 
     llm = LLM(args.model, device="cuda", tensor_parallel_size=args.gpus, max_num_seqs=args.concurrency,
               max_num_batched_tokens=args.max_num_batched_tokens, block_size=16,
+              kv_cache_dtype=args.kv_cache_dtype,
               max_model_len=args.input_len + args.output_len + 16,
               async_scheduling=not args.sync_scheduling, enforce_eager=args.enforce_eager)
     eng = llm.engine
@@ -215,6 +217,7 @@ def main():
                        "parallelism": f"tp{args.gpus}", "num_requests": args.num_requests,
                        "input_len": args.input_len, "output_len": args.output_len,
                        "max_concurrency": args.concurrency, "block_size": 16,
+                       "kv_cache_dtype": args.kv_cache_dtype,
                        "step_definition": "one full serve of the request set",
                        "l2": "inputs larger than L2: every engine step streams the weights "
                              "(>= 2 GB per rank) and the KV cache through the 126 MB L2",
