@@ -99,8 +99,10 @@ class ClockSampler:
                     if v.lower().startswith("active"):
                         reasons.add(n)
         if sm:
-            # samples taken while idle between serves would pull the median down: keep the loaded half
-            loaded = sorted(sm)[: max(1, len(sm))]
+            # samples taken while idle between serves would pull the median down: keep the samples
+            # drawn under load (power well above idle), or all of them when none qualifies
+            busy = [c for c, w in zip(sm, power) if w >= 0.5 * max(power)]
+            loaded = busy or sm
             out.update(sm_mhz=statistics.median(loaded), sm_max_mhz=max(mx), reasons=sorted(reasons),
                        samples=len(sm), power_w_max=max(power))
         return out
@@ -241,11 +243,14 @@ def main():
                                "ratio": round(e2e / 9654, 3)},
         }
         print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
-    # captured CUDA graphs hold NCCL kernels; destroying the communicator under them can block
     sys.stdout.flush()
-    os._exit(0)
+    if world == 1:
+        return 0
+    dist.barrier()
+    # Captured CUDA graphs hold NCCL kernels and destroying the communicator under them can block, so
+    # multi-rank processes skip interpreter teardown; the registered at-exit handlers still run first.
+    from vllm_torchtpu_b200.parallel.state import leave_process
+    leave_process(0)
 
 
 if __name__ == "__main__":

@@ -1,7 +1,7 @@
 """Decode-layer chain under tensor parallelism, one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \\
-        -m vllm_torchtpu_b200.parallel.bench_tp_decode --reqs 64 --ctx 1100
+        bench_tp_decode.py --reqs 64 --ctx 1100
 
 One CUDA graph of ``--layers`` Llama-3.1-8B-shaped decoder layers (per-rank shapes, distinct weights)
 is replayed; the two row-parallel projections of a layer are reduced across ranks by
@@ -15,6 +15,9 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import torch
 import torch.distributed as dist
@@ -28,12 +31,12 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--planes", default="push,fused,nccl,none")
     a = ap.parse_args()
-    from ..config import ParallelConfig
-    from ..ops import cuda
-    from ..ops import reference as ref
-    from ..runner.attn_metadata import AttentionMetadata
-    from . import communicator
-    from .state import init_distributed
+    from vllm_torchtpu_b200.config import ParallelConfig
+    from vllm_torchtpu_b200.ops import cuda
+    from vllm_torchtpu_b200.ops import reference as ref
+    from vllm_torchtpu_b200.parallel import communicator
+    from vllm_torchtpu_b200.parallel.state import init_distributed, leave_process
+    from vllm_torchtpu_b200.runner.attn_metadata import AttentionMetadata
     world, rank = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"])
     st = init_distributed(ParallelConfig(tensor_parallel_size=world, world_size=world, rank=rank,
                                          local_rank=int(os.environ["LOCAL_RANK"])), backend="nccl", timeout_s=120)
@@ -112,9 +115,7 @@ def main():
                               "status": cuda.check_status()}), flush=True)
         del g
     dist.barrier()
-    import sys
-    sys.stdout.flush()
-    os._exit(0)
+    leave_process(0)
 
 
 if __name__ == "__main__":

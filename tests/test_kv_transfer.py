@@ -118,3 +118,39 @@ def test_offload_store_reuses_prefix():
     for i in range(12):
         llm.generate([[(7 * i + j) % 1000 for j in range(64)]], sp)
     assert llm.engine.connector.store.stats()["evictions"] > 0
+
+
+def test_offload_store_keeps_lora_and_base_kv_apart_and_releases_pins():
+    """KV computed under a LoRA adapter must not be served to a base-model request with the same
+    tokens (k_proj / v_proj are adapter targets), and a request whose admission fails after a host
+    hit gives its pinned slots back."""
+    from types import SimpleNamespace
+    from vllm_torchtpu_b200.kv_transfer.offload import HostKVStore, OffloadSchedulerHalf, block_hashes
+    store = HostKVStore(1, (2, 1, 16, 8), torch.float32, 16, pin=False)
+    half = OffloadSchedulerHalf(store, 16)
+    toks = list(range(50))
+
+    def req(rid, lora):
+        return SimpleNamespace(request_id=rid, all_token_ids=toks, num_tokens=len(toks), num_computed_tokens=48,
+                               error=None, sampling_params=SimpleNamespace(lora_name=lora))
+    # a finished adapter request saves three blocks
+    delay, _ = half.request_finished(req("a", "adapter-1"), [5, 6, 7])
+    assert delay
+    for h in half._saves[0][1]:
+        store.commit(store.reserve(h), True)
+    assert store.stats()["pinned"] == 0
+    assert block_hashes(toks, 16, 3, ("adapter-1",)) != block_hashes(toks, 16, 3)
+    assert half.get_num_new_matched_tokens(req("base", None), 0) == (0, False)
+    assert half.get_num_new_matched_tokens(req("other", "adapter-2"), 0) == (0, False)
+    n, _ = half.get_num_new_matched_tokens(req("same", "adapter-1"), 0)
+    assert n == 48 and store.stats()["pinned"] == 3
+    # the scheduler could not allocate: the pins are returned; a second query does not stack pins
+    half.request_not_admitted(req("same", "adapter-1"))
+    assert store.stats()["pinned"] == 0
+    half.get_num_new_matched_tokens(req("same", "adapter-1"), 0)
+    half.get_num_new_matched_tokens(req("same", "adapter-1"), 0)
+    assert store.stats()["pinned"] == 3
+    half.update_state_after_alloc(req("same", "adapter-1"), [1, 2, 3], 48)
+    store.unpin(half._loads[0][1])
+    assert store.stats()["pinned"] == 0
+    store.close()

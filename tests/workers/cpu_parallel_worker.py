@@ -72,9 +72,9 @@ def main():
         print("RESULT " + json.dumps({"tokens": toks}), flush=True)
     if world > 1:
         import torch.distributed as dist
+        from vllm_torchtpu_b200.parallel.state import leave_process
         dist.barrier()
-    sys.stdout.flush()
-    os._exit(0)
+        leave_process(0)
 
 
 if __name__ == "__main__":

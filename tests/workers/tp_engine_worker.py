@@ -38,11 +38,9 @@ def main():
               flush=True)
     if world > 1:
         import torch.distributed as dist
+        from vllm_torchtpu_b200.parallel.state import leave_process
         dist.barrier()
-    # captured CUDA graphs still hold NCCL kernels: tearing the communicator down under them can
-    # block, so the process leaves without destroying the group
-    sys.stdout.flush()
-    os._exit(0)
+        leave_process(0)
 
 
 if __name__ == "__main__":

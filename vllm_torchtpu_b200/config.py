@@ -167,6 +167,9 @@ class ModelConfig:
             mc.num_experts_per_tok = cfg["num_experts_per_tok"]
             mc.moe_intermediate_size = cfg["moe_intermediate_size"]
             mc.moe_renormalize = cfg.get("norm_topk_prob", True)
+            dense_first = cfg.get("mlp_only_layers") or []
+            if dense_first and dense_first == list(range(len(dense_first))):
+                mc.first_dense_layers = len(dense_first)        # leading layers with a plain MLP
         elif arch.startswith("Qwen3Next"):
             mc.architecture, mc.qk_norm = "qwen3_next", True
             mc.num_experts = cfg.get("num_experts", 0)

@@ -781,26 +781,18 @@ static void set_fp8_scales(AttnParams& p, float k_scale, float v_scale) {
 template <int D, bool FP8>
 static cudaError_t launch_decode(dim3 grid, cudaStream_t stream, const AttnParams& p) {
   constexpr int smem = DecodeSmem<D, FP8>::TOTAL;
-  static bool set = false;
-  if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         smem);
-    if (e != cudaSuccess) return e;
-    set = true;
-  }
+  static unsigned long long seen = 0;
+  cudaError_t e = ensure_dynamic_smem(attn_decode_kernel<D, FP8>, smem, &seen);
+  if (e != cudaSuccess) return e;
   return launch_pdl(attn_decode_kernel<D, FP8>, grid, dim3(128), smem, stream, p);
 }
 
 template <int D, bool FP8>
 static cudaError_t launch_prefill(dim3 grid, cudaStream_t stream, const AttnParams& p) {
   constexpr int smem = 2 * 2 * 64 * D * (FP8 ? 1 : 2);
-  static bool set = false;
-  if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D, FP8>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    set = true;
-  }
+  static unsigned long long seen = 0;
+  cudaError_t e = ensure_dynamic_smem(attn_prefill_kernel<D, FP8>, smem, &seen);
+  if (e != cudaSuccess) return e;
   attn_prefill_kernel<D, FP8><<<grid, 128, smem, stream>>>(p);
   return cudaGetLastError();
 }

@@ -475,12 +475,8 @@ extern "C" int b200_attn_prefill_tc(const void* q, const void* kv, void* out, fl
   rc = b200_make_tmap_2d(&tmKV, kv, 2, (uint64_t)num_blocks * 2 * Hkv * block_size, (uint64_t)D, (uint64_t)D * 2,
                          16, 64);
   if (rc) return rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(fa::attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         fa::SMEM_TOTAL));
-    attr_set = true;
-  }
+  static unsigned long long attr_seen = 0;
+  B200_CUDA_CHECK(ensure_dynamic_smem(fa::attn_prefill_tc_kernel, fa::SMEM_TOTAL, &attr_seen));
   // ceil(q_len / BQ) <= ceil(q_len / 64) * (64 / BQ) for BQ <= 64; BQ = 128 needs at most as many tiles
   const int tiles = p.BQ >= 64 ? num_tiles_64 : num_tiles_64 * (64 / p.BQ);
   dim3 grid(Hkv, tiles);

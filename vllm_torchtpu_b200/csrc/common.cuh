@@ -397,6 +397,20 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
 extern "C" void b200_set_last_error(const char* msg, const char* file, int line);
 extern "C" int b200_pdl_enabled();
 
+// The dynamic shared-memory limit of a kernel is an attribute of (kernel, device): a process that
+// uses a second device must set it there too.  `seen` is a per-call-site bit mask over device ordinals.
+template <typename Kernel>
+static inline cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, unsigned long long* seen) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (*seen & bit) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) *seen |= bit;
+  return e;
+}
+
 // Launch with the programmatic-stream-serialization attribute: the grid may be scheduled while the
 // previous kernel of the stream is still draining.  The kernel must execute griddepcontrol.wait
 // (pdl_wait()) before it reads anything an earlier kernel wrote.

@@ -379,9 +379,9 @@ template <bool SWIGLU>
 static int launch_pairs(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int num_sms,
                         cudaStream_t stream) {
   static int max_pairs = 0;
+  static unsigned long long attr_seen = 0;
+  B200_CUDA_CHECK(ensure_dynamic_smem(gemm_bf16_2sm_kernel<SWIGLU>, SMEM, &attr_seen));
   if (max_pairs == 0) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_2sm_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SMEM));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (num_sms / 2));
     cfg.blockDim = dim3(THREADS);

@@ -358,12 +358,8 @@ template <int BN, int KIND = 0>
 static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int grid,
                   cudaStream_t stream) {
   using C = Cfg<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_fp8_block_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::SMEM));
-    attr_set = true;
-  }
+  static unsigned long long attr_seen = 0;
+  B200_CUDA_CHECK(ensure_dynamic_smem(gemm_fp8_block_kernel<BN, KIND>, C::SMEM, &attr_seen));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(NUM_THREADS);

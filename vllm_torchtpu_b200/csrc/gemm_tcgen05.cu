@@ -1185,12 +1185,8 @@ template <int BN, int NACC, int MODE>
 static int launch_gemm_v(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int grid,
                          cudaStream_t stream) {
   using Cfg = GemmCfg<BN, NACC>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<BN, NACC, MODE>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
-    attr_set = true;
-  }
+  static unsigned long long attr_seen = 0;
+  B200_CUDA_CHECK(ensure_dynamic_smem(gemm_bf16_kernel<BN, NACC, MODE>, Cfg::SMEM, &attr_seen));
   const int threads = (p.world > 1 && (p.ar_mode < 3 || p.ar_mode == 5)) ? NUM_THREADS_FUSED : NUM_THREADS;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);

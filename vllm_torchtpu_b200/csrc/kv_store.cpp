@@ -122,6 +122,15 @@ void b200_store_unpin(void* h, const int* slots, int n) {
     if (s->slots[slots[i]].pins > 0) --s->slots[slots[i]].pins;
 }
 
+// Sum of the pin counts of all slots (slots with a lookup or a save in flight).
+int b200_store_pinned(void* h) {
+  auto* s = static_cast<Store*>(h);
+  std::lock_guard<std::mutex> lock(s->mu);
+  int n = 0;
+  for (const Slot& sl : s->slots) n += sl.pins;
+  return n;
+}
+
 void b200_store_stats(void* h, uint64_t* out4) {
   auto* s = static_cast<Store*>(h);
   std::lock_guard<std::mutex> lock(s->mu);

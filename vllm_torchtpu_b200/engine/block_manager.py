@@ -7,12 +7,23 @@ that padded table entries point at.
 """
 from __future__ import annotations
 
+import hashlib
+import struct
 from collections import OrderedDict
 from typing import Optional
 
 
 def hash_block(parent: Optional[int], tokens: tuple, extra: tuple = ()) -> int:
-    return hash((parent, tokens, extra))
+    """Identity of a full KV block: SHA-256 over the parent block's identity, the block's token ids
+    and the request attributes that change the KV contents (``extra``: LoRA adapter name, model /
+    dtype namespace), truncated to 128 bits.  Stable across processes, unlike ``hash()``
+    (reference: the chained block hashes of the prefix cache the plugin inherits from vLLM)."""
+    h = hashlib.sha256()
+    h.update(b"\0" * 16 if parent is None else int(parent).to_bytes(16, "little"))
+    h.update(struct.pack(f"<{len(tokens)}q", *tokens))
+    if extra:
+        h.update(repr(tuple(extra)).encode())
+    return int.from_bytes(h.digest()[:16], "little")
 
 
 class KVBlock:

@@ -174,6 +174,7 @@ class Scheduler:
                         blocks = self.kv.allocate_slots(req, ext, cached_blocks)
                         if blocks is None:
                             req.num_computed_tokens = 0
+                            self.connector.request_not_admitted(req)
                             break
                         self.connector.update_state_after_alloc(req, req.block_ids, ext)
                         req.num_computed_tokens = num_cached + ext

@@ -68,6 +68,10 @@ class SchedulerConnectorBase:
     def get_num_new_matched_tokens(self, request, num_cached: int):
         return 0, False
 
+    def request_not_admitted(self, request) -> None:
+        """Called when ``get_num_new_matched_tokens`` reported matches but the request could not be
+        given its blocks in this step; connectors release what the query reserved."""
+
     def update_state_after_alloc(self, request, block_ids: list, num_external: int) -> None:
         pass
 

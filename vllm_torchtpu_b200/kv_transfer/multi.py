@@ -21,6 +21,11 @@ class _MultiSched(SchedulerConnectorBase):
                 return n, is_async
         return 0, False
 
+    def request_not_admitted(self, request):
+        i = self._owner.pop(request.request_id, None)
+        if i is not None:
+            self.parts[i].request_not_admitted(request)
+
     def update_state_after_alloc(self, request, block_ids, num_external):
         i = self._owner.get(request.request_id)
         if i is not None:

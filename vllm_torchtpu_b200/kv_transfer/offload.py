@@ -30,7 +30,7 @@ class HostKVStore:
     """Pinned host slab [layer][slot][block_bytes] + the native slot index."""
 
     def __init__(self, num_layers: int, block_shape: tuple, dtype, capacity: int, pin: bool,
-                 disk_dir: str = ""):
+                 disk_dir: str = "", namespace: str = ""):
         from ..ops import cuda
         self.lib = cuda.lib()
         self.lib.b200_store_create.restype = ctypes.c_void_p
@@ -39,9 +39,14 @@ class HostKVStore:
         self.layers = [torch.zeros((capacity,) + tuple(block_shape), dtype=dtype, pin_memory=pin)
                        for _ in range(num_layers)]
         self.pool = PoolInfo("host-store", self.layers)
-        self.disk_dir = disk_dir
+        # spilled blocks of another model, KV dtype or block geometry must never be read back: each
+        # (namespace, layers, shape, dtype) gets a directory of its own
+        self.disk_dir = ""
         if disk_dir:
-            os.makedirs(disk_dir, exist_ok=True)
+            import hashlib
+            tag = hashlib.sha256(repr((namespace, num_layers, tuple(block_shape), str(dtype))).encode()).hexdigest()
+            self.disk_dir = os.path.join(disk_dir, tag[:16])
+            os.makedirs(self.disk_dir, exist_ok=True)
 
     @staticmethod
     def key(h: int) -> int:
@@ -70,7 +75,8 @@ class HostKVStore:
     def stats(self) -> dict:
         out = (ctypes.c_uint64 * 4)()
         self.lib.b200_store_stats(self.h, out)
-        return {"hits": out[0], "misses": out[1], "evictions": out[2], "stored": out[3]}
+        return {"hits": out[0], "misses": out[1], "evictions": out[2], "stored": out[3],
+                "pinned": int(self.lib.b200_store_pinned(self.h))}
 
     # ---- disk tier: one file per evicted-but-wanted block is kept simple on purpose ----
     def spill(self, h: int, slot: int) -> None:
@@ -81,7 +87,7 @@ class HostKVStore:
         p = os.path.join(self.disk_dir, f"{self.key(h):016x}.pt") if self.disk_dir else ""
         if not p or not os.path.exists(p):
             return False
-        for l, t in zip(self.layers, torch.load(p)):
+        for l, t in zip(self.layers, torch.load(p, weights_only=True)):
             l[slot].copy_(t)
         return True
 
@@ -99,15 +105,30 @@ def block_hashes(token_ids: list, block_size: int, n_blocks: int, extra: tuple =
     return out
 
 
+def _kv_identity(request) -> tuple:
+    """What, besides the tokens, decides the contents of a request's KV blocks; the same tuple the
+    GPU prefix cache hashes (engine/block_manager.py)."""
+    name = request.sampling_params.lora_name
+    return (name,) if name else ()
+
+
 class OffloadSchedulerHalf(SchedulerConnectorBase):
     def __init__(self, store: HostKVStore, block_size: int):
         self.store, self.bs = store, block_size
         self._loads, self._saves = [], []
         self._pending_load: dict = {}
 
+    def request_not_admitted(self, request) -> None:
+        """The scheduler asked for matches but could not admit the request in this step: give the
+        pinned host slots back (the next attempt looks them up again)."""
+        prev = self._pending_load.pop(request.request_id, None)
+        if prev is not None:
+            self.store.unpin(prev[1])
+
     def get_num_new_matched_tokens(self, request, num_cached: int):
+        self.request_not_admitted(request)          # a repeated query must not leak the earlier pins
         usable = (request.num_tokens - 1) // self.bs
-        hashes = block_hashes(request.all_token_ids, self.bs, usable)
+        hashes = block_hashes(request.all_token_ids, self.bs, usable, _kv_identity(request))
         slots = self.store.lookup_prefix(hashes, pin=True)
         have = num_cached // self.bs
         if len(slots) <= have:
@@ -125,7 +146,7 @@ class OffloadSchedulerHalf(SchedulerConnectorBase):
         n_full = min(request.num_computed_tokens, request.num_tokens) // self.bs
         if request.error or n_full == 0:
             return False, None
-        hashes = block_hashes(request.all_token_ids, self.bs, n_full)
+        hashes = block_hashes(request.all_token_ids, self.bs, n_full, _kv_identity(request))
         self._saves.append((request.request_id, hashes, list(block_ids)[:n_full]))
         return True, None
 
@@ -202,7 +223,8 @@ def create_offloading_connector(cfg, runner, **kw) -> Connector:
     capacity = int(extra.get("num_blocks", max(8, int(gb * 2**30) // per_block)))
     is_cuda = layers[0].is_cuda
     store = HostKVStore(len(layers), block_shape, layers[0].dtype, capacity, pin=is_cuda,
-                        disk_dir=extra.get("disk_dir", envs.B200_OFFLOAD_DISK_DIR))
+                        disk_dir=extra.get("disk_dir", envs.B200_OFFLOAD_DISK_DIR),
+                        namespace=f"{cfg.model.name}/{cfg.model_path or ''}")
     c = Connector(OffloadSchedulerHalf(store, cfg.cache.block_size),
                   OffloadWorkerHalf(store, PoolInfo("gpu", layers), is_cuda))
     c.store = store

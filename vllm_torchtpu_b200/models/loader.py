@@ -36,23 +36,36 @@ def iter_safetensors(path: str) -> Iterator[tuple]:
                 yield name, sf.get_tensor(name)
 
 
-class _Pending:
-    """Collects the pieces of a fused parameter."""
+class _Collector:
+    """Buffers the pieces of one parameter (the q/k/v or gate/up parts of a fused matrix, and for
+    block-scaled fp8 checkpoints the ``weight_scale_inv`` grid of every part) until all of them have
+    been read, in whatever order the files list them, then calls ``done(parts)`` once."""
 
-    def __init__(self, need: tuple):
-        self.need = need
-        self.parts: dict = {}
+    def __init__(self, need: set, done):
+        self.need, self.done, self.parts = set(need), done, {}
 
-    def add(self, key, t):
-        self.parts[key] = t
-        return all(k in self.parts for k in self.need)
-
-    def cat(self):
-        return torch.cat([self.parts[k] for k in self.need], 0)
+    def add(self, key, tensor) -> bool:
+        self.parts[key] = tensor
+        if self.need.issubset(self.parts):
+            self.done(self.parts)
+            return True
+        return False
 
 
 def _set_vec(dst: torch.Tensor, src: torch.Tensor) -> None:
     dst.copy_(src.to(device=dst.device, dtype=dst.dtype))
+
+
+def list_tensor_names(path: str) -> set:
+    from safetensors import safe_open
+    names = set()
+    for f in sorted(glob.glob(os.path.join(path, "*.safetensors"))):
+        with safe_open(f, framework="pt", device="cpu") as sf:
+            names.update(sf.keys())
+    return names
+
+
+_FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
 
 
 def load_safetensors(model, path: str) -> None:
@@ -60,23 +73,50 @@ def load_safetensors(model, path: str) -> None:
     st = get_state()
     lo, hi = model.layer_range
     layers = {lo + i: l for i, l in enumerate(model.layers)}
-    pend: dict = {}
-    scales: dict = {}
+    names = list_tensor_names(path)
+    open_groups: dict = {}
     seen = 0
     rx = re.compile(r"^model\.layers\.(\d+)\.(.+)$")
 
-    def fused(key, need, part, tensor, target, suffix):
-        p = pend.setdefault((key, suffix), _Pending(need))
-        if p.add(part, tensor):
-            if suffix == "weight":
-                kw = {}
-                sp = pend.get((key, "weight_scale_inv"))
-                if sp is not None and all(k in sp.parts for k in need):
-                    kw["scale_inv"] = sp.cat()
-                target.load_weight(p.cat(), **kw)
-            elif suffix == "bias":
-                target.bias = target.shard_of(p.cat()[:, None])[:, 0].to(device=target.device,
-                                                                         dtype=target.dtype).contiguous()
+    def submit(gid, ckpt_prefixes: dict, part: str, kind: str, tensor, done) -> None:
+        """Piece ``kind`` ("weight" or "weight_scale_inv") of ``part`` of parameter group ``gid``;
+        ``ckpt_prefixes`` maps every part to its checkpoint name so that the group knows which scale
+        tensors the checkpoint holds.  ``done(parts)`` gets {(part, kind): tensor}."""
+        g = open_groups.get(gid)
+        if g is None:
+            need = set()
+            for pt, prefix in ckpt_prefixes.items():
+                need.add((pt, "weight"))
+                if prefix + ".weight_scale_inv" in names:
+                    need.add((pt, "weight_scale_inv"))
+            g = open_groups[gid] = _Collector(need, done)
+        if g.add((part, kind), tensor):
+            del open_groups[gid]
+
+    def cat_parts(parts, order, kind):
+        got = [parts.get((p, kind)) for p in order]
+        if any(t is None for t in got):
+            return None
+        return torch.cat(got, 0) if len(got) > 1 else got[0]
+
+    def load_linear(target, order, what):
+        def done(parts):
+            w = cat_parts(parts, order, "weight")
+            s = cat_parts(parts, order, "weight_scale_inv")
+            if w.dtype in _FP8_DTYPES and s is None:
+                raise ValueError(f"{what}: the checkpoint holds fp8 weights without weight_scale_inv")
+            bn = int(cfg.weight_block_size[0])
+            if s is not None and any(parts[(p, "weight")].shape[0] % bn for p in order[:-1]):
+                # the row blocks of the packed pieces do not line up with one grid: expand each piece
+                from ..quantization.fp8 import dequantize_weight_block
+                w = torch.cat([dequantize_weight_block(parts[(p, "weight")], parts[(p, "weight_scale_inv")].float(),
+                                                       tuple(cfg.weight_block_size)) for p in order], 0)
+                s = None
+            target.load_weight(w, **({"scale_inv": s} if s is not None else {}))
+        return done
+
+    def linear_piece(gid, target, prefixes: dict, part, kind, t, what):
+        submit(gid, prefixes, part, kind, t, load_linear(target, tuple(prefixes), what))
 
     for name, t in iter_safetensors(path):
         seen += 1
@@ -101,40 +141,66 @@ def load_safetensors(model, path: str) -> None:
             continue
         layer = layers[li]
         a = layer.self_attn
+        pre = f"model.layers.{li}."
         if rest == "input_layernorm.weight":
             _set_vec(layer.input_ln, t)
         elif rest == "post_attention_layernorm.weight":
             _set_vec(layer.post_ln, t)
         elif rest.startswith("self_attn."):
             sub = rest[len("self_attn."):]
+            ap = pre + "self_attn."
             pm = re.match(r"^([qkv])_proj\.(weight|bias|weight_scale_inv)$", sub)
+            om = re.match(r"^o_proj\.(weight|weight_scale_inv)$", sub)
+            mm = re.match(r"^(q_a_proj|q_b_proj|q_proj|kv_a_proj_with_mqa|kv_b_proj)\.(weight|weight_scale_inv)$", sub)
             if pm and hasattr(a, "qkv"):
-                fused(("qkv", li), ("q", "k", "v"), pm.group(1), t, a.qkv, pm.group(2))
-            elif sub == "o_proj.weight":
-                a.o.load_weight(t, scale_inv=scales.pop((li, "o"), None)) if hasattr(a, "o") else None
+                if pm.group(2) == "bias":
+                    def bias_done(parts, target=a.qkv):
+                        full = torch.cat([parts[(p, "weight")] for p in ("q", "k", "v")], 0)
+                        target.bias = target.shard_of(full[:, None])[:, 0].to(
+                            device=target.device, dtype=target.dtype).contiguous()
+                    g = open_groups.setdefault(("qkv_bias", li), _Collector(
+                        {(p, "weight") for p in ("q", "k", "v")}, bias_done))
+                    if g.add((pm.group(1), "weight"), t):
+                        del open_groups[("qkv_bias", li)]
+                else:
+                    linear_piece(("qkv", li), a.qkv, {p: f"{ap}{p}_proj" for p in ("q", "k", "v")},
+                                 pm.group(1), pm.group(2), t, f"{ap}qkv_proj")
+            elif om and hasattr(a, "o"):
+                linear_piece(("o", li), a.o, {"o": ap + "o_proj"}, "o", om.group(1), t, ap + "o_proj")
             elif sub == "q_norm.weight" and a.q_norm_w is not None:
                 _set_vec(a.q_norm_w, t)
             elif sub == "k_norm.weight" and a.k_norm_w is not None:
                 _set_vec(a.k_norm_w, t)
             elif hasattr(a, "kv_a"):                      # MLA
-                simple = {"q_a_proj.weight": "q_a", "q_b_proj.weight": "q_b", "q_proj.weight": "q_b",
-                          "kv_a_proj_with_mqa.weight": "kv_a"}
-                if sub in simple and getattr(a, simple[sub], None) is not None:
-                    getattr(a, simple[sub]).load_weight(t)
+                simple = {"q_a_proj": "q_a", "q_b_proj": "q_b", "q_proj": "q_b", "kv_a_proj_with_mqa": "kv_a"}
+                if mm and mm.group(1) in simple and getattr(a, simple[mm.group(1)], None) is not None:
+                    linear_piece((mm.group(1), li), getattr(a, simple[mm.group(1)]),
+                                 {"w": ap + mm.group(1)}, "w", mm.group(2), t, ap + mm.group(1))
+                elif mm and mm.group(1) == "kv_b_proj":
+                    def kvb_done(parts, a=a):
+                        w, s = parts[("w", "weight")], parts.get(("w", "weight_scale_inv"))
+                        if w.dtype in _FP8_DTYPES:
+                            if s is None:
+                                raise ValueError("kv_b_proj: fp8 weights without weight_scale_inv")
+                            from ..quantization.fp8 import dequantize_weight_block
+                            w = dequantize_weight_block(w, s.float(), tuple(cfg.weight_block_size))
+                        a.load_kv_b(w.to(device=model.device, dtype=cfg.dtype))
+                    submit(("kv_b", li), {"w": ap + "kv_b_proj"}, "w", mm.group(2), t, kvb_done)
                 elif sub == "q_a_layernorm.weight":
                     _set_vec(a.q_a_ln, t)
                 elif sub == "kv_a_layernorm.weight":
                     _set_vec(a.kv_a_ln, t)
-                elif sub == "kv_b_proj.weight":
-                    a.load_kv_b(t.to(device=model.device, dtype=cfg.dtype))
         elif rest.startswith("mlp."):
             sub = rest[len("mlp."):]
+            mp = pre + "mlp."
             mlp = layer.mlp
             pm = re.match(r"^(gate|up)_proj\.(weight|weight_scale_inv)$", sub)
+            dm = re.match(r"^down_proj\.(weight|weight_scale_inv)$", sub)
             if pm and hasattr(mlp, "gate_up"):
-                fused(("gu", li), ("gate", "up"), pm.group(1), t, mlp.gate_up, pm.group(2))
-            elif sub == "down_proj.weight" and hasattr(mlp, "down"):
-                mlp.down.load_weight(t)
+                linear_piece(("gu", li), mlp.gate_up, {p: f"{mp}{p}_proj" for p in ("gate", "up")},
+                             pm.group(1), pm.group(2), t, mp + "gate_up_proj")
+            elif dm and hasattr(mlp, "down"):
+                linear_piece(("down", li), mlp.down, {"d": mp + "down_proj"}, "d", dm.group(1), t, mp + "down_proj")
             elif hasattr(mlp, "experts"):
                 moe = mlp.experts
                 if sub == "gate.weight":
@@ -142,27 +208,33 @@ def load_safetensors(model, path: str) -> None:
                 elif sub == "gate.e_score_correction_bias" and moe.score_bias is not None:
                     _set_vec(moe.score_bias, t)
                 else:
-                    em = re.match(r"^experts\.(\d+)\.(gate|up|down)_proj\.weight$", sub)
-                    sm = re.match(r"^shared_experts?\.(gate|up|down)_proj\.weight$", sub)
+                    em = re.match(r"^experts\.(\d+)\.(gate|up|down)_proj\.(weight|weight_scale_inv)$", sub)
+                    sm = re.match(r"^(shared_experts?)\.(gate|up|down)_proj\.(weight|weight_scale_inv)$", sub)
                     if em:
                         e = int(em.group(1))
                         elo, ehi = moe.expert_range
                         if elo <= e < ehi:               # expert-parallel weight filter
-                            p = pend.setdefault(("exp", li, e), _Pending(("gate", "up", "down")))
-                            if p.add(em.group(2), t):
+                            def exp_done(parts, moe=moe, e=e, elo=elo):
                                 if moe.w13 is None:
                                     moe.method.alloc(moe)
-                                I, r, n = moe.intermediate_size, moe.tp_rank, moe.tp_size
-                                g = p.parts["gate"][r * I:(r + 1) * I] if n > 1 else p.parts["gate"]
-                                u = p.parts["up"][r * I:(r + 1) * I] if n > 1 else p.parts["up"]
-                                d = p.parts["down"][:, r * I:(r + 1) * I] if n > 1 else p.parts["down"]
-                                moe.method.load_expert(moe, e - elo, g, u, d)
-                                del pend[("exp", li, e)]
+                                moe.method.load_expert(
+                                    moe, e - elo, parts[("gate", "weight")], parts[("up", "weight")],
+                                    parts[("down", "weight")],
+                                    scales=tuple(parts.get((p, "weight_scale_inv")) for p in ("gate", "up", "down")))
+                            submit(("exp", li, e), {p: f"{mp}experts.{e}.{p}_proj" for p in ("gate", "up", "down")},
+                                   em.group(2), em.group(3), t, exp_done)
                     elif sm and mlp.shared is not None:
-                        if sm.group(1) == "down":
-                            mlp.shared.down.load_weight(t)
+                        sp = mp + sm.group(1) + "."
+                        if sm.group(2) == "down":
+                            linear_piece(("sdown", li), mlp.shared.down, {"d": sp + "down_proj"}, "d", sm.group(3), t,
+                                         sp + "down_proj")
                         else:
-                            fused(("sgu", li), ("gate", "up"), sm.group(1), t, mlp.shared.gate_up, "weight")
+                            linear_piece(("sgu", li), mlp.shared.gate_up,
+                                         {p: f"{sp}{p}_proj" for p in ("gate", "up")}, sm.group(2), sm.group(3), t,
+                                         sp + "gate_up_proj")
+    if open_groups:
+        missing = {str(k): sorted(map(str, g.need - set(g.parts))) for k, g in list(open_groups.items())[:4]}
+        raise ValueError(f"checkpoint {path} is incomplete; missing pieces (first groups): {missing}")
     logger.info("loaded %d tensors from %s on rank %d", seen, path, st.rank)
 
 

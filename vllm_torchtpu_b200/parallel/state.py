@@ -171,6 +171,24 @@ def set_state_for_test(**kw) -> ParallelState:
     return _STATE
 
 
+def leave_process(code: int = 0) -> None:
+    """End a multi-rank process without tearing the communicators down.
+
+    Captured CUDA graphs hold NCCL kernels, and destroying a communicator under them can block; so
+    ranks of a multi-GPU job skip the interpreter's teardown.  The registered at-exit handlers (coverage
+    and library-load recorders among them) still run first, and the standard streams are flushed."""
+    import atexit
+    import sys
+    sys.stdout.flush()
+    sys.stderr.flush()
+    try:
+        atexit._run_exitfuncs()
+    finally:
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(code)
+
+
 def destroy() -> None:
     global _STATE
     if dist.is_initialized():

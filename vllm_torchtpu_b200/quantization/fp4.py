@@ -135,6 +135,22 @@ class Mxfp4MoEMethod:
             c.append(q); d.append(s)
         moe.w13, moe.w13_scale, moe.w2, moe.w2_scale = map(torch.stack, (a, b, c, d))
 
+    def alloc(self, moe) -> None:
+        E, I, H = moe.num_local_experts, moe.intermediate_size, moe.hidden_size
+        moe.w13 = torch.zeros(E, 2 * I, H // 2, dtype=torch.uint8, device=moe.device)
+        moe.w2 = torch.zeros(E, H, I // 2, dtype=torch.uint8, device=moe.device)
+        moe.w13_scale = torch.zeros(E, 2 * I, H // 32, dtype=torch.uint8, device=moe.device)
+        moe.w2_scale = torch.zeros(E, H, I // 32, dtype=torch.uint8, device=moe.device)
+
+    def load_expert(self, moe, local_e, gate, up, down, scales=(None, None, None)) -> None:
+        """One expert from a bf16 (or block-scaled fp8) checkpoint, quantised to mxfp4 here."""
+        from .unquantized import dequant_expert_pieces, expert_tp_shard
+        g, u, d = expert_tp_shard(moe, *dequant_expert_pieces(moe, (gate, up, down), scales))
+        q, s = quantize_mxfp4(torch.cat([g, u], 0).to(moe.device).float())
+        moe.w13[local_e], moe.w13_scale[local_e] = q, s
+        q, s = quantize_mxfp4(d.to(moe.device).float())
+        moe.w2[local_e], moe.w2_scale[local_e] = q, s
+
     def apply(self, moe, x, topk_ids, topk_w):
         w13 = dequantize_mxfp4(moe.w13, moe.w13_scale).to(x.dtype)
         w2 = dequantize_mxfp4(moe.w2, moe.w2_scale).to(x.dtype)

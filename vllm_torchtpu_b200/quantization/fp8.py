@@ -96,6 +96,8 @@ class Fp8BlockLinearMethod(LinearMethodBase):
             self._set(layer, layer.shard_of(full_weight.to(layer.device)))
             return
         # checkpoint already quantised: slice weight and scale grid consistently
+        if scale_inv is None:
+            raise ValueError(f"{layer.name}: fp8 checkpoint weight without weight_scale_inv")
         w = layer.shard_of(full_weight.to(layer.device))
         deq_full_rows = layer.shard_of(dequantize_weight_block(full_weight.to(layer.device),
                                                                scale_inv.to(layer.device).float(), self.block))
@@ -103,7 +105,6 @@ class Fp8BlockLinearMethod(LinearMethodBase):
         aligned = (w.shape[0] % bn == 0 or w.shape[0] == full_weight.shape[0]) and \
                   (w.shape[1] % bk == 0 or w.shape[1] == full_weight.shape[1])
         if aligned and envs.B200_REQUANTIZE_BLOCK_SIZE is None:
-            _, s = quantize_weight_block(deq_full_rows, self.block)     # same grid, recomputed for the shard
             layer.weight, layer.weight_scale_inv = w.contiguous(), self._slice_scales(layer, scale_inv)
             if layer.weight_scale_inv is None:
                 layer.weight, layer.weight_scale_inv = quantize_weight_block(deq_full_rows, self.block)
@@ -111,16 +112,19 @@ class Fp8BlockLinearMethod(LinearMethodBase):
             layer.weight, layer.weight_scale_inv = quantize_weight_block(deq_full_rows, self.block)
 
     def _slice_scales(self, layer, scale_inv):
-        """Scale grid rows/cols of this rank's shard when the shard starts on block boundaries."""
-        try:
-            ones = torch.arange(scale_inv.numel(), dtype=torch.float32).view_as(scale_inv)
-            bn, bk = self.block
-            full_idx = ones.repeat_interleave(bn, 0)[:layer.full_out].repeat_interleave(bk, 1)[:, :layer.full_in]
-            shard_idx = layer.shard_of(full_idx)
-            rows = shard_idx[::bn, ::bk].long()
-            return scale_inv.to(layer.device).float().flatten()[rows.to(layer.device)].contiguous()
-        except Exception:
+        """Scale grid of this rank's shard, or None when some 128x128 block of the shard mixes
+        elements of several checkpoint blocks (e.g. half a k block packed next to half a v block)."""
+        bn, bk = self.block
+        ids = torch.arange(scale_inv.numel(), dtype=torch.float32).view_as(scale_inv)
+        full_idx = ids.repeat_interleave(bn, 0)[:layer.full_out].repeat_interleave(bk, 1)[:, :layer.full_in]
+        shard_idx = layer.shard_of(full_idx)
+        N, K = shard_idx.shape
+        nb, kb = -(-N // bn), -(-K // bk)
+        first = shard_idx[::bn, ::bk]
+        expect = first.repeat_interleave(bn, 0)[:N].repeat_interleave(bk, 1)[:, :K]
+        if first.shape != (nb, kb) or not torch.equal(expect, shard_idx):
             return None
+        return scale_inv.to(layer.device).float().flatten()[first.long().to(layer.device)].contiguous()
 
     def apply(self, layer, x, bias=None):
         if x.is_cuda:
@@ -198,6 +202,40 @@ class Fp8BlockMoEMethod:
             q13.append(a); s13.append(b); q2.append(c); s2.append(d)
         moe.w13, moe.w13_scale = torch.stack(q13), torch.stack(s13)
         moe.w2, moe.w2_scale = torch.stack(q2), torch.stack(s2)
+
+    def alloc(self, moe) -> None:
+        E, I, H = moe.num_local_experts, moe.intermediate_size, moe.hidden_size
+        bn, bk = self.block
+        moe.w13 = torch.zeros(E, 2 * I, H, dtype=FP8, device=moe.device)
+        moe.w2 = torch.zeros(E, H, I, dtype=FP8, device=moe.device)
+        moe.w13_scale = torch.ones(E, -(-2 * I // bn), -(-H // bk), dtype=torch.float32, device=moe.device)
+        moe.w2_scale = torch.ones(E, -(-H // bn), -(-I // bk), dtype=torch.float32, device=moe.device)
+
+    def load_expert(self, moe, local_e, gate, up, down, scales=(None, None, None)) -> None:
+        """One expert from the checkpoint (unsharded matrices).  Pieces that are already e4m3 with a
+        scale grid are kept bit-exact when this rank's slice starts and ends on block boundaries;
+        anything else (bf16 checkpoints, unaligned TP slices) goes through dequantise + quantise."""
+        from .unquantized import dequant_expert_pieces, expert_tp_shard
+        I, r, n = moe.intermediate_size, moe.tp_rank, moe.tp_size
+        bn, bk = self.block
+        dev = moe.device
+        all_fp8 = all(w.dtype == FP8 and s is not None for w, s in zip((gate, up, down), scales))
+        if all_fp8 and I % bn == 0 and I % bk == 0:
+            g, u, d = expert_tp_shard(moe, gate, up, down)
+            gs, us, ds = scales
+            rb, cb = I // bn, I // bk
+            if n > 1:
+                gs, us, ds = gs[r * rb:(r + 1) * rb], us[r * rb:(r + 1) * rb], ds[:, r * cb:(r + 1) * cb]
+            moe.w13[local_e, :I], moe.w13[local_e, I:] = g.to(dev), u.to(dev)
+            moe.w2[local_e] = d.to(dev)
+            moe.w13_scale[local_e, :rb], moe.w13_scale[local_e, rb:] = gs.to(dev).float(), us.to(dev).float()
+            moe.w2_scale[local_e] = ds.to(dev).float()
+            return
+        g, u, d = expert_tp_shard(moe, *dequant_expert_pieces(moe, (gate, up, down), scales))
+        q13, s13 = quantize_weight_block(torch.cat([g, u], 0).to(dev).float(), self.block)
+        q2, s2 = quantize_weight_block(d.to(dev).float(), self.block)
+        moe.w13[local_e], moe.w13_scale[local_e] = q13, s13
+        moe.w2[local_e], moe.w2_scale[local_e] = q2, s2
 
     def apply(self, moe, x, topk_ids, topk_w):
         if x.is_cuda:

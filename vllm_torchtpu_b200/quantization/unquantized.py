@@ -53,6 +53,28 @@ class UnquantizedLinearMethod(LinearMethodBase):
         return layer.weight.numel() * layer.weight.element_size()
 
 
+def dequant_expert_pieces(moe, pieces, scales):
+    """fp8 checkpoint pieces with their ``weight_scale_inv`` grids -> float tensors (others pass through)."""
+    out = []
+    for w, sc in zip(pieces, scales):
+        if w.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+            if sc is None:
+                raise ValueError(f"{moe.name}: fp8 expert weights without weight_scale_inv")
+            from .fp8 import dequantize_weight_block
+            w = dequantize_weight_block(w, sc.float(), tuple(getattr(moe.cfg, "weight_block_size", (128, 128))))
+        out.append(w)
+    return out
+
+
+def expert_tp_shard(moe, gate, up, down):
+    """Rows of gate / up and columns of down that belong to this rank when the experts' intermediate
+    dimension is sharded over tensor parallelism (no expert parallelism)."""
+    I, r, n = moe.intermediate_size, moe.tp_rank, moe.tp_size
+    if n == 1:
+        return gate, up, down
+    return gate[r * I:(r + 1) * I], up[r * I:(r + 1) * I], down[:, r * I:(r + 1) * I]
+
+
 class UnquantizedMoEMethod:
     name = "unquantized"
 
@@ -72,7 +94,10 @@ class UnquantizedMoEMethod:
         moe.w13 = torch.stack(w13).contiguous()
         moe.w2 = torch.stack(w2).contiguous()
 
-    def load_expert(self, moe, local_e, gate, up, down) -> None:
+    def load_expert(self, moe, local_e, gate, up, down, scales=(None, None, None)) -> None:
+        """Unsharded checkpoint matrices of one expert; the intermediate dimension is sliced for this
+        TP rank here.  Block-scaled fp8 pieces (``scales`` given) are expanded first."""
+        gate, up, down = expert_tp_shard(moe, *dequant_expert_pieces(moe, (gate, up, down), scales))
         I = moe.intermediate_size
         moe.w13[local_e, :I] = gate.to(moe.w13.dtype)
         moe.w13[local_e, I:] = up.to(moe.w13.dtype)
