@@ -17,8 +17,8 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(nproc, *args, timeout=240):
-    worker = os.path.join(HERE, "workers", "cpu_parallel_worker.py")
+def _run(nproc, *args, timeout=240, script="cpu_parallel_worker.py"):
+    worker = os.path.join(HERE, "workers", script)
     if nproc == 1:
         cmd = [sys.executable, worker, *args]
     else:
@@ -72,3 +72,10 @@ def test_tp2_pads_query_heads_that_do_not_divide():
     """3 query heads on 2 ranks: every KV group is zero-padded to 4 heads (q_proj rows and o_proj columns),
     the KV head is replicated, and the tokens equal the one-process run."""
     assert _run(2, "tp", "tiny-odd-heads") == _run(1, "tp", "tiny-odd-heads")
+
+
+@pytest.mark.parametrize("flags", [(), ("--async",)])
+def test_tp2_server_requests_reach_every_rank(single, flags):
+    """HTTP requests arrive at rank 0 only; it broadcasts them step by step and the follower rank runs
+    the same steps, so the completions equal the one-process tokens."""
+    assert _run(2, "cpu", *flags, script="serve_sync_worker.py") == single

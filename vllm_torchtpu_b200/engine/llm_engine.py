@@ -2,9 +2,15 @@
 
 One engine drives one model replica (all TP/PP ranks of that replica run this
 same loop in lockstep: the scheduler is deterministic, so every rank derives
-the same SchedulerOutput from the same request stream and no per-step broadcast
-is needed).  With async scheduling the loop keeps one step in flight: step n+1
-is scheduled and launched while step n's tokens travel back to the host.
+the same SchedulerOutput from the same request stream).  Offline, every rank is
+handed the same prompts.  Behind a server only the replica's first rank sees
+HTTP requests: it broadcasts, once per step, the requests added and aborted since
+the previous step, and the other ranks follow (``enable_request_sync`` /
+``follow``); this plays the part of the reference's executor, which broadcasts
+every scheduler output to its workers
+(reference: src/vllm_torchtpu/executors/tpu_multiproc_executor.py:29-61).
+With async scheduling the loop keeps one step in flight: step n+1 is scheduled
+and launched while step n's tokens travel back to the host.
 """
 from __future__ import annotations
 
@@ -25,6 +31,28 @@ from .request import Request
 from .scheduler import Scheduler
 
 logger = init_logger(__name__)
+
+
+class ReplicaRequestSync:
+    """Request stream of one replica, leader to followers: one object broadcast on the CPU (gloo)
+    group per engine step carrying the operations to apply before that step."""
+
+    def __init__(self, group):
+        self.group = group
+        self.is_leader = group.rank_in_group == 0
+        self.pending: list = []
+        self.stopped = False
+        self.last_exchange = time.monotonic()
+
+    def exchange(self, step: bool, stop: bool = False) -> dict:
+        import torch.distributed as dist
+        box = [None]
+        if self.is_leader:
+            box[0] = {"ops": self.pending, "step": step, "stop": stop}
+            self.pending = []
+        dist.broadcast_object_list(box, src=self.group.ranks[0], group=self.group.cpu_group)
+        self.last_exchange = time.monotonic()
+        return box[0]
 
 
 def make_scheduler(cfg: EngineConfig, num_blocks: int, connector=None, num_spec_tokens: int = 0):
@@ -87,6 +115,67 @@ class LLMEngine:
         self._next_id = 0
         self.eos_token_id: Optional[int] = None
         self.step_count = 0
+        self._sync: Optional[ReplicaRequestSync] = None
+        self._applying = False
+
+    # ---- request stream of a multi-rank replica behind a server ---------------------------------
+    def enable_request_sync(self) -> bool:
+        """Call on every rank before serving.  From then on requests are given to the first rank only
+        (``add_request`` / ``abort_request`` / the LoRA calls queue there) and reach the other ranks,
+        which run ``follow()``, with the next step."""
+        st = get_state()
+        if st.world_size == 1:
+            return False
+        if st.dp.size > 1:
+            raise NotImplementedError("one server per data-parallel replica: request sync covers TP x PP ranks")
+        self._sync = ReplicaRequestSync(st.world)
+        return True
+
+    def _queue_op(self, op: tuple) -> bool:
+        if self._sync is not None and self._sync.is_leader and not self._applying:
+            self._sync.pending.append(op)
+            return True
+        return False
+
+    def _sync_point(self, step: bool, stop: bool = False) -> dict:
+        msg = self._sync.exchange(step, stop)
+        self._applying = True
+        try:
+            for op in msg["ops"]:
+                kind = op[0]
+                try:
+                    if kind == "add":
+                        self.add_request(*op[1], **op[2])
+                    elif kind == "abort":
+                        self.abort_request(op[1])
+                    elif kind == "call":
+                        getattr(self, op[1])(*op[2])
+                except Exception as e:      # noqa: BLE001 - the leader validated the same operation
+                    logger.error("request operation %s failed on rank %d: %r", kind, get_state().rank, e)
+        finally:
+            self._applying = False
+        return msg
+
+    def idle_tick(self, every_s: float = 2.0) -> None:
+        """Leader, while idle: keep the followers' blocking receive from timing out."""
+        if self._sync is not None and self._sync.is_leader and not self._sync.stopped and \
+                time.monotonic() - self._sync.last_exchange > every_s:
+            self._sync_point(step=False)
+
+    def stop_followers(self) -> None:
+        if self._sync is not None and self._sync.is_leader and not self._sync.stopped:
+            self._sync.stopped = True
+            self._sync_point(step=False, stop=True)
+
+    def follow(self) -> None:
+        """Ranks other than the replica's first: apply what the leader broadcasts and step with it."""
+        assert self._sync is not None and not self._sync.is_leader
+        while True:
+            msg = self._sync_point(step=False)
+            if msg["stop"]:
+                return
+            if msg["step"]:
+                self._step_inner()
 
     # ---- requests ---------------------------------------------------------------
     def add_request(self, prompt_token_ids: list, sampling_params: Optional[SamplingParams] = None,
@@ -104,6 +193,9 @@ class LLMEngine:
             raise ValueError("empty prompt")
         rid = request_id or f"req-{self._next_id}"
         self._next_id += 1
+        if self._queue_op(("add", (list(prompt_token_ids), sp), dict(request_id=rid, mm_items=mm_items,
+                                                                      kv_transfer_params=kv_transfer_params))):
+            return rid          # applied on every rank, this one included, at the next step
         if sp.structured:
             if self.runner.structured is None:
                 from ..structured import StructuredDecodingManager
@@ -152,12 +244,18 @@ class LLMEngine:
     def add_lora(self, name: str, rank: int, alpha: float, weights: dict) -> bool:
         """weights: {"model.layers.N.self_attn.q_proj": (A [r, in], B [out, r]), ...}."""
         from ..lora import LoRAAdapter
+        if self._queue_op(("call", "add_lora", (name, rank, alpha, weights))):
+            return True
         return self._lora().add_adapter(LoRAAdapter(name, rank, alpha, weights))
 
     def remove_lora(self, name: str) -> bool:
+        if self._queue_op(("call", "remove_lora", (name,))):
+            return True
         return self._lora().remove_adapter(name)
 
     def pin_lora(self, name: str) -> bool:
+        if self._queue_op(("call", "pin_lora", (name,))):
+            return True
         return self._lora().pin_adapter(name)
 
     def list_loras(self) -> list:
@@ -185,9 +283,13 @@ class LLMEngine:
         return out
 
     def abort_request(self, request_id: str) -> None:
+        if self._queue_op(("abort", request_id)):
+            return
         self.scheduler.abort_request(request_id)
 
     def has_unfinished(self) -> bool:
+        if self._sync is not None and self._sync.pending:
+            return True
         if self._dp_lockstep:
             # a rank without requests keeps stepping (dummy batches) while any replica has work
             return self._dp_group_busy or self.scheduler.has_unfinished() or bool(self._inflight)
@@ -202,8 +304,15 @@ class LLMEngine:
             st = get_state()
             t_pad, eager = self.runner.step_shape(out)
             busy = 1 if (out.scheduled or self.scheduler.has_unfinished()) else 0
-            agreed = DeviceCommunicator(st.dp, None).cpu_all_reduce_max([t_pad, eager, busy])
+            throttled = hasattr(self.scheduler, "throttle_prefills")
+            pending = self.scheduler.pending_prefill_tokens() if throttled else 0
+            agreed = DeviceCommunicator(st.dp, None).cpu_all_reduce_max([t_pad, eager, busy, pending])
             self._dp_group_busy = bool(agreed[2])
+            if throttled:
+                # replicas admit prefills in the same steps, so that one replica's long prefill does
+                # not stretch the decode steps of the others more often than necessary
+                # (reference: src/vllm_torchtpu/core/tpu_scheduler.py:22-57)
+                self.scheduler.throttle_prefills([agreed[3]])
             if not self._dp_group_busy:
                 return out, self.runner.execute_model(out)           # nothing anywhere: empty result
             if not out.scheduled:
@@ -277,6 +386,9 @@ class LLMEngine:
         from ..engine.request import RequestStatus
         logger.error("step failed: %s", err)
         self.runner.status_dev.zero_()
+        mega = getattr(self.runner.model, "decode_mega", None)
+        if mega is not None:
+            mega.reset()                 # the persistent kernel left its barrier words mid-step
         self.device_errors = getattr(self, "device_errors", 0) + 1
         failed = []
         for s in out.scheduled:
@@ -291,6 +403,11 @@ class LLMEngine:
 
     def step(self) -> list:
         """Advance the engine; returns requests that finished."""
+        if self._sync is not None:
+            self._sync_point(step=True)
+        return self._step_inner()
+
+    def _step_inner(self) -> list:
         self.step_count += 1
         if not self.scheduler.async_mode:
             out, res = self._launch()

@@ -80,6 +80,7 @@ class AsyncEngine:
             except queue.Empty:
                 pass
             if not eng.has_unfinished():
+                eng.idle_tick()
                 time.sleep(0.001)
                 continue
             finished = eng.step()
@@ -148,3 +149,4 @@ class AsyncEngine:
     def shutdown(self):
         self._stop = True
         self._thread.join(timeout=2.0)
+        self.engine.stop_followers()

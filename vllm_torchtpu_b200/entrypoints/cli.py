@@ -2,8 +2,8 @@
 
 Flag names follow the ``vllm serve`` surface the reference is driven with
 (reference: docs/user_guide/parallelism.md:5-21, docs/user_guide/supported_models.md:58-77).
-Under tensor parallelism launch with ``torch.distributed.run``; every rank runs the engine in
-lockstep and rank 0 serves HTTP."""
+Under tensor or pipeline parallelism launch with ``torch.distributed.run``; rank 0 serves HTTP and
+broadcasts the request stream, the other ranks follow it step by step."""
 from __future__ import annotations
 
 import argparse
@@ -111,9 +111,17 @@ def main(argv=None) -> int:
     llm = make_llm(a)
     rank = int(os.environ.get("RANK", "0"))
     name = a.served_model_name or llm.engine.cfg.model.name
+    # several ranks: rank 0 takes the HTTP requests and broadcasts them step by step, the others follow
+    synced = llm.engine.enable_request_sync()
     if rank == 0:
         from .openai_server import serve
-        serve(llm.engine, name, llm.tokenizer, a.host, a.port)
-    else:
-        llm.engine.run_until_done()
+        try:
+            serve(llm.engine, name, llm.tokenizer, a.host, a.port)
+        finally:
+            llm.engine.stop_followers()
+    elif synced:
+        llm.engine.follow()
+    if synced:
+        from ..parallel.state import leave_process
+        leave_process(0)
     return 0

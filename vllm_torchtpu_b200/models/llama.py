@@ -189,6 +189,8 @@ class LlamaForCausalLM:
         self.norm = torch.ones(cfg.hidden_size, dtype=cfg.dtype, device=device)
         self.lm_head = None
         self.vocab_shard = cfg.vocab_size // st.tp.size if cfg.vocab_size % st.tp.size == 0 else None
+        self.decode_mega = None          # persistent decode kernel (ops/cuda_mega.py), set up with the KV cache
+        self.decode_mega_reason = "not set up"
 
     # ---- weights -------------------------------------------------------------
     def named_linears(self):
@@ -234,11 +236,40 @@ class LlamaForCausalLM:
         return n
 
     # ---- forward -------------------------------------------------------------
+    def setup_decode_fusion(self, kv_caches) -> None:
+        """(Re)build the persistent decode kernel's descriptors for these KV caches; models or layouts
+        it does not cover keep the per-layer kernels (the reason is kept for the log)."""
+        self.decode_mega = None
+        if not kv_caches or not torch.is_tensor(kv_caches[0]) or not kv_caches[0].is_cuda:
+            self.decode_mega_reason = "not on a GPU"
+            return
+        from ..ops.cuda_mega import DecodeMega
+        heap = get_tp_comm().heap if get_state().tp.size > 1 else None
+        why = DecodeMega.why_not(self, kv_caches, heap)
+        self.decode_mega_reason = why or ""
+        if why is None:
+            self.decode_mega = DecodeMega.build(self, kv_caches, kv_caches[0].device, heap)
+
+    def _use_decode_mega(self, meta, hidden, residual) -> bool:
+        m = self.decode_mega
+        if m is None or hidden is None or residual is not None:
+            return False
+        T = hidden.shape[0]
+        if T > m.maxt or meta.num_decode_reqs != meta.num_reqs or meta.max_query_len > 1:
+            return False
+        if meta.dcp_size > 1 or (meta.padded_num_reqs or meta.num_reqs) != T:
+            return False
+        from ..lora import wiring
+        return not wiring.active()
+
     def forward(self, input_ids, meta, kv_caches, *, hidden=None, residual=None):
         """Returns (hidden, residual) of the last local layer; the caller applies
         ``finalize`` on the last pipeline stage."""
         if hidden is None:
             hidden = ops.embedding(input_ids, self.embed)
+        if self._use_decode_mega(meta, hidden, residual):
+            # decode-only step: every layer in one persistent kernel; (0, residual stream) comes back
+            return self.decode_mega.run(hidden.contiguous(), meta, hidden.shape[0])
         for i, layer in enumerate(self.layers):
             hidden, residual = layer.forward(hidden, residual, kv_caches[i], meta)
         return ops.materialize(hidden), residual

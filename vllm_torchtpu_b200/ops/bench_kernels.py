@@ -5,6 +5,7 @@
     python -m vllm_torchtpu_b200.ops.bench_kernels attn-decode --reqs 64 --ctx 1100
     python -m vllm_torchtpu_b200.ops.bench_kernels attn-prefill --reqs 8 --q 1024
     python -m vllm_torchtpu_b200.ops.bench_kernels decode-layer --reqs 64 --ctx 1100
+    python -m vllm_torchtpu_b200.ops.bench_kernels decode-model --reqs 64 --ctx 1100 --tp 8
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, L2 flushed
 (a 256 MB buffer is rewritten) before every timed launch, median of the timed
@@ -213,6 +214,52 @@ def bench_decode_layer(reqs, ctx, layers=8, parts="all", iters=10, H=4096, I=143
             "status": cuda.check_status()}
 
 
+def bench_decode_model(reqs, ctx, layers=8, iters=10, H=4096, I=14336, Hq=32, Hkv=8, tp=1) -> list:
+    """A dense Llama-8B-shaped model of ``layers`` decoder layers (per-rank shapes of TP degree ``tp``,
+    run on one GPU without collectives) on a decode batch: the persistent decode kernel against the
+    per-layer kernel chain, both replayed from a CUDA graph; device time per layer."""
+    from ..config import ModelConfig
+    from ..models.llama import LlamaForCausalLM
+    from ..runner.attn_metadata import AttentionMetadata
+    from . import cuda
+    pk, tag = peaks()
+    I, Hq, Hkv = I // tp, Hq // tp, max(1, Hkv // tp)
+    cfg = ModelConfig(name="bench", num_layers=layers, hidden_size=H, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=128,
+                      intermediate_size=I, vocab_size=1024, max_model_len=ctx + 64, dtype=torch.bfloat16)
+    m = LlamaForCausalLM(cfg, "cuda")
+    m.init_dummy()
+    bs, dev = 16, "cuda"
+    nblk_per = -(-(ctx + 1) // bs)
+    nb = reqs * nblk_per + 1
+    kvs = [(torch.randn(nb, 2, Hkv, bs, 128, device=dev) * 0.5).bfloat16() for _ in range(layers)]
+    bt = (torch.randperm(nb - 1, device=dev) + 1).to(torch.int32).view(reqs, nblk_per).contiguous()
+    qsl = torch.arange(reqs + 1, device=dev, dtype=torch.int32)
+    sl = torch.full((reqs,), ctx + 1, device=dev, dtype=torch.int32)
+    pos = torch.full((reqs,), ctx, device=dev, dtype=torch.int32)
+    slots = (bt[:, ctx // bs].long() * bs + ctx % bs).to(torch.int32)
+    meta = AttentionMetadata(pos, slots, bt, sl, qsl, reqs, reqs, num_decode_reqs=reqs, max_query_len=1,
+                             max_seq_len=ctx + 1, padded_num_reqs=reqs, padded_num_tokens=reqs)
+    x0 = torch.randn(reqs, H, device=dev).bfloat16()
+    w_bytes = 2.0 * ((Hq + 2 * Hkv) * 128 * H + H * Hq * 128 + 2 * I * H + H * I)
+    kv_bytes = reqs * (ctx + 1) * 2 * Hkv * 128 * 2.0
+    roof_us = (w_bytes + kv_bytes) / (pk["hbm_gbs"] * 1e9) * 1e6
+    out = []
+    for mode in ("persistent", "per-layer"):
+        if mode == "persistent":
+            m.setup_decode_fusion(kvs)
+            if m.decode_mega is None:
+                out.append({"op": "decode_model", "mode": mode, "skipped": m.decode_mega_reason})
+                continue
+        else:
+            m.decode_mega = None
+        ms = time_fn(lambda: m.forward(None, meta, kvs, hidden=x0), iters, flush=False)
+        us = ms * 1e3 / layers
+        out.append({"op": "decode_model", "mode": mode, "reqs": reqs, "ctx": ctx, "layers": layers, "tp_shapes": tp,
+                    "us_per_layer": round(us, 2), "hbm_roofline_us": round(roof_us, 2),
+                    "frac_of_hbm": round(roof_us / us, 3), "peaks": tag, "status": cuda.check_status()})
+    return out
+
+
 def bench_gemm_swiglu(T, I, K, iters=20, impl="tcgen05") -> dict:
     """silu(x Wg^T) * (x Wu^T) with W = [2I, K]; 'cublas' is torch.matmul followed by an eager activation."""
     from . import cuda
@@ -284,7 +331,8 @@ LLAMA8B_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm-swiglu", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill", "decode-layer", "all"])
+    ap.add_argument("what", choices=["gemm", "gemm-swiglu", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill",
+                                     "decode-layer", "decode-model", "all"])
     ap.add_argument("--T", type=int, default=64)
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
@@ -313,6 +361,9 @@ def main():
     if a.what == "gemm-sustained":
         for impl in a.impls.split(","):
             print(json.dumps(bench_gemm_sustained(a.T, a.N, a.K, 3.0, impl)))
+    if a.what == "decode-model":
+        for row in bench_decode_model(a.reqs, a.ctx, a.layers, a.iters, tp=a.tp):
+            print(json.dumps(row))
     if a.what == "decode-layer":
         for parts in a.parts.split(","):
             print(json.dumps(bench_decode_layer(a.reqs, a.ctx, a.layers, parts, a.iters, tp=a.tp)))

@@ -235,6 +235,10 @@ class ModelRunner:
                             device=self.device) for _ in self.model.layers]
         if not hasattr(self, "bufs_prefill"):
             self._alloc_step_buffers()
+        if self.is_cuda and hasattr(self.model, "setup_decode_fusion"):
+            self.model.setup_decode_fusion(self.kv_caches)
+            if self.model.decode_mega is None:
+                logger.info("persistent decode kernel not used: %s", self.model.decode_mega_reason)
 
     # ------------------------------------------------------------ input prep
     def _update_batch(self, out) -> None:
