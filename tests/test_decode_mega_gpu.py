@@ -18,6 +18,17 @@ DEV = "cuda"
 BS = 16
 
 
+@pytest.fixture(autouse=True)
+def _persistent_kernel_on(monkeypatch):
+    """The persistent kernel is opt-in (B200_DECODE_MEGAKERNEL); these tests exercise it."""
+    from vllm_torchtpu_b200 import envs
+    monkeypatch.setenv("B200_DECODE_MEGAKERNEL", "1")
+    envs.reset()
+    yield
+    monkeypatch.delenv("B200_DECODE_MEGAKERNEL", raising=False)
+    envs.reset()
+
+
 def _model(L, H, Hq, Hkv, I, qk_norm=False, bias=False):
     cfg = ModelConfig(name="mega-test", num_layers=L, hidden_size=H, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=128,
                       intermediate_size=I, vocab_size=512, max_model_len=4096, dtype=torch.bfloat16,
@@ -104,7 +115,7 @@ def test_layers_match_per_layer_kernels(L, H, Hq, Hkv, I, R):
     want, got, kv_a, kv_b = _run_both(m, ctx)
     _assert_close(want, got)
     for a, b in zip(kv_a, kv_b):          # the new token's K / V rows landed in the same slots
-        assert (a.float() - b.float()).abs().max() < 0.06
+        assert (a.float() - b.float()).abs().max() <= 0.02 * a.float().abs().max()
 
 
 def test_qk_norm_bias_padded_rows_and_relaunch():
@@ -161,8 +172,6 @@ def test_engine_decodes_with_and_without_the_persistent_kernel(monkeypatch):
         toks[flag] = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
         torch.cuda.synchronize()
         assert cuda.check_status() == 0
-    monkeypatch.delenv("B200_DECODE_MEGAKERNEL")
-    envs.reset()
     same = sum(a == b for a, b in zip(toks["1"], toks["0"]))
     # random-init logits are nearly flat: a rounding difference may flip an arg-max late in a sequence
     assert same >= 3, toks

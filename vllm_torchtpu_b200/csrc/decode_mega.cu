@@ -43,30 +43,31 @@ constexpr int BN = 64;                  // token columns (UMMA N); a step has at
 constexpr int BK = 64;                  // bf16 per 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr int STAGES = 5;
+constexpr int STAGES = 8;
 constexpr int A_BYTES = BM * BK * 2;    // 16 KB
 constexpr int B_BYTES = BN * BK * 2;    // 8 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int RING_BYTES = STAGES * STAGE_BYTES;                 // 120 KB
-constexpr int BAR_OFF = RING_BYTES;
-constexpr int BAR_BYTES = 1024;
-constexpr int ATT_OFF = BAR_OFF + BAR_BYTES;                     // 1024-aligned
+constexpr int RING_BYTES = STAGES * STAGE_BYTES;                 // 192 KB
+// The attention phase borrows the ring: streaming bandwidth is bytes in flight per SM over memory
+// latency, and neither the weight ring nor the KV rings reach HBM speed on half of shared memory.
+// The producer does not load weights of the projections behind an attention phase until this CTA's
+// attention is done (attn_done), and attention starts only after the qkv GEMM has drained the ring.
 constexpr int D = 128;                                            // head dim
-constexpr int ATT_STAGES = 3;
+constexpr int ATT_STAGES = 6;
 constexpr int ATT_PAGE_BYTES = 16 * D * 2;                        // 16 tokens of K (or V)
 constexpr int ATT_STAGE_BYTES = 2 * ATT_PAGE_BYTES;
-constexpr int ATT_WARP_BYTES = ATT_STAGES * ATT_STAGE_BYTES;      // 24 KB per warp (>= [16][D] fp32 merge tile)
-constexpr int ATT_RING_BYTES = 4 * ATT_WARP_BYTES;                // 96 KB
-constexpr int SQ_OFF = ATT_OFF + ATT_RING_BYTES;                  // q rows [16][D] bf16
-constexpr int SQ_BYTES = 16 * D * 2;
-constexpr int CS_OFF = SQ_OFF + SQ_BYTES;                         // cos | sin, D floats
-constexpr int ML_OFF = CS_OFF + D * 4;                            // [4][16][2] floats
-constexpr int RED_OFF = ML_OFF + 4 * 16 * 2 * 4;                  // 32 floats + flags
+constexpr int ATT_WARP_BYTES = ATT_STAGES * ATT_STAGE_BYTES;      // 48 KB per warp (also q rows + cos / sin)
+constexpr int ATT_OFF = 0;
+static_assert(4 * ATT_WARP_BYTES <= RING_BYTES, "attention rings alias the GEMM ring");
+constexpr int BAR_OFF = RING_BYTES;
+constexpr int BAR_BYTES = 1024;
+constexpr int RED_OFF = BAR_OFF + BAR_BYTES;                      // block-sum scratch
 constexpr int SMEM_USED = RED_OFF + 256;
 constexpr int SMEM_BYTES = SMEM_USED + 1024;                      // + alignment slack
 static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 constexpr int TMEM_COLS = 2 * BN;                                 // two accumulators
 constexpr int MAXT = 64;
+constexpr int MAX_SLOTS = 5;             // split-K partial slots per weight tile, at most
 
 enum Kind : int { K_NORM_IN = 0, K_GEMM, K_ATTN, K_PUSH, K_NORM_POST, K_SWIGLU };
 
@@ -110,13 +111,17 @@ struct Params {
   float* attn_part_o;                   // [T * Hkv * splits][16][D]
   float* attn_part_ml;                  // [T * Hkv * splits][16][2]
   int* attn_counters;                   // [T * Hkv], zero between launches
-  int* ctrl;                            // [0] grid barrier, [1] exit count, [2] launch epoch, [3] abort
+  int* ctrl;                            // [0] barrier arrivals, [1] exit count, [2] launch epoch, [3] abort,
+                                        // [32] number of the last completed barrier (own cache line)
   int* status;
   int world, rank;
   uint8_t* peer[8];
   unsigned long long slab_off[2];       // receive slabs [src][64][H] bf16 of o_proj / down_proj partial rows
   unsigned long long flag_off[2];       // int[world][64 * 4]
   unsigned int spin_limit;
+  int dbg_layer, dbg_gi, dbg_ev_base;   // optional: rows dbg_ev_base.. of dbg get role events of one GEMM phase
+  unsigned long long* dbg;              // optional: %globaltimer of every CTA when it ends a phase's work and
+                                        // when it leaves the barrier after it, [2 * phase + {0, 1}][CTA]
 };
 
 __device__ __forceinline__ int phases_per_layer(const Params& p) { return p.world > 1 ? 10 : 8; }
@@ -173,13 +178,33 @@ struct Shared {
   uint32_t* tmem_slot;
   volatile int* abort_flag;
   volatile int* phase_open;
-  volatile int* s_last;
+  volatile int* attn_done;              // attention phases this CTA has finished (the ring is the producer's again)
 };
 
 __device__ __forceinline__ void raise_abort(const Params& p, const Shared& sh, int code) {
   *sh.abort_flag = 1;
   atomicExch(p.ctrl + 3, 1);
   if (p.status) atomicCAS(p.status, ST_OK, code);
+}
+
+// Bounded mbarrier wait that polls: the waits of this kernel sit on the critical path of every phase
+// and the waiting warps have nothing else to run.
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, const Params& p, const Shared& sh,
+                                          int code) {
+#pragma unroll 1
+  for (int it = 0; it < 256; ++it)
+    if (mbar_test(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+#pragma unroll 1
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_test(bar, parity)) return true;
+    if ((it & 63u) == 63u) {
+      if (*sh.abort_flag) return false;
+      if (global_timer_ns() - t0 > B200_WAIT_LIMIT_NS) break;
+    }
+  }
+  raise_abort(p, sh, code);
+  return false;
 }
 
 // named barrier of the 128 compute threads (warps 2..5)
@@ -191,12 +216,15 @@ __device__ __forceinline__ bool grid_barrier(const Params& p, const Shared& sh, 
   __threadfence();
   cbar();
   if (ct == 0) {
-    atomicAdd(p.ctrl, 1);
+    // the last CTA to arrive publishes the barrier number in a word of its own (ctrl[32], another
+    // cache line), so that the pollers do not fight the arriving atomics for the counter's line
+    const int gen = target / (int)gridDim.x;
+    if (atomicAdd(p.ctrl, 1) + 1 == target) st_release_gpu(p.ctrl + 32, gen);
     const unsigned long long t0 = global_timer_ns();
     bool ok = false;
 #pragma unroll 1
     for (uint32_t it = 0;; ++it) {
-      if (ld_acquire_gpu(p.ctrl) - target >= 0) { ok = true; break; }
+      if (ld_acquire_gpu(p.ctrl + 32) - gen >= 0) { ok = true; break; }
       if ((it & 15u) == 15u) {
         if (*sh.abort_flag || *reinterpret_cast<volatile int*>(p.ctrl + 3)) break;
         if (global_timer_ns() - t0 > B200_WAIT_LIMIT_NS) {
@@ -212,84 +240,166 @@ __device__ __forceinline__ bool grid_barrier(const Params& p, const Shared& sh, 
   return !*sh.abort_flag;
 }
 
+__device__ __forceinline__ void stamp_ev(const Params& p, int layer, int gi, int ev) {
+  if (p.dbg != nullptr && layer == p.dbg_layer && gi == p.dbg_gi)
+    p.dbg[(size_t)(p.dbg_ev_base + ev) * gridDim.x + blockIdx.x] = global_timer_ns();
+}
+
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
-// Sum of the fp32 partials of 8 consecutive columns [n, n+8) of row t of a projection.
+// Sum of the fp32 partials of 8 consecutive columns [n, n+8) of row t of a projection, in slot order.
+// The loads of four slots are issued together: a consumer phase is a chain of L2 round trips otherwise.
 __device__ __forceinline__ void sum_partials8(const float* part, const GemmShape& g, int t, int n, float (&acc)[8]) {
   const int tile = n / BM;
   const int ns = tile_num_segs(g, tile);
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    const float4* src = reinterpret_cast<const float4*>(part + ((size_t)s * MAXT + t) * g.N + n);
-    const float4 a = __ldcg(src), b = __ldcg(src + 1);
-    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
-    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  const size_t seg_stride = (size_t)MAXT * g.N;
+  const float* base = part + (size_t)t * g.N + n;
+  for (int s0 = 0; s0 < ns; s0 += 4) {
+    float4 a[4], b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (s0 + i < ns) {
+        const float4* src = reinterpret_cast<const float4*>(base + (size_t)(s0 + i) * seg_stride);
+        a[i] = __ldcg(src);
+        b[i] = __ldcg(src + 1);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (s0 + i < ns) {
+        acc[0] += a[i].x; acc[1] += a[i].y; acc[2] += a[i].z; acc[3] += a[i].w;
+        acc[4] += b[i].x; acc[5] += b[i].y; acc[6] += b[i].z; acc[7] += b[i].w;
+      }
+    }
   }
 }
 
 // ----------------------------------------------------------------- phases run by the compute warps
 // residual + sum -> residual; RMSNorm -> h.  Source of the sum: nothing (layer 0: x = hidden0), the
 // split-K partials of projection `src_g` (one rank), or the receive slab `slab` (tensor parallel).
-__device__ void phase_norm(const Params& p, const Shared& sh, uint8_t* smem, int ct, int layer, bool first,
+__device__ __noinline__ void phase_norm(const Params& p, const Shared& sh, uint8_t* smem, int ct, int layer, bool first,
                            int src_g, int slab, int use_idx, const __nv_bfloat16* weight, bool write_h) {
-  float* red = reinterpret_cast<float*>(smem + RED_OFF);
-  const int H = p.H;
+  // locals: fields read through the references would be re-read after every global store
+  float* const red = reinterpret_cast<float*>(smem + RED_OFF);
+  const int H = p.H, T = p.T, world = p.world;
+  const float eps = p.eps;
+  const GemmShape g = p.g[src_g];
+  const float* const part = p.part;
+  const __nv_bfloat16* const hidden0 = p.hidden0;
+  __nv_bfloat16* const residual = p.residual;
+  __nv_bfloat16* const hbuf = p.h;
+  const uint8_t* const recv = world > 1 ? p.peer[p.rank] + p.slab_off[slab] : nullptr;
+  const int* const flags = world > 1 ? reinterpret_cast<const int*>(p.peer[p.rank] + p.flag_off[slab]) : nullptr;
+  const unsigned int spin_limit = p.spin_limit;
+  volatile int* const abort_flag = sh.abort_flag;
   const int nvec = H >> 3;
-  for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
-    if (!first && p.world > 1) {
+  const size_t seg_stride = (size_t)MAXT * g.N;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    if (!first && world > 1) {
       // the partial rows of every rank (this one included) arrive as quarter rows with one flag each
-      if (ct < p.world * 4) {
-        const int* f = reinterpret_cast<const int*>(p.peer[p.rank] + p.flag_off[slab]) + (ct >> 2) * (MAXT * 4) +
-                       t * 4 + (ct & 3);
-        if (!wait_flag_ge(f, use_idx, p.status, p.spin_limit)) raise_abort(p, sh, ST_TIMEOUT_FLAG);
+      if (ct < world * 4) {
+        const int* f = flags + (ct >> 2) * (MAXT * 4) + t * 4 + (ct & 3);
+        if (!wait_flag_ge(f, use_idx, p.status, spin_limit)) raise_abort(p, sh, ST_TIMEOUT_FLAG);
       }
       cbar();
-      if (*sh.abort_flag) return;
+      if (*abort_flag) return;
     }
     float ss = 0.f;
-    bf16x8 keep[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int v = ct + u * 128;
-      if (v >= nvec) break;
-      bf16x8 x;
+    // two vectors per pass, every load of a pass in flight together (a pass costs one L2 round trip)
+#pragma unroll 1
+    for (int u0 = 0; u0 < 8; u0 += 2) {
+      if (ct + u0 * 128 >= nvec) break;
+      bf16x8 xs[2];
       if (first) {
-        x = *reinterpret_cast<const bf16x8*>(p.hidden0 + (size_t)t * H + v * 8);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int v = ct + (u0 + k) * 128;
+          if (v < nvec) xs[k] = *reinterpret_cast<const bf16x8*>(hidden0 + (size_t)t * H + v * 8);
+        }
       } else {
-        float acc[8];
-        if (p.world > 1) {
+        float acc[2][8];
+        bf16x8 res[2];
+        if (world > 1) {
+          uint4 raw[2][8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-          const uint8_t* recv = p.peer[p.rank] + p.slab_off[slab];
-          for (int r = 0; r < p.world; ++r) {
-            const uint4 raw = ld_relaxed_sys_v4(recv + (((size_t)r * MAXT + t) * H + v * 8) * 2);
-            const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+          for (int k = 0; k < 2; ++k) {
+            const int v = ct + (u0 + k) * 128;
+            if (v >= nvec) continue;
+            res[k] = *reinterpret_cast<const bf16x8*>(residual + (size_t)t * H + v * 8);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __bfloat1622float2(hh[j]);
-              acc[2 * j] += f.x;
-              acc[2 * j + 1] += f.y;
+            for (int r = 0; r < 8; ++r)
+              if (r < world) raw[k][r] = ld_relaxed_sys_v4(recv + (((size_t)r * MAXT + t) * H + v * 8) * 2);
+          }
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[k][j] = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              if (r < world) {
+                const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw[k][r]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = __bfloat1622float2(hh[j]);
+                  acc[k][2 * j] += f.x;
+                  acc[k][2 * j + 1] += f.y;
+                }
+              }
             }
           }
         } else {
-          sum_partials8(p.part, p.g[src_g], t, v * 8, acc);
+          float4 pa[2][MAX_SLOTS], pb[2][MAX_SLOTS];
+          int ns[2] = {0, 0};
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const int v = ct + (u0 + k) * 128;
+            if (v >= nvec) continue;
+            res[k] = *reinterpret_cast<const bf16x8*>(residual + (size_t)t * H + v * 8);
+            ns[k] = tile_num_segs(g, (v * 8) / BM);
+            const float* base = part + (size_t)t * g.N + v * 8;
+#pragma unroll
+            for (int sl = 0; sl < MAX_SLOTS; ++sl)
+              if (sl < ns[k]) {
+                const float4* src = reinterpret_cast<const float4*>(base + (size_t)sl * seg_stride);
+                pa[k][sl] = __ldcg(src);
+                pb[k][sl] = __ldcg(src + 1);
+              }
+          }
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[k][j] = 0.f;
+#pragma unroll
+            for (int sl = 0; sl < MAX_SLOTS; ++sl)
+              if (sl < ns[k]) {
+                acc[k][0] += pa[k][sl].x; acc[k][1] += pa[k][sl].y; acc[k][2] += pa[k][sl].z; acc[k][3] += pa[k][sl].w;
+                acc[k][4] += pb[k][sl].x; acc[k][5] += pb[k][sl].y; acc[k][6] += pb[k][sl].z; acc[k][7] += pb[k][sl].w;
+              }
+          }
         }
         // same roundings as a bf16 projection output followed by the bf16 residual add
-        const bf16x8 r = *reinterpret_cast<const bf16x8*>(p.residual + (size_t)t * H + v * 8);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 fa = __bfloat1622float2(__floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]));
-          const float2 fr = __bfloat1622float2(r.v[j]);
-          x.v[j] = __floats2bfloat162_rn(fa.x + fr.x, fa.y + fr.y);
+        for (int k = 0; k < 2; ++k) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 fa = __bfloat1622float2(__floats2bfloat162_rn(acc[k][2 * j], acc[k][2 * j + 1]));
+            const float2 fr = __bfloat1622float2(res[k].v[j]);
+            xs[k].v[j] = __floats2bfloat162_rn(fa.x + fr.x, fa.y + fr.y);
+          }
         }
       }
-      *reinterpret_cast<bf16x8*>(p.residual + (size_t)t * H + v * 8) = x;
-      keep[u] = x;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(x.v[j]);
-        ss += f.x * f.x + f.y * f.y;
+      for (int k = 0; k < 2; ++k) {
+        const int v = ct + (u0 + k) * 128;
+        if (v >= nvec) continue;
+        *reinterpret_cast<bf16x8*>(residual + (size_t)t * H + v * 8) = xs[k];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(xs[k].v[j]);
+          ss += f.x * f.x + f.y * f.y;
+        }
       }
     }
     if (!write_h) continue;
@@ -299,19 +409,28 @@ __device__ void phase_norm(const Params& p, const Shared& sh, uint8_t* smem, int
     cbar();
     const float tot = red[0] + red[1] + red[2] + red[3];
     cbar();
-    const float inv = rsqrtf(tot / (float)H + p.eps);
+    const float inv = rsqrtf(tot / (float)H + eps);
+    // second pass over the row this thread just wrote (its own stores: L1 / L2 hits, all in flight)
+    bf16x8 xr[8], wr[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int v = ct + u * 128;
+      if (v < nvec) {
+        xr[u] = *reinterpret_cast<const bf16x8*>(residual + (size_t)t * H + v * 8);
+        wr[u] = *reinterpret_cast<const bf16x8*>(weight + v * 8);
+      }
+    }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int v = ct + u * 128;
       if (v >= nvec) break;
-      const bf16x8 ww = *reinterpret_cast<const bf16x8*>(weight + v * 8);
       bf16x8 y;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(keep[u].v[j]), g2 = __bfloat1622float2(ww.v[j]);
+        const float2 f = __bfloat1622float2(xr[u].v[j]), g2 = __bfloat1622float2(wr[u].v[j]);
         y.v[j] = __floats2bfloat162_rn(f.x * inv * g2.x, f.y * inv * g2.y);
       }
-      *reinterpret_cast<bf16x8*>(p.h + (size_t)t * H + v * 8) = y;
+      *reinterpret_cast<bf16x8*>(hbuf + (size_t)t * H + v * 8) = y;
     }
   }
   (void)layer;
@@ -319,143 +438,214 @@ __device__ void phase_norm(const Params& p, const Shared& sh, uint8_t* smem, int
 
 // Tensor parallel: sum the split-K partials of a row-parallel projection, round to bf16 and store the
 // quarter row into the receive slab of every rank, then raise that quarter's flag there.
-__device__ void phase_push(const Params& p, const Shared& sh, int ct, int src_g, int slab, int use_idx) {
-  const int H = p.H;
+__device__ __noinline__ void phase_push(const Params& p, const Shared& sh, int ct, int src_g, int slab, int use_idx) {
+  const int H = p.H, T = p.T, world = p.world, rank = p.rank;
+  const GemmShape g = p.g[src_g];
+  const float* const part = p.part;
+  uint8_t* peer[8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) peer[r] = p.peer[r];
+  const unsigned long long slab_off = p.slab_off[slab], flag_off = p.flag_off[slab];
   const int qv = (H >> 3) >> 2;                       // 16-byte vectors per quarter row
-  const int units = p.T * 4;
+  const int units = T * 4;
   for (int u = blockIdx.x; u < units; u += gridDim.x) {
     const int t = u >> 2, q = u & 3;
     for (int v = ct; v < qv; v += 128) {
       const int n = (q * qv + v) * 8;
       float acc[8];
-      sum_partials8(p.part, p.g[src_g], t, n, acc);
+      sum_partials8(part, g, t, n, acc);
       uint4 o;
       __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
       for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-      for (int r = 0; r < p.world; ++r) {
-        const int d = (p.rank + r) % p.world;           // start with this rank, spread the links
-        *reinterpret_cast<uint4*>(p.peer[d] + p.slab_off[slab] + (((size_t)p.rank * MAXT + t) * H + n) * 2) = o;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < world) {
+          int d = rank + r;                              // start with this rank, spread the links
+          if (d >= world) d -= world;
+          *reinterpret_cast<uint4*>(peer[d] + slab_off + (((size_t)rank * MAXT + t) * H + n) * 2) = o;
+        }
       }
     }
     __threadfence_system();
     cbar();
-    if (ct < p.world)
-      st_release_sys(reinterpret_cast<int*>(p.peer[ct] + p.flag_off[slab]) + p.rank * (MAXT * 4) + u, use_idx);
+    if (ct < world)
+      st_release_sys(reinterpret_cast<int*>(p.peer[ct] + flag_off) + rank * (MAXT * 4) + u, use_idx);
   }
   (void)sh;
 }
 
 // act = silu(gate) * up from the partials of the gate/up projection (columns [0, I) gate, [I, 2I) up)
-__device__ void phase_swiglu(const Params& p, int ct) {
-  const int I = p.I;
+__device__ __noinline__ void phase_swiglu(const Params& p, int ct) {
+  const int I = p.I, T = p.T;
+  const GemmShape g = p.g[2];
+  const float* const part = p.part;
+  __nv_bfloat16* const act = p.act;
   const int nvec = I >> 3;
-  const int total = p.T * nvec;
-  for (int idx = blockIdx.x * 128 + ct; idx < total; idx += gridDim.x * 128) {
+  const int total = T * nvec;
+  const int stride = (int)gridDim.x * 128;
+  for (int idx = blockIdx.x * 128 + ct; idx < total; idx += stride) {
     const int t = idx / nvec, v = idx - t * nvec;
     float g8[8], u8[8];
-    sum_partials8(p.part, p.g[2], t, v * 8, g8);
-    sum_partials8(p.part, p.g[2], t, I + v * 8, u8);
+    sum_partials8(part, g, t, v * 8, g8);
+    sum_partials8(part, g, t, I + v * 8, u8);
     bf16x8 y;
 #pragma unroll
     for (int j = 0; j < 4; ++j)
       y.v[j] = __floats2bfloat162_rn(silu(g8[2 * j]) * u8[2 * j], silu(g8[2 * j + 1]) * u8[2 * j + 1]);
-    *reinterpret_cast<bf16x8*>(p.act + (size_t)t * I + v * 8) = y;
+    *reinterpret_cast<bf16x8*>(act + (size_t)t * I + v * 8) = y;
   }
 }
 
-// One (request, kv head, kv split) unit of decode attention: sum the qkv partials of the request's
-// token, bias, per-head q/k RMSNorm, RoPE, KV write (last split), then split-KV flash attention with
-// one 16-row mma.sync tile per kv head group, as in the stand-alone decode kernel.
-__device__ void attn_unit(const Params& p, const Shared& sh, uint8_t* smem, const LayerDesc& L, int ct, int r,
-                          int h, int z) {
-  const int lw = ct >> 5, lane = ct & 31;
-  const int G = p.Hq / p.Hkv;
+// The fields of Params / LayerDesc the attention phase uses, copied once per phase: the phase functions
+// are separate (not inlined) to keep their registers apart, and a field read through a reference would
+// be re-read from memory after every global store.
+struct AttnArgs {
+  const float* part;
+  const int* positions;
+  const int* slot_mapping;
+  const int* block_tables;
+  const int* seq_lens;
+  const float* inv_freq;
+  const __nv_bfloat16* qkv_bias;
+  const __nv_bfloat16* q_norm;
+  const __nv_bfloat16* k_norm;
+  __nv_bfloat16* kv_cache;
+  __nv_bfloat16* o;
+  float* part_o;
+  float* part_ml;
+  int* counters;
+  long long num_blocks;
+  GemmShape gq;
+  int Hq, Hkv, G, Z, rot_pairs, interleaved, max_blocks, block_size;
+  float eps, scale_log2;
+};
+
+__device__ __forceinline__ void attn_warp_unit(const AttnArgs& p, uint8_t* smem, int lw, int lane, int r, int h,
+                                               int z) {
+  const int G = p.G;
   const int t = r;
   const int seq_len = p.seq_lens[r];
-  if (seq_len <= 0) return;                                   // padded request (uniform for the CTA)
+  if (seq_len <= 0) return;                                   // padded request (uniform for the warp)
   const int ctx = seq_len - 1;
-  const int Z = p.kv_splits;
-  __nv_bfloat16* s_q = reinterpret_cast<__nv_bfloat16*>(smem + SQ_OFF);
-  float* cs = reinterpret_cast<float*>(smem + CS_OFF);
-  float (*s_ml)[16][2] = reinterpret_cast<float (*)[16][2]>(smem + ML_OFF);
-  const GemmShape& gq = p.g[0];
+  const int Z = p.Z;
+  uint8_t* ring = smem + ATT_OFF + lw * ATT_WARP_BYTES;
+  // q rows and cos / sin live in the ring until the fragments are in registers
+  __nv_bfloat16* s_q = reinterpret_cast<__nv_bfloat16*>(ring);             // [16][D] bf16
+  float* cs = reinterpret_cast<float*>(ring + 16 * D * 2);                  // cos | sin
+  const GemmShape gq = p.gq;
+  const __nv_bfloat16* const qkv_bias = p.qkv_bias;
+  const __nv_bfloat16* const q_norm = p.q_norm;
+  const __nv_bfloat16* const k_norm = p.k_norm;
+  __nv_bfloat16* const kv_cache = p.kv_cache;
+  const int C = (seq_len + 15) >> 4;
+  const int per = (C + Z - 1) / Z;
+  const int cb0 = min(C, z * per);
+  const int cb1 = min(C, (z + 1) * per);
+  const bool write_kv = (z == (C - 1) / per);               // this split reads the new token's K / V
 
-  // ---- prologue: q rows (and k, v of the new token on the last split)
+  // ---- prologue
   {
     const float pos = (float)p.positions[t];
-    for (int i = ct; i < p.rot_pairs; i += 128) {
-      float s, c;
-      sincosf(pos * p.inv_freq[i], &s, &c);
+    for (int i = lane; i < p.rot_pairs; i += 32) {
+      float sn, c;
+      sincosf(pos * p.inv_freq[i], &sn, &c);
       cs[i] = c;
-      cs[D / 2 + i] = s;
+      cs[D / 2 + i] = sn;
     }
-    for (int i = ct; i < (16 - G) * D / 2; i += 128) reinterpret_cast<uint32_t*>(s_q + G * D)[i] = 0u;
-    cbar();
+    for (int i = lane; i < (16 - G) * D / 2; i += 32) reinterpret_cast<uint32_t*>(s_q + G * D)[i] = 0u;
+    __syncwarp();
     const long long slot = p.slot_mapping[t];
-    const bool write_kv = (z == Z - 1);
     const int nrows = write_kv ? G + 2 : G;
     constexpr int EPL = D / 32;
-    for (int j = lw; j < nrows; j += 4) {
-      const int kind = j < G ? 0 : (j == G ? 1 : 2);
-      const int head_col = kind == 0 ? (h * G + j) : (kind == 1 ? p.Hq + h : p.Hq + p.Hkv + h);   // n tile index
-      int idx[EPL];
+    int idx[EPL];
 #pragma unroll
-      for (int u = 0; u < EPL / 2; ++u) {
-        const int i = lane * (EPL / 2) + u;
-        if (p.interleaved) { idx[2 * u] = 2 * i; idx[2 * u + 1] = 2 * i + 1; }
-        else { idx[2 * u] = i; idx[2 * u + 1] = i + D / 2; }
-      }
-      float x[EPL];
+    for (int u = 0; u < EPL / 2; ++u) {
+      const int i = lane * (EPL / 2) + u;
+      if (p.interleaved) { idx[2 * u] = 2 * i; idx[2 * u + 1] = 2 * i + 1; }
+      else { idx[2 * u] = i; idx[2 * u + 1] = i + D / 2; }
+    }
+    const size_t seg_stride = (size_t)MAXT * gq.N;
+    constexpr int RG = 3;                      // head rows per group of loads
+#pragma unroll 1
+    for (int j0 = 0; j0 < nrows; j0 += RG) {
+      float x[RG][EPL];
+      int head_col[RG];
+      {
+        float v[RG][MAX_SLOTS][EPL];
+        int ns[RG];
 #pragma unroll
-      for (int u = 0; u < EPL; ++u) x[u] = 0.f;
-      const int ns = tile_num_segs(gq, head_col);
-      for (int s = 0; s < ns; ++s) {
-        const float* src = p.part + ((size_t)s * MAXT + t) * gq.N + head_col * D;
+        for (int k = 0; k < RG; ++k) {
+          const int j = j0 + k;
+          head_col[k] = j < G ? (h * G + j) : (j == G ? p.Hq + h : p.Hq + p.Hkv + h);     // n tile index
+          ns[k] = j < nrows ? tile_num_segs(gq, head_col[k]) : 0;
+          const float* base = p.part + (size_t)t * gq.N + head_col[k] * D;
 #pragma unroll
-        for (int u = 0; u < EPL; ++u) x[u] += __ldcg(src + idx[u]);
-      }
+          for (int sl = 0; sl < MAX_SLOTS; ++sl)
+            if (sl < ns[k]) {
 #pragma unroll
-      for (int u = 0; u < EPL; ++u) {
-        if (L.qkv_bias != nullptr) x[u] += __bfloat162float(L.qkv_bias[head_col * D + idx[u]]);
-        x[u] = __bfloat162float(__float2bfloat16(x[u]));          // the projection's bf16 output
-      }
-      if (kind < 2) {
-        const __nv_bfloat16* nwp = kind == 0 ? L.q_norm : L.k_norm;
-        if (nwp != nullptr) {
-          float ss = 0.f;
-#pragma unroll
-          for (int u = 0; u < EPL; ++u) ss += x[u] * x[u];
-          ss = warp_sum(ss);
-          const float inv = rsqrtf(ss / (float)D + p.eps);
-#pragma unroll
-          for (int u = 0; u < EPL; ++u)
-            x[u] = __bfloat162float(__float2bfloat16(x[u] * inv * __bfloat162float(nwp[idx[u]])));
+              for (int u = 0; u < EPL; ++u) v[k][sl][u] = __ldcg(base + (size_t)sl * seg_stride + idx[u]);
+            }
         }
 #pragma unroll
-        for (int u = 0; u < EPL / 2; ++u) {
-          const int i = lane * (EPL / 2) + u;
-          if (i < p.rot_pairs) {
-            const float c = cs[i], s = cs[D / 2 + i];
-            const float a = x[2 * u], b = x[2 * u + 1];
-            x[2 * u] = a * c - b * s;
-            x[2 * u + 1] = b * c + a * s;
+        for (int k = 0; k < RG; ++k) {
+#pragma unroll
+          for (int u = 0; u < EPL; ++u) x[k][u] = 0.f;
+#pragma unroll
+          for (int sl = 0; sl < MAX_SLOTS; ++sl)
+            if (sl < ns[k]) {
+#pragma unroll
+              for (int u = 0; u < EPL; ++u) x[k][u] += v[k][sl][u];
+            }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < RG; ++k) {
+        const int j = j0 + k;
+        if (j >= nrows) break;
+        const int kind = j < G ? 0 : (j == G ? 1 : 2);
+#pragma unroll
+        for (int u = 0; u < EPL; ++u) {
+          if (qkv_bias != nullptr) x[k][u] += __bfloat162float(qkv_bias[head_col[k] * D + idx[u]]);
+          x[k][u] = __bfloat162float(__float2bfloat16(x[k][u]));          // the projection's bf16 output
+        }
+        if (kind < 2) {
+          const __nv_bfloat16* nwp = kind == 0 ? q_norm : k_norm;
+          if (nwp != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int u = 0; u < EPL; ++u) ss += x[k][u] * x[k][u];
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)D + p.eps);
+#pragma unroll
+            for (int u = 0; u < EPL; ++u)
+              x[k][u] = __bfloat162float(__float2bfloat16(x[k][u] * inv * __bfloat162float(nwp[idx[u]])));
+          }
+#pragma unroll
+          for (int u = 0; u < EPL / 2; ++u) {
+            const int i = lane * (EPL / 2) + u;
+            if (i < p.rot_pairs) {
+              const float c = cs[i], sn = cs[D / 2 + i];
+              const float a = x[k][2 * u], b = x[k][2 * u + 1];
+              x[k][2 * u] = a * c - b * sn;
+              x[k][2 * u + 1] = b * c + a * sn;
+            }
           }
         }
-      }
-      if (kind == 0) {
+        if (kind == 0) {
 #pragma unroll
-        for (int u = 0; u < EPL; ++u) s_q[j * D + idx[u]] = __float2bfloat16(x[u]);
-      } else if (slot >= 0 && slot < p.num_blocks * p.block_size) {
-        const long long blk = slot / p.block_size;
-        const int off = (int)(slot - blk * p.block_size);
-        __nv_bfloat16* dst = L.kv_cache + ((((size_t)blk * 2 + (kind - 1)) * p.Hkv + h) * p.block_size + off) * D;
+          for (int u = 0; u < EPL; ++u) s_q[j * D + idx[u]] = __float2bfloat16(x[k][u]);
+        } else if (slot >= 0 && slot < p.num_blocks * p.block_size) {
+          const long long blk = slot / p.block_size;
+          const int off = (int)(slot - blk * p.block_size);
+          __nv_bfloat16* dst = kv_cache + ((((size_t)blk * 2 + (kind - 1)) * p.Hkv + h) * p.block_size + off) * D;
 #pragma unroll
-        for (int u = 0; u < EPL; ++u) dst[idx[u]] = __float2bfloat16(x[u]);
+          for (int u = 0; u < EPL; ++u) dst[idx[u]] = __float2bfloat16(x[k][u]);
+        }
       }
     }
-    __threadfence();                 // the new K/V row is read back through L2 by this CTA's cp.async
-    cbar();
+    __threadfence();                 // the new K/V row is read back through L2 by this warp's cp.async
+    __syncwarp();
   }
 
   // ---- Q fragments: tile row g = q head g of this kv head's group
@@ -473,25 +663,16 @@ __device__ void attn_unit(const Params& p, const Shared& sh, uint8_t* smem, cons
       qf[ks][3] = *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + cb);
     }
   }
-  const int rows_valid = G;
+  __syncwarp();                      // the ring may be overwritten from here on
 
-  // this (split, warp) unit's range of 16-token chunks
-  const int C = (seq_len + 15) >> 4;
-  const int units = Z * 4;
-  const int per = (C + units - 1) / units;
-  const int uu = z * 4 + lw;
-  const int cb0 = min(C, uu * per);
-  const int cb1 = min(C, (uu + 1) * per);
-
-  uint8_t* ring = smem + ATT_OFF;
-  const uint32_t wbase = smem_u32(ring) + lw * ATT_WARP_BYTES;
+  const uint32_t wbase = smem_u32(ring);
   const int* bt = p.block_tables + (size_t)r * p.max_blocks;
   const size_t head_stride = (size_t)p.block_size * D;
   const int page_lo = (cb0 << 4) / p.block_size;
   const int page_hi = cb1 > cb0 ? (((cb1 << 4) - 1) / p.block_size) : page_lo - 1;
   int bt_base = page_lo;
   int bt_reg = (page_lo + lane <= page_hi) ? bt[page_lo + lane] : 0;
-  const __nv_bfloat16* kv = L.kv_cache;
+  const __nv_bfloat16* kv = kv_cache;
   auto issue = [&](int chunk, int stage) {
     const int tok = chunk << 4;
     const int page = tok / p.block_size, off = tok - page * p.block_size;
@@ -575,102 +756,95 @@ __device__ void attn_unit(const Params& p, const Shared& sh, uint8_t* smem, cons
   l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
   __syncwarp();
 
-  // ---- merge the 4 warps in shared memory (each warp reuses its own ring)
-  float* wo = reinterpret_cast<float*>(ring + lw * ATT_WARP_BYTES);
-#pragma unroll
-  for (int i = 0; i < D / 8; ++i) {
-    const int col = i * 8 + 2 * (lane & 3);
-    *reinterpret_cast<float2*>(wo + row0 * D + col) = make_float2(o[i][0], o[i][1]);
-    *reinterpret_cast<float2*>(wo + row1 * D + col) = make_float2(o[i][2], o[i][3]);
-  }
-  if ((lane & 3) == 0) {
-    s_ml[lw][row0][0] = m[0]; s_ml[lw][row0][1] = l[0];
-    s_ml[lw][row1][0] = m[1]; s_ml[lw][row1][1] = l[1];
-  }
-  cbar();
-  const int row = ct >> 3;                          // 16 rows x 8 threads
-  const int seg = ct & 7;
-  constexpr int SEG = D / 8;
-  float mm = -INFINITY;
-#pragma unroll
-  for (int w = 0; w < 4; ++w) mm = fmaxf(mm, s_ml[w][row][0]);
-  float Lsum = 0.f, acc[SEG];
-#pragma unroll
-  for (int d = 0; d < SEG; ++d) acc[d] = 0.f;
-#pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    const float mw = s_ml[w][row][0];
-    const float sc = (mw == -INFINITY) ? 0.f : ex2(mw - mm);
-    Lsum += s_ml[w][row][1] * sc;
-    const float* src = reinterpret_cast<const float*>(ring + w * ATT_WARP_BYTES) + row * D + seg * SEG;
-#pragma unroll
-    for (int d = 0; d < SEG; ++d) acc[d] += src[d] * sc;
-  }
-  const bool row_ok = row < rows_valid;
-  const int head = h * G + row;
-  auto finish = [&](float Lfin, const float* a) {
-    if (!row_ok) return;
-    const float inv = Lfin > 0.f ? 1.f / Lfin : 0.f;
-    __nv_bfloat16* dst = p.o + ((size_t)t * p.Hq + head) * D + seg * SEG;
-#pragma unroll
-    for (int d = 0; d < SEG; ++d) dst[d] = __float2bfloat16(a[d] * inv);
-  };
+  // rows of the tile held by this lane: row0 (accumulator halves 0, 1) and row0 + 8 (halves 2, 3);
+  // columns i * 8 + 2 * (lane & 3) + {0, 1}
+  const int cq = 2 * (lane & 3);
   if (Z == 1) {
-    finish(Lsum, acc);
-    cbar();                                           // the rings and s_q are reused by the next unit
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = half ? row1 : row0;
+      if (row >= G) continue;
+      const float inv = l[half] > 0.f ? 1.f / l[half] : 0.f;
+      __nv_bfloat16* dst = p.o + ((size_t)t * p.Hq + h * G + row) * D + cq;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2 * half] * inv, o[i][2 * half + 1] * inv);
+    }
     return;
   }
-  // ---- cross-split merge by the CTA that arrives last on this (request, kv head)
+  // ---- cross-split merge by the warp that arrives last on this (request, kv head)
   const size_t unit = ((size_t)r * p.Hkv + h) * Z;
-  float* po = p.attn_part_o + ((unit + z) * 16 + row) * D + seg * SEG;
 #pragma unroll
-  for (int d = 0; d < SEG; ++d) po[d] = acc[d];
-  if (seg == 0) {
-    p.attn_part_ml[((unit + z) * 16 + row) * 2 + 0] = mm;
-    p.attn_part_ml[((unit + z) * 16 + row) * 2 + 1] = Lsum;
+  for (int half = 0; half < 2; ++half) {
+    const int row = half ? row1 : row0;
+    if (row >= G) continue;
+    float* po = p.part_o + ((unit + z) * 16 + row) * D + cq;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(po + i * 8) = make_float2(o[i][2 * half], o[i][2 * half + 1]);
+    if ((lane & 3) == 0) {
+      p.part_ml[((unit + z) * 16 + row) * 2 + 0] = m[half];
+      p.part_ml[((unit + z) * 16 + row) * 2 + 1] = l[half];
+    }
   }
   __threadfence();
-  cbar();
-  if (ct == 0) {
-    const int old = atomicAdd(&p.attn_counters[r * p.Hkv + h], 1);
-    *sh.s_last = (old == Z - 1);
-  }
-  cbar();
-  if (*sh.s_last) {
-    __threadfence();
+  __syncwarp();
+  int last = 0;
+  if (lane == 0) last = (atomicAdd(&p.counters[r * p.Hkv + h], 1) == Z - 1);
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (!last) return;
+  __threadfence();
+  // lane owns 4 columns of every row of the group
+  for (int row = 0; row < G; ++row) {
     float mfin = -INFINITY;
-    for (int s2 = 0; s2 < Z; ++s2) mfin = fmaxf(mfin, __ldcg(&p.attn_part_ml[((unit + s2) * 16 + row) * 2]));
+    for (int s2 = 0; s2 < Z; ++s2) mfin = fmaxf(mfin, __ldcg(&p.part_ml[((unit + s2) * 16 + row) * 2]));
     float Lfin = 0.f;
-#pragma unroll
-    for (int d = 0; d < SEG; ++d) acc[d] = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s2 = 0; s2 < Z; ++s2) {
-      const float ms = __ldcg(&p.attn_part_ml[((unit + s2) * 16 + row) * 2]);
+      const float ms = __ldcg(&p.part_ml[((unit + s2) * 16 + row) * 2]);
       const float sc = (ms == -INFINITY) ? 0.f : ex2(ms - mfin);
-      Lfin += __ldcg(&p.attn_part_ml[((unit + s2) * 16 + row) * 2 + 1]) * sc;
-      const float* src = p.attn_part_o + ((unit + s2) * 16 + row) * D + seg * SEG;
-#pragma unroll
-      for (int d = 0; d < SEG; ++d) acc[d] += __ldcg(src + d) * sc;
+      Lfin += __ldcg(&p.part_ml[((unit + s2) * 16 + row) * 2 + 1]) * sc;
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_o + ((unit + s2) * 16 + row) * D) + lane);
+      acc.x += v.x * sc; acc.y += v.y * sc; acc.z += v.z * sc; acc.w += v.w * sc;
     }
-    finish(Lfin, acc);
-    if (ct == 0) p.attn_counters[r * p.Hkv + h] = 0;
+    const float inv = Lfin > 0.f ? 1.f / Lfin : 0.f;
+    uint2 pk;
+    pk.x = pack_bf16(acc.x * inv, acc.y * inv);
+    pk.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(p.o + ((size_t)t * p.Hq + h * G + row) * D + 4 * lane) = pk;
   }
-  cbar();
+  if (lane == 0) p.counters[r * p.Hkv + h] = 0;
 }
 
-__device__ void phase_attn(const Params& p, const Shared& sh, uint8_t* smem, const LayerDesc& L, int ct) {
-  const int Z = p.kv_splits;
-  const int total = p.T * p.Hkv * Z;
-  for (int u = blockIdx.x; u < total && !*sh.abort_flag; u += gridDim.x) {
-    const int z = u % Z, rh = u / Z;
-    attn_unit(p, sh, smem, L, ct, rh / p.Hkv, rh % p.Hkv, z);
+__device__ __noinline__ void phase_attn(const Params& p, const Shared& sh, uint8_t* smem, const LayerDesc& L, int ct) {
+  AttnArgs a;
+  a.part = p.part; a.positions = p.positions; a.slot_mapping = p.slot_mapping; a.block_tables = p.block_tables;
+  a.seq_lens = p.seq_lens; a.inv_freq = p.inv_freq; a.qkv_bias = L.qkv_bias; a.q_norm = L.q_norm;
+  a.k_norm = L.k_norm; a.kv_cache = L.kv_cache; a.o = p.o; a.part_o = p.attn_part_o; a.part_ml = p.attn_part_ml;
+  a.counters = p.attn_counters; a.num_blocks = p.num_blocks; a.gq = p.g[0]; a.Hq = p.Hq; a.Hkv = p.Hkv;
+  a.G = p.Hq / p.Hkv; a.Z = p.kv_splits; a.rot_pairs = p.rot_pairs; a.interleaved = p.interleaved;
+  a.max_blocks = p.max_blocks; a.block_size = p.block_size; a.eps = p.eps; a.scale_log2 = p.scale_log2;
+  const int lw = ct >> 5, lane = ct & 31;
+  const int total = p.T * a.Hkv * a.Z;
+  const int stride = (int)gridDim.x * 4;
+  volatile int* abort_flag = sh.abort_flag;
+  for (int u = blockIdx.x * 4 + lw; u < total && !*abort_flag; u += stride) {
+    const int z = u % a.Z, rh = u / a.Z;
+    attn_warp_unit(a, smem, lw, lane, rh / a.Hkv, rh % a.Hkv, z);
+    __syncwarp();
   }
 }
 
 // Epilogue of a GEMM phase: the accumulator of every segment of this CTA's range goes to its fp32
 // partial slot [seg][t][n] (thread = weight row n, 32 token columns per TMEM load).
-__device__ void phase_gemm_epilogue(const Params& p, const Shared& sh, int warp, int lane, int gi, uint32_t tmem_base,
-                                    int& segcount) {
-  const GemmShape& g = p.g[gi];
+__device__ __noinline__ void phase_gemm_epilogue(const Params& p, const Shared& sh, int warp, int lane, int gi, uint32_t tmem_base,
+                                    int& segcount_io, int layer) {
+  // locals: fields read through the references would be re-read after every global store
+  const GemmShape g = p.g[gi];
+  const int T = p.T;
+  float* const part = p.part;
+  uint64_t* const tfull = sh.tfull;
+  uint64_t* const tempty = sh.tempty;
+  int segcount = segcount_io;
   const int q = warp & 3;
   const int row = q * 32 + lane;
   int u = min(g.total, (int)blockIdx.x * g.U);
@@ -681,34 +855,44 @@ __device__ void phase_gemm_epilogue(const Params& p, const Shared& sh, int warp,
     const int slot = (int)blockIdx.x - tile_first_cta(g, tile);
     const int acc = segcount & 1;
     const uint32_t acc_ph = (segcount >> 1) & 1;
-    if (!mbar_wait(&sh.tfull[acc], acc_ph, sh.abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) return;
+    if (warp == 2 && lane == 0) stamp_ev(p, layer, gi, 0);
+    if (!mbar_spin(&tfull[acc], acc_ph, p, sh, ST_TIMEOUT_TMEM_FULL)) break;
+    if (warp == 2 && lane == 0) stamp_ev(p, layer, gi, 4);
     tc_fence_after();
     const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
     const int n = tile * BM + row;
-    float* dst = p.part + (size_t)slot * MAXT * g.N + n;
+    float* dst = part + (size_t)slot * MAXT * g.N + n;
+    const size_t ldn = (size_t)g.N;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
-      if (c0 >= p.T) break;
+      if (c0 >= T) break;
       uint32_t r[32];
       tmem_ld_32x32(taddr + c0, r);
       tmem_ld_wait();
       if (n < g.N) {
+        if (c0 + 32 <= T) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (c0 + j < p.T) dst[(size_t)(c0 + j) * g.N] = __uint_as_float(r[j]);
+          for (int j = 0; j < 32; ++j) dst[(size_t)(c0 + j) * ldn] = __uint_as_float(r[j]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < T) dst[(size_t)(c0 + j) * ldn] = __uint_as_float(r[j]);
+        }
       }
     }
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(&sh.tempty[acc]);
+    if (lane == 0) mbar_arrive(&tempty[acc]);
+    if (warp == 2 && lane == 0) stamp_ev(p, layer, gi, 5);
     ++segcount;
     u = seg_end;
   }
+  segcount_io = segcount;
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
 decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_constant__ CUtensorMap tmO,
-                     const __grid_constant__ CUtensorMap tmAct, const Params p) {
+                     const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BAR_OFF);
@@ -721,7 +905,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
   sh.tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
   sh.abort_flag = reinterpret_cast<volatile int*>(sh.tmem_slot + 1);
   sh.phase_open = reinterpret_cast<volatile int*>(sh.tmem_slot + 2);
-  sh.s_last = reinterpret_cast<volatile int*>(sh.tmem_slot + 3);
+  sh.attn_done = reinterpret_cast<volatile int*>(sh.tmem_slot + 3);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -736,7 +920,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
     mbar_init(&sh.tempty[1], 4);
     *sh.abort_flag = 0;
     *sh.phase_open = 0;
-    *sh.s_last = 0;
+    *sh.attn_done = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmH);
     tma_prefetch_desc(&tmO);
@@ -763,7 +947,8 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
       unsigned long long t_idle = 0;
       while (!xc.done) {
         bool progressed = false;
-        if (!wc.done && wcount - xcount < STAGES) {
+        // weights behind an attention phase wait until this CTA's attention has given the ring back
+        if (!wc.done && wcount - xcount < STAGES && *sh.attn_done >= wc.layer + (wc.gi >= 1 ? 1 : 0)) {
           const int s = wcount % STAGES;
           const uint32_t ph = (uint32_t)(wcount / STAGES) & 1u;
           if (mbar_test(&sh.empty[s], ph ^ 1u)) {
@@ -780,9 +965,10 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
         if (xcount < wcount) {
           const int ph_idx = gemm_phase(p, xc.layer, xc.gi);
           if (*sh.phase_open >= ph_idx) {
+            const bool acquired_new = acquired != ph_idx;
             if (acquired != ph_idx) {
-              // the operand was written by other CTAs (generic proxy) and is read by TMA (async proxy)
-              (void)ld_acquire_gpu(p.ctrl);
+              // the operand was written by other CTAs (generic proxy; this CTA acquired the barrier
+              // that follows their writes) and is read by TMA (async proxy)
               asm volatile("fence.proxy.async;" ::: "memory");
               acquired = ph_idx;
             }
@@ -790,6 +976,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
             const int tile = xc.u / g.kbt, kb = xc.u - tile * g.kbt;
             const int s = xcount % STAGES;
             const CUtensorMap* tx = xc.gi == 1 ? &tmO : (xc.gi == 3 ? &tmAct : &tmH);
+            if (acquired_new) stamp_ev(p, xc.layer, xc.gi, 1);
             mbar_expect_tx(&sh.fullX[s], B_BYTES);
             tma_load_2d(smem + s * STAGE_BYTES + A_BYTES, tx, &sh.fullX[s], kb * BK, 0);
             ++xcount;
@@ -829,19 +1016,20 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
         const int tile = mc.u / kbt;
         const int acc = segcount & 1;
         const uint32_t acc_ph = (segcount >> 1) & 1;
-        if (!mbar_wait(&sh.tempty[acc], acc_ph ^ 1, sh.abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
+        if (!mbar_spin(&sh.tempty[acc], acc_ph ^ 1, p, sh, ST_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool first = true;
         do {
           const int s = count % STAGES;
           const uint32_t ph = (uint32_t)(count / STAGES) & 1u;
-          if (!mbar_wait(&sh.fullW[s], ph, sh.abort_flag, p.status, ST_TIMEOUT_FULL) ||
-              !mbar_wait(&sh.fullX[s], ph, sh.abort_flag, p.status, ST_TIMEOUT_FULL)) {
+          if (!mbar_spin(&sh.fullW[s], ph, p, sh, ST_TIMEOUT_FULL) ||
+              !mbar_spin(&sh.fullX[s], ph, p, sh, ST_TIMEOUT_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          if (first) stamp_ev(p, layer, gi, 2);
           const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
           const uint64_t adesc = umma_desc_k_sw128(a_addr);
           const uint64_t bdesc = umma_desc_k_sw128(a_addr + A_BYTES);
@@ -854,6 +1042,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
           cur_next(mc, p);
         } while (!mc.done && mc.layer == layer && mc.gi == gi && mc.u / kbt == tile);
         if (ok) umma_commit(&sh.tfull[acc]);
+        stamp_ev(p, layer, gi, 3);
         ++segcount;
       }
     }
@@ -868,6 +1057,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
     // the barrier count must be the same on every CTA, so `barriers` counts them
     int barriers = 0;
     auto sync_phase = [&](bool barrier) {
+      if (p.dbg != nullptr && ct == 0) p.dbg[(size_t)(2 * pidx) * gridDim.x + blockIdx.x] = global_timer_ns();
       if (barrier) {
         ++barriers;
         alive = grid_barrier(p, sh, barriers * G, ct);
@@ -875,6 +1065,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
         cbar();
         alive = !*sh.abort_flag;
       }
+      if (p.dbg != nullptr && ct == 0) p.dbg[(size_t)(2 * pidx + 1) * gridDim.x + blockIdx.x] = global_timer_ns();
       ++pidx;
       if (ct == 0) *sh.phase_open = pidx;
       cbar();
@@ -886,13 +1077,17 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
       phase_norm(p, sh, smem, ct, l, l == 0, 3, 1, use_idx - 1, L.ln_in, true);
       sync_phase(true);
       if (!alive) break;
-      phase_gemm_epilogue(p, sh, warp, lane, 0, tmem_base, segcount);
+      phase_gemm_epilogue(p, sh, warp, lane, 0, tmem_base, segcount, l);
       sync_phase(true);
       if (!alive) break;
       phase_attn(p, sh, smem, L, ct);
+      // generic-proxy accesses of the ring are over; the next writer is TMA (async proxy)
+      fence_proxy_async_smem();
+      cbar();
+      if (ct == 0) *sh.attn_done = l + 1;
       sync_phase(true);
       if (!alive) break;
-      phase_gemm_epilogue(p, sh, warp, lane, 1, tmem_base, segcount);
+      phase_gemm_epilogue(p, sh, warp, lane, 1, tmem_base, segcount, l);
       sync_phase(true);
       if (!alive) break;
       if (p.world > 1) {
@@ -903,13 +1098,13 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
       phase_norm(p, sh, smem, ct, l, false, 1, 0, use_idx, L.ln_post, true);
       sync_phase(true);
       if (!alive) break;
-      phase_gemm_epilogue(p, sh, warp, lane, 2, tmem_base, segcount);
+      phase_gemm_epilogue(p, sh, warp, lane, 2, tmem_base, segcount, l);
       sync_phase(true);
       if (!alive) break;
       phase_swiglu(p, ct);
       sync_phase(true);
       if (!alive) break;
-      phase_gemm_epilogue(p, sh, warp, lane, 3, tmem_base, segcount);
+      phase_gemm_epilogue(p, sh, warp, lane, 3, tmem_base, segcount, l);
       sync_phase(true);
       if (!alive) break;
       if (p.world > 1) {
@@ -936,6 +1131,7 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmH, const __grid_const
       // every CTA is past its last barrier: re-arm the counters and open the next launch's epoch
       p.ctrl[0] = 0;
       p.ctrl[1] = 0;
+      p.ctrl[32] = 0;
       p.ctrl[2] = *reinterpret_cast<volatile int*>(p.ctrl + 2) + 1;
       __threadfence();
     }
@@ -985,6 +1181,11 @@ static int mega_grid(int num_sms) {
   cudaGetDevice(&dev);
   int& g = cached[dev & 63];
   if (g == 0) {
+    if (cudaFuncSetAttribute(decode_layers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
     int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_layers_kernel, THREADS, SMEM_BYTES) !=
             cudaSuccess || per_sm < 1) {
@@ -1003,6 +1204,10 @@ static size_t plan_gemm(GemmShape& g, int N, int K, int grid) {
   g.kbt = (K + BK - 1) / BK;
   g.total = g.n_tiles * g.kbt;
   g.U = (g.total + grid - 1) / grid;
+  // a consumer sums the partial slots of a tile one round trip per few slots: bound them, even if a
+  // small projection then runs on fewer CTAs
+  const int min_u = (g.kbt + MAX_SLOTS - 2) / (MAX_SLOTS - 1);
+  if (g.U < min_u) g.U = min_u;
   int max_segs = (g.kbt + g.U - 1) / g.U + 1;
   return (size_t)max_segs * MAXT * N * sizeof(float);
 }
@@ -1021,7 +1226,7 @@ extern "C" size_t b200_mega_partial_bytes(int H, int Hq, int Hkv, int I, int num
 // One decode step through `num_layers` decoder layers.  hidden0 [T, H] (embedding rows) -> residual
 // [T, H] = the residual stream after the last layer (the caller applies the final norm).  T <= 64 rows,
 // one per request (padded requests: seq_len 0, slot -1).  h / o / act are [64, *] operand buffers the
-// kernel owns between phases; part / attn_* are scratch; ctrl is int[4], zero before the first launch
+// kernel owns between phases; part / attn_* are scratch; ctrl is int[64], zero before the first launch
 // (the kernel re-arms it; after a launch that reported a status, zero it again).
 // Tensor parallel (world > 1): peers = heap bases, slab_off / flag_off = heap offsets of the two
 // receive slabs [world][64][H] bf16 and their flags int[world][256].
@@ -1035,6 +1240,7 @@ extern "C" int b200_mega_decode(const void* layers_dev, int num_layers, const vo
                                 int rank, void* const* peers, unsigned long long slab0_off,
                                 unsigned long long slab1_off, unsigned long long flag0_off,
                                 unsigned long long flag1_off, unsigned int spin_limit, int num_sms,
+                                unsigned long long* dbg, int dbg_layer, int dbg_gi, int dbg_ev_base,
                                 cudaStream_t stream) {
   if (T <= 0 || num_layers <= 0) return 0;
   if (T > MAXT || H % 128 || I % 128 || Hq % Hkv || (Hq / Hkv) > 16 || H > 128 * 8 * 8 || world < 1 || world > 8 ||
@@ -1082,6 +1288,7 @@ extern "C" int b200_mega_decode(const void* layers_dev, int num_layers, const vo
   p.slab_off[0] = slab0_off; p.slab_off[1] = slab1_off;
   p.flag_off[0] = flag0_off; p.flag_off[1] = flag1_off;
   p.spin_limit = spin_limit;
+  p.dbg = dbg; p.dbg_layer = dbg_layer; p.dbg_gi = dbg_gi; p.dbg_ev_base = dbg_ev_base;
   CUtensorMap tmH, tmO, tmAct;
   int rc = b200_make_tmap_2d(&tmH, h, 2, (uint64_t)MAXT, (uint64_t)H, (uint64_t)H * 2, BN, BK);
   if (rc) return rc;
@@ -1089,8 +1296,6 @@ extern "C" int b200_mega_decode(const void* layers_dev, int num_layers, const vo
   if (rc) return rc;
   rc = b200_make_tmap_2d(&tmAct, act, 2, (uint64_t)MAXT, (uint64_t)I, (uint64_t)I * 2, BN, BK);
   if (rc) return rc;
-  static unsigned long long attr_seen = 0;
-  B200_CUDA_CHECK(ensure_dynamic_smem(decode_layers_kernel, SMEM_BYTES, &attr_seen));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(THREADS);

@@ -26,7 +26,8 @@ int b200_mega_decode(const void* layers_dev, int num_layers, const void* hidden0
                      void* attn_part_ml, int* attn_counters, int* ctrl, int* status, int world, int rank,
                      void* const* peers, unsigned long long slab0_off, unsigned long long slab1_off,
                      unsigned long long flag0_off, unsigned long long flag1_off, unsigned int spin_limit,
-                     int num_sms, cudaStream_t stream);
+                     int num_sms, unsigned long long* dbg, int dbg_layer, int dbg_gi, int dbg_ev_base,
+                     cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -244,6 +244,10 @@ def bench_decode_model(reqs, ctx, layers=8, iters=10, H=4096, I=14336, Hq=32, Hk
     kv_bytes = reqs * (ctx + 1) * 2 * Hkv * 128 * 2.0
     roof_us = (w_bytes + kv_bytes) / (pk["hbm_gbs"] * 1e9) * 1e6
     out = []
+    import os
+    from .. import envs
+    os.environ["B200_DECODE_MEGAKERNEL"] = "1"
+    envs.reset()
     for mode in ("persistent", "per-layer"):
         if mode == "persistent":
             m.setup_decode_fusion(kvs)

@@ -126,7 +126,9 @@ class DecodeMega:
         self.attn_part_o = torch.empty(units * 16 * HEAD_DIM, dtype=torch.float32, device=device)
         self.attn_part_ml = torch.empty(units * 16 * 2, dtype=torch.float32, device=device)
         self.attn_counters = torch.zeros(T * self.Hkv, dtype=torch.int32, device=device)
-        self.ctrl = torch.zeros(8, dtype=torch.int32, device=device)
+        self.ctrl = torch.zeros(64, dtype=torch.int32, device=device)
+        self.dbg = None                  # int64 tensor [rows, CTAs]: phase end times (kernel header: Params::dbg)
+        self.dbg_event = (-1, -1, 0)     # (layer, projection, first row) of the role events of one GEMM phase
         self.slab = [0, 0]
         self.flag = [0, 0]
         if heap is not None:
@@ -139,16 +141,19 @@ class DecodeMega:
         self.ready = True
         return self
 
-    def kv_splits(self, T: int) -> int:
-        """KV splits per (request, kv head): enough units to give every SM work, and a unit count that
-        fills whole waves of the grid."""
+    def kv_splits(self, T: int, ctx_hint: int = 1024) -> int:
+        """KV splits per (request, kv head).  A (request, kv head, split) unit is one warp's work and an
+        SM runs four of them at a time: few long units leave warps idle, many short ones pay the fixed
+        prologue and merge per unit."""
         if envs.B200_ATTN_SPLIT_KV > 0:
             return min(self.max_splits, envs.B200_ATTN_SPLIT_KV)
         pairs = max(1, T * self.Hkv)
+        slots = 4 * self.sms
+        chunks = max(1, ctx_hint // 16)
         best, best_cost = 1, None
         for s in (1, 2, 4, 8):
-            waves = -(-pairs * s // self.sms)
-            cost = waves / s + 0.04 * s            # time ~ waves of 1/s-length units, plus a merge term
+            rounds = -(-pairs * s // slots)
+            cost = rounds * (chunks / s + 6.0)       # chunk times: streaming + prologue / merge per unit
             if best_cost is None or cost < best_cost - 1e-9:
                 best, best_cost = s, cost
         return best
@@ -175,12 +180,13 @@ class DecodeMega:
             c_int(self.kv_splits(T)), _p(self.attn_part_o), _p(self.attn_part_ml), _p(self.attn_counters),
             _p(self.ctrl), _p(ws.status), c_int(self.world), c_int(self.rank), peers,
             c_ulonglong(self.slab[0]), c_ulonglong(self.slab[1]), c_ulonglong(self.flag[0]),
-            c_ulonglong(self.flag[1]), ctypes.c_uint(spin), c_int(self.sms), _stream()), "mega_decode")
+            c_ulonglong(self.flag[1]), ctypes.c_uint(spin), c_int(self.sms), _p(self.dbg),
+            c_int(self.dbg_event[0]), c_int(self.dbg_event[1]), c_int(self.dbg_event[2]), _stream()), "mega_decode")
         count_launch()
         return self.zero_hidden[:T], self.residual[:T]
 
     def reset(self) -> None:
         """After a launch that reported a device status: re-arm the barrier words and counters."""
         self.ctrl[:2].zero_()
-        self.ctrl[3:].zero_()
+        self.ctrl[3:].zero_()          # keeps ctrl[2], the launch epoch the peers share
         self.attn_counters.zero_()
