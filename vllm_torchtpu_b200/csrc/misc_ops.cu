@@ -199,6 +199,29 @@ __global__ void tq4_decode_kernel(const uint8_t* __restrict__ k_codes, const __n
   for (int j = 0; j < 4; ++j) v[(size_t)row * 128 + 4 * lane + j] = __float2bfloat16(scale * vc[j] + zero);
 }
 
+// ------------------------------------------------------------------- KV cache write
+// cache[blk, 0 | 1, h, off, :] = k | v of token t, slot = slot_mapping[t] (negative: skipped), for
+// callers that hand over already-rotated keys (a host framework's attention layer).  16 bytes per thread.
+__global__ void kv_write_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                __nv_bfloat16* __restrict__ cache, const long long* __restrict__ slots64,
+                                const int* __restrict__ slots32, int Hkv, int D, int block_size, long long num_slots,
+                                long long ldk, long long ldv) {
+  const int t = blockIdx.x;
+  const long long slot = slots64 != nullptr ? slots64[t] : (long long)slots32[t];
+  if (slot < 0 || slot >= num_slots) return;
+  const long long blk = slot / block_size;
+  const int off = (int)(slot - blk * block_size);
+  const int vec_per_head = D >> 3;
+  for (int i = threadIdx.x; i < 2 * Hkv * vec_per_head; i += blockDim.x) {
+    const int kind = i / (Hkv * vec_per_head);
+    const int r = i - kind * Hkv * vec_per_head;
+    const int h = r / vec_per_head, c = r - h * vec_per_head;
+    const __nv_bfloat16* src = (kind == 0 ? k + (size_t)t * ldk : v + (size_t)t * ldv) + h * D + c * 8;
+    __nv_bfloat16* dst = cache + ((((size_t)blk * 2 + kind) * Hkv + h) * block_size + off) * D + c * 8;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -284,6 +307,22 @@ extern "C" int b200_tq4_decode(const void* k_codes, const void* k_norm, const vo
   tq4_decode_kernel<<<(rows + 7) / 8, 256, 0, stream>>>((const uint8_t*)k_codes, (const __nv_bfloat16*)k_norm,
                                                         (const uint8_t*)v_codes, (const __nv_bfloat16*)v_meta,
                                                         (__nv_bfloat16*)k, (__nv_bfloat16*)v, rows);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// k, v: [T, Hkv, D] bf16 with row strides ldk / ldv (elements); cache [blocks, 2, Hkv, block_size, D] bf16;
+// slot mapping as int64 (slots64) or int32 (slots32), exactly one of them non-null.
+extern "C" int b200_kv_write(const void* k, const void* v, void* cache, const long long* slots64, const int* slots32,
+                             int T, int Hkv, int D, int block_size, long long num_blocks, long long ldk, long long ldv,
+                             cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D % 8 || ldk % 8 || ldv % 8 || (slots64 == nullptr) == (slots32 == nullptr)) {
+    b200_set_last_error("kv_write: head_dim and strides multiples of 8, one slot mapping", __FILE__, __LINE__);
+    return -1;
+  }
+  b200::kv_write_kernel<<<T, 128, 0, stream>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)cache,
+                                               slots64, slots32, Hkv, D, block_size, num_blocks * block_size, ldk, ldv);
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

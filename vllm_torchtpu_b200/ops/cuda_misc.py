@@ -106,3 +106,22 @@ def tq4_decode(kc, kn, vc, vm):
                                        c_int(rows), _c._stream()), "tq4_decode")
     count_launch()
     return k, v
+
+
+def kv_write(key, value, kv_cache, slot_mapping):
+    """Write already-rotated keys / values [T, Hkv, D] (bf16, unit stride in D) into the paged cache
+    [blocks, 2, Hkv, block_size, D] at ``slot_mapping`` (int32 or int64; negative slots are skipped)."""
+    from ctypes import c_longlong
+    _c._require_bf16(key, value, kv_cache)
+    T, Hkv, D = key.shape
+    assert key.stride(2) == 1 and value.stride(2) == 1 and key.stride(1) == D and value.stride(1) == D
+    nb, _, _, bs, _ = kv_cache.shape
+    s64 = slot_mapping if slot_mapping.dtype == torch.int64 else None
+    s32 = slot_mapping if slot_mapping.dtype == torch.int32 else None
+    if s64 is None and s32 is None:
+        raise TypeError("slot_mapping must be int32 or int64")
+    n = min(T, slot_mapping.numel())
+    _c._check(_c.lib().b200_kv_write(_c._p(key), _c._p(value), _c._p(kv_cache), _c._p(s64), _c._p(s32), c_int(n),
+                                     c_int(Hkv), c_int(D), c_int(bs), c_longlong(nb), c_longlong(key.stride(0)),
+                                     c_longlong(value.stride(0)), _c._stream()), "kv_write")
+    count_launch()
