@@ -72,3 +72,11 @@ def test_tp2_moe_engine_fused_ep_plane_equals_gather_plane():
     assert fused["status"] == 0 and gathered["status"] == 0
     same = sum(a == b for a, b in zip(fused["tokens"], gathered["tokens"]))
     assert same >= 3, (fused, gathered)
+
+
+def test_ipc_transport_pulls_blocks_gpu_to_gpu():
+    """Data plane of disaggregated prefill / decode: the consumer process maps the producer's pool
+    (CUDA IPC) and one kernel copies the listed blocks of every layer over NVLink."""
+    _need(2)
+    r = _run("ipc_pull_worker.py", 2)
+    assert "IPC_PULL_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

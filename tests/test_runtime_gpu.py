@@ -1,0 +1,104 @@
+"""Runtime-side kernels on one GPU: a bounded device wait that runs out (status word, no hang), the
+paged-KV block mover with its range check and NaN screen, the KV write of the vLLM backend."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("needs a GPU", allow_module_level=True)
+
+from vllm_torchtpu_b200.kv_transfer.transport import PoolInfo, TransferError, copy_blocks, nan_blocks  # noqa: E402
+from vllm_torchtpu_b200.ops import cuda, cuda_misc  # noqa: E402
+
+DEV = "cuda"
+
+
+def test_flag_wait_runs_out_and_reports_status_without_hanging():
+    """The consumer of the push plane waits for tile flags of an epoch nobody raises: the wait gives up
+    after its iteration limit, the kernel returns, the status word reads 'waited for a flag' and the
+    context keeps working."""
+    T, N, world, max_tiles = 4, 1024, 2, 64
+    recv = torch.zeros(world * T * N, dtype=torch.bfloat16, device=DEV)
+    flags = torch.zeros(world * max_tiles, dtype=torch.int32, device=DEV)          # never raised
+    ctrl = torch.tensor([1, 0, 0, 0], dtype=torch.int32, device=DEV)               # producers "completed" epoch 1
+    residual = torch.ones(T, N, dtype=torch.bfloat16, device=DEV)
+    weight = torch.ones(N, dtype=torch.bfloat16, device=DEV)
+    y = torch.full((T, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    ws = cuda.Workspace.get(torch.device(DEV))
+    assert cuda.check_status() == 0
+    stride = (T * N * 2 + 255) // 256 * 256
+    cuda._check(cuda.lib().b200_reduce_pushed_rms_norm(
+        cuda._p(recv), ctypes.c_ulonglong(stride), cuda._p(flags), ctypes.c_int(max_tiles), cuda._p(ctrl),
+        cuda._p(residual), cuda._p(weight), cuda._p(y), ctypes.c_int(T), ctypes.c_int(N), ctypes.c_int(world),
+        ctypes.c_float(1e-5), cuda._p(ws.status), ctypes.c_uint(2000), cuda._stream()), "reduce_pushed_rms_norm")
+    torch.cuda.synchronize()                       # returns: the wait was bounded
+    assert cuda.check_status() == 5                # ST_TIMEOUT_FLAG, and the word is cleared by the read
+    assert torch.equal(y, torch.full_like(y, 7.0)) # rows whose flags never came are left untouched
+    # the context is intact: the next launch works and reports no status
+    x = torch.randn(T, N, device=DEV).bfloat16()
+    out = cuda.rms_norm(x, weight, 1e-5)
+    want = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5)
+    assert (out.float() - want).abs().max() < 2e-2 and cuda.check_status() == 0
+
+
+def _pools(nb_src=12, nb_dst=9, layers=3, shape=(2, 2, 16, 64)):
+    g = torch.Generator(device=DEV).manual_seed(0)
+    src = [torch.randn((nb_src,) + shape, device=DEV, generator=g).bfloat16() for _ in range(layers)]
+    dst = [torch.zeros((nb_dst,) + shape, dtype=torch.bfloat16, device=DEV) for _ in range(layers)]
+    return src, dst
+
+
+def test_block_copy_between_pools_and_pinned_host():
+    src, dst = _pools()
+    s_ids, d_ids = [3, 0, 11, 7], [1, 8, 2, 5]
+    copy_blocks(PoolInfo("a", src), PoolInfo("b", dst), s_ids, d_ids)
+    torch.cuda.synchronize()
+    for a, b in zip(src, dst):
+        assert torch.equal(b[d_ids], a[s_ids])
+        untouched = [i for i in range(b.shape[0]) if i not in d_ids]
+        assert int(b[untouched].abs().sum()) == 0
+    # device -> pinned host slab -> another device pool (the offload tier's two directions)
+    host = [torch.zeros((6,) + tuple(src[0].shape[1:]), dtype=torch.bfloat16, pin_memory=True) for _ in src]
+    copy_blocks(PoolInfo("a", src), PoolInfo("h", host), [2, 4], [5, 0])
+    torch.cuda.synchronize()
+    assert all(torch.equal(h[[5, 0]], a[[2, 4]].cpu()) for a, h in zip(src, host))
+    back = [torch.zeros_like(d) for d in dst]
+    copy_blocks(PoolInfo("h", host), PoolInfo("c", back), [5, 0], [3, 4])
+    torch.cuda.synchronize()
+    assert all(torch.equal(b[[3, 4]], a[[2, 4]]) for a, b in zip(src, back))
+    with pytest.raises(TransferError):
+        copy_blocks(PoolInfo("a", src), PoolInfo("b", dst), [12], [0])
+    assert cuda.check_status() == 0
+
+
+def test_nan_screen_flags_exactly_the_poisoned_blocks():
+    src, _ = _pools()
+    assert nan_blocks(PoolInfo("a", src), [0, 1, 2, 3]) == []
+    src[1][2, 0, 1, 3, 5] = float("nan")
+    src[2][9, 1, 0, 0, 0] = float("inf")
+    assert nan_blocks(PoolInfo("a", src), [0, 2, 5, 9, 11]) == [2, 9]
+    cpu = [t.cpu() for t in src]
+    assert nan_blocks(PoolInfo("cpu", cpu), [0, 2, 5, 9, 11]) == [2, 9]
+
+
+@pytest.mark.parametrize("slot_dtype", [torch.int32, torch.int64])
+def test_kv_write_into_paged_cache(slot_dtype):
+    T, Hkv, D, bs, nb = 37, 2, 128, 16, 9
+    g = torch.Generator(device=DEV).manual_seed(2)
+    qkv = torch.randn(T, (4 + 2 * Hkv) * D, device=DEV, generator=g).bfloat16()       # k / v are strided views
+    k = qkv[:, 4 * D:(4 + Hkv) * D].view(T, Hkv, D)
+    v = qkv[:, (4 + Hkv) * D:].view(T, Hkv, D)
+    cache = torch.zeros(nb, 2, Hkv, bs, D, dtype=torch.bfloat16, device=DEV)
+    slots = torch.randperm(nb * bs, device=DEV)[:T].to(slot_dtype)
+    slots[5] = -1
+    cuda_misc.kv_write(k, v, cache, slots)
+    torch.cuda.synchronize()
+    want = torch.zeros_like(cache)
+    for t, s in enumerate(slots.tolist()):
+        if s >= 0:
+            want[s // bs, 0, :, s % bs] = k[t]
+            want[s // bs, 1, :, s % bs] = v[t]
+    assert torch.equal(cache, want)

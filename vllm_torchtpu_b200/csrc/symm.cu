@@ -10,6 +10,8 @@
 //
 // Plays the role of the reference's in-kernel remote DMA + semaphore substrate
 // (reference: src/vllm_torchtpu/kernels/collectives/util.py:33-58).
+#include <cuda.h>
+
 #include "common.cuh"
 
 using namespace b200;
@@ -35,6 +37,33 @@ extern "C" int b200_ipc_get_handle(void* p, void* handle_out_64) {
   cudaIpcMemHandle_t h;
   B200_CUDA_CHECK(cudaIpcGetMemHandle(&h, p));
   memcpy(handle_out_64, &h, sizeof(h));
+  return 0;
+}
+
+// Base address and size of the allocation that holds `p`: an IPC handle names the whole allocation, so
+// an exporter that hands out a pointer inside a larger block (a caching allocator's segment) also
+// publishes the pointer's offset from this base.
+extern "C" int b200_ipc_range(const void* p, unsigned long long* base_out, unsigned long long* size_out) {
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      b200_set_last_error("cuMemGetAddressRange not available", __FILE__, __LINE__);
+      return -1;
+    }
+    fn = reinterpret_cast<RangeFn>(ptr);
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (fn(&base, &size, reinterpret_cast<CUdeviceptr>(p)) != CUDA_SUCCESS) {
+    b200_set_last_error("cuMemGetAddressRange failed", __FILE__, __LINE__);
+    return -2;
+  }
+  *base_out = (unsigned long long)base;
+  *size_out = (unsigned long long)size;
   return 0;
 }
 

@@ -77,6 +77,7 @@ _decl("B200_GEMM_2SM_MIN_T", int, 1024,
 _decl("B200_ATTN_PREFILL_IMPL", str, "tc", "prefill attention kernel: tcgen05 (head_dim 128) or legacy mma.sync",
       choices=("tc", "mma"))
 _decl("B200_ATTN_SPLIT_KV", int, 0, "force the decode split-KV factor (0 = heuristic)")
+_decl("B200_KV_SAVE_NAN_CHECK", bool, True, "screen KV blocks for NaN / Inf before they are stored or published")
 _decl("B200_DECODE_MEGAKERNEL", bool, False,
       "decode-only steps of at most 64 requests of dense models run all layers in one persistent kernel "
       "(experimental: measured slower than the per-layer kernels, see profiles/decode_persistent_kernel_phases.md)")

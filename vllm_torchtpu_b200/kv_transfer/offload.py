@@ -21,7 +21,7 @@ from .. import envs
 from ..engine.block_manager import hash_block
 from ..logger import init_logger
 from .base import Connector, ConnectorMetadata, SchedulerConnectorBase, WorkerConnectorBase
-from .transport import PoolInfo, copy_blocks
+from .transport import PoolInfo, copy_blocks, nan_blocks
 
 logger = init_logger(__name__)
 
@@ -164,6 +164,7 @@ class OffloadWorkerHalf(WorkerConnectorBase):
         self._jobs: list = []            # (request_id, event, slots)
         self.stream = torch.cuda.Stream() if is_cuda else None
         self.failed_saves = 0
+        self.nan_blocked = 0
 
     def start_load_kv(self, meta: Optional[ConnectorMetadata]) -> None:
         if meta is None:
@@ -179,6 +180,13 @@ class OffloadWorkerHalf(WorkerConnectorBase):
             return
         for rid, hashes, blocks in meta.sends:
             todo_slots, todo_blocks = [], []
+            # a block with a NaN / Inf is never stored, nor are the blocks behind it in the hash chain
+            bad = set(nan_blocks(self.gpu, list(blocks))) if envs.B200_KV_SAVE_NAN_CHECK else set()
+            if bad:
+                self.nan_blocked += len(bad)
+                cut = min(i for i, b in enumerate(blocks) if b in bad)
+                hashes, blocks = hashes[:cut], blocks[:cut]
+                logger.warning("request %s: %d KV blocks hold non-finite values, not stored", rid, len(bad))
             for h, b in zip(hashes, blocks):
                 slot = self.store.reserve(h)
                 if slot >= 0:

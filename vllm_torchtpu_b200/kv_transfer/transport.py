@@ -69,8 +69,11 @@ def copy_blocks(src: PoolInfo, dst: PoolInfo, src_ids: list, dst_ids: list) -> N
         s = torch.tensor(src_ids, dtype=torch.int32, device=dev)
         d = torch.tensor(dst_ids, dtype=torch.int32, device=dev)
         ws = cuda.Workspace.get(dev)
+        # both tables stay referenced until the launch is queued: a device copy of a host pool's table
+        # is a temporary, and its block must not be handed to the other table's allocation
+        src_tbl, dst_tbl = src.ptr_table().to(dev), dst.ptr_table().to(dev)
         cuda._check(cuda.lib().b200_kv_copy_blocks(
-            cuda._p(src.ptr_table().to(dev)), cuda._p(dst.ptr_table().to(dev)), cuda._p(s), cuda._p(d),
+            cuda._p(src_tbl), cuda._p(dst_tbl), cuda._p(s), cuda._p(d),
             ctypes.c_int(len(src_ids)), ctypes.c_int(len(src.layers)), ctypes.c_size_t(src.block_bytes),
             ctypes.c_longlong(src.num_blocks), ctypes.c_longlong(dst.num_blocks), cuda._p(ws.status),
             cuda._stream()), "kv_copy_blocks")
@@ -80,6 +83,35 @@ def copy_blocks(src: PoolInfo, dst: PoolInfo, src_ids: list, dst_ids: list) -> N
     si, di = torch.tensor(src_ids), torch.tensor(dst_ids)
     for a, b in zip(src.layers, dst.layers):
         b[di] = a[si].to(b.dtype)
+
+
+def nan_blocks(pool: PoolInfo, block_ids: list) -> list:
+    """Which of ``block_ids`` hold a non-finite bf16 value in any layer.  Saves and transfers of such
+    blocks are refused: a poisoned block would otherwise be served to later requests
+    (reference: src/vllm_torchtpu/distributed/kv_transfer/kv_save_nan_check.py:14-163)."""
+    if not block_ids:
+        return []
+    first = pool.layers[0]
+    if getattr(first, "dtype", None) != torch.bfloat16:
+        return []
+    if first.is_cuda:
+        from ..ops import count_launch, cuda
+        dev = first.device
+        ids = torch.tensor(block_ids, dtype=torch.int32, device=dev)
+        flags = torch.zeros(len(block_ids), dtype=torch.int32, device=dev)
+        cuda._check(cuda.lib().b200_kv_nan_check(
+            cuda._p(pool.ptr_table().to(dev)), cuda._p(ids), ctypes.c_int(len(block_ids)),
+            ctypes.c_int(len(pool.layers)), ctypes.c_size_t(pool.block_bytes), cuda._p(flags), cuda._stream()),
+            "kv_nan_check")
+        count_launch()
+        bad = flags.cpu().tolist()
+    else:
+        idx = torch.tensor(block_ids)
+        bad = [0] * len(block_ids)
+        for t in pool.layers:
+            nf = ~torch.isfinite(t[idx].float()).flatten(1).all(1)
+            bad = [b | int(x) for b, x in zip(bad, nf.tolist())]
+    return [b for b, f in zip(block_ids, bad) if f]
 
 
 class LocalTransport:
@@ -142,16 +174,22 @@ class IpcTransport:
     def register_pool(self, layers: list) -> None:
         from ..ops import cuda
         self.local = PoolInfo(self.engine_id, layers)
-        self._handles = []
+        self._handles, self._offsets = [], []
         for t in layers:
+            # the handle names the allocation that holds the tensor (a caching allocator's segment):
+            # the consumer adds the tensor's offset to the address it gets from opening the handle
+            base, size = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+            cuda._check(cuda.lib().b200_ipc_range(ctypes.c_void_p(t.data_ptr()), ctypes.byref(base),
+                                                  ctypes.byref(size)), "ipc_range")
             h = (ctypes.c_ubyte * 64)()
-            cuda._check(cuda.lib().b200_ipc_get_handle(ctypes.c_void_p(t.data_ptr()), h), "ipc_get_handle")
+            cuda._check(cuda.lib().b200_ipc_get_handle(ctypes.c_void_p(base.value), h), "ipc_get_handle")
             self._handles.append(bytes(h).hex())
+            self._offsets.append(t.data_ptr() - base.value)
 
     def export(self) -> dict:
         p = self.local
         return {"engine_id": self.engine_id, "num_blocks": p.num_blocks, "block_bytes": p.block_bytes,
-                "num_layers": len(p.layers), "kind": "ipc", "handles": self._handles}
+                "num_layers": len(p.layers), "kind": "ipc", "handles": self._handles, "offsets": self._offsets}
 
     def open_remote(self, info: dict) -> None:
         from ..ops import cuda
@@ -160,11 +198,15 @@ class IpcTransport:
         if info["block_bytes"] != self.local.block_bytes or info["num_layers"] != len(self.local.layers):
             raise TransferError("remote pool geometry differs (heterogeneous resharding is not enabled)")
         layers = []
-        for hx in info["handles"]:
-            buf = (ctypes.c_ubyte * 64).from_buffer_copy(bytes.fromhex(hx))
-            p = ctypes.c_void_p()
-            cuda._check(cuda.lib().b200_ipc_open(buf, ctypes.byref(p)), "ipc_open")
-            layers.append(_RawLayer(p.value, info["num_blocks"], info["block_bytes"], self.local.layers[0].device))
+        opened: dict = {}                    # several layers may live in one exported allocation
+        for hx, off in zip(info["handles"], info.get("offsets") or [0] * len(info["handles"])):
+            if hx not in opened:
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(bytes.fromhex(hx))
+                p = ctypes.c_void_p()
+                cuda._check(cuda.lib().b200_ipc_open(buf, ctypes.byref(p)), "ipc_open")
+                opened[hx] = p.value
+            layers.append(_RawLayer(opened[hx] + int(off), info["num_blocks"], info["block_bytes"],
+                                    self.local.layers[0].device))
         pool = PoolInfo.__new__(PoolInfo)
         pool.engine_id, pool.layers = info["engine_id"], layers
         pool.num_blocks, pool.block_bytes, pool._ptr_table = info["num_blocks"], info["block_bytes"], None
