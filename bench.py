@@ -6,6 +6,13 @@ tokens (EOS ignored), at most 64 requests in flight, block size 16, on a
 random-init Llama-3.1-8B-shaped bf16 model with TP = number of GPUs.  W warm-up
 serves are followed by exactly K timed serves between barrier + synchronize.
 
+``--model`` selects the other target configurations (their request shapes become
+the defaults): ``llama-3.1-70b-fp8`` (TP, block-scaled fp8 weights, 2048 / 256,
+c128), ``qwen3-30b-a3b`` and ``deepseek-v3`` (``--parallelism ep-dp``: experts
+sharded over all GPUs, attention data parallel, every rank serves its share of
+the requests in lockstep).  ``--num-layers`` runs a shallower copy of a preset
+(recorded in ``config``; such a line is kernel evidence, not a headline).
+
 Two numbers come out of the same timed serves:
   * ``value``   - output tokens / device time, where device time is the sum of the
     CUDA-event durations of every engine step (forward + sampling kernels), max
@@ -36,6 +43,15 @@ REFERENCE_UNAVAILABLE = (
     "not installable offline) and it contains no CUDA or NCCL code path")
 
 
+# no number is published for these configurations; the closest published ones (TPU v7x-8, other shapes)
+PROXIES = {
+    "llama-3.1-8b": {"note": "closest published proxy: Fin-R1-7B TP8 1024/1024 c64 on TPU v7x-8", "tok_s": 9654},
+    "qwen3-30b-a3b": {"note": "closest published proxy: Qwen3-Coder-30B-A3B TP8+EP 1024/1024 c64 on TPU v7x-8",
+                      "tok_s": 5589},
+    "deepseek-v3": {"note": "closest published proxy: DeepSeek-V2 TP8+EP 1024/1024 c64 on TPU v7x-8", "tok_s": 1619},
+}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -43,17 +59,31 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="llama-3.1-8b")
-    ap.add_argument("--num-requests", type=int, default=512)
-    ap.add_argument("--input-len", type=int, default=1024)
-    ap.add_argument("--output-len", type=int, default=128)
-    ap.add_argument("--concurrency", type=int, default=64)
+    ap.add_argument("--parallelism", default=None, choices=["tp", "ep-dp"],
+                    help="tp: tensor parallel over all GPUs; ep-dp: expert parallel + data-parallel attention")
+    ap.add_argument("--num-layers", type=int, default=0, help="run the first N layers of the preset (0 = all)")
+    ap.add_argument("--num-requests", type=int, default=None)
+    ap.add_argument("--input-len", type=int, default=None)
+    ap.add_argument("--output-len", type=int, default=None)
+    ap.add_argument("--concurrency", type=int, default=None)
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--kv-cache-dtype", default="auto", help="auto (= model dtype) or fp8 (e4m3 cache; not the headline config)")
     ap.add_argument("--sync-scheduling", action="store_true")
     ap.add_argument("--enforce-eager", action="store_true")
     ap.add_argument("--warmup-requests", type=int, default=0,
                     help="requests per warm-up serve (0 = the full workload)")
-    return ap.parse_args()
+    a = ap.parse_args()
+    # request shapes of the target configurations (BASELINE.json configs 2-5)
+    shapes = {"llama-3.1-8b": (512, 1024, 128, 64, "tp"), "llama-3.1-70b-fp8": (512, 2048, 256, 128, "tp"),
+              "llama-3.1-70b": (512, 2048, 256, 128, "tp"), "qwen3-30b-a3b": (1024, 1024, 256, 256, "ep-dp"),
+              "deepseek-v3": (512, 2048, 512, 256, "ep-dp")}
+    n, i, o, c, par = shapes.get(a.model, shapes["llama-3.1-8b"])
+    a.num_requests = a.num_requests or n
+    a.input_len = a.input_len or i
+    a.output_len = a.output_len or o
+    a.concurrency = a.concurrency or c
+    a.parallelism = a.parallelism or par
+    return a
 
 
 class ClockSampler:
@@ -155,16 +185,31 @@ def main():
             return subprocess.call(cmd)
         raise SystemExit(f"WORLD_SIZE={world} does not match --gpus {args.gpus}")
 
-    llm = LLM(args.model, device="cuda", tensor_parallel_size=args.gpus, max_num_seqs=args.concurrency,
+    ep_dp = args.parallelism == "ep-dp" and args.gpus > 1
+    model = args.model
+    if args.num_layers:
+        from vllm_torchtpu_b200.config import model_preset
+        model = model_preset(args.model)
+        if args.num_layers < model.num_layers:
+            model.num_layers = args.num_layers
+            model.name = f"{model.name}[first {args.num_layers} layers]"
+    # data-parallel attention: every replica keeps its share of the requests in flight
+    per_rank_conc = -(-args.concurrency // world) if ep_dp else args.concurrency
+    par = (dict(data_parallel_size=args.gpus, enable_expert_parallel=True) if ep_dp
+           else dict(tensor_parallel_size=args.gpus, enable_expert_parallel=args.parallelism == "ep-dp"))
+    llm = LLM(model, device="cuda", max_num_seqs=per_rank_conc,
               max_num_batched_tokens=args.max_num_batched_tokens, block_size=16,
               kv_cache_dtype=args.kv_cache_dtype,
               max_model_len=args.input_len + args.output_len + 16,
-              async_scheduling=not args.sync_scheduling, enforce_eager=args.enforce_eager)
+              async_scheduling=not args.sync_scheduling, enforce_eager=args.enforce_eager, **par)
     eng = llm.engine
     runner = eng.runner
     mcfg = eng.cfg.model
     sp = SamplingParams(temperature=0.0, max_tokens=args.output_len, ignore_eos=True)
     prompts = make_prompts(args.num_requests, args.input_len, mcfg.vocab_size, seed=0)
+    if ep_dp:
+        prompts = prompts[rank::world]
+    args.concurrency_total, args.concurrency = args.concurrency, per_rank_conc
 
     def barrier():
         if world > 1:
@@ -206,19 +251,31 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     wall_s, device_ms = float(t[0]), float(t[1])
+    if ep_dp:
+        # every replica served its own requests: the job's output is the sum
+        tok = torch.tensor([out_tokens], dtype=torch.int64, device="cuda")
+        dist.all_reduce(tok)
+        out_tokens = int(tok[0])
+        st_t = torch.tensor([status], dtype=torch.int32, device="cuda")
+        dist.all_reduce(st_t, op=dist.ReduceOp.MAX)
+        status = int(st_t[0])
+    proxy = None if args.num_layers else PROXIES.get(mcfg.name)
     if rank == 0:
         value = out_tokens / (device_ms / 1e3)
         e2e = out_tokens / wall_s
         line = {
-            "metric": "output tok/s (serving, 1024 in / 128 out, c64)", "value": round(value, 1),
+            "metric": f"output tok/s (serving, {args.input_len} in / {args.output_len} out, "
+                      f"c{args.concurrency_total})", "value": round(value, 1),
             "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(device_ms / args.steps, 2), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: uniform-random token ids, random-init N(0,0.02) weights",
-            "config": {"model": mcfg.name, "global_batch": args.concurrency, "seq_len": args.input_len,
-                       "parallelism": f"tp{args.gpus}", "num_requests": args.num_requests,
+            "config": {"model": mcfg.name, "global_batch": args.concurrency_total, "seq_len": args.input_len,
+                       "parallelism": (f"ep{args.gpus}+dp{args.gpus}-attention" if ep_dp else f"tp{args.gpus}"),
+                       "num_layers": mcfg.num_layers, "quantization": mcfg.quantization,
+                       "num_requests": args.num_requests,
                        "input_len": args.input_len, "output_len": args.output_len,
-                       "max_concurrency": args.concurrency, "block_size": 16,
+                       "max_concurrency": args.concurrency_total, "block_size": 16,
                        "kv_cache_dtype": args.kv_cache_dtype,
                        "step_definition": "one full serve of the request set",
                        "l2": "inputs larger than L2: every engine step streams the weights "
@@ -238,9 +295,7 @@ def main():
             "p50_ttft_ms": round(statistics.median(ttfts) * 1e3, 2) if ttfts else None,
             "p50_tpot_ms": round(statistics.median(tpots) * 1e3, 3) if tpots else None,
             "clocks": clocks, "device_status": status,
-            "proxy_baseline": {"note": "no published number for this config; closest published proxy is "
-                                       "Fin-R1-7B TP8 1024/1024 c64 on TPU v7x-8", "tok_s": 9654,
-                               "ratio": round(e2e / 9654, 3)},
+            "proxy_baseline": proxy and dict(proxy, ratio=round(e2e / proxy["tok_s"], 3)),
         }
         print(json.dumps(line))
     sys.stdout.flush()

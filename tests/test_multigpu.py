@@ -48,14 +48,70 @@ def _tokens(r):
     raise AssertionError(r.stdout[-3000:] + r.stderr[-3000:])
 
 
-def test_tp2_engine_fused_plane_equals_nccl_plane():
+def _max_lp_gap(a, b):
+    return max(abs(x - y) for ra, rb in zip(a, b) for x, y in zip(ra, rb))
+
+
+def _assert_same_distribution(x, y):
+    """Two planes of the same model: the log-probability of every prompt token (prefill logits of all
+    positions) and of the sampled tokens up to the first differing token (decode logits) agree."""
+    assert x["status"] == 0 and y["status"] == 0
+    assert _max_lp_gap(x["prompt_lp"], y["prompt_lp"]) < 0.08, _max_lp_gap(x["prompt_lp"], y["prompt_lp"])
+    for ta, tb, la, lb in zip(x["tokens"], y["tokens"], x["sample_lp"], y["sample_lp"]):
+        n = next((i for i, (p, q) in enumerate(zip(ta, tb)) if p != q), len(ta))
+        assert n >= 1, (ta, tb)                     # the first sampled token comes from the prefill
+        assert max(abs(p - q) for p, q in zip(la[:n], lb[:n])) < 0.08
+    assert sum(a == b for a, b in zip(x["tokens"], y["tokens"])) >= 3, (x["tokens"], y["tokens"])
+
+
+def test_tp2_engine_fused_plane_matches_nccl_plane_in_log_probabilities():
     _need(2)
-    fused = _tokens(_run("tp_engine_worker.py", 2))
-    nccl = _tokens(_run("tp_engine_worker.py", 2, env={"B200_TP_COMM": "nccl"}))
-    assert fused["status"] == 0
-    # both planes sum bf16 partials in fp32 in rank order, so the tokens agree
-    same = sum(a == b for a, b in zip(fused["tokens"], nccl["tokens"]))
-    assert same >= 3, (fused, nccl)
+    fused = _tokens(_run("tp_engine_worker.py", 2, "--lp"))
+    nccl = _tokens(_run("tp_engine_worker.py", 2, "--lp", env={"B200_TP_COMM": "nccl"}))
+    _assert_same_distribution(fused, nccl)
+
+
+def test_tp2_engine_graph_decode_matches_single_gpu():
+    _need(2)
+    one = _tokens(_run("tp_engine_worker.py", 1))
+    two = _tokens(_run("tp_engine_worker.py", 2))
+    assert one["status"] == 0 and two["status"] == 0
+    assert sum(a == b for a, b in zip(one["tokens"], two["tokens"])) >= 3, (one, two)
+
+
+def test_tp2_persistent_decode_kernel_matches_per_layer_kernels():
+    """The persistent decode kernel with its push plane between two GPUs against the per-layer path."""
+    _need(2)
+    mega = _tokens(_run("tp_engine_worker.py", 2, env={"B200_DECODE_MEGAKERNEL": "1"}))
+    base = _tokens(_run("tp_engine_worker.py", 2))
+    assert mega["persistent_decode"] and not base["persistent_decode"]
+    assert mega["status"] == 0 and base["status"] == 0
+    assert sum(a == b for a, b in zip(mega["tokens"], base["tokens"])) >= 3, (mega, base)
+    assert all(a[:3] == b[:3] for a, b in zip(mega["tokens"], base["tokens"])), (mega, base)
+
+
+def test_pp2_engine_on_gpus_matches_single_gpu():
+    _need(2)
+    one = _tokens(_run("tp_engine_worker.py", 1))
+    pp = _tokens(_run("tp_engine_worker.py", 2, "--pp"))
+    assert pp["status"] == 0
+    assert sum(a == b for a, b in zip(one["tokens"], pp["tokens"])) >= 3, (one, pp)
+
+
+def test_dp2_expert_parallel_lockstep_on_gpus():
+    """Two replicas with their own requests, experts sharded over both GPUs, steps in lockstep."""
+    _need(2)
+    one = _tokens(_run("tp_engine_worker.py", 1, "--moe"))
+    dp = _tokens(_run("tp_engine_worker.py", 2, "--moe", "--dpep"))
+    assert dp["status"] == 0
+    assert sum(a == b for a, b in zip(one["tokens"], dp["tokens"])) >= 3, (one, dp)
+
+
+def test_tp2_server_requests_reach_both_gpus():
+    _need(2)
+    r = _run("serve_sync_worker.py", 2, "cuda")
+    served = _tokens(r)["tokens"]
+    assert len(served) == 3 and all(len(t) == 8 for t in served)
 
 
 @pytest.mark.parametrize("nproc", [2, 4])

@@ -60,6 +60,15 @@ def test_dp2_with_expert_parallel_lockstep_matches_single_process():
     assert _run(2, "dpep", "tiny-moe") == _run(1, "tp", "tiny-moe")
 
 
+def test_dp2_with_expert_parallel_and_async_scheduling_terminates_together():
+    """One step in flight per replica: the replicas still agree on when the group is idle, so nobody is
+    left alone in a collective."""
+    one = _run(1, "tp", "tiny-moe")
+    assert _run(2, "dpep", "tiny-moe", "--async") == one
+    # the benchmark's closed-loop client (requests added while others are in flight, two serves)
+    assert _run(2, "dpep", "tiny-moe", "--async", "--closed-loop") == one
+
+
 def test_tp2_lora_matches_single_process(single):
     """Adapters sharded like the base weights (B rows of column-parallel targets, A columns of row-parallel
     targets with the partial update added before the all-reduce) reproduce the one-process tokens."""

@@ -102,3 +102,18 @@ def test_kv_write_into_paged_cache(slot_dtype):
             want[s // bs, 0, :, s % bs] = k[t]
             want[s // bs, 1, :, s % bs] = v[t]
     assert torch.equal(cache, want)
+
+
+def test_vocab_parallel_argmax_exchange():
+    """Every rank reduces its vocabulary shard to (value, index) pairs; the pairs of all ranks pick the
+    global arg-max (first index on ties).  The shards of a 4-rank layout are emulated on one GPU."""
+    from vllm_torchtpu_b200.ops import cuda_tp
+    R, V, world = 9, 4096, 4
+    g = torch.Generator(device=DEV).manual_seed(4)
+    logits = torch.randn(R, V, device=DEV, generator=g).bfloat16()
+    logits[3, 100] = logits[3, 3000] = 9.0            # a tie across shards
+    shard = V // world
+    vals, idxs = zip(*[cuda_tp.argmax_pair(logits[:, r * shard:(r + 1) * shard]) for r in range(world)])
+    got = cuda_tp.select_best(torch.stack(vals).contiguous(), torch.stack(idxs).contiguous(), shard)
+    want = logits.float().argmax(-1)
+    assert torch.equal(got.long(), want) and int(got[3]) == 100

@@ -57,8 +57,19 @@ def main():
         assert llm.engine.add_lora("ad", 4, 16.0, weights)
         sp = [SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True, lora_name="ad" if i != 1 else None)
               for i in range(len(mine))]
-    outs = llm.generate(mine, sp)
-    toks = [o.outputs[0].token_ids for o in outs]
+    if "--closed-loop" in sys.argv:
+        # the benchmark's client: at most one request in flight per replica, new ones added as others finish,
+        # two serves back to back (the replicas must leave each serve in the same step)
+        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+        import bench
+        toks = None
+        for _ in range(2):
+            done = bench.serve(llm.engine, mine, sp, 1)
+            by_prompt = {tuple(r.prompt_token_ids): r.output_token_ids for r in done}
+            toks = [list(by_prompt[tuple(p)]) for p in mine]
+    else:
+        outs = llm.generate(mine, sp)
+        toks = [o.outputs[0].token_ids for o in outs]
     if mode == "dpep":
         import torch.distributed as dist
         every = [None] * world

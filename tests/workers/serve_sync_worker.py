@@ -17,7 +17,8 @@ def main():
     device = sys.argv[1] if len(sys.argv) > 1 else "cpu"
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    kw = dict(num_gpu_blocks_override=64) if device == "cpu" else dict(num_gpu_blocks_override=256)
+    # the CUDA kernels take bf16; the preset's fp32 is the CPU oracle's dtype
+    kw = dict(num_gpu_blocks_override=64) if device == "cpu" else dict(num_gpu_blocks_override=256, dtype="bfloat16")
     llm = LLM("tiny-llama", device=device, tensor_parallel_size=world, max_num_seqs=8, max_num_batched_tokens=64,
               block_size=16, async_scheduling="--async" in sys.argv, **kw)
     eng = llm.engine

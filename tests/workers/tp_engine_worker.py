@@ -26,16 +26,44 @@ def main():
                           num_kv_heads=8, head_dim=128, intermediate_size=2048, vocab_size=4096,
                           max_model_len=512, dtype=torch.bfloat16, qk_norm=True, num_experts=8,
                           num_experts_per_tok=2, moe_intermediate_size=256)
-    llm = LLM(cfg, device="cuda", tensor_parallel_size=world, max_num_seqs=8, max_num_batched_tokens=256,
-              num_gpu_blocks_override=256, enforce_eager="--eager" in sys.argv, enable_expert_parallel=ep)
+    par = dict(tensor_parallel_size=world)
+    if "--pp" in sys.argv:
+        par = dict(pipeline_parallel_size=world)
+    if "--dpep" in sys.argv:                       # data-parallel attention, experts sharded over the replicas
+        par = dict(data_parallel_size=world)
+        ep = True
+    llm = LLM(cfg, device="cuda", max_num_seqs=8, max_num_batched_tokens=256,
+              num_gpu_blocks_override=256, enforce_eager="--eager" in sys.argv, enable_expert_parallel=ep, **par)
     rng = np.random.RandomState(0)
     prompts = [rng.randint(0, 4096, size=n).tolist() for n in (8, 33, 70, 150)]
-    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    rank = int(os.environ.get("RANK", "0"))
+    mine = prompts
+    if "--dpep" in sys.argv:
+        mine = [p for i, p in enumerate(prompts) if i % world == rank]
+    lp = "--lp" in sys.argv
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True, logprobs=1 if lp else None,
+                        prompt_logprobs=0 if lp else None)
+    outs = llm.generate(mine, sp)
     torch.cuda.synchronize()
     status = cuda.check_status()
-    if int(os.environ.get("RANK", "0")) == 0:
-        print("RESULT " + json.dumps({"tokens": [o.outputs[0].token_ids for o in outs], "status": status}),
-              flush=True)
+    toks = [o.outputs[0].token_ids for o in outs]
+    if "--dpep" in sys.argv and world > 1:
+        import torch.distributed as dist
+        every = [None] * world
+        dist.all_gather_object(every, toks)
+        merged = [None] * len(prompts)
+        for r, part in enumerate(every):
+            for j, t in enumerate(part):
+                merged[r + j * world] = t
+        toks = merged
+    res = {"tokens": toks, "status": status,
+           "persistent_decode": getattr(llm.engine.runner.model, "decode_mega", None) is not None}
+    if lp:
+        # log-probabilities of the sampled tokens (decode steps) and of every prompt token (prefill)
+        res["sample_lp"] = [[e["logprob"] for e in o.outputs[0].logprobs] for o in outs]
+        res["prompt_lp"] = [[e["logprob"] for e in o.prompt_logprobs[1:]] for o in outs]
+    if rank == 0:
+        print("RESULT " + json.dumps(res), flush=True)
     if world > 1:
         import torch.distributed as dist
         from vllm_torchtpu_b200.parallel.state import leave_process

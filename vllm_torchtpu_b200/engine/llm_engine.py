@@ -291,8 +291,12 @@ class LLMEngine:
         if self._sync is not None and self._sync.pending:
             return True
         if self._dp_lockstep:
-            # a rank without requests keeps stepping (dummy batches) while any replica has work
-            return self._dp_group_busy or self.scheduler.has_unfinished() or bool(self._inflight)
+            # Replicas coupled by expert parallelism must call step() the same number of times (every
+            # step holds a host all-reduce and the MoE collectives), so the loop condition is the flag
+            # they agreed on in the last step; a replica without requests keeps stepping (placeholder
+            # batches) while any other has work.  Launches left in flight when the group goes idle hold
+            # no requests; drain() retires them without a collective.
+            return self._dp_group_busy or self.scheduler.has_unfinished()
         return self.scheduler.has_unfinished() or bool(self._inflight)
 
     # ---- stepping ---------------------------------------------------------------
@@ -303,7 +307,8 @@ class LLMEngine:
             from ..parallel.communicator import DeviceCommunicator
             st = get_state()
             t_pad, eager = self.runner.step_shape(out)
-            busy = 1 if (out.scheduled or self.scheduler.has_unfinished()) else 0
+            busy = 1 if (out.scheduled or self.scheduler.has_unfinished()
+                         or any(o.scheduled for o, _ in self._inflight)) else 0
             throttled = hasattr(self.scheduler, "throttle_prefills")
             pending = self.scheduler.pending_prefill_tokens() if throttled else 0
             agreed = DeviceCommunicator(st.dp, None).cpu_all_reduce_max([t_pad, eager, busy, pending])
@@ -413,7 +418,16 @@ class LLMEngine:
             out, res = self._launch()
             return self._retire(out, res)
         finished = []
-        if self.scheduler.has_unfinished() or self._dp_lockstep:
+        if self._dp_lockstep:
+            # one launch (and one agreement) per step on every replica; all but the newest launch are
+            # retired, and a launch without requests right away
+            self._inflight.append(self._launch())
+            while len(self._inflight) > 1:
+                finished += self._retire(*self._inflight.popleft())
+            if self._inflight and not self._inflight[-1][0].scheduled:
+                finished += self._retire(*self._inflight.popleft())
+            return finished
+        if self.scheduler.has_unfinished():
             self._inflight.append(self._launch())
         if len(self._inflight) > 1 or (self._inflight and not self.scheduler.has_unfinished()):
             out, res = self._inflight.popleft()

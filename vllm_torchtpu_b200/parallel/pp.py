@@ -109,6 +109,12 @@ class NcclTransport(Transport):
                 return self.dist.irecv(tensor, src, group=self.group, tag=tag)
         return self.dist.irecv(tensor, src, group=self.group, tag=tag)
 
+    def drain(self) -> None:
+        """Block the calling (helper) thread until the transfers issued so far have left: a NCCL
+        handle's ``wait()`` only orders streams, and the payload is released right after."""
+        if self.stream is not None:
+            self.stream.synchronize()
+
 
 @dataclass
 class _PostedRecv:
@@ -180,11 +186,9 @@ class PPHandoff:
             self._outstanding_cv.notify_all()
 
     def zero_residual(self, rows: int) -> torch.Tensor:
-        z = self._zero_residual.get(rows)
-        if z is None:
-            z = self._zero_residual[rows] = torch.zeros(rows, self.hidden_size, dtype=self.dtype,
-                                                        device=self.device)
-        return z
+        """A fresh zero residual: the fused add + RMSNorm kernels update the residual in place, so a
+        cached tensor would carry one forward's residual stream into the next."""
+        return torch.zeros(rows, self.hidden_size, dtype=self.dtype, device=self.device)
 
     # ---- receiving side --------------------------------------------------------
     def begin_step(self, padded_rows_per_forward: list) -> None:
@@ -281,6 +285,9 @@ class PPHandoff:
                           for i, t in enumerate(payload)]
                     for h in hs:
                         h.wait()
+                    drain = getattr(self.t, "drain", None)
+                    if drain is not None:
+                        drain()
             except BaseException as e:           # noqa: BLE001
                 self._fail(e)
             finally:
