@@ -99,6 +99,28 @@ def main():
             print(f"[rank {rank}] gemm_push {(T, N, K)}: y {e1} residual {e2} sum {e3} tol {tol} "
                   f"status {cuda.check_status()}", flush=True)
 
+    # fp8 push plane: block-scaled e4m3 weights, partial pushed from the epilogue (token tiles 32 / 64 /
+    # 128, cluster split-K and plain), alternating with bf16 push launches on the same control block
+    from vllm_torchtpu_b200.quantization.fp8 import fp8_block_gemm_reference, quantize_weight_block
+    for (T, N, K) in [(1, 512, 256), (16, 1024, 512), (48, 4096, 1792), (64, 4096, 512), (128, 2048, 1024)]:
+        assert ft.can_push(T, N)
+        g = torch.Generator(device=dev).manual_seed(91 * rank + T)
+        x = torch.randn(T, K, device=dev, generator=g).bfloat16()
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+        wq, wsi = quantize_weight_block(w)
+        part = fp8_block_gemm_reference(x, wq, wsi).float()
+        dist.all_reduce(part)
+        for rep in range(3):
+            got = cuda.fp8_block_gemm_push(x, wq, wsi, heap).materialize()
+            cuda.gemm_push(x, w, heap).materialize()
+        torch.cuda.synchronize()
+        err = (got.float() - part).abs().max().item()
+        tol = 3e-2 * part.abs().max().item() + 2e-2
+        if err > tol or cuda.check_status() != 0:
+            ok = False
+            print(f"[rank {rank}] fp8_block_gemm_push {(T, N, K)}: err {err} tol {tol} "
+                  f"status {cuda.check_status()}", flush=True)
+
     # all-gather -> GEMM: row-sharded activations, gathered inside the column-parallel GEMM
     for (T_loc, N, K) in [(32, 512, 256), (64, 1536, 4096), (256, 1024, 512), (1024, 3584, 4096)]:
         g = torch.Generator(device=dev).manual_seed(31 * rank + T_loc)
@@ -161,6 +183,18 @@ def main():
             if rank == 0:
                 print(f"TIMING T={T} N={N} K={K}: push gemm + reduce/add/norm {t_push:.1f} us "
                       f"(plain add+norm alone {t_norm:.1f} us)", flush=True)
+            if T <= 128:
+                wq, wsi = quantize_weight_block(w)
+
+                def plain_fp8():
+                    y = cuda.fp8_block_gemm(x, wq, wsi)
+                    dist.all_reduce(y)
+                    return cuda.fused_add_rms_norm(y, res, nw, 1e-5)
+                t_f8 = timed(lambda: cuda.fp8_block_gemm_push(x, wq, wsi, heap).add_rms_norm(res, nw, 1e-5))
+                t_f8_plain = timed(plain_fp8)
+                if rank == 0:
+                    print(f"TIMING fp8 T={T} N={N} K={K}: push gemm + reduce/add/norm {t_f8:.1f} us, "
+                          f"fp8 gemm + nccl + add/norm {t_f8_plain:.1f} us", flush=True)
         t_fused = timed(lambda: cuda.gemm_all_reduce(x, w, heap))
         t_nccl = timed(plain)
         t_gemm = timed(lambda: cuda.gemm(x, w))

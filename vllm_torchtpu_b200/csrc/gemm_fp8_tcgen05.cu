@@ -59,7 +59,23 @@ struct Params {
   int cluster_splitk;
   const int* group_off;             // grouped: int[num_groups + 1]
   int num_groups, w_rows_per_group, ws_rows_per_group;
+  // ---- tensor-parallel push plane (world > 1): the bf16 partial [T, N] of this rank goes into the
+  // receive slab every rank keeps for it, one flag per (source rank, output tile); the consumer
+  // (b200_reduce_pushed_rms_norm) sums the slabs.  Same protocol, flags and epoch word as the bf16
+  // GEMM's push mode, so launches of the two kernels may alternate on one control block.
+  int world, rank, max_tiles;
+  uint8_t* peer[8];
+  unsigned long long part_off, part_src_stride, tile_flag_off;
+  int* epoch_ptr;
+  int* cta_done;
 };
+
+// index of output tile (n_tile, t_tile) in the raster the consumer uses (groups of 16 weight tiles)
+__device__ __forceinline__ int raster_tile(int n_tile, int t_tile, int n_tiles, int t_tiles) {
+  const int g = n_tile / 16, first_n = g * 16;
+  const int gsize = min(16, n_tiles - first_n);
+  return g * 16 * t_tiles + t_tile * gsize + (n_tile - first_n);
+}
 
 struct Work {
   int w_row, ws_row, t_row, t_valid, n0, kb0, kb1;
@@ -136,6 +152,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   }
   pdl_launch_dependents();
   pdl_wait();
+  // bumped by the last CTA of a push launch to exit: read by every thread before any CTA can do so
+  const int epoch = p.world > 1 ? (*reinterpret_cast<volatile int*>(p.epoch_ptr) + 1) : 0;
+  const int ndst = p.world > 1 ? p.world : 1;
   if (p.group_off != nullptr) {
     for (int e = threadIdx.x; e < p.num_groups; e += blockDim.x)
       s_prefix[e + 1] = (p.group_off[e + 1] - p.group_off[e] + BN - 1) / BN;
@@ -253,12 +272,31 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         float* part = reinterpret_cast<float*>(smem);      // ring is idle: this CTA has one work item
 #pragma unroll
         for (int c = 0; c < BN; ++c) part[c * BM + row] = acc[c];
-      } else if (n < p.N) {
-        const float bias = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;
-        __nv_bfloat16* yp = p.Y + (size_t)k.t_row * p.ldy + n;
+      } else {
+        if (n < p.N) {
+          const float bias = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;
+          for (int d = 0; d < ndst; ++d) {
+            __nv_bfloat16* yp =
+                p.world > 1 ? reinterpret_cast<__nv_bfloat16*>(p.peer[d] + p.part_off + (size_t)p.rank * p.part_src_stride) +
+                                  (size_t)k.t_row * p.N + n
+                            : p.Y + (size_t)k.t_row * p.ldy + n;
+            const size_t ld = p.world > 1 ? (size_t)p.N : (size_t)p.ldy;
 #pragma unroll
-        for (int c = 0; c < BN; ++c)
-          if (c < k.t_valid) yp[(size_t)c * p.ldy] = __float2bfloat16(acc[c] + bias);
+            for (int c = 0; c < BN; ++c)
+              if (c < k.t_valid) yp[(size_t)c * ld] = __float2bfloat16(acc[c] + bias);
+          }
+        }
+        if (p.world > 1) {
+          // the tile has been pushed: release its flag at every rank
+          __threadfence_system();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int t = (int)threadIdx.x - 64;
+          if (t < p.world) {
+            const int tile = raster_tile(k.n0 / BM, k.t_row / BN, p.n_tiles, p.t_tiles);
+            st_release_sys(reinterpret_cast<int*>(p.peer[t] + p.tile_flag_off) + (size_t)p.rank * p.max_tiles + tile,
+                           epoch);
+          }
+        }
       }
     }
   }
@@ -290,15 +328,30 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         for (int r2 = 0; r2 < 8; ++r2)
           if (r2 < S) { a.x += v[r2].x; a.y += v[r2].y; a.z += v[r2].z; a.w += v[r2].w; }
         const float vals[4] = {a.x, a.y, a.z, a.w};
-        __nv_bfloat16* yp = p.Y + (size_t)(k.t_row + c) * p.ldy + n4;
+        for (int d = 0; d < ndst; ++d) {
+          __nv_bfloat16* yp =
+              p.world > 1 ? reinterpret_cast<__nv_bfloat16*>(p.peer[d] + p.part_off + (size_t)p.rank * p.part_src_stride) +
+                                (size_t)(k.t_row + c) * p.N + n4
+                          : p.Y + (size_t)(k.t_row + c) * p.ldy + n4;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+          for (int j = 0; j < 4; ++j)
+            if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+        }
       }
+      if (p.world > 1) __threadfence_system();
     }
     __syncwarp();
     cluster_arrive_release();
     cluster_wait_acquire();
+    if (p.world > 1 && cluster_ctarank() == 0 && warp == 2 && (int)blockIdx.x < total_work && !*abort_flag) {
+      // every CTA of the cluster has stored and fenced its columns: release the tile's flag
+      const Work k = get_work<BN>(blockIdx.x, p, s_prefix);
+      if (lane < p.world) {
+        const int tile = raster_tile(k.n0 / BM, k.t_row / BN, p.n_tiles, p.t_tiles);
+        st_release_sys(reinterpret_cast<int*>(p.peer[lane] + p.tile_flag_off) + (size_t)p.rank * p.max_tiles + tile,
+                       epoch);
+      }
+    }
   }
 
   tc_fence_before();
@@ -306,6 +359,15 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+  if (p.world > 1 && threadIdx.x == 64) {
+    __threadfence();
+    const int arrived = atomicAdd(p.cta_done, 1) + 1;
+    if (arrived == (int)gridDim.x) {
+      *p.cta_done = 0;
+      *p.epoch_ptr = epoch;          // every CTA of this launch has read the old value by now
+      __threadfence();
+    }
   }
 }
 
@@ -484,6 +546,74 @@ extern "C" int b200_gemm_fp8_block(const void* Xq, const float* xs, const void* 
     p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
   }
   p.cluster_splitk = p.splits > 1 ? 1 : 0;
+  CUtensorMap tmW, tmX;
+  int rc = fp8_common(p, Xq, Wq, N, T, bn, K, &tmW, &tmX);
+  if (rc) return rc;
+  const int total = tiles * p.splits;
+  const int grid = p.cluster_splitk ? total : (total < num_sms ? total : num_sms);
+  switch (bn) {
+    case 32: return f8::launch<32>(tmW, tmX, p, grid, stream);
+    case 64: return f8::launch<64>(tmW, tmX, p, grid, stream);
+    default: return f8::launch<128>(tmW, tmX, p, grid, stream);
+  }
+}
+
+// Row-parallel block-scaled fp8 GEMM whose bf16 partial is pushed to every rank of the tensor-parallel
+// group (decode-sized outputs): the partial lands in the receive slab at heap offset part_off that each
+// rank keeps per source rank, flags int[world][max_tiles] at tile_flag_off are raised with this
+// launch's epoch, and b200_reduce_pushed_rms_norm on every rank sums what it received.  ctrl is the
+// control block the bf16 push GEMM uses (epoch, CTA counter).
+extern "C" int b200_gemm_fp8_block_push(const void* Xq, const float* xs, const void* Wq, const float* ws, int T, int N,
+                                        int K, void* const* peers, int rank, int world,
+                                        unsigned long long part_off, unsigned long long part_bytes,
+                                        unsigned long long tile_flag_off, int max_tiles, int* ctrl, int* status,
+                                        int num_sms, cudaStream_t stream) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 2 || world > 8 || N % 8) {
+    b200_set_last_error("gemm_fp8_block_push: 2 <= world <= 8 and N % 8 == 0 required", __FILE__, __LINE__);
+    return -3;
+  }
+  const int bn = T <= 32 ? 32 : (T <= 64 ? 64 : 128);
+  f8::Params p;
+  memset(&p, 0, sizeof(p));
+  p.w_scale = ws;
+  p.x_scale = xs;
+  p.status = status;
+  p.T = T; p.N = N; p.K = K; p.ldy = N;
+  p.n_tiles = (N + f8::BM - 1) / f8::BM;
+  p.t_tiles = (T + bn - 1) / bn;
+  p.kb_total = (K + f8::BKB - 1) / f8::BKB;
+  p.ws_ld = p.kb_total;
+  p.xs_ld = p.kb_total;
+  const int tiles = p.n_tiles * p.t_tiles;
+  if (tiles > max_tiles) {
+    b200_set_last_error("gemm_fp8_block_push: more tiles than flag slots", __FILE__, __LINE__);
+    return -4;
+  }
+  int splits = 1;
+  if (tiles * 2 <= num_sms) {
+    splits = num_sms / tiles;
+    const int by_k = p.kb_total / 4 > 0 ? p.kb_total / 4 : 1;
+    if (splits > by_k) splits = by_k;
+    if (splits > 1) splits = f8::fit_splits(splits, tiles, bn);
+  }
+  p.splits = splits;
+  p.kb_per_split = (p.kb_total + splits - 1) / splits;
+  while (p.splits > 1 && (p.splits - 1) * p.kb_per_split >= p.kb_total) {
+    --p.splits;
+    p.kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+  }
+  p.cluster_splitk = p.splits > 1 ? 1 : 0;
+  p.world = world; p.rank = rank; p.max_tiles = max_tiles;
+  for (int i = 0; i < 8; ++i) p.peer[i] = i < world ? (uint8_t*)peers[i] : nullptr;
+  p.part_off = part_off;
+  p.part_src_stride = ((unsigned long long)T * N * 2ull + 255ull) & ~255ull;
+  if (p.part_src_stride * world > part_bytes) {
+    b200_set_last_error("gemm_fp8_block_push: receive region too small for this shape", __FILE__, __LINE__);
+    return -5;
+  }
+  p.tile_flag_off = tile_flag_off;
+  p.epoch_ptr = ctrl; p.cta_done = ctrl + 1;
   CUtensorMap tmW, tmX;
   int rc = fp8_common(p, Xq, Wq, N, T, bn, K, &tmW, &tmX);
   if (rc) return rc;

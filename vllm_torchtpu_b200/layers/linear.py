@@ -140,13 +140,14 @@ class RowParallelLinear(LinearBase):
                 y = wiring.apply(self, x, self.method.apply(self, x, None))
                 y = comm.all_reduce(y)
                 return y + self.bias if self.bias is not None else y
-        if (x.is_cuda and comm.heap is not None and comm.heap.fused_tp is not None
-                and self.method.supports_fused_reduce):
-            ft = comm.heap.fused_tp
-            if (self.defer_reduce and self.bias is None and not self.lora_targets
-                    and hasattr(self.method, "apply_push")
-                    and ft.can_push(x.numel() // x.shape[-1], self.out_features)):
+        fused = x.is_cuda and comm.heap is not None and comm.heap.fused_tp is not None
+        if (fused and self.defer_reduce and self.bias is None and not self.lora_targets
+                and hasattr(self.method, "apply_push")):
+            ft, T = comm.heap.fused_tp, x.numel() // x.shape[-1]
+            can = getattr(self.method, "can_push", None)
+            if can(ft, T, self.out_features) if can is not None else ft.can_push(T, self.out_features):
                 return self.method.apply_push(self, x, comm)
+        if fused and self.method.supports_fused_reduce:
             y = self.method.apply_fused_all_reduce(self, x, comm)
         else:
             y = comm.all_reduce(self.method.apply(self, x, None))

@@ -1,7 +1,7 @@
 """Bindings of the block-scaled fp8 tcgen05 GEMM family."""
 from __future__ import annotations
 
-from ctypes import c_int, c_void_p
+from ctypes import c_int, c_ulonglong, c_void_p
 
 import torch
 
@@ -43,6 +43,27 @@ def fp8_block_gemm(x, wq, w_scale_inv, bias=None, block=(128, 128), out=None):
         c_int(K), c_int(y.stride(0)), _c._p(ws.status), c_int(_c._sms), _c._stream()), "gemm_fp8_block")
     count_launch()
     return y.reshape(*lead, N)
+
+
+def fp8_block_gemm_push(x, wq, w_scale_inv, heap):
+    """Row-parallel block-scaled fp8 ``x @ wq.T`` whose bf16 partial is pushed to every rank of ``heap``
+    from the GEMM epilogue; returns the :class:`PendingReduce` the next add + RMSNorm (or
+    ``materialize``) completes.  For at most 128 tokens within ``FusedTP.can_push``."""
+    st = heap.fused_tp
+    x2 = x.reshape(-1, x.shape[-1])
+    T, K = x2.shape
+    N = wq.shape[0]
+    xq, xs = quant_act_1x128(x2)
+    part = st.parts[st.flip]
+    st.flip ^= 1
+    ws = _c.Workspace.get(x.device)
+    _c._check(_c.lib().b200_gemm_fp8_block_push(
+        _c._p(xq), _c._p(xs), _c._p(wq), _c._p(w_scale_inv), c_int(T), c_int(N), c_int(K),
+        heap.peers_c, c_int(heap.rank), c_int(heap.world), c_ulonglong(part.offset),
+        c_ulonglong(st.part_bytes), c_ulonglong(st.tile_flags.offset), c_int(_c.FusedTP.MAX_TILES),
+        _c._p(st.ctrl), _c._p(ws.status), c_int(_c._sms), _c._stream()), "gemm_fp8_block_push")
+    count_launch()
+    return _c.PendingReduce(heap, part, T, N, x.shape[:-1])
 
 
 def fp8_rowwise_gemm(xq, xs, wq, w_scale, out_dtype):

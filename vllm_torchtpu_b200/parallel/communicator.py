@@ -43,7 +43,9 @@ class DeviceCommunicator:
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.size == 1:
             return x
-        if self.heap is not None and self.plane != "nccl" and x.is_cuda:
+        if (self.heap is not None and self.plane != "nccl" and x.is_cuda and x.dtype == torch.bfloat16
+                and x.numel() * 2 <= self.heap.ar_stage_bytes):
+            # small tensors: one kernel over the peer heap; larger ones exceed its staging buffer
             from ..ops import cuda_ops
             return cuda_ops().p2p_all_reduce(x, self.heap)
         dist.all_reduce(x, group=self.group.device_group)

@@ -132,6 +132,15 @@ class Fp8BlockLinearMethod(LinearMethodBase):
         y = fp8_block_gemm_reference(x, layer.weight, layer.weight_scale_inv, self.block)
         return y if bias is None else (y.float() + bias.float()).to(y.dtype)
 
+    def can_push(self, fused_tp, T: int, N: int) -> bool:
+        # the consumer derives the token tile from T; the fp8 kernel's largest token tile is 128
+        return T <= 128 and fused_tp.can_push(T, N)
+
+    def apply_push(self, layer, x, comm):
+        """Row-parallel product whose partial goes to every rank from the GEMM epilogue (decode-sized
+        outputs); the add + RMSNorm that follows sums what arrived."""
+        return ops.cuda_ops().fp8_block_gemm_push(x, layer.weight, layer.weight_scale_inv, comm.heap)
+
     def weight_bytes(self, layer) -> int:
         return layer.weight.numel() + layer.weight_scale_inv.numel() * 4
 
