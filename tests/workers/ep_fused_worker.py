@@ -54,6 +54,37 @@ def main():
         if err > tol or status != 0:
             ok = False
             print(f"[rank {rank}] moe_experts_ep T={T}: err {err} tol {tol} status {status}", flush=True)
+    # fp8 experts on the same plane (quantised rows, grouped fp8 GEMMs, routed epilogue) against the
+    # single-rank fp8 pipeline over all experts
+    from vllm_torchtpu_b200.ops.cuda_fp8 import moe_experts_fp8
+    from vllm_torchtpu_b200.quantization.fp8 import quantize_weight_block
+    q13, s13, q2, s2 = [], [], [], []
+    for e in range(E):
+        a, b = quantize_weight_block(w13[e])
+        c, d = quantize_weight_block(w2[e])
+        q13.append(a); s13.append(b); q2.append(c); s2.append(d)
+    q13, s13, q2, s2 = torch.stack(q13), torch.stack(s13), torch.stack(q2), torch.stack(s2)
+    lq13, ls13 = q13[lo:lo + e_local].contiguous(), s13[lo:lo + e_local].contiguous()
+    lq2, ls2 = q2[lo:lo + e_local].contiguous(), s2[lo:lo + e_local].contiguous()
+    for it, T in enumerate([1, 7 + rank, 64, 200 - 13 * rank, T_max]):
+        gr = torch.Generator(device=dev).manual_seed(500 * it + rank)
+        x = torch.randn(T, H, device=dev, generator=gr).bfloat16()
+        logits = torch.randn(T, E, device=dev, generator=gr)
+        topk_w, topk_ids = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+        topk_ids = topk_ids.to(torch.int32).contiguous()
+        topk_w = topk_w.float().contiguous()
+        want = moe_experts_fp8(x, q13, s13, q2, s2, topk_ids, topk_w, 0)
+        for rep in range(2):
+            torch.cuda.synchronize()
+            dist.barrier()
+            got = cuda.moe_experts_ep_fp8(x, lq13, ls13, lq2, ls2, topk_ids, topk_w, heap, E)
+        torch.cuda.synchronize()
+        err = (got.float() - want.float()).abs().max().item()
+        tol = 3e-2 * want.float().abs().max().item() + 2e-2
+        status = cuda.check_status()
+        if err > tol or status != 0:
+            ok = False
+            print(f"[rank {rank}] moe_experts_ep_fp8 T={T}: err {err} tol {tol} status {status}", flush=True)
     t = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     if rank == 0:

@@ -68,6 +68,11 @@ struct Params {
   unsigned long long part_off, part_src_stride, tile_flag_off;
   int* epoch_ptr;
   int* cta_done;
+  // ---- routed rows (expert-parallel combine inside a grouped launch): output row r goes to slot
+  // row_route[r].y of rank row_route[r].x at heap offset route_ret_off (row length N); the last CTA
+  // to exit raises int[world] flags at ret_flag_off of every rank with the epoch in *epoch_ptr
+  const int2* row_route;
+  unsigned long long route_ret_off, ret_flag_off;
 };
 
 // index of output tile (n_tile, t_tile) in the raster the consumer uses (groups of 16 weight tiles)
@@ -153,8 +158,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   pdl_launch_dependents();
   pdl_wait();
   // bumped by the last CTA of a push launch to exit: read by every thread before any CTA can do so
-  const int epoch = p.world > 1 ? (*reinterpret_cast<volatile int*>(p.epoch_ptr) + 1) : 0;
-  const int ndst = p.world > 1 ? p.world : 1;
+  const bool push = p.world > 1 && p.row_route == nullptr;
+  const int epoch = push ? (*reinterpret_cast<volatile int*>(p.epoch_ptr) + 1) : 0;
+  const int ndst = push ? p.world : 1;
   if (p.group_off != nullptr) {
     for (int e = threadIdx.x; e < p.num_groups; e += blockDim.x)
       s_prefix[e + 1] = (p.group_off[e + 1] - p.group_off[e] + BN - 1) / BN;
@@ -272,6 +278,18 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         float* part = reinterpret_cast<float*>(smem);      // ring is idle: this CTA has one work item
 #pragma unroll
         for (int c = 0; c < BN; ++c) part[c * BM + row] = acc[c];
+      } else if (p.row_route != nullptr) {
+        if (n < p.N) {
+#pragma unroll
+          for (int c = 0; c < BN; ++c) {
+            if (c < k.t_valid) {
+              const int2 rt = __ldg(p.row_route + k.t_row + c);
+              reinterpret_cast<__nv_bfloat16*>(p.peer[rt.x] + p.route_ret_off)[(size_t)rt.y * p.N + n] =
+                  __float2bfloat16(acc[c]);
+            }
+          }
+        }
+        __threadfence_system();
       } else {
         if (n < p.N) {
           const float bias = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;
@@ -286,7 +304,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
               if (c < k.t_valid) yp[(size_t)c * ld] = __float2bfloat16(acc[c] + bias);
           }
         }
-        if (p.world > 1) {
+        if (p.world > 1 && p.row_route == nullptr) {
           // the tile has been pushed: release its flag at every rank
           __threadfence_system();
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -365,7 +383,15 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     const int arrived = atomicAdd(p.cta_done, 1) + 1;
     if (arrived == (int)gridDim.x) {
       *p.cta_done = 0;
-      *p.epoch_ptr = epoch;          // every CTA of this launch has read the old value by now
+      if (p.row_route != nullptr) {
+        // every CTA fenced its routed stores before it arrived: tell all ranks their rows are back
+        __threadfence_system();
+        const int ep_epoch = *reinterpret_cast<volatile int*>(p.epoch_ptr);
+        for (int r = 0; r < p.world; ++r)
+          st_release_sys(reinterpret_cast<int*>(p.peer[r] + p.ret_flag_off) + p.rank, ep_epoch);
+      } else {
+        *p.epoch_ptr = epoch;        // every CTA of this launch has read the old value by now
+      }
       __threadfence();
     }
   }
@@ -392,6 +418,47 @@ __global__ void quant_act_1x128_kernel(const __nv_bfloat16* __restrict__ x, __nv
   for (int j = 0; j < 4; ++j)
     if (c0 + j < K) xq[(size_t)t * K + c0 + j] = __nv_fp8_e4m3(fminf(fmaxf(v[j] * inv, -448.f), 448.f));
   if (lane == 0) xs[(size_t)t * groups + g] = scale;
+}
+
+// Same quantisation over the first *rows_ptr rows (all T when rows_ptr is null) with a grid that does not
+// depend on the row count, optionally fused behind SiLU(gate) * up: with SWIGLU the input row holds
+// [gate(K) | up(K)] (row stride ldx) and the product, rounded to bf16 as the stand-alone activation
+// kernel would, is what gets quantised.  One warp per (row, 128-column group), grid-stride.
+template <bool SWIGLU>
+__global__ void quant_rows_1x128_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_e4m3* __restrict__ xq,
+                                        float* __restrict__ xs, int T, int K, int ldx, int groups,
+                                        const int* __restrict__ rows_ptr) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int rows = rows_ptr != nullptr ? min(T, *rows_ptr) : T;
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)rows * groups;
+  for (long long gw = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); gw < total;
+       gw += (long long)gridDim.x * warps_per_block) {
+    const int t = (int)(gw / groups), g = (int)(gw % groups);
+    const int c0 = g * 128 + lane * 4;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (c0 + j >= K) { v[j] = 0.f; continue; }
+      const float a = __bfloat162float(x[(size_t)t * ldx + c0 + j]);
+      if (SWIGLU) {
+        const float u = __bfloat162float(x[(size_t)t * ldx + K + c0 + j]);
+        v[j] = __bfloat162float(__float2bfloat16(a / (1.f + __expf(-a)) * u));
+      } else {
+        v[j] = a;
+      }
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    amax = warp_max(amax);
+    const float scale = fmaxf(amax, 1e-12f) / 448.f;
+    const float inv = 1.f / scale;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (c0 + j < K) xq[(size_t)t * K + c0 + j] = __nv_fp8_e4m3(fminf(fmaxf(v[j] * inv, -448.f), 448.f));
+    if (lane == 0) xs[(size_t)t * groups + g] = scale;
+  }
 }
 
 // x [T, K] bf16 -> xq [T, K] int8 and xs [T] fp32 (amax / 127): one CTA per row
@@ -496,6 +563,25 @@ extern "C" int b200_quant_act_1x128(const void* x, void* xq, float* xs, int T, i
   const int blocks = (int)((warps + 7) / 8);
   f8::quant_act_1x128_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_fp8_e4m3*)xq, xs, T, K,
                                                          ldx, groups);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// Quantisation of at most T rows, of which the first *rows_ptr are live (device word; null = all T), with
+// SiLU(gate) * up in front when swiglu != 0 (x then has 2K columns per row).
+extern "C" int b200_quant_rows_1x128(const void* x, void* xq, float* xs, int T, int K, int ldx, const int* rows_ptr,
+                                     int swiglu, int num_sms, cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int groups = (K + 127) / 128;
+  const long long warps = (long long)T * groups;
+  long long blocks = (warps + 7) / 8;
+  if (blocks > (long long)num_sms * 8) blocks = (long long)num_sms * 8;
+  if (swiglu)
+    f8::quant_rows_1x128_kernel<true><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_fp8_e4m3*)xq,
+                                                                       xs, T, K, ldx, groups, rows_ptr);
+  else
+    f8::quant_rows_1x128_kernel<false><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_fp8_e4m3*)xq,
+                                                                        xs, T, K, ldx, groups, rows_ptr);
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
@@ -655,6 +741,54 @@ extern "C" int b200_grouped_gemm_fp8_block(const void* Xq, const float* xs, cons
   p.num_groups = num_groups;
   p.w_rows_per_group = N;
   p.ws_rows_per_group = N / f8::BM;
+  CUtensorMap tmW, tmX;
+  int rc = fp8_common(p, Xq, Wq, num_groups * N, R, bn, K, &tmW, &tmX);
+  if (rc) return rc;
+  switch (bn) {
+    case 32: return f8::launch<32>(tmW, tmX, p, num_sms, stream);
+    case 64: return f8::launch<64>(tmW, tmX, p, num_sms, stream);
+    default: return f8::launch<128>(tmW, tmX, p, num_sms, stream);
+  }
+}
+
+// Grouped block-scaled fp8 GEMM whose output rows are scattered to the ranks that sent the tokens
+// (expert-parallel combine inside the epilogue): same contract as b200_grouped_gemm_bf16_routed.
+extern "C" int b200_grouped_gemm_fp8_block_routed(const void* Xq, const float* xs, const void* Wq, const float* ws,
+                                                  const int* group_off, int num_groups, int R, int N, int K,
+                                                  int avg_rows_hint, void* const* peers, int rank, int world,
+                                                  const void* route, unsigned long long ret_off,
+                                                  unsigned long long ret_flag_off, int* ctrl, int* status,
+                                                  int num_sms, cudaStream_t stream) {
+  if (R <= 0 || N <= 0 || K <= 0 || num_groups <= 0) return 0;
+  if (N % f8::BM || num_groups > f8::MAX_GROUPS || world < 2 || world > 8) {
+    b200_set_last_error("grouped_gemm_fp8_routed: N % 128 == 0, <= 1024 groups, 2 <= world <= 8 required",
+                        __FILE__, __LINE__);
+    return -3;
+  }
+  const int bn = avg_rows_hint <= 32 ? 32 : (avg_rows_hint <= 64 ? 64 : 128);
+  f8::Params p;
+  memset(&p, 0, sizeof(p));
+  p.w_scale = ws;
+  p.x_scale = xs;
+  p.status = status;
+  p.T = R; p.N = N; p.K = K; p.ldy = N;
+  p.n_tiles = N / f8::BM;
+  p.t_tiles = (R + bn - 1) / bn;
+  p.kb_total = (K + f8::BKB - 1) / f8::BKB;
+  p.ws_ld = p.kb_total;
+  p.xs_ld = p.kb_total;
+  p.splits = 1;
+  p.kb_per_split = p.kb_total;
+  p.group_off = group_off;
+  p.num_groups = num_groups;
+  p.w_rows_per_group = N;
+  p.ws_rows_per_group = N / f8::BM;
+  p.world = world; p.rank = rank;
+  for (int i = 0; i < 8; ++i) p.peer[i] = i < world ? (uint8_t*)peers[i] : nullptr;
+  p.row_route = reinterpret_cast<const int2*>(route);
+  p.route_ret_off = ret_off;
+  p.ret_flag_off = ret_flag_off;
+  p.epoch_ptr = ctrl; p.cta_done = ctrl + 1;
   CUtensorMap tmW, tmX;
   int rc = fp8_common(p, Xq, Wq, num_groups * N, R, bn, K, &tmW, &tmX);
   if (rc) return rc;

@@ -264,6 +264,65 @@ def bench_decode_model(reqs, ctx, layers=8, iters=10, H=4096, I=14336, Hq=32, Hk
     return out
 
 
+def bench_fp8_gemm(T, N, K, iters=20) -> list:
+    """Block-scaled e4m3 GEMM (128x128 weight scales, 1x128 activation scales) of this package, with and
+    without the activation quantisation kernel, next to ``torch._scaled_mm`` on the same e4m3 operands
+    (library kernel; per-tensor scales, and row-wise scales where the library accepts them) and to the
+    bf16 tcgen05 GEMM of the same shape.  Roofline: fp8 weight + activation bytes and bf16 output bytes
+    over the measured copy bandwidth, FLOPs over twice the measured bf16 GEMM rate."""
+    from . import cuda
+    from ..quantization.fp8 import fp8_block_gemm_reference, quantize_weight_block
+    pk, tag = peaks()
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    wq, wsi = quantize_weight_block(w)
+    xq, xs = cuda.quant_act_1x128(x)
+    y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    ws = cuda.Workspace.get(x.device)
+    from ctypes import c_int
+
+    def gemm_only():
+        cuda._check(cuda.lib().b200_gemm_fp8_block(
+            cuda._p(xq), cuda._p(xs), cuda._p(wq), cuda._p(wsi), cuda._p(y), None, c_int(T), c_int(N), c_int(K),
+            c_int(N), cuda._p(ws.status), c_int(cuda._sms), cuda._stream()), "gemm_fp8_block")
+    flops = 2.0 * T * N * K
+    byts = float(T * K + N * K + 2 * T * N)
+    t_roof = max(flops / (2 * pk["bf16_tflops"] * 1e12), byts / (pk["hbm_gbs"] * 1e9)) * 1e3
+    rows = []
+
+    def row(impl, ms, err=None, note=None):
+        r = {"op": "fp8-gemm", "impl": impl, "T": T, "N": N, "K": K, "ms": round(ms, 4),
+             "tflops": round(flops / ms / 1e9, 1), "gbs": round(byts / ms / 1e6, 1),
+             "roofline_ms": round(t_roof, 4), "frac_of_roofline": round(t_roof / ms, 3), "peaks": tag,
+             "rel_err": err, "status": cuda.check_status()}
+        if note:
+            r["note"] = note
+        rows.append(r)
+    want = fp8_block_gemm_reference(x, wq, wsi).float() if T * N <= (1 << 24) else None
+    ms = time_fn(gemm_only, iters)
+    err = float((y.float() - want).abs().max() / want.abs().max()) if want is not None else None
+    row("tcgen05 block-scaled (operands quantised)", ms, err)
+    ms = time_fn(lambda: cuda.fp8_block_gemm(x, wq, wsi, out=y), iters)
+    row("tcgen05 block-scaled + activation quant kernel", ms)
+    one = torch.ones((), device="cuda", dtype=torch.float32)
+    wt = wq.t()                                   # column-major second operand, as the library wants
+    try:
+        ms = time_fn(lambda: torch._scaled_mm(xq, wt, scale_a=one, scale_b=one, out_dtype=torch.bfloat16), iters)
+        row("torch._scaled_mm per-tensor scales", ms, note="library kernel; coarser scaling than the block kernel")
+    except Exception as e:                        # noqa: BLE001 - recorded in the output
+        rows.append({"op": "fp8-gemm", "impl": "torch._scaled_mm per-tensor scales", "unavailable": str(e)[:200]})
+    try:
+        sa = torch.ones(T, 1, device="cuda", dtype=torch.float32)
+        sb = torch.ones(1, N, device="cuda", dtype=torch.float32)
+        ms = time_fn(lambda: torch._scaled_mm(xq, wt, scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16), iters)
+        row("torch._scaled_mm row-wise scales", ms, note="library kernel")
+    except Exception as e:                        # noqa: BLE001
+        rows.append({"op": "fp8-gemm", "impl": "torch._scaled_mm row-wise scales", "unavailable": str(e)[:200]})
+    ms = time_fn(lambda: cuda.gemm(x, w, out=y), iters)
+    row("tcgen05 bf16 (same shape)", ms, note="bf16 operands: twice the weight bytes")
+    return rows
+
+
 def bench_gemm_swiglu(T, I, K, iters=20, impl="tcgen05") -> dict:
     """silu(x Wg^T) * (x Wu^T) with W = [2I, K]; 'cublas' is torch.matmul followed by an eager activation."""
     from . import cuda
@@ -335,7 +394,7 @@ LLAMA8B_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm-swiglu", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill",
+    ap.add_argument("what", choices=["gemm", "fp8-gemm", "gemm-swiglu", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill",
                                      "decode-layer", "decode-model", "all"])
     ap.add_argument("--T", type=int, default=64)
     ap.add_argument("--N", type=int, default=4096)
@@ -360,6 +419,9 @@ def main():
                     continue
                 for impl in ("tcgen05", "cublas"):
                     print(json.dumps(bench_gemm(T, N, K, max(5, a.iters // 2), impl, check=(T <= 1024))))
+    if a.what == "fp8-gemm":
+        for r in bench_fp8_gemm(a.T, a.N, a.K, a.iters):
+            print(json.dumps(r))
     if a.what == "gemm-swiglu":
         print(json.dumps(bench_gemm_swiglu(a.T, a.N, a.K, a.iters, a.impl)))
     if a.what == "gemm-sustained":

@@ -25,6 +25,36 @@ def quant_act_1x128(x):
     return xq, xs
 
 
+def quant_rows_1x128(x, K: int, rows=None, swiglu: bool = False, out=None):
+    """Quantise the first ``rows[0]`` rows (device int32; all rows when None) of bf16 ``x`` to e4m3 with
+    1x128 scales.  With ``swiglu`` the rows hold [gate(K) | up(K)] and SiLU(gate) * up is quantised, so
+    the activation never goes back to memory in bf16.  ``out``: (xq [T, K], xs [T, ceil(K/128)])."""
+    _c._require_bf16(x)
+    assert x.stride(-1) == 1 and x.shape[1] == (2 * K if swiglu else K)
+    T = x.shape[0]
+    if out is None:
+        out = (torch.empty((T, K), dtype=FP8, device=x.device),
+               torch.empty((T, (K + 127) // 128), dtype=torch.float32, device=x.device))
+    xq, xs = out
+    _c._check(_c.lib().b200_quant_rows_1x128(_c._p(x), _c._p(xq), _c._p(xs), c_int(T), c_int(K), c_int(x.stride(0)),
+                                             _c._p(rows), c_int(1 if swiglu else 0), c_int(_c._sms),
+                                             _c._stream()), "quant_rows_1x128")
+    count_launch()
+    return xq, xs
+
+
+def _grouped_fp8_launch(xq, xs, wq, w_scale, group_off, avg_rows: int, y):
+    R, K = xq.shape
+    E, N = wq.shape[0], wq.shape[1]
+    ws = _c.Workspace.get(xq.device)
+    _c._check(_c.lib().b200_grouped_gemm_fp8_block(
+        _c._p(xq), _c._p(xs), _c._p(wq), _c._p(w_scale), _c._p(y), _c._p(group_off), c_int(E), c_int(R),
+        c_int(N), c_int(K), c_int(max(1, avg_rows)), _c._p(ws.status), c_int(_c._sms), _c._stream()),
+        "grouped_gemm_fp8_block")
+    count_launch()
+    return y
+
+
 def fp8_block_gemm(x, wq, w_scale_inv, bias=None, block=(128, 128), out=None):
     """x bf16 [T,K]; wq e4m3 [N,K]; w_scale_inv fp32 [ceil(N/128), ceil(K/128)] -> bf16 [T,N]."""
     if tuple(block) != (128, 128):
@@ -90,13 +120,7 @@ def grouped_fp8_gemm(x_perm, wq, w_scale, group_off, avg_rows: int):
     E, N = wq.shape[0], wq.shape[1]
     xq, xs = quant_act_1x128(x_perm)
     y = torch.empty((R, N), dtype=torch.bfloat16, device=x_perm.device)
-    ws = _c.Workspace.get(x_perm.device)
-    _c._check(_c.lib().b200_grouped_gemm_fp8_block(
-        _c._p(xq), _c._p(xs), _c._p(wq), _c._p(w_scale), _c._p(y), _c._p(group_off), c_int(E), c_int(R),
-        c_int(N), c_int(K), c_int(max(1, avg_rows)), _c._p(ws.status), c_int(_c._sms), _c._stream()),
-        "grouped_gemm_fp8_block")
-    count_launch()
-    return y
+    return _grouped_fp8_launch(xq, xs, wq, w_scale, group_off, avg_rows, y)
 
 
 def moe_experts_fp8(x, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, expert_offset, block=(128, 128)):
@@ -109,9 +133,59 @@ def moe_experts_fp8(x, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, expert_of
                                                          E_local)
     avg = (T * k + E_local - 1) // E_local
     h = grouped_fp8_gemm(x_perm, w13, w13_scale, group_off, avg)
-    a = _c.silu_and_mul(h)
-    y = grouped_fp8_gemm(a, w2, w2_scale, group_off, avg)
+    aq, a_s = quant_rows_1x128(h, w2.shape[2], swiglu=True)       # SiLU*mul fused into the quantisation
+    y = torch.empty((h.shape[0], w2.shape[1]), dtype=torch.bfloat16, device=x.device)
+    _grouped_fp8_launch(aq, a_s, w2, w2_scale, group_off, avg, y)
     return cuda_moe.moe_unpermute(y, inv_pos, topk_w.contiguous(), T)
+
+
+def moe_experts_ep_fp8(x, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, heap, num_experts: int):
+    """Block-scaled fp8 experts under expert parallelism on the fused plane: bf16 rows are PUT into the
+    owners' receive buffers, the owners quantise what arrived (the row count stays on the device), run
+    the grouped fp8 tcgen05 GEMMs with SiLU*mul fused into the second quantisation, and the epilogue of
+    the second GEMM stores every output row into the return slot of the rank the token came from."""
+    import ctypes
+    from . import cuda_moe
+    st = heap.ep_state
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E_local, I = w13.shape[0], w2.shape[2]
+    if T > st.max_tokens or k != st.k or H != st.H or num_experts != st.E:
+        raise RuntimeError("fused EP plane was configured for a different shape")
+    L = _c.lib()
+    ws = _c.Workspace.get(x.device)
+    spin = ctypes.c_uint(min(heap.spin_limit, 2**31 - 1))
+    x = x.contiguous()
+    ids = topk_ids.contiguous()
+    _c._check(L.b200_ep_dispatch(heap.peers_c, c_int(heap.rank), c_int(heap.world), st.layout, _c._p(st.ctrl),
+                                 _c._p(st.fill), _c._p(st.group_off), _c._p(x), _c._p(ids), c_int(T), c_int(k),
+                                 c_int(H), c_int(num_experts), c_int(st.cap), _c._p(ws.status), spin,
+                                 _c._stream()), "ep_dispatch")
+    count_launch(3)
+    bound = st.cap               # rows the receive buffer holds; the live count is group_off[E_local]
+    f8 = st.fp8_scratch(I)
+    rows = st.group_off[E_local:]
+    recv_x = heap.tensor(st.recv_x, (st.cap, H), torch.bfloat16)[:bound]
+    avg = max(1, (T * k) // max(1, E_local))
+    xq, xs = quant_rows_1x128(recv_x, H, rows=rows, out=(f8["xq1"][:bound], f8["xs1"][:bound]))
+    h = _grouped_fp8_launch(xq, xs, w13, w13_scale, st.group_off, avg, f8["h"][:bound])
+    aq, a_s = quant_rows_1x128(h, I, rows=rows, swiglu=True, out=(f8["xq2"][:bound], f8["xs2"][:bound]))
+    _c._check(L.b200_grouped_gemm_fp8_block_routed(
+        _c._p(aq), _c._p(a_s), _c._p(w2), _c._p(w2_scale), _c._p(st.group_off), c_int(E_local), c_int(bound),
+        c_int(H), c_int(I), c_int(avg), heap.peers_c, c_int(heap.rank), c_int(heap.world),
+        c_void_p(heap.local_ptr + st.recv_route.offset), c_ulonglong(st.ret.offset),
+        c_ulonglong(st.ret_flag.offset), _c._p(st.ctrl), _c._p(ws.status), c_int(_c._sms), _c._stream()),
+        "grouped_gemm_fp8_routed")
+    count_launch()
+    out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+    topk_w = topk_w.contiguous()
+    _c._check(L.b200_ep_combine(c_void_p(heap.local_ptr), c_ulonglong(st.ret.offset),
+                                c_ulonglong(st.ret_flag.offset), _c._p(st.ctrl), _c._p(ids),
+                                _c._p(topk_w), _c._p(out), c_int(T), c_int(k), c_int(H),
+                                c_int(num_experts), c_int(heap.world), _c._p(ws.status), spin, _c._stream()),
+              "ep_combine")
+    count_launch()
+    return out
 
 
 def quant_act_int8(x):

@@ -137,6 +137,20 @@ class EpState:
         self.group_off = torch.zeros(num_experts // world + 1, dtype=torch.int32, device=dev)
         self.act = torch.zeros(self.cap, inter, dtype=torch.bfloat16, device=dev)
 
+    def fp8_scratch(self, inter: int) -> dict:
+        """Local buffers of the fp8 expert pipeline (quantised rows, scales, gate|up product), made on
+        first use outside graph capture."""
+        if getattr(self, "_fp8", None) is None:
+            dev, cap, H = self.heap.device, self.cap, self.H
+            f8 = torch.float8_e4m3fn
+            self._fp8 = {
+                "xq1": torch.zeros(cap, H, dtype=f8, device=dev),
+                "xs1": torch.zeros(cap, (H + 127) // 128, dtype=torch.float32, device=dev),
+                "h": torch.zeros(cap, 2 * inter, dtype=torch.bfloat16, device=dev),
+                "xq2": torch.zeros(cap, inter, dtype=f8, device=dev),
+                "xs2": torch.zeros(cap, (inter + 127) // 128, dtype=torch.float32, device=dev)}
+        return self._fp8
+
     @staticmethod
     def heap_bytes(max_tokens, top_k, hidden, num_experts, world, capacity_factor) -> int:
         worst = world * max_tokens * top_k

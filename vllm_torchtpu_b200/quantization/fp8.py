@@ -256,5 +256,9 @@ class Fp8BlockMoEMethod:
                           for e in range(moe.w2.shape[0])]).to(x.dtype)
         return ops.ref.moe_experts(x, w13, w2, topk_ids, topk_w, moe.expert_range[0])
 
+    def apply_fused_ep(self, moe, x, topk_ids, topk_w, comm):
+        return ops.cuda_ops().moe_experts_ep_fp8(x, moe.w13, moe.w13_scale, moe.w2, moe.w2_scale, topk_ids, topk_w,
+                                                 comm.heap, moe.num_experts)
+
     def weight_bytes(self, moe) -> int:
         return moe.w13.numel() + moe.w2.numel() + 4 * (moe.w13_scale.numel() + moe.w2_scale.numel())
