@@ -23,6 +23,28 @@ def test_quant_act_matches_reference():
     assert ((xq.float() * xs.repeat_interleave(128, 1)[:, :640]) - x.float()).abs().max() <= 0.07 * x.float().abs().max()
 
 
+def test_quant_rows_bounded_by_device_count_and_fused_swiglu():
+    """Only the first rows[0] rows are written; with swiglu the quantised values are those of
+    quantising SiLU(gate) * up (rounded to bf16) on its own."""
+    T, K = 90, 384
+    x = (torch.randn(T, 2 * K, device=DEV) * 2).bfloat16()
+    rows = torch.tensor([53], dtype=torch.int32, device=DEV)
+    xq = torch.zeros(T, K, dtype=torch.float8_e4m3fn, device=DEV)
+    xs = torch.full((T, 3), -1.0, device=DEV)
+    cu().quant_rows_1x128(x, K, rows=rows, swiglu=True, out=(xq, xs))
+    act = (torch.nn.functional.silu(x[:, :K].float()) * x[:, K:].float()).bfloat16()
+    rq, rs = cu().quant_act_1x128(act)
+    torch.cuda.synchronize()
+    assert (xs[53:] == -1.0).all() and (xq[53:].float() == 0).all()
+    torch.testing.assert_close(xs[:53], rs[:53], rtol=2e-2, atol=0)
+    deq = xq[:53].float() * xs[:53].repeat_interleave(128, 1)
+    assert (deq - act[:53].float()).abs().max() <= 0.07 * act.float().abs().max()
+    # plain form over all rows equals the per-row kernel
+    xq2, xs2 = cu().quant_rows_1x128(x, 2 * K)
+    rq2, rs2 = cu().quant_act_1x128(x)
+    assert torch.equal(xs2, rs2) and torch.equal(xq2.view(torch.uint8), rq2.view(torch.uint8))
+
+
 @pytest.mark.parametrize("T,N,K", [(16, 256, 512), (64, 1280, 8192), (100, 384, 1024), (128, 7168, 2048),
                                    (300, 1024, 640), (1, 128, 128)])
 def test_fp8_block_gemm(T, N, K):
@@ -36,6 +58,52 @@ def test_fp8_block_gemm(T, N, K):
     want = q.fp8_block_gemm_reference(x, wq, ws, out_dtype=torch.float32)
     err = (y.float() - want).abs().max().item()
     assert err <= 2e-2 * want.abs().max().item() + 1e-2, err
+
+
+@pytest.mark.parametrize("T,N,K,bias", [(1500, 4096, 1024, False), (4096, 1280, 2048, True), (777, 6152, 640, True),
+                                        (129, 28672, 512, False)])
+def test_fp8_block_gemm_many_token_kernel(T, N, K, bias):
+    """Token-major kernel (tokens on the TMEM lanes): ragged token and weight tiles, bias, N not a multiple
+    of the 256-row tile."""
+    from vllm_torchtpu_b200.ops import cuda_fp8
+    assert cuda_fp8.use_rows_kernel(T, N)
+    g = torch.Generator(device=DEV).manual_seed(T + N)
+    x = torch.randn(T, K, device=DEV, generator=g).bfloat16()
+    w = torch.randn(N, K, device=DEV, generator=g) * 0.05
+    b = torch.randn(N, device=DEV, generator=g).bfloat16() if bias else None
+    wq, ws = q.quantize_weight_block(w)
+    y = cu().fp8_block_gemm(x, wq, ws, b)
+    torch.cuda.synchronize()
+    assert cu().check_status() == 0
+    want = q.fp8_block_gemm_reference(x, wq, ws, out_dtype=torch.float32)
+    if bias:
+        want = want + b.float()
+    err = (y.float() - want).abs().max().item()
+    assert err <= 2e-2 * want.abs().max().item() + 1e-2, err
+
+
+def test_fp8_grouped_gemm_many_token_kernel():
+    """Grouped form: uneven groups (one empty, one of a single row) against the per-group reference."""
+    from vllm_torchtpu_b200.ops import cuda_fp8
+    E, N, K = 6, 1024, 512
+    sizes = [700, 0, 1, 1300, 257, 3000]
+    R = sum(sizes)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    x = torch.randn(R, K, device=DEV, generator=g).bfloat16()
+    w = torch.randn(E, N, K, device=DEV, generator=g) * 0.05
+    qs = [q.quantize_weight_block(w[e]) for e in range(E)]
+    wq, ws = torch.stack([a for a, _ in qs]), torch.stack([b for _, b in qs])
+    off = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device=DEV)
+    y = cuda_fp8.grouped_fp8_gemm(x, wq, ws, off, R // E)
+    torch.cuda.synchronize()
+    assert cu().check_status() == 0
+    lo = 0
+    for e, n in enumerate(sizes):
+        if n:
+            want = q.fp8_block_gemm_reference(x[lo:lo + n], wq[e], ws[e], out_dtype=torch.float32)
+            err = (y[lo:lo + n].float() - want).abs().max().item()
+            assert err <= 2e-2 * want.abs().max().item() + 1e-2, (e, err)
+        lo += n
 
 
 def test_fp8_moe_experts():

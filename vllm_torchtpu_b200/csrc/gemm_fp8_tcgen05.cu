@@ -461,6 +461,63 @@ __global__ void quant_rows_1x128_kernel(const __nv_bfloat16* __restrict__ x, __n
   }
 }
 
+// Vectorised form for K % 8 == 0 and 16-byte aligned rows: a thread owns 8 consecutive elements (one
+// 16-byte load, one 8-byte store), 16 threads own a 128-column group, grid-stride over (row, group) pairs.
+template <bool SWIGLU>
+__global__ void quant_rows_1x128_vec_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_e4m3* __restrict__ xq,
+                                            float* __restrict__ xs, int T, int K, int ldx, int groups,
+                                            const int* __restrict__ rows_ptr) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int rows = rows_ptr != nullptr ? min(T, *rows_ptr) : T;
+  const int sub = threadIdx.x & 15;
+  const long long total = (long long)rows * groups;
+  const long long stride = (long long)gridDim.x * (blockDim.x >> 4);
+  for (long long gi = (long long)blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4); gi < total; gi += stride) {
+    const int t = (int)(gi / groups), g = (int)(gi % groups);
+    const int c0 = g * 128 + sub * 8;
+    float v[8];
+    if (c0 < K) {
+      const uint4 a = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + c0);
+      const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+      if (SWIGLU) {
+        const uint4 u = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + K + c0);
+        const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 af = __bfloat1622float2(ah[j]), uf = __bfloat1622float2(uh[j]);
+          v[2 * j] = __bfloat162float(__float2bfloat16(af.x / (1.f + __expf(-af.x)) * uf.x));
+          v[2 * j + 1] = __bfloat162float(__float2bfloat16(af.y / (1.f + __expf(-af.y)) * uf.y));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 af = __bfloat1622float2(ah[j]);
+          v[2 * j] = af.x;
+          v[2 * j + 1] = af.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = fmaxf(amax, 1e-12f) / 448.f;
+    const float inv = 1.f / scale;
+    if (c0 < K) {
+      __align__(8) __nv_fp8_e4m3 o8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o8[j] = __nv_fp8_e4m3(fminf(fmaxf(v[j] * inv, -448.f), 448.f));
+      *reinterpret_cast<uint2*>(xq + (size_t)t * K + c0) = *reinterpret_cast<const uint2*>(o8);
+    }
+    if (sub == 0) xs[(size_t)t * groups + g] = scale;
+  }
+}
+
 // x [T, K] bf16 -> xq [T, K] int8 and xs [T] fp32 (amax / 127): one CTA per row
 __global__ void quant_act_int8_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ xq,
                                       float* __restrict__ xs, int K, int ldx) {
@@ -576,6 +633,19 @@ extern "C" int b200_quant_rows_1x128(const void* x, void* xq, float* xs, int T, 
   const long long warps = (long long)T * groups;
   long long blocks = (warps + 7) / 8;
   if (blocks > (long long)num_sms * 8) blocks = (long long)num_sms * 8;
+  if (K % 8 == 0 && ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(xq) & 7) == 0) {
+    long long vb = (warps + 15) / 16;                  // 16 groups per 256-thread block
+    if (vb > (long long)num_sms * 8) vb = (long long)num_sms * 8;
+    if (swiglu)
+      f8::quant_rows_1x128_vec_kernel<true><<<(int)vb, 256, 0, stream>>>(
+          (const __nv_bfloat16*)x, (__nv_fp8_e4m3*)xq, xs, T, K, ldx, groups, rows_ptr);
+    else
+      f8::quant_rows_1x128_vec_kernel<false><<<(int)vb, 256, 0, stream>>>(
+          (const __nv_bfloat16*)x, (__nv_fp8_e4m3*)xq, xs, T, K, ldx, groups, rows_ptr);
+    B200_CUDA_CHECK(cudaGetLastError());
+    return 0;
+  }
   if (swiglu)
     f8::quant_rows_1x128_kernel<true><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_fp8_e4m3*)xq,
                                                                        xs, T, K, ldx, groups, rows_ptr);

@@ -278,13 +278,10 @@ def bench_fp8_gemm(T, N, K, iters=20) -> list:
     wq, wsi = quantize_weight_block(w)
     xq, xs = cuda.quant_act_1x128(x)
     y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
-    ws = cuda.Workspace.get(x.device)
-    from ctypes import c_int
+    from . import cuda_fp8
 
     def gemm_only():
-        cuda._check(cuda.lib().b200_gemm_fp8_block(
-            cuda._p(xq), cuda._p(xs), cuda._p(wq), cuda._p(wsi), cuda._p(y), None, c_int(T), c_int(N), c_int(K),
-            c_int(N), cuda._p(ws.status), c_int(cuda._sms), cuda._stream()), "gemm_fp8_block")
+        cuda_fp8.fp8_block_gemm_quantised(xq, xs, wq, wsi, y)
     flops = 2.0 * T * N * K
     byts = float(T * K + N * K + 2 * T * N)
     t_roof = max(flops / (2 * pk["bf16_tflops"] * 1e12), byts / (pk["hbm_gbs"] * 1e9)) * 1e3

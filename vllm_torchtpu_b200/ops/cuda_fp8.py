@@ -19,9 +19,11 @@ def quant_act_1x128(x):
     T, K = x.shape
     xq = torch.empty((T, K), dtype=FP8, device=x.device)
     xs = torch.empty((T, (K + 127) // 128), dtype=torch.float32, device=x.device)
-    _c._check(_c.lib().b200_quant_act_1x128(_c._p(x), _c._p(xq), _c._p(xs), c_int(T), c_int(K),
-                                            c_int(x.stride(0)), _c._stream()), "quant_act_1x128")
-    count_launch()
+    if T:
+        _c._check(_c.lib().b200_quant_rows_1x128(_c._p(x), _c._p(xq), _c._p(xs), c_int(T), c_int(K),
+                                                 c_int(x.stride(0)), c_void_p(0), c_int(0), c_int(_c._sms),
+                                                 _c._stream()), "quant_rows_1x128")
+        count_launch()
     return xq, xs
 
 
@@ -47,12 +49,27 @@ def _grouped_fp8_launch(xq, xs, wq, w_scale, group_off, avg_rows: int, y):
     R, K = xq.shape
     E, N = wq.shape[0], wq.shape[1]
     ws = _c.Workspace.get(xq.device)
+    from .. import envs
+    if envs.B200_FP8_ROWS_MIN_TILES >= 0 and avg_rows >= 256 and use_rows_kernel(R, N):
+        _c._check(_c.lib().b200_grouped_gemm_fp8_block_rows(
+            _c._p(xq), _c._p(xs), _c._p(wq), _c._p(w_scale), _c._p(y), _c._p(group_off), c_int(E), c_int(R),
+            c_int(N), c_int(K), _c._p(ws.status), c_int(_c._sms), _c._stream()), "grouped_gemm_fp8_block_rows")
+        count_launch()
+        return y
     _c._check(_c.lib().b200_grouped_gemm_fp8_block(
         _c._p(xq), _c._p(xs), _c._p(wq), _c._p(w_scale), _c._p(y), _c._p(group_off), c_int(E), c_int(R),
         c_int(N), c_int(K), c_int(max(1, avg_rows)), _c._p(ws.status), c_int(_c._sms), _c._stream()),
         "grouped_gemm_fp8_block")
     count_launch()
     return y
+
+
+def use_rows_kernel(T: int, N: int) -> bool:
+    """The many-token kernel (tokens on the TMEM lanes, one scale scalar per thread and K block) pays off
+    once its 128 x 256 tiles fill most of the SMs; below that the weight-major kernel with split-K does."""
+    from .. import envs
+    min_tiles = envs.B200_FP8_ROWS_MIN_TILES
+    return min_tiles >= 0 and T > 128 and (-(-T // 128)) * (-(-N // 256)) >= min_tiles
 
 
 def fp8_block_gemm(x, wq, w_scale_inv, bias=None, block=(128, 128), out=None):
@@ -67,12 +84,21 @@ def fp8_block_gemm(x, wq, w_scale_inv, bias=None, block=(128, 128), out=None):
     y = out if out is not None else torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
     if T == 0:
         return y.reshape(*lead, N)
-    ws = _c.Workspace.get(x.device)
-    _c._check(_c.lib().b200_gemm_fp8_block(
-        _c._p(xq), _c._p(xs), _c._p(wq), _c._p(w_scale_inv), _c._p(y), _c._p(bias), c_int(T), c_int(N),
-        c_int(K), c_int(y.stride(0)), _c._p(ws.status), c_int(_c._sms), _c._stream()), "gemm_fp8_block")
-    count_launch()
+    fp8_block_gemm_quantised(xq, xs, wq, w_scale_inv, y, bias)
     return y.reshape(*lead, N)
+
+
+def fp8_block_gemm_quantised(xq, xs, wq, w_scale_inv, y, bias=None):
+    """The GEMM alone on operands that are already e4m3 with their scales; picks the kernel by shape."""
+    T, K = xq.shape
+    N = wq.shape[0]
+    ws = _c.Workspace.get(xq.device)
+    fn, name = ((_c.lib().b200_gemm_fp8_block_rows, "gemm_fp8_block_rows") if use_rows_kernel(T, N)
+                else (_c.lib().b200_gemm_fp8_block, "gemm_fp8_block"))
+    _c._check(fn(_c._p(xq), _c._p(xs), _c._p(wq), _c._p(w_scale_inv), _c._p(y), _c._p(bias), c_int(T), c_int(N),
+                 c_int(K), c_int(y.stride(0)), _c._p(ws.status), c_int(_c._sms), _c._stream()), name)
+    count_launch()
+    return y
 
 
 def fp8_block_gemm_push(x, wq, w_scale_inv, heap):
