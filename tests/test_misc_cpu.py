@@ -147,3 +147,35 @@ def test_pad_q_heads_keeps_the_kv_group_mapping():
     po = pad_q_heads(o, 1, Hkv, G, Gp, D)
     assert po.shape == (H, Hkv * Gp * D)
     torch.testing.assert_close(po.reshape(H, Hkv, Gp, D)[:, :, :G].reshape(H, -1), o)
+
+
+def test_fused_ep_plane_is_called_once_per_call_tokens_rows():
+    """A step longer than the plane's call size goes through it in several calls, the same number on
+    every rank (the agreed row count decides, not this rank's own)."""
+    import types
+
+    import torch
+
+    from vllm_torchtpu_b200.layers.moe import FusedMoE
+
+    calls = []
+
+    class Method:
+        def apply_fused_ep(self, moe, x, ids, w, comm):
+            calls.append(x.shape[0])
+            return x * 2
+
+    moe = FusedMoE.__new__(FusedMoE)
+    moe.method = Method()
+    comm = types.SimpleNamespace(heap=types.SimpleNamespace(ep_state=types.SimpleNamespace(max_tokens=4)))
+    x = torch.arange(22, dtype=torch.float32).reshape(11, 2)
+    ids = torch.zeros(11, 2, dtype=torch.int32)
+    w = torch.ones(11, 2)
+    y = moe._fused_ep_calls(x, ids, w, comm)
+    assert calls == [4, 4, 3] and torch.equal(y, x * 2)
+    calls.clear()
+    y = moe._fused_ep_calls(x[:3], ids[:3], w[:3], comm, rows=9)      # peers hold 9 rows: three calls here too
+    assert calls == [3, 0, 0] and torch.equal(y, x[:3] * 2)
+    calls.clear()
+    moe._fused_ep_calls(x[:4], ids[:4], w[:4], comm)
+    assert calls == [4]

@@ -4,9 +4,10 @@
 //
 // tcgen05.mma (kind::f8f6f4, fp32 accumulate) cannot apply a different scale to every 128-wide
 // K block inside one accumulation, so each K block is accumulated on its own in TMEM (two
-// partial buffers, ping-pong) and the four epilogue warps "promote" it: tcgen05.ld the partial,
-// multiply by the block's scale product and add into fp32 register accumulators while the tensor
-// core already works on the next block.  A weight tile is exactly one scale row (BM = 128), so
+// partial buffers, ping-pong) and the promotion warps (four, or eight from 64 tokens per tile on, so that
+// a warp's share of a K block is at most two TMEM loads, issued together) "promote" it: tcgen05.ld the
+// partial, multiply by the block's scale product and add into fp32 register accumulators while the
+// tensor core already works on the next block.  A weight tile is exactly one scale row (BM = 128), so
 // the weight scale is one scalar per (tile, K block); activation scales are one per column.
 // Layouts: Wq [N, K] e4m3 K-major (the checkpoint layout), ws [ceil(N/128), ceil(K/128)] fp32
 // (``weight_scale_inv``), Xq [T, K] e4m3, xs [T, ceil(K/128)] fp32 from the quantisation kernel
@@ -30,19 +31,24 @@ namespace f8 {
 
 constexpr int BM = 128;
 constexpr int BKB = 128;          // K elements (= bytes) per stage row: one scale block
-constexpr int NUM_THREADS = 192;
 constexpr int MAX_GROUPS = 1024;
 
 template <int BN>
 struct Cfg {
+  // promotion warps: four cover the 128 TMEM lanes; from 64 tokens on a second set of four takes half of
+  // the columns, so that a warp never has more than 64 columns (two TMEM loads) per K block
+  static constexpr int EPI_WARPS = BN >= 64 ? 8 : 4;
+  static constexpr int CW = BN / (EPI_WARPS / 4);
+  static constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int A_BYTES = BM * BKB;
   static constexpr int B_BYTES = BN * BKB;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES_RAW = 180224 / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int PREFIX_BYTES = (MAX_GROUPS + 1) * 4;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + PREFIX_BYTES + 1024;
+  static constexpr int PREFIX_BYTES = (MAX_GROUPS + 1) * 4 + 12;      // keeps what follows 16-byte aligned
+  static constexpr int SCALE_BYTES = EPI_WARPS * 2 * CW * 4;          // per promotion warp: two rows of column scales
+  static constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + PREFIX_BYTES + SCALE_BYTES + 1024;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static_assert(BM * BN * 4 <= STAGES * STAGE_BYTES, "split-K partial must fit in the stage ring");
 };
@@ -119,8 +125,9 @@ __device__ __forceinline__ Work get_work(int w, const Params& p, const int* s_pr
   return k;
 }
 
-template <int BN, int KIND>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// MODE 0: output to Y; 1: tensor-parallel push plane; 2: routed rows (expert-parallel combine)
+template <int BN, int KIND, int MODE>
+__global__ void __launch_bounds__(Cfg<BN>::NUM_THREADS, 1)
 gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                       const Params p) {
   using C = Cfg<BN>;
@@ -135,6 +142,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_prefix = reinterpret_cast<int*>(smem + STAGES * C::STAGE_BYTES + C::BAR_BYTES);
+  float* s_scale = reinterpret_cast<float*>(smem + STAGES * C::STAGE_BYTES + C::BAR_BYTES + C::PREFIX_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -144,8 +152,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     }
     mbar_init(&pfull[0], 1);
     mbar_init(&pfull[1], 1);
-    mbar_init(&pempty[0], 4);
-    mbar_init(&pempty[1], 4);
+    mbar_init(&pempty[0], C::EPI_WARPS);
+    mbar_init(&pempty[1], C::EPI_WARPS);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
@@ -158,9 +166,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   pdl_launch_dependents();
   pdl_wait();
   // bumped by the last CTA of a push launch to exit: read by every thread before any CTA can do so
-  const bool push = p.world > 1 && p.row_route == nullptr;
-  const int epoch = push ? (*reinterpret_cast<volatile int*>(p.epoch_ptr) + 1) : 0;
-  const int ndst = push ? p.world : 1;
+  constexpr bool PUSH = MODE == 1, ROUTED = MODE == 2;
+  const int epoch = PUSH ? (*reinterpret_cast<volatile int*>(p.epoch_ptr) + 1) : 0;
+  const int ndst = PUSH ? p.world : 1;
   if (p.group_off != nullptr) {
     for (int e = threadIdx.x; e < p.num_groups; e += blockDim.x)
       s_prefix[e + 1] = (p.group_off[e + 1] - p.group_off[e] + BN - 1) / BN;
@@ -228,34 +236,52 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       }
     }
   } else {
+    // promotion warps: warp w reads TMEM lanes 32 * (w % 4).. (its quarter of the weight rows) and the
+    // CW columns (tokens) from col0 on; all of its TMEM loads of a K block are in flight together
+    constexpr int CW = C::CW;
     const int q = warp & 3;
     const int row = q * 32 + lane;
+    const int col0 = ((warp - 2) >> 2) * CW;
     uint32_t pc = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const Work k = get_work<BN>(w, p, s_prefix);
-      float acc[BN];
+      float acc[CW];
 #pragma unroll
-      for (int c = 0; c < BN; ++c) acc[c] = 0.f;
+      for (int c = 0; c < CW; ++c) acc[c] = 0.f;
       for (int kb = k.kb0; kb < k.kb1; ++kb, ++pc) {
         const int pb = pc & 1;
-        const float sw = KIND == 1 ? 1.f : p.w_scale[(size_t)k.ws_row * p.ws_ld + kb];
+        // the scale of column c is a warp-uniform value per accumulator register: lane j fetches the
+        // scale product of column c0 + j, the warp parks the row in shared memory and reads it back four
+        // columns per broadcast load (a shuffle per column would cost four times the issue slots)
+        float* srow = s_scale + ((warp - 2) * 2 + pb) * CW;
+        if (KIND == 0) {
+          const float sw = p.w_scale[(size_t)k.ws_row * p.ws_ld + kb];
+#pragma unroll
+          for (int c0 = 0; c0 < CW; c0 += 32) {
+            const int c = col0 + c0 + lane;
+            srow[c0 + lane] = c < k.t_valid ? sw * p.x_scale[(size_t)(k.t_row + c) * p.xs_ld + kb] : 0.f;
+          }
+          __syncwarp();
+        }
         if (!mbar_wait(&pfull[pb], (pc >> 1) & 1, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + pb * BN + ((uint32_t)(q * 32) << 16);
+        const uint32_t taddr = tmem_base + pb * BN + col0 + ((uint32_t)(q * 32) << 16);
+        uint32_t r[CW];
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          // lane j fetches the activation scale of column c0 + j; it is handed round by shuffle
-          const int t = k.t_row + c0 + lane;
-          float mine = 0.f;
-          if (KIND == 0 && c0 + lane < k.t_valid) mine = sw * p.x_scale[(size_t)t * p.xs_ld + kb];
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c0, r);
-          tmem_ld_wait();
+        for (int c0 = 0; c0 < CW; c0 += 32) tmem_ld_32x32(taddr + c0, r + c0);
+        tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (KIND == 1) acc[c0 + j] += (float)(int)r[j];
-            else acc[c0 + j] = fmaf(__uint_as_float(r[j]), __shfl_sync(0xffffffffu, mine, j), acc[c0 + j]);
+        for (int j = 0; j < CW; j += 4) {
+          if (KIND == 1) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[j + u] += (float)(int)r[j + u];
+          } else {
+            const float4 s4 = *reinterpret_cast<const float4*>(srow + j);
+            acc[j] = fmaf(__uint_as_float(r[j]), s4.x, acc[j]);
+            acc[j + 1] = fmaf(__uint_as_float(r[j + 1]), s4.y, acc[j + 1]);
+            acc[j + 2] = fmaf(__uint_as_float(r[j + 2]), s4.z, acc[j + 2]);
+            acc[j + 3] = fmaf(__uint_as_float(r[j + 3]), s4.w, acc[j + 3]);
           }
         }
         tc_fence_before();
@@ -264,12 +290,13 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       }
       if (!ok) break;
       const int n = k.n0 + row;
+      const int cv = k.t_valid - col0;               // live columns of this warp (may be <= 0)
       if (KIND == 1) {
         // per-channel weight scale (this thread's row) times per-token activation scale (the column)
         const float wsn = n < p.N ? p.w_scale[k.ws_row * BM + row] : 0.f;
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          const float mine = (c0 + lane < k.t_valid) ? p.x_scale[k.t_row + c0 + lane] : 0.f;
+        for (int c0 = 0; c0 < CW; c0 += 32) {
+          const float mine = (c0 + lane < cv) ? p.x_scale[k.t_row + col0 + c0 + lane] : 0.f;
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[c0 + j] *= wsn * __shfl_sync(0xffffffffu, mine, j);
         }
@@ -277,13 +304,13 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       if (p.cluster_splitk) {
         float* part = reinterpret_cast<float*>(smem);      // ring is idle: this CTA has one work item
 #pragma unroll
-        for (int c = 0; c < BN; ++c) part[c * BM + row] = acc[c];
-      } else if (p.row_route != nullptr) {
+        for (int c = 0; c < CW; ++c) part[(col0 + c) * BM + row] = acc[c];
+      } else if (ROUTED) {
         if (n < p.N) {
 #pragma unroll
-          for (int c = 0; c < BN; ++c) {
-            if (c < k.t_valid) {
-              const int2 rt = __ldg(p.row_route + k.t_row + c);
+          for (int c = 0; c < CW; ++c) {
+            if (c < cv) {
+              const int2 rt = __ldg(p.row_route + k.t_row + col0 + c);
               reinterpret_cast<__nv_bfloat16*>(p.peer[rt.x] + p.route_ret_off)[(size_t)rt.y * p.N + n] =
                   __float2bfloat16(acc[c]);
             }
@@ -295,19 +322,19 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
           const float bias = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;
           for (int d = 0; d < ndst; ++d) {
             __nv_bfloat16* yp =
-                p.world > 1 ? reinterpret_cast<__nv_bfloat16*>(p.peer[d] + p.part_off + (size_t)p.rank * p.part_src_stride) +
-                                  (size_t)k.t_row * p.N + n
-                            : p.Y + (size_t)k.t_row * p.ldy + n;
-            const size_t ld = p.world > 1 ? (size_t)p.N : (size_t)p.ldy;
+                PUSH ? reinterpret_cast<__nv_bfloat16*>(p.peer[d] + p.part_off + (size_t)p.rank * p.part_src_stride) +
+                           (size_t)(k.t_row + col0) * p.N + n
+                     : p.Y + (size_t)(k.t_row + col0) * p.ldy + n;
+            const size_t ld = PUSH ? (size_t)p.N : (size_t)p.ldy;
 #pragma unroll
-            for (int c = 0; c < BN; ++c)
-              if (c < k.t_valid) yp[(size_t)c * ld] = __float2bfloat16(acc[c] + bias);
+            for (int c = 0; c < CW; ++c)
+              if (c < cv) yp[(size_t)c * ld] = __float2bfloat16(acc[c] + bias);
           }
         }
-        if (p.world > 1 && p.row_route == nullptr) {
+        if (PUSH) {
           // the tile has been pushed: release its flag at every rank
           __threadfence_system();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
           const int t = (int)threadIdx.x - 64;
           if (t < p.world) {
             const int tile = raster_tile(k.n0 / BM, k.t_row / BN, p.n_tiles, p.t_tiles);
@@ -325,7 +352,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     cluster_wait_acquire();
     if (warp >= 2 && !*abort_flag && (int)blockIdx.x < total_work) {
       const Work k = get_work<BN>(blockIdx.x, p, s_prefix);
-      const int q = warp & 3;
+      const int ew = warp - 2;
       const uint32_t rank = cluster_ctarank();
       const int S = p.splits;
       const int n4 = k.n0 + 4 * lane;
@@ -336,7 +363,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
           if (n4 + j < p.N) b4[j] = __bfloat162float(p.bias[n4 + j]);
       }
       const uint32_t part_local = smem_u32(smem);
-      for (int c = (int)rank + S * q; c < k.t_valid; c += 4 * S) {
+      for (int c = (int)rank + S * ew; c < k.t_valid; c += C::EPI_WARPS * S) {
         float4 v[8];                     // all partials of the column are requested before the first is used
 #pragma unroll
         for (int r2 = 0; r2 < 8; ++r2)
@@ -348,20 +375,20 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         const float vals[4] = {a.x, a.y, a.z, a.w};
         for (int d = 0; d < ndst; ++d) {
           __nv_bfloat16* yp =
-              p.world > 1 ? reinterpret_cast<__nv_bfloat16*>(p.peer[d] + p.part_off + (size_t)p.rank * p.part_src_stride) +
-                                (size_t)(k.t_row + c) * p.N + n4
-                          : p.Y + (size_t)(k.t_row + c) * p.ldy + n4;
+              PUSH ? reinterpret_cast<__nv_bfloat16*>(p.peer[d] + p.part_off + (size_t)p.rank * p.part_src_stride) +
+                         (size_t)(k.t_row + c) * p.N + n4
+                   : p.Y + (size_t)(k.t_row + c) * p.ldy + n4;
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
         }
       }
-      if (p.world > 1) __threadfence_system();
+      if (PUSH) __threadfence_system();
     }
     __syncwarp();
     cluster_arrive_release();
     cluster_wait_acquire();
-    if (p.world > 1 && cluster_ctarank() == 0 && warp == 2 && (int)blockIdx.x < total_work && !*abort_flag) {
+    if (PUSH && cluster_ctarank() == 0 && warp == 2 && (int)blockIdx.x < total_work && !*abort_flag) {
       // every CTA of the cluster has stored and fenced its columns: release the tile's flag
       const Work k = get_work<BN>(blockIdx.x, p, s_prefix);
       if (lane < p.world) {
@@ -378,12 +405,12 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
-  if (p.world > 1 && threadIdx.x == 64) {
+  if (MODE != 0 && threadIdx.x == 64) {
     __threadfence();
     const int arrived = atomicAdd(p.cta_done, 1) + 1;
     if (arrived == (int)gridDim.x) {
       *p.cta_done = 0;
-      if (p.row_route != nullptr) {
+      if (ROUTED) {
         // every CTA fenced its routed stores before it arrived: tell all ranks their rows are back
         __threadfence_system();
         const int ep_epoch = *reinterpret_cast<volatile int*>(p.epoch_ptr);
@@ -540,15 +567,15 @@ __global__ void quant_act_int8_kernel(const __nv_bfloat16* __restrict__ x, int8_
   if (threadIdx.x == 0) xs[t] = scale;
 }
 
-template <int BN, int KIND = 0>
-static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int grid,
-                  cudaStream_t stream) {
+template <int BN, int KIND, int MODE>
+static int launch_mode(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int grid,
+                       cudaStream_t stream) {
   using C = Cfg<BN>;
   static unsigned long long attr_seen = 0;
-  B200_CUDA_CHECK(ensure_dynamic_smem(gemm_fp8_block_kernel<BN, KIND>, C::SMEM, &attr_seen));
+  B200_CUDA_CHECK(ensure_dynamic_smem(gemm_fp8_block_kernel<BN, KIND, MODE>, C::SMEM, &attr_seen));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(C::NUM_THREADS);
   cfg.dynamicSmemBytes = C::SMEM;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -565,17 +592,25 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& 
   ++na;
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_fp8_block_kernel<BN, KIND>, tmW, tmX, p));
+  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_fp8_block_kernel<BN, KIND, MODE>, tmW, tmX, p));
   return 0;
+}
+
+template <int BN, int KIND = 0>
+static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& p, int grid,
+                  cudaStream_t stream) {
+  if (KIND == 0 && p.row_route != nullptr) return launch_mode<BN, 0, 2>(tmW, tmX, p, grid, stream);
+  if (KIND == 0 && p.world > 1) return launch_mode<BN, 0, 1>(tmW, tmX, p, grid, stream);
+  return launch_mode<BN, KIND, 0>(tmW, tmX, p, grid, stream);
 }
 
 template <int BN>
 static int max_clusters(int splits) {
   using C = Cfg<BN>;
-  cudaFuncSetAttribute(gemm_fp8_block_kernel<BN, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+  cudaFuncSetAttribute(gemm_fp8_block_kernel<BN, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits * 64);
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(C::NUM_THREADS);
   cfg.dynamicSmemBytes = C::SMEM;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -585,7 +620,7 @@ static int max_clusters(int splits) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm_fp8_block_kernel<BN, 0>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_fp8_block_kernel<BN, 0, 0>, &cfg) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }

@@ -96,8 +96,10 @@ _decl("B200_SYMM_HEAP_MB", int, 512, "size of the per-rank symmetric heap")
 _decl("B200_FP8_ROWS_MIN_TILES", int, 96,
       "fp8 block GEMM: use the token-major kernel from this many 128x256 output tiles (-1: never)")
 _decl("B200_MOE_FUSED_EP", bool, True, "dispatch/combine inside the expert kernel over peer memory")
-_decl("B200_MOE_EP_CAPACITY_FACTOR", float, 2.0,
-      "fused EP plane: rows an owner can receive per call, as a multiple of max_tokens * top_k")
+_decl("B200_MOE_EP_CAPACITY_FACTOR", float, 0.0,
+      "fused EP plane: rows an owner can receive per call, as a multiple of call tokens * top_k; "
+      "0 sizes for the worst case (every row of every rank routed to one owner), so nothing is ever dropped")
+_decl("B200_MOE_EP_CALL_TOKENS", int, 2048, "fused EP plane: tokens per rank and call; longer steps make several calls")
 _decl("B200_MOE_FUSED_EP_MIN_TOKENS", int, 0, "use the AG/RS path below this many tokens")
 _decl("B200_MOE_SEQUENCE_PARALLEL", bool, False, "reduce-scatter after attention, all-gather before experts")
 _decl("B200_MOE_TOPK_WEIGHTS_FLOAT32", bool, True, "keep routing weights in fp32")

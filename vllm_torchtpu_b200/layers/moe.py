@@ -111,12 +111,27 @@ class FusedMoE:
         st = get_state()
         tp = st.tp.size
         if tp == 1:
-            return self.method.apply_fused_ep(self, x, topk_ids, topk_w, comm)
+            return self._fused_ep_calls(x, topk_ids, topk_w, comm)
         T = x.shape[0]
         chunk = -(-T // tp)
         lo = min(T, st.tp.rank_in_group * chunk)
         hi = min(T, lo + chunk)
-        y = self.method.apply_fused_ep(self, x[lo:hi], topk_ids[lo:hi], topk_w[lo:hi], comm)
+        y = self._fused_ep_calls(x[lo:hi], topk_ids[lo:hi], topk_w[lo:hi], comm, rows=chunk)
         if hi - lo < chunk:
             y = torch.cat([y, y.new_zeros(chunk - (hi - lo), y.shape[1])], 0)
         return get_tp_comm().all_gather(y, 0)[:T]
+
+    def _fused_ep_calls(self, x, topk_ids, topk_w, comm, rows=None):
+        """One call of the plane per ``max_tokens`` rows.  Every rank of the EP group makes the same number
+        of calls: ``rows`` is the row count the ranks agree on (a TP slice may be shorter on the last
+        rank; replicas in lockstep pad their steps to one length)."""
+        step = comm.heap.ep_state.max_tokens
+        T = x.shape[0]
+        n_calls = max(1, -(-(rows if rows is not None else T) // step))
+        if n_calls == 1:
+            return self.method.apply_fused_ep(self, x, topk_ids, topk_w, comm)
+        outs = []
+        for i in range(n_calls):
+            lo, hi = min(T, i * step), min(T, (i + 1) * step)
+            outs.append(self.method.apply_fused_ep(self, x[lo:hi], topk_ids[lo:hi], topk_w[lo:hi], comm))
+        return torch.cat(outs, 0)

@@ -111,8 +111,9 @@ class EpState:
     """Heap regions and local scratch of the fused expert-parallel plane (one per EP heap).
 
     ``cap`` rows can be received per call; a call that would need more sets the device status word
-    (``ops.cuda.check_status``) and drops the excess rows.  The worst case is world * T_max * k rows;
-    the default keeps ``capacity_factor`` times the balanced load."""
+    (``ops.cuda.check_status``) and drops the excess rows.  The worst case is world * T_max * k rows
+    (every row of every rank routed to one owner: random-init routers of deep models come close); that
+    is the default, and a positive ``capacity_factor`` keeps that multiple of the balanced load instead."""
 
     def __init__(self, heap, max_tokens: int, top_k: int, hidden: int, inter: int, num_experts: int,
                  capacity_factor: float):
@@ -120,7 +121,7 @@ class EpState:
         world = heap.world
         self.heap, self.max_tokens, self.k, self.H, self.E = heap, max_tokens, top_k, hidden, num_experts
         worst = world * max_tokens * top_k
-        self.cap = int(min(worst, max(1024, capacity_factor * max_tokens * top_k)))
+        self.cap = worst if capacity_factor <= 0 else int(min(worst, max(1024, capacity_factor * max_tokens * top_k)))
         self.cnt = heap.alloc("ep_cnt", world * num_experts * 4)
         self.cnt_flag = heap.alloc("ep_cnt_flag", world * 4)
         self.data_flag = heap.alloc("ep_data_flag", world * 4)
@@ -154,7 +155,7 @@ class EpState:
     @staticmethod
     def heap_bytes(max_tokens, top_k, hidden, num_experts, world, capacity_factor) -> int:
         worst = world * max_tokens * top_k
-        cap = int(min(worst, max(1024, capacity_factor * max_tokens * top_k)))
+        cap = worst if capacity_factor <= 0 else int(min(worst, max(1024, capacity_factor * max_tokens * top_k)))
         return (cap * hidden * 2 + cap * 8 + max_tokens * top_k * hidden * 2 + world * num_experts * 4
                 + (1 << 20))
 

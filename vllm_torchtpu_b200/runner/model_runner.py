@@ -39,7 +39,7 @@ logger = init_logger(__name__)
 DEVICE_STATUS_NAMES = {1: "a GEMM consumer waited for a TMA stage", 2: "a TMA producer waited for a free stage",
                        3: "an epilogue waited for its accumulator", 4: "an MMA issuer waited for a free accumulator",
                        5: "a kernel waited for a flag of a peer GPU or of another CTA",
-                       6: "an index was out of range (bounds-checked build)",
+                       6: "an index was out of range, or a receive buffer of the expert-parallel plane overflowed",
                        7: "a kernel waited for its copies in flight"}
 
 
@@ -175,7 +175,8 @@ class ModelRunner:
         if self.is_cuda and st.expert_parallel and st.ep.size > 1 and getattr(self.mcfg, "num_experts", 0):
             from ..parallel.communicator import ensure_ep_heap
             # tokens are identical on the ranks of a TP group: each of them dispatches one slice
-            per_rank = -(-self.max_tokens // st.tp.size)
+            # longer steps go through the plane in several calls, which bounds the receive buffers
+            per_rank = min(-(-self.max_tokens // st.tp.size), envs.B200_MOE_EP_CALL_TOKENS)
             ensure_ep_heap(per_rank, self.mcfg.num_experts_per_tok, self.mcfg.hidden_size,
                            self.mcfg.moe_intermediate_size, self.mcfg.num_experts)
         logger.info("model %s loaded: %.2f GB weights on this rank in %.1fs", self.mcfg.name,
