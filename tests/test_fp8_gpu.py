@@ -144,3 +144,24 @@ def test_int8_w8a8_gemm_matches_reference(T, N, K):
     want = q8.int8_gemm_reference(x, wq, ws)
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2 * want.float().abs().max().item())
     assert cuda.check_status() == 0
+
+
+def test_fp8_per_tensor_linear_quantises_activations_in_one_kernel():
+    """Per-tensor weight scale, per-token activation scale: the kernel path against the same arithmetic in fp32."""
+    from vllm_torchtpu_b200.ops import launch_count
+    T, N, K = 77, 640, 1024
+    g = torch.Generator(device=DEV).manual_seed(11)
+    x = (torch.randn(T, K, device=DEV, generator=g) * 2).bfloat16()
+    w = torch.randn(N, K, device=DEV, generator=g) * 0.05
+    s = w.abs().max() / 448.0
+    wq = (w / s).clamp(-448, 448).to(torch.float8_e4m3fn)
+    before = launch_count()
+    y = cu().fp8_per_tensor_gemm(x, wq, s.reshape(1))
+    assert launch_count() - before == 2                     # activation quantisation + GEMM
+    torch.cuda.synchronize()
+    assert cu().check_status() == 0
+    xs = x.float().abs().amax(-1, keepdim=True).clamp_min(1e-12) / 448.0
+    xq = (x.float() / xs).clamp(-448, 448).to(torch.float8_e4m3fn)
+    want = (xq.float() @ wq.float().t()) * xs * s
+    err = (y.float() - want).abs().max().item()
+    assert err <= 2e-2 * want.abs().max().item() + 1e-2, err

@@ -545,6 +545,28 @@ __global__ void quant_rows_1x128_vec_kernel(const __nv_bfloat16* __restrict__ x,
   }
 }
 
+// x [T, K] bf16 -> xq [T, K] e4m3 with ONE scale per row (amax / 448), written `reps` times into
+// xs [T, reps] so that the block-scaled GEMM can consume it as its per-(row, K block) scale: one CTA per row
+__global__ void quant_act_rowwise_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_e4m3* __restrict__ xq,
+                                         float* __restrict__ xs, int K, int ldx, int reps) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) amax = fmaxf(amax, fabsf(__bfloat162float(x[(size_t)t * ldx + i])));
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = (threadIdx.x & 31) < (blockDim.x >> 5) ? red[threadIdx.x & 31] : 0.f;
+  amax = warp_max(amax);
+  const float scale = fmaxf(amax, 1e-12f) / 448.f;
+  const float inv = 1.f / scale;
+  for (int i = threadIdx.x; i < K; i += blockDim.x)
+    xq[(size_t)t * K + i] =
+        __nv_fp8_e4m3(fminf(fmaxf(__bfloat162float(x[(size_t)t * ldx + i]) * inv, -448.f), 448.f));
+  for (int i = threadIdx.x; i < reps; i += blockDim.x) xs[(size_t)t * reps + i] = scale;
+}
+
 // x [T, K] bf16 -> xq [T, K] int8 and xs [T] fp32 (amax / 127): one CTA per row
 __global__ void quant_act_int8_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ xq,
                                       float* __restrict__ xs, int K, int ldx) {
@@ -902,6 +924,14 @@ extern "C" int b200_grouped_gemm_fp8_block_routed(const void* Xq, const float* x
     case 64: return f8::launch<64>(tmW, tmX, p, num_sms, stream);
     default: return f8::launch<128>(tmW, tmX, p, num_sms, stream);
   }
+}
+
+extern "C" int b200_quant_act_rowwise(const void* x, void* xq, float* xs, int T, int K, int ldx, int reps,
+                                      cudaStream_t stream) {
+  if (T == 0) return 0;
+  f8::quant_act_rowwise_kernel<<<T, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_fp8_e4m3*)xq, xs, K, ldx, reps);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
 }
 
 extern "C" int b200_quant_act_int8(const void* x, void* xq, float* xs, int T, int K, int ldx, cudaStream_t stream) {

@@ -10,9 +10,15 @@ def create_connector(cfg, runner, **kw) -> Connector:
     name = (cfg.kv_transfer or {}).get("kv_connector")
     if name in ("B200P2PConnector", "B200HostConnector"):
         from .p2p_connector import create_p2p_connector
-        if name == "B200HostConnector":
+        if name == "B200HostConnector" and kw.get("transport") is None:
+            # same protocol, blocks handed over through this process's address space instead of CUDA IPC
+            # (producer and consumer engines in one process, or pools that live in host memory)
             from .transport import LocalTransport
-            kw.setdefault("transport", None)
+            engine_id = (cfg.kv_transfer or {}).get("engine_id")
+            if engine_id:
+                kw["transport"] = LocalTransport(engine_id)
+            else:
+                cfg.kv_transfer.setdefault("kv_connector_extra_config", {}).setdefault("transport", "local")
         return create_p2p_connector(cfg, runner, **kw)
     if name == "B200OffloadingConnector":
         from .offload import create_offloading_connector

@@ -122,9 +122,34 @@ def fp8_block_gemm_push(x, wq, w_scale_inv, heap):
     return _c.PendingReduce(heap, part, T, N, x.shape[:-1])
 
 
+def fp8_per_tensor_gemm(x, wq, w_scale, bias=None, ws_grid=None):
+    """W8A8 with one weight scale per tensor and one activation scale per token: the activation is
+    quantised by one kernel (row amax -> e4m3), the product runs on the block-scaled tcgen05 kernel
+    with both scales repeated over its K blocks (dequantisation happens block by block either way)."""
+    _c._require_bf16(x)
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    T, K = x2.shape
+    N = wq.shape[0]
+    kb = (K + 127) // 128
+    y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return y.reshape(*lead, N)
+    xq = torch.empty((T, K), dtype=FP8, device=x.device)
+    xs_b = torch.empty((T, kb), dtype=torch.float32, device=x.device)
+    _c._check(_c.lib().b200_quant_act_rowwise(_c._p(x2), _c._p(xq), _c._p(xs_b), c_int(T), c_int(K),
+                                              c_int(x2.stride(0)), c_int(kb), _c._stream()), "quant_act_rowwise")
+    count_launch()
+    if ws_grid is None:
+        ws_grid = w_scale.reshape(1, 1).float().expand((N + 127) // 128, kb).contiguous()
+    fp8_block_gemm_quantised(xq, xs_b, wq, ws_grid, y, bias)
+    return y.reshape(*lead, N)
+
+
 def fp8_rowwise_gemm(xq, xs, wq, w_scale, out_dtype):
-    """Per-tensor weight scale, per-row activation scale: expressed through the block kernel by
-    broadcasting both scales over the K blocks (dequant happens block by block either way)."""
+    """Operands already quantised (per-row activation scales xs [T], per-tensor weight scale)."""
     xq = xq.contiguous()
     T, K = xq.shape
     N = wq.shape[0]
@@ -132,11 +157,7 @@ def fp8_rowwise_gemm(xq, xs, wq, w_scale, out_dtype):
     xs_b = xs.reshape(T, 1).float().expand(T, kb).contiguous()
     ws_b = w_scale.reshape(1, 1).float().expand((N + 127) // 128, kb).contiguous()
     y = torch.empty((T, N), dtype=torch.bfloat16, device=xq.device)
-    ws = _c.Workspace.get(xq.device)
-    _c._check(_c.lib().b200_gemm_fp8_block(
-        _c._p(xq), _c._p(xs_b), _c._p(wq), _c._p(ws_b), _c._p(y), c_void_p(0), c_int(T), c_int(N),
-        c_int(K), c_int(y.stride(0)), _c._p(ws.status), c_int(_c._sms), _c._stream()), "gemm_fp8_block")
-    count_launch()
+    fp8_block_gemm_quantised(xq, xs_b, wq, ws_b, y)
     return y.to(out_dtype)
 
 

@@ -174,6 +174,12 @@ class Fp8PerTensorLinearMethod(LinearMethodBase):
             self._set(layer, w)
 
     def apply(self, layer, x, bias=None):
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            if not hasattr(layer, "_ws_grid"):       # the per-tensor scale repeated over the GEMM's block grid
+                N, K = layer.weight.shape
+                layer._ws_grid = layer.weight_scale.reshape(1, 1).float().expand(
+                    -(-N // 128), -(-K // 128)).contiguous()
+            return ops.cuda_ops().fp8_per_tensor_gemm(x, layer.weight, layer.weight_scale, bias, layer._ws_grid)
         xf = x.float()
         xs = xf.abs().amax(-1, keepdim=True).clamp_min(1e-12) / FP8_MAX
         xq = (xf / xs).clamp(-FP8_MAX, FP8_MAX).to(FP8)
