@@ -116,3 +116,34 @@ def test_deepseek_style_engine_runs_on_gpu_and_matches_dense_logits():
     graph = [o.outputs[0].token_ids for o in make().generate(prompts, sp)]
     assert eager == graph
     assert cuda.check_status() == 0
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_mla_absorb_and_unabsorb_match_einsum(interleaved):
+    """W_UK / W_UV as grouped GEMMs over the heads, rope of the rope dims, against fp32 einsum + the
+    reference rotary embedding."""
+    from vllm_torchtpu_b200.ops import cuda
+    from vllm_torchtpu_b200.ops import reference as ref
+    T, H, nope, rope, L, v = 37, 16, 128, 64, 512, 128
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(T, H, nope + rope, device="cuda", generator=g).bfloat16()
+    kv = torch.randn(T, L + rope, device="cuda", generator=g).bfloat16()
+    w_uk = (torch.randn(H, nope, L, device="cuda", generator=g) * 0.05).bfloat16()
+    w_uv = (torch.randn(H, L, v, device="cuda", generator=g) * 0.05).bfloat16()
+    pos = torch.randint(0, 4000, (T,), device="cuda", generator=g, dtype=torch.int32)
+    inv_freq = (1.0 / (10000 ** (torch.arange(0, rope, 2, device="cuda").float() / rope))).contiguous()
+    q_latent, k_pe = cuda.mla_absorb(q, kv, pos, inv_freq, w_uk.transpose(1, 2).contiguous(), nope, rope, L,
+                                     interleaved)
+    torch.cuda.synchronize()
+    want_ql = torch.einsum("thn,hnl->thl", q[..., :nope].float(), w_uk.float())
+    want_qpe = ref.apply_rope(q[..., nope:], pos, inv_freq, interleaved).float()
+    want_kpe = ref.apply_rope(kv[:, L:].reshape(T, 1, rope), pos, inv_freq, interleaved).reshape(T, rope).float()
+    assert (q_latent[..., :L].float() - want_ql).abs().max() <= 2e-2 * want_ql.abs().max() + 1e-2
+    assert (q_latent[..., L:].float() - want_qpe).abs().max() <= 3e-2
+    assert (k_pe.float() - want_kpe).abs().max() <= 3e-2
+    o_lat = torch.randn(T, H, L, device="cuda", generator=g).bfloat16()
+    y = cuda.mla_unabsorb(o_lat, w_uv.transpose(1, 2).contiguous())
+    torch.cuda.synchronize()
+    want = torch.einsum("thl,hlv->thv", o_lat.float(), w_uv.float()).reshape(T, H * v)
+    assert (y.float() - want).abs().max() <= 2e-2 * want.abs().max() + 1e-2
+    assert cuda.check_status() == 0

@@ -268,7 +268,90 @@ __global__ void mla_write_cache_kernel(__nv_bfloat16* __restrict__ cache, const 
 }  // namespace mla
 }  // namespace b200
 
+namespace b200 {
+namespace mla {
+
+// dst[b * dst_sb + a * dst_sa + d] = src[a * src_sa + b * src_sb + d] for a < A, b < B, d < D (elements;
+// D and all strides multiples of 8 so that the copy runs in 16-byte pieces).  Turns [T, H, D] slices into
+// the head-major [H, T, D] rows the grouped GEMM wants (heads as groups) and back.
+__global__ void permute_rows_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int A,
+                                    int B, int D8, long long src_sa, long long src_sb, long long dst_sa,
+                                    long long dst_sb) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long total = (long long)A * B * D8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int d = (int)(i % D8);
+    const long long ab = i / D8;
+    const int b = (int)(ab % B);
+    const int a = (int)(ab / B);
+    const uint4 v = *reinterpret_cast<const uint4*>(src + a * src_sa + b * src_sb + d * 8);
+    *reinterpret_cast<uint4*>(dst + a * dst_sa + b * dst_sb + d * 8) = v;
+  }
+}
+
+// Rotary embedding of `pairs` dimension pairs of src[t, h, :] (strides in elements) written to dst[t, h, :]:
+// interleaved pairs (2i, 2i+1) or split halves (i, i + pairs), angles position * inv_freq[i] in fp32.
+__global__ void rope_rows_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                 const int* __restrict__ positions, const float* __restrict__ inv_freq, int T, int H,
+                                 int pairs, int interleaved, long long src_st, long long src_sh, long long dst_st,
+                                 long long dst_sh) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long total = (long long)T * H * pairs;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int j = (int)(i % pairs);
+    const long long th = i / pairs;
+    const int h = (int)(th % H);
+    const int t = (int)(th / H);
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
+    const int i0 = interleaved ? 2 * j : j, i1 = interleaved ? 2 * j + 1 : j + pairs;
+    const __nv_bfloat16* s = src + t * src_st + h * src_sh;
+    __nv_bfloat16* d = dst + t * dst_st + h * dst_sh;
+    const float x0 = __bfloat162float(s[i0]), x1 = __bfloat162float(s[i1]);
+    d[i0] = __float2bfloat16(x0 * cs - x1 * sn);
+    d[i1] = __float2bfloat16(x1 * cs + x0 * sn);
+  }
+}
+
+}  // namespace mla
+}  // namespace b200
+
 using namespace b200;
+
+extern "C" int b200_permute_rows(const void* src, void* dst, int A, int B, int D, long long src_sa, long long src_sb,
+                                 long long dst_sa, long long dst_sb, cudaStream_t stream) {
+  if (A <= 0 || B <= 0 || D <= 0) return 0;
+  if (D % 8 || src_sa % 8 || src_sb % 8 || dst_sa % 8 || dst_sb % 8 || (reinterpret_cast<uintptr_t>(src) & 15) ||
+      (reinterpret_cast<uintptr_t>(dst) & 15)) {
+    b200_set_last_error("permute_rows: D, the strides and both addresses must be multiples of 8 elements",
+                        __FILE__, __LINE__);
+    return -1;
+  }
+  const long long total = (long long)A * B * (D / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  B200_CUDA_CHECK(launch_pdl(mla::permute_rows_kernel, dim3((unsigned)blocks), dim3(256), (size_t)0, stream,
+                             (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, A, B, D / 8, src_sa, src_sb, dst_sa,
+                             dst_sb));
+  return 0;
+}
+
+extern "C" int b200_rope_rows(const void* src, void* dst, const int* positions, const float* inv_freq, int T, int H,
+                              int pairs, int interleaved, long long src_st, long long src_sh, long long dst_st,
+                              long long dst_sh, cudaStream_t stream) {
+  if (T <= 0 || H <= 0 || pairs <= 0) return 0;
+  const long long total = (long long)T * H * pairs;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  B200_CUDA_CHECK(launch_pdl(mla::rope_rows_kernel, dim3((unsigned)blocks), dim3(256), (size_t)0, stream,
+                             (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, positions, inv_freq, T, H, pairs,
+                             interleaved, src_st, src_sh, dst_st, dst_sh));
+  return 0;
+}
 
 extern "C" int b200_mla_write_cache(void* cache, const void* kv_c, const void* k_pe, const int* slots, int T, int L,
                                     int R, int ld_c, int ld_pe, long long num_slots, cudaStream_t stream) {

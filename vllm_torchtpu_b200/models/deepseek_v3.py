@@ -94,6 +94,9 @@ class MLAAttention:
         w = w[r * self.H:(r + 1) * self.H]
         self.w_uk = w[:, :self.nope, :].contiguous()                         # [H, nope, L]
         self.w_uv = w[:, self.nope:, :].transpose(1, 2).contiguous()         # [H, L, v]
+        # K-major copies for the grouped GEMM (heads as groups): [H, L, nope] and [H, v, L]
+        self.w_uk_t = self.w_uk.transpose(1, 2).contiguous()
+        self.w_uv_t = self.w_uv.transpose(1, 2).contiguous()
 
     def weight_bytes(self):
         n = sum(l.weight_bytes() for l in self.linears())
@@ -111,6 +114,15 @@ class MLAAttention:
         q = q.view(T, self.H, self.nope + self.rope)
         kv = self.kv_a(x)
         kv_c = ops.rms_norm(kv[:, :self.kv_lora].contiguous(), self.kv_a_ln, self.eps)
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.w_uk_t.dtype == torch.bfloat16 and T > 0:
+            # absorbed form on the package's kernels: W_UK / W_UV as grouped tcgen05 GEMMs over the heads
+            cu = ops.cuda_ops()
+            q_latent, k_pe = cu.mla_absorb(q.contiguous(), kv, meta.positions, self.inv_freq, self.w_uk_t,
+                                           self.nope, self.rope, self.kv_lora, self.cfg.rope_interleaved)
+            ops.mla_write_cache(cache, kv_c, k_pe, meta.slot_mapping)
+            topk = self._index(x, cache, meta) if self.index_topk else None
+            o_lat = ops.mla_paged_attention(q_latent, cache, meta, self.scale, self.kv_lora, topk_indices=topk)
+            return self.o(cu.mla_unabsorb(o_lat, self.w_uv_t))
         k_pe = kv[:, self.kv_lora:].reshape(T, 1, self.rope)
         q_pe = ops.ref.apply_rope(q[..., self.nope:], meta.positions, self.inv_freq, self.cfg.rope_interleaved)
         k_pe = ops.ref.apply_rope(k_pe, meta.positions, self.inv_freq, self.cfg.rope_interleaved).reshape(T, self.rope)
