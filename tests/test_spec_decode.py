@@ -96,3 +96,35 @@ def test_engine_with_draft_head_and_adaptive_verification_is_lossless():
     with pytest.raises(ValueError):
         LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False,
             speculative_config={"method": "ngram", "enable_adaptive_verification": True})
+
+
+def test_medusa_heads_load_from_a_checkpoint_and_reproduce_plain_decoding(tmp_path):
+    """Heads written as a Medusa checkpoint (identity-like blocks + the target's own projection) draft the
+    token the target would produce next from the same hidden state, so some drafts are accepted, and the
+    output equals plain greedy decoding whatever is accepted."""
+    import torch
+    from safetensors.torch import save_file
+
+    from vllm_torchtpu_b200 import SamplingParams
+    from vllm_torchtpu_b200.engine.llm import LLM
+    prompts = [[5, 6, 7, 8, 9, 10, 11], [21, 22, 23, 24], [3, 4, 9, 10, 2, 17]]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    kw = dict(device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    plain_llm = LLM("tiny-llama", **kw)
+    plain = [o.outputs[0].token_ids for o in plain_llm.generate(prompts, sp)]
+    H = plain_llm.engine.cfg.model.hidden_size
+    lm_head = plain_llm.engine.runner.model.lm_head
+    tensors = {}
+    for i in range(2):
+        tensors[f"medusa_heads.{i}.0.linear.weight"] = torch.zeros(H, H)
+        tensors[f"medusa_heads.{i}.0.linear.bias"] = torch.zeros(H)
+        tensors[f"medusa_heads.{i}.1.weight"] = lm_head.float().clone()
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    spec_llm = LLM("tiny-llama", speculative_config={"method": "medusa", "num_speculative_tokens": 2,
+                                                      "model": str(tmp_path)}, **kw)
+    got = [o.outputs[0].token_ids for o in spec_llm.generate(prompts, sp)]
+    assert got == plain
+    prop = spec_llm.engine.spec
+    assert prop.num_speculative_tokens == 2 and prop.stats["proposed"] > 0
+    assert len(prop.blocks) == 2 and prop.heads[0] is not None
+    assert spec_llm.engine.runner.stats.get("spec_drafted", 0) > 0

@@ -259,9 +259,189 @@ __global__ void philox_uniform_kernel(float* out, int R, int V, unsigned long lo
     out[i] = uniform_at(seed, step, (int)(i / V), (int)(i % V));
 }
 
+// ------------------------------------------------------------------ speculative decoding
+// Acceptance of drafts from a deterministic proposer (n-gram, greedy draft head).  The target's own sampler
+// has drawn one token per verified row; a draft is kept while it equals that token, which is rejection
+// sampling against a one-hot draft distribution (accept with p(x), else the draw from p is the replacement).
+// Request r owns rows [off_r, off_r + k_r] of `target` (off_r = sum of k_i + 1 before it) and its drafts are
+// the step's input tokens behind the last known one: input_ids[qsl[r+1] - k_r + i].
+// out [R, kmax + 1] (unused entries -1), count [R].  One thread per request.
+__global__ void spec_accept_kernel(const int* __restrict__ target, const int* __restrict__ input_ids,
+                                   const int* __restrict__ qsl, const int* __restrict__ spec_k, int R, int kmax,
+                                   int* __restrict__ out, int* __restrict__ count) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= R) return;
+  int off = 0;
+  for (int i = 0; i < r; ++i) off += spec_k[i] + 1;
+  const int k = min(spec_k[r], kmax);
+  const int* draft = input_ids + qsl[r + 1] - k;
+  int n = 0;
+  bool all = true;
+  for (int i = 0; i < k; ++i) {
+    const int t = target[off + i];
+    out[r * (kmax + 1) + n++] = t;
+    if (draft[i] != t) { all = false; break; }
+  }
+  if (all) out[r * (kmax + 1) + n++] = target[off + k];
+  count[r] = n;
+  for (int i = n; i <= kmax; ++i) out[r * (kmax + 1) + i] = -1;
+}
+
+__device__ __forceinline__ float block_max_f(float v, float* red) {
+  v = warp_max(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+// Rejection sampling against a drafter that SAMPLED its tokens from q (draft_probs [R, kmax, V], or null for
+// a one-hot q).  Row i of request r: p = softmax(logits / T_r); draft x is kept when u_i * q(x) <= p(x);
+// at the first rejection the replacement is drawn from normalise(max(p - q, 0)) by inverse CDF with
+// u'_i, and when every draft is kept a bonus token is drawn from the last row.  T_r == 0: keep while
+// x == argmax, replacement / bonus = argmax.  One CTA per request; every pass re-reads the row (L2 resident).
+template <typename T>
+__global__ void rejection_sample_kernel(const T* __restrict__ logits, int ld, int V, const int* __restrict__ drafts,
+                                        const float* __restrict__ draft_probs, const int* __restrict__ spec_k,
+                                        const float* __restrict__ temperature, const float* __restrict__ uniform,
+                                        const float* __restrict__ resample_uniform, int kmax,
+                                        int* __restrict__ out, int* __restrict__ count) {
+  __shared__ float red[32];
+  __shared__ float seg[SAMPLE_THREADS];
+  __shared__ int s_pick;
+  const int r = blockIdx.x;
+  int off = 0;
+  for (int i = 0; i < r; ++i) off += spec_k[i] + 1;
+  const int k = min(spec_k[r], kmax);
+  const float temp = temperature[r];
+  const int per = (V + blockDim.x - 1) / blockDim.x;
+  const int v0 = threadIdx.x * per, v1 = min(V, v0 + per);
+  int n = 0;
+  for (int i = 0; i <= k; ++i) {
+    const T* row = logits + (size_t)(off + i) * ld;
+    const bool bonus = i == k;
+    const int x = bonus ? -1 : drafts[r * kmax + i];
+    const float* q = (draft_probs != nullptr && !bonus) ? draft_probs + ((size_t)r * kmax + i) * V : nullptr;
+    // row maximum (and its first index, for temperature 0)
+    float m = -INFINITY;
+    int mi = 0x7fffffff;
+    for (int v = v0; v < v1; ++v) {
+      const float l = load_logit(row, v);
+      if (l > m) { m = l; mi = v; }
+    }
+    const float gmax = block_max_f(m, red);
+    if (temp <= 0.f) {
+      // greedy: smallest index that attains the maximum
+      __syncthreads();
+      if (threadIdx.x == 0) s_pick = 0x7fffffff;
+      __syncthreads();
+      if (m == gmax) atomicMin(&s_pick, mi);
+      __syncthreads();
+      const int am = s_pick;
+      if (threadIdx.x == 0) out[r * (kmax + 1) + n] = am;
+      ++n;
+      if (bonus || x != am) break;
+      continue;
+    }
+    const float inv_t = 1.f / temp;
+    float z = 0.f;
+    for (int v = v0; v < v1; ++v) z += __expf((load_logit(row, v) - gmax) * inv_t);
+    const float Z = block_sum_f(z, red);
+    bool accept = false;
+    if (!bonus) {
+      const float px = __expf((load_logit(row, x) - gmax) * inv_t) / Z;
+      const float qx = q != nullptr ? q[x] : 1.f;
+      accept = qx > 0.f && uniform[r * kmax + i] * qx <= px;
+      if (accept) {
+        if (threadIdx.x == 0) out[r * (kmax + 1) + n] = x;
+        ++n;
+        continue;
+      }
+    }
+    // draw from the residual (or from p itself for the bonus token) by inverse CDF
+    float mine = 0.f;
+    for (int v = v0; v < v1; ++v) {
+      const float pv = __expf((load_logit(row, v) - gmax) * inv_t) / Z;
+      const float rv = bonus ? pv : fmaxf(pv - (q != nullptr ? q[v] : (v == x ? 1.f : 0.f)), 0.f);
+      mine += rv;
+    }
+    __syncthreads();
+    seg[threadIdx.x] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float total = 0.f;
+      for (int t = 0; t < (int)blockDim.x; ++t) total += seg[t];
+      const float want = resample_uniform[r * (kmax + 1) + i] * total;
+      float c = 0.f;
+      int pick = -1, last_nonzero = -1;
+      for (int t = 0; t < (int)blockDim.x && pick < 0; ++t) {
+        if (seg[t] > 0.f) last_nonzero = t;
+        if (c + seg[t] >= want && seg[t] > 0.f) {
+          // walk this thread's segment
+          const int a = t * per, b = min(V, a + per);
+          for (int v = a; v < b; ++v) {
+            const float pv = __expf((load_logit(row, v) - gmax) * inv_t) / Z;
+            const float rv = bonus ? pv : fmaxf(pv - (q != nullptr ? q[v] : (v == x ? 1.f : 0.f)), 0.f);
+            if (rv > 0.f) {
+              pick = v;
+              c += rv;
+              if (c >= want) break;
+            }
+          }
+        } else {
+          c += seg[t];
+        }
+      }
+      if (pick < 0) {
+        // an all-zero residual (p == q): fall back to the row's most likely token
+        pick = last_nonzero >= 0 ? min(V - 1, last_nonzero * per) : 0;
+        float best = -INFINITY;
+        for (int v = 0; v < V; ++v) {
+          const float l = load_logit(row, v);
+          if (l > best) { best = l; pick = v; }
+        }
+      }
+      out[r * (kmax + 1) + n] = pick;
+    }
+    ++n;
+    break;
+  }
+  if (threadIdx.x == 0) {
+    count[r] = n;
+    for (int i = n; i <= kmax; ++i) out[r * (kmax + 1) + i] = -1;
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_spec_accept(const int* target, const int* input_ids, const int* qsl, const int* spec_k, int R,
+                                int kmax, int* out, int* count, cudaStream_t stream) {
+  if (R == 0) return 0;
+  spec_accept_kernel<<<(R + 127) / 128, 128, 0, stream>>>(target, input_ids, qsl, spec_k, R, kmax, out, count);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_rejection_sample(const void* logits, int dtype, int R, int V, int ld, const int* drafts,
+                                     const float* draft_probs, const int* spec_k, const float* temperature,
+                                     const float* uniform, const float* resample_uniform, int kmax, int* out,
+                                     int* count, cudaStream_t stream) {
+  if (R == 0) return 0;
+  if (dtype == 0)
+    rejection_sample_kernel<__nv_bfloat16><<<R, SAMPLE_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)logits, ld, V, drafts, draft_probs, spec_k, temperature, uniform, resample_uniform,
+        kmax, out, count);
+  else
+    rejection_sample_kernel<float><<<R, SAMPLE_THREADS, 0, stream>>>(
+        (const float*)logits, ld, V, drafts, draft_probs, spec_k, temperature, uniform, resample_uniform, kmax,
+        out, count);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
 
 // dtype: 0 = bf16 logits, 1 = fp32 logits
 extern "C" int b200_argmax(const void* logits, int dtype, int R, int V, int ld, int* out, cudaStream_t stream) {

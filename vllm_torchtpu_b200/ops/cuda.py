@@ -396,6 +396,33 @@ def sample(logits, temperature, top_k, top_p, uniform=None, all_greedy=False, se
     return out
 
 
+def spec_accept(target_tokens, input_ids, query_start_loc, spec_k, R: int, kmax: int):
+    """Device-side acceptance of deterministic drafts (see ``spec_accept_kernel``): returns
+    (tokens [R, kmax + 1] padded with -1, count [R])."""
+    out = torch.empty((R, kmax + 1), dtype=torch.int32, device=target_tokens.device)
+    cnt = torch.empty(R, dtype=torch.int32, device=target_tokens.device)
+    _check(lib().b200_spec_accept(_p(target_tokens), _p(input_ids), _p(query_start_loc), _p(spec_k), c_int(R),
+                                  c_int(kmax), _p(out), _p(cnt), _stream()), "spec_accept")
+    count_launch()
+    return out, cnt
+
+
+def rejection_sample(logits, drafts, draft_probs, spec_k, temperature, uniform, resample_uniform):
+    """Rejection sampling of sampled drafts on the device.  logits [sum(k_i + 1), V] (rows of request r are
+    consecutive), drafts [R, kmax] int32, draft_probs [R, kmax, V] fp32 or None (one-hot), spec_k [R] int32,
+    temperature [R], uniform [R, kmax], resample_uniform [R, kmax + 1] -> (tokens [R, kmax + 1], count [R])."""
+    R, kmax = drafts.shape
+    V = logits.shape[1]
+    out = torch.empty((R, kmax + 1), dtype=torch.int32, device=logits.device)
+    cnt = torch.empty(R, dtype=torch.int32, device=logits.device)
+    _check(lib().b200_rejection_sample(
+        _p(logits), c_int(_logit_dtype(logits)), c_int(R), c_int(V), c_int(logits.stride(0)), _p(drafts),
+        _p(draft_probs), _p(spec_k), _p(temperature), _p(uniform), _p(resample_uniform), c_int(kmax), _p(out),
+        _p(cnt), _stream()), "rejection_sample")
+    count_launch()
+    return out, cnt
+
+
 def gather_logprobs(logits, token_ids, k: int):
     R, V = logits.shape
     dev = logits.device

@@ -106,6 +106,20 @@ class StepResult:
         # a draft is kept while it equals the target's token at its position
         from ..sample.rejection_sampler import greedy_accept
         spec_k, drafts, stats = self.extra["spec_k"], self.extra["drafts"], self.extra["stats"]
+        kmax = self.extra.get("device_accept")
+        if kmax is not None:
+            # the acceptance ran on the device: counts [R] followed by tokens [R, kmax + 1]
+            n = self.num_reqs
+            flat = self.tokens_host[: n * (kmax + 2)].tolist()
+            out = {}
+            for i, (rid, k, s) in enumerate(zip(self.req_ids, spec_k.tolist(), self.samples)):
+                if s:
+                    base = n + i * (kmax + 1)
+                    acc = flat[base:base + flat[i]]
+                    out[rid] = acc
+                    stats["spec_accepted"] = stats.get("spec_accepted", 0) + len(acc) - 1
+                    stats["spec_drafted"] = stats.get("spec_drafted", 0) + k
+            return out
         rows = self.tokens_host[: int(spec_k.sum()) + self.num_reqs].tolist()
         out, off = {}, 0
         for rid, k, d, s in zip(self.req_ids, spec_k.tolist(), drafts, self.samples):
@@ -187,6 +201,7 @@ class ModelRunner:
         self.bufs_prefill = StepBuffers(self.max_tokens, self.max_reqs, mb, self.device)
         self.bufs_decode = StepBuffers(self.max_reqs, self.max_reqs, mb, self.device)
         self.last_tokens = torch.zeros(self.max_reqs, dtype=torch.int32, device=self.device)
+        self._spec_k_dev = torch.zeros(self.max_reqs, dtype=torch.int32, device=self.device)
         self.tokens_host = [torch.zeros(self.max_reqs * 9, dtype=torch.int32, pin_memory=self.is_cuda)
                             for _ in range(4)]
         self.status_host = [torch.zeros(1, dtype=torch.int32, pin_memory=self.is_cuda) for _ in range(4)]
@@ -688,6 +703,17 @@ class ModelRunner:
         self._tok_ring = (self._tok_ring + 1) % len(self.tokens_host)
         ev = None
         rows = p["L_pad"] if p.get("has_spec") else R
+        device_accept = None
+        if p.get("has_spec") and self.is_cuda and envs.B200_DEVICE_SPEC_ACCEPT:
+            kmax = int(p["spec_k"].max())
+            if 0 < kmax <= 7:
+                # drafts are judged where the target tokens are: the host reads counts and accepted tokens
+                k_dev = self._spec_k_dev[:n]
+                k_dev.copy_(torch.from_numpy(np.ascontiguousarray(p["spec_k"], dtype=np.int32)), non_blocking=True)
+                acc, cnt = ops.cuda_ops().spec_accept(tokens, bufs.input_ids, meta.query_start_loc, k_dev, n, kmax)
+                tokens = torch.cat([cnt, acc.flatten()])
+                rows = n * (kmax + 2)
+                device_accept = kmax
         if self.is_cuda:
             host[:rows].copy_(tokens[:rows], non_blocking=True)
             # the status word of the bounded device waits travels with the tokens: a kernel that gave
@@ -709,6 +735,8 @@ class ModelRunner:
         if p.get("has_spec"):
             res.extra = {"spec_k": p["spec_k"], "drafts": [list(s.spec_token_ids) for s in p["scheds"]],
                          "stats": self.stats}
+            if device_accept is not None:
+                res.extra["device_accept"] = device_accept
         return res
 
     def note_sampled(self, result: dict) -> None:

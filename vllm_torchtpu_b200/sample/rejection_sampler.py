@@ -5,6 +5,10 @@ by the target token; if all k drafts are kept a bonus token is appended.
 Random: draft token x_i (drawn from q_i) is kept with probability min(1, p_i(x_i) / q_i(x_i)); at
 the first rejection a token is drawn from normalise(max(p_i - q_i, 0)); all kept -> bonus token
 from p_{k}.  Deterministic drafters (n-gram) have one-hot q.
+The functions below state the rule on the host (the CPU path and the oracle of the tests); on a GPU the
+same rules run as kernels: ``ops.cuda.spec_accept`` (deterministic drafts, judged against the tokens the
+target's sampler drew; the runner's verification steps use it) and ``ops.cuda.rejection_sample`` (sampled
+drafts with their distributions).
 (reference: src/vllm_torchtpu/layers/adapter/sample/rejection_sampler.py:35-686)"""
 from __future__ import annotations
 

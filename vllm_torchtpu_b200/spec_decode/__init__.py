@@ -1,9 +1,11 @@
 """Speculative decoding: drafters propose k tokens, the target model verifies them in one step
 and a rejection sampler decides how many are kept.
 
-Drafters: ``ngram`` (prompt lookup), ``suffix`` (longest-suffix match over prompt + output),
-``eagle3`` / ``mtp`` (a small draft head run on the target's hidden state), ``dflash`` /
-``dspark`` (parallel block drafting) share the draft-head proposer.
+Drafters: ``ngram`` (prompt lookup), ``suffix`` (longest-suffix match over prompt + output), ``medusa``
+(K residual-block heads on the target's hidden state, loaded from a checkpoint and run batched on the
+device).  ``eagle3`` / ``mtp`` / ``dflash`` / ``dspark`` select a toy stand-in: a random one-matrix
+recurrent head that accepts next to nothing and exists to exercise the hidden-state hand-off; the
+attention layer of those drafters is not built.
 (reference: src/vllm_torchtpu/spec_decode/, docs/user_guide/speculative_decoding.md:5-16)"""
 from __future__ import annotations
 
@@ -16,6 +18,9 @@ def create_proposer(cfg, runner):
         from .ngram import NgramProposer
         return NgramProposer(k, int(sc.get("prompt_lookup_min", 2)), int(sc.get("prompt_lookup_max", 4)),
                              suffix=(method == "suffix"))
+    if method == "medusa":
+        from .medusa import MedusaProposer
+        return MedusaProposer(cfg, runner, k, sc.get("model"), int(sc.get("num_hidden_layers", 1)))
     if method in ("eagle3", "mtp", "dflash", "dspark"):
         from .draft_head import DraftHeadProposer
         return DraftHeadProposer(cfg, runner, k, method)
