@@ -117,3 +117,15 @@ def test_vocab_parallel_argmax_exchange():
     got = cuda_tp.select_best(torch.stack(vals).contiguous(), torch.stack(idxs).contiguous(), shard)
     want = logits.float().argmax(-1)
     assert torch.equal(got.long(), want) and int(got[3]) == 100
+
+
+def test_bounds_checked_attention_library_counts_bad_block_ids():
+    """The attention kernels built with -DB200_BOUNDS_CHECK: clean tables count nothing, an id outside the
+    pool is clamped and counted (a child process, since the library is chosen when it is first loaded)."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    r = subprocess.run([sys.executable, os.path.join(here, "workers", "bounds_check_worker.py")],
+                       capture_output=True, text=True, timeout=240)
+    assert "BOUNDS_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

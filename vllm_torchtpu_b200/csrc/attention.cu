@@ -248,7 +248,10 @@ __global__ void __launch_bounds__(128, 2) attn_decode_kernel(const AttnParams p)
       bt_reg = (page + lane <= page_hi) ? bt[page + lane] : 0;
     }
     long long blk = __shfl_sync(0xffffffffu, bt_reg, page - bt_base);
-    if (blk < 0 || blk >= p.num_blocks) blk = 0;
+    if (blk < 0 || blk >= p.num_blocks || page >= p.max_blocks) {
+      if (lane == 0) B200_NOTE_BAD_INDEX();
+      blk = 0;
+    }
     const size_t ko = (((size_t)blk * 2 + 0) * p.Hkv + h) * head_stride + (size_t)off * D;
     const size_t vo = (((size_t)blk * 2 + 1) * p.Hkv + h) * head_stride + (size_t)off * D;
     const uint32_t sb = wbase + stage * STAGE_BYTES;
@@ -517,8 +520,11 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
       const int tok = tok0 + g * 16;
       if (tok >= kv_end) break;
       const int page = tok / p.block_size, off = tok - page * p.block_size;
-      long long blk = bt[page];
-      if (blk < 0 || blk >= p.num_blocks) blk = 0;
+      long long blk = page < p.max_blocks ? bt[page] : -1;
+      if (blk < 0 || blk >= p.num_blocks) {
+        if (threadIdx.x == 0) B200_NOTE_BAD_INDEX();
+        blk = 0;
+      }
       const size_t ko = (((size_t)blk * 2 + 0) * p.Hkv + h) * head_stride + (size_t)off * D;
       const size_t vo = (((size_t)blk * 2 + 1) * p.Hkv + h) * head_stride + (size_t)off * D;
       if constexpr (FP8) {
@@ -973,5 +979,12 @@ extern "C" int b200_attn_decode_static(const void* q, const void* kv, void* out,
   if (D == 128) attn_decode_kernel<128><<<grid, 128, kDecodeSmem128, stream>>>(p);
   else attn_decode_kernel<64><<<grid, 128, kDecodeSmem64, stream>>>(p);
   B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// Number of out-of-range block ids / page indices the attention kernels of this file met since the last
+// call (always 0 unless built with -DB200_BOUNDS_CHECK); the counter is reset.
+extern "C" int b200_bad_index_count_attention(unsigned int* out) {
+  B200_TAKE_BAD_INDEX_COUNT(out);
   return 0;
 }

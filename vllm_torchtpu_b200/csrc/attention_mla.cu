@@ -124,9 +124,13 @@ __global__ void __launch_bounds__(128) mla_attn_kernel(const Params p) {
       long long blk = 0;
       int off = 0;
       if (ok) {
-        blk = bt[pos / p.block_size];
+        const int page = pos / p.block_size;
+        blk = page < p.max_blocks ? bt[page] : -1;
         off = pos % p.block_size;
-        if (blk < 0 || blk >= p.num_blocks) blk = 0;
+        if (blk < 0 || blk >= p.num_blocks) {
+          B200_NOTE_BAD_INDEX();
+          blk = 0;
+        }
       }
       s_ptr[stage][threadIdx.x] = p.cache + ((size_t)blk * p.block_size + off) * p.Dq;
       s_valid[stage][threadIdx.x] = ok ? 1 : 0;
@@ -395,5 +399,11 @@ extern "C" int b200_mla_attention(const void* q, const void* cache, void* out, f
   else if (L == 128) MLA_LAUNCH(32);
   else MLA_LAUNCH(16);
 #undef MLA_LAUNCH
+  return 0;
+}
+
+// see b200_bad_index_count_attention
+extern "C" int b200_bad_index_count_attention_mla(unsigned int* out) {
+  B200_TAKE_BAD_INDEX_COUNT(out);
   return 0;
 }

@@ -178,8 +178,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           if (tok < kv_end) {
             const int page = tok / p.block_size;
             off = tok - page * p.block_size;
-            blk = bt[page];
-            if (blk < 0 || blk >= p.num_blocks) blk = 0;
+            blk = page < p.max_blocks ? bt[page] : -1;
+            if (blk < 0 || blk >= p.num_blocks) {
+              B200_NOTE_BAD_INDEX();
+              blk = 0;
+            }
           }
           row = ((blk * 2 + kv) * p.Hkv + h) * p.block_size + off;     // cache as [(blocks, 2, Hkv, bs), D]
         }
@@ -482,5 +485,11 @@ extern "C" int b200_attn_prefill_tc(const void* q, const void* kv, void* out, fl
   dim3 grid(Hkv, tiles);
   B200_CUDA_CHECK(launch_pdl(fa::attn_prefill_tc_kernel, grid, dim3(fa::NUM_THREADS), (size_t)fa::SMEM_TOTAL, stream,
                              tmQ, tmKV, p));
+  return 0;
+}
+
+// see b200_bad_index_count_attention
+extern "C" int b200_bad_index_count_attention_tc(unsigned int* out) {
+  B200_TAKE_BAD_INDEX_COUNT(out);
   return 0;
 }

@@ -30,6 +30,23 @@ enum : int {
   ST_TIMEOUT_DRAIN = 7,
 };
 
+// Bounds-checked build (-DB200_BOUNDS_CHECK): the attention kernels always clamp a block id that falls
+// outside the pool; this build also counts such ids, and page indices past the end of a block-table row,
+// per translation unit, so that tests can assert that none occurred.
+#ifdef B200_BOUNDS_CHECK
+static __device__ unsigned int b200_bad_index_count = 0;
+#define B200_NOTE_BAD_INDEX() atomicAdd(&b200_bad_index_count, 1u)
+#define B200_TAKE_BAD_INDEX_COUNT(out)                                                          \
+  do {                                                                                          \
+    unsigned int _zero = 0;                                                                     \
+    if (cudaMemcpyFromSymbol((out), b200_bad_index_count, sizeof(unsigned int)) != cudaSuccess) return -1; \
+    if (cudaMemcpyToSymbol(b200_bad_index_count, &_zero, sizeof(unsigned int)) != cudaSuccess) return -1;  \
+  } while (0)
+#else
+#define B200_NOTE_BAD_INDEX() ((void)0)
+#define B200_TAKE_BAD_INDEX_COUNT(out) (*(out) = 0u)
+#endif
+
 #ifndef B200_WAIT_LIMIT_NS
 #define B200_WAIT_LIMIT_NS 1000000000ull     // one second
 #endif

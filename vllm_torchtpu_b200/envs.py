@@ -93,6 +93,8 @@ _decl("B200_TP_ONE_SHOT_BYTES", int, 4 * 2**20,
 _decl("B200_TP_DEFER_REDUCE", bool, True,
       "small row-parallel outputs are pushed to every rank and summed inside the following add+RMSNorm kernel")
 _decl("B200_SYMM_HEAP_MB", int, 512, "size of the per-rank symmetric heap")
+_decl("B200_BOUNDS_CHECK", bool, False,
+      "load the attention kernels from the bounds-checked library (out-of-range block ids are counted)")
 _decl("B200_DEVICE_SPEC_ACCEPT", bool, True, "speculative decoding: judge the drafts on the device")
 _decl("B200_FP8_ROWS_MIN_TILES", int, 96,
       "fp8 block GEMM: use the token-major kernel from this many 128x256 output tiles (-1: never)")

@@ -21,6 +21,33 @@ _lib = None
 _sms = 148
 
 
+class _Overlay:
+    """Symbols of ``over`` where it defines them, of ``main`` otherwise."""
+
+    def __init__(self, main, over):
+        self._main, self._over = main, over
+
+    def __getattr__(self, name):
+        try:
+            f = getattr(self._over, name)
+        except AttributeError:
+            f = getattr(self._main, name)
+        setattr(self, name, f)
+        return f
+
+
+def bad_index_count() -> int:
+    """Out-of-range block ids / page indices seen by the attention kernels since the last call (counted only
+    by the bounds-checked library, ``B200_BOUNDS_CHECK=1``)."""
+    total = 0
+    for name in ("b200_bad_index_count_attention", "b200_bad_index_count_attention_tc",
+                 "b200_bad_index_count_attention_mla"):
+        v = ctypes.c_uint(0)
+        _check(getattr(lib(), name)(ctypes.byref(v)), name)
+        total += v.value
+    return total
+
+
 def lib():
     global _lib, _sms
     if _lib is not None:
@@ -29,9 +56,17 @@ def lib():
     path = envs.B200_KERNEL_LIB or _build.lib_path()
     if not os.path.exists(path):
         raise RuntimeError(f"kernel library {path} is missing; run `python -m vllm_torchtpu_b200.csrc.build`")
-    _lib = ctypes.CDLL(path)
+    _lib = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
     _lib.b200_get_last_error.restype = ctypes.c_char_p
     _lib.b200_attn_decode_scratch_bytes.restype = c_size_t
+    if envs.B200_BOUNDS_CHECK:
+        # the attention kernels from the bounds-checked library, everything else from the main one
+        checked = _build.checked_lib_path()
+        if not os.path.exists(checked):
+            raise RuntimeError(f"{checked} is missing; run `python -m vllm_torchtpu_b200.csrc.build`")
+        over = ctypes.CDLL(checked)
+        over.b200_attn_decode_scratch_bytes.restype = c_size_t
+        _lib = _Overlay(_lib, over)
     if torch.cuda.is_available():
         _sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     return _lib
