@@ -114,7 +114,8 @@ class MLAAttention:
         q = q.view(T, self.H, self.nope + self.rope)
         kv = self.kv_a(x)
         kv_c = ops.rms_norm(kv[:, :self.kv_lora].contiguous(), self.kv_a_ln, self.eps)
-        if x.is_cuda and x.dtype == torch.bfloat16 and self.w_uk_t.dtype == torch.bfloat16 and T > 0:
+        if (x.is_cuda and x.dtype == torch.bfloat16 and self.w_uk_t.dtype == torch.bfloat16 and T > 0
+                and self.kv_lora % 128 == 0 and self.vdim % 128 == 0 and self.nope % 8 == 0 and self.rope % 8 == 0):
             # absorbed form on the package's kernels: W_UK / W_UV as grouped tcgen05 GEMMs over the heads
             cu = ops.cuda_ops()
             q_latent, k_pe = cu.mla_absorb(q.contiguous(), kv, meta.positions, self.inv_freq, self.w_uk_t,

@@ -710,7 +710,8 @@ class ModelRunner:
                 # drafts are judged where the target tokens are: the host reads counts and accepted tokens
                 k_dev = self._spec_k_dev[:n]
                 k_dev.copy_(torch.from_numpy(np.ascontiguousarray(p["spec_k"], dtype=np.int32)), non_blocking=True)
-                acc, cnt = ops.cuda_ops().spec_accept(tokens, bufs.input_ids, meta.query_start_loc, k_dev, n, kmax)
+                acc, cnt = ops.cuda_ops().spec_accept(tokens, bufs.dev_view("input_ids"), meta.query_start_loc, k_dev, n,
+                                                      kmax)
                 tokens = torch.cat([cnt, acc.flatten()])
                 rows = n * (kmax + 2)
                 device_accept = kmax
