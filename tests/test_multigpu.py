@@ -98,6 +98,15 @@ def test_pp2_engine_on_gpus_matches_single_gpu():
     assert sum(a == b for a, b in zip(one["tokens"], pp["tokens"])) >= 3, (one, pp)
 
 
+def test_tp2_decode_context_parallel_on_gpus_matches_single_gpu_in_log_probabilities():
+    """KV cache sharded by position over two GPUs: all-gathered query heads attend the local share
+    (position-aware causal mask in the prefill kernel), partial results merged by their log-sum-exp."""
+    _need(2)
+    one = _tokens(_run("tp_engine_worker.py", 1, "--mqa", "--lp"))
+    dcp = _tokens(_run("tp_engine_worker.py", 2, "--dcp", "--lp"))
+    _assert_same_distribution(one, dcp)
+
+
 def test_dp2_expert_parallel_lockstep_on_gpus():
     """Two replicas with their own requests, experts sharded over both GPUs, steps in lockstep."""
     _need(2)

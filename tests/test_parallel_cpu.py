@@ -50,6 +50,13 @@ def test_pp2_async_scheduling_matches_single_process(single):
     assert _run(2, "pp", "tiny-llama", "--async") == single
 
 
+@pytest.mark.parametrize("flags", [(), ("--il2",)])
+def test_tp2_decode_context_parallel_matches_single_process(flags):
+    """The KV cache of every sequence dealt over two ranks by position (chunked prefill of a 70-token
+    prompt in 64-token steps included): same tokens as one process with the whole cache."""
+    assert _run(2, "dcp", "tiny-mqa", *flags) == _run(1, "tp", "tiny-mqa")
+
+
 def test_ep2_moe_matches_single_process():
     assert _run(2, "ep", "tiny-moe") == _run(1, "tp", "tiny-moe")
 

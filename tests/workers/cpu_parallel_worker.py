@@ -20,6 +20,11 @@ def main():
     kw = {}
     if mode in ("tp", "tplora"):
         kw["tensor_parallel_size"] = world
+    elif mode == "dcp":
+        # KV cache dealt over the ranks by position (runs of 2 tokens), attention merged by log-sum-exp
+        kw["tensor_parallel_size"] = world
+        kw["decode_context_parallel_size"] = world
+        kw["cp_kv_cache_interleave_size"] = 2 if "--il2" in sys.argv else 1
     elif mode == "pp":
         kw["pipeline_parallel_size"] = world
     elif mode == "ep":

@@ -27,6 +27,10 @@ def main():
                           max_model_len=512, dtype=torch.bfloat16, qk_norm=True, num_experts=8,
                           num_experts_per_tok=2, moe_intermediate_size=256)
     par = dict(tensor_parallel_size=world)
+    if "--mqa" in sys.argv or "--dcp" in sys.argv:
+        cfg.num_kv_heads = 1
+    if "--dcp" in sys.argv and world > 1:           # the cache of the one KV head dealt over the ranks by position
+        par.update(decode_context_parallel_size=world, cp_kv_cache_interleave_size=1)
     if "--pp" in sys.argv:
         par = dict(pipeline_parallel_size=world)
     if "--dpep" in sys.argv:                       # data-parallel attention, experts sharded over the replicas

@@ -250,6 +250,9 @@ def model_preset(name: str) -> ModelConfig:
     n = name.lower()
     if n in ("tiny-llama", "tiny"):
         return _preset(name="tiny-llama", dtype=torch.float32, max_model_len=256)
+    if n in ("tiny-mqa",):
+        # one KV head, replicated over tensor-parallel ranks: the shape decode context parallelism is for
+        return _preset(name="tiny-mqa", dtype=torch.float32, num_kv_heads=1, max_model_len=256)
     if n in ("tiny-moe",):
         return _preset(name="tiny-moe", architecture="qwen3_moe", qk_norm=True, dtype=torch.float32,
                        num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, max_model_len=256)
@@ -340,6 +343,9 @@ class CacheConfig:
     kv_cache_memory_bytes: Optional[int] = None
     enable_prefix_caching: bool = False
     kv_cache_dtype: str = "auto"
+    # tokens the scheduler counts per block; under decode context parallelism a block holds block_size
+    # tokens on every rank of the DCP group, block_size * dcp in all (0: block_size)
+    tokens_per_block: int = 0
 
 
 @dataclass

@@ -43,7 +43,19 @@ struct AttnParams {
   long long num_blocks;
   float scale_log2, softcap;
   float v_scale;                 // fp8 cache: dequantisation factor of V (K's is folded into scale_log2)
+  // decode context parallelism (prefill kernel): the cache of this rank holds the positions p with
+  // (p / dcp_interleave) % dcp_size == dcp_rank, seq_lens are LOCAL lengths and global_seq_lens the true
+  // ones; a query at global position g sees the first dcp_local_len(g + 1) local keys
+  const int* global_seq_lens;
+  int dcp_size, dcp_rank, dcp_interleave;
 };
+
+// number of positions < n that live on `rank` when positions are dealt round-robin in runs of `il`
+__device__ __forceinline__ int dcp_local_len(int n, int rank, int size, int il) {
+  const int period = il * size;
+  const int full = n / period, rem = n - full * period;
+  return full * il + min(max(rem - rank * il, 0), il);
+}
 
 // ---- fp8 (e4m3) cache path --------------------------------------------------------------------
 // The raw bytes go to shared memory (16-byte chunk c of token row r at a swizzled position) and are
@@ -485,6 +497,13 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
   if (seq_len <= 0) return;
   const int ctx = seq_len - q_len;
   const int row0 = q0 + warp * 16 + (lane >> 2), row1 = row0 + 8;   // rows inside the request
+  // index of the last key row `row` may see: ctx + row, or under decode context parallelism the number of
+  // local keys at global positions <= the row's, minus one
+  const bool dcp = p.dcp_size > 1;
+  const int gctx = dcp ? p.global_seq_lens[r] - q_len : ctx;
+  auto last_key = [&](int row) {
+    return dcp ? dcp_local_len(gctx + row + 1, p.dcp_rank, p.dcp_size, p.dcp_interleave) - 1 : ctx + row;
+  };
 
   uint32_t qf[D / 16][4];
   {
@@ -503,7 +522,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
       }
     }
   }
-  const int kv_end = p.non_causal ? seq_len : min(seq_len, ctx + q0 + BQ);   // causal bound of the tile
+  const int kv_end = p.non_causal ? seq_len : min(seq_len, last_key(q0 + BQ - 1) + 1);   // causal bound of the tile
   int kv_begin = 0;
   if (p.window > 0) kv_begin = max(0, ctx + q0 - p.window + 1) / BKV * BKV;
   const int nchunks = (kv_end - kv_begin + BKV - 1) / BKV;
@@ -542,7 +561,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  const int lim0 = p.non_causal ? 0x3fffffff : ctx + row0, lim1 = p.non_causal ? 0x3fffffff : ctx + row1;
+  const int lim0 = p.non_causal ? 0x3fffffff : last_key(row0), lim1 = p.non_causal ? 0x3fffffff : last_key(row1);
 
   if (nchunks > 0) issue(0, 0);
   cp_async_commit();
@@ -555,7 +574,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const AttnParams p
     const uint32_t sb = sbase + stage * STAGE_BYTES;
     const int tok0 = kv_begin + c * BKV;
     // skip groups entirely above this warp's diagonal
-    const int warp_max_key = p.non_causal ? 0x3fffffff : ctx + q0 + warp * 16 + 15;
+    const int warp_max_key = p.non_causal ? 0x3fffffff : last_key(q0 + warp * 16 + 15);
     float s[BKV / 8][4];
 #pragma unroll
     for (int i = 0; i < BKV / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -699,6 +718,8 @@ static void fill_params(AttnParams& p, const void* q, const void* kv, void* out,
   p.sinks = sinks;
   p.v_scale = 1.f;
   p.non_causal = 0;
+  p.global_seq_lens = nullptr;
+  p.dcp_size = 1; p.dcp_rank = 0; p.dcp_interleave = 1;
   (void)D;
 }
 
@@ -796,11 +817,17 @@ extern "C" int b200_attn_decode_fp8kv(const void* q, const void* kv, void* out, 
 }
 
 // num_tiles = sum over requests of ceil(q_len / 64) (computed by the caller from host metadata).
+struct DcpArgs {
+  const int* global_seq_lens = nullptr;
+  int size = 1, rank = 0, interleave = 1;
+};
+
 static int attn_prefill_impl(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
                              const int* seq_lens, const int* qsl, int req_begin, int req_end,
                              int num_tiles, int max_blocks, int block_size, long long num_blocks, int Hq,
                              int Hkv, int D, float scale, int window, float softcap, const float* sinks,
-                             int kv_fp8, float k_scale, float v_scale, cudaStream_t stream) {
+                             int kv_fp8, float k_scale, float v_scale, cudaStream_t stream,
+                             const DcpArgs& dcp = DcpArgs()) {
   if (req_end <= req_begin || num_tiles <= 0) return 0;
   if (block_size % 16 || (Hq % Hkv)) {
     b200_set_last_error("attn_prefill: block_size % 16 == 0 required", __FILE__, __LINE__);
@@ -813,6 +840,15 @@ static int attn_prefill_impl(const void* q, const void* kv, void* out, float* ls
   p.req_end = req_end;
   p.num_splits = 1;
   p.part_o = nullptr; p.part_ml = nullptr; p.counters = nullptr;
+  if (dcp.size > 1) {
+    if (dcp.global_seq_lens == nullptr || dcp.interleave <= 0 || window > 0) {
+      b200_set_last_error("attn_prefill: decode context parallelism needs the global lengths and no sliding window",
+                          __FILE__, __LINE__);
+      return -1;
+    }
+    p.global_seq_lens = dcp.global_seq_lens;
+    p.dcp_size = dcp.size; p.dcp_rank = dcp.rank; p.dcp_interleave = dcp.interleave;
+  }
   dim3 grid(Hq, num_tiles);
   if (kv_fp8) set_fp8_scales(p, k_scale, v_scale);
   if (D == 128 && kv_fp8) B200_CUDA_CHECK((launch_prefill<128, true>(grid, stream, p)));
@@ -825,6 +861,21 @@ static int attn_prefill_impl(const void* q, const void* kv, void* out, float* ls
   }
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
+}
+
+// Prefill over a cache sharded by position (decode context parallelism): seq_lens are this rank's local
+// lengths, global_seq_lens the true ones; query rows see the local keys whose global position is not
+// after their own.  A request without local keys gets zeros and lse = -inf from the caller's initial fill.
+extern "C" int b200_attn_prefill_dcp(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                                     const int* seq_lens, const int* global_seq_lens, const int* qsl,
+                                     int req_begin, int req_end, int num_tiles, int max_blocks, int block_size,
+                                     long long num_blocks, int Hq, int Hkv, int D, float scale, float softcap,
+                                     int dcp_size, int dcp_rank, int dcp_interleave, cudaStream_t stream) {
+  DcpArgs dcp;
+  dcp.global_seq_lens = global_seq_lens;
+  dcp.size = dcp_size; dcp.rank = dcp_rank; dcp.interleave = dcp_interleave;
+  return attn_prefill_impl(q, kv, out, lse, block_tables, seq_lens, qsl, req_begin, req_end, num_tiles, max_blocks,
+                           block_size, num_blocks, Hq, Hkv, D, scale, 0, softcap, nullptr, 0, 1.f, 1.f, stream, dcp);
 }
 
 extern "C" int b200_attn_prefill(const void* q, const void* kv, void* out, float* lse, const int* block_tables,

@@ -57,9 +57,9 @@ class Scheduler:
     def __init__(self, scheduler_config, cache_config, num_blocks: int, *, connector=None,
                  num_spec_tokens: int = 0, sliding_window=None, abort_on_preemption: bool = False):
         self.cfg = scheduler_config
-        self.kv = KVCacheManager(num_blocks, cache_config.block_size,
-                                 cache_config.enable_prefix_caching, sliding_window)
-        self.block_size = cache_config.block_size
+        tokens_per_block = getattr(cache_config, "tokens_per_block", 0) or cache_config.block_size
+        self.kv = KVCacheManager(num_blocks, tokens_per_block, cache_config.enable_prefix_caching, sliding_window)
+        self.block_size = tokens_per_block
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self.requests: dict[str, Request] = {}

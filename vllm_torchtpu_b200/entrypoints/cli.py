@@ -47,6 +47,7 @@ def make_llm(a):
                enable_expert_parallel=a.enable_expert_parallel,
                prefill_context_parallel_size=a.prefill_context_parallel_size,
                decode_context_parallel_size=a.decode_context_parallel_size,
+               cp_kv_cache_interleave_size=a.cp_kv_cache_interleave_size,
                max_model_len=a.max_model_len, max_num_seqs=a.max_num_seqs,
                max_num_batched_tokens=a.max_num_batched_tokens, block_size=a.block_size,
                gpu_memory_utilization=a.gpu_memory_utilization,

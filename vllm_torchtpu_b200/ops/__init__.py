@@ -72,7 +72,9 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
     return ref.paged_attention(q, kv_cache, meta.block_tables, meta.seq_lens, meta.query_start_loc,
                                scale, num_reqs=meta.num_reqs, sliding_window=sliding_window,
                                softcap=softcap, sinks=sinks, k_scale=k_scale, v_scale=v_scale,
-                               return_lse=return_lse)
+                               return_lse=return_lse, global_seq_lens=meta.global_seq_lens,
+                               dcp_size=meta.dcp_size, dcp_rank=meta.dcp_rank,
+                               dcp_interleave=meta.dcp_interleave)
 
 
 def mla_write_cache(cache, kv_c, k_pe, slot_mapping):

@@ -335,7 +335,17 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
             tiles = int(((ql + 63) // 64).sum())
         else:
             tiles = (T + 63) // 64 + (R - nd)
-        if D == 128 and G in (1, 2, 4, 8) and envs.B200_ATTN_PREFILL_IMPL == "tc" and not kv_fp8:
+        if meta.dcp_size > 1:
+            # the cache holds this rank's share of the positions: local lengths, visibility by global position
+            if kv_fp8 or window or sinks is not None:
+                raise NotImplementedError("decode context parallelism: bf16 cache, no sliding window, no sinks")
+            _check(L.b200_attn_prefill_dcp(
+                _p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),
+                _p(meta.global_seq_lens), _p(meta.query_start_loc), c_int(nd), c_int(R), c_int(tiles),
+                c_int(max_blocks), c_int(bs), c_longlong(nb), c_int(Hq), c_int(Hkv), c_int(D), c_float(scale),
+                c_float(cap), c_int(meta.dcp_size), c_int(meta.dcp_rank), c_int(meta.dcp_interleave), _stream()),
+                "attn_prefill_dcp")
+        elif D == 128 and G in (1, 2, 4, 8) and envs.B200_ATTN_PREFILL_IMPL == "tc" and not kv_fp8:
             # tcgen05 kernel: one CTA per (kv head, 128 / G positions), K/V shared by the GQA group
             _check(L.b200_attn_prefill_tc(
                 _p(q), _p(kv_cache), _p(out), _p(lse), _p(meta.block_tables), _p(meta.seq_lens),

@@ -133,11 +133,17 @@ def rope_and_cache(qkv, positions, inv_freq, kv_cache, slot_mapping, num_q_heads
 def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale, *,
                     num_reqs: Optional[int] = None, sliding_window: Optional[int] = None,
                     softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
-                    k_scale: float = 1.0, v_scale: float = 1.0, return_lse: bool = False):
+                    k_scale: float = 1.0, v_scale: float = 1.0, return_lse: bool = False,
+                    global_seq_lens=None, dcp_size: int = 1, dcp_rank: int = 0, dcp_interleave: int = 1):
     """Causal attention of packed ragged queries over the paged cache.
 
     q: [T, Hq, D]; returns [T, Hq, D] (rows beyond query_start_loc[num_reqs] are zero).
     Query j of request r sits at absolute position seq_len - q_len + j.
+
+    Under decode context parallelism (``dcp_size`` > 1) the cache holds the positions p with
+    ``(p // dcp_interleave) % dcp_size == dcp_rank``, ``seq_lens`` are local lengths and
+    ``global_seq_lens`` the true ones: a query at global position g sees the local keys whose global
+    position is <= g.
     """
     T, Hq, D = q.shape
     Hkv, bs = kv_cache.shape[2], kv_cache.shape[3]
@@ -152,6 +158,7 @@ def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale,
         q_len, kv_len = qe - qs, sl[r]
         if q_len <= 0 or kv_len <= 0:
             continue
+        gl = int(global_seq_lens[r]) if dcp_size > 1 else kv_len
         nblk = -(-kv_len // bs)
         blocks = block_tables[r, :nblk].long()
         k = kv_cache[blocks, 0].float() * k_scale        # [nblk, Hkv, bs, D]
@@ -162,8 +169,14 @@ def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale,
         s = torch.einsum("hgqd,hkd->hgqk", qr, k) * scale
         if softcap:
             s = softcap * torch.tanh(s / softcap)
-        qpos = torch.arange(kv_len - q_len, kv_len, device=q.device)[:, None]
         kpos = torch.arange(kv_len, device=q.device)[None, :]
+        if dcp_size > 1:
+            g = torch.arange(gl - q_len, gl, device=q.device) + 1          # keys at global positions < g
+            period = dcp_interleave * dcp_size
+            vis = (g // period) * dcp_interleave + (g % period - dcp_rank * dcp_interleave).clamp(0, dcp_interleave)
+            qpos = (vis - 1)[:, None]
+        else:
+            qpos = torch.arange(kv_len - q_len, kv_len, device=q.device)[:, None]
         mask = kpos <= qpos
         if sliding_window:
             mask &= kpos > qpos - sliding_window
@@ -174,7 +187,8 @@ def paged_attention(q, kv_cache, block_tables, seq_lens, query_start_loc, scale,
             l = torch.logsumexp(s_all, dim=-1)
         else:
             l = torch.logsumexp(s, dim=-1)
-        p = torch.exp(s - l[..., None])
+        p = torch.exp(s - torch.where(torch.isfinite(l), l, torch.zeros_like(l))[..., None])
+        p = torch.where(torch.isfinite(s), p, torch.zeros_like(p))      # rows that see no key stay zero
         o = torch.einsum("hgqk,hkd->hgqd", p, v)
         out[qs:qe] = o.reshape(Hq, q_len, D).permute(1, 0, 2).to(q.dtype)
         lse[qs:qe] = l.reshape(Hq, q_len).t()

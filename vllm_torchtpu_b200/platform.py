@@ -169,6 +169,24 @@ class B200Platform:
         tp = p.tensor_parallel_size
         if not m.is_mla and m.num_kv_heads % tp and tp % m.num_kv_heads:
             raise ValueError(f"{m.num_kv_heads} kv heads cannot be sharded or replicated over tp={tp}")
+        dcp = p.decode_context_parallel_size
+        if dcp > 1:
+            # the ranks of a DCP group (consecutive TP ranks) must hold the same KV head: the cache of that
+            # head is what gets dealt over them
+            if m.is_mla:
+                raise ValueError("decode context parallelism is implemented for GQA attention (the latent "
+                                 "cache kernels have no position-sharded form)")
+            if tp % (m.num_kv_heads * dcp):
+                raise ValueError(f"decode_context_parallel_size={dcp} needs every KV head replicated over at "
+                                 f"least {dcp} ranks: tp={tp} must be a multiple of kv heads x dcp = "
+                                 f"{m.num_kv_heads * dcp}")
+            if m.sliding_window or kvd in ("fp8", "fp8_e4m3"):
+                raise ValueError("decode context parallelism: no sliding window, bf16 KV cache")
+            if c.block_size % max(1, p.cp_kv_cache_interleave_size):
+                raise ValueError("cp_kv_cache_interleave_size must divide block_size")
+            if cfg.kv_transfer or cfg.speculative:
+                raise ValueError("decode context parallelism does not combine with KV transfer or "
+                                 "speculative decoding")
         if m.num_q_heads % tp:
             if m.is_mla or m.num_q_heads % m.num_kv_heads or m.architecture not in ("llama", "qwen3_moe"):
                 raise ValueError(f"{m.num_q_heads} query heads do not divide over tp={tp}")

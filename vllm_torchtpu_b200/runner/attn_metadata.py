@@ -32,6 +32,8 @@ class AttentionMetadata:
     # context-parallel extras
     dcp_rank: int = 0
     dcp_size: int = 1
+    dcp_interleave: int = 1
+    global_seq_lens: Optional[torch.Tensor] = None   # [R] true lengths when seq_lens are a rank's local share
     # state slots for linear-attention layers (one per request)
     state_slots: Optional[torch.Tensor] = None
     # padded sizes when running inside a captured graph

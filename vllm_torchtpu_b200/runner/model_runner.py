@@ -140,6 +140,9 @@ class ModelRunner:
         self.is_cuda = self.device.type == "cuda"
         self.mcfg = cfg.model
         self.block_size = cfg.cache.block_size
+        st0 = get_state()
+        self.dcp_size, self.dcp_rank = st0.dcp.size, st0.dcp.rank_in_group
+        self.dcp_interleave = max(1, cfg.parallel.cp_kv_cache_interleave_size)
         self.max_reqs = cfg.scheduler.max_num_seqs
         self.max_tokens = cfg.scheduler.max_num_batched_tokens
         self.batch = InputBatch(self.max_reqs, self.mcfg.max_model_len, self.block_size)
@@ -323,8 +326,22 @@ class ModelRunner:
         L_pad = L if has_spec else R_pad
         rslots = slots[row_req]
         ids = b.token_ids[tslots, np.minimum(pos, b.token_ids.shape[1] - 1)]
-        blk = b.block_table[tslots, pos // self.block_size]
-        slot_map = blk.astype(np.int64) * self.block_size + pos % self.block_size
+        seq_lens_np = starts + num_new
+        if self.dcp_size > 1:
+            # the cache is dealt over the DCP ranks by position in runs of `il`: a token is written only by
+            # its owner, at its index among the owner's tokens; the scheduler's blocks hold block_size * dcp
+            # tokens, block_size of them on every rank, so the block index carries over
+            c, d, il = self.dcp_size, self.dcp_rank, self.dcp_interleave
+            local = (pos // (il * c)) * il + pos % il
+            blk = b.block_table[tslots, local // self.block_size]
+            slot_map = np.where((pos // il) % c == d,
+                                blk.astype(np.int64) * self.block_size + local % self.block_size, -1)
+            full, rem = np.divmod(seq_lens_np, il * c)
+            local_lens = full * il + np.clip(rem - d * il, 0, il)
+        else:
+            blk = b.block_table[tslots, pos // self.block_size]
+            slot_map = blk.astype(np.int64) * self.block_size + pos % self.block_size
+            local_lens = seq_lens_np
 
         hv = bufs.host_view
         v = hv("input_ids", T_pad); v[:T] = ids; v[T:] = 0
@@ -332,7 +349,8 @@ class ModelRunner:
         v = hv("slot_mapping", T_pad); v[:T] = slot_map; v[T:] = -1
         v = hv("token_src", T_pad); v[:T] = np.where(known, -1, tslots); v[T:] = -1
         v = hv("query_start_loc", R_pad + 1); v[:n + 1] = qsl; v[n + 1:] = T
-        v = hv("seq_lens", R_pad); v[:n] = starts + num_new; v[n:] = 0
+        v = hv("seq_lens", R_pad); v[:n] = local_lens; v[n:] = 0
+        v = hv("global_seq_lens", R_pad); v[:n] = seq_lens_np; v[n:] = 0
         v = hv("logits_indices", L_pad); v[:L] = rows; v[L:] = 0
         v = hv("top_k", L_pad); v[:L] = b.top_k[rslots]; v[L:] = 0
         v = hv("batch_slots", R_pad); v[:n] = slots; v[n:] = -1
@@ -343,7 +361,7 @@ class ModelRunner:
         if R_pad > n:
             bufs.np_bt[n:R_pad] = 0
         all_greedy = bool((b.temperature[slots] <= 1e-5).all())
-        seq_lens_np = starts + num_new
+        seq_lens_np = local_lens
         return dict(scheds=scheds, n=n, T=T, R_pad=R_pad, T_pad=T_pad, num_decode=num_decode,
                     decode_only=decode_only, bufs=bufs, all_greedy=all_greedy,
                     max_q=int(num_new.max()) if n else 0, max_seq=int(seq_lens_np.max()) if n else 0,
@@ -361,7 +379,9 @@ class ModelRunner:
             logits_indices=dv("logits_indices", p.get("L_pad", R)),
             request_distribution=(p["num_decode"], p["num_decode"], p["n"]),
             padded_num_reqs=R, padded_num_tokens=T, state_slots=dv("batch_slots", R),
-            seq_lens_cpu=torch.from_numpy(p["seq_lens_np"]), query_start_loc_cpu=torch.from_numpy(p["qsl_np"]))
+            seq_lens_cpu=torch.from_numpy(p["seq_lens_np"]), query_start_loc_cpu=torch.from_numpy(p["qsl_np"]),
+            dcp_size=self.dcp_size, dcp_rank=self.dcp_rank, dcp_interleave=self.dcp_interleave,
+            global_seq_lens=dv("global_seq_lens", R) if self.dcp_size > 1 else None)
 
     # --------------------------------------------------------------- forward
     def _forward_and_sample(self, bufs, meta, T, R, all_greedy: bool, L=None):
@@ -674,7 +694,7 @@ class ModelRunner:
                              and s.start < s.request.num_prompt_tokens] or None
         use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
                      and p["T_pad"] == p["R_pad"] and envs.B200_CUDA_GRAPHS and self._step_bitmask is None and lora_idx is None
-                     and self._step_extras is None and not self.keep_hidden
+                     and self._step_extras is None and not self.keep_hidden and self.dcp_size == 1
                      and get_state().pp.size == 1)          # pipeline stages hand off through host threads
         if use_graph:
             key = (R, p["all_greedy"])
