@@ -64,19 +64,27 @@ struct Params {
   int topk_k, T, H, Dq, L, num_reqs, max_blocks, block_size;
   long long num_blocks;
   float scale_log2;
+  // split-KV: CTA (token, head group, split) covers an equal share of the token's 16-row chunks and writes a
+  // normalised partial [splits, T, H, L] with its log-sum-exp [splits, T, H]; mla_merge_kernel combines them
+  int splits;
+  __nv_bfloat16* part_o;
+  float* part_lse;
 };
+
+constexpr int NST = 3;                // cp.async stages of 16 cache rows
 
 // LW = value columns per warp (L / 4).
 template <int LW>
 __global__ void __launch_bounds__(128) mla_attn_kernel(const Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ const __nv_bfloat16* s_ptr[2][16];
-  __shared__ int s_valid[2][16];
+  __shared__ const __nv_bfloat16* s_ptr[NST][16];
+  __shared__ int s_valid[NST][16];
   __shared__ float s_part[4][16][17];
   pdl_launch_dependents();
   pdl_wait();
   const int groups = (p.H + 15) >> 4;
-  const int t = blockIdx.x / groups, g = blockIdx.x - t * groups;
+  const int sp = blockIdx.x % p.splits, tg = blockIdx.x / p.splits;
+  const int t = tg / groups, g = tg - t * groups;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // request of this token: largest r with qsl[r] <= t
   int lo = 0, hi = p.num_reqs;
@@ -89,7 +97,10 @@ __global__ void __launch_bounds__(128) mla_attn_kernel(const Params p) {
   if (t >= p.qsl[p.num_reqs] || q_len <= 0 || kv_len <= 0) return;       // padded token
   const int qpos = kv_len - q_len + (t - qs);
   const int n_kv = p.topk ? p.topk_k : qpos + 1;
-  const int chunks = (n_kv + 15) >> 4;
+  const int chunks_all = (n_kv + 15) >> 4;
+  const int per_split = (chunks_all + p.splits - 1) / p.splits;
+  const int chunk_lo = sp * per_split;
+  const int chunks = max(0, min(chunks_all, chunk_lo + per_split) - chunk_lo);     // of this split
   const int rows_valid = min(16, p.H - g * 16);
   const int ksteps = p.Dq >> 4;                    // Dq % 16 == 0
   const int nch = p.Dq >> 3;                       // 16-byte chunks per row
@@ -117,7 +128,7 @@ __global__ void __launch_bounds__(128) mla_attn_kernel(const Params p) {
 
   auto prefetch = [&](int c, int stage) {
     if (threadIdx.x < 16) {
-      const int i = (c << 4) + threadIdx.x;
+      const int i = ((chunk_lo + c) << 4) + threadIdx.x;
       int pos = -1;
       if (i < n_kv) pos = p.topk ? p.topk[(size_t)t * p.topk_k + i] : i;
       const bool ok = pos >= 0 && pos <= qpos && pos < kv_len;
@@ -148,13 +159,17 @@ __global__ void __launch_bounds__(128) mla_attn_kernel(const Params p) {
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   const int mi = lane >> 3, rr = lane & 7;
 
-  if (chunks > 0) prefetch(0, 0);
-  cp_commit();
-  for (int c = 0; c < chunks; ++c) {
-    const int stage = c & 1;
-    if (c + 1 < chunks) prefetch(c + 1, stage ^ 1);
+#pragma unroll
+  for (int c = 0; c < NST - 1; ++c) {
+    if (c < chunks) prefetch(c, c);
     cp_commit();
-    cp_wait<1>();
+  }
+  for (int c = 0; c < chunks; ++c) {
+    const int stage = c % NST;
+    // the stage refilled here was consumed in the previous iteration (which ended with a barrier)
+    if (c + NST - 1 < chunks) prefetch(c + NST - 1, (c + NST - 1) % NST);
+    cp_commit();
+    cp_wait<NST - 1>();
     __syncthreads();
     const uint32_t sb = sbase + stage * STAGE;
     // ---- partial scores over this warp's part of Dq
@@ -237,21 +252,61 @@ __global__ void __launch_bounds__(128) mla_attn_kernel(const Params p) {
   l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1); l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
   const int row0 = lane >> 2, row1 = row0 + 8;
   const float inv0 = l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
+  __nv_bfloat16* out = p.splits > 1 ? p.part_o + (size_t)sp * p.T * p.H * p.L : p.out;
+  float* lse = p.splits > 1 ? p.part_lse + (size_t)sp * p.T * p.H : p.lse;
 #pragma unroll
   for (int i = 0; i < LW / 8; ++i) {
     const int colv = warp * LW + i * 8 + 2 * (lane & 3);
     if (row0 < rows_valid)
-      *reinterpret_cast<uint32_t*>(p.out + ((size_t)t * p.H + g * 16 + row0) * p.L + colv) =
+      *reinterpret_cast<uint32_t*>(out + ((size_t)t * p.H + g * 16 + row0) * p.L + colv) =
           pack2(o[i][0] * inv0, o[i][1] * inv0);
     if (row1 < rows_valid)
-      *reinterpret_cast<uint32_t*>(p.out + ((size_t)t * p.H + g * 16 + row1) * p.L + colv) =
+      *reinterpret_cast<uint32_t*>(out + ((size_t)t * p.H + g * 16 + row1) * p.L + colv) =
           pack2(o[i][2] * inv1, o[i][3] * inv1);
   }
-  if (p.lse != nullptr && warp == 0 && (lane & 3) == 0) {
+  if (lse != nullptr && warp == 0 && (lane & 3) == 0) {
     if (row0 < rows_valid)
-      p.lse[(size_t)t * p.H + g * 16 + row0] = l[0] > 0.f ? (m[0] + log2f(l[0])) * 0.6931471805599453f : -INFINITY;
+      lse[(size_t)t * p.H + g * 16 + row0] = l[0] > 0.f ? (m[0] + log2f(l[0])) * 0.6931471805599453f : -INFINITY;
     if (row1 < rows_valid)
-      p.lse[(size_t)t * p.H + g * 16 + row1] = l[1] > 0.f ? (m[1] + log2f(l[1])) * 0.6931471805599453f : -INFINITY;
+      lse[(size_t)t * p.H + g * 16 + row1] = l[1] > 0.f ? (m[1] + log2f(l[1])) * 0.6931471805599453f : -INFINITY;
+  }
+}
+
+// out[t, h, :] = sum_s softmax_s(lse[s, t, h]) * part_o[s, t, h, :]; one CTA per (t, h), 8 columns per thread.
+// A (token, head) whose splits all saw no key (padded rows) keeps zeros and lse = -inf.
+__global__ void mla_merge_kernel(const __nv_bfloat16* __restrict__ part_o, const float* __restrict__ part_lse,
+                                 __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int splits, int TH, int L) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int th = blockIdx.x;
+  float mx = -INFINITY;
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_lse[(size_t)s * TH + th]);
+  float den = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float v = part_lse[(size_t)s * TH + th];
+    den += v == -INFINITY ? 0.f : __expf(v - mx);
+  }
+  if (lse != nullptr && threadIdx.x == 0) lse[th] = den > 0.f ? mx + __logf(den) : -INFINITY;
+  for (int c = threadIdx.x * 8; c < L; c += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (den > 0.f) {
+      for (int s = 0; s < splits; ++s) {
+        const float v = part_lse[(size_t)s * TH + th];
+        if (v == -INFINITY) continue;
+        const float w = __expf(v - mx) / den;
+        const uint4 raw = *reinterpret_cast<const uint4*>(part_o + ((size_t)s * TH + th) * L + c);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h2[j]);
+          acc[2 * j] += w * f.x;
+          acc[2 * j + 1] += w * f.y;
+        }
+      }
+    }
+    uint4 o;
+    o.x = pack2(acc[0], acc[1]); o.y = pack2(acc[2], acc[3]); o.z = pack2(acc[4], acc[5]); o.w = pack2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + (size_t)th * L + c) = o;
   }
 }
 
@@ -368,10 +423,12 @@ extern "C" int b200_mla_write_cache(void* cache, const void* kv_c, const void* k
 
 // q [T, H, Dq], cache [num_blocks, block_size, Dq], out [T, H, L], lse [T, H] or null,
 // topk [T, topk_k] or null.  Dq % 16 == 0, Dq <= 576, L in {64, 128, 256, 512}.
+// splits > 1: part_o [splits, T, H, L] bf16 and part_lse [splits, T, H] fp32 are scratch of the caller.
 extern "C" int b200_mla_attention(const void* q, const void* cache, void* out, float* lse, const int* block_tables,
                                   const int* seq_lens, const int* qsl, const int* topk, int topk_k, int T,
                                   int num_reqs, int H, int Dq, int L, int max_blocks, int block_size,
-                                  long long num_blocks, float scale, cudaStream_t stream) {
+                                  long long num_blocks, float scale, int splits, void* part_o, float* part_lse,
+                                  cudaStream_t stream) {
   if (T <= 0 || num_reqs <= 0) return 0;
   if (Dq % 16 || Dq > 4 * mla::KS_MAX * 16 || L > Dq || (L != 64 && L != 128 && L != 256 && L != 512)) {
     b200_set_last_error("mla_attention: Dq % 16 == 0, Dq <= 576 and kv_lora in {64,128,256,512} required",
@@ -385,9 +442,14 @@ extern "C" int b200_mla_attention(const void* q, const void* cache, void* out, f
   p.T = T; p.H = H; p.Dq = Dq; p.L = L; p.num_reqs = num_reqs; p.max_blocks = max_blocks;
   p.block_size = block_size; p.num_blocks = num_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
+  if (splits < 1 || (splits > 1 && (part_o == nullptr || part_lse == nullptr))) {
+    b200_set_last_error("mla_attention: split-KV needs its scratch", __FILE__, __LINE__);
+    return -1;
+  }
+  p.splits = splits; p.part_o = (__nv_bfloat16*)part_o; p.part_lse = part_lse;
   const int nch = Dq / 8;
-  const int smem = 2 * 16 * (((nch + 7) & ~7) << 4);
-  const dim3 grid(T * ((H + 15) / 16));
+  const int smem = mla::NST * 16 * (((nch + 7) & ~7) << 4);
+  const dim3 grid(T * ((H + 15) / 16) * splits);
 #define MLA_LAUNCH(LWV)                                                                                      \
   do {                                                                                                       \
     B200_CUDA_CHECK(cudaFuncSetAttribute(mla::mla_attn_kernel<LWV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
@@ -399,6 +461,10 @@ extern "C" int b200_mla_attention(const void* q, const void* cache, void* out, f
   else if (L == 128) MLA_LAUNCH(32);
   else MLA_LAUNCH(16);
 #undef MLA_LAUNCH
+  if (splits > 1)
+    B200_CUDA_CHECK(launch_pdl(mla::mla_merge_kernel, dim3(T * H), dim3(64), (size_t)0, stream,
+                               (const __nv_bfloat16*)part_o, (const float*)part_lse, (__nv_bfloat16*)out, lse,
+                               splits, T * H, L));
   return 0;
 }
 

@@ -320,6 +320,92 @@ def bench_fp8_gemm(T, N, K, iters=20) -> list:
     return rows
 
 
+def bench_misc(iters=20) -> list:
+    """Element-wise, routing, sampling and MLA kernels at serving shapes: device time (graph replay, L2
+    flushed), algorithmic bytes over the measured copy bandwidth."""
+    from ..runner.attn_metadata import AttentionMetadata
+    from . import cuda
+    from . import reference as ref
+    pk, tag = peaks()
+    rows = []
+
+    def row(op, shape, ms, byts, note=None):
+        r = {"op": op, "shape": shape, "us": round(ms * 1e3, 2), "gbs": round(byts / ms / 1e6, 1),
+             "frac_of_hbm": round(byts / ms / 1e6 / pk["hbm_gbs"], 3), "peaks": tag, "status": cuda.check_status()}
+        if note:
+            r["note"] = note
+        rows.append(r)
+    dev = "cuda"
+    for T in (64, 8192):
+        H, I = 4096, 14336
+        x = torch.randn(T, H, device=dev).bfloat16()
+        res = torch.randn(T, H, device=dev).bfloat16()
+        w = torch.ones(H, device=dev).bfloat16()
+        row("rms_norm", [T, H], time_fn(lambda: cuda.rms_norm(x, w, 1e-5), iters), 2.0 * T * H * 2)
+        row("fused_add_rms_norm", [T, H], time_fn(lambda: cuda.fused_add_rms_norm(x, res, w, 1e-5), iters),
+            4.0 * T * H * 2)
+        gu = torch.randn(T, 2 * I, device=dev).bfloat16()
+        row("silu_and_mul", [T, 2 * I], time_fn(lambda: cuda.silu_and_mul(gu), iters), 3.0 * T * I * 2)
+        row("quant_act_1x128", [T, I], time_fn(lambda: cuda.quant_act_1x128(gu[:, :I].contiguous()), iters),
+            T * I * 3.0 + T * I * 2.0, note="includes the contiguous copy of the slice")
+        row("quant_rows_1x128 swiglu", [T, 2 * I], time_fn(lambda: cuda.quant_rows_1x128(gu, I, swiglu=True), iters),
+            T * I * 5.0)
+        # RoPE + q/k norm-free KV write, Llama-8B heads
+        Hq, Hkv, D, bs = 32, 8, 128, 16
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=dev).bfloat16()
+        nb = T // bs + 2
+        cache = torch.zeros(nb, 2, Hkv, bs, D, device=dev, dtype=torch.bfloat16)
+        pos = torch.arange(T, device=dev, dtype=torch.int32)
+        slots = torch.arange(T, device=dev, dtype=torch.int32)
+        inv_freq = ref.rope_inv_freq(D, 500000.0, None).to(dev)
+        row("rope_and_cache", [T, Hq, Hkv, D],
+            time_fn(lambda: cuda.rope_and_cache(qkv, pos, inv_freq, cache, slots, Hq, Hkv, D), iters),
+            T * (Hq + 2 * Hkv) * D * 2.0 + T * (Hq + 2 * Hkv) * D * 2.0)
+        # MoE routing / permutation, Qwen3-30B-A3B shape
+        E, k, Hm = 128, 8, 2048
+        logits = torch.randn(T, E, device=dev)
+        row("moe_route", [T, E, k], time_fn(lambda: cuda.moe_route(logits, k), iters), T * E * 4.0 + T * k * 8.0)
+        ids, wts = cuda.moe_route(logits, k)
+        xm = torch.randn(T, Hm, device=dev).bfloat16()
+        row("moe_permute", [T, k, Hm], time_fn(lambda: cuda.moe_permute(xm, ids, 0, E), iters),
+            T * Hm * 2.0 + T * k * Hm * 2.0)
+        xp, goff, _, inv = cuda.moe_permute(xm, ids, 0, E)
+        row("moe_unpermute", [T, k, Hm], time_fn(lambda: cuda.moe_unpermute(xp, inv, wts, T), iters),
+            T * k * Hm * 2.0 + T * Hm * 2.0)
+    # sampling over the Llama-3 vocabulary
+    R, V = 64, 128256
+    lg = torch.randn(R, V, device=dev).bfloat16()
+    row("argmax", [R, V], time_fn(lambda: cuda.argmax(lg), iters), R * V * 2.0)
+    temp = torch.full((R,), 0.8, device=dev)
+    tk = torch.full((R,), 50, device=dev, dtype=torch.int32)
+    tp = torch.full((R,), 0.9, device=dev)
+    row("sample top-k 50 top-p 0.9", [R, V], time_fn(lambda: cuda.sample(lg, temp, tk, tp, None, False, 1), iters),
+        R * V * 2.0, note="several passes over the row by design (bisection); bytes = one pass")
+    # MLA decode, DeepSeek-V3 per-rank shape at TP8: 16 heads, latent 512 + 64
+    for reqs, ctx in ((64, 2048),):
+        Hh, L, Rr, bs = 16, 512, 64, 16
+        nblk = -(-ctx // bs)
+        cache = (torch.randn(reqs * nblk + 1, bs, L + Rr, device=dev) * 0.3).bfloat16()
+        bt = (torch.randperm(reqs * nblk, device=dev) + 1).to(torch.int32).view(reqs, nblk).contiguous()
+        q = torch.randn(reqs, Hh, L + Rr, device=dev).bfloat16()
+        qsl = torch.arange(reqs + 1, device=dev, dtype=torch.int32)
+        sl = torch.full((reqs,), ctx, device=dev, dtype=torch.int32)
+        meta = AttentionMetadata(None, None, bt, sl, qsl, reqs, reqs, num_decode_reqs=reqs, max_seq_len=ctx,
+                                 padded_num_reqs=reqs, padded_num_tokens=reqs)
+        row("mla_decode", [reqs, ctx, Hh, L + Rr],
+            time_fn(lambda: cuda.mla_paged_attention(q, cache, meta, (128 + 64) ** -0.5, L), iters),
+            reqs * ctx * (L + Rr) * 2.0, note="bytes = one read of every latent row")
+        w_uk_t = (torch.randn(Hh, L, 128, device=dev) * 0.05).bfloat16()
+        qq = torch.randn(reqs, Hh, 192, device=dev).bfloat16()
+        kvx = torch.randn(reqs, L + Rr, device=dev).bfloat16()
+        pos = torch.full((reqs,), ctx - 1, device=dev, dtype=torch.int32)
+        inv_freq = ref.rope_inv_freq(64, 10000.0, None).to(dev)
+        row("mla_absorb (permute, grouped GEMM, permute, 2 x rope)", [reqs, Hh, 128, L],
+            time_fn(lambda: cuda.mla_absorb(qq, kvx, pos, inv_freq, w_uk_t, 128, 64, L, False), iters),
+            Hh * L * 128 * 2.0 + reqs * Hh * (192 + L + 64) * 2.0, note="five launches")
+    return rows
+
+
 def bench_gemm_swiglu(T, I, K, iters=20, impl="tcgen05") -> dict:
     """silu(x Wg^T) * (x Wu^T) with W = [2I, K]; 'cublas' is torch.matmul followed by an eager activation."""
     from . import cuda
@@ -391,7 +477,7 @@ LLAMA8B_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "fp8-gemm", "gemm-swiglu", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill",
+    ap.add_argument("what", choices=["gemm", "fp8-gemm", "misc", "gemm-swiglu", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill",
                                      "decode-layer", "decode-model", "all"])
     ap.add_argument("--T", type=int, default=64)
     ap.add_argument("--N", type=int, default=4096)
@@ -416,6 +502,9 @@ def main():
                     continue
                 for impl in ("tcgen05", "cublas"):
                     print(json.dumps(bench_gemm(T, N, K, max(5, a.iters // 2), impl, check=(T <= 1024))))
+    if a.what == "misc":
+        for r in bench_misc(a.iters):
+            print(json.dumps(r))
     if a.what == "fp8-gemm":
         for r in bench_fp8_gemm(a.T, a.N, a.K, a.iters):
             print(json.dumps(r))

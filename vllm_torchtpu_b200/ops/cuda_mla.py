@@ -36,12 +36,26 @@ def mla_paged_attention(q_latent, cache, meta, scale, kv_lora_rank: int, *, topk
     if topk_indices is not None:
         topk = topk_indices.to(torch.int32).contiguous()
         K = topk.shape[1]
+    # split-KV when the batch alone leaves SMs idle (decode): about three CTAs per SM and at least four
+    # 16-row chunks per split.  Inside a captured graph the choice depends on the batch shape only (lengths
+    # change between replays; a split without keys contributes lse = -inf).
+    groups = (H + 15) // 16
+    splits = 1
+    if T * groups < 2 * _c._sms:
+        splits = max(1, min(16, (3 * _c._sms) // max(1, T * groups)))
+        if not torch.cuda.is_current_stream_capturing():
+            n_kv = K if topk is not None else max(1, int(meta.max_seq_len or 0))
+            splits = max(1, min(splits, n_kv // 64))
+    part_o = part_lse = None
+    if splits > 1:
+        part_o = torch.empty((splits, T, H, kv_lora_rank), dtype=q.dtype, device=q.device)
+        part_lse = torch.empty((splits, T, H), dtype=torch.float32, device=q.device)
     _c._check(_c.lib().b200_mla_attention(
         _c._p(q), _c._p(cache), _c._p(out), _c._p(lse), _c._p(meta.block_tables), _c._p(meta.seq_lens),
         _c._p(meta.query_start_loc), _c._p(topk), c_int(K), c_int(T), c_int(meta.num_reqs), c_int(H), c_int(Dq),
         c_int(kv_lora_rank), c_int(meta.block_tables.shape[1]), c_int(bs), c_longlong(nb), c_float(scale),
-        _c._stream()), "mla_attention")
-    count_launch()
+        c_int(splits), _c._p(part_o), _c._p(part_lse), _c._stream()), "mla_attention")
+    count_launch(2 if splits > 1 else 1)
     if return_lse:
         return out, lse
     return out
