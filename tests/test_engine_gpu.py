@@ -183,3 +183,32 @@ def test_vision_encoder_on_gpu_matches_cpu():
         assert a.shape == b.shape
         err = (a.float().cpu() - b).abs().max().item()
         assert err < 0.05 * b.abs().max().item() + 0.02, err
+
+
+def test_fp8_block_quantised_engine_matches_its_dequantised_dense_forward():
+    """Llama-style model with block-scaled fp8 linears (activation quantisation shared between projections,
+    SiLU*mul fused into the down projection's quantisation): prefill logits against the dense fp32 forward
+    over the dequantised weights."""
+    from vllm_torchtpu_b200.models.reference_forward import dense_llama_logits
+    cfg = _cfg()
+    cfg.quantization = "fp8_block"
+    llm = LLM(cfg, device="cuda", max_num_seqs=8, max_num_batched_tokens=256, num_gpu_blocks_override=512,
+              init_dist=False, enforce_eager=True)
+    eng = llm.engine
+    p = _prompts()[3]
+    eng.add_request(p, SamplingParams(max_tokens=1))
+    out = eng.scheduler.schedule()
+    r = eng.runner
+    r._update_batch(out)
+    prep = r._prepare_inputs(out)
+    prep["bufs"].upload(prep["R_pad"])
+    _, logits = r._forward_and_sample(prep["bufs"], r._make_meta(prep), prep["T_pad"], prep["R_pad"], True)
+    want = dense_llama_logits(r.model, p)[-1]
+    err = (logits[0].float() - want).abs().max().item()
+    # activations go through e4m3 in the kernel path and stay bf16 in the dense forward
+    assert err < 0.12 * want.abs().max().item() + 0.05, err
+    fresh = LLM(cfg, device="cuda", max_num_seqs=8, max_num_batched_tokens=256, num_gpu_blocks_override=512,
+                init_dist=False)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    toks = [o.outputs[0].token_ids for o in fresh.generate(_prompts()[:3], sp)]
+    assert all(len(t) == 8 for t in toks)

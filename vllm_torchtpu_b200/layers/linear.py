@@ -129,6 +129,21 @@ class RowParallelLinear(LinearBase):
         k = self.in_features
         return full_weight[:, self.tp_rank * k:(self.tp_rank + 1) * k]
 
+    def forward_quantised(self, xq, xs):
+        """Forward on an activation the caller has already quantised for this layer's method (block-scaled
+        fp8: e4m3 rows with 1x128 scales, e.g. SiLU*mul fused into the quantisation kernel).  GPU only, no
+        LoRA on this layer."""
+        m = self.method
+        if self.tp_size == 1 or not self.reduce_results:
+            return m.apply_quantised(self, xq, xs, self.bias)
+        comm = get_tp_comm()
+        fused = comm.heap is not None and comm.heap.fused_tp is not None
+        if (fused and self.defer_reduce and self.bias is None
+                and m.can_push(comm.heap.fused_tp, xq.shape[0], self.out_features)):
+            return m.apply_push_quantised(self, xq, xs, comm)
+        y = comm.all_reduce(m.apply_quantised(self, xq, xs, None))
+        return y + self.bias if self.bias is not None else y
+
     def forward(self, x):
         if self.tp_size == 1 or not self.reduce_results:
             return self.method.apply(self, x, self.bias)

@@ -112,6 +112,14 @@ class LlamaMLP:
                 and not gu.lora_targets):
             # gate and up tiles share the activation tile; SiLU*mul happens in the GEMM epilogue
             return self.down(ops.cuda_ops().gemm_swiglu(x, gu.weight))
+        if (x.is_cuda and x.dtype == torch.bfloat16 and hasattr(self.down.method, "apply_quantised")
+                and not self.down.lora_targets and type(self.down.method) is type(gu.method)):
+            # block-scaled fp8: SiLU*mul runs inside the quantisation kernel of the down projection's input
+            h = self.gate_up(x)
+            h2 = h.reshape(-1, h.shape[-1])
+            xq, xs = ops.cuda_ops().quant_rows_1x128(h2, h2.shape[1] // 2, swiglu=True)
+            y = self.down.forward_quantised(xq, xs)
+            return y if not isinstance(y, torch.Tensor) else y.reshape(*x.shape[:-1], y.shape[-1])
         return self.down(ops.silu_and_mul(self.gate_up(x)))
 
 

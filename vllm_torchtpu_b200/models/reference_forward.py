@@ -14,6 +14,15 @@ def _rms(x, w, eps):
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
 
 
+def dense_weight(lin) -> torch.Tensor:
+    """fp32 weight of a linear layer whatever its storage (block-scaled fp8 is dequantised)."""
+    scale = getattr(lin, "weight_scale_inv", None)
+    if scale is not None:
+        from ..quantization.fp8 import dequantize_weight_block
+        return dequantize_weight_block(lin.weight, scale).float()
+    return lin.weight.float()
+
+
 @torch.no_grad()
 def dense_llama_hidden(model, token_ids: list) -> torch.Tensor:
     """Final-norm hidden states [S, H] of one sequence (fp32 math)."""
@@ -31,7 +40,7 @@ def dense_llama_logits(model, token_ids: list, return_hidden: bool = False) -> t
     for layer in model.layers:
         a = layer.self_attn
         h = _rms(x, layer.input_ln, cfg.rms_norm_eps)
-        qkv = h @ a.qkv.weight.float().t()
+        qkv = h @ dense_weight(a.qkv).t()
         if a.qkv.bias is not None:
             qkv = qkv + a.qkv.bias.float()
         q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], -1)
@@ -47,12 +56,12 @@ def dense_llama_logits(model, token_ids: list, return_hidden: bool = False) -> t
         mask = torch.ones(S, S, dtype=torch.bool, device=ids.device).tril()
         s = s.masked_fill(~mask, float("-inf"))
         o = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(S, Hq * D)
-        x = x + o @ a.o.weight.float().t()
+        x = x + o @ dense_weight(a.o).t()
         h = _rms(x, layer.post_ln, cfg.rms_norm_eps)
         if hasattr(layer.mlp, "gate_up"):
-            gu = h @ layer.mlp.gate_up.weight.float().t()
+            gu = h @ dense_weight(layer.mlp.gate_up).t()
             I = gu.shape[-1] // 2
-            x = x + (F.silu(gu[:, :I]) * gu[:, I:]) @ layer.mlp.down.weight.float().t()
+            x = x + (F.silu(gu[:, :I]) * gu[:, I:]) @ dense_weight(layer.mlp.down).t()
         else:
             x = x + layer.mlp.forward(h.to(cfg.dtype)).float()
     x = _rms(x, model.norm, cfg.rms_norm_eps)

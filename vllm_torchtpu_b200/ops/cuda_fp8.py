@@ -72,6 +72,23 @@ def use_rows_kernel(T: int, N: int) -> bool:
     return min_tiles >= 0 and T > 128 and (-(-T // 128)) * (-(-N // 256)) >= min_tiles
 
 
+_last_quant = None       # (tensor kept alive, key, xq, xs): the activation most recently quantised
+
+
+def quant_act_shared(x2):
+    """``quant_act_1x128`` that recognises the activation it quantised last: projections that read the same
+    tensor (q_a / kv_a of MLA, a shared expert next to the router) quantise it once.  The tensor is kept
+    alive while cached, so its address cannot be handed to another tensor; an in-place write bumps its
+    version and misses."""
+    global _last_quant
+    key = (x2.data_ptr(), tuple(x2.shape), tuple(x2.stride()), x2._version)
+    if _last_quant is not None and _last_quant[1] == key:
+        return _last_quant[2], _last_quant[3]
+    xq, xs = quant_act_1x128(x2)
+    _last_quant = (x2, key, xq, xs)
+    return xq, xs
+
+
 def fp8_block_gemm(x, wq, w_scale_inv, bias=None, block=(128, 128), out=None):
     """x bf16 [T,K]; wq e4m3 [N,K]; w_scale_inv fp32 [ceil(N/128), ceil(K/128)] -> bf16 [T,N]."""
     if tuple(block) != (128, 128):
@@ -80,7 +97,7 @@ def fp8_block_gemm(x, wq, w_scale_inv, bias=None, block=(128, 128), out=None):
     x2 = x.reshape(-1, x.shape[-1])
     T, K = x2.shape
     N = wq.shape[0]
-    xq, xs = quant_act_1x128(x2)
+    xq, xs = quant_act_shared(x2)
     y = out if out is not None else torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
     if T == 0:
         return y.reshape(*lead, N)
@@ -105,21 +122,26 @@ def fp8_block_gemm_push(x, wq, w_scale_inv, heap):
     """Row-parallel block-scaled fp8 ``x @ wq.T`` whose bf16 partial is pushed to every rank of ``heap``
     from the GEMM epilogue; returns the :class:`PendingReduce` the next add + RMSNorm (or
     ``materialize``) completes.  For at most 128 tokens within ``FusedTP.can_push``."""
-    st = heap.fused_tp
     x2 = x.reshape(-1, x.shape[-1])
-    T, K = x2.shape
+    xq, xs = quant_act_shared(x2)
+    return fp8_block_gemm_push_quantised(xq, xs, wq, w_scale_inv, heap, x.shape[:-1])
+
+
+def fp8_block_gemm_push_quantised(xq, xs, wq, w_scale_inv, heap, lead_shape=None):
+    """The push GEMM on an activation that is already e4m3 with 1x128 scales."""
+    st = heap.fused_tp
+    T, K = xq.shape
     N = wq.shape[0]
-    xq, xs = quant_act_1x128(x2)
     part = st.parts[st.flip]
     st.flip ^= 1
-    ws = _c.Workspace.get(x.device)
+    ws = _c.Workspace.get(xq.device)
     _c._check(_c.lib().b200_gemm_fp8_block_push(
         _c._p(xq), _c._p(xs), _c._p(wq), _c._p(w_scale_inv), c_int(T), c_int(N), c_int(K),
         heap.peers_c, c_int(heap.rank), c_int(heap.world), c_ulonglong(part.offset),
         c_ulonglong(st.part_bytes), c_ulonglong(st.tile_flags.offset), c_int(_c.FusedTP.MAX_TILES),
         _c._p(st.ctrl), _c._p(ws.status), c_int(_c._sms), _c._stream()), "gemm_fp8_block_push")
     count_launch()
-    return _c.PendingReduce(heap, part, T, N, x.shape[:-1])
+    return _c.PendingReduce(heap, part, T, N, lead_shape if lead_shape is not None else (T,))
 
 
 def fp8_per_tensor_gemm(x, wq, w_scale, bias=None, ws_grid=None):

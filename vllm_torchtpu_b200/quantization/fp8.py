@@ -132,6 +132,14 @@ class Fp8BlockLinearMethod(LinearMethodBase):
         y = fp8_block_gemm_reference(x, layer.weight, layer.weight_scale_inv, self.block)
         return y if bias is None else (y.float() + bias.float()).to(y.dtype)
 
+    def apply_quantised(self, layer, xq, xs, bias=None):
+        """The product on an activation that is already e4m3 with 1x128 scales (GPU)."""
+        y = torch.empty((xq.shape[0], layer.weight.shape[0]), dtype=torch.bfloat16, device=xq.device)
+        return ops.cuda_ops().fp8_block_gemm_quantised(xq, xs, layer.weight, layer.weight_scale_inv, y, bias)
+
+    def apply_push_quantised(self, layer, xq, xs, comm):
+        return ops.cuda_ops().fp8_block_gemm_push_quantised(xq, xs, layer.weight, layer.weight_scale_inv, comm.heap)
+
     def can_push(self, fused_tp, T: int, N: int) -> bool:
         # the consumer derives the token tile from T; the fp8 kernel's largest token tile is 128
         return T <= 128 and fused_tp.can_push(T, N)
