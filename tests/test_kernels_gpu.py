@@ -173,6 +173,21 @@ def test_argmax_and_sampling():
     assert torch.equal(got2, got)
 
 
+def test_sampling_cluster_kernel_on_an_odd_vocabulary():
+    """Rows of odd length start on odd element offsets (two-byte loads instead of pairs) and the last CTA of
+    the cluster holds a ragged tail."""
+    R, V = 6, 50001
+    g = torch.Generator(device=DEV).manual_seed(5)
+    logits = (torch.randn(R, V, device=DEV, generator=g) * 2.5).bfloat16()
+    temp = torch.tensor([0.8, 0.0, 1.0, 1.2, 0.6, 1.0], device=DEV)
+    top_k = torch.tensor([40, 0, 0, 3, 0, 2000], device=DEV, dtype=torch.int32)
+    top_p = torch.tensor([0.9, 1.0, 0.7, 1.0, 1.0, 0.99], device=DEV)
+    u = cu().philox_uniform(R, V, 11, 1, DEV)
+    got = cu().sample(logits, temp, top_k, top_p, uniform=u)
+    want = ref.sample(logits, temp, top_k, top_p, uniform=u)
+    assert torch.equal(got.long(), want)
+
+
 def test_logprobs():
     R, V = 5, 32000
     logits = torch.randn(R, V, device=DEV).bfloat16()

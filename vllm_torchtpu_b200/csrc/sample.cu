@@ -9,6 +9,8 @@
 // either supplied (tests) or generated in the kernel with Philox keyed by
 // (seed, step, row, column), so every tensor-parallel rank draws the same token.
 // One CTA per row; each pass re-reads the row (bf16, L2 resident).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -106,9 +108,38 @@ argmax_kernel(const T* __restrict__ logits, int ld, int V, int* __restrict__ out
   __shared__ ArgMax red[32];
   const T* row = logits + (size_t)blockIdx.x * ld;
   ArgMax a{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = load_logit(row, i);
-    if (v > a.v) a = ArgMax{v, i};
+  int head = 0;                                  // elements before the 16-byte aligned body
+  if (sizeof(T) == 2) {
+    // bf16 rows: 16-byte loads over the aligned body (a thread's indices still grow, so `>` keeps the
+    // smallest index among equal values), scalar loads for the ragged ends
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(row);
+    head = min(V, (int)(((16 - (addr & 15)) & 15) >> 1));
+    const int nvec = (V - head) >> 3;
+    const uint4* body = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(row) + head);
+    for (int q = threadIdx.x; q < nvec; q += blockDim.x) {
+      const uint4 w = body[q];
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h2[j]);
+        const int i = head + q * 8 + 2 * j;
+        if (f.x > a.v) a = ArgMax{f.x, i};
+        if (f.y > a.v) a = ArgMax{f.y, i + 1};
+      }
+    }
+    for (int i = threadIdx.x; i < head; i += blockDim.x) {
+      const float v = load_logit(row, i);
+      if (v > a.v || (v == a.v && i < a.i)) a = ArgMax{v, i};
+    }
+    for (int i = head + nvec * 8 + threadIdx.x; i < V; i += blockDim.x) {
+      const float v = load_logit(row, i);
+      if (v > a.v) a = ArgMax{v, i};
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = load_logit(row, i);
+      if (v > a.v) a = ArgMax{v, i};
+    }
   }
   a = block_argmax(a, red);
   if (threadIdx.x == 0) out[blockIdx.x] = a.i < V ? a.i : 0;
@@ -203,6 +234,259 @@ sample_kernel(const T* __restrict__ logits, int ld, int V, const float* __restri
   }
   a = block_argmax(a, red);
   if (threadIdx.x == 0) out[r] = a.i < V ? a.i : 0;
+}
+
+// ---- the same sampler with the row held in registers by a cluster of four CTAs ------------------------
+// The single-CTA kernel above re-reads its row from L2 in every bisection pass (about 70 passes over 128 K
+// logits: 1.2 ms for 64 rows).  Here a cluster of SAMPLE_CL CTAs owns a row: CTA c keeps elements
+// [c * seg, (c + 1) * seg) as packed bf16 logits in registers (64 per thread), so a pass is 64 compares per
+// thread, a block reduction and one exchange of a few words over distributed shared memory.  The threshold
+// searches are 4-ary (three thresholds per pass), which halves the number of cluster barriers.  Same
+// thresholds, same Philox noise and same Gumbel-max draw as the single-CTA kernel.
+constexpr int SAMPLE_CL = 4;
+constexpr int SAMPLE_CT = 512;                    // threads per CTA of the cluster kernel
+constexpr int SAMPLE_NPT = 64;                    // elements per thread: V <= 4 * 512 * 64 = 131072
+
+struct ClusterXchg {
+  float f[2][4];                                  // [parity][word]
+  int i[2][4];
+};
+
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_dsmem_s32(uint32_t addr) {
+  int v;
+  asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+// Every thread of every CTA of the cluster passes up to three per-thread values; all threads get the three
+// cluster-wide sums.  `par` alternates between calls, so a slot is rewritten only after a later barrier.
+// three block sums with one pair of barriers; red holds 3 x 32 words; every thread of warp 0 gets the sums
+__device__ __forceinline__ void block_sum3_f(float& a, float& b, float& c, float* red) {
+  a = warp_sum(a); b = warp_sum(b); c = warp_sum(c);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) { red[warp] = a; red[32 + warp] = b; red[64 + warp] = c; }
+  __syncthreads();
+  if (warp == 0) {
+    a = warp_sum(lane < nw ? red[lane] : 0.f);
+    b = warp_sum(lane < nw ? red[32 + lane] : 0.f);
+    c = warp_sum(lane < nw ? red[64 + lane] : 0.f);
+  }
+}
+__device__ __forceinline__ void block_sum3_i(int& a, int& b, int& c, int* red) {
+  a = warp_sum(a); b = warp_sum(b); c = warp_sum(c);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) { red[warp] = a; red[32 + warp] = b; red[64 + warp] = c; }
+  __syncthreads();
+  if (warp == 0) {
+    a = warp_sum(lane < nw ? red[lane] : 0);
+    b = warp_sum(lane < nw ? red[32 + lane] : 0);
+    c = warp_sum(lane < nw ? red[64 + lane] : 0);
+  }
+}
+
+__device__ __forceinline__ void cluster_sum3_f(float& a, float& b, float& c, ClusterXchg* x, float* red, int& par) {
+  block_sum3_f(a, b, c, red);
+  if (threadIdx.x == 0) { x->f[par][0] = a; x->f[par][1] = b; x->f[par][2] = c; }
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  const uint32_t base = smem_u32(&x->f[par][0]);
+  float sa = 0.f, sb = 0.f, sc = 0.f;
+#pragma unroll
+  for (int r = 0; r < SAMPLE_CL; ++r) {
+    const uint32_t ra = mapa_shared(base, r);
+    sa += ld_dsmem_f32(ra);
+    sb += ld_dsmem_f32(ra + 4);
+    sc += ld_dsmem_f32(ra + 8);
+  }
+  a = sa; b = sb; c = sc;
+  par ^= 1;
+}
+__device__ __forceinline__ void cluster_sum3_i(int& a, int& b, int& c, ClusterXchg* x, int* red, int& par) {
+  block_sum3_i(a, b, c, red);
+  if (threadIdx.x == 0) { x->i[par][0] = a; x->i[par][1] = b; x->i[par][2] = c; }
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  const uint32_t base = smem_u32(&x->i[par][0]);
+  int sa = 0, sb = 0, sc = 0;
+#pragma unroll
+  for (int r = 0; r < SAMPLE_CL; ++r) {
+    const uint32_t ra = mapa_shared(base, r);
+    sa += ld_dsmem_s32(ra);
+    sb += ld_dsmem_s32(ra + 4);
+    sc += ld_dsmem_s32(ra + 8);
+  }
+  a = sa; b = sb; c = sc;
+  par ^= 1;
+}
+// cluster-wide arg-max of (value, index): smaller index wins ties
+__device__ __forceinline__ ArgMax cluster_argmax(ArgMax a, ClusterXchg* x, ArgMax* red, int& par) {
+  a = block_argmax(a, red);
+  if (threadIdx.x == 0) { x->f[par][3] = a.v; x->i[par][3] = a.i; }
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  const uint32_t bf = smem_u32(&x->f[par][3]), bi = smem_u32(&x->i[par][3]);
+  ArgMax best{-INFINITY, 0x7fffffff};
+#pragma unroll
+  for (int r = 0; r < SAMPLE_CL; ++r) {
+    const ArgMax o{ld_dsmem_f32(mapa_shared(bf, r)), ld_dsmem_s32(mapa_shared(bi, r))};
+    best = better(best, o);
+  }
+  par ^= 1;
+  return best;
+}
+
+// bf16 logits only (fp32 rows would not fit the register budget): a thread keeps 32 packed pairs, element j of
+// thread t is row index cr * seg + ((j >> 1) * 512 + t) * 2 + (j & 1).
+__global__ void __launch_bounds__(SAMPLE_CT, 1)
+sample_cluster_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
+                      const int* __restrict__ top_k, const float* __restrict__ top_p,
+                      const float* __restrict__ uniform, unsigned long long seed, unsigned long long step,
+                      const long long* __restrict__ step_ptr, int* __restrict__ out) {
+  if (step_ptr != nullptr) step += (unsigned long long)(*step_ptr);
+  __shared__ ArgMax red[32];
+  __shared__ float redf[96];
+  __shared__ int redi[96];
+  __shared__ ClusterXchg xchg;
+  const int r = blockIdx.x / SAMPLE_CL;
+  const int cr = (int)cluster_ctarank();
+  const __nv_bfloat16* row = logits + (size_t)r * ld;
+  const float temp = temperature[r];
+  const bool greedy = temp <= 1e-5f;
+  const float inv_t = greedy ? 1.f : 1.f / temp;
+  // elements per CTA: a multiple of 2 * 512 so that pairs never straddle CTAs
+  const int seg = ((V + SAMPLE_CL - 1) / SAMPLE_CL + 2 * SAMPLE_CT - 1) / (2 * SAMPLE_CT) * (2 * SAMPLE_CT);
+  const int base = cr * seg + 2 * (int)threadIdx.x;
+  int par = 0;
+  // order-preserving 32-bit keys of the scaled logits; padding holds the key of -inf (KEY_NEG)
+  uint32_t key[SAMPLE_NPT];
+  const uint32_t KEY_NEG = f2key(-INFINITY);
+  const bool pair_ok = ((reinterpret_cast<uintptr_t>(row) & 3) == 0);
+#pragma unroll
+  for (int jj = 0; jj < SAMPLE_NPT / 2; ++jj) {
+    const int i = base + jj * 2 * SAMPLE_CT;
+    float x0 = -INFINITY, x1 = -INFINITY;
+    if (jj * 2 * SAMPLE_CT < seg && i < V) {
+      if (pair_ok && i + 1 < V) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + i));
+        x0 = f.x; x1 = f.y;
+      } else {
+        x0 = __bfloat162float(row[i]);
+        if (i + 1 < V) x1 = __bfloat162float(row[i + 1]);
+      }
+    }
+    key[2 * jj] = f2key(x0 * inv_t);
+    key[2 * jj + 1] = f2key(x1 * inv_t);
+  }
+  auto idx = [&](int j) -> int { return base + (j >> 1) * 2 * SAMPLE_CT + (j & 1); };
+  // every CTA of the cluster must be resident before the first remote read
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  if (greedy) {
+    ArgMax a{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int j = 0; j < SAMPLE_NPT; ++j) {
+      const float x = key2f(key[j]);
+      if (x > a.v) a = ArgMax{x, idx(j)};
+    }
+    a = cluster_argmax(a, &xchg, red, par);
+    if (cr == 0 && threadIdx.x == 0) out[r] = a.i < V ? a.i : 0;
+    cluster_arrive_release();                   // nobody leaves while a peer may still read its slots
+    cluster_wait_acquire();
+    return;
+  }
+  int k = top_k[r];
+  if (k <= 0 || k > V) k = V;
+  const float pp = top_p[r];
+  auto sat = [](unsigned long long t) -> uint32_t { return t > 0xffffffffull ? 0xffffffffu : (uint32_t)t; };
+
+  // ---- top-k threshold: largest key with count(x >= key) >= k.  Padding (-inf) is never counted: every
+  // threshold tried is above KEY_NEG once lo has passed it, and below that the real elements decide.
+  uint32_t kth = 0;
+  if (k < V) {
+    unsigned long long lo = KEY_NEG, hi = 0xffffffffull;   // count(>= KEY_NEG + 1) is the number of finite logits
+    for (int it = 0; it < 40 && lo < hi; ++it) {
+      const unsigned long long q = (hi - lo) >> 2, stp = q > 0 ? q : 1;
+      const unsigned long long t1 = lo + stp, t2 = t1 + stp, t3 = t2 + stp;
+      const uint32_t u1 = sat(t1), u2 = sat(t2), u3 = sat(t3);
+      int c1 = 0, c2 = 0, c3 = 0;
+#pragma unroll
+      for (int j = 0; j < SAMPLE_NPT; ++j) {
+        c1 += key[j] >= u1; c2 += key[j] >= u2; c3 += key[j] >= u3;
+      }
+      cluster_sum3_i(c1, c2, c3, &xchg, redi, par);
+      if (t3 <= hi && c3 >= k) lo = t3;
+      else if (t2 <= hi && c2 >= k) { lo = t2; hi = min(hi, t3 - 1); }
+      else if (t1 <= hi && c1 >= k) { lo = t1; hi = min(hi, t2 - 1); }
+      else hi = min(hi, t1 - 1);
+    }
+    kth = (uint32_t)lo;
+  }
+  if (kth <= KEY_NEG) kth = KEY_NEG + 1;          // the kept set never contains padding
+  // ---- softmax statistics over the kept set
+  ArgMax m{-INFINITY, 0x7fffffff};
+#pragma unroll
+  for (int j = 0; j < SAMPLE_NPT; ++j) {
+    if (key[j] >= kth) {
+      const float x = key2f(key[j]);
+      if (x > m.v) m = ArgMax{x, idx(j)};
+    }
+  }
+  const float mx = cluster_argmax(m, &xchg, red, par).v;
+  uint32_t thr = kth;
+  if (pp < 1.f) {
+    float z = 0.f, z2 = 0.f, z3 = 0.f;
+#pragma unroll
+    for (int j = 0; j < SAMPLE_NPT; ++j)
+      if (key[j] >= kth) z += __expf(key2f(key[j]) - mx);
+    cluster_sum3_f(z, z2, z3, &xchg, redf, par);
+    // largest key such that mass(x >= key) >= top_p * Z (ties at the threshold are all kept)
+    unsigned long long lo = kth, hi = f2key(mx);
+    const float want = pp * z;
+    for (int it = 0; it < 40 && lo < hi; ++it) {
+      const unsigned long long q = (hi - lo) >> 2, stp = q > 0 ? q : 1;
+      const unsigned long long t1 = lo + stp, t2 = t1 + stp, t3 = t2 + stp;
+      const uint32_t u1 = sat(t1), u2 = sat(t2), u3 = sat(t3);
+      float m1 = 0.f, m2 = 0.f, m3 = 0.f;
+#pragma unroll
+      for (int j = 0; j < SAMPLE_NPT; ++j) {
+        if (key[j] >= u1) {
+          const float e = __expf(key2f(key[j]) - mx);
+          m1 += e;
+          if (key[j] >= u2) m2 += e;
+          if (key[j] >= u3) m3 += e;
+        }
+      }
+      cluster_sum3_f(m1, m2, m3, &xchg, redf, par);
+      if (t3 <= hi && m3 >= want) lo = t3;
+      else if (t2 <= hi && m2 >= want) { lo = t2; hi = min(hi, t3 - 1); }
+      else if (t1 <= hi && m1 >= want) { lo = t1; hi = min(hi, t2 - 1); }
+      else hi = min(hi, t1 - 1);
+    }
+    thr = (uint32_t)lo;
+  }
+  // ---- Gumbel-max over the kept set
+  ArgMax a{-INFINITY, 0x7fffffff};
+#pragma unroll
+  for (int j = 0; j < SAMPLE_NPT; ++j) {
+    const int i = idx(j);
+    if (key[j] >= thr) {
+      float u = uniform != nullptr ? uniform[(size_t)r * V + i] : uniform_at(seed, step, r, i);
+      u = fminf(fmaxf(u, 1e-20f), 1.f - 1e-7f);
+      const float v = key2f(key[j]) - __logf(-__logf(u));
+      if (v > a.v || (v == a.v && i < a.i)) a = ArgMax{v, i};
+    }
+  }
+  a = cluster_argmax(a, &xchg, red, par);
+  if (cr == 0 && threadIdx.x == 0) out[r] = a.i < V ? a.i : 0;
+  cluster_arrive_release();
+  cluster_wait_acquire();
 }
 
 // logprob of chosen token + top-k logprobs (k <= 32) with fp32 logsumexp
@@ -443,6 +727,16 @@ extern "C" int b200_rejection_sample(const void* logits, int dtype, int R, int V
   return 0;
 }
 
+// B200_SAMPLE_CLUSTER=0 keeps the single-CTA sampler (read once)
+static bool sample_cluster_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("B200_SAMPLE_CLUSTER");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
 // dtype: 0 = bf16 logits, 1 = fp32 logits
 extern "C" int b200_argmax(const void* logits, int dtype, int R, int V, int ld, int* out, cudaStream_t stream) {
   if (R == 0) return 0;
@@ -459,6 +753,23 @@ extern "C" int b200_sample(const void* logits, int dtype, int R, int V, int ld, 
                            unsigned long long seed, unsigned long long step, const long long* step_ptr,
                            int* out, cudaStream_t stream) {
   if (R == 0) return 0;
+  if (dtype == 0 && V <= SAMPLE_CL * SAMPLE_CT * SAMPLE_NPT && V >= SAMPLE_CL * SAMPLE_CT * 2 &&
+      sample_cluster_enabled()) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(R * SAMPLE_CL);
+    cfg.blockDim = dim3(SAMPLE_CT);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = SAMPLE_CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, sample_cluster_kernel, (const __nv_bfloat16*)logits, ld, V, temperature,
+                                       top_k, top_p, uniform, seed, step, step_ptr, out));
+    return 0;
+  }
   if (dtype == 0)
     sample_kernel<__nv_bfloat16><<<R, SAMPLE_THREADS, 0, stream>>>((const __nv_bfloat16*)logits, ld, V,
                                                                   temperature, top_k, top_p, uniform, seed,
