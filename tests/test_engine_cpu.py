@@ -193,3 +193,28 @@ def test_device_wait_timeout_fails_the_step_not_the_engine():
     with pytest.raises(DeviceWaitTimeout) as ei:
         StepResult([], [], None, None, 0, status_host=torch.tensor([3], dtype=torch.int32)).get()
     assert ei.value.code == 3 and "accumulator" in str(ei.value)
+
+
+def test_scheduler_blocks_split_into_kernel_blocks_generate_the_same_tokens():
+    """64-token scheduler blocks over 16-token kernel pages: the block-table rows the kernels read list four
+    kernel blocks per scheduler block, and generation (prefix cache on) matches the plain configuration."""
+    import numpy as np
+
+    from vllm_torchtpu_b200 import SamplingParams
+    from vllm_torchtpu_b200.engine.llm import LLM
+    from vllm_torchtpu_b200.runner.kernel_block_table import KernelBlockTable
+    t = KernelBlockTable(2, 16, 4)
+    t.set_row(0, [3, 1])
+    t.append(0, [7])
+    assert t.table[0, :12].tolist() == [12, 13, 14, 15, 4, 5, 6, 7, 28, 29, 30, 31] and t.num_blocks[0] == 12
+    rng = np.random.RandomState(1)
+    shared = rng.randint(0, 1000, size=70).tolist()
+    prompts = [shared + rng.randint(0, 1000, size=n).tolist() for n in (5, 40)] + [rng.randint(0, 1000, size=9).tolist()]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    kw = dict(device="cpu", max_num_seqs=4, max_num_batched_tokens=64, block_size=16, init_dist=False,
+              num_gpu_blocks_override=64, enable_prefix_caching=True)
+    plain = [o.outputs[0].token_ids for o in LLM("tiny-llama", **kw).generate(prompts, sp)]
+    coarse_llm = LLM("tiny-llama", scheduler_block_size=64, **kw)
+    coarse = [o.outputs[0].token_ids for o in coarse_llm.generate(prompts, sp)]
+    assert coarse == plain
+    assert coarse_llm.engine.scheduler.block_size == 64 and coarse_llm.engine.scheduler.kv.pool.num_blocks == 16

@@ -346,6 +346,13 @@ class CacheConfig:
     # tokens the scheduler counts per block; under decode context parallelism a block holds block_size
     # tokens on every rank of the DCP group, block_size * dcp in all (0: block_size)
     tokens_per_block: int = 0
+    # tokens per scheduler block when it is a multiple of block_size (the kernels' page): a scheduler block
+    # then owns that many consecutive kernel blocks of the pool (0: same as block_size)
+    scheduler_block_size: int = 0
+
+    @property
+    def kernel_blocks_per_block(self) -> int:
+        return max(1, self.scheduler_block_size // self.block_size) if self.scheduler_block_size else 1
 
 
 @dataclass

@@ -20,7 +20,7 @@ class LLM:
                  tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1,
                  data_parallel_size: int = 1, enable_expert_parallel: bool = False,
                  prefill_context_parallel_size: int = 1, decode_context_parallel_size: int = 1,
-                 cp_kv_cache_interleave_size: int = 1,
+                 cp_kv_cache_interleave_size: int = 1, scheduler_block_size: int = 0,
                  max_model_len: Optional[int] = None, max_num_seqs: int = 256,
                  max_num_batched_tokens: int = 8192, block_size: int = 16,
                  gpu_memory_utilization: float = 0.9, num_gpu_blocks_override: Optional[int] = None,
@@ -60,7 +60,8 @@ class LLM:
             model=mc, parallel=pc,
             cache=CacheConfig(block_size, gpu_memory_utilization, num_gpu_blocks_override, None,
                               enable_prefix_caching, kv_cache_dtype,
-                              block_size * decode_context_parallel_size if decode_context_parallel_size > 1 else 0),
+                              block_size * decode_context_parallel_size if decode_context_parallel_size > 1
+                              else scheduler_block_size, scheduler_block_size),
             scheduler=SchedulerConfig(max_num_seqs, max_num_batched_tokens, True, scheduler_cls,
                                       async_scheduling),
             device=device, enforce_eager=enforce_eager,

@@ -86,6 +86,8 @@ class LLMEngine:
             dist.all_reduce(t, op=dist.ReduceOp.MIN, group=st.world.cpu_group)
             num_blocks = int(t.item())
         self.runner.init_kv_cache(num_blocks)
+        # the scheduler counts its own (possibly larger) blocks: each owns m consecutive kernel blocks
+        num_blocks //= cfg.cache.kernel_blocks_per_block
         self.connector = None
         if cfg.kv_transfer:
             from ..kv_transfer.factory import create_connector

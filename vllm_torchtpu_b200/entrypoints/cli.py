@@ -25,6 +25,8 @@ def add_engine_args(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--max-num-seqs", type=int, default=256)
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--scheduler-block-size", type=int, default=0,
+                    help="tokens per scheduler block (a multiple of --block-size, the kernels' page; 0: the same)")
     ap.add_argument("--gpu-memory-utilization", type=float, default=0.9)
     ap.add_argument("--num-gpu-blocks-override", type=int, default=None)
     ap.add_argument("--kv-cache-dtype", default="auto")
@@ -48,6 +50,7 @@ def make_llm(a):
                prefill_context_parallel_size=a.prefill_context_parallel_size,
                decode_context_parallel_size=a.decode_context_parallel_size,
                cp_kv_cache_interleave_size=a.cp_kv_cache_interleave_size,
+               scheduler_block_size=a.scheduler_block_size,
                max_model_len=a.max_model_len, max_num_seqs=a.max_num_seqs,
                max_num_batched_tokens=a.max_num_batched_tokens, block_size=a.block_size,
                gpu_memory_utilization=a.gpu_memory_utilization,

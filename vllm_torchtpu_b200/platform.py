@@ -169,6 +169,12 @@ class B200Platform:
         tp = p.tensor_parallel_size
         if not m.is_mla and m.num_kv_heads % tp and tp % m.num_kv_heads:
             raise ValueError(f"{m.num_kv_heads} kv heads cannot be sharded or replicated over tp={tp}")
+        if c.scheduler_block_size:
+            if c.scheduler_block_size % c.block_size:
+                raise ValueError("scheduler_block_size must be a multiple of block_size (the kernels' page)")
+            if p.decode_context_parallel_size > 1 or cfg.kv_transfer:
+                raise ValueError("scheduler_block_size does not combine with decode context parallelism or "
+                                 "KV transfer")
         dcp = p.decode_context_parallel_size
         if dcp > 1:
             # the ranks of a DCP group (consecutive TP ranks) must hold the same KV head: the cache of that

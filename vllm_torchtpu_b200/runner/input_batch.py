@@ -17,18 +17,21 @@ import torch
 
 
 class InputBatch:
-    def __init__(self, max_reqs: int, max_model_len: int, block_size: int):
+    def __init__(self, max_reqs: int, max_model_len: int, block_size: int, kernel_blocks_per_block: int = 1):
         self.max_reqs = max_reqs
         self.max_model_len = max_model_len
         self.block_size = block_size
-        self.max_blocks = -(-max_model_len // block_size) + 1
+        # rows list kernel blocks; a scheduler block may cover several (its last one may be partly unused)
+        self.max_blocks = -(-max_model_len // block_size) + kernel_blocks_per_block
         self.req_ids: list = [None] * max_reqs
         self.slot_of: dict = {}
         self.free_slots = list(range(max_reqs - 1, -1, -1))
         self.token_ids = np.zeros((max_reqs, max_model_len + 8), dtype=np.int32)
         self.num_known = np.zeros(max_reqs, dtype=np.int32)
-        self.block_table = np.zeros((max_reqs, self.max_blocks), dtype=np.int32)
-        self.num_blocks = np.zeros(max_reqs, dtype=np.int32)
+        from .kernel_block_table import KernelBlockTable
+        self.kbt = KernelBlockTable(max_reqs, self.max_blocks, kernel_blocks_per_block)
+        self.block_table = self.kbt.table
+        self.num_blocks = self.kbt.num_blocks
         self.temperature = np.zeros(max_reqs, dtype=np.float32)
         self.top_k = np.zeros(max_reqs, dtype=np.int32)
         self.top_p = np.ones(max_reqs, dtype=np.float32)
@@ -46,9 +49,7 @@ class InputBatch:
         n = len(toks)
         self.token_ids[slot, :n] = toks
         self.num_known[slot] = n
-        nb = len(block_ids)
-        self.block_table[slot, :nb] = block_ids
-        self.num_blocks[slot] = nb
+        self.kbt.set_row(slot, block_ids)
         sp = req.sampling_params
         self.temperature[slot] = sp.temperature
         self.top_k[slot] = sp.top_k if sp.top_k and sp.top_k > 0 else 0
@@ -58,10 +59,7 @@ class InputBatch:
     def append_blocks(self, slot: int, new_block_ids: list) -> None:
         if not new_block_ids:
             return
-        nb = int(self.num_blocks[slot])
-        k = len(new_block_ids)
-        self.block_table[slot, nb:nb + k] = new_block_ids
-        self.num_blocks[slot] = nb + k
+        self.kbt.append(slot, new_block_ids)
 
     def append_token(self, slot: int, token: int) -> None:
         n = int(self.num_known[slot])

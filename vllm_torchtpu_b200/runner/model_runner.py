@@ -145,7 +145,8 @@ class ModelRunner:
         self.dcp_interleave = max(1, cfg.parallel.cp_kv_cache_interleave_size)
         self.max_reqs = cfg.scheduler.max_num_seqs
         self.max_tokens = cfg.scheduler.max_num_batched_tokens
-        self.batch = InputBatch(self.max_reqs, self.mcfg.max_model_len, self.block_size)
+        self.batch = InputBatch(self.max_reqs, self.mcfg.max_model_len, self.block_size,
+                                cfg.cache.kernel_blocks_per_block)
         self.model = None
         self.kv_caches: list = []
         self.num_blocks = 0
