@@ -57,3 +57,71 @@ def test_engine_respects_choice_constraint():
     outs = llm.generate([[1, 2, 3, 4], [5, 6, 7]], [sp, free])
     assert outs[0].outputs[0].token_ids in ([11, 12, 13, 0], [500, 0])
     assert len(outs[1].outputs[0].token_ids) == 4
+
+
+def test_json_schema_regex_accepts_exactly_the_schema():
+    import json
+
+    import regex
+
+    from vllm_torchtpu_b200.structured.json_schema import any_json_object_regex, schema_to_regex
+    schema = {
+        "type": "object",
+        "properties": {
+            "name": {"type": "string", "maxLength": 8},
+            "age": {"type": "integer"},
+            "tags": {"type": "array", "items": {"enum": ["a", "b"]}, "minItems": 1, "maxItems": 3},
+            "score": {"type": ["number", "null"]},
+            "address": {"$ref": "#/$defs/addr"},
+        },
+        "required": ["name", "age"],
+        "$defs": {"addr": {"type": "object", "properties": {"zip": {"type": "string", "pattern": "^[0-9]{5}$"}},
+                           "required": ["zip"]}},
+    }
+    rx = regex.compile(schema_to_regex(schema))
+    good = [
+        {"name": "ann", "age": 3},
+        {"name": "", "age": -12, "tags": ["a", "b"], "score": 1.5e3},
+        {"name": "x", "age": 0, "score": None, "address": {"zip": "12345"}},
+    ]
+    for g in good:
+        assert rx.fullmatch(json.dumps(g)) is not None, g
+        assert rx.fullmatch(json.dumps(g, separators=(",", ":"))) is not None, g
+    bad = [
+        '{"age": 3}',                                      # required property missing
+        '{"name": "toolongname", "age": 3}',               # maxLength
+        '{"name": "a", "age": 3.5}',                       # integer
+        '{"name": "a", "age": 3, "tags": []}',             # minItems
+        '{"name": "a", "age": 3, "tags": ["c"]}',          # enum
+        '{"name": "a", "age": 3, "extra": 1}',             # undeclared property
+        '{"age": 3, "name": "a"}',                         # declaration order
+        '{"name": "a", "age": 3, "address": {"zip": "1234"}}',
+    ]
+    for b in bad:
+        assert rx.fullmatch(b) is None, b
+    # a prefix of a valid text is a partial match (what the token mask is built from)
+    assert rx.fullmatch('{"name": "an', partial=True) is not None
+    anyobj = regex.compile(any_json_object_regex())
+    assert anyobj.fullmatch('{"a": [1, {"b": null}], "c": "d"}') is not None
+    assert anyobj.fullmatch('[1, 2]') is None
+
+
+def test_engine_generates_json_that_satisfies_a_schema():
+    import json
+
+    from vllm_torchtpu_b200 import SamplingParams
+    from vllm_torchtpu_b200.engine.llm import LLM
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=2, init_dist=False)
+    V = llm.engine.cfg.model.vocab_size
+    # a toy vocabulary: JSON punctuation, digits, letters, and filler tokens that never fit
+    pieces = ['{', '}', '"', ':', ',', ' ', 'ok', 'n', 'true', 'false', '0', '1', '7', '42', 'x', 'y']
+    vocab = pieces + [f"<{i}>" for i in range(V - len(pieces))]
+    eos = V - 1
+    llm.engine.vocab_strings, llm.engine.eos_token_id = vocab, eos
+    schema = {"type": "object", "properties": {"ok": {"type": "boolean"}, "n": {"type": "integer"}},
+              "required": ["ok", "n"]}
+    sp = SamplingParams(temperature=0.0, max_tokens=40, structured={"json": schema}, stop_token_ids=[eos])
+    out = llm.generate([[1, 2, 3]], sp)[0].outputs[0].token_ids
+    text = "".join(vocab[t] for t in out if t != eos)
+    obj = json.loads(text)
+    assert set(obj) == {"ok", "n"} and isinstance(obj["ok"], bool) and isinstance(obj["n"], int)

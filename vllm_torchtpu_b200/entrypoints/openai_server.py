@@ -18,6 +18,25 @@ from ..sampling_params import SamplingParams
 from .async_engine import AsyncEngine
 
 
+def _structured_spec(body: dict):
+    """``structured_outputs`` / ``guided`` pass through; ``guided_json`` / ``guided_regex`` / ``guided_choice`` and
+    the OpenAI ``response_format`` (``json_schema`` / ``json_object``) are mapped onto the same spec."""
+    spec = body.get("structured_outputs") or body.get("guided")
+    if spec:
+        return spec
+    if body.get("guided_json") is not None:
+        return {"json": body["guided_json"]}
+    if body.get("guided_regex"):
+        return {"regex": body["guided_regex"]}
+    rf = body.get("response_format") or {}
+    if rf.get("type") == "json_schema":
+        js = rf.get("json_schema") or {}
+        return {"json": js.get("schema", js)}
+    if rf.get("type") == "json_object":
+        return {"json_object": True}
+    return None
+
+
 def _logprobs_from_body(body: dict):
     """Completions: ``logprobs`` = number of alternatives.  Chat: ``logprobs`` is a flag and
     ``top_logprobs`` the number."""
@@ -41,7 +60,7 @@ def _sampling_from_body(body: dict) -> SamplingParams:
         min_tokens=int(body.get("min_tokens", 0) or 0), ignore_eos=bool(body.get("ignore_eos", False)),
         stop_token_ids=list(body.get("stop_token_ids") or []), logprobs=_logprobs_from_body(body),
         prompt_logprobs=body.get("prompt_logprobs"), lora_name=body.get("lora_name"),
-        seed=body.get("seed"), structured=body.get("structured_outputs") or body.get("guided") or None)
+        seed=body.get("seed"), structured=_structured_spec(body))
 
 
 def build_app(engine, model_name: str, tokenizer=None):

@@ -117,10 +117,18 @@ class StructuredDecodingManager:
     def add_request(self, request_id: str, spec: dict) -> None:
         if "choice" in spec:
             self.grammars[request_id] = ChoiceGrammar(spec["choice"], self.eos)
-        elif "regex" in spec:
+        elif "regex" in spec or "json" in spec or spec.get("json_object"):
             if self.vocab is None:
-                raise ValueError("regex-constrained decoding needs the tokenizer vocabulary")
-            self.grammars[request_id] = RegexGrammar(spec["regex"], self.vocab, self.eos)
+                raise ValueError("regex- and schema-constrained decoding need the tokenizer vocabulary")
+            if "regex" in spec:
+                pattern = spec["regex"]
+            elif "json" in spec:
+                from .json_schema import schema_to_regex
+                pattern = schema_to_regex(spec["json"])
+            else:
+                from .json_schema import any_json_object_regex
+                pattern = any_json_object_regex()
+            self.grammars[request_id] = RegexGrammar(pattern, self.vocab, self.eos)
         else:
             raise ValueError(f"unsupported structured output spec: {sorted(spec)}")
 
