@@ -80,11 +80,11 @@ def test_embedding_pooling_matches_dense_hidden_states():
     vocab = llm.engine.cfg.model.vocab_size
     prompts = [rng.randint(0, vocab, size=n).tolist() for n in (7, 50)]        # 50 > 32: two chunks
     model = llm.engine.runner.model
-    for mode in ("last", "mean"):
+    for mode in ("last", "mean", "max", "cls", "all"):
         got = llm.embed(prompts, pooling=mode, normalize=False)
         for p, g in zip(prompts, got):
             h = dense_llama_hidden(model, p)                                    # [len, H] after the final norm
-            want = h[-1] if mode == "last" else h.mean(0)
+            want = {"last": h[-1], "mean": h.mean(0), "max": h.max(0).values, "cls": h[0], "all": h}[mode]
             torch.testing.assert_close(torch.tensor(g), want.float(), rtol=2e-3, atol=2e-3)
     unit = llm.embed(prompts[:1])[0]
     assert abs(sum(a * a for a in unit) - 1.0) < 1e-4
@@ -218,3 +218,15 @@ def test_scheduler_blocks_split_into_kernel_blocks_generate_the_same_tokens():
     coarse = [o.outputs[0].token_ids for o in coarse_llm.generate(prompts, sp)]
     assert coarse == plain
     assert coarse_llm.engine.scheduler.block_size == 64 and coarse_llm.engine.scheduler.kv.pool.num_blocks == 16
+
+
+def test_kv_block_counts_are_reconciled_per_pipeline_stage():
+    import pytest
+
+    from vllm_torchtpu_b200.engine.kv_block_agreement import reconcile, within_tolerance
+    assert within_tolerance([1000, 1003, 998]) and not within_tolerance([1000, 990])
+    assert within_tolerance([100000, 100400]) and not within_tolerance([100000, 100600])      # 0.5 %
+    # two stages of two ranks: each stage settles on its minimum, the engine on the smaller stage
+    assert reconcile({0: 1000, 1: 1002, 2: 800, 3: 799}, {0: 0, 1: 0, 2: 1, 3: 1}) == 799
+    with pytest.raises(ValueError, match="stage 1"):
+        reconcile({0: 1000, 1: 1002, 2: 800, 3: 700}, {0: 0, 1: 0, 2: 1, 3: 1})

@@ -86,7 +86,7 @@ def test_embeddings_and_lora_adapter_routes(client, tmp_path):
     data = r.json()["data"]
     assert len(data) == 2 and abs(sum(a * a for a in data[0]["embedding"]) - 1.0) < 1e-3
     assert r.json()["usage"]["prompt_tokens"] == 7
-    assert client.post("/v1/embeddings", json={"input": [1, 2], "pooling": "max"}).status_code == 400
+    assert client.post("/v1/embeddings", json={"input": [1, 2], "pooling": "median"}).status_code == 400
     body = {"prompt": [3, 1, 4, 1, 5, 9, 2, 6], "max_tokens": 4, "temperature": 0, "ignore_eos": True}
     base = client.post("/v1/completions", json=body).json()["choices"][0]["token_ids"]
     g = torch.Generator().manual_seed(0)
@@ -104,3 +104,38 @@ def test_embeddings_and_lora_adapter_routes(client, tmp_path):
     assert client.post("/v1/completions", json=body).json()["choices"][0]["token_ids"] == base
     assert client.post("/v1/unload_lora_adapter", json={"lora_name": "ad"}).json()["unloaded"]
     assert client.post("/v1/load_lora_adapter", json={"lora_name": "x", "lora_path": "/nonexistent"}).status_code == 400
+
+
+def test_chat_prompt_continue_final_message_with_and_without_template_support():
+    import pytest
+
+    from vllm_torchtpu_b200.entrypoints.chat_template import build_chat_prompt
+
+    class Tok:
+        """Template: <role>content</s> per message, generation prompt '<assistant>'."""
+        supports_continue = True
+
+        def apply_chat_template(self, messages, add_generation_prompt=False, tokenize=True,
+                                continue_final_message=None, **kw):
+            if continue_final_message is not None and not self.supports_continue:
+                raise TypeError("unexpected keyword continue_final_message")
+            text = ""
+            for i, m in enumerate(messages):
+                last = i == len(messages) - 1
+                text += f"<{m['role']}>{m['content']}" + ("" if last and continue_final_message else "</s>")
+            if add_generation_prompt:
+                text += "<assistant>"
+            return [ord(c) for c in text] if tokenize else text
+
+    enc = lambda s: [ord(c) for c in s]
+    dec = lambda ids: "".join(chr(i) for i in ids)
+    msgs = [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "The answer is"}]
+    tok = Tok()
+    assert dec(build_chat_prompt(tok, enc, msgs[:1])) == "<user>hi</s><assistant>"
+    want = "<user>hi</s><assistant>The answer is"
+    assert dec(build_chat_prompt(tok, enc, msgs, continue_final_message=True)) == want
+    tok.supports_continue = False                      # a template that always closes the last message
+    assert dec(build_chat_prompt(tok, enc, msgs, continue_final_message=True)) == want
+    assert dec(build_chat_prompt(None, enc, msgs, continue_final_message=True)) == "user: hi\\nassistant: The answer is"
+    with pytest.raises(ValueError):
+        build_chat_prompt(tok, enc, msgs[:1], continue_final_message=True)

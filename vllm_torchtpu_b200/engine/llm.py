@@ -15,6 +15,9 @@ from ..sampling_params import SamplingParams
 from .llm_engine import LLMEngine
 
 
+POOLING_MODES = ("last", "mean", "max", "cls", "all")     # "all": one vector per prompt token
+
+
 class LLM:
     def __init__(self, model: Union[str, ModelConfig] = "tiny-llama", *, tokenizer=None,
                  tensor_parallel_size: int = 1, pipeline_parallel_size: int = 1,
@@ -92,8 +95,8 @@ class LLM:
     def embed(self, prompts: Sequence, pooling: str = "last", normalize: bool = True) -> list:
         """Pooled final hidden state per prompt (``last`` token or ``mean`` over the prompt), optionally
         L2-normalised: the embedding-model path (reference: src/vllm_torchtpu/runner/tpu_pooling.py)."""
-        if pooling not in ("last", "mean"):
-            raise ValueError("pooling must be 'last' or 'mean'")
+        if pooling not in POOLING_MODES:
+            raise ValueError(f"pooling must be one of {POOLING_MODES}")
         sp = SamplingParams(temperature=0.0, max_tokens=1, pooling=pooling)
         outs = self.generate(prompts, sp)
         vecs = []

@@ -81,10 +81,9 @@ class LLMEngine:
         self.runner.load_model()
         num_blocks = self.runner.determine_num_blocks()
         if st.world_size > 1 and st.world.cpu_group is not None:
-            import torch.distributed as dist
-            t = torch.tensor([num_blocks], dtype=torch.int64)
-            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=st.world.cpu_group)
-            num_blocks = int(t.item())
+            # the ranks of a pipeline stage must agree within a tolerance; everyone adopts the minimum
+            from .kv_block_agreement import agree_over_group
+            num_blocks = agree_over_group(num_blocks, st.rank, st.pp.rank_in_group, st.world.cpu_group)
         self.runner.init_kv_cache(num_blocks)
         # the scheduler counts its own (possibly larger) blocks: each owns m consecutive kernel blocks
         num_blocks //= cfg.cache.kernel_blocks_per_block

@@ -86,11 +86,15 @@ def build_app(engine, model_name: str, tokenizer=None):
             return " ".join(str(i) for i in ids)
         return tokenizer.decode(ids)
 
-    def chat_prompt(messages: list) -> list:
-        if tokenizer is not None and hasattr(tokenizer, "apply_chat_template"):
-            return tokenizer.apply_chat_template(messages, add_generation_prompt=True, tokenize=True)
-        text = "\n".join(f"{m.get('role', 'user')}: {m.get('content', '')}" for m in messages) + "\nassistant:"
-        return encode(text)
+    def chat_prompt(body: dict) -> list:
+        from .chat_template import build_chat_prompt
+        try:
+            return build_chat_prompt(tokenizer, encode, body.get("messages", []),
+                                     add_generation_prompt=body.get("add_generation_prompt", True),
+                                     continue_final_message=bool(body.get("continue_final_message", False)),
+                                     chat_template_kwargs=body.get("chat_template_kwargs"))
+        except ValueError as e:
+            raise HTTPException(400, str(e))
 
     async def run(body: dict, prompt_ids: list, chat: bool):
         try:
@@ -172,7 +176,7 @@ def build_app(engine, model_name: str, tokenizer=None):
     @app.post("/v1/chat/completions")
     async def chat_completions(request: Request):
         body = await request.json()
-        return await run(body, chat_prompt(body.get("messages", [])), chat=True)
+        return await run(body, chat_prompt(body), chat=True)
 
     @app.post("/v1/embeddings")
     async def embeddings(request: Request):
@@ -184,8 +188,8 @@ def build_app(engine, model_name: str, tokenizer=None):
         many = isinstance(inp, list) and inp and not isinstance(inp[0], int)
         prompts = inp if many else [inp]
         pooling = body.get("pooling", "last")
-        if pooling not in ("last", "mean"):
-            raise HTTPException(400, "pooling must be 'last' or 'mean'")
+        if pooling not in ("last", "mean", "max", "cls"):
+            raise HTTPException(400, "pooling must be 'last', 'mean', 'max' or 'cls'")
         data, used = [], 0
         for i, pr in enumerate(prompts):
             ids = encode(pr)

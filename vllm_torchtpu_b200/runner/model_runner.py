@@ -576,6 +576,16 @@ class ModelRunner:
                 part = hn[lo:hi].sum(0)
                 acc[0] = part if acc[0] is None else acc[0] + part
                 acc[1] += hi - lo
+            elif mode == "max":
+                part = hn[lo:hi].max(0).values
+                acc[0], acc[1] = (part if acc[0] is None else torch.maximum(acc[0], part)), 1
+            elif mode == "cls":
+                if acc[0] is None:                   # the first row of the first chunk
+                    acc[0], acc[1] = hn[lo].clone(), 1
+            elif mode == "all":
+                # one vector per prompt token (token classification / late-interaction retrieval)
+                acc[0] = hn[lo:hi].clone() if acc[0] is None else torch.cat([acc[0], hn[lo:hi]], 0)
+                acc[1] = 1
             elif last_chunk:
                 acc[0], acc[1] = hn[hi - 1].clone(), 1
         self._pool_plan = None

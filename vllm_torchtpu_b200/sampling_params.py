@@ -23,7 +23,7 @@ class SamplingParams:
     seed: Optional[int] = None
     structured: Optional[dict] = None   # {"regex": ...} | {"json": schema} | {"choice": [...]}
     lora_name: Optional[str] = None
-    pooling: Optional[str] = None        # "last" or "mean": return a pooled hidden state of the prompt
+    pooling: Optional[str] = None        # last | mean | max | cls | all: return pooled hidden state(s) of the prompt
 
     @property
     def greedy(self) -> bool:
