@@ -136,6 +136,6 @@ def test_chat_prompt_continue_final_message_with_and_without_template_support():
     assert dec(build_chat_prompt(tok, enc, msgs, continue_final_message=True)) == want
     tok.supports_continue = False                      # a template that always closes the last message
     assert dec(build_chat_prompt(tok, enc, msgs, continue_final_message=True)) == want
-    assert dec(build_chat_prompt(None, enc, msgs, continue_final_message=True)) == "user: hi\\nassistant: The answer is"
+    assert dec(build_chat_prompt(None, enc, msgs, continue_final_message=True)) == "user: hi\nassistant: The answer is"
     with pytest.raises(ValueError):
         build_chat_prompt(tok, enc, msgs[:1], continue_final_message=True)
