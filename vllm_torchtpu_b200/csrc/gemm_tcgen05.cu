@@ -1044,6 +1044,34 @@ extern "C" int b200_make_tmap_2d(void* out_map, const void* ptr, int elem_bytes,
   return 0;
 }
 
+// 2D byte tensor map without swizzle: the box lands in shared memory as dense rows of box_cols bytes
+// (box_cols a multiple of 16).  For operands that threads read back themselves.
+extern "C" int b200_make_tmap_2d_bytes_linear(void* out_map, const void* ptr, uint64_t rows, uint64_t cols,
+                                              uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols) {
+  auto fn = b200::get_encode_fn();
+  if (!fn) {
+    b200_set_last_error("cuTensorMapEncodeTiled not available", __FILE__, __LINE__);
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (row_stride_bytes & 15) || (box_cols & 15)) {
+    b200_set_last_error("TMA operand must be 16-byte aligned with 16-byte multiple row stride and box width",
+                        __FILE__, __LINE__);
+    return -2;
+  }
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr),
+                  gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    b200_set_last_error("cuTensorMapEncodeTiled failed", __FILE__, __LINE__);
+    return (int)r;
+  }
+  return 0;
+}
+
 // bf16 3D tensor map: dims (x fastest, y, z), byte strides of y and z, box (bx, by, bz), SWIZZLE_128B.
 extern "C" int b200_make_tmap_3d_bf16(void* out_map, const void* ptr, uint64_t dx, uint64_t dy, uint64_t dz,
                                       uint64_t stride_y_bytes, uint64_t stride_z_bytes, uint32_t bx, uint32_t by,

@@ -22,6 +22,8 @@ int b200_gemm_bf16(const void* X, const void* W, void* Y, const void* bias, int 
 
 int b200_make_tmap_2d(void* out_map, const void* ptr, int elem_bytes, uint64_t rows, uint64_t cols,
                       uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols);
+int b200_make_tmap_2d_bytes_linear(void* out_map, const void* ptr, uint64_t rows, uint64_t cols,
+                                   uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols);
 int b200_make_tmap_3d_bf16(void* out_map, const void* ptr, uint64_t dx, uint64_t dy, uint64_t dz,
                            uint64_t stride_y_bytes, uint64_t stride_z_bytes, uint32_t bx, uint32_t by,
                            uint32_t bz);

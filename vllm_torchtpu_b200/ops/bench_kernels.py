@@ -320,6 +320,46 @@ def bench_fp8_gemm(T, N, K, iters=20) -> list:
     return rows
 
 
+def bench_w4a16(T, N, K, iters=20) -> list:
+    """mxfp4 / nvfp4 weights expanded in shared memory in front of tcgen05 (W4A16) next to the bf16 GEMM of
+    the same shape.  Roofline: packed weight + scale + activation + output bytes over the measured copy
+    bandwidth, FLOPs over the measured bf16 GEMM rate."""
+    from . import cuda
+    from ..quantization import fp4 as q
+    pk, tag = peaks()
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05)
+    rows = []
+    flops = 2.0 * T * N * K
+    for fmt in ("mxfp4", "nvfp4"):
+        if fmt == "mxfp4":
+            wp, sc = q.quantize_mxfp4(w)
+            gs = None
+            wd = q.dequantize_mxfp4(wp, sc)
+        else:
+            wp, sc, gs = q.quantize_nvfp4(w)
+            wd = q.dequantize_nvfp4(wp, sc, gs)
+        wp, sc = wp.contiguous(), sc.contiguous()
+        ms = time_fn(lambda: cuda.w4a16_gemm(x, wp, sc, fmt, gs), iters)
+        err = None
+        if T * N <= (1 << 24):
+            y = cuda.w4a16_gemm(x, wp, sc, fmt, gs)
+            want = x.float() @ wd.bfloat16().float().t()
+            err = float((y.float() - want).abs().max() / want.abs().max())
+        byts = float(N * K // 2 + sc.numel() + 2 * T * K + 2 * T * N)
+        t_roof = max(flops / (pk["bf16_tflops"] * 1e12), byts / (pk["hbm_gbs"] * 1e9)) * 1e3
+        rows.append({"op": "w4a16-gemm", "fmt": fmt, "T": T, "N": N, "K": K, "ms": round(ms, 4),
+                     "tflops": round(flops / ms / 1e9, 1), "gbs": round(byts / ms / 1e6, 1),
+                     "roofline_ms": round(t_roof, 4), "frac_of_roofline": round(t_roof / ms, 3), "peaks": tag,
+                     "rel_err": err, "status": cuda.check_status()})
+    wb = w.bfloat16()
+    y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    ms = time_fn(lambda: cuda.gemm(x, wb, out=y), iters)
+    rows.append({"op": "w4a16-gemm", "fmt": "bf16 weights (same shape)", "T": T, "N": N, "K": K, "ms": round(ms, 4),
+                 "tflops": round(flops / ms / 1e9, 1)})
+    return rows
+
+
 def bench_misc(iters=20) -> list:
     """Element-wise, routing, sampling and MLA kernels at serving shapes: device time (graph replay, L2
     flushed), algorithmic bytes over the measured copy bandwidth."""
@@ -477,7 +517,7 @@ LLAMA8B_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "fp8-gemm", "misc", "gemm-swiglu", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill",
+    ap.add_argument("what", choices=["gemm", "fp8-gemm", "w4a16-gemm", "misc", "gemm-swiglu", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill",
                                      "decode-layer", "decode-model", "all"])
     ap.add_argument("--T", type=int, default=64)
     ap.add_argument("--N", type=int, default=4096)
@@ -502,6 +542,9 @@ def main():
                     continue
                 for impl in ("tcgen05", "cublas"):
                     print(json.dumps(bench_gemm(T, N, K, max(5, a.iters // 2), impl, check=(T <= 1024))))
+    if a.what == "w4a16-gemm":
+        for r in bench_w4a16(a.T, a.N, a.K, a.iters):
+            print(json.dumps(r))
     if a.what == "misc":
         for r in bench_misc(a.iters):
             print(json.dumps(r))

@@ -684,6 +684,7 @@ from .cuda_moe import (EpState, gemm_swiglu, grouped_gemm, moe_experts, moe_expe
 from .cuda_fp8 import (fp8_block_gemm, fp8_block_gemm_push, fp8_block_gemm_push_quantised,  # noqa: E402,F401
                        fp8_block_gemm_quantised, fp8_per_tensor_gemm, fp8_rowwise_gemm, grouped_fp8_gemm, int8_gemm,  # noqa: E402,F401
                        moe_experts_ep_fp8, moe_experts_fp8, quant_act_1x128, quant_act_int8, quant_rows_1x128)
+from .cuda_fp4 import grouped_w4a16_gemm, moe_experts_w4a16, w4a16_gemm  # noqa: E402,F401
 from .cuda_gdn import gdn_forward, kda_forward, short_conv  # noqa: E402,F401
 from .cuda_mla import (mla_absorb, mla_paged_attention, mla_unabsorb, mla_write_cache,  # noqa: E402,F401
                        permute_rows, rope_rows)

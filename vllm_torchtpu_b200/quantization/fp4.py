@@ -89,7 +89,13 @@ class _Fp4Base(LinearMethodBase):
             raise NotImplementedError("pre-packed fp4 checkpoints are re-sharded by the loader")
         self._set(layer, layer.shard_of(full_weight.to(layer.device)))
 
+    fmt = None            # name of the kernel format, set by the subclasses
+
     def apply(self, layer, x, bias=None):
+        if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 64 == 0:
+            # W4A16 on the tensor cores: the packed weight is expanded tile by tile in shared memory
+            return ops.cuda_ops().w4a16_gemm(x, layer.weight, layer.weight_scale, self.fmt,
+                                             layer.weight_global_scale, bias)
         w = self.dequant(layer).to(x.dtype)
         y = ops.gemm(x, w)
         return y if bias is None else (y.float() + bias.float()).to(y.dtype)
@@ -99,6 +105,8 @@ class _Fp4Base(LinearMethodBase):
 
 
 class Mxfp4LinearMethod(_Fp4Base):
+    fmt = "mxfp4"
+
     def _set(self, layer, w):
         layer.weight, layer.weight_scale = quantize_mxfp4(w)
 
@@ -107,6 +115,8 @@ class Mxfp4LinearMethod(_Fp4Base):
 
 
 class Nvfp4LinearMethod(_Fp4Base):
+    fmt = "nvfp4"
+
     def _set(self, layer, w):
         layer.weight, layer.weight_scale, layer.weight_global_scale = quantize_nvfp4(w)
 
@@ -152,6 +162,10 @@ class Mxfp4MoEMethod:
         moe.w2[local_e], moe.w2_scale[local_e] = q, s
 
     def apply(self, moe, x, topk_ids, topk_w):
+        I, H = moe.intermediate_size, moe.hidden_size
+        if x.is_cuda and x.dtype == torch.bfloat16 and H % 128 == 0 and I % 128 == 0:
+            return ops.cuda_ops().moe_experts_w4a16(x, moe.w13, moe.w13_scale, moe.w2, moe.w2_scale, topk_ids, topk_w,
+                                                    moe.expert_range[0], "mxfp4")
         w13 = dequantize_mxfp4(moe.w13, moe.w13_scale).to(x.dtype)
         w2 = dequantize_mxfp4(moe.w2, moe.w2_scale).to(x.dtype)
         if x.is_cuda:
