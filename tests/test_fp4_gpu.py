@@ -58,3 +58,24 @@ def test_w4a16_moe_experts_match_dequantised_experts():
     want = ref.moe_experts(x, d13, d2, ids, w, 0)
     err = (got.float() - want.float()).abs().max().item()
     assert err <= 3e-2 * want.float().abs().max().item() + 1e-2, err
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+def test_dequant_kernel_is_bit_exact_and_large_token_counts_use_it(fmt):
+    from vllm_torchtpu_b200.ops import cuda_fp4
+    g = torch.Generator(device=DEV).manual_seed(2)
+    w = torch.randn(384, 512, device=DEV, generator=g) * 0.3
+    w[0, :32] *= 200.0                                   # a group with a large scale
+    if fmt == "mxfp4":
+        wp, sc = q.quantize_mxfp4(w)
+        gs, wd = None, q.dequantize_mxfp4(wp, sc)
+    else:
+        wp, sc, gs = q.quantize_nvfp4(w)
+        wd = q.dequantize_nvfp4(wp, sc, gs)
+    got = cuda_fp4.dequant_w4(wp.contiguous(), sc.contiguous(), fmt, gs)
+    torch.cuda.synchronize()
+    assert torch.equal(got, wd.bfloat16())
+    x = torch.randn(cuda_fp4.DEQUANT_FROM_TOKENS + 5, 512, device=DEV, generator=g).bfloat16()
+    y = cu().w4a16_gemm(x, wp.contiguous(), sc.contiguous(), fmt, gs)
+    want = x.float() @ wd.bfloat16().float().t()
+    assert (y.float() - want).abs().max() <= 1e-2 * want.abs().max() + 1e-2

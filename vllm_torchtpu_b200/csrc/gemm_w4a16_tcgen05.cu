@@ -5,15 +5,20 @@
 //                                                                       nvfp4: G = 16, scale = e4m3 * global
 //
 // The weight never exists in bf16 in global memory: a tile is expanded in shared memory, in front of the
-// tensor core.  Roles of a CTA (320 threads), persistent over (weight tile, token tile) pairs:
+// tensor core.  Roles of a CTA (704 threads), persistent over (weight tile, token tile) pairs:
 //
 //   warp 0      TMA producer: packed weight bytes [128 rows x 32 B] and the activation tile [BN x 128 B]
-//   warps 2-5   expansion: thread = weight row; 64 nibbles -> e2m1 value x group scale -> bf16, written as
-//               the 128-byte K-major row of the UMMA A operand at its SWIZZLE_128B position, then
-//               fence.proxy.async and an arrive on the stage's "expanded" barrier
-//   warp 1      tcgen05.mma kind::f16 (M 128 = weight rows, N = tokens, K 16 x 4 per stage), accumulators
-//               double-buffered in TMEM
-//   warps 6-9   epilogue: TMEM -> bf16 -> Y (+ bias)
+//   warps 2-17  expansion, four groups of four warps, K blocks dealt round-robin: thread = weight row; 64 nibbles ->
+//               e2m1 value x group scale -> bf16 pairs, stored with tcgen05.st into a slot of TENSOR MEMORY (lane = weight row, 32-bit column = two
+//               consecutive k): the A operand never touches shared memory, so there is no generic-to-async
+//               proxy fence per K block
+//   warp 1      tcgen05.mma kind::f16 with A from tensor memory and B (the activation tile) from shared
+//               memory (M 128 = weight rows, N = tokens, K 16 x 4 per stage), accumulators double-buffered
+//               in TMEM columns [0, 2 BN), eight A slots of 32 columns in [256, 512)
+//   warps 18-21 epilogue: TMEM -> bf16 -> Y (+ bias)
+//
+// Few output tiles (decode-sized N): split-K as a thread-block cluster, the CTAs of a cluster take K ranges
+// of one tile, leave fp32 partials in their shared memory and sum them over DSMEM.
 //
 // Same orientation as the bf16 GEMM (weights are the 128-row operand, so decode batches keep full MMA
 // rows).  Grouped mode takes device-side row offsets per expert.  Every wait is bounded.
@@ -34,20 +39,31 @@ namespace w4 {
 constexpr int BM = 128;            // weight rows per tile (UMMA M)
 constexpr int BK = 64;             // K elements per stage: one 128-byte bf16 row
 constexpr int RAW_BYTES = BM * BK / 2;
-constexpr int A_BYTES = BM * BK * 2;
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 704;     // TMA warp, MMA warp, 16 expansion warps, 4 epilogue warps
+constexpr int EXP_GROUPS = 4;        // expansion groups of four warps, K blocks dealt round-robin
+constexpr int EPI_WARP0 = 2 + 4 * EXP_GROUPS;
 constexpr int MAX_GROUPS = 1024;
+
+// Two rings: load slots in shared memory (packed weight bytes + activation tile) and expanded A tiles in
+// tensor memory (32 columns each).
+constexpr int A_STAGES = 8;
+constexpr int A_COLS = BK / 2;                  // 32-bit columns of one expanded tile
+constexpr int A_TMEM_BASE = 256;                // accumulators use columns [0, 256)
 
 template <int BN>
 struct Cfg {
   static constexpr int B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = RAW_BYTES + A_BYTES + B_BYTES;      // multiples of 1024 each
+  static constexpr int STAGE_BYTES = RAW_BYTES + B_BYTES;                // load ring slot (multiple of 1024)
   static constexpr int STAGES_RAW = 196608 / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
+  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
+  static_assert(2 * BN <= A_TMEM_BASE, "accumulators and A slots share the 512 TMEM columns");
+  static_assert(STAGES >= EXP_GROUPS + 2,
+                "an expansion group publishes a block when it reaches its next one: the producer must run that far ahead");
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int BAR_BYTES = 512;
   static constexpr int PREFIX_BYTES = (MAX_GROUPS + 1) * 4 + 12;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + PREFIX_BYTES + 64 + 1024;
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int SMEM = RING_BYTES + BAR_BYTES + PREFIX_BYTES + 64 + 1024;
+  static constexpr int TMEM_COLS = 512;
 };
 
 struct Params {
@@ -60,21 +76,93 @@ struct Params {
   int n_tiles, t_tiles, kb_total;
   const int* group_off;              // grouped: int[num_groups + 1]
   int num_groups, w_rows_per_group, gs_per_group;
+  int splits, kb_per_split;          // cluster split-K (dense mode): work item = (tile, split)
 };
 
 struct Work {
-  int w_row, t_row, t_valid, n0;
+  int w_row, t_row, t_valid, n0, kb0, kb1;
 };
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp writes lane (base + i)
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// kind::f16 with the A operand in tensor memory (lane = row, column = two consecutive k), B in shared memory
+__device__ __forceinline__ void umma_f16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// e2m1 -> fp32 without a table: with the two exponent bits in the low bits of the fp32 exponent field and the
+// mantissa bit on top of the fraction, the fp32 value is e2m1 * 2^-126 for every code (the e = 0 codes are
+// fp32 subnormals, which the multiplies below handle exactly).  The 2^126 is undone in two exact steps so
+// that no realistic group scale overflows: 2^64 here, 2^62 folded into the group scale by the caller.
+// Byte j of `wd` holds elements 2j (low nibble) and 2j + 1 (high nibble); returns them as a bf16 pair.
+// Power-of-two group scales (mxfp4) stay in bf16: the same bit placement in a bf16 pair gives e2m1 * 2^-126
+// per half (bf16 has the fp32 exponent range), and two exact bf16x2 multiplies, by 2^64 and by the group
+// scale times 2^62, finish the job with a fifth of the instructions.  `s62x2` holds that scale in both halves.
+template <int J>
+__device__ __forceinline__ uint32_t e2m1_pair_to_bf16x2_pow2(uint32_t wd, uint32_t s62x2) {
+  // low nibble of byte J -> bits [8:6] and sign bit 15; high nibble -> bits [24:22] and sign bit 31
+  constexpr int LO = 6 - 8 * J, HI = 18 - 8 * J;
+  const uint32_t lo_b = LO >= 0 ? (wd << (LO >= 0 ? LO : 0)) : (wd >> (LO < 0 ? -LO : 0));
+  const uint32_t hi_b = HI >= 0 ? (wd << (HI >= 0 ? HI : 0)) : (wd >> (HI < 0 ? -HI : 0));
+  constexpr int SL = 12 - 8 * J, SH = 24 - 8 * J;            // nibble bit 3 -> bit 15 / bit 31
+  const uint32_t sl_b = SL >= 0 ? (wd << (SL >= 0 ? SL : 0)) : (wd >> (SL < 0 ? -SL : 0));
+  const uint32_t sh_b = wd << SH;
+  uint32_t v = (lo_b & 0x000001C0u) | (hi_b & 0x01C00000u) | (sl_b & 0x00008000u) | (sh_b & 0x80000000u);
+  uint32_t out;
+  asm("{\n\t"
+      ".reg .b32 t;\n\t"
+      "mul.bf16x2 t, %1, %2;\n\t"
+      "mul.bf16x2 %0, t, %3;\n\t"
+      "}"
+      : "=r"(out)
+      : "r"(v), "r"(0x5F805F80u), "r"(s62x2));              // 0x5F80 = 2^64 in bf16
+  return out;
+}
+
+template <int J>
+__device__ __forceinline__ uint32_t e2m1_pair_to_bf16x2(uint32_t wd, float scale62) {
+  constexpr int LO = 22 - 8 * J, HI = 18 - 8 * J;            // nibble bit 0 -> bit 22
+  const uint32_t lo_b = LO >= 0 ? (wd << (LO >= 0 ? LO : 0)) : (wd >> (LO < 0 ? -LO : 0));
+  const uint32_t hi_b = HI >= 0 ? (wd << (HI >= 0 ? HI : 0)) : (wd >> (HI < 0 ? -HI : 0));
+  // magnitude bits land on [24:22]; the sign bit (nibble bit 3) is 6 positions higher than bit 25
+  const uint32_t lo = (lo_b & 0x01C00000u) | (((wd >> (8 * J + 3)) & 1u) << 31);
+  const uint32_t hi = (hi_b & 0x01C00000u) | (((wd >> (8 * J + 7)) & 1u) << 31);
+  constexpr float TWO64 = 18446744073709551616.f;
+  __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(lo) * TWO64 * scale62,
+                                            __uint_as_float(hi) * TWO64 * scale62);
+  return *reinterpret_cast<uint32_t*>(&b2);
+}
 
 template <int BN>
 __device__ __forceinline__ Work get_work(int w, const Params& p, const int* s_prefix) {
   Work k;
   if (p.group_off == nullptr) {
-    const int n_tile = w % p.n_tiles, t_tile = w / p.n_tiles;
+    const int tile = w / p.splits, split = w - tile * p.splits;
+    const int n_tile = tile % p.n_tiles, t_tile = tile / p.n_tiles;
     k.w_row = n_tile * BM;
     k.n0 = n_tile * BM;
     k.t_row = t_tile * BN;
     k.t_valid = min(BN, p.T - k.t_row);
+    k.kb0 = split * p.kb_per_split;
+    k.kb1 = min(p.kb_total, k.kb0 + p.kb_per_split);
   } else {
     const int tt = w / p.n_tiles, n_tile = w - tt * p.n_tiles;
     int lo = 0, hi = p.num_groups;
@@ -88,6 +176,8 @@ __device__ __forceinline__ Work get_work(int w, const Params& p, const int* s_pr
     k.n0 = n_tile * BM;
     k.t_row = r0 + t_tile * BN;
     k.t_valid = min(BN, rows - t_tile * BN);
+    k.kb0 = 0;
+    k.kb1 = p.kb_total;
   }
   return k;
 }
@@ -100,23 +190,26 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
-  uint64_t* full = bars;                         // TMA bytes of the stage have landed
-  uint64_t* expanded = bars + STAGES;            // the A tile of the stage has been written
-  uint64_t* empty = bars + 2 * STAGES;           // the MMAs that read the stage have completed
-  uint64_t* tfull = bars + 3 * STAGES;
-  uint64_t* tempty = bars + 3 * STAGES + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::RING_BYTES);
+  uint64_t* full = bars;                         // load slot: TMA bytes have landed
+  uint64_t* empty = bars + STAGES;               // load slot: packed bytes read (4 warps) and X consumed (1 commit)
+  uint64_t* afull = bars + 2 * STAGES;           // A slot: expanded tile written (4 warps)
+  uint64_t* aempty = bars + 2 * STAGES + A_STAGES;   // A slot: the MMAs that read it have completed
+  uint64_t* tfull = bars + 2 * STAGES + 2 * A_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* s_prefix = reinterpret_cast<int*>(smem + STAGES * C::STAGE_BYTES + C::BAR_BYTES);
-  float* s_lut = reinterpret_cast<float*>(smem + STAGES * C::STAGE_BYTES + C::BAR_BYTES + C::PREFIX_BYTES);
+  int* s_prefix = reinterpret_cast<int*>(smem + C::RING_BYTES + C::BAR_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
       mbar_init(&full[i], 1);
-      mbar_init(&expanded[i], 4);
-      mbar_init(&empty[i], 1);
+      mbar_init(&empty[i], 5);
+    }
+    for (int i = 0; i < A_STAGES; ++i) {
+      mbar_init(&afull[i], 4);
+      mbar_init(&aempty[i], 1);
     }
     mbar_init(&tfull[0], 1);
     mbar_init(&tfull[1], 1);
@@ -126,12 +219,6 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     mbar_fence_init();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
-  }
-  if (threadIdx.x < 16) {
-    // e2m1: sign, two exponent bits, one mantissa bit
-    const int c = threadIdx.x, e = (c >> 1) & 3, m = c & 1;
-    const float mag = e == 0 ? 0.5f * m : (1.f + 0.5f * m) * (float)(1 << (e - 1));
-    s_lut[c] = (c & 8) ? -mag : mag;
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -152,8 +239,8 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total_work = p.group_off != nullptr ? s_prefix[p.num_groups] * p.n_tiles : p.n_tiles * p.t_tiles;
-  const int kb_total = p.kb_total;
+  const int total_work = p.group_off != nullptr ? s_prefix[p.num_groups] * p.n_tiles
+                                                : p.n_tiles * p.t_tiles * p.splits;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -162,12 +249,12 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const Work k = get_work<BN>(w, p, s_prefix);
-        for (int kb = 0; kb < kb_total; ++kb) {
+        for (int kb = k.kb0; kb < k.kb1; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* st = smem + s * C::STAGE_BYTES;
           mbar_expect_tx(&full[s], RAW_BYTES + C::B_BYTES);
-          tma_load_2d(st, &tmW, &full[s], kb * (BK / 2), k.w_row);                  // packed bytes
-          tma_load_2d(st + RAW_BYTES + A_BYTES, &tmX, &full[s], kb * BK, k.t_row);   // activations
+          tma_load_2d(st, &tmW, &full[s], kb * (BK / 2), k.w_row);          // packed bytes
+          tma_load_2d(st + RAW_BYTES, &tmX, &full[s], kb * BK, k.t_row);     // activations
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
@@ -177,92 +264,123 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
-      int s = 0;
-      uint32_t ph = 0, tile_i = 0;
+      int s = 0, as = 0;
+      uint32_t ph = 0, aph = 0, tile_i = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
+        const Work k = get_work<BN>(w, p, s_prefix);
         const int acc = tile_i & 1;
         if (!mbar_wait(&tempty[acc], ((tile_i >> 1) & 1) ^ 1, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY)) break;
         tc_fence_after();
-        for (int kb = 0; kb < kb_total; ++kb) {
+        for (int kb = k.kb0; kb < k.kb1; ++kb) {
           if (!mbar_wait(&full[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL) ||
-              !mbar_wait(&expanded[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL)) {
+              !mbar_wait(&afull[as], aph, abort_flag, p.status, ST_TIMEOUT_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES + RAW_BYTES);
-          const uint64_t adesc = umma_desc_k_sw128(a_addr);
-          const uint64_t bdesc = umma_desc_k_sw128(a_addr + A_BYTES);
+          const uint32_t a_tmem = tmem_base + A_TMEM_BASE + as * A_COLS;
+          const uint64_t bdesc = umma_desc_k_sw128(smem_u32(smem + s * C::STAGE_BYTES + RAW_BYTES));
 #pragma unroll
           for (int q = 0; q < BK / 16; ++q)      // K = 16 per instruction: 32 bytes along the 128-byte row
-            umma_f16(tmem_base + acc * BN, adesc + 2 * q, bdesc + 2 * q, idesc, (kb > 0 || q > 0) ? 1u : 0u);
-          umma_commit(&empty[s]);
+            umma_f16_a_tmem(tmem_base + acc * BN, a_tmem + 8 * q, bdesc + 2 * q, idesc,
+                            (kb > k.kb0 || q > 0) ? 1u : 0u);
+          umma_commit(&empty[s]);               // the activation tile of the load slot
+          umma_commit(&aempty[as]);             // the expanded tile
           if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (++as == A_STAGES) { as = 0; aph ^= 1; }
         }
         if (ok) umma_commit(&tfull[acc]);
       }
     }
-  } else if (warp < 6) {
-    // ---- expansion: this thread owns weight row `row` of every tile
-    const int row = threadIdx.x - 64;
-    int s = 0;
-    uint32_t ph = 0;
+  } else if (warp < EPI_WARP0) {
+    // ---- expansion.  Four groups of four warps take the K blocks round-robin (a K block costs a warp a chain of
+    // barrier waits, conversion and a TMEM store whose latencies add up, so four blocks are worked on at
+    // once); inside a group a warp owns its TMEM lane quarter: weight rows 32 * (warp % 4) + lane, all 64
+    // values of the row.  The completion of a block's TMEM store is awaited after the next block's values
+    // have been computed.
+    const int row = (warp & 3) * 32 + lane, grp = (warp - 2) >> 2;
+    int s = 0, as = 0;
+    uint32_t ph = 0, aph = 0;
     bool ok = true;
     constexpr int G = FMT == 0 ? 32 : 16;
+    constexpr int SPB = BK / G;                  // scale bytes per K block
     const int sc_ld = p.K / G;
+    int pending = -1;                            // A slot whose store has been issued but not published
+    auto publish = [&]() {
+      if (pending >= 0) {
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&afull[pending]);
+        pending = -1;
+      }
+    };
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const Work k = get_work<BN>(w, p, s_prefix);
       const bool live = k.n0 + row < p.N;
       const uint8_t* sc_row = p.scales + (size_t)(k.w_row + row) * sc_ld;
       float gs = 1.f;
       if (FMT == 1) gs = p.global_scale[p.gs_per_group ? (k.w_row / p.w_rows_per_group) : 0];
-      for (int kb = 0; kb < kb_total; ++kb) {
-        // group scales of this row's 64 values (2 for mxfp4, 4 for nvfp4), fetched before the wait
-        float sc[BK / G];
+      for (int kb = k.kb0; kb < k.kb1; ++kb) {
+        if (((kb - k.kb0) % EXP_GROUPS) == grp) {
+          // group scales of this block (a few bytes per row; the row's scales share cache lines over K)
+          float sc[SPB];
 #pragma unroll
-        for (int g = 0; g < BK / G; ++g) {
-          const int gi = kb * (BK / G) + g;
-          float v = 0.f;
-          if (live && gi < sc_ld) {
-            const uint8_t b = __ldg(sc_row + gi);
+          for (int g = 0; g < SPB; ++g) {
+            const int gi = kb * SPB + g;
+            const uint8_t b = (live && gi < sc_ld) ? __ldg(sc_row + gi) : 0;
             if (FMT == 0) {
-              v = __uint_as_float((uint32_t)b << 23);                 // 2^(b - 127); b = 0 gives 0
+              // 2^(b - 127) * 2^62 = 2^(b - 65): exponent field b + 62 (finite for b <= 192)
+              sc[g] = live ? __uint_as_float(min((uint32_t)b + 62u, 254u) << 23) : 0.f;
             } else {
               const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
-              v = __half2float(*reinterpret_cast<const __half*>(&h)) * gs;
+              sc[g] = live ? __half2float(*reinterpret_cast<const __half*>(&h)) * gs * 4611686018427387904.f : 0.f;
             }
           }
-          sc[g] = v;
-        }
-        if (!mbar_wait(&full[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
-        const uint8_t* st = smem + s * C::STAGE_BYTES;
-        // the packed tile was written by TMA without swizzle: dense rows of 32 bytes
-        uint4 raw[2];
-        raw[0] = *reinterpret_cast<const uint4*>(st + row * 32);
-        raw[1] = *reinterpret_cast<const uint4*>(st + row * 32 + 16);
-        uint8_t* a_row = const_cast<uint8_t*>(st) + RAW_BYTES + row * 128;
-        const uint32_t* words = reinterpret_cast<const uint32_t*>(raw);
+          if (!mbar_wait(&full[s], ph, abort_flag, p.status, ST_TIMEOUT_FULL)) { ok = false; break; }
+          // the packed tile was written by TMA without swizzle: dense rows of 32 bytes
+          const uint8_t* st = smem + s * C::STAGE_BYTES;
+          uint4 raw[2];
+          raw[0] = *reinterpret_cast<const uint4*>(st + row * 32);
+          raw[1] = *reinterpret_cast<const uint4*>(st + row * 32 + 16);
+          const uint32_t* words = reinterpret_cast<const uint32_t*>(raw);
+          uint32_t cols[32];                     // the row's 64 values as 32 bf16 pairs
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {            // 16-byte chunk c of the bf16 row = 8 values = one packed word
-          const uint32_t wd = words[c];
-          const float s8 = sc[(c * 8) / G];
-          uint32_t pk[4];
+          for (int c = 0; c < 8; ++c) {          // 8 values = one packed word
+            const uint32_t wd = words[c];
+            float s8 = sc[0];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float lo = s_lut[(wd >> (8 * j)) & 0xF] * s8;
-            const float hi = s_lut[(wd >> (8 * j + 4)) & 0xF] * s8;
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
-            pk[j] = *reinterpret_cast<uint32_t*>(&b2);
+            for (int g = 1; g < SPB; ++g)
+              if ((c * 8) / G == g) s8 = sc[g];
+            uint4 o;
+            if (FMT == 0) {
+              // a power of two is exact in bf16: the top half of its fp32 bits, in both halves of the pair
+              const uint32_t s2 = (__float_as_uint(s8) >> 16) * 0x00010001u;
+              o = make_uint4(e2m1_pair_to_bf16x2_pow2<0>(wd, s2), e2m1_pair_to_bf16x2_pow2<1>(wd, s2),
+                             e2m1_pair_to_bf16x2_pow2<2>(wd, s2), e2m1_pair_to_bf16x2_pow2<3>(wd, s2));
+            } else {
+              o = make_uint4(e2m1_pair_to_bf16x2<0>(wd, s8), e2m1_pair_to_bf16x2<1>(wd, s8),
+                             e2m1_pair_to_bf16x2<2>(wd, s8), e2m1_pair_to_bf16x2<3>(wd, s8));
+            }
+            cols[4 * c] = o.x; cols[4 * c + 1] = o.y; cols[4 * c + 2] = o.z; cols[4 * c + 3] = o.w;
           }
-          *reinterpret_cast<uint4*>(a_row + ((c ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty[s]);   // the packed bytes of this warp's rows are in registers
+          publish();                               // the previous block's store has had this long to land
+          if (!mbar_wait(&aempty[as], aph ^ 1, abort_flag, p.status, ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t ta = tmem_base + A_TMEM_BASE + as * A_COLS + ((uint32_t)((warp & 3) * 32) << 16);
+          tmem_st_32x32b_x16(ta, cols);
+          tmem_st_32x32b_x16(ta + 16, cols + 16);
+          pending = as;
         }
-        fence_proxy_async_smem();                // generic-proxy writes before the tensor core's reads
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&expanded[s]);
         if (++s == STAGES) { s = 0; ph ^= 1; }
+        if (++as == A_STAGES) { as = 0; aph ^= 1; }
       }
+      if (!ok) break;
     }
+    publish();
   } else {
     // ---- epilogue: TMEM lane = weight row, column = token
     const int q = warp & 3;
@@ -282,7 +400,12 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         uint32_t r[32];
         tmem_ld_32x32(taddr + c0, r);
         tmem_ld_wait();
-        if (n < p.N) {
+        if (p.splits > 1) {
+          // fp32 partial of this K range: part[token][weight row] in the (now idle) stage ring
+          float* part = reinterpret_cast<float*>(smem);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) part[(c0 + j) * BM + row] = __uint_as_float(r[j]);
+        } else if (n < p.N) {
           __nv_bfloat16* yp = p.Y + (size_t)(k.t_row + c0) * p.ldy + n;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
@@ -293,6 +416,46 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
     }
+  }
+
+  if (p.splits > 1) {
+    // every CTA of the cluster has its partial in shared memory: sum them over DSMEM.  Epilogue warp e of
+    // cluster rank r takes tokens r + S * e, r + S * (e + 4), ...; a lane owns four consecutive weight rows.
+    __syncwarp();
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (warp >= EPI_WARP0 && !*abort_flag && (int)blockIdx.x < total_work) {
+      const Work k = get_work<BN>(blockIdx.x, p, s_prefix);
+      const int ew = warp - EPI_WARP0;
+      const uint32_t rank = cluster_ctarank();
+      const int S = p.splits;
+      const int n4 = k.n0 + 4 * lane;
+      float b4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n4 + j < p.N) b4[j] = __bfloat162float(p.bias[n4 + j]);
+      }
+      const uint32_t part_local = smem_u32(smem);
+      for (int c = (int)rank + S * ew; c < k.t_valid; c += 4 * S) {
+        float4 v[8];
+#pragma unroll
+        for (int r2 = 0; r2 < 8; ++r2)
+          if (r2 < S) v[r2] = ld_dsmem_v4(mapa_shared(part_local + (uint32_t)((c * BM + 4 * lane) * 4), r2));
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r2 = 0; r2 < 8; ++r2)
+          if (r2 < S) { a.x += v[r2].x; a.y += v[r2].y; a.z += v[r2].z; a.w += v[r2].w; }
+        const float vals[4] = {a.x, a.y, a.z, a.w};
+        __nv_bfloat16* yp = p.Y + (size_t)(k.t_row + c) * p.ldy + n4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n4 + j < p.N) yp[j] = __float2bfloat16(vals[j] + b4[j]);
+      }
+    }
+    __syncwarp();
+    cluster_arrive_release();       // nobody leaves while a peer may still read its partial
+    cluster_wait_acquire();
   }
 
   tc_fence_before();
@@ -313,11 +476,20 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmX, const Params& 
   cfg.blockDim = dim3(NUM_THREADS);
   cfg.dynamicSmemBytes = C::SMEM;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (p.splits > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = p.splits;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[na].val.programmaticStreamSerializationAllowed = 1;
+  ++na;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = na;
   B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_w4a16_kernel<BN, FMT>, tmW, tmX, p));
   return 0;
 }
@@ -328,8 +500,7 @@ static int dispatch(int bn, const CUtensorMap& tmW, const CUtensorMap& tmX, cons
   switch (bn) {
     case 32: return launch<32, FMT>(tmW, tmX, p, grid, stream);
     case 64: return launch<64, FMT>(tmW, tmX, p, grid, stream);
-    case 128: return launch<128, FMT>(tmW, tmX, p, grid, stream);
-    default: return launch<256, FMT>(tmW, tmX, p, grid, stream);
+    default: return launch<128, FMT>(tmW, tmX, p, grid, stream);
   }
 }
 
@@ -346,7 +517,7 @@ static int run(const void* X, const void* Wp, const void* scales, const float* g
     b200_set_last_error("gemm_w4a16 (grouped): N % 128 == 0 required", __FILE__, __LINE__);
     return -3;
   }
-  const int bn = rows_hint <= 32 ? 32 : (rows_hint <= 64 ? 64 : (rows_hint <= 128 ? 128 : 256));
+  const int bn = rows_hint <= 32 ? 32 : (rows_hint <= 64 ? 64 : 128);
   Params p;
   memset(&p, 0, sizeof(p));
   p.Y = (__nv_bfloat16*)Y;
@@ -369,8 +540,23 @@ static int run(const void* X, const void* Wp, const void* scales, const float* g
   if (rc) return rc;
   rc = b200_make_tmap_2d(&tmX, X, 2, (uint64_t)T, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn, BK);
   if (rc) return rc;
-  const int total = group_off != nullptr ? num_sms : p.n_tiles * p.t_tiles;
-  const int grid = total < num_sms ? total : num_sms;
+  // few tiles: cluster split-K (2, 4 or 8 CTAs per tile, at least four K blocks each); the fp32 partial
+  // [bn][128] of a CTA has to fit in the stage ring, which it does for every bn
+  p.splits = 1;
+  p.kb_per_split = p.kb_total;
+  const int tiles = p.n_tiles * p.t_tiles;
+  if (group_off == nullptr && tiles * 2 <= num_sms) {
+    int sp = num_sms / tiles;
+    sp = sp >= 8 ? 8 : (sp >= 4 ? 4 : 2);
+    while (sp > 1 && p.kb_total / sp < 4) sp >>= 1;
+    if (sp > 1) {
+      p.splits = sp;
+      p.kb_per_split = (p.kb_total + sp - 1) / sp;
+      if ((sp - 1) * p.kb_per_split >= p.kb_total) { p.splits = 1; p.kb_per_split = p.kb_total; }
+    }
+  }
+  const int total = group_off != nullptr ? num_sms : tiles * p.splits;
+  const int grid = p.splits > 1 ? total : (total < num_sms ? total : num_sms);
   return fmt == 0 ? dispatch<0>(bn, tmW, tmX, p, grid, stream) : dispatch<1>(bn, tmW, tmX, p, grid, stream);
 }
 
@@ -386,6 +572,60 @@ extern "C" int b200_gemm_w4a16(const void* X, const void* Wp, const void* scales
                                int* status, int num_sms, cudaStream_t stream) {
   return w4::run(X, Wp, scales, global_scale, Y, bias, nullptr, 0, 0, T, N, K, ldx, ldy, fmt, T, status, num_sms,
                  stream);
+}
+
+// Whole-tensor expansion to bf16 [rows, K] (for prefill-sized products, where expanding every tile once per
+// token tile would cost more than one pass over the weight): one thread per 8 values.
+namespace b200 {
+namespace w4 {
+template <int FMT>
+__global__ void dequant_w4_kernel(const uint8_t* __restrict__ wp, const uint8_t* __restrict__ scales,
+                                  const float* __restrict__ global_scale, __nv_bfloat16* __restrict__ out,
+                                  long long rows, int K) {
+  constexpr int G = FMT == 0 ? 32 : 16;
+  const long long words = rows * (K / 8);
+  const float gs = FMT == 1 ? global_scale[0] : 1.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < words;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / (K / 8);
+    const int c = (int)(i - r * (K / 8));
+    const uint32_t wd = __ldg(reinterpret_cast<const uint32_t*>(wp) + i);
+    const uint8_t b = __ldg(scales + r * (K / G) + (c * 8) / G);
+    float sc;
+    if (FMT == 0) {
+      sc = __uint_as_float(min((uint32_t)b + 62u, 254u) << 23);
+    } else {
+      const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+      sc = __half2float(*reinterpret_cast<const __half*>(&h)) * gs * 4611686018427387904.f;
+    }
+    *reinterpret_cast<uint4*>(out + i * 8) =
+        make_uint4(e2m1_pair_to_bf16x2<0>(wd, sc), e2m1_pair_to_bf16x2<1>(wd, sc),
+                   e2m1_pair_to_bf16x2<2>(wd, sc), e2m1_pair_to_bf16x2<3>(wd, sc));
+  }
+}
+}  // namespace w4
+}  // namespace b200
+
+// out [rows, K] bf16 = dequant(wp [rows, K / 2], scales); K % 8 == 0 (mxfp4: K % 32, nvfp4: K % 16).
+extern "C" int b200_dequant_w4(const void* wp, const void* scales, const float* global_scale, void* out,
+                               long long rows, int K, int fmt, cudaStream_t stream) {
+  if (rows <= 0 || K <= 0) return 0;
+  if (K % 32 || (fmt != 0 && fmt != 1) || (fmt == 1 && global_scale == nullptr)) {
+    b200_set_last_error("dequant_w4: K % 32 == 0, format mxfp4 (0) or nvfp4 (1, with its global scale)", __FILE__,
+                        __LINE__);
+    return -3;
+  }
+  const long long words = rows * (K / 8);
+  long long blocks = (words + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (fmt == 0)
+    w4::dequant_w4_kernel<0><<<(int)blocks, 256, 0, stream>>>((const uint8_t*)wp, (const uint8_t*)scales,
+                                                              global_scale, (__nv_bfloat16*)out, rows, K);
+  else
+    w4::dequant_w4_kernel<1><<<(int)blocks, 256, 0, stream>>>((const uint8_t*)wp, (const uint8_t*)scales,
+                                                              global_scale, (__nv_bfloat16*)out, rows, K);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
 }
 
 // Grouped form: rows [group_off[e], group_off[e+1]) of X use expert e's packed weights Wp [E, N, K / 2] and

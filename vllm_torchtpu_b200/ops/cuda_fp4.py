@@ -10,6 +10,19 @@ from . import count_launch
 from . import cuda as _c
 
 FMT = {"mxfp4": 0, "nvfp4": 1}
+DEQUANT_FROM_TOKENS = 1024
+
+
+def dequant_w4(w_packed, scales, fmt: str, global_scale=None):
+    """Packed e2m1 [..., rows, K / 2] with its group scales -> bf16 [..., rows, K]."""
+    from ctypes import c_longlong
+    K = w_packed.shape[-1] * 2
+    rows = w_packed.numel() // w_packed.shape[-1]
+    out = torch.empty(w_packed.shape[:-1] + (K,), dtype=torch.bfloat16, device=w_packed.device)
+    _c._check(_c.lib().b200_dequant_w4(_c._p(w_packed), _c._p(scales), _c._p(global_scale), _c._p(out),
+                                       c_longlong(rows), c_int(K), c_int(FMT[fmt]), _c._stream()), "dequant_w4")
+    count_launch()
+    return out
 
 
 def w4a16_gemm(x, w_packed, scales, fmt: str, global_scale=None, bias=None):
@@ -22,6 +35,10 @@ def w4a16_gemm(x, w_packed, scales, fmt: str, global_scale=None, bias=None):
         x2 = x2.contiguous()
     T, K = x2.shape
     N = w_packed.shape[0]
+    if T >= DEQUANT_FROM_TOKENS:
+        # many tokens: one pass over the weight into a bf16 scratch, then the bf16 tcgen05 GEMM (the fused
+        # kernel would expand every weight tile once per token tile)
+        return _c.gemm(x2, dequant_w4(w_packed, scales, fmt, global_scale), bias).reshape(*lead, N)
     y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
     if T == 0:
         return y.reshape(*lead, N)
