@@ -230,3 +230,26 @@ def test_kv_block_counts_are_reconciled_per_pipeline_stage():
     assert reconcile({0: 1000, 1: 1002, 2: 800, 3: 799}, {0: 0, 1: 0, 2: 1, 3: 1}) == 799
     with pytest.raises(ValueError, match="stage 1"):
         reconcile({0: 1000, 1: 1002, 2: 800, 3: 700}, {0: 0, 1: 0, 2: 1, 3: 1})
+
+
+def test_update_weights_in_place_changes_the_output_like_a_fresh_engine(tmp_path):
+    """Weights handed over in memory (a trainer's step): the engine that took them generates what an engine
+    loaded from the same checkpoint generates, and no longer what it generated before."""
+    import torch
+
+    from vllm_torchtpu_b200 import SamplingParams
+    from vllm_torchtpu_b200.engine.llm import LLM
+    from vllm_torchtpu_b200.models.loader import iter_safetensors, save_hf_checkpoint
+    kw = dict(device="cpu", max_num_seqs=4, block_size=16, init_dist=False, enable_prefix_caching=True)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    prompts = [[5, 6, 7, 8, 9], [100, 101, 102]]
+    donor = LLM("tiny-llama", seed=123, **kw)
+    save_hf_checkpoint(donor.engine.runner.model, str(tmp_path))
+    want = [o.outputs[0].token_ids for o in donor.generate(prompts, sp)]
+    llm = LLM("tiny-llama", seed=0, **kw)
+    before = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert before != want
+    n = llm.engine.update_weights(dict(iter_safetensors(str(tmp_path))))
+    assert n > 0
+    after = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    assert after == want

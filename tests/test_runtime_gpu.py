@@ -129,3 +129,25 @@ def test_bounds_checked_attention_library_counts_bad_block_ids():
     r = subprocess.run([sys.executable, os.path.join(here, "workers", "bounds_check_worker.py")],
                        capture_output=True, text=True, timeout=240)
     assert "BOUNDS_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_kernel_library_can_be_reloaded_between_requests():
+    """reload_kernels maps the library again under a fresh name, re-captures the decode graphs, and the engine
+    keeps generating the same tokens."""
+    import torch
+
+    from vllm_torchtpu_b200 import SamplingParams
+    from vllm_torchtpu_b200.config import ModelConfig
+    from vllm_torchtpu_b200.engine.llm import LLM
+    from vllm_torchtpu_b200.ops import cuda
+    cfg = ModelConfig(name="t", num_layers=2, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                      intermediate_size=1024, vocab_size=2048, max_model_len=256, dtype=torch.bfloat16)
+    llm = LLM(cfg, device="cuda", max_num_seqs=4, max_num_batched_tokens=128, num_gpu_blocks_override=128,
+              init_dist=False)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    before = [o.outputs[0].token_ids for o in llm.generate([[1, 2, 3, 4, 5]], sp)]
+    old = cuda.lib()
+    llm.engine.reload_kernels()
+    assert cuda.lib() is not old
+    after = [o.outputs[0].token_ids for o in llm.generate([[1, 2, 3, 4, 5]], sp)]
+    assert after == before and cuda.check_status() == 0

@@ -242,6 +242,42 @@ class LLMEngine:
             self.runner.lora_manager = self.lora_manager
         return self.lora_manager
 
+    # ---- weights and kernels at run time -------------------------------------------------------------
+    def update_weights(self, named_tensors) -> int:
+        """Replace model weights in place from checkpoint-named tensors (a dict or an iterable of
+        (name, tensor) in Hugging Face layout, unsharded: every rank takes its shard), e.g. after a
+        trainer's optimizer step.  Partial updates are allowed as long as fused parameters come complete
+        (q, k and v together; gate and up together).  Cached prefixes are dropped: they were computed with
+        the old weights.  Call between steps, with no request in flight.
+        (reference: src/vllm_torchtpu/worker/tpu_worker.py sync_weights)"""
+        if self.scheduler.has_unfinished() or self._inflight:
+            raise RuntimeError("update_weights needs an idle engine")
+        items = list(named_tensors.items()) if isinstance(named_tensors, dict) else list(named_tensors)
+        from ..models.loader import load_named_tensors
+        load_named_tensors(self.runner.model, iter(items), {n for n, _ in items}, source="update_weights")
+        self.scheduler.kv.pool.reset_prefix_cache()
+        mega = getattr(self.runner.model, "decode_mega", None)
+        if mega is not None:
+            self.runner.model.setup_decode_fusion(self.runner)      # descriptors point at the old tensors
+        if self.runner.graphs:
+            # captured graphs hold the addresses of the replaced tensors
+            self.runner.graphs.clear()
+            self.runner.capture_model()
+        return len(items)
+
+    def reload_kernels(self, path: Optional[str] = None) -> str:
+        """Load the kernel library again (after a rebuild, or from ``path``) and re-capture the decode graphs:
+        kernels can be iterated on without restarting the server.
+        (reference: src/vllm_torchtpu/worker/tpu_worker.py:862 reload_kernels)"""
+        if self.scheduler.has_unfinished() or self._inflight:
+            raise RuntimeError("reload_kernels needs an idle engine")
+        from ..ops import cuda
+        loaded = cuda.reload_lib(path)
+        if self.runner.graphs:
+            self.runner.graphs.clear()
+            self.runner.capture_model()
+        return loaded
+
     def add_lora(self, name: str, rank: int, alpha: float, weights: dict) -> bool:
         """weights: {"model.layers.N.self_attn.q_proj": (A [r, in], B [out, r]), ...}."""
         from ..lora import LoRAAdapter

@@ -69,11 +69,18 @@ _FP8_DTYPES = (torch.float8_e4m3fn, torch.float8_e5m2)
 
 
 def load_safetensors(model, path: str) -> None:
+    load_named_tensors(model, iter_safetensors(path), list_tensor_names(path), source=path)
+
+
+def load_named_tensors(model, tensors, names: set, source: str = "memory") -> None:
+    """Load checkpoint-named tensors (Hugging Face layout) from any iterator of (name, tensor): a directory
+    of safetensors files, or tensors handed over in memory by a trainer (``LLMEngine.update_weights``).
+    ``names`` is the set of all names the iterator will yield (fused parameters wait for their pieces)."""
+    path = source
     cfg = model.cfg
     st = get_state()
     lo, hi = model.layer_range
     layers = {lo + i: l for i, l in enumerate(model.layers)}
-    names = list_tensor_names(path)
     open_groups: dict = {}
     seen = 0
     rx = re.compile(r"^model\.layers\.(\d+)\.(.+)$")
@@ -118,7 +125,7 @@ def load_safetensors(model, path: str) -> None:
     def linear_piece(gid, target, prefixes: dict, part, kind, t, what):
         submit(gid, prefixes, part, kind, t, load_linear(target, tuple(prefixes), what))
 
-    for name, t in iter_safetensors(path):
+    for name, t in tensors:
         seen += 1
         if name == "model.embed_tokens.weight":
             if model.pp_first or cfg.tie_word_embeddings:

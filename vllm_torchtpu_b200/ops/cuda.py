@@ -48,6 +48,27 @@ def bad_index_count() -> int:
     return total
 
 
+def reload_lib(path: Optional[str] = None) -> str:
+    """Forget the loaded kernel library and load it again, from ``path`` or from the in-tree build.  A copy
+    under a fresh name is opened, because the dynamic loader hands back the already mapped object for a
+    path it knows."""
+    global _lib
+    import shutil
+    import tempfile
+    from ..csrc import build as _build
+    src = path or envs.B200_KERNEL_LIB or _build.lib_path()
+    if not os.path.exists(src):
+        raise RuntimeError(f"kernel library {src} is missing")
+    fd, tmp = tempfile.mkstemp(prefix="libb200_kernels_", suffix=".so")
+    os.close(fd)
+    shutil.copyfile(src, tmp)
+    new = ctypes.CDLL(tmp, mode=ctypes.RTLD_GLOBAL)
+    new.b200_get_last_error.restype = ctypes.c_char_p
+    new.b200_attn_decode_scratch_bytes.restype = c_size_t
+    _lib = new
+    return src
+
+
 def lib():
     global _lib, _sms
     if _lib is not None:
