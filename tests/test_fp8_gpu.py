@@ -46,7 +46,9 @@ def test_quant_rows_bounded_by_device_count_and_fused_swiglu():
 
 
 @pytest.mark.parametrize("T,N,K", [(16, 256, 512), (64, 1280, 8192), (100, 384, 1024), (128, 7168, 2048),
-                                   (300, 1024, 640), (1, 128, 128)])
+                                   (300, 1024, 640), (1, 128, 128),
+                                   # more tiles than SMs with a short last wave: main launch + split-K tail launch
+                                   (64, 28672, 1024), (16, 20000, 2048)])
 def test_fp8_block_gemm(T, N, K):
     g = torch.Generator(device=DEV).manual_seed(T + N)
     x = torch.randn(T, K, device=DEV, generator=g).bfloat16()

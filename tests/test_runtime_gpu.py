@@ -146,6 +146,8 @@ def test_kernel_library_can_be_reloaded_between_requests():
               init_dist=False)
     sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
     before = [o.outputs[0].token_ids for o in llm.generate([[1, 2, 3, 4, 5]], sp)]
+    again = [o.outputs[0].token_ids for o in llm.generate([[1, 2, 3, 4, 5]], sp)]
+    assert again == before                                   # the engine is deterministic across calls
     old = cuda.lib()
     llm.engine.reload_kernels()
     assert cuda.lib() is not old

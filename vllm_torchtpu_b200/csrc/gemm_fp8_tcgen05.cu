@@ -79,6 +79,9 @@ struct Params {
   // to exit raises int[world] flags at ret_flag_off of every rank with the epoch in *epoch_ptr
   const int2* row_route;
   unsigned long long route_ret_off, ret_flag_off;
+  // dense launches may cover a sub-range of the output tiles (the ragged last wave of a persistent launch is
+  // run as a second, split-K launch): tiles [tile_offset, tile_offset + launch_tiles), 0 = all
+  int tile_offset, launch_tiles;
 };
 
 // index of output tile (n_tile, t_tile) in the raster the consumer uses (groups of 16 weight tiles)
@@ -96,7 +99,8 @@ template <int BN>
 __device__ __forceinline__ Work get_work(int w, const Params& p, const int* s_prefix) {
   Work k;
   if (p.group_off == nullptr) {
-    const int tile = w / p.splits, split = w - tile * p.splits;
+    const int local = w / p.splits, split = w - local * p.splits;
+    const int tile = local + p.tile_offset;
     const int n_tile = tile % p.n_tiles, t_tile = tile / p.n_tiles;
     k.w_row = n_tile * BM;
     k.ws_row = n_tile;
@@ -182,8 +186,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total_work = p.group_off != nullptr ? s_prefix[p.num_groups] * p.n_tiles
-                                                : p.n_tiles * p.t_tiles * p.splits;
+  const int total_work = p.group_off != nullptr
+                             ? s_prefix[p.num_groups] * p.n_tiles
+                             : (p.launch_tiles > 0 ? p.launch_tiles : p.n_tiles * p.t_tiles) * p.splits;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -762,13 +767,43 @@ extern "C" int b200_gemm_fp8_block(const void* Xq, const float* xs, const void* 
   CUtensorMap tmW, tmX;
   int rc = fp8_common(p, Xq, Wq, N, T, bn, K, &tmW, &tmX);
   if (rc) return rc;
-  const int total = tiles * p.splits;
-  const int grid = p.cluster_splitk ? total : (total < num_sms ? total : num_sms);
-  switch (bn) {
-    case 32: return f8::launch<32>(tmW, tmX, p, grid, stream);
-    case 64: return f8::launch<64>(tmW, tmX, p, grid, stream);
-    default: return f8::launch<128>(tmW, tmX, p, grid, stream);
+  auto go = [&](const f8::Params& q, int grid) {
+    switch (bn) {
+      case 32: return f8::launch<32>(tmW, tmX, q, grid, stream);
+      case 64: return f8::launch<64>(tmW, tmX, q, grid, stream);
+      default: return f8::launch<128>(tmW, tmX, q, grid, stream);
+    }
+  };
+  // A persistent launch over a few waves ends with a ragged wave: 224 tiles on 148 SMs take the time of two
+  // full waves.  When the last wave fills at most half of the SMs, its tiles run as a second launch with
+  // cluster split-K, so that the whole machine shares them.
+  const int tail = tiles % num_sms;
+  if (p.splits == 1 && tiles > num_sms && tiles <= 4 * num_sms && tail > 0 && tail * 2 <= num_sms &&
+      p.kb_total >= 8) {
+    int sp = num_sms / tail;
+    const int by_k = p.kb_total / 4;
+    if (sp > by_k) sp = by_k;
+    if (sp > 1) sp = f8::fit_splits(sp, tail, bn);
+    if (sp > 1) {
+      f8::Params main = p, rest = p;
+      main.launch_tiles = tiles - tail;
+      rc = go(main, num_sms);
+      if (rc) return rc;
+      rest.tile_offset = tiles - tail;
+      rest.launch_tiles = tail;
+      rest.splits = sp;
+      rest.kb_per_split = (p.kb_total + sp - 1) / sp;
+      while (rest.splits > 1 && (rest.splits - 1) * rest.kb_per_split >= p.kb_total) {
+        --rest.splits;
+        rest.kb_per_split = (p.kb_total + rest.splits - 1) / rest.splits;
+      }
+      rest.cluster_splitk = rest.splits > 1 ? 1 : 0;
+      const int total = tail * rest.splits;
+      return go(rest, rest.cluster_splitk ? total : (total < num_sms ? total : num_sms));
+    }
   }
+  const int total = tiles * p.splits;
+  return go(p, p.cluster_splitk ? total : (total < num_sms ? total : num_sms));
 }
 
 // Row-parallel block-scaled fp8 GEMM whose bf16 partial is pushed to every rank of the tensor-parallel

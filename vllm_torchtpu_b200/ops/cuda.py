@@ -62,7 +62,8 @@ def reload_lib(path: Optional[str] = None) -> str:
     fd, tmp = tempfile.mkstemp(prefix="libb200_kernels_", suffix=".so")
     os.close(fd)
     shutil.copyfile(src, tmp)
-    new = ctypes.CDLL(tmp, mode=ctypes.RTLD_GLOBAL)
+    # local scope and own symbols first: the copy must not bind to the functions of the library it replaces
+    new = ctypes.CDLL(tmp, mode=os.RTLD_LOCAL | os.RTLD_DEEPBIND)
     new.b200_get_last_error.restype = ctypes.c_char_p
     new.b200_attn_decode_scratch_bytes.restype = c_size_t
     _lib = new
