@@ -49,6 +49,87 @@ def test_safetensors_roundtrip_dense_and_moe(tmp_path):
         assert got == want, preset
 
 
+def _rewrite_checkpoint(d, rename):
+    """Rewrite the tensors of a saved checkpoint through ``rename(dict) -> dict``."""
+    from safetensors.torch import load_file, save_file
+    f = str(d / "model.safetensors")
+    save_file({k: v.contiguous() for k, v in rename(load_file(f)).items()}, f)
+
+
+def test_mixtral_phi3_and_qwen2_moe_checkpoint_layouts(tmp_path):
+    """Mixtral (block_sparse_moe / w1 w3 w2 names), Phi-3 (fused qkv_proj and gate_up_proj tensors) and
+    Qwen2-MoE (a shared expert behind a sigmoid gate) load into the Llama / Qwen-MoE models and reproduce
+    the tokens of the model they were written from."""
+    import re
+    from vllm_torchtpu_b200.models.loader import save_hf_checkpoint
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+
+    def run(path_or_preset, **kw):
+        llm = LLM(path_or_preset, device="cpu", max_num_seqs=4, block_size=16, init_dist=False, **kw)
+        return llm, [o.outputs[0].token_ids for o in llm.generate(_prompts(), sp)]
+
+    from vllm_torchtpu_b200.config import ModelConfig
+
+    def donor(hf):
+        mc = ModelConfig.from_hf_dict(hf)
+        mc.dtype, mc.max_model_len = torch.float32, 256
+        return run(mc)
+
+    # Mixtral
+    hf = _hf_cfg("MixtralForCausalLM", num_local_experts=8, num_experts_per_tok=2, intermediate_size=128)
+    src, want = donor(hf)
+    assert src.engine.runner.model.layers[0].self_attn.q_norm_w is None
+    d = tmp_path / "mixtral"
+    save_hf_checkpoint(src.engine.runner.model, str(d), hf)
+    back = {"gate_proj": "w1", "up_proj": "w3", "down_proj": "w2"}
+
+    def to_mixtral(t):
+        out = {}
+        for k, v in t.items():
+            k = k.replace(".mlp.", ".block_sparse_moe.")
+            k = re.sub(r"(experts\.\d+\.)(gate_proj|up_proj|down_proj)", lambda m: m.group(1) + back[m.group(2)], k)
+            out[k] = v
+        return out
+    _rewrite_checkpoint(d, to_mixtral)
+    _, got = run(str(d), dtype="float32")
+    assert got == want
+
+    # Phi-3
+    src, want = run("tiny-llama")
+    d = tmp_path / "phi3"
+    save_hf_checkpoint(src.engine.runner.model, str(d), _hf_cfg("Phi3ForCausalLM"))
+
+    def to_phi3(t):
+        out = {k: v for k, v in t.items() if not re.search(r"\.(q|k|v|gate|up)_proj\.", k)}
+        for i in range(2):
+            a, m = f"model.layers.{i}.self_attn.", f"model.layers.{i}.mlp."
+            out[a + "qkv_proj.weight"] = torch.cat([t[a + f"{p}_proj.weight"] for p in "qkv"], 0)
+            out[m + "gate_up_proj.weight"] = torch.cat([t[m + "gate_proj.weight"], t[m + "up_proj.weight"]], 0)
+        return out
+    _rewrite_checkpoint(d, to_phi3)
+    _, got = run(str(d), dtype="float32")
+    assert got == want
+
+    # Qwen2-MoE: the gate is read from the checkpoint and changes the output
+    hf = _hf_cfg("Qwen2MoeForCausalLM", num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+                 shared_expert_intermediate_size=192, norm_topk_prob=False)
+    mc = ModelConfig.from_hf_dict(hf)
+    assert mc.shared_expert_gate and mc.shared_expert_intermediate_size == 192 and mc.attention_bias
+    src, want = donor(hf)
+    blk = src.engine.runner.model.layers[0].mlp
+    assert blk.shared_gate is not None and blk.shared.down.weight.shape[1] == 192
+    x = torch.randn(3, 256)
+    full = blk.forward(x)
+    gate = torch.sigmoid(x @ blk.shared_gate)[:, None]
+    torch.testing.assert_close(full, blk.experts.forward(x) + gate * blk.shared.forward(x), rtol=1e-5, atol=1e-5)
+    d = tmp_path / "qwen2moe"
+    save_hf_checkpoint(src.engine.runner.model, str(d), hf)
+    dst, got = run(str(d), dtype="float32")
+    assert got == want
+    torch.testing.assert_close(dst.engine.runner.model.layers[1].mlp.shared_gate,
+                               src.engine.runner.model.layers[1].mlp.shared_gate)
+
+
 def test_hf_config_mapping():
     from vllm_torchtpu_b200.config import ModelConfig
     mc = ModelConfig.from_hf_dict({"architectures": ["DeepseekV3ForCausalLM"], "num_hidden_layers": 61,

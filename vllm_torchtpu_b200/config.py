@@ -57,6 +57,8 @@ class ModelConfig:
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     num_shared_experts: int = 0
+    shared_expert_intermediate_size: int = 0   # 0: moe_intermediate_size x num_shared_experts
+    shared_expert_gate: bool = False           # shared expert output scaled by sigmoid(x . w) (Qwen2-MoE, Qwen3-Next)
     first_dense_layers: int = 0          # leading layers with a dense FFN
     moe_scoring: str = "softmax"         # softmax | sigmoid
     moe_renormalize: bool = True
@@ -133,7 +135,8 @@ class ModelConfig:
                 n += h * (self.q_size + 2 * self.kv_size) + self.q_size * h
             if self.layer_is_moe(i):
                 n += self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
-                n += self.num_shared_experts * 3 * h * self.moe_intermediate_size
+                n += 3 * h * (self.shared_expert_intermediate_size
+                              or self.num_shared_experts * self.moe_intermediate_size)
             else:
                 n += 3 * h * self.intermediate_size
         return n
@@ -157,8 +160,29 @@ class ModelConfig:
         mc.tie_word_embeddings = cfg.get("tie_word_embeddings", False)
         mc.dtype = parse_dtype(cfg.get("torch_dtype", "bfloat16"))
         mc.sliding_window = cfg.get("sliding_window") if cfg.get("use_sliding_window", True) else None
-        if arch.startswith(("Llama", "Mistral")):
-            mc.architecture = "llama"
+        if arch.startswith(("Llama", "Mistral", "Phi3")):
+            mc.architecture = "llama"                   # Phi-3: fused qkv_proj / gate_up_proj in the checkpoint
+        elif arch.startswith("Mixtral"):
+            # Llama attention, every FFN a mixture of experts whose size is `intermediate_size`
+            mc.architecture = "qwen3_moe"
+            mc.num_experts = cfg["num_local_experts"]
+            mc.num_experts_per_tok = cfg["num_experts_per_tok"]
+            mc.moe_intermediate_size = cfg["intermediate_size"]
+            mc.moe_renormalize = True
+        elif arch.startswith("Qwen2Moe"):
+            mc.architecture, mc.attention_bias = "qwen3_moe", True
+            mc.num_experts = cfg["num_experts"]
+            mc.num_experts_per_tok = cfg["num_experts_per_tok"]
+            mc.moe_intermediate_size = cfg["moe_intermediate_size"]
+            mc.moe_renormalize = cfg.get("norm_topk_prob", False)
+            mc.shared_expert_intermediate_size = cfg.get("shared_expert_intermediate_size", 0)
+            mc.num_shared_experts = 1 if mc.shared_expert_intermediate_size else 0
+            mc.shared_expert_gate = mc.num_shared_experts > 0
+            if cfg.get("decoder_sparse_step", 1) != 1:
+                raise ValueError("Qwen2-MoE with decoder_sparse_step != 1 is not supported")
+            dense_first = cfg.get("mlp_only_layers") or []
+            if dense_first and dense_first == list(range(len(dense_first))):
+                mc.first_dense_layers = len(dense_first)
         elif arch.startswith("Qwen2"):
             mc.architecture, mc.attention_bias = "llama", True
         elif arch.startswith("Qwen3Moe"):
@@ -175,7 +199,9 @@ class ModelConfig:
             mc.num_experts = cfg.get("num_experts", 0)
             mc.num_experts_per_tok = cfg.get("num_experts_per_tok", 0)
             mc.moe_intermediate_size = cfg.get("moe_intermediate_size", 0)
-            mc.num_shared_experts = 1 if cfg.get("shared_expert_intermediate_size") else 0
+            mc.shared_expert_intermediate_size = cfg.get("shared_expert_intermediate_size", 0)
+            mc.num_shared_experts = 1 if mc.shared_expert_intermediate_size else 0
+            mc.shared_expert_gate = mc.num_shared_experts > 0
             mc.full_attention_interval = cfg.get("full_attention_interval", 4)
             mc.gdn_num_k_heads = cfg.get("linear_num_key_heads", 16)
             mc.gdn_num_v_heads = cfg.get("linear_num_value_heads", 32)

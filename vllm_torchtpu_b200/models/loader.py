@@ -72,6 +72,20 @@ def load_safetensors(model, path: str) -> None:
     load_named_tensors(model, iter_safetensors(path), list_tensor_names(path), source=path)
 
 
+_MIXTRAL_EXPERT = {"w1": "gate_proj", "w3": "up_proj", "w2": "down_proj"}
+
+
+def canonical_name(name: str) -> str:
+    """Checkpoint name → the Llama / Qwen-MoE naming the loader walks: Mixtral keeps its experts under
+    ``block_sparse_moe`` with ``w1 / w3 / w2`` for gate / up / down."""
+    if ".block_sparse_moe." in name:
+        name = name.replace(".block_sparse_moe.", ".mlp.")
+        m = re.match(r"^(.*\.experts\.\d+\.)(w[123])(\..+)$", name)
+        if m:
+            name = m.group(1) + _MIXTRAL_EXPERT[m.group(2)] + m.group(3)
+    return name
+
+
 def load_named_tensors(model, tensors, names: set, source: str = "memory") -> None:
     """Load checkpoint-named tensors (Hugging Face layout) from any iterator of (name, tensor): a directory
     of safetensors files, or tensors handed over in memory by a trainer (``LLMEngine.update_weights``).
@@ -84,6 +98,7 @@ def load_named_tensors(model, tensors, names: set, source: str = "memory") -> No
     open_groups: dict = {}
     seen = 0
     rx = re.compile(r"^model\.layers\.(\d+)\.(.+)$")
+    names = {canonical_name(n) for n in names}
 
     def submit(gid, ckpt_prefixes: dict, part: str, kind: str, tensor, done) -> None:
         """Piece ``kind`` ("weight" or "weight_scale_inv") of ``part`` of parameter group ``gid``;
@@ -127,6 +142,7 @@ def load_named_tensors(model, tensors, names: set, source: str = "memory") -> No
 
     for name, t in tensors:
         seen += 1
+        name = canonical_name(name)
         if name == "model.embed_tokens.weight":
             if model.pp_first or cfg.tie_word_embeddings:
                 model.embed = t.to(device=model.device, dtype=cfg.dtype)
@@ -172,6 +188,8 @@ def load_named_tensors(model, tensors, names: set, source: str = "memory") -> No
                 else:
                     linear_piece(("qkv", li), a.qkv, {p: f"{ap}{p}_proj" for p in ("q", "k", "v")},
                                  pm.group(1), pm.group(2), t, f"{ap}qkv_proj")
+            elif sub == "qkv_proj.weight" and hasattr(a, "qkv"):
+                a.qkv.load_weight(t)                     # Phi-3: q, k, v rows already stacked in this order
             elif om and hasattr(a, "o"):
                 linear_piece(("o", li), a.o, {"o": ap + "o_proj"}, "o", om.group(1), t, ap + "o_proj")
             elif sub == "q_norm.weight" and a.q_norm_w is not None:
@@ -206,6 +224,8 @@ def load_named_tensors(model, tensors, names: set, source: str = "memory") -> No
             if pm and hasattr(mlp, "gate_up"):
                 linear_piece(("gu", li), mlp.gate_up, {p: f"{mp}{p}_proj" for p in ("gate", "up")},
                              pm.group(1), pm.group(2), t, mp + "gate_up_proj")
+            elif sub == "gate_up_proj.weight" and hasattr(mlp, "gate_up"):
+                mlp.gate_up.load_weight(t)               # Phi-3: gate rows then up rows
             elif dm and hasattr(mlp, "down"):
                 linear_piece(("down", li), mlp.down, {"d": mp + "down_proj"}, "d", dm.group(1), t, mp + "down_proj")
             elif hasattr(mlp, "experts"):
@@ -214,6 +234,8 @@ def load_named_tensors(model, tensors, names: set, source: str = "memory") -> No
                     moe.gate.load_weight(t)
                 elif sub == "gate.e_score_correction_bias" and moe.score_bias is not None:
                     _set_vec(moe.score_bias, t)
+                elif sub == "shared_expert_gate.weight" and getattr(mlp, "shared_gate", None) is not None:
+                    _set_vec(mlp.shared_gate, t.reshape(-1))
                 else:
                     em = re.match(r"^experts\.(\d+)\.(gate|up|down)_proj\.(weight|weight_scale_inv)$", sub)
                     sm = re.match(r"^(shared_experts?)\.(gate|up|down)_proj\.(weight|weight_scale_inv)$", sub)
@@ -263,6 +285,10 @@ def save_hf_checkpoint(model, path: str, hf_config: Optional[dict] = None) -> No
             out[pre + "self_attn.v_proj.weight"], out[pre + "self_attn.o_proj.weight"] = v, a.o.weight
             if a.q_norm_w is not None:
                 out[pre + "self_attn.q_norm.weight"], out[pre + "self_attn.k_norm.weight"] = a.q_norm_w, a.k_norm_w
+            if a.qkv.bias is not None:
+                for p_, b_ in zip("qkv", a.qkv.bias.split([cfg.num_q_heads * D, cfg.num_kv_heads * D,
+                                                            cfg.num_kv_heads * D], 0)):
+                    out[pre + f"self_attn.{p_}_proj.bias"] = b_
         mlp = l.mlp
         if hasattr(mlp, "gate_up"):
             I = mlp.gate_up.weight.shape[0] // 2
@@ -276,6 +302,12 @@ def save_hf_checkpoint(model, path: str, hf_config: Optional[dict] = None) -> No
                 out[pre + f"mlp.experts.{e}.gate_proj.weight"] = moe.w13[e, :I]
                 out[pre + f"mlp.experts.{e}.up_proj.weight"] = moe.w13[e, I:]
                 out[pre + f"mlp.experts.{e}.down_proj.weight"] = moe.w2[e]
+            if getattr(mlp, "shared", None) is not None:
+                sw, sp_ = mlp.shared.gate_up.weight, pre + "mlp.shared_expert."
+                out[sp_ + "gate_proj.weight"], out[sp_ + "up_proj.weight"] = sw[:sw.shape[0] // 2], sw[sw.shape[0] // 2:]
+                out[sp_ + "down_proj.weight"] = mlp.shared.down.weight
+                if mlp.shared_gate is not None:
+                    out[pre + "mlp.shared_expert_gate.weight"] = mlp.shared_gate[None, :]
     save_file({k: v.detach().cpu().contiguous() for k, v in out.items()}, os.path.join(path, "model.safetensors"))
     if hf_config is not None:
         with open(os.path.join(path, "config.json"), "w") as f:
