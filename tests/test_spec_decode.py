@@ -128,3 +128,132 @@ def test_medusa_heads_load_from_a_checkpoint_and_reproduce_plain_decoding(tmp_pa
     assert prop.num_speculative_tokens == 2 and prop.stats["proposed"] > 0
     assert len(prop.blocks) == 2 and prop.heads[0] is not None
     assert spec_llm.engine.runner.stats.get("spec_drafted", 0) > 0
+
+
+def _spec_llm(method, k=3, **kw):
+    sc = {"method": method, "num_speculative_tokens": k}
+    sc.update(kw.pop("spec", {}))
+    return LLM("tiny-llama", device="cpu", block_size=16, init_dist=False, speculative_config=sc, **kw)
+
+
+def _logged_drafts(llm, prompts, sp):
+    """Generate and return (outputs, {(prompt index, sequence length): drafts})."""
+    llm.engine.spec.log = []
+    outs = llm.generate(prompts, sp)
+    order = {o.request_id: i for i, o in enumerate(outs)}
+    return [o.outputs[0].token_ids for o in outs], {(order[r], n): d for r, n, d in llm.engine.spec.log}
+
+
+@pytest.mark.parametrize("method", ["mtp", "eagle", "eagle3"])
+def test_draft_layer_kv_cache_is_consistent_across_batching_and_lossless(method):
+    """A draft layer's proposals are a function of the sequence alone: whole-prompt steps and 16-token
+    prompt chunks (catch-up passes split differently, other batch composition) give the same drafts at
+    the same sequence lengths, and the engine's tokens equal plain decoding."""
+    prompts = [np.random.RandomState(11).randint(0, 1024, size=n).tolist() for n in (7, 37, 20)]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    plain = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    want = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    a = _spec_llm(method, max_num_seqs=4)
+    got_a, drafts_a = _logged_drafts(a, prompts, sp)
+    b = _spec_llm(method, max_num_seqs=2, max_num_batched_tokens=16)
+    got_b, drafts_b = _logged_drafts(b, prompts, sp)
+    assert got_a == want and got_b == want
+    common = set(drafts_a) & set(drafts_b)
+    assert len(common) >= 6
+    for key in common:
+        n = min(len(drafts_a[key]), len(drafts_b[key]))
+        assert drafts_a[key][:n] == drafts_b[key][:n], key
+    st = a.engine.spec.stats
+    assert st["proposed"] > 0 and st["catch_up_rows"] >= sum(len(p) for p in prompts)
+    assert not a.engine.scheduler.async_mode
+
+
+def test_mtp_draft_layer_that_mirrors_a_bigram_target_is_accepted_in_full():
+    """Target whose layers add nothing (next token = f(last token)) and an MTP module that ignores the
+    hidden state and repeats the target's head: every draft is right, so every verification step keeps
+    k + 1 tokens; this walks the multi-row acceptance path of the catch-up pass."""
+    prompts = [np.random.RandomState(5).randint(0, 1024, size=n).tolist() for n in (9, 18)]
+    sp = SamplingParams(temperature=0.0, max_tokens=17, ignore_eos=True)
+
+    def flatten(model_layers):
+        for l in model_layers:
+            l.self_attn.o.weight.zero_()
+            l.mlp.down.weight.zero_()
+    plain = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    flatten(plain.engine.runner.model.layers)
+    want = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    spec = _spec_llm("mtp", k=3, max_num_seqs=4)
+    flatten(spec.engine.runner.model.layers)
+    d = spec.engine.spec
+    flatten([d.layer])
+    H = d.fc.shape[0]
+    d.fc = torch.cat([torch.eye(H), torch.zeros(H, H)], 1).to(d.fc.dtype)
+    d.out_norm.copy_(spec.engine.runner.model.norm)
+    got = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]
+    assert got == want
+    rs = spec.engine.runner.stats
+    assert rs["spec_drafted"] > 0 and rs["spec_accepted"] == rs["spec_drafted"]
+
+
+@pytest.mark.parametrize("method", ["mtp", "eagle", "eagle3"])
+def test_draft_layer_checkpoints_load(tmp_path, method):
+    from safetensors.torch import save_file
+    from vllm_torchtpu_b200.config import model_preset
+    m = model_preset("tiny-llama")
+    H, D, I, V, L = m.hidden_size, m.head_dim, m.intermediate_size, m.vocab_size, m.num_layers
+    g = torch.Generator().manual_seed(3)
+    rnd = lambda *s: torch.randn(*s, generator=g) * 0.05       # noqa: E731
+    attn_in = 2 * H if method == "eagle3" else H
+    layer = {"self_attn.q_proj.weight": rnd(m.num_q_heads * D, attn_in),
+             "self_attn.k_proj.weight": rnd(m.num_kv_heads * D, attn_in),
+             "self_attn.v_proj.weight": rnd(m.num_kv_heads * D, attn_in),
+             "self_attn.o_proj.weight": rnd(H, m.num_q_heads * D),
+             "mlp.gate_proj.weight": rnd(I, H), "mlp.up_proj.weight": rnd(I, H), "mlp.down_proj.weight": rnd(H, I),
+             "post_attention_layernorm.weight": 1 + rnd(H)}
+    if method == "mtp":
+        pre = f"model.layers.{L}."
+        t = {pre + k: v for k, v in layer.items()}
+        t.update({pre + "input_layernorm.weight": 1 + rnd(H), pre + "enorm.weight": 1 + rnd(H),
+                  pre + "hnorm.weight": 1 + rnd(H), pre + "eh_proj.weight": rnd(H, 2 * H),
+                  pre + "shared_head.norm.weight": 1 + rnd(H), pre + "shared_head.head.weight": rnd(V, H),
+                  "model.layers.0.input_layernorm.weight": rnd(H)})       # a target tensor: ignored
+        fc_name, norm_name = pre + "eh_proj.weight", pre + "shared_head.norm.weight"
+    elif method == "eagle":
+        t = {"layers.0." + k: v for k, v in layer.items()}
+        t.update({"fc.weight": rnd(H, 2 * H), "fc.bias": rnd(H), "embed_tokens.weight": rnd(V, H)})
+        fc_name, norm_name = "fc.weight", None
+    else:
+        t = {"midlayer." + k: v for k, v in layer.items()}
+        t.update({"midlayer.input_layernorm.weight": 1 + rnd(H), "midlayer.hidden_norm.weight": 1 + rnd(H),
+                  "fc.weight": rnd(H, 3 * H), "norm.weight": 1 + rnd(H), "lm_head.weight": rnd(64, H),
+                  "d2t": torch.arange(64) * 3, "t2d": torch.zeros(V, dtype=torch.bool)})
+        fc_name, norm_name = "fc.weight", "norm.weight"
+    d = tmp_path / method
+    d.mkdir()
+    save_file({k: v.contiguous() for k, v in t.items()}, str(d / "model.safetensors"))
+    llm = _spec_llm(method, max_num_seqs=4, spec={"model": str(d)}, dtype="float32")
+    p = llm.engine.spec
+    key = next(k for k in t if k.endswith("self_attn.q_proj.weight"))
+    stem = key[: -len("self_attn.q_proj.weight")]
+    qkv = torch.cat([t[stem + f"self_attn.{x}_proj.weight"] for x in "qkv"], 0)
+    torch.testing.assert_close(p.layer.self_attn.qkv.weight, qkv)
+    torch.testing.assert_close(p.layer.mlp.down.weight, t[stem + "mlp.down_proj.weight"])
+    torch.testing.assert_close(p.layer.post_ln, t[stem + "post_attention_layernorm.weight"])
+    torch.testing.assert_close(p.fc, t[fc_name])
+    if norm_name:
+        torch.testing.assert_close(p.out_norm, t[norm_name])
+    if method == "eagle":
+        torch.testing.assert_close(p.fc_bias, t["fc.bias"])
+        assert p.embed is not None and p.head is None
+    if method == "eagle3":
+        torch.testing.assert_close(p.hidden_norm, t["midlayer.hidden_norm.weight"])
+        assert p.head.shape == (64, H) and p.d2t[5] == 15
+    prompts = [np.random.RandomState(2).randint(0, 1024, size=n).tolist() for n in (6, 19)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    plain = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False, dtype="float32")
+    assert [o.outputs[0].token_ids for o in llm.generate(prompts, sp)] == \
+        [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    if method == "eagle3":          # drafts come from the reduced vocabulary, mapped through d2t
+        llm.engine.spec.log = []
+        llm.generate(prompts, sp)
+        assert all(tok % 4 == 0 and tok < 64 * 4 for _, _, dr in llm.engine.spec.log for tok in dr)

@@ -105,3 +105,42 @@ def test_engine_ngram_spec_decode_with_device_acceptance_equals_plain_decode():
     spec = [o.outputs[0].token_ids for o in spec_llm.generate(prompts, sp)]
     assert spec_llm.engine.runner.stats.get("spec_drafted", 0) > 0
     assert spec == plain
+
+
+@pytest.mark.parametrize("method", ["mtp", "eagle", "eagle3"])
+def test_draft_layer_engine_run_is_lossless_on_the_device(method):
+    """A draft layer with attention (its own KV tensor behind the target's block tables) runs its catch-up
+    and look-ahead passes on the package's kernels; the engine's tokens equal plain decoding."""
+    import numpy as np
+    from vllm_torchtpu_b200 import LLM, SamplingParams
+    prompts = [np.random.RandomState(4).randint(0, 1024, size=n).tolist() for n in (9, 40, 23)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    plain = LLM("tiny-llama", device=DEV, max_num_seqs=4, block_size=16, init_dist=False)
+    want = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    del plain
+    spec = LLM("tiny-llama", device=DEV, max_num_seqs=4, block_size=16, init_dist=False, max_num_batched_tokens=32,
+               speculative_config={"method": method, "num_speculative_tokens": 3})
+    got = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]
+    assert got == want
+    st = spec.engine.spec.stats
+    assert st["proposed"] > 0 and st["catch_up_rows"] >= sum(len(p) for p in prompts)
+
+
+def test_mtp_layer_mirroring_a_bigram_target_is_accepted_on_the_device():
+    import numpy as np
+    from vllm_torchtpu_b200 import LLM, SamplingParams
+    prompts = [np.random.RandomState(5).randint(0, 1024, size=n).tolist() for n in (9, 18)]
+    sp = SamplingParams(temperature=0.0, max_tokens=17, ignore_eos=True)
+    spec = LLM("tiny-llama", device=DEV, max_num_seqs=4, block_size=16, init_dist=False,
+               speculative_config={"method": "mtp", "num_speculative_tokens": 3})
+    d = spec.engine.spec
+    for l in list(spec.engine.runner.model.layers) + [d.layer]:
+        l.self_attn.o.weight.zero_()
+        l.mlp.down.weight.zero_()
+    H = d.fc.shape[0]
+    d.fc = torch.cat([torch.eye(H), torch.zeros(H, H)], 1).to(device=d.fc.device, dtype=d.fc.dtype)
+    d.out_norm.copy_(spec.engine.runner.model.norm)
+    outs = spec.generate(prompts, sp)
+    assert all(len(o.outputs[0].token_ids) == 17 for o in outs)
+    rs = spec.engine.runner.stats
+    assert rs["spec_drafted"] > 0 and rs["spec_accepted"] >= 0.8 * rs["spec_drafted"]

@@ -79,6 +79,10 @@ class LLMEngine:
             torch.cuda.set_device(st.local_rank)
         self.runner = ModelRunner(self.cfg, dev)
         self.runner.load_model()
+        if cfg.speculative:
+            from ..spec_decode import DRAFT_LAYER_METHODS
+            if cfg.speculative.get("method") in DRAFT_LAYER_METHODS:
+                self.runner.extra_kv_layers = 1         # the draft layer's KV tensor counts in the HBM budget
         num_blocks = self.runner.determine_num_blocks()
         if st.world_size > 1 and st.world.cpu_group is not None:
             # the ranks of a pipeline stage must agree within a tolerance; everyone adopts the minimum

@@ -199,6 +199,8 @@ class LlamaForCausalLM:
         self.vocab_shard = cfg.vocab_size // st.tp.size if cfg.vocab_size % st.tp.size == 0 else None
         self.decode_mega = None          # persistent decode kernel (ops/cuda_mega.py), set up with the KV cache
         self.decode_mega_reason = "not set up"
+        self.aux_layers: tuple = ()      # layers whose input (hidden + residual) an Eagle-3 drafter reads
+        self.aux_hidden: list = []
 
     # ---- weights -------------------------------------------------------------
     def named_linears(self):
@@ -260,7 +262,7 @@ class LlamaForCausalLM:
 
     def _use_decode_mega(self, meta, hidden, residual) -> bool:
         m = self.decode_mega
-        if m is None or hidden is None or residual is not None:
+        if m is None or hidden is None or residual is not None or self.aux_layers:
             return False
         T = hidden.shape[0]
         if T > m.maxt or meta.num_decode_reqs != meta.num_reqs or meta.max_query_len > 1:
@@ -278,7 +280,11 @@ class LlamaForCausalLM:
         if self._use_decode_mega(meta, hidden, residual):
             # decode-only step: every layer in one persistent kernel; (0, residual stream) comes back
             return self.decode_mega.run(hidden.contiguous(), meta, hidden.shape[0])
+        self.aux_hidden = []
         for i, layer in enumerate(self.layers):
+            if i in self.aux_layers:
+                hidden = ops.materialize(hidden)
+                self.aux_hidden += [hidden if residual is None else hidden + residual] * self.aux_layers.count(i)
             hidden, residual = layer.forward(hidden, residual, kv_caches[i], meta)
         return ops.materialize(hidden), residual
 

@@ -99,7 +99,7 @@ class B200Platform:
     supported_kv_cache_dtypes = ("auto", "bfloat16", "fp8", "fp8_e4m3")
     supported_connectors = ("B200P2PConnector", "B200HostConnector", "B200MultiConnector",
                             "B200OffloadingConnector", "DecodeBenchConnector")
-    supported_spec_methods = ("ngram", "suffix", "medusa", "eagle3", "mtp", "dflash", "dspark")
+    supported_spec_methods = ("ngram", "suffix", "medusa", "eagle", "eagle3", "mtp", "dflash", "dspark")
 
     # ---- device facts ---------------------------------------------------
     @classmethod
@@ -236,6 +236,13 @@ class B200Platform:
                                  "(no state checkpoints to roll rejected drafts back)")
             if s.async_scheduling and method in ("ngram", "suffix"):
                 raise ValueError("async scheduling is only supported with eagle-family drafters")
+            if s.async_scheduling and method in ("mtp", "eagle", "eagle3"):
+                # the draft layer catches up on a step's rows and drafts from its tokens before the next
+                # step is scheduled
+                logger.info("speculative method %s: async scheduling switched off", method)
+                s.async_scheduling = False
+            if method in ("mtp", "eagle", "eagle3") and p.decode_context_parallel_size > 1:
+                raise ValueError("draft layers are not built for decode context parallelism")
         if cfg.kv_transfer:
             name = cfg.kv_transfer.get("kv_connector")
             if name not in cls.supported_connectors:

@@ -65,6 +65,8 @@ class StepResult:
     extra: dict = field(default_factory=dict)
     lp: Optional[dict] = None       # sample / prompt logprob tensors of the step (device or host)
     hidden: Optional[torch.Tensor] = None   # final-norm hidden state of every sampled row (draft heads)
+    hidden_all: Optional[torch.Tensor] = None   # ... of every row of the step (drafters with their own KV cache)
+    rows: Optional[dict] = None     # row layout of the step: query_start_loc, first position, batch slot per request
     status_host: Optional[torch.Tensor] = None   # copy of the device status word taken after the step
 
     def take_logprobs(self):
@@ -166,6 +168,9 @@ class ModelRunner:
         self.mm_manager = None           # multimodal encoder manager (runner/mm_encoder.py)
         self._mm_plan = None             # (request id, first prompt token, first row, rows) of this step
         self._last_h = None
+        self.keep_all_hidden = False     # a draft layer with attention wants the hidden state of every row
+        self._last_h_all = None
+        self.extra_kv_layers = 0         # KV layers a drafter allocates beside the model's (HBM budget)
         self._pool_plan = None           # pooling requests of the current step: (id, row lo, row hi, mode, last chunk)
         self._pool_acc: dict = {}        # request id -> [sum or last row, count]
         if envs.B200_STAGE_TIMING and self.is_cuda:
@@ -222,6 +227,8 @@ class ModelRunner:
             return c.num_gpu_blocks_override
         kv_dtype = B200Platform.kv_cache_torch_dtype(c.kv_cache_dtype, self.mcfg.dtype)
         per_block = self.model.kv_bytes_per_block(self.block_size, kv_dtype)
+        if self.extra_kv_layers:
+            per_block += self.extra_kv_layers * per_block // max(1, len(self.model.layers))
         if c.kv_cache_memory_bytes:
             return max(2, c.kv_cache_memory_bytes // per_block)
         if not self.is_cuda:
@@ -410,6 +417,9 @@ class ModelRunner:
         h = self.model.finalize(*rows)
         if self.keep_hidden:
             self._last_h = h
+        if self.keep_all_hidden:
+            aux = getattr(self.model, "aux_hidden", None)
+            self._last_h_all = torch.cat(aux, -1) if aux else self.model.finalize(hidden, residual)
         st = get_state()
         if (self.is_cuda and all_greedy and st.tp.size > 1 and envs.B200_GREEDY_TOP_TOKENS
                 and self.model.vocab_shard is not None and ex is None):
@@ -761,6 +771,12 @@ class ModelRunner:
                          host, ev, n, rows * 4 + 4, status_host=st_host)
         if self.keep_hidden:
             res.hidden, self._last_h = self._last_h, None
+        if self.keep_all_hidden:
+            res.hidden_all, self._last_h_all = self._last_h_all, None
+            n_ = p["n"]
+            slots_ = p["bufs"].host_view("batch_slots", n_).copy()
+            res.rows = {"qsl": p["qsl_np"][:n_ + 1].copy(), "slots": slots_,
+                        "pos0": p["bufs"].host_view("positions", p["T"])[p["qsl_np"][:n_]].copy()}
         if self._step_extras is not None:
             res.lp = self._step_extras["out"]
             self._step_extras = None

@@ -3,11 +3,14 @@ and a rejection sampler decides how many are kept.
 
 Drafters: ``ngram`` (prompt lookup), ``suffix`` (longest-suffix match over prompt + output), ``medusa``
 (K residual-block heads on the target's hidden state, loaded from a checkpoint and run batched on the
-device).  ``eagle3`` / ``mtp`` / ``dflash`` / ``dspark`` select a toy stand-in: a random one-matrix
-recurrent head that accepts next to nothing and exists to exercise the hidden-state hand-off; the
-attention layer of those drafters is not built.
+device), ``mtp`` / ``eagle`` / ``eagle3`` (one transformer layer with attention and its own KV cache behind
+the target's block tables, ``draft_layer.py``).  ``dflash`` / ``dspark`` select a toy stand-in: a random
+one-matrix recurrent head that accepts next to nothing and exists to exercise the hidden-state hand-off.
 (reference: src/vllm_torchtpu/spec_decode/, docs/user_guide/speculative_decoding.md:5-16)"""
 from __future__ import annotations
+
+
+DRAFT_LAYER_METHODS = ("mtp", "eagle", "eagle3")      # drafters that keep a KV cache of their own
 
 
 def create_proposer(cfg, runner):
@@ -21,7 +24,10 @@ def create_proposer(cfg, runner):
     if method == "medusa":
         from .medusa import MedusaProposer
         return MedusaProposer(cfg, runner, k, sc.get("model"), int(sc.get("num_hidden_layers", 1)))
-    if method in ("eagle3", "mtp", "dflash", "dspark"):
+    if method in DRAFT_LAYER_METHODS:
+        from .draft_layer import DraftLayerProposer
+        return DraftLayerProposer(cfg, runner, k, method, sc.get("model"))
+    if method in ("dflash", "dspark"):
         from .draft_head import DraftHeadProposer
         return DraftHeadProposer(cfg, runner, k, method)
     raise ValueError(f"unknown speculative method {method!r}")
