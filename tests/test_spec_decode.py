@@ -257,3 +257,18 @@ def test_draft_layer_checkpoints_load(tmp_path, method):
         llm.engine.spec.log = []
         llm.generate(prompts, sp)
         assert all(tok % 4 == 0 and tok < 64 * 4 for _, _, dr in llm.engine.spec.log for tok in dr)
+
+
+@pytest.mark.parametrize("preset", ["tiny-mla", "tiny-moe"])
+def test_mtp_module_takes_the_layer_class_of_its_target(preset):
+    """The MTP module of an MLA + MoE target is an MLA + MoE layer with a latent cache of its own."""
+    prompts = [np.random.RandomState(4).randint(0, 1024, size=n).tolist() for n in (9, 30)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    plain = LLM(preset, device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    want = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    spec = LLM(preset, device="cpu", max_num_seqs=4, block_size=16, init_dist=False,
+               speculative_config={"method": "mtp", "num_speculative_tokens": 2})
+    assert [o.outputs[0].token_ids for o in spec.generate(prompts, sp)] == want
+    d = spec.engine.spec
+    assert type(d.layer) is type(spec.engine.runner.model.layers[-1]) and hasattr(d.layer.mlp, "experts")
+    assert d.kv_cache.shape == spec.engine.runner.kv_caches[-1].shape and d.stats["proposed"] > 0

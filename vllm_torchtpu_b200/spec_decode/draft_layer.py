@@ -97,23 +97,23 @@ class DraftLayerProposer:
         else:
             self._init_random()
         # one more KV tensor, addressed by the target's block tables
-        like = next(c for c in runner.kv_caches if torch.is_tensor(c) and c.dim() >= 4)
-        self.kv_cache = torch.zeros_like(like)
+        def blank(c):
+            return torch.zeros_like(c) if torch.is_tensor(c) else type(c)(blank(x) for x in c)
+        self.kv_cache = blank(runner.kv_caches[-1])     # the draft layer has the shape of the last target layer
         self._res = None
         self.last_confidences: dict = {}
         self.stats = {"proposed": 0, "requests": 0, "catch_up_rows": 0, "passes": 0}
         self.log = None                     # tests: list of (request id, sequence length, drafts)
 
     # ---- weights -------------------------------------------------------------------------------------
-    def _linears(self):
-        return list(self.layer.self_attn.linears()) + list(self.layer.mlp.linears())
-
     def _init_random(self) -> None:
         std, seed = self.m.init_std, self.m.seed
-        for lin in self._linears():
-            lin.init_dummy(std, seed)
-        if hasattr(self.layer.mlp, "init_dummy") and hasattr(self.layer.mlp, "experts"):
-            self.layer.mlp.init_dummy(std, seed)
+        for part in (self.layer.self_attn, self.layer.mlp):
+            if hasattr(part, "init_dummy"):             # MLA attention (absorbed kv_b), MLP and MoE blocks
+                part.init_dummy(std, seed)
+            else:
+                for lin in part.linears():
+                    lin.init_dummy(std, seed)
         self.fc = seeded_normal(f"draft.{self.kind}.fc", tuple(self.fc.shape), std, self.dtype, self.device, seed)
 
     def _load(self, path: str) -> None:
