@@ -107,19 +107,26 @@ def test_engine_ngram_spec_decode_with_device_acceptance_equals_plain_decode():
     assert spec == plain
 
 
+def _bf16_cfg():
+    from vllm_torchtpu_b200.config import ModelConfig
+    return ModelConfig(name="t", num_layers=2, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                       intermediate_size=1024, vocab_size=2048, max_model_len=512, dtype=torch.bfloat16)
+
+
 @pytest.mark.parametrize("method", ["mtp", "eagle", "eagle3"])
 def test_draft_layer_engine_run_is_lossless_on_the_device(method):
     """A draft layer with attention (its own KV tensor behind the target's block tables) runs its catch-up
     and look-ahead passes on the package's kernels; the engine's tokens equal plain decoding."""
     import numpy as np
     from vllm_torchtpu_b200 import LLM, SamplingParams
-    prompts = [np.random.RandomState(4).randint(0, 1024, size=n).tolist() for n in (9, 40, 23)]
+    prompts = [np.random.RandomState(4).randint(0, 2048, size=n).tolist() for n in (9, 40, 23)]
     sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
-    plain = LLM("tiny-llama", device=DEV, max_num_seqs=4, block_size=16, init_dist=False)
+    kw = dict(device=DEV, max_num_seqs=4, num_gpu_blocks_override=256, init_dist=False)
+    plain = LLM(_bf16_cfg(), max_num_batched_tokens=256, **kw)
     want = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
     del plain
-    spec = LLM("tiny-llama", device=DEV, max_num_seqs=4, block_size=16, init_dist=False, max_num_batched_tokens=32,
-               speculative_config={"method": method, "num_speculative_tokens": 3})
+    spec = LLM(_bf16_cfg(), max_num_batched_tokens=32,
+               speculative_config={"method": method, "num_speculative_tokens": 3}, **kw)
     got = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]
     assert got == want
     st = spec.engine.spec.stats
@@ -129,9 +136,9 @@ def test_draft_layer_engine_run_is_lossless_on_the_device(method):
 def test_mtp_layer_mirroring_a_bigram_target_is_accepted_on_the_device():
     import numpy as np
     from vllm_torchtpu_b200 import LLM, SamplingParams
-    prompts = [np.random.RandomState(5).randint(0, 1024, size=n).tolist() for n in (9, 18)]
+    prompts = [np.random.RandomState(5).randint(0, 2048, size=n).tolist() for n in (9, 18)]
     sp = SamplingParams(temperature=0.0, max_tokens=17, ignore_eos=True)
-    spec = LLM("tiny-llama", device=DEV, max_num_seqs=4, block_size=16, init_dist=False,
+    spec = LLM(_bf16_cfg(), device=DEV, max_num_seqs=4, num_gpu_blocks_override=256, init_dist=False,
                speculative_config={"method": "mtp", "num_speculative_tokens": 3})
     d = spec.engine.spec
     for l in list(spec.engine.runner.model.layers) + [d.layer]:
