@@ -136,6 +136,48 @@ def test_hybrid_linear_attention_models_on_gpu(arch, extra):
     assert cuda.check_status() == 0
 
 
+@pytest.mark.parametrize("arch,extra", [
+    ("qwen3_next", dict(qk_norm=True, full_attention_interval=2, gdn_num_k_heads=2, gdn_num_v_heads=4)),
+    ("kimi_linear", dict(full_attention_interval=4, gdn_num_k_heads=4, gdn_num_v_heads=4, kda_gate_rank=32)),
+])
+def test_speculative_decoding_on_hybrids_on_gpu(arch, extra):
+    """Verification steps on a hybrid: the recurrent state of requests that rejected drafts is restored from
+    the snapshot and the accepted rows are replayed through the recurrence kernels; tokens equal plain
+    decoding (a drafter that knows the continuation and spoils every other call's second draft)."""
+    cfg = ModelConfig(name="h", architecture=arch, num_layers=4, hidden_size=512, num_q_heads=8, num_kv_heads=2,
+                      head_dim=128, intermediate_size=1024, vocab_size=2048, max_model_len=512,
+                      dtype=torch.bfloat16, gdn_head_k_dim=64, gdn_head_v_dim=64, **extra)
+    sp = SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True)
+    kw = dict(device="cuda", max_num_seqs=8, max_num_batched_tokens=256, num_gpu_blocks_override=512,
+              init_dist=False, enforce_eager=True)
+    prompts = _prompts()[:3]
+    want = [o.outputs[0].token_ids for o in LLM(cfg, **kw).generate(prompts, sp)]
+    spec = LLM(cfg, speculative_config={"method": "ngram", "num_speculative_tokens": 3}, **kw)
+
+    def propose(out, sampled):
+        drafts = {}
+        for s in out.scheduled:
+            r = s.request
+            if not sampled.get(r.request_id) or r.status.finished:
+                continue
+            i = prompts.index(list(r.prompt_token_ids))
+            n = len(r.output_token_ids) + len(sampled[r.request_id])
+            d = list(want[i][n:min(n + 3, sp.max_tokens - 1)])
+            if n % 2 and len(d) > 1:
+                d[1] = (d[1] + 1) % 2048
+            if d:
+                drafts[r.request_id] = d
+        return drafts
+    spec.engine.spec.propose = propose
+    got = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]
+    st = spec.engine.runner.stats
+    assert st.get("spec_drafted", 0) > 0 and st.get("state_rollbacks", 0) > 0
+    # a bf16 tie between the 1-row and the (k + 1)-row kernels may flip one continuation
+    assert sum(int(a == b) for a, b in zip(got, want)) >= len(prompts) - 1, (got, want)
+    from vllm_torchtpu_b200.ops import cuda
+    assert cuda.check_status() == 0
+
+
 def test_logprobs_min_tokens_prompt_logprobs_on_gpu():
     """The logprob kernel, the min_tokens mask and chunked prompt logprobs on the device path (these
     steps leave the CUDA graphs), against the dense fp32 forward."""

@@ -209,7 +209,73 @@ def test_kimi_linear_hybrid_engine_is_chunk_and_batch_invariant():
     assert got == want
 
 
-def test_hybrid_models_reject_speculative_decoding():
-    with pytest.raises(ValueError, match="state checkpoints"):
-        LLM("tiny-kda", device="cpu", max_num_seqs=4, block_size=16, init_dist=False,
-            speculative_config={"method": "ngram", "num_speculative_tokens": 2})
+@pytest.mark.parametrize("preset", ["tiny-gdn", "tiny-kda"])
+def test_speculative_decoding_on_hybrids_rolls_recurrent_state_back(preset):
+    """Verification steps fold k + 1 rows into the recurrent state; rejected drafts are undone from a snapshot
+    plus a replay of the accepted rows, so the tokens equal plain decoding.  The drafter of this test knows the
+    right continuation and spoils its second draft on every other call: full and partial acceptance both occur."""
+    rng = np.random.RandomState(3)
+    prompts = [rng.randint(0, 1024, size=n).tolist() for n in (22, 13, 27)]
+    sp = SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True)
+    kw = dict(device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    want = [o.outputs[0].token_ids for o in LLM(preset, **kw).generate(prompts, sp)]
+    spec = LLM(preset, speculative_config={"method": "ngram", "num_speculative_tokens": 3}, **kw)
+
+    def propose(out, sampled):
+        drafts = {}
+        for s in out.scheduled:
+            r = s.request
+            if not sampled.get(r.request_id) or r.status.finished:
+                continue
+            i = prompts.index(list(r.prompt_token_ids))
+            n = len(r.output_token_ids) + len(sampled[r.request_id])
+            d = list(want[i][n:min(n + 3, sp.max_tokens - 1)])
+            if n % 2 and len(d) > 1:
+                d[1] = (d[1] + 1) % 1024
+            if d:
+                drafts[r.request_id] = d
+        return drafts
+    spec.engine.spec.propose = propose
+    got = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]
+    st = spec.engine.runner.stats
+    assert st.get("spec_drafted", 0) > 0 and 0 < st.get("spec_accepted", 0) < st["spec_drafted"]
+    assert st.get("state_rollbacks", 0) > 0
+    assert got == want
+    assert not spec.engine.scheduler.async_mode
+
+
+def test_state_rollback_equals_running_only_the_accepted_rows():
+    """Layer-level statement: after a step of k + 1 rows per request, rollback(accepted) leaves the pools as
+    if only the accepted rows had run."""
+    from vllm_torchtpu_b200.config import model_preset
+    from vllm_torchtpu_b200.models.qwen3_next import GatedDeltaNet
+    from vllm_torchtpu_b200.runner.attn_metadata import AttentionMetadata
+    from vllm_torchtpu_b200.runner.spec_boundary_state import StateRollback
+    cfg = model_preset("tiny-gdn")
+    layer = GatedDeltaNet("l", cfg, "cpu", None)
+    layer.init_dummy(0.05, 0)
+    torch.manual_seed(0)
+
+    def pools():
+        cs, rs = layer.state_shapes(4)
+        g = torch.Generator().manual_seed(1)
+        return torch.randn(cs, generator=g) * 0.1, torch.randn(rs, generator=g) * 0.1
+
+    def meta(qsl, seq, slots, rb=None):
+        t = lambda x: torch.tensor(x, dtype=torch.int32)       # noqa: E731
+        return AttentionMetadata(positions=t([0] * qsl[-1]), slot_mapping=t([-1] * qsl[-1]),
+                                 block_tables=t([[0]] * len(seq)), seq_lens=t(seq), query_start_loc=t(qsl),
+                                 num_reqs=len(seq), num_tokens=qsl[-1], state_slots=t(slots), state_rollback=rb)
+    # three requests: a decode row (no drafts), and two verifying requests with k = 3 and k = 2
+    x = torch.randn(1 + 4 + 3, cfg.hidden_size) * 0.5
+    qsl, pos0, slots = [0, 1, 5, 8], [9, 20, 14], [2, 0, 3]
+    seq = [pos0[i] + qsl[i + 1] - qsl[i] for i in range(3)]
+    cache = pools()
+    rb = StateRollback([1, 2], [0, 3], [1, 5], [4, 3], [20, 14], "cpu")
+    layer.forward(x, cache, meta(qsl, seq, slots, rb))
+    assert rb.rollback([2, 3]) == 1                   # request 1 keeps 2 of 4 rows, request 2 keeps all 3
+    want = pools()
+    rows = [0, 1, 2, 5, 6, 7]
+    layer.forward(x[rows], want, meta([0, 1, 3, 6], [10, 22, 17], slots))
+    for got_pool, want_pool in zip(cache, want):
+        torch.testing.assert_close(got_pool, want_pool, rtol=1e-5, atol=1e-6)

@@ -70,14 +70,13 @@ class KimiDeltaAttention:
     def state_shapes(self, max_reqs: int):
         return (max_reqs + 1, self.channels, self.K - 1), (max_reqs + 1, self.H, self.dk, self.dv)
 
-    def forward(self, x, cache, meta):
+    def recur(self, inputs, meta, cache):
+        """The stateful part: short conv with its carried window + KDA recurrence over the rows ``meta``
+        describes; advances the pools in place.  inputs = (mixed [T, C], a [T, H, dk], b [T, H])."""
+        mixed, a, b = inputs
         conv_pool, rec_pool = cache
-        T, H, dk, dv = x.shape[0], self.H, self.dk, self.dv
-        mixed = self.in_qkv(x)
-        a = self.f_b(self.f_a(x)).reshape(T, H, dk)
-        b = self.b_proj(x)
-        gate = self.g_b(self.g_a(x)).reshape(T, H, dv)
-        if x.is_cuda:
+        T, H, dk, dv = mixed.shape[0], self.H, self.dk, self.dv
+        if mixed.is_cuda:
             cu = ops.cuda_ops()
             y = cu.short_conv(mixed, meta, conv_pool, self.conv_w)
             q, k, v = y.split([H * dk, H * dk, H * dv], dim=-1)
@@ -96,6 +95,19 @@ class KimiDeltaAttention:
             q, k, v = y.split([H * dk, H * dk, H * dv], dim=-1)
             o = gref.kda_forward(q.reshape(T, H, dk), k.reshape(T, H, dk), v.reshape(T, H, dv), a, b, meta, rec_pool,
                                  self.A_log, self.dt_bias, self.lower_bound)
+        return o
+
+    def forward(self, x, cache, meta):
+        T, H, dk, dv = x.shape[0], self.H, self.dk, self.dv
+        mixed = self.in_qkv(x)
+        a = self.f_b(self.f_a(x)).reshape(T, H, dk)
+        b = self.b_proj(x)
+        gate = self.g_b(self.g_a(x)).reshape(T, H, dv)
+        inputs = (mixed.contiguous(), a.contiguous(), b.contiguous())
+        rb = getattr(meta, "state_rollback", None)
+        if rb is not None:
+            rb.capture(self, cache, inputs)        # verification step: rejected drafts are rolled back later
+        o = self.recur(inputs, meta, cache)
         o = ops.rms_norm(o.reshape(T * H, dv), self.norm_w, self.eps).reshape(T, H, dv)
         o = (o.float() * torch.sigmoid(gate.float())).to(x.dtype)
         return self.out(o.reshape(T, H * dv))

@@ -61,21 +61,29 @@ class GatedDeltaNet:
     def state_shapes(self, max_reqs: int):
         return (max_reqs + 1, self.channels, self.K - 1), (max_reqs + 1, self.Hv, self.dk, self.dv)
 
-    def forward(self, x, cache, meta):
+    def recur(self, inputs, meta, cache):
+        """The stateful part: conv window + delta-rule recurrence over the rows ``meta`` describes; advances
+        the pools in place.  inputs = (mixed [T, C], a [T, Hv], b [T, Hv])."""
+        mixed, a, b = inputs
         conv_pool, rec_pool = cache
+        if mixed.is_cuda:
+            return ops.cuda_ops().gdn_forward(mixed, a, b, meta, conv_pool, rec_pool, self.conv_w, self.A_log,
+                                              self.dt_bias, self.Hk, self.Hv, self.dk, self.dv)
+        return gref.gdn_forward(mixed, a, b, None, meta, conv_pool, rec_pool, self.conv_w, self.A_log,
+                                self.dt_bias, self.Hk, self.Hv, self.dk, self.dv)
+
+    def forward(self, x, cache, meta):
         T = x.shape[0]
         qkvz = self.in_qkvz(x)
         kd, vd = self.Hk * self.dk, self.Hv * self.dv
         mixed, z = qkvz[:, :2 * kd + vd], qkvz[:, 2 * kd + vd:]
         ba = self.in_ba(x)
         b, a = ba[:, :self.Hv], ba[:, self.Hv:]
-        if x.is_cuda:
-            o = ops.cuda_ops().gdn_forward(mixed.contiguous(), a.contiguous(), b.contiguous(), meta, conv_pool,
-                                           rec_pool, self.conv_w, self.A_log, self.dt_bias, self.Hk, self.Hv,
-                                           self.dk, self.dv)
-        else:
-            o = gref.gdn_forward(mixed, a, b, None, meta, conv_pool, rec_pool, self.conv_w, self.A_log,
-                                 self.dt_bias, self.Hk, self.Hv, self.dk, self.dv)
+        inputs = (mixed.contiguous(), a.contiguous(), b.contiguous())
+        rb = getattr(meta, "state_rollback", None)
+        if rb is not None:
+            rb.capture(self, cache, inputs)        # verification step: rejected drafts are rolled back later
+        o = self.recur(inputs, meta, cache)
         o = ops.rms_norm(o.reshape(T * self.Hv, self.dv), self.norm_w, self.eps).reshape(T, self.Hv, self.dv)
         zf = z.reshape(T, self.Hv, self.dv).float()
         o = (o.float() * torch.nn.functional.silu(zf)).to(x.dtype)

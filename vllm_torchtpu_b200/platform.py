@@ -228,12 +228,11 @@ class B200Platform:
             method = cfg.speculative.get("method")
             if method not in cls.supported_spec_methods:
                 raise ValueError(f"speculative method {method!r} not in {cls.supported_spec_methods}")
-            if m.is_hybrid_gdn:
-                # rejected drafts would have advanced the recurrent state: verification needs a window
-                # of per-position state checkpoints (the reference keeps K+1 of them), which the
-                # recurrence kernels here do not write
-                raise ValueError("speculative decoding is not supported for linear-attention hybrids "
-                                 "(no state checkpoints to roll rejected drafts back)")
+            if m.is_hybrid_gdn and s.async_scheduling:
+                # rejected drafts advance the recurrent state; it is rebuilt (snapshot + replay of the accepted
+                # rows, runner/spec_boundary_state.py) when the host has the step's tokens, before the next launch
+                logger.info("speculative decoding on a linear-attention hybrid: async scheduling switched off")
+                s.async_scheduling = False
             if s.async_scheduling and method in ("ngram", "suffix"):
                 raise ValueError("async scheduling is only supported with eagle-family drafters")
             if s.async_scheduling and method in ("mtp", "eagle", "eagle3"):

@@ -36,6 +36,8 @@ class AttentionMetadata:
     global_seq_lens: Optional[torch.Tensor] = None   # [R] true lengths when seq_lens are a rank's local share
     # state slots for linear-attention layers (one per request)
     state_slots: Optional[torch.Tensor] = None
+    # verification step on a hybrid: recurrent layers hand their snapshots and inputs to this object
+    state_rollback: Optional[object] = None
     # padded sizes when running inside a captured graph
     padded_num_reqs: Optional[int] = None
     padded_num_tokens: Optional[int] = None

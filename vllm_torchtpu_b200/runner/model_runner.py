@@ -677,6 +677,17 @@ class ModelRunner:
         bufs, n, R, T = p["bufs"], p["n"], p["R_pad"], p["T_pad"]
         self.stats["h2d_bytes"] += bufs.upload(R)
         meta = self._make_meta(p)
+        self._pending_rollback = None
+        if p.get("has_spec") and self.mcfg.is_hybrid_gdn:
+            # recurrent layers fold all k + 1 rows into their state: keep what it takes to undo rejected ones
+            from .spec_boundary_state import StateRollback
+            k_, qsl_ = p["spec_k"], p["qsl_np"]
+            idx_ = np.nonzero(k_ > 0)[0]
+            start_ = qsl_[idx_ + 1] - 1 - k_[idx_]
+            rb = StateRollback(idx_, bufs.host_view("batch_slots", n)[idx_], start_, k_[idx_] + 1,
+                               bufs.host_view("positions", p["T"])[start_], self.device)
+            meta.state_rollback = rb
+            self._pending_rollback = (rb, [p["scheds"][int(i)].request.request_id for i in idx_])
         self.stats["steps"] += 1
         ev0 = None
         if self.timing_events is not None and self.is_cuda:
@@ -788,7 +799,13 @@ class ModelRunner:
         return res
 
     def note_sampled(self, result: dict) -> None:
-        """Host learnt the tokens of a finished step: extend the persistent rows."""
+        """Host learnt the tokens of a finished step: extend the persistent rows; on a hybrid, rebuild the
+        recurrent state of requests that rejected drafts."""
+        pend, self._pending_rollback = getattr(self, "_pending_rollback", None), None
+        if pend is not None:
+            rb, rids = pend
+            n_back = rb.rollback([len(result.get(rid) or ()) for rid in rids])
+            self.stats["state_rollbacks"] = self.stats.get("state_rollbacks", 0) + n_back
         for rid, toks in result.items():
             slot = self.batch.slot_of.get(rid)
             if slot is not None:
