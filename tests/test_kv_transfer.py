@@ -154,3 +154,95 @@ def test_offload_store_keeps_lora_and_base_kv_apart_and_releases_pins():
     store.unpin(half._loads[0][1])
     assert store.stats()["pinned"] == 0
     store.close()
+
+
+# ---- engines of different tensor-parallel degree --------------------------------------------------------
+def _rank_pool(full, tp, rank, H):
+    """One rank's slice of full caches [N, 2, H, bs, D] (heads replicated when tp > H)."""
+    h = max(1, H // tp)
+    lo = (rank // max(1, tp // H)) * h
+    return [t[:, :, lo:lo + h].contiguous() for t in full]
+
+
+@pytest.mark.parametrize("H,tp_p,tp_c", [(4, 2, 1), (4, 1, 2), (8, 4, 2), (8, 2, 4), (2, 4, 1), (2, 1, 4), (4, 2, 2)])
+def test_reshard_plan_moves_head_ranges_between_tp_degrees(H, tp_p, tp_c):
+    from vllm_torchtpu_b200.kv_transfer.reshard import KVGeometry, plan_pull, readers_of
+    from vllm_torchtpu_b200.kv_transfer.transport import PoolInfo, copy_block_spans
+    torch.manual_seed(0)
+    N, bs, D, L = 6, 4, 8, 2
+    full = [torch.randn(N, 2, H, bs, D).to(torch.bfloat16) for _ in range(L)]
+    prod = [PoolInfo(f"p{r}", _rank_pool(full, tp_p, r, H)) for r in range(tp_p)]
+    src_ids, dst_ids = [4, 1, 3], [0, 5, 2]
+    reads = {r: set() for r in range(tp_p)}
+    for cr in range(tp_c):
+        want = _rank_pool(full, tp_c, cr, H)
+        dst = PoolInfo("c", [torch.zeros_like(t) for t in want])
+        cg = KVGeometry.of_cache(dst.layers[0], tp_c, cr, H)
+        pg = KVGeometry.of_cache(prod[0].layers[0], tp_p, 0, H)
+        plan = plan_pull(cg, pg)
+        for pr, span in plan:
+            copy_block_spans(prod[pr], dst, src_ids, dst_ids, span)
+            reads[pr].add(cr)
+        for got, w in zip(dst.layers, want):
+            torch.testing.assert_close(got[dst_ids], w[src_ids])
+            untouched = [i for i in range(N) if i not in dst_ids]
+            assert not got[untouched].any()
+    # the producer's view of who reads from it agrees with what the consumers planned
+    for pr in range(tp_p):
+        pg = KVGeometry.of_cache(prod[pr].layers[0], tp_p, pr, H)
+        proto = KVGeometry.of_cache(_rank_pool(full, tp_c, 0, H)[0], tp_c, 0, H)
+        assert set(readers_of(pg, tp_c, proto)) == reads[pr]
+
+
+def test_reshard_plan_of_latent_caches_and_mismatches():
+    from vllm_torchtpu_b200.kv_transfer.reshard import KVGeometry, plan_pull
+    lat = torch.zeros(4, 16, 72, dtype=torch.bfloat16)
+    c = KVGeometry.of_cache(lat, 4, 3, 1)
+    p = KVGeometry.of_cache(lat, 2, 0, 1)
+    (pr, span), = plan_pull(c, p)
+    assert pr == 1 and span.nbytes == 16 * 72 * 2 and span.chunks == 1
+    gqa = KVGeometry.of_cache(torch.zeros(4, 2, 2, 16, 8, dtype=torch.bfloat16), 1, 0, 2)
+    with pytest.raises(ValueError):
+        plan_pull(gqa, p)
+    with pytest.raises(ValueError):
+        plan_pull(gqa, KVGeometry(1, 0, 4, gqa.head_bytes, 2 * gqa.block_bytes))
+
+
+@pytest.mark.parametrize("tp_p,tp_c", [(2, 1), (1, 2)])
+def test_worker_halves_pull_across_tp_degrees_and_producers_wait_for_all_readers(tp_p, tp_c):
+    """Worker halves of a producer engine and a consumer engine with different degrees, one pair per rank in
+    this process: every consumer rank assembles its blocks from the producer ranks that hold its heads, and a
+    producer rank releases the transfer only when all its readers have acknowledged."""
+    from vllm_torchtpu_b200.kv_transfer.p2p_connector import P2PWorkerHalf, _Shared, rank_engine_id
+    from vllm_torchtpu_b200.kv_transfer.reshard import KVGeometry
+    torch.manual_seed(1)
+    H, N, bs, D, L = 4, 8, 4, 8, 2
+    full = [torch.randn(N, 2, H, bs, D).to(torch.bfloat16) for _ in range(L)]
+    tag = f"rs{tp_p}{tp_c}"
+
+    def half(base, tp, rank, layers, role):
+        eid = rank_engine_id(base, rank, tp)
+        tr = LocalTransport(eid)
+        tr.register_pool(layers)
+        sh = _Shared(eid, role, bs, "recompute", KVGeometry.of_cache(layers[0], tp, rank, H), base)
+        return sh, P2PWorkerHalf(sh, tr, lambda h, eid=eid: InProcessChannel(eid, h))
+    prods = [half(tag + "P", tp_p, r, _rank_pool(full, tp_p, r, H), base.KVConnectorRole.PRODUCER)
+             for r in range(tp_p)]
+    cons = [half(tag + "C", tp_c, r, [torch.zeros_like(t) for t in _rank_pool(full, tp_c, r, H)],
+                 base.KVConnectorRole.CONSUMER) for r in range(tp_c)]
+    remote, local = [5, 2, 7], [1, 3, 0]
+    for sh, _ in prods:
+        sh.pending_sends["u1"] = base.SendMeta("req", "u1", remote, 12, base.now() + 60)
+    geom = prods[0][0].geometry.to_dict()
+    for cr, (sh, w) in enumerate(cons):
+        lm = base.LoadMeta("req", "u1", tag + "P", remote, local, 12, remote_geometry=geom)
+        w.start_load_kv(base.ConnectorMetadata([], [lm], []))
+        assert w.get_finished_recving() == ["req"] and not sh.load_failed
+        for got, want in zip(LocalTransport._pools[sh.engine_id].layers, _rank_pool(full, tp_c, cr, H)):
+            torch.testing.assert_close(got[local], want[remote])
+        done = [bool(pw.get_finished_sending()) for _, pw in prods]
+        if cr < tp_c - 1 and tp_p == 1:
+            assert done == [False]              # the second reader has not reported yet
+    assert all(not sh.pending_sends for sh, _ in prods)
+    for _, w in prods + cons:
+        w.close()

@@ -74,6 +74,36 @@ def test_block_copy_between_pools_and_pinned_host():
     assert cuda.check_status() == 0
 
 
+@pytest.mark.parametrize("H,tp_p,tp_c", [(8, 4, 2), (8, 2, 4), (2, 4, 1), (4, 1, 2)])
+def test_head_range_spans_move_between_pools_of_different_tp_degree(H, tp_p, tp_c):
+    """The span copy kernel assembles a consumer rank's blocks from the producer ranks that hold its heads."""
+    from vllm_torchtpu_b200.kv_transfer.reshard import KVGeometry, plan_pull
+    from vllm_torchtpu_b200.kv_transfer.transport import copy_block_spans
+    g = torch.Generator(device=DEV).manual_seed(0)
+    N, bs, D, L = 10, 16, 128, 3
+    full = [torch.randn((N, 2, H, bs, D), device=DEV, generator=g).bfloat16() for _ in range(L)]
+
+    def rank_pool(tp, rank):
+        h = max(1, H // tp)
+        lo = (rank // max(1, tp // H)) * h
+        return [t[:, :, lo:lo + h].contiguous() for t in full]
+    prod = [PoolInfo(f"p{r}", rank_pool(tp_p, r)) for r in range(tp_p)]
+    src_ids, dst_ids = [4, 1, 9, 3], [0, 5, 2, 7]
+    for cr in range(tp_c):
+        want = rank_pool(tp_c, cr)
+        dst = PoolInfo("c", [torch.zeros_like(t) for t in want])
+        plan = plan_pull(KVGeometry.of_cache(dst.layers[0], tp_c, cr, H),
+                         KVGeometry.of_cache(prod[0].layers[0], tp_p, 0, H))
+        for pr, span in plan:
+            copy_block_spans(prod[pr], dst, src_ids, dst_ids, span)
+        torch.cuda.synchronize()
+        for got, w in zip(dst.layers, want):
+            assert torch.equal(got[dst_ids], w[src_ids])
+            untouched = [i for i in range(N) if i not in dst_ids]
+            assert int(got[untouched].abs().sum()) == 0
+    assert cuda.check_status() == 0
+
+
 def test_nan_screen_flags_exactly_the_poisoned_blocks():
     src, _ = _pools()
     assert nan_blocks(PoolInfo("a", src), [0, 1, 2, 3]) == []

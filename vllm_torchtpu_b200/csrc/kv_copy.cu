@@ -33,6 +33,34 @@ __global__ void kv_copy_blocks_kernel(const uint8_t* const* __restrict__ src_lay
   }
 }
 
+// Part of a block: `chunks` pieces of `span_bytes`, piece c at src_off + c * src_stride of the source block and at
+// dst_off + c * dst_stride of the destination block.  Source and destination blocks may differ in size: this is
+// the move between engines whose tensor-parallel degrees differ (a [2, heads, block_size, head_dim] block of a
+// rank holds that rank's KV heads only; a head range is one piece of the K half and one of the V half).
+__global__ void kv_copy_block_spans_kernel(const uint8_t* const* __restrict__ src_layers,
+                                           uint8_t* const* __restrict__ dst_layers,
+                                           const int* __restrict__ src_ids, const int* __restrict__ dst_ids, int n,
+                                           size_t src_block_bytes, size_t dst_block_bytes, size_t src_off,
+                                           size_t dst_off, size_t span_bytes, int chunks, size_t src_stride,
+                                           size_t dst_stride, long long src_blocks, long long dst_blocks,
+                                           int* status) {
+  const int l = blockIdx.y;
+  const size_t nvec = span_bytes >> 4;
+  for (int i = blockIdx.x; i < n; i += gridDim.x) {
+    const long long s = src_ids[i], d = dst_ids[i];
+    if (s < 0 || s >= src_blocks || d < 0 || d >= dst_blocks) {
+      if (threadIdx.x == 0 && status) atomicCAS(status, ST_OK, ST_BAD_INDEX);
+      continue;
+    }
+    const uint8_t* sb = src_layers[l] + (size_t)s * src_block_bytes + src_off;
+    uint8_t* db = dst_layers[l] + (size_t)d * dst_block_bytes + dst_off;
+    for (size_t v = threadIdx.x; v < nvec * (size_t)chunks; v += blockDim.x) {
+      const size_t c = v / nvec, e = v - c * nvec;
+      reinterpret_cast<uint4*>(db + c * dst_stride)[e] = reinterpret_cast<const uint4*>(sb + c * src_stride)[e];
+    }
+  }
+}
+
 // NaN/Inf screen of the rows about to be saved: flags[i] = 1 if block i of any layer holds a
 // non-finite bf16 value (asynchronous KV stores are gated on it,
 // reference: src/vllm_torchtpu/distributed/kv_transfer/kv_save_nan_check.py:14-163).
@@ -67,6 +95,31 @@ extern "C" int b200_kv_copy_blocks(const void* const* src_layers_dev, void* cons
   kv_copy_blocks_kernel<<<grid, 256, 0, stream>>>((const uint8_t* const*)src_layers_dev,
                                                   (uint8_t* const*)dst_layers_dev, src_ids_dev, dst_ids_dev, n,
                                                   num_layers, block_bytes, src_blocks, dst_blocks, status);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int b200_kv_copy_block_spans(const void* const* src_layers_dev, void* const* dst_layers_dev,
+                                        const int* src_ids_dev, const int* dst_ids_dev, int n, int num_layers,
+                                        size_t src_block_bytes, size_t dst_block_bytes, size_t src_off,
+                                        size_t dst_off, size_t span_bytes, int chunks, size_t src_stride,
+                                        size_t dst_stride, long long src_blocks, long long dst_blocks, int* status,
+                                        cudaStream_t stream) {
+  if (n <= 0 || num_layers <= 0 || chunks <= 0 || span_bytes == 0) return 0;
+  if ((src_block_bytes | dst_block_bytes | src_off | dst_off | span_bytes | src_stride | dst_stride) % 16) {
+    b200_set_last_error("kv_copy_block_spans: sizes and offsets must be multiples of 16 bytes", __FILE__, __LINE__);
+    return -1;
+  }
+  if (src_off + (size_t)(chunks - 1) * src_stride + span_bytes > src_block_bytes ||
+      dst_off + (size_t)(chunks - 1) * dst_stride + span_bytes > dst_block_bytes) {
+    b200_set_last_error("kv_copy_block_spans: span leaves the block", __FILE__, __LINE__);
+    return -1;
+  }
+  dim3 grid(n < 1024 ? n : 1024, num_layers);
+  kv_copy_block_spans_kernel<<<grid, 256, 0, stream>>>(
+      (const uint8_t* const*)src_layers_dev, (uint8_t* const*)dst_layers_dev, src_ids_dev, dst_ids_dev, n,
+      src_block_bytes, dst_block_bytes, src_off, dst_off, span_bytes, chunks, src_stride, dst_stride, src_blocks,
+      dst_blocks, status);
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

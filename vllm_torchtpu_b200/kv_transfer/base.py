@@ -49,6 +49,7 @@ class LoadMeta:
     num_tokens: int
     remote_host: str = "127.0.0.1"
     remote_port: int = 0
+    remote_geometry: Optional[dict] = None      # the producer's block layout when degrees may differ
 
 
 @dataclass

@@ -17,9 +17,18 @@ tpu_connector.py:1331, docs/user_guide/disaggregated_serving.md:62-147):
      ``B200_P2P_WAIT_PULL_TIMEOUT`` seconds;
   7. a failed pull marks the request's blocks as load errors; by policy the request is
      recomputed locally (``recompute``) or finished with an error (``fail``).
+
+Engines of several tensor-parallel ranks: every rank runs both halves over its own pool, rank r under the
+engine id ``<engine_id>/r<r>`` and on port ``port + r``; transfer ids are derived from the request id, so
+all ranks of the producer name a transfer alike and rank 0's ``kv_transfer_params`` speak for all.  Producer
+and consumer may differ in degree: ``kv_transfer_params["remote_geometry"]`` carries the producer's block
+layout, each consumer rank works out which head ranges to fetch from which producer ranks
+(``reshard.plan_pull``) and a producer rank frees a transfer when every consumer rank that reads from it has
+acknowledged (``reshard.readers_of``).
 """
 from __future__ import annotations
 
+import hashlib
 import threading
 import uuid as uuidlib
 from typing import Optional
@@ -29,6 +38,7 @@ from ..logger import init_logger
 from .base import (ConnectorMetadata, Connector, KVConnectorRole, LoadMeta, SchedulerConnectorBase, SendMeta,
                    WorkerConnectorBase, now)
 from .stats import KVConnectorStats
+from .reshard import KVGeometry, plan_pull, readers_of, same_layout
 from .transport import InProcessChannel, IpcTransport, LocalTransport, TcpChannel, TransferError
 
 logger = init_logger(__name__)
@@ -37,8 +47,12 @@ logger = init_logger(__name__)
 class _Shared:
     """State both halves see (they live in one process)."""
 
-    def __init__(self, engine_id: str, role: str, block_size: int, policy: str):
+    def __init__(self, engine_id: str, role: str, block_size: int, policy: str, geometry: KVGeometry = None,
+                 base_engine_id: str = None):
         self.engine_id, self.role, self.block_size, self.policy = engine_id, role, block_size, policy
+        self.geometry = geometry                 # this rank's block layout (None: single-rank, equal layouts)
+        self.base_engine_id = base_engine_id or engine_id      # engine id without the rank suffix
+        self.acks: dict = {}                     # uuid -> consumer ranks that acknowledged (producer)
         self.lock = threading.Lock()
         self.pending_sends: dict = {}        # uuid -> SendMeta (producer)
         self.pulled: set = set()             # uuids the consumer reported as taken
@@ -75,7 +89,8 @@ class P2PSchedulerHalf(SchedulerConnectorBase):
         remote = list(p["remote_block_ids"])[first:need]
         local = list(block_ids)[first:need]
         lm = LoadMeta(request.request_id, p["uuid"], p["remote_engine_id"], remote, local, num_external,
-                      p.get("remote_host", "127.0.0.1"), p.get("remote_port", 0))
+                      p.get("remote_host", "127.0.0.1"), p.get("remote_port", 0),
+                      remote_geometry=p.get("remote_geometry"))
         with self.s.lock:
             self.s.loads[request.request_id] = lm
         self._new_loads.append(lm)
@@ -103,15 +118,23 @@ class P2PSchedulerHalf(SchedulerConnectorBase):
         p = request.kv_transfer_params or {}
         if self.s.role == KVConnectorRole.BOTH and not p.get("do_remote_decode", False):
             return False, None
-        uid = uuidlib.uuid4().hex
+        # the same id on every rank of this engine (the ranks schedule alike)
+        uid = hashlib.sha1(f"{self.s.base_engine_id}:{request.request_id}:{request.num_computed_tokens}"
+                           .encode()).hexdigest()[:32]
         sm = SendMeta(request.request_id, uid, list(block_ids), request.num_computed_tokens,
                       now() + envs.B200_P2P_WAIT_PULL_TIMEOUT)
         with self.s.lock:
             self.s.pending_sends[uid] = sm
         self._new_sends.append(sm)
         host, port = (self.s.address or ("127.0.0.1", 0))[:2]
-        return True, {"uuid": uid, "remote_engine_id": self.s.engine_id, "remote_block_ids": list(block_ids),
-                      "remote_host": host, "remote_port": port, "num_tokens": request.num_computed_tokens}
+        g = self.s.geometry
+        if g is not None and isinstance(port, int):
+            port -= g.rank                       # the port of rank 0; rank r listens on port + r
+        params = {"uuid": uid, "remote_engine_id": self.s.base_engine_id, "remote_block_ids": list(block_ids),
+                  "remote_host": host, "remote_port": port, "num_tokens": request.num_computed_tokens}
+        if g is not None:
+            params["remote_geometry"] = g.to_dict()
+        return True, params
 
     def build_connector_meta(self, scheduler_output) -> ConnectorMetadata:
         m = ConnectorMetadata(self._new_sends, self._new_loads, [])
@@ -136,7 +159,17 @@ class P2PWorkerHalf(WorkerConnectorBase):
         if op == "PULLED":
             with self.s.lock:
                 if msg["uuid"] in self.s.pending_sends:
-                    self.s.pulled.add(msg["uuid"])
+                    g, cg = self.s.geometry, msg.get("consumer_geometry")
+                    if g is None or not cg:
+                        self.s.pulled.add(msg["uuid"])
+                    else:
+                        # free when every consumer rank that reads from this rank has reported
+                        c = KVGeometry.from_dict(cg)
+                        got = self.s.acks.setdefault(msg["uuid"], set())
+                        got.add(c.rank)
+                        if got >= set(readers_of(g, c.tp, c)):
+                            self.s.pulled.add(msg["uuid"])
+                            del self.s.acks[msg["uuid"]]
             return {"ok": True}
         if op == "PING":
             return {"ok": True, "engine_id": self.s.engine_id}
@@ -149,19 +182,25 @@ class P2PWorkerHalf(WorkerConnectorBase):
         for lm in meta.loads:
             t0 = now()
             try:
-                addr = self._address_of(lm)
-                if lm.remote_engine not in self._opened:
-                    hello = self.channel.request(addr, {"op": "HELLO"}, envs.B200_KV_STAGE_WAIT_TIMEOUT_SECS)
-                    if not hello.get("ok"):
-                        raise TransferError(hello.get("error", "handshake refused"))
-                    self.transport.open_remote(hello["pool"])
-                    self._opened.add(lm.remote_engine)
-                self.transport.pull(lm.remote_engine, lm.remote_block_ids, lm.local_block_ids)
-                try:
-                    self.channel.request(addr, {"op": "PULLED", "uuid": lm.uuid}, 5.0)
-                except (OSError, TimeoutError, ConnectionError) as e:
-                    # data is here; the producer will free the blocks when its timer expires
-                    logger.warning("could not acknowledge pull of %s: %r", lm.uuid, e)
+                for engine, addr, span in self._sources(lm):
+                    if engine not in self._opened:
+                        hello = self.channel.request(addr, {"op": "HELLO"}, envs.B200_KV_STAGE_WAIT_TIMEOUT_SECS)
+                        if not hello.get("ok"):
+                            raise TransferError(hello.get("error", "handshake refused"))
+                        self.transport.open_remote(hello["pool"])
+                        self._opened.add(engine)
+                    if span is None:
+                        self.transport.pull(engine, lm.remote_block_ids, lm.local_block_ids)
+                    else:
+                        self.transport.pull(engine, lm.remote_block_ids, lm.local_block_ids, span)
+                    ack = {"op": "PULLED", "uuid": lm.uuid}
+                    if self.s.geometry is not None and lm.remote_geometry:
+                        ack["consumer_geometry"] = self.s.geometry.to_dict()
+                    try:
+                        self.channel.request(addr, ack, 5.0)
+                    except (OSError, TimeoutError, ConnectionError) as e:
+                        # data is here; the producer will free the blocks when its timer expires
+                        logger.warning("could not acknowledge pull of %s: %r", lm.uuid, e)
                 with self.s.lock:
                     self.s.load_done.add(lm.request_id)
                 self._recv_done.append(lm.request_id)
@@ -173,10 +212,21 @@ class P2PWorkerHalf(WorkerConnectorBase):
                     self.s.error_blocks.update(lm.local_block_ids)
                 self.s.stats.record_load(len(lm.local_block_ids), now() - t0, ok=False)
 
-    def _address_of(self, lm: LoadMeta):
-        if isinstance(self.channel, InProcessChannel):
-            return ("inproc", lm.remote_engine)
-        return (lm.remote_host, lm.remote_port)
+    def _sources(self, lm: LoadMeta) -> list:
+        """[(engine id, control address, Span or None)] this rank fetches a transfer from."""
+        inproc = isinstance(self.channel, InProcessChannel)
+        g, rg = self.s.geometry, lm.remote_geometry
+        if g is None or not rg:
+            addr = ("inproc", lm.remote_engine) if inproc else (lm.remote_host, lm.remote_port)
+            return [(lm.remote_engine, addr, None)]
+        prod = KVGeometry.from_dict(rg)
+        out = []
+        for pr, span in plan_pull(g, prod):
+            engine = rank_engine_id(lm.remote_engine, pr, prod.tp)
+            addr = ("inproc", engine) if inproc else (lm.remote_host, lm.remote_port + pr)
+            peer = KVGeometry(prod.tp, pr, prod.num_kv_heads, prod.head_bytes, prod.block_bytes)
+            out.append((engine, addr, None if same_layout(g, peer) else span))
+        return out
 
     def get_finished_recving(self) -> list:
         out, self._recv_done = self._recv_done, []
@@ -209,13 +259,26 @@ class P2PWorkerHalf(WorkerConnectorBase):
         self.channel.close()
 
 
+def rank_engine_id(engine_id: str, rank: int, tp: int) -> str:
+    return engine_id if tp <= 1 else f"{engine_id}/r{rank}"
+
+
 def create_p2p_connector(cfg, runner, *, transport=None, channel_factory=None) -> Connector:
+    from ..parallel.state import get_state
     kt = cfg.kv_transfer or {}
     role = kt.get("kv_role", KVConnectorRole.BOTH)
-    engine_id = kt.get("engine_id") or f"engine-{uuidlib.uuid4().hex[:8]}"
+    tp = get_state().tp
+    if tp.size > 1 and not kt.get("engine_id"):
+        raise ValueError("kv_transfer with tensor parallelism needs an explicit engine_id (the same on every rank)")
+    base_id = kt.get("engine_id") or f"engine-{uuidlib.uuid4().hex[:8]}"
+    engine_id = rank_engine_id(base_id, tp.rank_in_group, tp.size)
     extra = kt.get("kv_connector_extra_config", {})
     policy = kt.get("kv_load_failure_policy", "recompute")
-    shared = _Shared(engine_id, role, cfg.cache.block_size, policy)
+    geometry = None
+    first = runner.kv_caches[0] if runner.kv_caches else None
+    if first is not None and hasattr(first, "dim"):
+        geometry = KVGeometry.of_cache(first, tp.size, tp.rank_in_group, cfg.model.num_kv_heads)
+    shared = _Shared(engine_id, role, cfg.cache.block_size, policy, geometry, base_id)
     if transport is None:
         kind = extra.get("transport", "ipc" if str(runner.device).startswith("cuda") else "local")
         transport = IpcTransport(engine_id) if kind == "ipc" else LocalTransport(engine_id)
@@ -226,6 +289,10 @@ def create_p2p_connector(cfg, runner, *, transport=None, channel_factory=None) -
         else:
             host = extra.get("host", "127.0.0.1")
             port = int(extra.get("port", 0))
+            if tp.size > 1:
+                if not port:
+                    raise ValueError("kv_transfer with tensor parallelism needs a fixed port (rank r listens on port + r)")
+                port += tp.rank_in_group
             channel_factory = lambda h: TcpChannel(host, port, h)
     worker = P2PWorkerHalf(shared, transport, channel_factory)
     sched = P2PSchedulerHalf(shared)

@@ -85,6 +85,46 @@ def copy_blocks(src: PoolInfo, dst: PoolInfo, src_ids: list, dst_ids: list) -> N
         b[di] = a[si].to(b.dtype)
 
 
+def copy_block_spans(src: PoolInfo, dst: PoolInfo, src_ids: list, dst_ids: list, span) -> None:
+    """Part of every block (``reshard.Span``): pools of different block sizes, e.g. a head range of a
+    tensor-parallel producer into the blocks of a consumer with another degree."""
+    if len(src_ids) != len(dst_ids):
+        raise TransferError("block id lists differ in length")
+    if not src_ids:
+        return
+    if len(src.layers) != len(dst.layers):
+        raise TransferError("source and destination pools have different layer counts")
+    if max(src_ids) >= src.num_blocks or max(dst_ids) >= dst.num_blocks or min(src_ids + dst_ids) < 0:
+        raise TransferError("block id out of range")
+    last = (span.chunks - 1)
+    if (span.src_off + last * span.src_stride + span.nbytes > src.block_bytes
+            or span.dst_off + last * span.dst_stride + span.nbytes > dst.block_bytes):
+        raise TransferError("span leaves the block")
+    if dst.layers[0].is_cuda or src.layers[0].is_cuda:
+        from ..ops import count_launch, cuda
+        dev = dst.layers[0].device if dst.layers[0].is_cuda else src.layers[0].device
+        s = torch.tensor(src_ids, dtype=torch.int32, device=dev)
+        d = torch.tensor(dst_ids, dtype=torch.int32, device=dev)
+        ws = cuda.Workspace.get(dev)
+        src_tbl, dst_tbl = src.ptr_table().to(dev), dst.ptr_table().to(dev)
+        z = ctypes.c_size_t
+        cuda._check(cuda.lib().b200_kv_copy_block_spans(
+            cuda._p(src_tbl), cuda._p(dst_tbl), cuda._p(s), cuda._p(d), ctypes.c_int(len(src_ids)),
+            ctypes.c_int(len(src.layers)), z(src.block_bytes), z(dst.block_bytes), z(span.src_off), z(span.dst_off),
+            z(span.nbytes), ctypes.c_int(span.chunks), z(span.src_stride), z(span.dst_stride),
+            ctypes.c_longlong(src.num_blocks), ctypes.c_longlong(dst.num_blocks), cuda._p(ws.status),
+            cuda._stream()), "kv_copy_block_spans")
+        count_launch()
+        return
+    si, di = torch.tensor(src_ids), torch.tensor(dst_ids)
+    for a, b in zip(src.layers, dst.layers):
+        av = a.reshape(a.shape[0], -1).view(torch.uint8)
+        bv = b.reshape(b.shape[0], -1).view(torch.uint8)
+        for c in range(span.chunks):
+            so, do = span.src_off + c * span.src_stride, span.dst_off + c * span.dst_stride
+            bv[di, do:do + span.nbytes] = av[si, so:so + span.nbytes]
+
+
 def nan_blocks(pool: PoolInfo, block_ids: list) -> list:
     """Which of ``block_ids`` hold a non-finite bf16 value in any layer.  Saves and transfers of such
     blocks are refused: a poisoned block would otherwise be served to later requests
@@ -132,11 +172,14 @@ class LocalTransport:
         if info["engine_id"] not in LocalTransport._pools:
             raise TransferError(f"unknown engine {info['engine_id']}")
 
-    def pull(self, remote_engine: str, remote_ids: list, local_ids: list) -> None:
+    def pull(self, remote_engine: str, remote_ids: list, local_ids: list, span=None) -> None:
         src = LocalTransport._pools.get(remote_engine)
         if src is None:
             raise TransferError(f"source engine {remote_engine} unreachable")
-        copy_blocks(src, LocalTransport._pools[self.engine_id], remote_ids, local_ids)
+        if span is None:
+            copy_blocks(src, LocalTransport._pools[self.engine_id], remote_ids, local_ids)
+        else:
+            copy_block_spans(src, LocalTransport._pools[self.engine_id], remote_ids, local_ids, span)
 
 
 class _RawLayer:
@@ -195,8 +238,8 @@ class IpcTransport:
         from ..ops import cuda
         if info["engine_id"] in self.remotes:
             return
-        if info["block_bytes"] != self.local.block_bytes or info["num_layers"] != len(self.local.layers):
-            raise TransferError("remote pool geometry differs (heterogeneous resharding is not enabled)")
+        if info["num_layers"] != len(self.local.layers):
+            raise TransferError("remote pool has another number of layers")
         layers = []
         opened: dict = {}                    # several layers may live in one exported allocation
         for hx, off in zip(info["handles"], info.get("offsets") or [0] * len(info["handles"])):
@@ -214,11 +257,14 @@ class IpcTransport:
                                        device=self.local.layers[0].device)
         self.remotes[info["engine_id"]] = pool
 
-    def pull(self, remote_engine: str, remote_ids: list, local_ids: list) -> None:
+    def pull(self, remote_engine: str, remote_ids: list, local_ids: list, span=None) -> None:
         src = self.remotes.get(remote_engine)
         if src is None:
             raise TransferError(f"source engine {remote_engine} is not mapped")
-        copy_blocks(src, self.local, remote_ids, local_ids)
+        if span is None:
+            copy_blocks(src, self.local, remote_ids, local_ids)
+        else:
+            copy_block_spans(src, self.local, remote_ids, local_ids, span)
 
 
 # --------------------------------------------------------------- control plane
