@@ -597,29 +597,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         if (lane == 0) mbar_arrive(&tempty[acc]);
       } else if (FULL && p.row_route != nullptr) {
         // expert-parallel combine: every output row is stored into the return slot of the rank that
-        // sent the token (a peer's heap or this rank's own)
+        // sent the token (a peer's heap or this rank's own).  32 tokens x 128 columns are turned in shared
+        // memory so that a token's 256 bytes leave as sixteen 16-byte stores (NVLink packets of 2-byte
+        // stores were the bottleneck); the stores are fenced once, before the CTA reports itself done.
+        __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + Cfg::PUSH_OFF);
+        const int seg = row & 15, jt = row >> 4;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
-          if (c0 >= t_valid) break;
+          if (c0 >= t_valid) break;               // uniform over the four epilogue warps
           uint32_t r[32];
           tmem_ld_32x32(taddr + c0, r);
           tmem_ld_wait();
-          if (n < p.N) {
+          __nv_bfloat16* st = stg + (push_count & 1) * (32 * BM);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (c0 + j < t_valid) {
-                const int2 rt = __ldg(p.row_route + t0 + c0 + j);
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peer[rt.x] + p.route_ret_off) +
-                                     (size_t)rt.y * p.N + n;
-                *dst = __float2bfloat16(__uint_as_float(r[j]));
-              }
+          for (int j = 0; j < 32; ++j) st[j * BM + row] = __float2bfloat16(__uint_as_float(r[j]));
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int j = jt + 8 * i;
+            if (c0 + j < t_valid) {
+              const int2 rt = __ldg(p.row_route + t0 + c0 + j);
+              const uint4 v = *reinterpret_cast<const uint4*>(st + j * BM + seg * 8);
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.peer[rt.x] + p.route_ret_off) +
+                                        (size_t)rt.y * p.N + wk.n0 + seg * 8) = v;
             }
           }
+          ++push_count;
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[acc]);
-        __threadfence_system();
       } else if (FULL && p.splits == 1 && fused && p.ar_mode < 2) {
         // partial tile -> the owner's slab [BN][BM] bf16, 32 columns (8 KB) per bulk copy
         uint8_t* slab = reinterpret_cast<uint8_t*>(tile_dst<BN, MODE>(p, wk, 0).base);
@@ -971,7 +978,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
   if (fused && threadIdx.x == 64) {      // a thread that holds the epoch (warp 0 does not)
-    __threadfence();
+    // the barrier above ordered every thread's stores before this fence (system scope for the routed rows
+    // that went to peers)
+    if (p.ar_mode == 4) __threadfence_system();
+    else __threadfence();
     const int arrived = atomicAdd(p.cta_done, 1) + 1;
     if (arrived == (int)gridDim.x) {
       *p.cta_done = 0;

@@ -80,6 +80,8 @@ __global__ void __launch_bounds__(1024) ep_count_kernel(const EpParams p) {
 // grid: any; one warp per (token, k) pair.
 __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpParams p) {
   __shared__ int base[EP_MAX_EXPERTS];     // first row of (expert e, this source rank) at e's owner
+  __shared__ int s_tot[EP_MAX_EXPERTS];    // rows of expert e over all source ranks
+  __shared__ int s_base2[EP_MAX_EXPERTS];
   __shared__ int s_ok, s_last;
   const int epoch = *reinterpret_cast<volatile int*>(p.ctrl);
   const int e_local = p.E / p.world;
@@ -92,25 +94,40 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpParams p) {
   __syncthreads();
   const int* cnt = reinterpret_cast<const int*>(p.peer[p.rank] + p.lay.cnt_off);   // [world][E]
   if (s_ok) {
+    // per-expert totals and this rank's share in front of it, from one coalesced pass over the count
+    // matrix; then an exclusive prefix over each owner's experts out of shared memory
     for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
-      const int owner = e / e_local, first = owner * e_local;
-      int b = 0;
-      for (int e2 = first; e2 < e; ++e2)
-        for (int s = 0; s < p.world; ++s) b += __ldcg(cnt + (size_t)s * p.E + e2);
-      for (int s = 0; s < p.rank; ++s) b += __ldcg(cnt + (size_t)s * p.E + e);
-      base[e] = b;
+      int tot = 0, before = 0;
+      for (int s = 0; s < p.world; ++s) {
+        const int c = __ldcg(cnt + (size_t)s * p.E + e);
+        tot += c;
+        if (s < p.rank) before += c;
+      }
+      s_tot[e] = tot;
+      base[e] = before;
+    }
+  }
+  __syncthreads();
+  if (s_ok) {
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+      const int first = (e / e_local) * e_local;
+      int b = base[e];
+      for (int e2 = first; e2 < e; ++e2) b += s_tot[e2];
+      s_base2[e] = b;
     }
     if (blockIdx.x == 0) {
       // row offsets of this rank's own experts for the grouped GEMMs
       for (int le = threadIdx.x; le <= e_local; le += blockDim.x) {
         int b = 0;
-        for (int e2 = p.rank * e_local; e2 < p.rank * e_local + le; ++e2)
-          for (int s = 0; s < p.world; ++s) b += __ldcg(cnt + (size_t)s * p.E + e2);
+        for (int e2 = p.rank * e_local; e2 < p.rank * e_local + le; ++e2) b += s_tot[e2];
         p.group_off[le] = b < p.cap ? b : p.cap;
         if (le == e_local && b > p.cap) atomicCAS(p.status, ST_OK, ST_BAD_INDEX);
       }
     }
   }
+  __syncthreads();
+  if (s_ok)
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) base[e] = s_base2[e];
   __syncthreads();
   if (s_ok) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;

@@ -160,7 +160,7 @@ class EpState:
                 + (1 << 20))
 
 
-def moe_experts_ep(x, w13, w2, topk_ids, topk_w, heap, num_experts: int):
+def moe_experts_ep(x, w13, w2, topk_ids, topk_w, heap, num_experts: int, phase_events: list = None):
     """MoE expert computation under expert parallelism with the dispatch / combine all-to-all done by
     NVLink stores inside the pipeline: rows are PUT into the owners' receive buffers, the owners run
     the grouped tcgen05 GEMMs on what they received, and the epilogue of the second GEMM stores each
@@ -174,6 +174,14 @@ def moe_experts_ep(x, w13, w2, topk_ids, topk_w, heap, num_experts: int):
     E_local, I = w13.shape[0], w2.shape[2]
     if T > st.max_tokens or k != st.k or H != st.H or num_experts != st.E:
         raise RuntimeError("fused EP plane was configured for a different shape")
+
+    def mark():
+        # measurement aid: an event after every phase (dispatch, first GEMM, routed GEMM, combine)
+        if phase_events is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            phase_events.append(e)
+    mark()
     L = _c.lib()
     ws = _c.Workspace.get(x.device)
     spin = ctypes.c_uint(min(heap.spin_limit, 2**31 - 1))
@@ -184,9 +192,11 @@ def moe_experts_ep(x, w13, w2, topk_ids, topk_w, heap, num_experts: int):
                                  c_int(H), c_int(num_experts), c_int(st.cap), _c._p(ws.status), spin,
                                  _c._stream()), "ep_dispatch")
     count_launch(3)
+    mark()
     recv_x = heap.tensor(st.recv_x, (st.cap, H), torch.bfloat16)
     avg = max(1, (T * k) // max(1, E_local))
     grouped_gemm(recv_x, w13, st.group_off, True, avg, out=st.act)
+    mark()
     _c._check(L.b200_grouped_gemm_bf16_routed(
         _c._p(st.act), _c._p(w2), _c._p(st.group_off), c_int(E_local), c_int(st.cap), c_int(H), c_int(I),
         c_int(avg), heap.peers_c, c_int(heap.rank), c_int(heap.world),
@@ -194,6 +204,7 @@ def moe_experts_ep(x, w13, w2, topk_ids, topk_w, heap, num_experts: int):
         c_ulonglong(st.ret_flag.offset), _c._p(st.ctrl), _c._p(ws.status), c_int(_c._sms), _c._stream()),
         "grouped_gemm_routed")
     count_launch()
+    mark()
     out = torch.empty((T, H), dtype=x.dtype, device=x.device)
     topk_w = topk_w.contiguous()
     _c._check(L.b200_ep_combine(c_void_p(heap.local_ptr), c_ulonglong(st.ret.offset),
@@ -202,4 +213,5 @@ def moe_experts_ep(x, w13, w2, topk_ids, topk_w, heap, num_experts: int):
                                 c_int(num_experts), c_int(heap.world), _c._p(ws.status), spin, _c._stream()),
               "ep_combine")
     count_launch()
+    mark()
     return out
