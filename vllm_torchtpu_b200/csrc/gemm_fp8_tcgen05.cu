@@ -48,7 +48,10 @@ struct Cfg {
   static constexpr int BAR_BYTES = 256;
   static constexpr int PREFIX_BYTES = (MAX_GROUPS + 1) * 4 + 12;      // keeps what follows 16-byte aligned
   static constexpr int SCALE_BYTES = EPI_WARPS * 2 * CW * 4;          // per promotion warp: two rows of column scales
-  static constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + PREFIX_BYTES + SCALE_BYTES + 1024;
+  // routed rows: per set of four promotion warps two buffers of [32 tokens][128 rows] bf16
+  static constexpr int ROUTE_BYTES = (EPI_WARPS / 4) * 2 * 32 * BM * 2;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + BAR_BYTES + PREFIX_BYTES + SCALE_BYTES + ROUTE_BYTES + 1024;
+  static_assert(SMEM <= 232448, "shared memory budget");
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static_assert(BM * BN * 4 <= STAGES * STAGE_BYTES, "split-K partial must fit in the stage ring");
 };
@@ -147,6 +150,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_prefix = reinterpret_cast<int*>(smem + STAGES * C::STAGE_BYTES + C::BAR_BYTES);
   float* s_scale = reinterpret_cast<float*>(smem + STAGES * C::STAGE_BYTES + C::BAR_BYTES + C::PREFIX_BYTES);
+  __nv_bfloat16* s_route = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * C::STAGE_BYTES + C::BAR_BYTES +
+                                                            C::PREFIX_BYTES + C::SCALE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -248,6 +253,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     const int row = q * 32 + lane;
     const int col0 = ((warp - 2) >> 2) * CW;
     uint32_t pc = 0;
+    uint32_t route_count = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const Work k = get_work<BN>(w, p, s_prefix);
@@ -311,17 +317,32 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 #pragma unroll
         for (int c = 0; c < CW; ++c) part[(col0 + c) * BM + row] = acc[c];
       } else if (ROUTED) {
-        if (n < p.N) {
+        // every output row goes to the return slot of the rank that sent the token: 32 tokens x 128 rows are
+        // turned in shared memory so that a token's 256 bytes leave as sixteen 16-byte stores; the stores
+        // are fenced once, before the CTA reports itself done
+        const int grp = (warp - 2) >> 2;
+        __nv_bfloat16* stg = s_route + grp * (2 * 32 * BM);
+        const int seg = row & 15, jt = row >> 4;
 #pragma unroll
-          for (int c = 0; c < CW; ++c) {
-            if (c < cv) {
-              const int2 rt = __ldg(p.row_route + k.t_row + col0 + c);
-              reinterpret_cast<__nv_bfloat16*>(p.peer[rt.x] + p.route_ret_off)[(size_t)rt.y * p.N + n] =
-                  __float2bfloat16(acc[c]);
+        for (int c0 = 0; c0 < CW; c0 += 32) {
+          if (c0 < cv) {                              // uniform over the four warps of the set
+            __nv_bfloat16* st = stg + (route_count & 1) * (32 * BM);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) st[j * BM + row] = __float2bfloat16(acc[c0 + j]);
+            asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int j = jt + 8 * i;
+              if (c0 + j < cv) {
+                const int2 rt = __ldg(p.row_route + k.t_row + col0 + c0 + j);
+                const uint4 v = *reinterpret_cast<const uint4*>(st + j * BM + seg * 8);
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.peer[rt.x] + p.route_ret_off) +
+                                          (size_t)rt.y * p.N + k.n0 + seg * 8) = v;
+              }
             }
+            ++route_count;
           }
         }
-        __threadfence_system();
       } else {
         if (n < p.N) {
           const float bias = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;
@@ -411,7 +432,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
   if (MODE != 0 && threadIdx.x == 64) {
-    __threadfence();
+    // the barrier above ordered every thread's stores before this fence (system scope for routed rows)
+    if (ROUTED) __threadfence_system();
+    else __threadfence();
     const int arrived = atomicAdd(p.cta_done, 1) + 1;
     if (arrived == (int)gridDim.x) {
       *p.cta_done = 0;
