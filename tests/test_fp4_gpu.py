@@ -79,3 +79,46 @@ def test_dequant_kernel_is_bit_exact_and_large_token_counts_use_it(fmt):
     y = cu().w4a16_gemm(x, wp.contiguous(), sc.contiguous(), fmt, gs)
     want = x.float() @ wd.bfloat16().float().t()
     assert (y.float() - want).abs().max() <= 1e-2 * want.abs().max() + 1e-2
+
+
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("T,N,K,bias", [(1, 256, 128, False), (16, 1024, 512, True), (64, 1280, 4096, False),
+                                        (100, 200, 256, True), (1100, 384, 1024, False)])
+def test_int4_group_weights_on_the_w4a16_kernel(group, T, N, K, bias):
+    """AWQ / GPTQ style weights (unsigned nibbles, fp16 group scales, zero points) stay packed: the fused kernel
+    for decode sizes, the dequant kernel + bf16 GEMM from 1024 tokens; the dequant kernel is bit-exact against
+    (nibble - zero) * scale rounded to bf16."""
+    from vllm_torchtpu_b200.ops import cuda_fp4
+    from vllm_torchtpu_b200.quantization.int4 import dequantize_int4_group, quantize_int4_group
+    g = torch.Generator(device=DEV).manual_seed(T + N + group)
+    x = torch.randn(T, K, device=DEV, generator=g).bfloat16()
+    w = torch.randn(N, K, device=DEV, generator=g) * 0.05 + 0.01
+    b = torch.randn(N, device=DEV, generator=g).bfloat16() if bias else None
+    wp, sc, zp = quantize_int4_group(w, group)
+    wd = dequantize_int4_group(wp, sc, zp, group).bfloat16()
+    got_w = cuda_fp4.dequant_int4(wp.contiguous(), sc.half().contiguous(), zp.contiguous(), group)
+    assert torch.equal(got_w, wd)
+    y = cuda_fp4.w4a16_int4_gemm(x, wp.contiguous(), sc.half().contiguous(), zp.contiguous(), group, b)
+    torch.cuda.synchronize()
+    assert cu().check_status() == 0
+    want = x.float() @ wd.float().t()
+    if bias:
+        want = want + b.float()
+    err = (y.float() - want).abs().max().item()
+    assert err <= 1e-2 * want.abs().max().item() + 1e-2, err
+
+
+def test_int4_linear_method_runs_packed_on_the_device():
+    from vllm_torchtpu_b200.layers.linear import ColumnParallelLinear
+    from vllm_torchtpu_b200.quantization import QuantConfig
+    lin = ColumnParallelLinear("l", 512, [768], dtype=torch.bfloat16, device=DEV, quant_config=QuantConfig("awq"))
+    lin.init_dummy(0.05, 0)
+    assert lin.weight.dtype == torch.uint8 and lin.weight.shape == (768, 256) and lin.weight_scale_h is not None
+    from vllm_torchtpu_b200.quantization.int4 import dequantize_int4_group
+    x = torch.randn(20, 512, device=DEV).bfloat16()
+    from vllm_torchtpu_b200 import ops
+    before = ops.launch_count()
+    y = lin(x)
+    assert ops.launch_count() - before == 1          # one fused kernel, no dequantised copy of the weight
+    want = x.float() @ dequantize_int4_group(lin.weight, lin.weight_scale, lin.weight_zero, lin.group).bfloat16().float().t()
+    assert (y.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item() + 1e-2

@@ -71,6 +71,8 @@ struct Params {
   const __nv_bfloat16* bias;
   const uint8_t* scales;             // mxfp4: e8m0 [rows, K / 32]; nvfp4: e4m3 [rows, K / 16]
   const float* global_scale;         // nvfp4: one fp32 per tensor (or per group of rows: see gs_per_group)
+  const uint8_t* zeros;              // int4: zero point per group, uint8 [rows, K >> group_shift]; scales are fp16 there
+  int group_shift;                   // int4: log2 of the group size (32 ... K)
   int* status;
   int T, N, K, ldy;
   int n_tiles, t_tiles, kb_total;
@@ -151,6 +153,21 @@ __device__ __forceinline__ uint32_t e2m1_pair_to_bf16x2(uint32_t wd, float scale
   return *reinterpret_cast<uint32_t*>(&b2);
 }
 
+// Unsigned 4-bit integers with a group scale and zero point (AWQ / GPTQ): nibble u placed in the top fraction
+// bits of 128.0f gives 128 + u exactly; (that - (128 + zero)) * scale is one exact subtraction and one rounded
+// product in fp32, then one rounding to bf16: the same two roundings as dequantising in fp32 and casting.
+// `zp` = 128 + zero point.
+template <int J>
+__device__ __forceinline__ uint32_t int4_pair_to_bf16x2(uint32_t wd, float scale, float zp) {
+  constexpr int LO = 16 - 8 * J, HI = 12 - 8 * J;            // nibble bit 0 -> bit 16
+  const uint32_t lo_b = LO >= 0 ? (wd << (LO >= 0 ? LO : 0)) : (wd >> (LO < 0 ? -LO : 0));
+  const uint32_t hi_b = HI >= 0 ? (wd << (HI >= 0 ? HI : 0)) : (wd >> (HI < 0 ? -HI : 0));
+  const float lo = __uint_as_float(0x43000000u | (lo_b & 0x000F0000u));
+  const float hi = __uint_as_float(0x43000000u | (hi_b & 0x000F0000u));
+  __nv_bfloat162 b2 = __floats2bfloat162_rn((lo - zp) * scale, (hi - zp) * scale);
+  return *reinterpret_cast<uint32_t*>(&b2);
+}
+
 template <int BN>
 __device__ __forceinline__ Work get_work(int w, const Params& p, const int* s_prefix) {
   Work k;
@@ -182,7 +199,7 @@ __device__ __forceinline__ Work get_work(int w, const Params& p, const int* s_pr
   return k;
 }
 
-// FMT 0: mxfp4, FMT 1: nvfp4
+// FMT 0: mxfp4, FMT 1: nvfp4, FMT 2: int4 with fp16 group scales and uint8 zero points
 template <int BN, int FMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params p) {
@@ -303,9 +320,9 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     int s = 0, as = 0;
     uint32_t ph = 0, aph = 0;
     bool ok = true;
-    constexpr int G = FMT == 0 ? 32 : 16;
+    constexpr int G = FMT == 1 ? 16 : 32;        // int4: the block is read as two halves of 32 (groups are >= 32)
     constexpr int SPB = BK / G;                  // scale bytes per K block
-    const int sc_ld = p.K / G;
+    const int sc_ld = FMT == 2 ? (p.K >> p.group_shift) : p.K / G;
     int pending = -1;                            // A slot whose store has been issued but not published
     auto publish = [&]() {
       if (pending >= 0) {
@@ -319,15 +336,24 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const Work k = get_work<BN>(w, p, s_prefix);
       const bool live = k.n0 + row < p.N;
-      const uint8_t* sc_row = p.scales + (size_t)(k.w_row + row) * sc_ld;
+      const uint8_t* sc_row = p.scales + (size_t)(k.w_row + row) * sc_ld * (FMT == 2 ? 2 : 1);
+      const uint8_t* zp_row = FMT == 2 ? p.zeros + (size_t)(k.w_row + row) * sc_ld : nullptr;
       float gs = 1.f;
       if (FMT == 1) gs = p.global_scale[p.gs_per_group ? (k.w_row / p.w_rows_per_group) : 0];
       for (int kb = k.kb0; kb < k.kb1; ++kb) {
         if (((kb - k.kb0) % EXP_GROUPS) == grp) {
           // group scales of this block (a few bytes per row; the row's scales share cache lines over K)
-          float sc[SPB];
+          float sc[SPB], zp[SPB];
 #pragma unroll
           for (int g = 0; g < SPB; ++g) {
+            if (FMT == 2) {
+              const int gi = (kb * BK + g * 32) >> p.group_shift;
+              const bool in = live && gi < sc_ld;
+              sc[g] = in ? __half2float(__ldg(reinterpret_cast<const __half*>(sc_row) + gi)) : 0.f;
+              zp[g] = 128.f + (in ? (float)__ldg(zp_row + gi) : 0.f);
+              continue;
+            }
+            zp[g] = 0.f;
             const int gi = kb * SPB + g;
             const uint8_t b = (live && gi < sc_ld) ? __ldg(sc_row + gi) : 0;
             if (FMT == 0) {
@@ -349,12 +375,15 @@ gemm_w4a16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 #pragma unroll
           for (int c = 0; c < 8; ++c) {          // 8 values = one packed word
             const uint32_t wd = words[c];
-            float s8 = sc[0];
+            float s8 = sc[0], z8 = zp[0];
 #pragma unroll
             for (int g = 1; g < SPB; ++g)
-              if ((c * 8) / G == g) s8 = sc[g];
+              if ((c * 8) / G == g) { s8 = sc[g]; z8 = zp[g]; }
             uint4 o;
-            if (FMT == 0) {
+            if (FMT == 2) {
+              o = make_uint4(int4_pair_to_bf16x2<0>(wd, s8, z8), int4_pair_to_bf16x2<1>(wd, s8, z8),
+                             int4_pair_to_bf16x2<2>(wd, s8, z8), int4_pair_to_bf16x2<3>(wd, s8, z8));
+            } else if (FMT == 0) {
               // a power of two is exact in bf16: the top half of its fp32 bits, in both halves of the pair
               const uint32_t s2 = (__float_as_uint(s8) >> 16) * 0x00010001u;
               o = make_uint4(e2m1_pair_to_bf16x2_pow2<0>(wd, s2), e2m1_pair_to_bf16x2_pow2<1>(wd, s2),
@@ -506,12 +535,22 @@ static int dispatch(int bn, const CUtensorMap& tmW, const CUtensorMap& tmX, cons
 
 static int run(const void* X, const void* Wp, const void* scales, const float* global_scale, void* Y,
                const void* bias, const int* group_off, int num_groups, int gs_per_group, int T, int N, int K,
-               int ldx, int ldy, int fmt, int rows_hint, int* status, int num_sms, cudaStream_t stream) {
+               int ldx, int ldy, int fmt, int rows_hint, int* status, int num_sms, cudaStream_t stream,
+               const void* zeros = nullptr, int group = 0) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
-  if (K % BK || (fmt != 0 && fmt != 1) || (fmt == 1 && global_scale == nullptr) || num_groups > MAX_GROUPS) {
-    b200_set_last_error("gemm_w4a16: K % 64 == 0, format mxfp4 (0) or nvfp4 (1, with its global scale), "
+  if (K % BK || fmt < 0 || fmt > 2 || (fmt == 1 && global_scale == nullptr) || num_groups > MAX_GROUPS) {
+    b200_set_last_error("gemm_w4a16: K % 64 == 0, format mxfp4 (0), nvfp4 (1, with its global scale) or int4 (2), "
                         "at most 1024 groups", __FILE__, __LINE__);
     return -3;
+  }
+  int group_shift = 0;
+  if (fmt == 2) {
+    while ((1 << group_shift) < group) ++group_shift;
+    if (zeros == nullptr || group < 32 || (1 << group_shift) != group || K % group) {
+      b200_set_last_error("gemm_w4a16 (int4): zero points, and a power-of-two group size >= 32 that divides K",
+                          __FILE__, __LINE__);
+      return -3;
+    }
   }
   if (group_off != nullptr && N % BM) {
     b200_set_last_error("gemm_w4a16 (grouped): N % 128 == 0 required", __FILE__, __LINE__);
@@ -524,6 +563,8 @@ static int run(const void* X, const void* Wp, const void* scales, const float* g
   p.bias = (const __nv_bfloat16*)bias;
   p.scales = (const uint8_t*)scales;
   p.global_scale = global_scale;
+  p.zeros = (const uint8_t*)zeros;
+  p.group_shift = group_shift;
   p.status = status;
   p.T = T; p.N = N; p.K = K; p.ldy = ldy;
   p.n_tiles = (N + BM - 1) / BM;
@@ -557,6 +598,7 @@ static int run(const void* X, const void* Wp, const void* scales, const float* g
   }
   const int total = group_off != nullptr ? num_sms : tiles * p.splits;
   const int grid = p.splits > 1 ? total : (total < num_sms ? total : num_sms);
+  if (fmt == 2) return dispatch<2>(bn, tmW, tmX, p, grid, stream);
   return fmt == 0 ? dispatch<0>(bn, tmW, tmX, p, grid, stream) : dispatch<1>(bn, tmW, tmX, p, grid, stream);
 }
 
@@ -605,6 +647,56 @@ __global__ void dequant_w4_kernel(const uint8_t* __restrict__ wp, const uint8_t*
 }
 }  // namespace w4
 }  // namespace b200
+
+namespace b200 {
+namespace w4 {
+__global__ void dequant_int4_kernel(const uint8_t* __restrict__ wp, const __half* __restrict__ scales,
+                                    const uint8_t* __restrict__ zeros, __nv_bfloat16* __restrict__ out,
+                                    long long rows, int K, int group_shift) {
+  const long long words = rows * (K / 8);
+  const int gpr = K >> group_shift;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < words;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / (K / 8);
+    const int c = (int)(i - r * (K / 8));
+    const uint32_t wd = __ldg(reinterpret_cast<const uint32_t*>(wp) + i);
+    const long long gi = r * gpr + ((c * 8) >> group_shift);
+    const float sc = __half2float(__ldg(scales + gi));
+    const float zp = 128.f + (float)__ldg(zeros + gi);
+    *reinterpret_cast<uint4*>(out + i * 8) =
+        make_uint4(int4_pair_to_bf16x2<0>(wd, sc, zp), int4_pair_to_bf16x2<1>(wd, sc, zp),
+                   int4_pair_to_bf16x2<2>(wd, sc, zp), int4_pair_to_bf16x2<3>(wd, sc, zp));
+  }
+}
+}  // namespace w4
+}  // namespace b200
+
+// int4 (AWQ / GPTQ style): Wp [N, K / 2] packed nibbles (low nibble = even k), scales fp16 [N, K / group], zero
+// points uint8 [N, K / group]; value = (nibble - zero) * scale.  group a power of two >= 32 that divides K.
+extern "C" int b200_gemm_w4a16_int4(const void* X, const void* Wp, const void* scales, const void* zeros, void* Y,
+                                    const void* bias, int T, int N, int K, int ldx, int ldy, int group, int* status,
+                                    int num_sms, cudaStream_t stream) {
+  return w4::run(X, Wp, scales, nullptr, Y, bias, nullptr, 0, 0, T, N, K, ldx, ldy, 2, T, status, num_sms, stream,
+                 zeros, group);
+}
+
+extern "C" int b200_dequant_int4(const void* wp, const void* scales, const void* zeros, void* out, long long rows,
+                                 int K, int group, cudaStream_t stream) {
+  if (rows <= 0 || K <= 0) return 0;
+  int shift = 0;
+  while ((1 << shift) < group) ++shift;
+  if (K % 8 || group < 8 || (1 << shift) != group || K % group) {
+    b200_set_last_error("dequant_int4: K % 8 == 0 and a power-of-two group size >= 8 that divides K", __FILE__,
+                        __LINE__);
+    return -3;
+  }
+  long long blocks = (rows * (K / 8) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  w4::dequant_int4_kernel<<<(int)blocks, 256, 0, stream>>>((const uint8_t*)wp, (const __half*)scales,
+                                                           (const uint8_t*)zeros, (__nv_bfloat16*)out, rows, K, shift);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
 
 // out [rows, K] bf16 = dequant(wp [rows, K / 2], scales); K % 8 == 0 (mxfp4: K % 32, nvfp4: K % 16).
 extern "C" int b200_dequant_w4(const void* wp, const void* scales, const float* global_scale, void* out,

@@ -352,6 +352,22 @@ def bench_w4a16(T, N, K, iters=20) -> list:
                      "tflops": round(flops / ms / 1e9, 1), "gbs": round(byts / ms / 1e6, 1),
                      "roofline_ms": round(t_roof, 4), "frac_of_roofline": round(t_roof / ms, 3), "peaks": tag,
                      "rel_err": err, "status": cuda.check_status()})
+    # AWQ / GPTQ style int4 (fp16 group scales and zero points, group 128) on the same kernel
+    from ..quantization.int4 import dequantize_int4_group, quantize_int4_group
+    from . import cuda_fp4
+    wp, sc, zp = quantize_int4_group(w, 128)
+    wp, sh, zp = wp.contiguous(), sc.half().contiguous(), zp.contiguous()
+    ms = time_fn(lambda: cuda_fp4.w4a16_int4_gemm(x, wp, sh, zp, 128), iters)
+    err = None
+    if T * N <= (1 << 24):
+        want = x.float() @ dequantize_int4_group(wp, sc, zp, 128).bfloat16().float().t()
+        err = float((cuda_fp4.w4a16_int4_gemm(x, wp, sh, zp, 128).float() - want).abs().max() / want.abs().max())
+    byts = float(N * K // 2 + 3 * sh.numel() + 2 * T * K + 2 * T * N)
+    t_roof = max(flops / (pk["bf16_tflops"] * 1e12), byts / (pk["hbm_gbs"] * 1e9)) * 1e3
+    rows.append({"op": "w4a16-gemm", "fmt": "int4 g128", "T": T, "N": N, "K": K, "ms": round(ms, 4),
+                 "tflops": round(flops / ms / 1e9, 1), "gbs": round(byts / ms / 1e6, 1),
+                 "roofline_ms": round(t_roof, 4), "frac_of_roofline": round(t_roof / ms, 3), "peaks": tag,
+                 "rel_err": err, "status": cuda.check_status()})
     wb = w.bfloat16()
     y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
     ms = time_fn(lambda: cuda.gemm(x, wb, out=y), iters)

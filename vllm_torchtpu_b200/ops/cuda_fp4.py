@@ -1,5 +1,5 @@
 """Bindings of the W4A16 tcgen05 GEMM (``csrc/gemm_w4a16_tcgen05.cu``): packed e2m1 weights with mxfp4 or
-nvfp4 group scales, bf16 activations.  The weight stays 4-bit in HBM; tiles are expanded in shared memory."""
+nvfp4 group scales, or unsigned 4-bit integers with group scales and zero points (AWQ / GPTQ), bf16 activations.  The weight stays 4-bit in HBM; tiles are expanded in shared memory."""
 from __future__ import annotations
 
 from ctypes import c_int
@@ -47,6 +47,48 @@ def w4a16_gemm(x, w_packed, scales, fmt: str, global_scale=None, bias=None):
         _c._p(x2), _c._p(w_packed), _c._p(scales), _c._p(global_scale), _c._p(y), _c._p(bias), c_int(T), c_int(N),
         c_int(K), c_int(x2.stride(0)), c_int(N), c_int(FMT[fmt]), _c._p(ws.status), c_int(_c._sms), _c._stream()),
         "gemm_w4a16")
+    count_launch()
+    return y.reshape(*lead, N)
+
+
+def dequant_int4(w_packed, scales, zeros, group: int):
+    """Packed unsigned nibbles [rows, K / 2], fp16 scales and uint8 zero points [rows, K / group] -> bf16 [rows, K]."""
+    from ctypes import c_longlong
+    K = w_packed.shape[-1] * 2
+    rows = w_packed.numel() // w_packed.shape[-1]
+    out = torch.empty(w_packed.shape[:-1] + (K,), dtype=torch.bfloat16, device=w_packed.device)
+    _c._check(_c.lib().b200_dequant_int4(_c._p(w_packed), _c._p(scales), _c._p(zeros), _c._p(out), c_longlong(rows),
+                                         c_int(K), c_int(group), _c._stream()), "dequant_int4")
+    count_launch()
+    return out
+
+
+def int4_kernel_ok(K: int, group: int) -> bool:
+    return K % 64 == 0 and group >= 32 and group & (group - 1) == 0 and K % group == 0
+
+
+def w4a16_int4_gemm(x, w_packed, scales, zeros, group: int, bias=None):
+    """AWQ / GPTQ style weights on the W4A16 kernel: x bf16 [..., K]; w_packed uint8 [N, K / 2] (low nibble = even
+    k), scales fp16 [N, K / group], zeros uint8 [N, K / group]; value = (nibble - zero) * scale -> bf16 [..., N]."""
+    _c._require_bf16(x, bias)
+    if scales.dtype != torch.float16 or zeros.dtype != torch.uint8:
+        raise TypeError("int4 weights take fp16 scales and uint8 zero points")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    T, K = x2.shape
+    N = w_packed.shape[0]
+    if T >= DEQUANT_FROM_TOKENS or not int4_kernel_ok(K, group):
+        return _c.gemm(x2, dequant_int4(w_packed, scales, zeros, group), bias).reshape(*lead, N)
+    y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return y.reshape(*lead, N)
+    ws = _c.Workspace.get(x.device)
+    _c._check(_c.lib().b200_gemm_w4a16_int4(
+        _c._p(x2), _c._p(w_packed), _c._p(scales), _c._p(zeros), _c._p(y), _c._p(bias), c_int(T), c_int(N), c_int(K),
+        c_int(x2.stride(0)), c_int(N), c_int(group), _c._p(ws.status), c_int(_c._sms), _c._stream()),
+        "gemm_w4a16_int4")
     count_launch()
     return y.reshape(*lead, N)
 
