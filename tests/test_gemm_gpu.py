@@ -34,6 +34,16 @@ def test_gemm(T, N, K):
     _run(T, N, K)
 
 
+@pytest.mark.parametrize("T,N,K,bias", [(64, 28672, 4096, False), (64, 6144, 4096, True), (64, 4096, 4096, False),
+                                        (32, 2304, 1024, True), (128, 9600, 2048, False), (300, 4000, 1024, True),
+                                        (512, 4096, 4096, False), (17, 19000, 512, False)])
+def test_gemm_tile_counts_that_do_not_fill_the_sms(T, N, K, bias):
+    """Tile counts that leave SMs idle under whole-tile scheduling (224, 48, 32 ... tiles on 148 SMs), run twice
+    (split-K counters and cluster launches are re-armed by the kernel)."""
+    _run(T, N, K, bias=bias)
+    _run(T, N, K, bias=bias)
+
+
 def test_gemm_bias():
     _run(64, 512, 1024, bias=True)
     _run(500, 512, 1024, bias=True)

@@ -14,7 +14,8 @@ def cu():
 
 
 @pytest.mark.parametrize("T,I,K", [(16, 256, 512), (64, 1536, 2048), (200, 768, 1024), (1000, 512, 512),
-                                   (64, 1792, 4096), (64, 7168, 4096), (33, 3584, 4096), (5, 640, 4096)])
+                                   (64, 1792, 4096), (64, 7168, 4096), (33, 3584, 4096), (5, 640, 4096),
+                                   (64, 14336, 4096), (48, 11008, 2048), (128, 12000, 1024)])
 def test_gemm_swiglu(T, I, K):
     g = torch.Generator(device=DEV).manual_seed(T)
     x = torch.randn(T, K, device=DEV, generator=g).bfloat16()
