@@ -272,3 +272,19 @@ def test_mtp_module_takes_the_layer_class_of_its_target(preset):
     d = spec.engine.spec
     assert type(d.layer) is type(spec.engine.runner.model.layers[-1]) and hasattr(d.layer.mlp, "experts")
     assert d.kv_cache.shape == spec.engine.runner.kv_caches[-1].shape and d.stats["proposed"] > 0
+
+
+@pytest.mark.parametrize("preset", ["tiny-gdn", "tiny-kda"])
+def test_mtp_on_linear_attention_hybrids(preset):
+    """The MTP module of a hybrid is a full-attention layer; its drafts are verified in k + 1 rows and the
+    recurrent layers' state is rolled back for the rejected ones."""
+    prompts = [np.random.RandomState(4).randint(0, 1024, size=n).tolist() for n in (9, 30)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    plain = LLM(preset, device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    want = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    spec = LLM(preset, device="cpu", max_num_seqs=4, block_size=16, init_dist=False,
+               speculative_config={"method": "mtp", "num_speculative_tokens": 2})
+    assert [o.outputs[0].token_ids for o in spec.generate(prompts, sp)] == want
+    d = spec.engine.spec
+    assert hasattr(d.layer.self_attn, "qkv") and d.kv_cache.dim() == 5
+    assert spec.engine.runner.stats.get("state_rollbacks", 0) > 0 and d.stats["proposed"] > 0

@@ -70,8 +70,13 @@ class DraftLayerProposer:
         if kind == "mtp" and m.quantization:
             from ..quantization import QuantConfig
             quant = QuantConfig(m.quantization, m.weight_block_size, ignored_layers=("lm_head", "embed", "gate."))
-        self.layer_idx = L
-        self.layer = model.layer_cls(L, m, self.device, quant)
+        self.layer_idx = L                  # checkpoint index of the module (model.layers.<L>.*)
+        # on a linear-attention hybrid the module is a full-attention layer: build it at the index of the
+        # target's last full-attention layer and give it a cache of that layer's shape
+        self.build_idx = L
+        if m.is_hybrid_gdn:
+            self.build_idx = max(i for i in range(L) if m.layer_is_full_attention(i))
+        self.layer = model.layer_cls(self.build_idx, m, self.device, quant)
         H = m.hidden_size
         one = lambda: torch.ones(H, dtype=self.dtype, device=self.device)      # noqa: E731
         self.eps = m.rms_norm_eps
@@ -99,7 +104,9 @@ class DraftLayerProposer:
         # one more KV tensor, addressed by the target's block tables
         def blank(c):
             return torch.zeros_like(c) if torch.is_tensor(c) else type(c)(blank(x) for x in c)
-        self.kv_cache = blank(runner.kv_caches[-1])     # the draft layer has the shape of the last target layer
+        # the draft layer has the shape of the target layer it was modelled on
+        self.kv_cache = blank(runner.kv_caches[self.build_idx - model.layer_range[0]] if m.is_hybrid_gdn
+                              else runner.kv_caches[-1])
         self._res = None
         self.last_confidences: dict = {}
         self.stats = {"proposed": 0, "requests": 0, "catch_up_rows": 0, "passes": 0}
