@@ -217,3 +217,33 @@ def test_encoder_attention_bidirectional(Hq, Hkv, D):
     got = cu().encoder_attention(q, k, v, offs)
     want = ref.encoder_attention(q, k, v, offs)
     _close(got, want, 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("spec", ["silu", "gelu", "gelu_tanh", "swigluoai", "swigluoai:1.5:2", "silu_clamp:3",
+                                  "situ:3:none", "situ:3:2"])
+def test_gated_activation_kernels(spec):
+    from vllm_torchtpu_b200.ops import cuda
+    from vllm_torchtpu_b200.ops import reference as ref
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = (torch.randn(37, 2 * 1032, device=DEV, generator=g) * 4).bfloat16()
+    got = cuda.gated_act_and_mul(x, spec)
+    want = ref.gated_act_and_mul(x.float(), spec)
+    torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2)
+
+
+def test_moe_experts_with_oai_swiglu_on_the_device():
+    from vllm_torchtpu_b200.ops import cuda
+    from vllm_torchtpu_b200.ops import reference as ref
+    g = torch.Generator(device=DEV).manual_seed(1)
+    T, H, I, E, k = 50, 256, 128, 8, 2
+    x = torch.randn(T, H, device=DEV, generator=g).bfloat16()
+    w13 = (torch.randn(E, 2 * I, H, device=DEV, generator=g) * 0.08).bfloat16()
+    w2 = (torch.randn(E, H, I, device=DEV, generator=g) * 0.08).bfloat16()
+    logits = torch.randn(T, E, device=DEV, generator=g)
+    wt, ids = torch.topk(torch.softmax(logits, -1), k, -1)
+    ids, wt = ids.int().contiguous(), wt.float().contiguous()
+    got = cuda.moe_experts(x, w13, w2, ids, wt, 0, act="swigluoai")
+    want = ref.moe_experts(x, w13, w2, ids, wt, 0, act="swigluoai")
+    err = (got.float() - want.float()).abs().max().item()
+    assert err <= 3e-2 * want.float().abs().max().item() + 2e-2, err
+    assert cuda.check_status() == 0

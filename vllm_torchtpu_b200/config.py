@@ -56,6 +56,7 @@ class ModelConfig:
     num_experts: int = 0
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
+    hidden_act: str = "silu"                   # gated activation of the MLP / experts (ops.reference.parse_gated_act)
     num_shared_experts: int = 0
     shared_expert_intermediate_size: int = 0   # 0: moe_intermediate_size x num_shared_experts
     shared_expert_gate: bool = False           # shared expert output scaled by sigmoid(x . w) (Qwen2-MoE, Qwen3-Next)
@@ -160,6 +161,11 @@ class ModelConfig:
         mc.tie_word_embeddings = cfg.get("tie_word_embeddings", False)
         mc.dtype = parse_dtype(cfg.get("torch_dtype", "bfloat16"))
         mc.sliding_window = cfg.get("sliding_window") if cfg.get("use_sliding_window", True) else None
+        act = cfg.get("hidden_act") or cfg.get("hidden_activation") or "silu"
+        mc.hidden_act = {"silu": "silu", "swish": "silu", "gelu": "gelu", "gelu_new": "gelu_tanh",
+                         "gelu_pytorch_tanh": "gelu_tanh", "gelu_tanh": "gelu_tanh"}.get(act, act)
+        if cfg.get("swiglu_limit") and mc.hidden_act == "silu" and cfg.get("swiglu_oai", False):
+            mc.hidden_act = f"swigluoai:1.702:{float(cfg['swiglu_limit'])}"
         if arch.startswith(("Llama", "Mistral", "Phi3")):
             mc.architecture = "llama"                   # Phi-3: fused qkv_proj / gate_up_proj in the checkpoint
         elif arch.startswith("Mixtral"):

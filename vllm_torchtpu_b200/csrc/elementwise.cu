@@ -80,6 +80,51 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat
   }
 }
 
+// Gated activations of MoE / MLP blocks, y[t, i] = act(gate, up) with gate = x[t, i], up = x[t, I + i]:
+//   0 silu(g) * u            1 gelu(g) * u (erf)          2 gelu_tanh(g) * u
+//   3 swigluoai: g' = min(g, limit), u' = clamp(u, +-limit), (u' + 1) * g' * sigmoid(alpha * g')   (a = alpha, b = limit)
+//   4 silu with clamp: silu(min(g, limit)) * clamp(u, +-limit)                                         (b = limit)
+//   5 situ: beta * tanh(g / beta) * sigmoid(g) * (linear_beta > 0 ? linear_beta * tanh(u / linear_beta) : u)
+//      (a = beta, b = linear_beta or 0)
+// (reference: src/vllm_torchtpu/kernels/megablox/gmm_v2.py:30-58, 100-121)
+template <int ACT>
+__device__ __forceinline__ float gated_act(float g, float u, float a, float b) {
+  if (ACT == 0) return g / (1.f + __expf(-g)) * u;
+  if (ACT == 1) return 0.5f * g * (1.f + erff(g * 0.70710678118654752f)) * u;
+  if (ACT == 2) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  if (ACT == 3) {
+    const float gc = fminf(g, b), uc = fminf(fmaxf(u, -b), b);
+    return (uc + 1.f) * gc / (1.f + __expf(-a * gc));
+  }
+  if (ACT == 4) {
+    const float gc = fminf(g, b), uc = fminf(fmaxf(u, -b), b);
+    return gc / (1.f + __expf(-gc)) * uc;
+  }
+  const float gg = a * tanhf(g / a) / (1.f + __expf(-g));
+  return gg * (b > 0.f ? b * tanhf(u / b) : u);
+}
+
+template <int ACT>
+__global__ void gated_act_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int T, int I,
+                                 float a, float b) {
+  const int nvec = I >> 3;
+  const size_t total = (size_t)T * nvec;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / nvec;
+    const int i = (int)(idx - t * nvec);
+    const bf16x8 g = *reinterpret_cast<const bf16x8*>(x + t * 2 * I + i * 8);
+    const bf16x8 u = *reinterpret_cast<const bf16x8*>(x + t * 2 * I + I + i * 8);
+    bf16x8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 fg = __bfloat1622float2(g.v[j]), fu = __bfloat1622float2(u.v[j]);
+      o.v[j] = __floats2bfloat162_rn(gated_act<ACT>(fg.x, fu.x, a, b), gated_act<ACT>(fg.y, fu.y, a, b));
+    }
+    *reinterpret_cast<bf16x8*>(y + t * I + i * 8) = o;
+  }
+}
+
 // out[t] = table[ token_src[t] >= 0 ? last_tokens[token_src[t]] : ids[t] ]
 __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ token_src,
                                  const int* __restrict__ last_tokens, const __nv_bfloat16* __restrict__ table,
@@ -250,6 +295,31 @@ extern "C" int b200_silu_and_mul(const void* x, void* y, int T, int I, cudaStrea
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   silu_mul_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, T, I);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// x [T, 2I] (gate columns first) -> y [T, I]; act and its parameters a, b as listed at gated_act.
+extern "C" int b200_gated_act(const void* x, void* y, int T, int I, int act, float a, float b,
+                              cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (I % 8 || act < 0 || act > 5) {
+    b200_set_last_error("gated_act: width must be a multiple of 8, activation 0..5", __FILE__, __LINE__);
+    return -1;
+  }
+  size_t total = (size_t)T * (I / 8);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+  __nv_bfloat16* yp = (__nv_bfloat16*)y;
+  switch (act) {
+    case 0: gated_act_kernel<0><<<blocks, 256, 0, stream>>>(xp, yp, T, I, a, b); break;
+    case 1: gated_act_kernel<1><<<blocks, 256, 0, stream>>>(xp, yp, T, I, a, b); break;
+    case 2: gated_act_kernel<2><<<blocks, 256, 0, stream>>>(xp, yp, T, I, a, b); break;
+    case 3: gated_act_kernel<3><<<blocks, 256, 0, stream>>>(xp, yp, T, I, a, b); break;
+    case 4: gated_act_kernel<4><<<blocks, 256, 0, stream>>>(xp, yp, T, I, a, b); break;
+    default: gated_act_kernel<5><<<blocks, 256, 0, stream>>>(xp, yp, T, I, a, b); break;
+  }
   B200_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

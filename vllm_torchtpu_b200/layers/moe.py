@@ -50,6 +50,7 @@ class FusedMoE:
         self.dtype = cfg.dtype
         self.hidden_size = cfg.hidden_size
         self.num_experts = cfg.num_experts
+        self.activation = getattr(cfg, "hidden_act", "silu")
         self.top_k = cfg.num_experts_per_tok
         self.use_ep = st.expert_parallel and st.ep.size > 1
         self.ep_size = st.ep.size if self.use_ep else 1
@@ -95,7 +96,7 @@ class FusedMoE:
                 y = get_tp_comm().all_reduce(y)
             return y
         comm = get_ep_comm()
-        if (x.is_cuda and envs.B200_MOE_FUSED_EP and comm.heap is not None
+        if (x.is_cuda and envs.B200_MOE_FUSED_EP and comm.heap is not None and self.activation == "silu"
                 and getattr(comm.heap, "ep_state", None) is not None
                 and x.shape[0] >= envs.B200_MOE_FUSED_EP_MIN_TOKENS and hasattr(self.method, "apply_fused_ep")):
             return self._forward_fused_ep(x, topk_ids, topk_w, comm)

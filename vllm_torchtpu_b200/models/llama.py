@@ -95,6 +95,7 @@ class LlamaMLP:
                                             [intermediate_size, intermediate_size], **kw)
         self.down = RowParallelLinear(f"{name}.down_proj", intermediate_size, cfg.hidden_size,
                                       reduce_results=reduce_results, **kw)
+        self.act = getattr(cfg, "hidden_act", "silu")
 
     def linears(self):
         return [self.gate_up, self.down]
@@ -108,6 +109,11 @@ class LlamaMLP:
 
     def forward(self, x):
         gu = self.gate_up
+        if self.act != "silu":
+            # other gated activations (GELU-tanh, clamped and OAI-style SwiGLU, SiTU): GEMM, activation kernel, GEMM
+            h = self.gate_up(x)
+            return self.down(ops.gated_act_and_mul(h.reshape(-1, h.shape[-1]), self.act).reshape(
+                *x.shape[:-1], h.shape[-1] // 2))
         if (x.is_cuda and gu.bias is None and getattr(gu.method, "supports_fused_reduce", False)
                 and not gu.lora_targets):
             # gate and up tiles share the activation tile; SiLU*mul happens in the GEMM epilogue

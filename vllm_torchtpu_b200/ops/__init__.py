@@ -43,6 +43,12 @@ def fused_add_rms_norm(x, residual, weight, eps):
     return ref.fused_add_rms_norm(x, residual, weight, eps)
 
 
+def gated_act_and_mul(x, spec: str = "silu"):
+    if spec == "silu":
+        return silu_and_mul(x)
+    return cuda_ops().gated_act_and_mul(x, spec) if _on_gpu(x) else ref.gated_act_and_mul(x, spec)
+
+
 def silu_and_mul(x):
     return cuda_ops().silu_and_mul(x) if _on_gpu(x) else ref.silu_and_mul(x)
 

@@ -186,6 +186,21 @@ def fused_add_rms_norm(x, residual, weight, eps):
     return y, residual
 
 
+def gated_act_and_mul(x, spec: str = "silu"):
+    """x [T, 2I] bf16 (gate columns first) -> act(gate, up) [T, I]; ``spec`` as in
+    ``ops.reference.parse_gated_act`` (silu, gelu, gelu_tanh, swigluoai, silu_clamp, situ)."""
+    from .reference import parse_gated_act
+    _require_bf16(x)
+    act, a, b = parse_gated_act(spec)
+    x = x.contiguous()
+    T, I2 = x.shape
+    y = torch.empty((T, I2 // 2), dtype=x.dtype, device=x.device)
+    _check(lib().b200_gated_act(_p(x), _p(y), c_int(T), c_int(I2 // 2), c_int(act), ctypes.c_float(a),
+                                ctypes.c_float(b), _stream()), "gated_act")
+    count_launch()
+    return y
+
+
 def silu_and_mul(x):
     _require_bf16(x)
     x = x.contiguous()

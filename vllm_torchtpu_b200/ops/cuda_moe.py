@@ -93,7 +93,7 @@ def moe_unpermute(y, inv_pos, topk_w, T: int):
     return out
 
 
-def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0):
+def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0, act: str = "silu"):
     """Σ_k w_k · FFN_e(x) over the local experts: permute → grouped SwiGLU GEMM → grouped GEMM →
     weighted un-permute.  w13: [E_local, 2I, H] (gate rows first), w2: [E_local, H, I]."""
     T, H = x.shape
@@ -101,8 +101,12 @@ def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0):
     k = topk_ids.shape[1]
     x_perm, group_off, _, inv_pos = moe_permute(x.contiguous(), topk_ids.contiguous(), expert_offset, E_local)
     avg = (T * k + E_local - 1) // E_local
-    act = grouped_gemm(x_perm, w13, group_off, True, avg)
-    y = grouped_gemm(act, w2, group_off, False, avg)
+    if act == "silu":
+        h = grouped_gemm(x_perm, w13, group_off, True, avg)          # SiLU * mul in the GEMM epilogue
+    else:
+        # other gated activations: one grouped GEMM over the stacked [gate; up] rows, then the activation kernel
+        h = _c.gated_act_and_mul(grouped_gemm(x_perm, w13, group_off, False, avg), act)
+    y = grouped_gemm(h, w2, group_off, False, avg)
     return moe_unpermute(y, inv_pos, topk_w.contiguous(), T)
 
 

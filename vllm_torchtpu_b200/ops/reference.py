@@ -39,6 +39,52 @@ def fused_add_rms_norm(x, residual, weight, eps):
     return rms_norm(r, weight, eps), r
 
 
+GATED_ACTS = ("silu", "gelu", "gelu_tanh", "swigluoai", "silu_clamp", "situ")
+
+
+def parse_gated_act(spec: str) -> tuple:
+    """"silu" | "gelu" | "gelu_tanh" | "swigluoai[:alpha:limit]" | "silu_clamp[:limit]" | "situ:beta[:linear_beta]"
+    -> (index into GATED_ACTS, a, b)."""
+    parts = str(spec).split(":")
+    name = {"silu_and_mul_with_clamp": "silu_clamp"}.get(parts[0], parts[0])
+    if name not in GATED_ACTS:
+        raise ValueError(f"unknown gated activation {spec!r}; known: {GATED_ACTS}")
+    nums = [float(p) if p not in ("", "none") else 0.0 for p in parts[1:]]
+    if name == "swigluoai":
+        a, b = (nums + [1.702, 7.0][len(nums):])[:2]
+    elif name == "silu_clamp":
+        a, b = 0.0, (nums + [10.0])[0]
+    elif name == "situ":
+        if not nums:
+            raise ValueError("situ needs its beta: 'situ:<beta>[:<linear_beta>]'")
+        a, b = nums[0], (nums[1] if len(nums) > 1 else 0.0)
+    else:
+        a, b = 0.0, 0.0
+    return GATED_ACTS.index(name), a, b
+
+
+def gated_act_and_mul(x: torch.Tensor, spec: str = "silu") -> torch.Tensor:
+    """x [..., 2I] (gate columns first) -> act(gate, up) [..., I] in fp32 then the input dtype
+    (reference: src/vllm_torchtpu/kernels/megablox/gmm_v2.py:30-58)."""
+    act, a, b = parse_gated_act(spec)
+    I = x.shape[-1] // 2
+    g, u = x[..., :I].float(), x[..., I:].float()
+    if act == 0:
+        y = F.silu(g) * u
+    elif act == 1:
+        y = F.gelu(g) * u
+    elif act == 2:
+        y = F.gelu(g, approximate="tanh") * u
+    elif act == 3:
+        gc, uc = g.clamp(max=b), u.clamp(-b, b)
+        y = (uc + 1.0) * gc * torch.sigmoid(a * gc)
+    elif act == 4:
+        y = F.silu(g.clamp(max=b)) * u.clamp(-b, b)
+    else:
+        y = a * torch.tanh(g / a) * torch.sigmoid(g) * (b * torch.tanh(u / b) if b > 0 else u)
+    return y.to(x.dtype)
+
+
 def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
     d = x.shape[-1] // 2
     g, u = x[..., :d].float(), x[..., d:].float()
@@ -289,9 +335,9 @@ def moe_route(router_logits, top_k: int, scoring: str = "softmax", renormalize: 
     return ids.to(torch.int32), (w * routed_scaling).float()
 
 
-def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0):
+def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0, act: str = "silu"):
     """Σ_k w_k · FFN_e(x) over the experts this rank owns.  w13: [E_local, 2I, H] (gate rows first),
-    w2: [E_local, H, I]."""
+    w2: [E_local, H, I]; ``act``: gated activation (``parse_gated_act``)."""
     T, H = x.shape
     E_local = w13.shape[0]
     out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
@@ -303,8 +349,7 @@ def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0):
             continue
         wt = (topk_w * sel).sum(-1)[rows]
         h = xf[rows] @ w13[e].float().t()
-        I = h.shape[-1] // 2
-        a = (F.silu(h[:, :I]) * h[:, I:]).to(x.dtype).float()
+        a = gated_act_and_mul(h, act).to(x.dtype).float()
         y = (a @ w2[e].float().t()).to(x.dtype).float()
         out[rows] += y * wt[:, None]
     return out.to(x.dtype)

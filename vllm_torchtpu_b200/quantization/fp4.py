@@ -165,12 +165,12 @@ class Mxfp4MoEMethod:
         I, H = moe.intermediate_size, moe.hidden_size
         if x.is_cuda and x.dtype == torch.bfloat16 and H % 128 == 0 and I % 128 == 0:
             return ops.cuda_ops().moe_experts_w4a16(x, moe.w13, moe.w13_scale, moe.w2, moe.w2_scale, topk_ids, topk_w,
-                                                    moe.expert_range[0], "mxfp4")
+                                                    moe.expert_range[0], "mxfp4", act=moe.activation)
         w13 = dequantize_mxfp4(moe.w13, moe.w13_scale).to(x.dtype)
         w2 = dequantize_mxfp4(moe.w2, moe.w2_scale).to(x.dtype)
         if x.is_cuda:
-            return ops.cuda_ops().moe_experts(x, w13, w2, topk_ids, topk_w, moe.expert_range[0])
-        return ops.ref.moe_experts(x, w13, w2, topk_ids, topk_w, moe.expert_range[0])
+            return ops.cuda_ops().moe_experts(x, w13, w2, topk_ids, topk_w, moe.expert_range[0], act=moe.activation)
+        return ops.ref.moe_experts(x, w13, w2, topk_ids, topk_w, moe.expert_range[0], act=moe.activation)
 
     def weight_bytes(self, moe) -> int:
         return sum(t.numel() for t in (moe.w13, moe.w2, moe.w13_scale, moe.w2_scale))

@@ -261,6 +261,8 @@ class Fp8BlockMoEMethod:
         moe.w2[local_e], moe.w2_scale[local_e] = q2, s2
 
     def apply(self, moe, x, topk_ids, topk_w):
+        if getattr(moe, "activation", "silu") != "silu":
+            raise NotImplementedError("block-scaled fp8 experts are built for the SiLU gate only")
         if x.is_cuda:
             return ops.cuda_ops().moe_experts_fp8(x, moe.w13, moe.w13_scale, moe.w2, moe.w2_scale, topk_ids,
                                                   topk_w, moe.expert_range[0], self.block)

@@ -110,8 +110,9 @@ class UnquantizedMoEMethod:
 
     def apply(self, moe, x, topk_ids, topk_w):
         if x.is_cuda:
-            return ops.cuda_ops().moe_experts(x, moe.w13, moe.w2, topk_ids, topk_w, moe.expert_range[0])
-        return ops.ref.moe_experts(x, moe.w13, moe.w2, topk_ids, topk_w, moe.expert_range[0])
+            return ops.cuda_ops().moe_experts(x, moe.w13, moe.w2, topk_ids, topk_w, moe.expert_range[0],
+                                              act=moe.activation)
+        return ops.ref.moe_experts(x, moe.w13, moe.w2, topk_ids, topk_w, moe.expert_range[0], act=moe.activation)
 
     def apply_fused_ep(self, moe, x, topk_ids, topk_w, comm):
         return ops.cuda_ops().moe_experts_ep(x, moe.w13, moe.w2, topk_ids, topk_w, comm.heap, moe.num_experts)
