@@ -37,3 +37,31 @@ def test_gated_activation_family_and_moe_option():
             e = int(ids[t, j])
             want[t] += wt[t, j] * (ref.gated_act_and_mul((xx[t] @ w13[e].t())[None], "swigluoai")[0] @ w2[e].t())
     torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
+
+
+def test_yarn_rope_frequencies_and_attention_factor():
+    """YaRN against the published recipe: fast dimensions keep their frequency, slow ones are divided by the
+    factor, a linear ramp in between; cos / sin multiplier 0.1 ln(factor) + 1 unless the config overrides it."""
+    import math
+    from vllm_torchtpu_b200.ops import reference as ref
+    D, theta, factor, old = 64, 150000.0, 32.0, 4096
+    sc = {"rope_type": "yarn", "factor": factor, "original_max_position_embeddings": old, "beta_fast": 32.0,
+          "beta_slow": 1.0, "truncate": False}
+    inv = ref.rope_inv_freq(D, theta, sc).double()
+    base = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
+
+    def corr(rot):
+        return D * math.log(old / (rot * 2 * math.pi)) / (2 * math.log(theta))
+    lo, hi = corr(32.0), corr(1.0)
+    ramp = ((torch.arange(D // 2, dtype=torch.float64) - lo) / (hi - lo)).clamp(0, 1)
+    want = base / factor * ramp + base * (1 - ramp)
+    torch.testing.assert_close(inv, want, rtol=1e-6, atol=0)
+    assert torch.allclose(inv[:3], base[:3], rtol=1e-6) and torch.allclose(inv[-3:], base[-3:] / factor, rtol=1e-6)
+    assert abs(ref.rope_attention_factor(sc) - (0.1 * math.log(32.0) + 1)) < 1e-9
+    assert ref.rope_attention_factor({**sc, "attention_factor": 1.25}) == 1.25
+    assert ref.rope_attention_factor({**sc, "mscale": 1.0, "mscale_all_dim": 1.0}) == 1.0     # DeepSeek-V3
+    assert ref.rope_attention_factor({"rope_type": "llama3", "factor": 8.0}) == 1.0
+    trunc = ref.rope_inv_freq(D, theta, {**sc, "truncate": True}).double()
+    lo_t, hi_t = math.floor(lo), math.ceil(hi)
+    ramp_t = ((torch.arange(D // 2, dtype=torch.float64) - lo_t) / (hi_t - lo_t)).clamp(0, 1)
+    torch.testing.assert_close(trunc, base / factor * ramp_t + base * (1 - ramp_t), rtol=1e-6, atol=0)

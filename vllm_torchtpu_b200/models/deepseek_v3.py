@@ -55,8 +55,9 @@ class MLAAttention:
         self.w_uk = None            # [H, nope, kv_lora]
         self.w_uv = None            # [H, kv_lora, vdim]
         self.o = RowParallelLinear(f"{name}.o_proj", cfg.num_q_heads * self.vdim, cfg.hidden_size, **kw)
-        self.inv_freq = ops.ref.rope_inv_freq(self.rope, cfg.rope_theta, None).to(device)
-        self.scale = qk ** -0.5
+        self.inv_freq = ops.ref.rope_inv_freq(self.rope, cfg.rope_theta, cfg.rope_scaling).to(device)
+        af = ops.ref.rope_attention_factor(cfg.rope_scaling)
+        self.scale = qk ** -0.5 * af * af
         if cfg.rope_scaling and "factor" in cfg.rope_scaling:
             m = yarn_mscale(cfg.rope_scaling["factor"], cfg.rope_scaling.get("mscale_all_dim", 0.0))
             self.scale *= m * m

@@ -142,8 +142,9 @@ class LlamaAttention:
             self.q_norm_w = torch.ones(cfg.head_dim, dtype=cfg.dtype, device=device)
             self.k_norm_w = torch.ones(cfg.head_dim, dtype=cfg.dtype, device=device)
         inv_freq = ops.ref.rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling).to(device)
+        af = ops.ref.rope_attention_factor(cfg.rope_scaling)      # YaRN: cos / sin carry it on q and k
         self.attn = PagedAttention(self.qkv.q_per_rank, self.qkv.kv_per_rank, cfg.head_dim, inv_freq,
-                                   rope_interleaved=cfg.rope_interleaved, q_norm_w=self.q_norm_w,
+                                   scale=cfg.head_dim ** -0.5 * af * af, rope_interleaved=cfg.rope_interleaved, q_norm_w=self.q_norm_w,
                                    k_norm_w=self.k_norm_w, eps=cfg.rms_norm_eps,
                                    sliding_window=cfg.sliding_window, softcap=cfg.logit_softcap)
 

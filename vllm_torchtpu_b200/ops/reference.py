@@ -115,7 +115,41 @@ def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None,
         inv = scaled
     elif scaling and scaling.get("rope_type", scaling.get("type")) == "linear":
         inv = inv / scaling["factor"]
+    elif scaling and scaling.get("rope_type", scaling.get("type")) == "yarn":
+        # YaRN: dimensions that turn often inside the original context keep their frequency, slow ones are
+        # interpolated by `factor`, with a linear ramp between the two correction dimensions
+        factor = float(scaling["factor"])
+        old = float(scaling.get("original_max_position_embeddings", 4096))
+        fast, slow = float(scaling.get("beta_fast", 32)), float(scaling.get("beta_slow", 1))
+
+        def corr_dim(rot):
+            return rd * math.log(old / (rot * 2 * math.pi)) / (2 * math.log(theta))
+        lo, hi = corr_dim(fast), corr_dim(slow)
+        if scaling.get("truncate", True):
+            lo, hi = math.floor(lo), math.ceil(hi)
+        lo, hi = max(lo, 0), min(hi, rd - 1)
+        if lo == hi:
+            hi += 0.001
+        ramp = ((torch.arange(rd // 2, dtype=torch.float64) - lo) / (hi - lo)).clamp(0, 1)
+        keep = 1.0 - ramp
+        inv = inv / factor * (1.0 - keep) + inv * keep
     return inv.float()
+
+
+def yarn_mscale(factor: float, mscale: float = 1.0) -> float:
+    return 1.0 if factor <= 1 else 0.1 * mscale * math.log(factor) + 1.0
+
+
+def rope_attention_factor(scaling: Optional[dict]) -> float:
+    """Multiplier of cos / sin under YaRN (both q and k carry it, so attention logits scale by its square)."""
+    if not scaling or scaling.get("rope_type", scaling.get("type")) != "yarn":
+        return 1.0
+    if scaling.get("attention_factor") is not None:
+        return float(scaling["attention_factor"])
+    factor = float(scaling["factor"])
+    if scaling.get("mscale") and scaling.get("mscale_all_dim"):
+        return yarn_mscale(factor, scaling["mscale"]) / yarn_mscale(factor, scaling["mscale_all_dim"])
+    return yarn_mscale(factor)
 
 
 def apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
