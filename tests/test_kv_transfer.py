@@ -246,3 +246,111 @@ def test_worker_halves_pull_across_tp_degrees_and_producers_wait_for_all_readers
     assert all(not sh.pending_sends for sh, _ in prods)
     for _, w in prods + cons:
         w.close()
+
+
+# ---- controller -------------------------------------------------------------------------------------------
+def test_controller_registry_heartbeats_picks_and_unreachable_marking():
+    from vllm_torchtpu_b200.kv_transfer.controller import ControllerClient, KVController
+    now = [100.0]
+    ctl = KVController("127.0.0.1", 0, ttl_s=5.0, clock=lambda: now[0])
+    try:
+        cl = ControllerClient(ctl.address())
+        assert cl.pick("prefill") is None
+        assert not cl.register(engine_id="", role="prefill")["ok"]
+        for eid, role, url in (("p0", "prefill", "http://p0"), ("p1", "prefill", "http://p1"),
+                               ("d0", "decode", "http://d0"), ("b0", "both", "http://b0")):
+            assert cl.register(engine_id=eid, role=role, http_url=url, tp=2, model="m")["ok"]
+        cl.heartbeat("p0", {"running": 4, "waiting": 3, "free_blocks": 10})
+        cl.heartbeat("p1", {"running": 1, "waiting": 0, "free_blocks": 900})
+        cl.heartbeat("b0", {"running": 9, "waiting": 9})
+        assert cl.pick("prefill")["engine_id"] == "p1"              # least loaded
+        assert cl.pick("prefill", exclude=["p1"])["engine_id"] == "p0"
+        assert cl.pick("decode")["engine_id"] == "d0"
+        assert cl.pick("decode", model="other") is None
+        # a reported engine is skipped until it answers again
+        cl.report_unreachable("p1", reporter="d0")
+        assert cl.pick("prefill")["engine_id"] == "p0"
+        cl.heartbeat("p1", {"running": 0, "waiting": 0})
+        assert cl.pick("prefill")["engine_id"] == "p1"
+        # no heartbeat within the time-to-live: not alive, not picked
+        now[0] += 6.0
+        cl.heartbeat("p0", {"running": 0, "waiting": 0})
+        assert cl.pick("prefill")["engine_id"] == "p0"
+        alive = {e["engine_id"]: e["alive"] for e in cl.list("prefill")}
+        assert alive == {"p0": True, "p1": False, "b0": False}
+        # a restarted controller forgets the engines; the next heartbeat registers again
+        ctl.engines.clear()
+        cl._engine = {"engine_id": "p0", "role": "prefill", "http_url": "http://p0"}
+        assert cl.heartbeat("p0", {"running": 0})["ok"] and cl.pick("prefill")["engine_id"] == "p0"
+        cl.deregister("p0")
+        assert cl.pick("prefill") is None
+    finally:
+        ctl.close()
+
+
+def test_proxy_picks_from_the_controller_and_reports_dead_instances():
+    """The proxy asks the controller for instances; a prefill instance that cannot be connected to is reported
+    and the retry goes to the other one."""
+    import asyncio
+    from vllm_torchtpu_b200.kv_transfer.controller import ControllerClient, KVController
+    from vllm_torchtpu_b200.kv_transfer.proxy import build_proxy_app
+    ctl = KVController("127.0.0.1", 0, ttl_s=60.0)
+    try:
+        cl = ControllerClient(ctl.address())
+        cl.register(engine_id="dead", role="prefill", http_url="http://dead")
+        cl.register(engine_id="live", role="prefill", http_url="http://live")
+        cl.register(engine_id="dec", role="decode", http_url="http://dec")
+        cl.heartbeat("live", {"running": 5})           # the dead one looks idle, so it is picked first
+        posts = []
+
+        class Resp:
+            def __init__(self, data): self.status, self._d = 200, data
+            async def json(self): return self._d
+            async def text(self): return ""
+            async def __aenter__(self): return self
+            async def __aexit__(self, *a): return False
+
+        class Client:
+            async def __aenter__(self): return self
+            async def __aexit__(self, *a): return False
+
+            def post(self, url, json=None):
+                posts.append(url)
+                if url.startswith("http://dead"):
+                    raise ConnectionError("Cannot connect to host dead")
+                if url.startswith("http://live"):
+                    return Resp({"kv_transfer_params": {"uuid": "u", "remote_block_ids": [1]}})
+                return Resp({"choices": [{"text": "ok"}], "seen": json.get("kv_transfer_params")})
+        app = build_proxy_app([], [], retries=2, client_factory=Client, controller=cl)
+        from starlette.testclient import TestClient
+        r = TestClient(app).post("/v1/completions", json={"prompt": "x", "max_tokens": 4})
+        assert r.status_code == 200 and r.json()["seen"]["uuid"] == "u"
+        assert posts[0].startswith("http://dead") and posts[1].startswith("http://live") and posts[2].startswith("http://dec")
+        assert app.state.counts["reported_unreachable"] == 1
+        assert {e["engine_id"]: e["alive"] for e in cl.list("prefill")}["dead"] is False
+    finally:
+        ctl.close()
+
+
+def test_engines_register_with_the_controller_and_report_load():
+    from vllm_torchtpu_b200.kv_transfer.controller import ControllerClient, KVController
+    ctl = KVController("127.0.0.1", 0, ttl_s=60.0)
+    try:
+        addr = "%s:%d" % ctl.address()
+        extra = {"transport": "local", "channel": "inproc", "controller": addr, "heartbeat_s": 0.05}
+        pre = _llm("kv_producer", "PC", kv_connector_extra_config={**extra, "http_url": "http://pre:8100"})
+        dec = _llm("kv_consumer", "DC", kv_connector_extra_config={**extra, "http_url": "http://dec:8200"})
+        cl = ControllerClient(ctl.address())
+        got = {e["engine_id"]: e for e in cl.list()}
+        assert got["PC"]["role"] == "prefill" and got["DC"]["role"] == "decode"
+        assert got["PC"]["http_url"] == "http://pre:8100" and got["PC"]["geometry"]["num_kv_heads"] > 0
+        assert cl.pick("prefill")["engine_id"] == "PC" and cl.pick("decode")["engine_id"] == "DC"
+        import time
+        deadline = time.time() + 5
+        while time.time() < deadline and "free_blocks" not in {e["engine_id"]: e for e in cl.list()}["PC"]["load"]:
+            time.sleep(0.05)
+        assert {e["engine_id"]: e for e in cl.list()}["PC"]["load"]["free_blocks"] > 0     # the scheduler's counts
+        pre.engine.connector.controller.stop()
+        dec.engine.connector.controller.stop()
+    finally:
+        ctl.close()

@@ -110,6 +110,10 @@ class LLMEngine:
             self.adaptive = AdaptiveVerificationManager(StepCostTable(samples), num_spec)
         self.scheduler = make_scheduler(self.cfg, num_blocks,
                                         self.connector.scheduler if self.connector else None, num_spec)
+        if self.connector is not None and getattr(self.connector, "controller", None) is not None:
+            sch = self.scheduler
+            self.connector.load_fn = lambda: {"running": len(sch.running), "waiting": len(sch.waiting),
+                                              "free_blocks": sch.kv.pool.num_free_blocks}
         self.runner.capture_model()
         # Data-parallel replicas coupled by expert parallelism run their steps in lockstep: the MoE
         # collectives of a step need every rank, with equal padded row counts on the gather plane

@@ -77,6 +77,11 @@ def main(argv=None) -> int:
     p.add_argument("--decoder-ports", nargs="+", type=int, default=[8200])
     p.add_argument("--host", default="0.0.0.0")
     p.add_argument("--port", type=int, default=8000)
+    p.add_argument("--controller", default="", help="host:port of a KV controller: pick instances from its registry")
+    c = sub.add_parser("controller", help="registry of prefill / decode engines (heartbeats, load-aware picks)")
+    c.add_argument("--host", default="0.0.0.0")
+    c.add_argument("--port", type=int, default=7600)
+    c.add_argument("--ttl", type=float, default=10.0, help="seconds without a heartbeat before an engine is skipped")
     e = sub.add_parser("envs", help="list the environment knobs")
     x = sub.add_parser("export", help="write a serving directory (weights, configuration, shape plan, manifest)")
     add_engine_args(x)
@@ -110,7 +115,12 @@ def main(argv=None) -> int:
         return 0
     if a.cmd == "proxy":
         from ..kv_transfer.proxy import run_proxy
-        run_proxy(a.prefiller_hosts, a.prefiller_ports, a.decoder_hosts, a.decoder_ports, a.host, a.port)
+        run_proxy(a.prefiller_hosts, a.prefiller_ports, a.decoder_hosts, a.decoder_ports, a.host, a.port,
+                  controller=a.controller)
+        return
+    if a.cmd == "controller":
+        from ..kv_transfer.controller import run_controller
+        run_controller(a.host, a.port, a.ttl)
         return 0
     llm = make_llm(a)
     rank = int(os.environ.get("RANK", "0"))

@@ -207,6 +207,12 @@ class P2PWorkerHalf(WorkerConnectorBase):
                 self.s.stats.record_load(len(lm.local_block_ids), now() - t0, ok=True)
             except (TransferError, OSError, TimeoutError, ConnectionError, PermissionError) as e:
                 logger.warning("KV load of request %s failed: %r", lm.request_id, e)
+                ctl = getattr(self, "controller", None)
+                if ctl is not None and isinstance(e, (OSError, TimeoutError, ConnectionError)):
+                    try:                               # the source does not answer: keep others away from it
+                        ctl.report_unreachable(lm.remote_engine, reporter=self.s.engine_id)
+                    except (OSError, TimeoutError, ConnectionError):
+                        pass
                 with self.s.lock:
                     self.s.load_failed[lm.request_id] = repr(e)
                     self.s.error_blocks.update(lm.local_block_ids)
@@ -298,4 +304,24 @@ def create_p2p_connector(cfg, runner, *, transport=None, channel_factory=None) -
     sched = P2PSchedulerHalf(shared)
     c = Connector(sched, worker)
     c.shared = shared
+    c.controller = None
+    ctl_addr = extra.get("controller")
+    if ctl_addr and tp.rank_in_group == 0:
+        # rank 0 speaks for the engine: register with the controller and report load with every heartbeat
+        # (the engine replaces `load_fn` with its scheduler's counts)
+        from .controller import ControllerClient
+        h, pt = (ctl_addr.rsplit(":", 1) if isinstance(ctl_addr, str) else ctl_addr)
+        client = ControllerClient((h, int(pt)))
+        role_name = {KVConnectorRole.PRODUCER: "prefill", KVConnectorRole.CONSUMER: "decode"}.get(role, "both")
+        kv_host, kv_port = (shared.address or ("127.0.0.1", 0))[:2]
+        c.load_fn = lambda: {"running": len(shared.loads), "waiting": 0, "pending_sends": len(shared.pending_sends)}
+        try:
+            client.register(engine_id=base_id, role=role_name, http_url=extra.get("http_url", ""),
+                            kv_host=str(kv_host), kv_port=int(kv_port) if isinstance(kv_port, int) else 0,
+                            tp=tp.size, model=cfg.model.name, geometry=geometry.to_dict() if geometry else None)
+            client.start_heartbeats(base_id, lambda: c.load_fn(), float(extra.get("heartbeat_s", 2.0)))
+            c.controller = client
+            worker.controller = client
+        except (OSError, TimeoutError, ConnectionError) as e:
+            logger.warning("KV controller %s not reachable: %r", ctl_addr, e)
     return c
