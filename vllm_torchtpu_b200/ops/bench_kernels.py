@@ -376,7 +376,7 @@ def bench_w4a16(T, N, K, iters=20) -> list:
     return rows
 
 
-def bench_misc(iters=20) -> list:
+def bench_misc(iters=20, only: str = "") -> list:
     """Element-wise, routing, sampling and MLA kernels at serving shapes: device time (graph replay, L2
     flushed), algorithmic bytes over the measured copy bandwidth."""
     from ..runner.attn_metadata import AttentionMetadata
@@ -385,7 +385,10 @@ def bench_misc(iters=20) -> list:
     pk, tag = peaks()
     rows = []
 
-    def row(op, shape, ms, byts, note=None):
+    def row(op, shape, fn, byts, note=None):
+        if only and only not in op:
+            return                                  # --only <substring>: time one kernel family (profiler captures)
+        ms = time_fn(fn, iters)
         r = {"op": op, "shape": shape, "us": round(ms * 1e3, 2), "gbs": round(byts / ms / 1e6, 1),
              "frac_of_hbm": round(byts / ms / 1e6 / pk["hbm_gbs"], 3), "peaks": tag, "status": cuda.check_status()}
         if note:
@@ -397,14 +400,14 @@ def bench_misc(iters=20) -> list:
         x = torch.randn(T, H, device=dev).bfloat16()
         res = torch.randn(T, H, device=dev).bfloat16()
         w = torch.ones(H, device=dev).bfloat16()
-        row("rms_norm", [T, H], time_fn(lambda: cuda.rms_norm(x, w, 1e-5), iters), 2.0 * T * H * 2)
-        row("fused_add_rms_norm", [T, H], time_fn(lambda: cuda.fused_add_rms_norm(x, res, w, 1e-5), iters),
+        row("rms_norm", [T, H], lambda: cuda.rms_norm(x, w, 1e-5), 2.0 * T * H * 2)
+        row("fused_add_rms_norm", [T, H], lambda: cuda.fused_add_rms_norm(x, res, w, 1e-5),
             4.0 * T * H * 2)
         gu = torch.randn(T, 2 * I, device=dev).bfloat16()
-        row("silu_and_mul", [T, 2 * I], time_fn(lambda: cuda.silu_and_mul(gu), iters), 3.0 * T * I * 2)
-        row("quant_act_1x128", [T, I], time_fn(lambda: cuda.quant_act_1x128(gu[:, :I].contiguous()), iters),
+        row("silu_and_mul", [T, 2 * I], lambda: cuda.silu_and_mul(gu), 3.0 * T * I * 2)
+        row("quant_act_1x128", [T, I], lambda: cuda.quant_act_1x128(gu[:, :I].contiguous()),
             T * I * 3.0 + T * I * 2.0, note="includes the contiguous copy of the slice")
-        row("quant_rows_1x128 swiglu", [T, 2 * I], time_fn(lambda: cuda.quant_rows_1x128(gu, I, swiglu=True), iters),
+        row("quant_rows_1x128 swiglu", [T, 2 * I], lambda: cuda.quant_rows_1x128(gu, I, swiglu=True),
             T * I * 5.0)
         # RoPE + q/k norm-free KV write, Llama-8B heads
         Hq, Hkv, D, bs = 32, 8, 128, 16
@@ -415,27 +418,27 @@ def bench_misc(iters=20) -> list:
         slots = torch.arange(T, device=dev, dtype=torch.int32)
         inv_freq = ref.rope_inv_freq(D, 500000.0, None).to(dev)
         row("rope_and_cache", [T, Hq, Hkv, D],
-            time_fn(lambda: cuda.rope_and_cache(qkv, pos, inv_freq, cache, slots, Hq, Hkv, D), iters),
+            lambda: cuda.rope_and_cache(qkv, pos, inv_freq, cache, slots, Hq, Hkv, D),
             T * (Hq + 2 * Hkv) * D * 2.0 + T * (Hq + 2 * Hkv) * D * 2.0)
         # MoE routing / permutation, Qwen3-30B-A3B shape
         E, k, Hm = 128, 8, 2048
         logits = torch.randn(T, E, device=dev)
-        row("moe_route", [T, E, k], time_fn(lambda: cuda.moe_route(logits, k), iters), T * E * 4.0 + T * k * 8.0)
+        row("moe_route", [T, E, k], lambda: cuda.moe_route(logits, k), T * E * 4.0 + T * k * 8.0)
         ids, wts = cuda.moe_route(logits, k)
         xm = torch.randn(T, Hm, device=dev).bfloat16()
-        row("moe_permute", [T, k, Hm], time_fn(lambda: cuda.moe_permute(xm, ids, 0, E), iters),
+        row("moe_permute", [T, k, Hm], lambda: cuda.moe_permute(xm, ids, 0, E),
             T * Hm * 2.0 + T * k * Hm * 2.0)
         xp, goff, _, inv = cuda.moe_permute(xm, ids, 0, E)
-        row("moe_unpermute", [T, k, Hm], time_fn(lambda: cuda.moe_unpermute(xp, inv, wts, T), iters),
+        row("moe_unpermute", [T, k, Hm], lambda: cuda.moe_unpermute(xp, inv, wts, T),
             T * k * Hm * 2.0 + T * Hm * 2.0)
     # sampling over the Llama-3 vocabulary
     R, V = 64, 128256
     lg = torch.randn(R, V, device=dev).bfloat16()
-    row("argmax", [R, V], time_fn(lambda: cuda.argmax(lg), iters), R * V * 2.0)
+    row("argmax", [R, V], lambda: cuda.argmax(lg), R * V * 2.0)
     temp = torch.full((R,), 0.8, device=dev)
     tk = torch.full((R,), 50, device=dev, dtype=torch.int32)
     tp = torch.full((R,), 0.9, device=dev)
-    row("sample top-k 50 top-p 0.9", [R, V], time_fn(lambda: cuda.sample(lg, temp, tk, tp, None, False, 1), iters),
+    row("sample top-k 50 top-p 0.9", [R, V], lambda: cuda.sample(lg, temp, tk, tp, None, False, 1),
         R * V * 2.0, note="several passes over the row by design (bisection); bytes = one pass")
     # MLA decode, DeepSeek-V3 per-rank shape at TP8: 16 heads, latent 512 + 64
     for reqs, ctx in ((64, 2048),):
@@ -449,7 +452,7 @@ def bench_misc(iters=20) -> list:
         meta = AttentionMetadata(None, None, bt, sl, qsl, reqs, reqs, num_decode_reqs=reqs, max_seq_len=ctx,
                                  padded_num_reqs=reqs, padded_num_tokens=reqs)
         row("mla_decode", [reqs, ctx, Hh, L + Rr],
-            time_fn(lambda: cuda.mla_paged_attention(q, cache, meta, (128 + 64) ** -0.5, L), iters),
+            lambda: cuda.mla_paged_attention(q, cache, meta, (128 + 64) ** -0.5, L),
             reqs * ctx * (L + Rr) * 2.0, note="bytes = one read of every latent row")
         w_uk_t = (torch.randn(Hh, L, 128, device=dev) * 0.05).bfloat16()
         qq = torch.randn(reqs, Hh, 192, device=dev).bfloat16()
@@ -457,7 +460,7 @@ def bench_misc(iters=20) -> list:
         pos = torch.full((reqs,), ctx - 1, device=dev, dtype=torch.int32)
         inv_freq = ref.rope_inv_freq(64, 10000.0, None).to(dev)
         row("mla_absorb (permute, grouped GEMM, permute, 2 x rope)", [reqs, Hh, 128, L],
-            time_fn(lambda: cuda.mla_absorb(qq, kvx, pos, inv_freq, w_uk_t, 128, 64, L, False), iters),
+            lambda: cuda.mla_absorb(qq, kvx, pos, inv_freq, w_uk_t, 128, 64, L, False),
             Hh * L * 128 * 2.0 + reqs * Hh * (192 + L + 64) * 2.0, note="five launches")
     return rows
 
@@ -542,6 +545,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=1100)
     ap.add_argument("--q", type=int, default=1024)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--only", default="", help="misc: time only the rows whose name contains this")
     ap.add_argument("--impl", default="tcgen05", choices=["tcgen05", "2sm", "cublas"])
     ap.add_argument("--impls", default="tcgen05,cublas", help="gemm-sustained: implementations to run")
     ap.add_argument("--layers", type=int, default=8)
@@ -562,7 +566,7 @@ def main():
         for r in bench_w4a16(a.T, a.N, a.K, a.iters):
             print(json.dumps(r))
     if a.what == "misc":
-        for r in bench_misc(a.iters):
+        for r in bench_misc(a.iters, a.only):
             print(json.dumps(r))
     if a.what == "fp8-gemm":
         for r in bench_fp8_gemm(a.T, a.N, a.K, a.iters):
