@@ -82,3 +82,26 @@ def test_tiny_moe_engine_on_gpu():
     graph = [o.outputs[0].token_ids for o in LLM(cfg, **kw).generate(prompts, sp)]
     assert eager == graph
     assert cu().check_status() == 0
+
+
+@pytest.mark.parametrize("sim", ["", "uniform", "hash"])
+def test_route_post_kernel_matches_reference(sim):
+    from vllm_torchtpu_b200.ops import reference as ref
+    g = torch.Generator(device=DEV).manual_seed(0)
+    T, k, E = 77, 8, 128
+    ids = torch.randint(0, E, (T, k), device=DEV, generator=g, dtype=torch.int32)
+    w = torch.rand(T, k, device=DEV, generator=g)
+    nv = torch.tensor([50], dtype=torch.int32, device=DEV)
+    want_ids, want_w = ref.moe_route_post(ids.cpu().clone(), w.cpu().clone(), E, nv.cpu(), sim)
+    got_ids, got_w = cu().moe_route_post(ids, w, E, nv, sim)
+    assert torch.equal(got_ids.cpu(), want_ids)
+    torch.testing.assert_close(got_w.cpu(), want_w)
+    # masked pairs drop out of the expert pipeline
+    x = torch.randn(T, 256, device=DEV, generator=g).bfloat16()
+    w13 = (torch.randn(E, 256, 256, device=DEV, generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(E, 256, 128, device=DEV, generator=g) * 0.05).bfloat16()
+    y = cu().moe_experts(x, w13, w2, got_ids, got_w, 0)
+    torch.cuda.synchronize()
+    assert not y[50:].float().abs().sum().item() and cu().check_status() == 0
+    want = ref.moe_experts(x, w13, w2, got_ids, got_w, 0)
+    assert (y.float() - want.float()).abs().max().item() <= 3e-2 * want.float().abs().max().item() + 2e-2

@@ -65,3 +65,25 @@ def test_yarn_rope_frequencies_and_attention_factor():
     lo_t, hi_t = math.floor(lo), math.ceil(hi)
     ramp_t = ((torch.arange(D // 2, dtype=torch.float64) - lo_t) / (hi_t - lo_t)).clamp(0, 1)
     torch.testing.assert_close(trunc, base / factor * ramp_t + base * (1 - ramp_t), rtol=1e-6, atol=0)
+
+
+def test_route_padding_mask_and_routing_simulation():
+    from vllm_torchtpu_b200.ops import reference as ref
+    T, k, E = 10, 4, 16
+    ids = torch.randint(0, E, (T, k), dtype=torch.int32)
+    w = torch.rand(T, k)
+    keep_ids, keep_w = ids.clone(), w.clone()
+    ref.moe_route_post(ids, w, E, torch.tensor([7], dtype=torch.int32), "")
+    assert torch.equal(ids[:7], keep_ids[:7]) and (ids[7:] == -1).all() and (w[7:] == 0).all()
+    torch.testing.assert_close(w[:7], keep_w[:7])
+    ref.moe_route_post(ids, w, E, None, "uniform")
+    counts = torch.bincount(ids.flatten().long(), minlength=E)
+    assert counts.max() - counts.min() <= 1 and torch.allclose(w, torch.full_like(w, 0.25))
+    ref.moe_route_post(ids, w, E, None, "hash")
+    assert all(len(set(r.tolist())) == k for r in ids) and int(ids.min()) >= 0 and int(ids.max()) < E
+    # masked rows contribute nothing to the experts' output
+    x = torch.randn(T, 8)
+    w13, w2 = torch.randn(E, 12, 8) * 0.3, torch.randn(E, 8, 6) * 0.3
+    ref.moe_route_post(ids, w, E, torch.tensor([4], dtype=torch.int32), "")
+    y = ref.moe_experts(x, w13, w2, ids, w, 0)
+    assert not y[4:].any() and y[:4].abs().sum() > 0

@@ -194,7 +194,44 @@ __global__ void moe_unpermute_kernel(const __nv_bfloat16* __restrict__ y, const 
 
 }  // namespace b200
 
+namespace b200 {
+// After routing: rows at or beyond *num_valid (padding of a captured bucket or of a lockstep step) lose their
+// experts (id -1 is ignored by permute, dispatch and combine), and a routing simulation may replace the
+// router's choice: 1 = round-robin over (token, k), perfectly balanced; 2 = hashed start expert per token with
+// the k experts E / k apart.  Simulated weights are 1 / k.
+// (reference: src/vllm_torchtpu/layers/adapter/token_padding.py, moe_routing.py routing simulation)
+__global__ void moe_route_post_kernel(int* __restrict__ ids, float* __restrict__ w, int T, int k, int E,
+                                      const int* __restrict__ num_valid, int sim) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * k) return;
+  const int t = i / k, j = i - t * k;
+  if (num_valid != nullptr && t >= *num_valid) {
+    ids[i] = -1;
+    w[i] = 0.f;
+    return;
+  }
+  if (sim == 1) {
+    ids[i] = i % E;
+    w[i] = 1.f / (float)k;
+  } else if (sim == 2) {
+    uint32_t h = (uint32_t)t * 2654435761u;
+    h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+    const int stride = E / k > 0 ? E / k : 1;
+    ids[i] = (int)((h % (uint32_t)E + (uint32_t)(j * stride)) % (uint32_t)E);
+    w[i] = 1.f / (float)k;
+  }
+}
+}  // namespace b200
+
 using namespace b200;
+
+extern "C" int b200_moe_route_post(int* ids, float* w, int T, int k, int E, const int* num_valid, int sim,
+                                   cudaStream_t stream) {
+  if (T * k == 0 || (num_valid == nullptr && sim == 0)) return 0;
+  moe_route_post_kernel<<<(T * k + 255) / 256, 256, 0, stream>>>(ids, w, T, k, E, num_valid, sim);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
 
 // dtype: 0 = bf16 logits, 1 = fp32 logits
 extern "C" int b200_moe_route(const void* logits, int dtype, int ld, int T, int E, int top_k, int sigmoid,

@@ -98,6 +98,9 @@ _decl("B200_BOUNDS_CHECK", bool, False,
 _decl("B200_DEVICE_SPEC_ACCEPT", bool, True, "speculative decoding: judge the drafts on the device")
 _decl("B200_FP8_ROWS_MIN_TILES", int, 96,
       "fp8 block GEMM: use the token-major kernel from this many 128x256 output tiles (-1: never)")
+_decl("B200_MOE_ROUTING_SIM", str, "",
+      "replace the router's choice: 'uniform' (round-robin, perfectly balanced) or 'hash' (hashed per token); "
+      "for benchmarks with random-init routers")
 _decl("B200_MOE_FUSED_EP", bool, True, "dispatch/combine inside the expert kernel over peer memory")
 _decl("B200_MOE_EP_CAPACITY_FACTOR", float, 0.0,
       "fused EP plane: rows an owner can receive per call, as a multiple of call tokens * top_k; "

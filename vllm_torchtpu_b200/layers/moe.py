@@ -26,6 +26,16 @@ from ..quantization import get_moe_method
 from .linear import ReplicatedLinear
 
 
+_step_num_valid = None       # device int32[1]: rows of the current step that are real tokens (None: all)
+
+
+def set_step_valid_tokens(t) -> None:
+    """The runner names, per step, the device word that holds the number of real token rows; rows behind it
+    (bucket padding, lockstep padding) are masked out of the routing."""
+    global _step_num_valid
+    _step_num_valid = t
+
+
 def expert_placement(num_experts: int, ep_size: int, policy: str = "linear",
                      static_perm: Optional[list] = None) -> list:
     """``owner[e]`` = (rank, local index) for every global expert id."""
@@ -84,9 +94,19 @@ class FusedMoE:
     def route(self, x: torch.Tensor):
         logits = self.gate(x)
         c = self.cfg
-        return ops.moe_route(logits, self.top_k, scoring=c.moe_scoring, renormalize=c.moe_renormalize,
-                             routed_scaling=c.moe_routed_scaling, score_bias=self.score_bias,
-                             n_group=c.moe_n_group, topk_group=c.moe_topk_group)
+        ids, w = ops.moe_route(logits, self.top_k, scoring=c.moe_scoring, renormalize=c.moe_renormalize,
+                               routed_scaling=c.moe_routed_scaling, score_bias=self.score_bias,
+                               n_group=c.moe_n_group, topk_group=c.moe_topk_group)
+        sim = envs.B200_MOE_ROUTING_SIM
+        nv = _step_num_valid
+        if nv is not None and nv.device != ids.device:
+            nv = None
+        if sim or nv is not None:
+            # padded rows take no expert; a routing simulation (benchmarks with random-init routers) replaces
+            # the router's choice by a balanced or hashed one
+            post = ops.cuda_ops().moe_route_post if ids.is_cuda else ops.ref.moe_route_post
+            ids, w = post(ids, w, self.num_experts, nv, sim)
+        return ids, w
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         topk_ids, topk_w = self.route(x)

@@ -716,7 +716,7 @@ def p2p_all_reduce(x, heap):
     return x
 
 
-from .cuda_moe import (EpState, gemm_swiglu, grouped_gemm, moe_experts, moe_experts_ep,  # noqa: E402,F401
+from .cuda_moe import (EpState, gemm_swiglu, grouped_gemm, moe_experts, moe_experts_ep, moe_route_post,  # noqa: E402,F401
                        moe_permute, moe_route, moe_unpermute)
 from .cuda_fp8 import (fp8_block_gemm, fp8_block_gemm_push, fp8_block_gemm_push_quantised,  # noqa: E402,F401
                        fp8_block_gemm_quantised, fp8_per_tensor_gemm, fp8_rowwise_gemm, grouped_fp8_gemm, int8_gemm,  # noqa: E402,F401

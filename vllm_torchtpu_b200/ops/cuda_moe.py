@@ -67,6 +67,19 @@ def moe_route(router_logits, top_k, scoring="softmax", renormalize=True, routed_
     return ids, w
 
 
+ROUTE_SIM = {"": 0, "off": 0, "uniform": 1, "hash": 2}
+
+
+def moe_route_post(ids, w, num_experts: int, num_valid=None, sim: str = ""):
+    """In place: rows from ``num_valid[0]`` (device int32) on lose their experts; ``sim`` replaces the
+    router's choice by a balanced ("uniform") or hashed assignment with weights 1 / k."""
+    T, k = ids.shape
+    _c._check(_c.lib().b200_moe_route_post(_c._p(ids), _c._p(w), c_int(T), c_int(k), c_int(num_experts),
+                                           _c._p(num_valid), c_int(ROUTE_SIM[sim]), _c._stream()), "moe_route_post")
+    count_launch()
+    return ids, w
+
+
 def moe_permute(x, topk_ids, e_lo: int, e_local: int):
     T, H = x.shape
     k = topk_ids.shape[1]

@@ -369,6 +369,29 @@ def moe_route(router_logits, top_k: int, scoring: str = "softmax", renormalize: 
     return ids.to(torch.int32), (w * routed_scaling).float()
 
 
+def moe_route_post(ids, w, num_experts: int, num_valid=None, sim: str = ""):
+    """Padding mask and routing simulation after the router (same rules as the CUDA kernel)."""
+    T, k = ids.shape
+    if sim == "uniform":
+        ids.copy_((torch.arange(T * k, device=ids.device) % num_experts).view(T, k).to(ids.dtype))
+        w.fill_(1.0 / k)
+    elif sim == "hash":
+        t = torch.arange(T, device=ids.device, dtype=torch.int64)
+        h = (t * 2654435761) & 0xFFFFFFFF
+        h = h ^ (h >> 15)
+        h = (h * 2246822519) & 0xFFFFFFFF
+        h = h ^ (h >> 13)
+        stride = max(1, num_experts // k)
+        j = torch.arange(k, device=ids.device, dtype=torch.int64)
+        ids.copy_(((h % num_experts)[:, None] + j[None, :] * stride) % num_experts)
+        w.fill_(1.0 / k)
+    if num_valid is not None:
+        n = int(num_valid[0])
+        ids[n:] = -1
+        w[n:] = 0
+    return ids, w
+
+
 def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0, act: str = "silu"):
     """Σ_k w_k · FFN_e(x) over the experts this rank owns.  w13: [E_local, 2I, H] (gate rows first),
     w2: [E_local, H, I]; ``act``: gated activation (``parse_gated_act``)."""

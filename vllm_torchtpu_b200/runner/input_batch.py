@@ -91,7 +91,8 @@ class StepBuffers:
         pad = lambda n: (n + 3) // 4 * 4        # keep every array 16-byte aligned
         sizes = [("input_ids", T), ("positions", T), ("slot_mapping", T), ("token_src", T),
                  ("query_start_loc", R + 1), ("seq_lens", R), ("logits_indices", T), ("top_k", T),
-                 ("batch_slots", R), ("temperature", T), ("top_p", T), ("rng_step", 2), ("global_seq_lens", R)]
+                 ("batch_slots", R), ("temperature", T), ("top_p", T), ("rng_step", 2), ("global_seq_lens", R),
+                 ("num_valid", 1)]
         self.offsets, off = {}, 0
         for name, n in sizes:
             self.offsets[name] = (off, n)

@@ -365,6 +365,7 @@ class ModelRunner:
         v = hv("temperature", L_pad, np.float32); v[:L] = b.temperature[rslots]; v[L:] = 0
         v = hv("top_p", L_pad, np.float32); v[:L] = b.top_p[rslots]; v[L:] = 1
         hv("rng_step").view(np.int64)[0] = self.stats["steps"]
+        hv("num_valid")[0] = T
         bufs.np_bt[:n] = b.block_table[slots]
         if R_pad > n:
             bufs.np_bt[n:R_pad] = 0
@@ -395,6 +396,18 @@ class ModelRunner:
     def _forward_and_sample(self, bufs, meta, T, R, all_greedy: bool, L=None):
         """Everything that runs on the device for one step (also the captured region).
         ``L`` = number of sampled rows when it differs from the request count (spec-verify steps)."""
+        if not self.mcfg.is_moe:
+            return self._forward_and_sample_inner(bufs, meta, T, R, all_greedy, L)
+        # rows behind the real tokens (bucket or lockstep padding) take no expert: the routing reads the
+        # step's count of real rows from this device word
+        from ..layers.moe import set_step_valid_tokens
+        set_step_valid_tokens(bufs.dev_view("num_valid", 1))
+        try:
+            return self._forward_and_sample_inner(bufs, meta, T, R, all_greedy, L)
+        finally:
+            set_step_valid_tokens(None)
+
+    def _forward_and_sample_inner(self, bufs, meta, T, R, all_greedy: bool, L=None):
         dv = bufs.dev_view
         n_req_pad, verify = R, L is not None
         R = L if verify else R
@@ -659,6 +672,7 @@ class ModelRunner:
         hv("temperature", 1, np.float32)[:] = 0
         hv("top_p", 1, np.float32)[:] = 1
         bufs.np_bt[:1] = 0
+        hv("num_valid")[0] = 0                     # every row of a placeholder step is padding: no expert work
         bufs.upload(1)
         p = dict(bufs=bufs, n=1, T=per, R_pad=1, T_pad=T, num_decode=0, max_q=per, max_seq=per,
                  seq_lens_np=np.full(1, per, dtype=np.int64), qsl_np=np.array([0, per], dtype=np.int64))
@@ -858,6 +872,7 @@ class ModelRunner:
         hv("temperature", R, np.float32)[:] = 0
         hv("top_p", R, np.float32)[:] = 1
         bufs.np_bt[:R] = 0
+        hv("num_valid")[0] = R
         bufs.upload(R)
         p = dict(bufs=bufs, n=R, T=R, R_pad=R, T_pad=R, num_decode=R, max_q=1, max_seq=1,
                  seq_lens_np=np.ones(R, dtype=np.int64), qsl_np=np.arange(R + 1, dtype=np.int64))
@@ -890,6 +905,7 @@ class ModelRunner:
         hv("temperature", R, np.float32)[:] = 0
         hv("top_p", R, np.float32)[:] = 1
         bufs.np_bt[:R] = 0
+        hv("num_valid")[0] = T
         bufs.upload(R)
         p = dict(bufs=bufs, n=R, T=T, R_pad=R, T_pad=T, num_decode=0, max_q=per, max_seq=per,
                  seq_lens_np=np.full(R, per, dtype=np.int64), qsl_np=qsl)
