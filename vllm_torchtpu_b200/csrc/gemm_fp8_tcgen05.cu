@@ -343,6 +343,45 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
             ++route_count;
           }
         }
+      } else if (PUSH && (p.N & 7) == 0 && k.n0 + BM <= p.N) {
+        // pushed partial (every rank receives a copy): turned in shared memory like the routed rows, sixteen
+        // 16-byte stores per token and destination instead of 2-byte stores
+        const float bias = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;
+        const int grp = (warp - 2) >> 2;
+        __nv_bfloat16* stg = s_route + grp * (2 * 32 * BM);
+        const int seg = row & 15, jt = row >> 4;
+#pragma unroll
+        for (int c0 = 0; c0 < CW; c0 += 32) {
+          if (c0 < cv) {                              // uniform over the four warps of the set
+            __nv_bfloat16* st = stg + (route_count & 1) * (32 * BM);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) st[j * BM + row] = __float2bfloat16(acc[c0 + j] + bias);
+            asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int j = jt + 8 * i;
+              if (c0 + j < cv) {
+                const uint4 v = *reinterpret_cast<const uint4*>(st + j * BM + seg * 8);
+                for (int d = 0; d < ndst; ++d)
+                  *reinterpret_cast<uint4*>(
+                      reinterpret_cast<__nv_bfloat16*>(p.peer[d] + p.part_off + (size_t)p.rank * p.part_src_stride) +
+                      (size_t)(k.t_row + col0 + c0 + j) * p.N + k.n0 + seg * 8) = v;
+              }
+            }
+            ++route_count;
+          }
+        }
+        {
+          // the tile has been pushed: release its flag at every rank
+          __threadfence_system();
+          asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
+          const int t = (int)threadIdx.x - 64;
+          if (t < p.world) {
+            const int tile = raster_tile(k.n0 / BM, k.t_row / BN, p.n_tiles, p.t_tiles);
+            st_release_sys(reinterpret_cast<int*>(p.peer[t] + p.tile_flag_off) + (size_t)p.rank * p.max_tiles + tile,
+                           epoch);
+          }
+        }
       } else {
         if (n < p.N) {
           const float bias = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;

@@ -661,8 +661,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
       } else if (p.splits == 1) {
         const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+        // pushed partials (every rank receives a copy): 32 tokens x 128 columns are turned in shared memory so
+        // that a token's 256 bytes leave as sixteen 16-byte stores per destination instead of 2-byte stores
+        const bool vec_push = push_out && (p.N & 7) == 0 && wk.n0 + BM <= p.N;
+        if (vec_push) {
+          __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + Cfg::PUSH_OFF);
+          const int seg = row & 15, jt = row >> 4;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            if (c0 >= t_valid) break;             // uniform over the four epilogue warps
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c0, r);
+            tmem_ld_wait();
+            __nv_bfloat16* st = stg + (push_count & 1) * (32 * BM);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) st[j * BM + row] = __float2bfloat16(__uint_as_float(r[j]) + bias);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int j = jt + 8 * i;
+              if (c0 + j < t_valid) {
+                const uint4 v = *reinterpret_cast<const uint4*>(st + j * BM + seg * 8);
+                for (int d = 0; d < ndst; ++d) {
+                  const TileDst td = tile_dst<BN, MODE>(p, wk, d);
+                  *reinterpret_cast<uint4*>(td.base + (size_t)(c0 + j) * td.cs + seg * 8) = v;
+                }
+              }
+            }
+            ++push_count;
+          }
+        }
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN && !vec_push; c0 += 32) {
           if (c0 >= t_valid) break;               // warp-uniform
           uint32_t r[32];
           tmem_ld_32x32(taddr + c0, r);
