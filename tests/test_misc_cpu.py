@@ -179,3 +179,18 @@ def test_fused_ep_plane_is_called_once_per_call_tokens_rows():
     calls.clear()
     moe._fused_ep_calls(x[:4], ids[:4], w[:4], comm)
     assert calls == [4]
+
+
+def test_docs_list_every_environment_variable_and_guided_choice_maps_to_a_regex():
+    import os
+    import re
+    from vllm_torchtpu_b200 import envs
+    from vllm_torchtpu_b200.entrypoints.openai_server import _structured_spec
+    doc = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "docs", "reference",
+                            "env_vars.md")).read()
+    missing = [n for n in envs.declared() if f"`{n}`" not in doc]
+    assert not missing, f"docs/reference/env_vars.md lacks {missing}"
+    spec = _structured_spec({"guided_choice": ["yes", "no way", "a.b"]})
+    rx = re.compile(spec["regex"])
+    assert all(rx.fullmatch(s) for s in ("yes", "no way", "a.b")) and not rx.fullmatch("axb")
+    assert _structured_spec({"response_format": {"type": "json_object"}}) == {"json_object": True}

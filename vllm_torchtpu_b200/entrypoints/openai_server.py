@@ -28,6 +28,9 @@ def _structured_spec(body: dict):
         return {"json": body["guided_json"]}
     if body.get("guided_regex"):
         return {"regex": body["guided_regex"]}
+    if body.get("guided_choice"):
+        import re as _re
+        return {"regex": "(" + "|".join(_re.escape(str(c)) for c in body["guided_choice"]) + ")"}
     rf = body.get("response_format") or {}
     if rf.get("type") == "json_schema":
         js = rf.get("json_schema") or {}
