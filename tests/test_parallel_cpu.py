@@ -95,3 +95,33 @@ def test_tp2_server_requests_reach_every_rank(single, flags):
     """HTTP requests arrive at rank 0 only; it broadcasts them step by step and the follower rank runs
     the same steps, so the completions equal the one-process tokens."""
     assert _run(2, "cpu", *flags, script="serve_sync_worker.py") == single
+
+
+def test_export_from_a_tensor_parallel_engine(tmp_path):
+    """A TP2 engine loaded from a checkpoint exports its serving directory (rank 0 copies the checkpoint, the
+    plan records the degrees); the directory validates and a single-rank engine loaded from it repeats the tokens."""
+    import numpy as np
+    from vllm_torchtpu_b200 import SamplingParams
+    from vllm_torchtpu_b200.engine.llm import LLM
+    from vllm_torchtpu_b200.export import load_serving_dir, validate_serving_dir
+    from vllm_torchtpu_b200.models.loader import save_hf_checkpoint
+    donor = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    ckpt = str(tmp_path / "ckpt")
+    hf = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4,
+          "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 512, "vocab_size": 1024,
+          "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 256, "torch_dtype": "float32"}
+    save_hf_checkpoint(donor.engine.runner.model, ckpt, hf)
+    out = str(tmp_path / "serving")
+    toks = _run(2, "tp", ckpt, "--export", out)
+    assert validate_serving_dir(out) == []
+    meta = json.load(open(os.path.join(out, "metadata.json")))
+    assert meta["parallel"]["tensor_parallel_size"] == 2 and meta["parallel"]["world_size"] == 2
+    assert "serving_checkpoint/model.safetensors" in meta["manifest"]
+    llm = load_serving_dir(out, device="cpu", init_dist=False, tensor_parallel_size=1)
+    rng = np.random.RandomState(0)
+    prompts = [rng.randint(0, 1024, size=n).tolist() for n in (5, 23, 70)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    assert [o.outputs[0].token_ids for o in llm.generate(prompts, sp)] == toks
+    meta["parallel"]["world_size"] = 3
+    json.dump(meta, open(os.path.join(out, "metadata.json"), "w"))
+    assert any("parallel plan" in p for p in validate_serving_dir(out))

@@ -84,6 +84,10 @@ def main():
             for j, t in enumerate(part):
                 merged[r + j * world] = t
         toks = merged
+    if "--export" in sys.argv:
+        # every rank calls the exporter; rank 0 writes the directory
+        from vllm_torchtpu_b200.export import export_serving_dir
+        export_serving_dir(llm, sys.argv[sys.argv.index("--export") + 1])
     if rank == 0:
         print("RESULT " + json.dumps({"tokens": toks}), flush=True)
     if world > 1:

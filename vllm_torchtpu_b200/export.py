@@ -10,6 +10,12 @@ the SHA-256 of every file, so that a serving host can verify it before it starts
       serving_checkpoint/config.json        Hugging Face style model configuration
       serving_checkpoint/model.safetensors  weights
 
+An engine that was loaded from a checkpoint directory (any architecture, any number of ranks) is exported by
+copying that checkpoint: rank 0 writes, the other ranks wait; the parallel plan of the exporting engine
+(tensor / pipeline / data / expert / context parallel degrees) is recorded and is the default of the loader,
+which shards at load time.  A random-init engine is written from its parameters (single rank, Llama and
+Qwen-MoE families).
+
 (reference: src/vllm_torchtpu/experimental/export/ — exporter to a serving directory with
 ``metadata.json``, per-bucket programs and ``serving_checkpoint/``, validator; the per-bucket compiled
 programs of the reference have no counterpart here because decode buckets are CUDA graphs captured
@@ -54,16 +60,39 @@ def _sha256(path: str) -> str:
     return h.hexdigest()
 
 
+_CKPT_FILES = (".safetensors", ".json", ".model", ".txt", ".tiktoken", ".jinja")
+
+
+def _copy_checkpoint(src: str, dst: str) -> None:
+    import shutil
+    for name in sorted(os.listdir(src)):
+        p = os.path.join(src, name)
+        if os.path.isfile(p) and name.endswith(_CKPT_FILES):
+            shutil.copyfile(p, os.path.join(dst, name))
+
+
 def export_serving_dir(llm, out_dir: str) -> dict:
-    """Write the serving directory of a loaded single-rank engine; returns the metadata."""
+    """Write the serving directory of a loaded engine; returns the metadata (on every rank)."""
     from .models.loader import save_hf_checkpoint
+    from .parallel.state import get_state
     eng = llm.engine
     cfg = eng.cfg
-    if cfg.parallel.world_size != 1:
-        raise ValueError("export runs on a single-rank engine; the serving host shards at load time")
+    st = get_state()
+    world = cfg.parallel.world_size
+    src = getattr(cfg, "model_path", None)
+    if world != 1 and not src:
+        raise ValueError("a random-init engine is exported from a single rank; engines of several ranks are "
+                         "exported from the checkpoint directory they were loaded from")
     ckpt = os.path.join(out_dir, "serving_checkpoint")
-    os.makedirs(ckpt, exist_ok=True)
-    save_hf_checkpoint(eng.runner.model, ckpt, to_hf_config(cfg.model))
+    if st.rank == 0 or world == 1:
+        os.makedirs(ckpt, exist_ok=True)
+        if src:
+            _copy_checkpoint(src, ckpt)
+        else:
+            save_hf_checkpoint(eng.runner.model, ckpt, to_hf_config(cfg.model))
+    if world > 1 and st.world.cpu_group is not None:
+        import torch.distributed as dist
+        dist.barrier(group=st.world.cpu_group)            # the files are complete before anybody hashes them
     manifest = {}
     for name in sorted(os.listdir(ckpt)):
         p = os.path.join(ckpt, name)
@@ -78,12 +107,22 @@ def export_serving_dir(llm, out_dir: str) -> dict:
                    "max_num_batched_tokens": cfg.scheduler.max_num_batched_tokens,
                    "max_model_len": cfg.model.max_model_len,
                    "enable_prefix_caching": cfg.cache.enable_prefix_caching},
+        "parallel": {"tensor_parallel_size": cfg.parallel.tensor_parallel_size,
+                     "pipeline_parallel_size": cfg.parallel.pipeline_parallel_size,
+                     "data_parallel_size": cfg.parallel.data_parallel_size,
+                     "enable_expert_parallel": bool(cfg.parallel.enable_expert_parallel),
+                     "decode_context_parallel_size": cfg.parallel.decode_context_parallel_size,
+                     "world_size": world},
         "plan": {"token_buckets": list(cfg.token_buckets), "request_buckets": list(cfg.request_buckets),
                  "decode_graphs": [[int(r), bool(g)] for (r, g) in sorted(eng.runner.graphs)]},
         "manifest": manifest,
     }
-    with open(os.path.join(out_dir, "metadata.json"), "w") as f:
-        json.dump(meta, f, indent=1, sort_keys=True)
+    if st.rank == 0 or world == 1:
+        with open(os.path.join(out_dir, "metadata.json"), "w") as f:
+            json.dump(meta, f, indent=1, sort_keys=True)
+    if world > 1 and st.world.cpu_group is not None:
+        import torch.distributed as dist
+        dist.barrier(group=st.world.cpu_group)
     return meta
 
 
@@ -117,6 +156,21 @@ def validate_serving_dir(path: str, check_hashes: bool = True) -> list:
         b = plan.get(name) or []
         if not b or b != sorted(b):
             problems.append(f"plan.{name} must be a non-empty ascending list")
+    par = meta.get("parallel")
+    if par is not None:
+        prod = par.get("tensor_parallel_size", 1) * par.get("pipeline_parallel_size", 1) * \
+            par.get("data_parallel_size", 1)
+        if prod != par.get("world_size", prod):
+            problems.append(f"parallel plan: tp x pp x dp = {prod}, world_size {par.get('world_size')}")
+        cfg_path = os.path.join(path, "serving_checkpoint", "config.json")
+        if os.path.isfile(cfg_path):
+            try:
+                with open(cfg_path) as f:
+                    hf = json.load(f)
+                if hf.get("num_hidden_layers", 1) < par.get("pipeline_parallel_size", 1):
+                    problems.append("parallel plan: more pipeline stages than layers")
+            except ValueError:
+                problems.append("serving_checkpoint/config.json is not JSON")
     eng = meta.get("engine") or {}
     if plan.get("request_buckets") and eng.get("max_num_seqs", 0) > plan["request_buckets"][-1]:
         problems.append("max_num_seqs exceeds the largest request bucket")
@@ -136,6 +190,11 @@ def load_serving_dir(path: str, device: Optional[str] = None, **overrides):
               block_size=eng["block_size"], kv_cache_dtype=eng["kv_cache_dtype"],
               enable_prefix_caching=eng["enable_prefix_caching"], max_model_len=eng["max_model_len"],
               dtype=meta["model"]["dtype"])
+    par = meta.get("parallel") or {}
+    for key in ("tensor_parallel_size", "pipeline_parallel_size", "data_parallel_size", "enable_expert_parallel",
+                "decode_context_parallel_size"):
+        if key in par and par[key] not in (1, False):
+            kw[key] = par[key]                          # the exporting engine's plan; overrides win
     kw.update(overrides)
     if device is None:
         device = "cuda" if torch.cuda.is_available() else "cpu"
