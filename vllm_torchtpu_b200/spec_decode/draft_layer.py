@@ -97,6 +97,12 @@ class DraftLayerProposer:
             a.qkv = QKVParallelLinear(f"model.layers.{L}.self_attn.qkv_proj", 2 * H, m.num_q_heads, m.num_kv_heads,
                                       m.head_dim, unpadded_q=m.num_q_heads_unpadded, bias=m.attention_bias,
                                       dtype=m.dtype, device=self.device, quant_config=None)
+        par = cfg.parallel
+        if (par.data_parallel_size > 1 and par.enable_expert_parallel and hasattr(self.layer.mlp, "experts")):
+            # the replicas draft at different times and with different row counts, but an expert-parallel
+            # layer needs every rank of the group in each of its collectives
+            raise ValueError("a draft layer with expert-parallel experts under data-parallel attention is not "
+                             "built (its passes would have to run in lockstep over the replicas)")
         if path:
             self._load(path)
         else:
