@@ -139,3 +139,36 @@ def test_chat_prompt_continue_final_message_with_and_without_template_support():
     assert dec(build_chat_prompt(None, enc, msgs, continue_final_message=True)) == "user: hi\nassistant: The answer is"
     with pytest.raises(ValueError):
         build_chat_prompt(tok, enc, msgs[:1], continue_final_message=True)
+
+
+def test_update_weights_and_reload_kernel_routes(tmp_path):
+    """/update_weights loads checkpoint-named tensors from disk into the running model (the outputs change, the
+    prefix cache is dropped); /reload_kernel calls the engine's kernel reload and reports a busy engine as 409."""
+    import torch
+    from safetensors.torch import save_file
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    app = build_app(llm.engine, "tiny-llama", None)
+    with TestClient(app) as c:
+        body = {"prompt": list(range(3, 20)), "max_tokens": 6, "temperature": 0.0, "ignore_eos": True}
+        before = c.post("/v1/completions", json=body).json()["choices"][0]
+        g = torch.Generator().manual_seed(5)
+        mc = llm.engine.cfg.model
+        new = {"lm_head.weight": torch.randn(mc.vocab_size, mc.hidden_size, generator=g) * 0.05}
+        f = tmp_path / "delta.safetensors"
+        save_file(new, str(f))
+        r = c.post("/update_weights", json={"path": str(f)})
+        assert r.status_code == 200 and r.json()["tensors"] == 1
+        torch.testing.assert_close(llm.engine.runner.model.lm_head, new["lm_head.weight"])
+        after = c.post("/v1/completions", json=body).json()["choices"][0]
+        assert after != before
+        assert c.post("/update_weights", json={"path": str(tmp_path / "missing")}).status_code == 400
+        calls = []
+        llm.engine.reload_kernels = lambda path=None: calls.append(path) or "lib.so"
+        r = c.post("/reload_kernel", json={"path": "/x/lib.so"})
+        assert r.status_code == 200 and r.json()["library"] == "lib.so" and calls == ["/x/lib.so"]
+
+        def busy(path=None):
+            raise RuntimeError("reload_kernels needs an idle engine")
+        llm.engine.reload_kernels = busy
+        assert c.post("/reload_kernel").status_code == 409
+    app.state.async_engine.shutdown()

@@ -10,6 +10,7 @@ Prompts may be text (needs a tokenizer) or token-id lists; a model without a tok
 answers with token ids rendered as text.
 """
 import json
+import os
 import time
 import uuid
 from typing import Optional
@@ -260,6 +261,38 @@ def build_app(engine, model_name: str, tokenizer=None):
         if m["ttft_n"]:
             lines.append(f"b200_time_to_first_token_seconds_mean {m['ttft_sum'] / m['ttft_n']:.6f}")
         return PlainTextResponse("\n".join(lines) + "\n")
+
+    @app.post("/reload_kernel")
+    async def reload_kernel(request: Request):
+        """Development aid: load the kernel library again (after a rebuild, or from ``path``) and re-capture the
+        decode graphs without restarting the server; the engine must be idle
+        (reference: src/vllm_torchtpu/platforms/tpu_platform.py:269 /reload_kernel)."""
+        body = await request.json() if await request.body() else {}
+        try:
+            loaded = await aeng.call(lambda eng: eng.reload_kernels(body.get("path")))
+        except RuntimeError as e:
+            raise HTTPException(409, str(e))
+        return {"status": "reloaded", "library": loaded}
+
+    @app.post("/update_weights")
+    async def update_weights(request: Request):
+        """Load checkpoint-named tensors from safetensors files on the server's disk into the running model
+        (``{"path": file-or-directory}``); cached prefixes are dropped; the engine must be idle."""
+        body = await request.json()
+        path = body.get("path")
+        if not path or not os.path.exists(path):
+            raise HTTPException(400, "path to a safetensors file or directory is required")
+
+        def load(eng):
+            from ..models.loader import iter_safetensors
+            return eng.update_weights(list(iter_safetensors(path)))
+        try:
+            n = await aeng.call(load)
+        except RuntimeError as e:
+            raise HTTPException(409, str(e))
+        except (ValueError, OSError) as e:
+            raise HTTPException(400, str(e))
+        return {"status": "updated", "tensors": int(n)}
 
     @app.post("/start_profile")
     async def start_profile(request: Request):

@@ -27,7 +27,7 @@ logger = init_logger(__name__)
 
 def iter_safetensors(path: str) -> Iterator[tuple]:
     from safetensors import safe_open
-    files = sorted(glob.glob(os.path.join(path, "*.safetensors")))
+    files = [path] if os.path.isfile(path) else sorted(glob.glob(os.path.join(path, "*.safetensors")))
     if not files:
         raise FileNotFoundError(f"no .safetensors files in {path}")
     for f in files:
