@@ -98,6 +98,9 @@ _decl("B200_BOUNDS_CHECK", bool, False,
 _decl("B200_DEVICE_SPEC_ACCEPT", bool, True, "speculative decoding: judge the drafts on the device")
 _decl("B200_FP8_ROWS_MIN_TILES", int, 96,
       "fp8 block GEMM: use the token-major kernel from this many 128x256 output tiles (-1: never)")
+_decl("B200_SAFETENSORS_PREFETCH", bool, True, "checkpoint loading: ask the kernel to read the next file ahead")
+_decl("B200_LOAD_EVICT_PAGE_CACHE", bool, False,
+      "checkpoint loading: drop every consumed file from the page cache (large checkpoints on small hosts)")
 _decl("B200_MOE_ROUTING_SIM", str, "",
       "replace the router's choice: 'uniform' (round-robin, perfectly balanced) or 'hash' (hashed per token); "
       "for benchmarks with random-init routers")

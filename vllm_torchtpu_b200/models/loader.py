@@ -25,15 +25,40 @@ from ..parallel.state import get_state
 logger = init_logger(__name__)
 
 
+def _fadvise(path: str, advice: int) -> None:
+    """Page-cache hint for a whole file (no-op where the platform has none)."""
+    if not hasattr(os, "posix_fadvise"):
+        return
+    try:
+        fd = os.open(path, os.O_RDONLY)
+        try:
+            os.posix_fadvise(fd, 0, 0, advice)
+        finally:
+            os.close(fd)
+    except OSError:
+        pass
+
+
 def iter_safetensors(path: str) -> Iterator[tuple]:
+    """(name, tensor) of every tensor in a safetensors file or in the files of a directory.  While a file is
+    parsed the kernel is asked to read the next one ahead (``B200_SAFETENSORS_PREFETCH``), and a consumed file
+    can be dropped from the page cache so that a large checkpoint does not push the host out of memory
+    (``B200_LOAD_EVICT_PAGE_CACHE``)
+    (reference: src/vllm_torchtpu/model_loader_patches.py — prefetch load strategy, page-cache eviction)."""
     from safetensors import safe_open
+    from .. import envs
     files = [path] if os.path.isfile(path) else sorted(glob.glob(os.path.join(path, "*.safetensors")))
     if not files:
         raise FileNotFoundError(f"no .safetensors files in {path}")
-    for f in files:
+    prefetch, evict = envs.B200_SAFETENSORS_PREFETCH, envs.B200_LOAD_EVICT_PAGE_CACHE
+    for i, f in enumerate(files):
+        if prefetch and i + 1 < len(files):
+            _fadvise(files[i + 1], getattr(os, "POSIX_FADV_WILLNEED", 3))
         with safe_open(f, framework="pt", device="cpu") as sf:
             for name in sf.keys():
                 yield name, sf.get_tensor(name)
+        if evict:
+            _fadvise(f, getattr(os, "POSIX_FADV_DONTNEED", 4))
 
 
 class _Collector:
