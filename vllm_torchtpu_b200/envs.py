@@ -98,6 +98,10 @@ _decl("B200_BOUNDS_CHECK", bool, False,
 _decl("B200_DEVICE_SPEC_ACCEPT", bool, True, "speculative decoding: judge the drafts on the device")
 _decl("B200_FP8_ROWS_MIN_TILES", int, 96,
       "fp8 block GEMM: use the token-major kernel from this many 128x256 output tiles (-1: never)")
+_decl("B200_SAMPLE_CLUSTER", bool, True,
+      "top-k / top-p sampling as a 4-CTA cluster per row (0: the one-CTA bisection kernel); read by the kernel library")
+_decl("B200_FP8_ROWS_SKIP_PROMOTE", bool, False,
+      "measurement aid of the token-major fp8 GEMM: skip the promotion (output undefined); read by the kernel library")
 _decl("B200_SAFETENSORS_PREFETCH", bool, True, "checkpoint loading: ask the kernel to read the next file ahead")
 _decl("B200_LOAD_EVICT_PAGE_CACHE", bool, False,
       "checkpoint loading: drop every consumed file from the page cache (large checkpoints on small hosts)")
