@@ -288,3 +288,84 @@ def test_mtp_on_linear_attention_hybrids(preset):
     d = spec.engine.spec
     assert hasattr(d.layer.self_attn, "qkv") and d.kv_cache.dim() == 5
     assert spec.engine.runner.stats.get("state_rollbacks", 0) > 0 and d.stats["proposed"] > 0
+
+
+@pytest.mark.parametrize("method,layers", [("dflash", 1), ("dflash", 2), ("dspark", 1)])
+def test_block_drafter_is_lossless_and_independent_of_batching(method, layers):
+    """Parallel block drafting: context keys / values from the target's hidden states, all k drafts from one
+    non-causal block pass.  The engine's tokens equal plain decoding, and the drafts are a function of the
+    sequence alone (whole prompts against 16-token chunks with another batch composition)."""
+    prompts = [np.random.RandomState(12).randint(0, 1000, size=n).tolist() for n in (7, 37, 20)]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    plain = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    want = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    spec = {"num_hidden_layers": layers}
+    a = _spec_llm(method, max_num_seqs=4, spec=spec)
+    got_a, drafts_a = _logged_drafts(a, prompts, sp)
+    b = _spec_llm(method, max_num_seqs=2, max_num_batched_tokens=16, spec=spec)
+    got_b, drafts_b = _logged_drafts(b, prompts, sp)
+    assert got_a == want and got_b == want
+    common = set(drafts_a) & set(drafts_b)
+    assert len(common) >= 6
+    for key in common:
+        n = min(len(drafts_a[key]), len(drafts_b[key]))
+        assert drafts_a[key][:n] == drafts_b[key][:n], key
+    d = a.engine.spec
+    assert len(d.layers) == layers and len(d.kv_caches) == layers
+    assert d.stats["passes"] > 0 and d.stats["context_rows"] >= sum(len(p) for p in prompts)
+    assert d.stats["proposed"] <= d.stats["passes"] * 3 * len(prompts)      # one pass drafts all k tokens of a step
+    assert a.engine.scheduler.lookahead_extra == 2 and not a.engine.scheduler.async_mode
+
+
+def test_block_drafter_rows_see_the_whole_block_and_checkpoints_load(tmp_path):
+    """A mask row's output depends on LATER block rows too (the block is not causal), and a checkpoint in the
+    drafter's naming loads (layers through the package's loader, fc / norm / head / d2t / Markov head)."""
+    from safetensors.torch import save_file
+    from vllm_torchtpu_b200.config import model_preset
+    m = model_preset("tiny-llama")
+    H, D, I, V, L = m.hidden_size, m.head_dim, m.intermediate_size, m.vocab_size, m.num_layers
+    g = torch.Generator().manual_seed(3)
+    rnd = lambda *s: torch.randn(*s, generator=g) * 0.05       # noqa: E731
+    t = {"fc.weight": rnd(H, 3 * H), "norm.weight": 1 + rnd(H), "lm_head.weight": rnd(64, H),
+         "d2t": torch.arange(64) * 3, "markov_head.embed.weight": rnd(V, 8), "markov_head.proj.weight": rnd(64, 8)}
+    for l in range(2):
+        pre = f"layers.{l}."
+        t.update({pre + "self_attn.q_proj.weight": rnd(m.num_q_heads * D, H),
+                  pre + "self_attn.k_proj.weight": rnd(m.num_kv_heads * D, H),
+                  pre + "self_attn.v_proj.weight": rnd(m.num_kv_heads * D, H),
+                  pre + "self_attn.o_proj.weight": rnd(H, m.num_q_heads * D),
+                  pre + "mlp.gate_proj.weight": rnd(I, H), pre + "mlp.up_proj.weight": rnd(I, H),
+                  pre + "mlp.down_proj.weight": rnd(H, I), pre + "input_layernorm.weight": 1 + rnd(H),
+                  pre + "post_attention_layernorm.weight": 1 + rnd(H)})
+    d = tmp_path / "dspark"
+    d.mkdir()
+    save_file({k: v.contiguous() for k, v in t.items()}, str(d / "model.safetensors"))
+    llm = _spec_llm("dspark", max_num_seqs=4, spec={"model": str(d), "num_hidden_layers": 2, "mask_token_id": 5},
+                    dtype="float32")
+    p = llm.engine.spec
+    torch.testing.assert_close(p.fc, t["fc.weight"])
+    torch.testing.assert_close(p.layers[1].mlp.down.weight, t["layers.1.mlp.down_proj.weight"])
+    torch.testing.assert_close(p.layers[0].input_ln, t["layers.0.input_layernorm.weight"])
+    assert p.head.shape == (64, H) and p.markov_embed.shape == (V, 8) and p.mask_token_id == 5
+    prompts = [np.random.RandomState(2).randint(0, 1000, size=n).tolist() for n in (6, 19)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    plain = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False, dtype="float32")
+    llm.engine.spec.log = []
+    assert [o.outputs[0].token_ids for o in llm.generate(prompts, sp)] == \
+        [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    assert all(tok % 4 == 0 and tok < 64 * 4 for _, _, dr in llm.engine.spec.log for tok in dr)
+    # non-causal block: the first mask row changes when a later row's token changes
+    q = _spec_llm("dflash", max_num_seqs=4)
+    q.generate([prompts[0]], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    dq = q.engine.spec
+    bslots, start = np.array([0]), np.array([3])
+    meta = dq._block_meta(bslots, start, 3)
+
+    def first_mask_state(last_token):
+        ids = torch.tensor([7, dq.mask_token_id, last_token], dtype=torch.int32)
+        hidden, residual = ops_embedding(ids, q.engine.runner.model.embed), None
+        for lay, cache in zip(dq.layers, dq.kv_caches):
+            hidden, residual = lay.forward(hidden, residual, cache, meta)
+        return (hidden + residual)[1].clone()
+    from vllm_torchtpu_b200.ops import embedding as ops_embedding
+    assert not torch.allclose(first_mask_state(11), first_mask_state(12))

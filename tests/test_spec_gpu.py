@@ -151,3 +151,25 @@ def test_mtp_layer_mirroring_a_bigram_target_is_accepted_on_the_device():
     assert all(len(o.outputs[0].token_ids) == 17 for o in outs)
     rs = spec.engine.runner.stats
     assert rs["spec_drafted"] > 0 and rs["spec_accepted"] >= 0.8 * rs["spec_drafted"]
+
+
+@pytest.mark.parametrize("method,layers", [("dflash", 2), ("dspark", 1)])
+def test_block_drafter_engine_run_is_lossless_on_the_device(method, layers):
+    """Parallel block drafting on the package's kernels: context K/V written by the RoPE + cache kernel, the block
+    rows run as one-row requests over context + block (non-causal inside the block)."""
+    import numpy as np
+    from vllm_torchtpu_b200 import LLM, SamplingParams
+    prompts = [np.random.RandomState(4).randint(0, 2000, size=n).tolist() for n in (9, 40, 23)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    kw = dict(device=DEV, max_num_seqs=4, num_gpu_blocks_override=256, init_dist=False)
+    plain = LLM(_bf16_cfg(), max_num_batched_tokens=256, **kw)
+    want = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    del plain
+    spec = LLM(_bf16_cfg(), max_num_batched_tokens=32,
+               speculative_config={"method": method, "num_speculative_tokens": 3, "num_hidden_layers": layers}, **kw)
+    got = [o.outputs[0].token_ids for o in spec.generate(prompts, sp)]
+    assert got == want
+    st = spec.engine.spec.stats
+    assert st["proposed"] > 0 and st["context_rows"] >= sum(len(p) for p in prompts)
+    from vllm_torchtpu_b200.ops import cuda
+    assert cuda.check_status() == 0

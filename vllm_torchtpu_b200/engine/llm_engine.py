@@ -82,7 +82,8 @@ class LLMEngine:
         if cfg.speculative:
             from ..spec_decode import DRAFT_LAYER_METHODS
             if cfg.speculative.get("method") in DRAFT_LAYER_METHODS:
-                self.runner.extra_kv_layers = 1         # the draft layer's KV tensor counts in the HBM budget
+                self.runner.extra_kv_layers = int(cfg.speculative.get("num_hidden_layers", 1)) \
+                    if cfg.speculative.get("method") in ("dflash", "dspark") else 1        # the draft layer's KV tensor counts in the HBM budget
         num_blocks = self.runner.determine_num_blocks()
         if st.world_size > 1 and st.world.cpu_group is not None:
             # the ranks of a pipeline stage must agree within a tolerance; everyone adopts the minimum
@@ -114,6 +115,8 @@ class LLMEngine:
             sch = self.scheduler
             self.connector.load_fn = lambda: {"running": len(sch.running), "waiting": len(sch.waiting),
                                               "free_blocks": sch.kv.pool.num_free_blocks}
+        if self.spec is not None and num_spec:
+            self.scheduler.lookahead_extra = int(getattr(self.spec, "extra_lookahead", 0))
         self.runner.capture_model()
         # Data-parallel replicas coupled by expert parallelism run their steps in lockstep: the MoE
         # collectives of a step need every rank, with equal padded row counts on the gather plane

@@ -66,6 +66,7 @@ class Scheduler:
         self.finished_since_last: list[str] = []
         self.connector = connector
         self.num_spec_tokens = num_spec_tokens
+        self.lookahead_extra = 0            # slots a drafter writes beyond the verification rows
         self.abort_on_preemption = abort_on_preemption
         self.step_id = 0
         self.async_mode = scheduler_config.async_scheduling
@@ -127,7 +128,7 @@ class Scheduler:
                 continue
             new_blocks = None
             while True:
-                new_blocks = self.kv.allocate_slots(req, n, lookahead=self.num_spec_tokens)
+                new_blocks = self.kv.allocate_slots(req, n, lookahead=self.num_spec_tokens + self.lookahead_extra)
                 if new_blocks is not None:
                     break
                 victim = self._pick_victim(req)
@@ -195,7 +196,7 @@ class Scheduler:
                 if n < want and not self.cfg.enable_chunked_prefill:
                     break
                 new_blocks = self.kv.allocate_slots(req, n, cached_blocks or None,
-                                                    lookahead=self.num_spec_tokens)
+                                                    lookahead=self.num_spec_tokens + self.lookahead_extra)
                 if new_blocks is None:
                     if not req.block_ids:
                         req.num_computed_tokens = 0

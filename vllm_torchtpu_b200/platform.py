@@ -99,7 +99,7 @@ class B200Platform:
     supported_kv_cache_dtypes = ("auto", "bfloat16", "fp8", "fp8_e4m3")
     supported_connectors = ("B200P2PConnector", "B200HostConnector", "B200MultiConnector",
                             "B200OffloadingConnector", "DecodeBenchConnector")
-    supported_spec_methods = ("ngram", "suffix", "medusa", "eagle", "eagle3", "mtp", "dflash", "dspark")
+    supported_spec_methods = ("ngram", "suffix", "medusa", "eagle", "eagle3", "mtp", "dflash", "dspark", "toy_head")
 
     # ---- device facts ---------------------------------------------------
     @classmethod
@@ -235,12 +235,12 @@ class B200Platform:
                 s.async_scheduling = False
             if s.async_scheduling and method in ("ngram", "suffix"):
                 raise ValueError("async scheduling is only supported with eagle-family drafters")
-            if s.async_scheduling and method in ("mtp", "eagle", "eagle3"):
+            if s.async_scheduling and method in ("mtp", "eagle", "eagle3", "dflash", "dspark"):
                 # the draft layer catches up on a step's rows and drafts from its tokens before the next
                 # step is scheduled
                 logger.info("speculative method %s: async scheduling switched off", method)
                 s.async_scheduling = False
-            if method in ("mtp", "eagle", "eagle3") and p.decode_context_parallel_size > 1:
+            if method in ("mtp", "eagle", "eagle3", "dflash", "dspark") and p.decode_context_parallel_size > 1:
                 raise ValueError("draft layers are not built for decode context parallelism")
         if cfg.kv_transfer:
             name = cfg.kv_transfer.get("kv_connector")

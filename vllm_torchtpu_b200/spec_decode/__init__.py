@@ -4,13 +4,14 @@ and a rejection sampler decides how many are kept.
 Drafters: ``ngram`` (prompt lookup), ``suffix`` (longest-suffix match over prompt + output), ``medusa``
 (K residual-block heads on the target's hidden state, loaded from a checkpoint and run batched on the
 device), ``mtp`` / ``eagle`` / ``eagle3`` (one transformer layer with attention and its own KV cache behind
-the target's block tables, ``draft_layer.py``).  ``dflash`` / ``dspark`` select a toy stand-in: a random
-one-matrix recurrent head that accepts next to nothing and exists to exercise the hidden-state hand-off.
+the target's block tables, ``draft_layer.py``), ``dflash`` / ``dspark`` (parallel block drafting: context keys and
+values from the target's hidden states, all k drafts from one non-causal block pass, ``dflash.py``).  ``toy_head`` is
+a random one-matrix recurrent head that accepts next to nothing and exists to exercise the hidden-state hand-off.
 (reference: src/vllm_torchtpu/spec_decode/, docs/user_guide/speculative_decoding.md:5-16)"""
 from __future__ import annotations
 
 
-DRAFT_LAYER_METHODS = ("mtp", "eagle", "eagle3")      # drafters that keep a KV cache of their own
+DRAFT_LAYER_METHODS = ("mtp", "eagle", "eagle3", "dflash", "dspark")      # drafters that keep KV caches of their own
 
 
 def create_proposer(cfg, runner):
@@ -24,10 +25,14 @@ def create_proposer(cfg, runner):
     if method == "medusa":
         from .medusa import MedusaProposer
         return MedusaProposer(cfg, runner, k, sc.get("model"), int(sc.get("num_hidden_layers", 1)))
+    if method in ("dflash", "dspark"):
+        from .dflash import DFlashProposer
+        return DFlashProposer(cfg, runner, k, method, sc.get("model"), int(sc.get("num_hidden_layers", 1)),
+                              sc.get("mask_token_id"))
     if method in DRAFT_LAYER_METHODS:
         from .draft_layer import DraftLayerProposer
         return DraftLayerProposer(cfg, runner, k, method, sc.get("model"))
-    if method in ("dflash", "dspark"):
+    if method == "toy_head":
         from .draft_head import DraftHeadProposer
         return DraftHeadProposer(cfg, runner, k, method)
     raise ValueError(f"unknown speculative method {method!r}")
