@@ -194,3 +194,20 @@ def test_docs_list_every_environment_variable_and_guided_choice_maps_to_a_regex(
     rx = re.compile(spec["regex"])
     assert all(rx.fullmatch(s) for s in ("yes", "no way", "a.b")) and not rx.fullmatch("axb")
     assert _structured_spec({"response_format": {"type": "json_object"}}) == {"json_object": True}
+
+
+def test_example_scripts_run_on_cpu():
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for name in ("offline_inference", "offline_lora_inference", "multi_modal_inference"):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(root, "examples", name + ".py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        out = mod.main(["--device", "cpu", "--model", "tiny-llama"])
+        assert out
+    spec = importlib.util.spec_from_file_location("oi", os.path.join(root, "examples", "offline_inference.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    outs = mod.main(["--device", "cpu", "--speculative-config", '{"method": "ngram", "num_speculative_tokens": 2}'])
+    assert len(outs) == 2

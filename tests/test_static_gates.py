@@ -7,7 +7,7 @@ SRC_EXT = (".py", ".cu", ".cuh", ".h", ".cpp")
 
 
 def _sources():
-    for top in ("vllm_torchtpu_b200", "tests", "benchmarks"):
+    for top in ("vllm_torchtpu_b200", "tests", "benchmarks", "examples"):
         for d, _, files in os.walk(os.path.join(ROOT, top)):
             if "__pycache__" in d or os.sep + "build" in d:
                 continue
