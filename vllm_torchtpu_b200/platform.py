@@ -99,7 +99,7 @@ class B200Platform:
     supported_kv_cache_dtypes = ("auto", "bfloat16", "fp8", "fp8_e4m3")
     supported_connectors = ("B200P2PConnector", "B200HostConnector", "B200MultiConnector",
                             "B200OffloadingConnector", "DecodeBenchConnector")
-    supported_spec_methods = ("ngram", "suffix", "medusa", "eagle", "eagle3", "mtp", "dflash", "dspark", "toy_head")
+    supported_spec_methods = ("ngram", "suffix", "medusa", "eagle", "eagle3", "mtp", "dflash", "dspark")
 
     # ---- device facts ---------------------------------------------------
     @classmethod

@@ -5,8 +5,7 @@ Drafters: ``ngram`` (prompt lookup), ``suffix`` (longest-suffix match over promp
 (K residual-block heads on the target's hidden state, loaded from a checkpoint and run batched on the
 device), ``mtp`` / ``eagle`` / ``eagle3`` (one transformer layer with attention and its own KV cache behind
 the target's block tables, ``draft_layer.py``), ``dflash`` / ``dspark`` (parallel block drafting: context keys and
-values from the target's hidden states, all k drafts from one non-causal block pass, ``dflash.py``).  ``toy_head`` is
-a random one-matrix recurrent head that accepts next to nothing and exists to exercise the hidden-state hand-off.
+values from the target's hidden states, all k drafts from one non-causal block pass, ``dflash.py``).
 (reference: src/vllm_torchtpu/spec_decode/, docs/user_guide/speculative_decoding.md:5-16)"""
 from __future__ import annotations
 
@@ -32,7 +31,4 @@ def create_proposer(cfg, runner):
     if method in DRAFT_LAYER_METHODS:
         from .draft_layer import DraftLayerProposer
         return DraftLayerProposer(cfg, runner, k, method, sc.get("model"))
-    if method == "toy_head":
-        from .draft_head import DraftHeadProposer
-        return DraftHeadProposer(cfg, runner, k, method)
     raise ValueError(f"unknown speculative method {method!r}")
