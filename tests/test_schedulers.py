@@ -158,3 +158,59 @@ def test_pp_chunk_policies():
     s.add_request(req(0, 1000))
     out = s.schedule()
     assert out.scheduled[0].num_new_tokens == 256      # lone prompt spread over 4 stages
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("caching,spec", [(False, 0), (True, 0), (True, 3), (False, 2)])
+def test_scheduler_randomised_run_keeps_the_block_pool_consistent(seed, caching, spec):
+    """Random arrivals (shared prefixes), aborts, speculative tokens with random acceptance and a pool small
+    enough to force preemption: after every step the reference counts equal the holders, no free block is
+    held by a request, the token budget and the sequence limit are respected, and at the end every block is
+    free and every request finished once."""
+    import random
+    rng = random.Random(1000 * seed + 17 * spec + caching)
+    s = mk(blocks=14, max_seqs=5, budget=48, caching=caching, num_spec_tokens=spec)
+    pool = s.kv.pool
+    finished, submitted, next_id = [], {}, 0
+    prefixes = [[rng.randrange(50) for _ in range(32)] for _ in range(3)]
+    for step in range(3000):
+        if step < 150 and rng.random() < 0.35:
+            p = list(rng.choice(prefixes))[:rng.choice([0, 16, 32])] + [rng.randrange(1000) for _ in range(rng.randrange(1, 40))]
+            r = Request(f"r{next_id}", p, SamplingParams(max_tokens=rng.randrange(1, 40), ignore_eos=True))
+            submitted[r.request_id] = r
+            s.add_request(r)
+            next_id += 1
+        if submitted and rng.random() < 0.03:
+            s.abort_request(rng.choice(list(submitted)))
+        if not s.has_unfinished():
+            if step >= 150:
+                break
+            continue
+        out = s.schedule()
+        assert sum(x.num_new_tokens for x in out.scheduled) <= 48 and len(s.running) <= 5
+        sampled, spec_next = {}, {}
+        for x in out.scheduled:
+            if not x.samples:
+                continue
+            k = len(x.spec_token_ids)
+            acc = rng.randrange(0, k + 1)                       # accepted drafts, then the sampled token
+            sampled[x.request.request_id] = list(x.spec_token_ids[:acc]) + [rng.randrange(1000)]
+            if spec and rng.random() < 0.7:
+                spec_next[x.request.request_id] = [rng.randrange(1000) for _ in range(rng.randrange(1, spec + 1))]
+        finished += [r.request_id for r in s.update_from_output(out, sampled, spec_next or None)]
+        # invariants of the pool
+        holders = {}
+        for r in list(s.running) + list(s.waiting):
+            for b in r.block_ids:
+                holders[b] = holders.get(b, 0) + 1
+        for blk in pool.blocks[1:]:
+            assert blk.ref_cnt == holders.get(blk.block_id, 0), (step, blk.block_id, blk.ref_cnt, holders.get(blk.block_id))
+            assert (blk.ref_cnt == 0) == (blk.block_id in pool.free)
+        for r in s.running:
+            assert len(r.block_ids) * 16 >= r.num_computed_tokens
+    assert not s.has_unfinished()
+    assert pool.num_free_blocks == pool.num_blocks - 1
+    assert len(finished) == len(set(finished))
+    assert s.stats["preemptions"] > 0                 # the pool is small enough to force recomputation
+    done_or_aborted = {rid for rid, r in submitted.items() if r.status.finished}
+    assert done_or_aborted == set(submitted)
