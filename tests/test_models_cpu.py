@@ -279,3 +279,13 @@ def test_state_rollback_equals_running_only_the_accepted_rows():
     layer.forward(x[rows], want, meta([0, 1, 3, 6], [10, 22, 17], slots))
     for got_pool, want_pool in zip(cache, want):
         torch.testing.assert_close(got_pool, want_pool, rtol=1e-5, atol=1e-6)
+
+
+def test_checkpoint_features_without_kernels_are_refused():
+    from vllm_torchtpu_b200.config import ModelConfig
+    base = _hf_cfg("Qwen3NextForCausalLM", num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128)
+    ModelConfig.from_hf_dict(base)
+    for extra, word in (({"partial_rotary_factor": 0.25}, "partial_rotary"), ({"attn_output_gate": True}, "output_gate"),
+                        ({"head_dim": 256}, "head_dim")):
+        with pytest.raises(ValueError, match=word):
+            ModelConfig.from_hf_dict({**base, **extra})

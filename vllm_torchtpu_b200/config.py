@@ -255,6 +255,14 @@ class ModelConfig:
             mc.index_head_dim = cfg.get("index_head_dim", 0)
         else:
             raise ValueError(f"unsupported architecture {arch}")
+        # features of real checkpoints that the kernels here do not cover are refused, not ignored
+        prf = cfg.get("partial_rotary_factor", (cfg.get("rope_parameters") or {}).get("partial_rotary_factor", 1.0))
+        if prf not in (None, 1, 1.0):
+            raise ValueError(f"partial_rotary_factor {prf}: rotary embeddings over a part of the head are not built")
+        if cfg.get("attn_output_gate"):
+            raise ValueError("attn_output_gate (gated attention output) is not built")
+        if mc.architecture != "deepseek_v3" and mc.head_dim not in (64, 128):
+            raise ValueError(f"head_dim {mc.head_dim}: the attention kernels are built for 64 and 128")
         q = cfg.get("quantization_config")
         if q:
             method = q.get("quant_method")
