@@ -198,6 +198,31 @@ def test_moe_engine_with_padded_decode_buckets_on_gpu():
     assert cuda.check_status() == 0
 
 
+@pytest.mark.parametrize("quant", [None, "mxfp4"])
+def test_gpt_oss_shape_on_gpu(quant):
+    """GPT-OSS shape on the device: 64-wide heads with sinks, window and full layers in alternation, YaRN, biased
+    router and experts with the OAI SwiGLU, a hidden size below the padded down projection; bf16 experts and mxfp4
+    experts on the W4A16 kernel.  Batched chunked prefill repeats one-at-a-time serving."""
+    from vllm_torchtpu_b200.config import model_preset
+    cfg = model_preset("tiny-gpt-oss")
+    cfg.dtype, cfg.quantization = torch.bfloat16, quant
+    if quant:
+        cfg.quant_ignored = ("self_attn",)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    mk = lambda mbt: LLM(cfg, device="cuda", max_num_seqs=8, max_num_batched_tokens=mbt,
+                         num_gpu_blocks_override=256, init_dist=False)
+    rng = np.random.RandomState(1)
+    prompts = [rng.randint(0, 1000, size=n).tolist() for n in (8, 17, 40, 64)]
+    one = mk(256)
+    want = [one.generate([p], sp)[0].outputs[0].token_ids for p in prompts]
+    if quant:
+        assert one.engine.runner.model.layers[0].mlp.experts.w13.dtype == torch.uint8
+    got = [o.outputs[0].token_ids for o in mk(32).generate(prompts, sp)]
+    assert sum(int(a == b) for a, b in zip(got, want)) >= len(prompts) - 1, (got, want)
+    from vllm_torchtpu_b200.ops import cuda
+    assert cuda.check_status() == 0
+
+
 def test_logprobs_min_tokens_prompt_logprobs_on_gpu():
     """The logprob kernel, the min_tokens mask and chunked prompt logprobs on the device path (these
     steps leave the CUDA graphs), against the dense fp32 forward."""

@@ -289,3 +289,117 @@ def test_checkpoint_features_without_kernels_are_refused():
                         ({"head_dim": 256}, "head_dim")):
         with pytest.raises(ValueError, match=word):
             ModelConfig.from_hf_dict({**base, **extra})
+
+
+def _gpt_oss_hf_cfg(**kw):
+    d = {"architectures": ["GptOssForCausalLM"], "num_hidden_layers": 4, "hidden_size": 192, "num_attention_heads": 4,
+         "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 128, "vocab_size": 1024, "rms_norm_eps": 1e-5,
+         "rope_theta": 150000.0, "max_position_embeddings": 256, "torch_dtype": "float32", "num_local_experts": 8,
+         "num_experts_per_tok": 2, "sliding_window": 8, "swiglu_limit": 7.0, "attention_bias": True,
+         "layer_types": ["sliding_attention", "full_attention"] * 2,
+         "rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64,
+                          "beta_fast": 32.0, "beta_slow": 1.0, "truncate": False}}
+    d.update(kw)
+    return d
+
+
+def _gpt_oss_tensors(model, packed: bool):
+    """The model's parameters under the published GPT-OSS names and layouts (expert stacks input-major with gate
+    and up interleaved; ``packed``: experts as mxfp4 blocks + scales)."""
+    from vllm_torchtpu_b200.quantization.fp4 import quantize_mxfp4
+    cfg = model.cfg
+    D, H = cfg.head_dim, cfg.hidden_size
+    out = {"model.embed_tokens.weight": model.embed, "model.norm.weight": model.norm, "lm_head.weight": model.lm_head}
+
+    def interleave(gate, up):                       # rows: gate_0, up_0, gate_1, up_1, ...
+        return torch.stack([gate, up], 1).flatten(0, 1)
+    for i, l in enumerate(model.layers):
+        pre = f"model.layers.{i}."
+        a = l.self_attn
+        sizes = [cfg.num_q_heads * D, cfg.num_kv_heads * D, cfg.num_kv_heads * D]
+        for nme, w, b in zip("qkv", a.qkv.weight.split(sizes, 0), a.qkv.bias.split(sizes, 0)):
+            out[pre + f"self_attn.{nme}_proj.weight"], out[pre + f"self_attn.{nme}_proj.bias"] = w, b
+        out[pre + "self_attn.o_proj.weight"], out[pre + "self_attn.o_proj.bias"] = a.o.weight, a.o.bias
+        out[pre + "self_attn.sinks"] = l.sinks
+        out[pre + "input_layernorm.weight"], out[pre + "post_attention_layernorm.weight"] = l.input_ln, l.post_ln
+        moe = l.mlp.experts
+        out[pre + "mlp.router.weight"], out[pre + "mlp.router.bias"] = moe.gate.weight, moe.gate.bias
+        I = moe.intermediate_size
+        w13 = torch.stack([interleave(moe.w13[e, :I], moe.w13[e, I:]) for e in range(moe.num_experts)])   # [E, 2I, H]
+        w2 = moe.w2[:, :H]                                                                            # [E, H, I]
+        out[pre + "mlp.experts.gate_up_proj_bias"] = torch.stack(
+            [interleave(moe.b13[e, :I], moe.b13[e, I:]) for e in range(moe.num_experts)])
+        out[pre + "mlp.experts.down_proj_bias"] = moe.b2[:, :H]
+        if packed:
+            q13 = [quantize_mxfp4(w13[e].float()) for e in range(moe.num_experts)]
+            q2 = [quantize_mxfp4(w2[e].float()) for e in range(moe.num_experts)]
+            out[pre + "mlp.experts.gate_up_proj_blocks"] = torch.stack([q for q, _ in q13]).unflatten(-1, (-1, 16))
+            out[pre + "mlp.experts.gate_up_proj_scales"] = torch.stack([s for _, s in q13])
+            out[pre + "mlp.experts.down_proj_blocks"] = torch.stack([q for q, _ in q2]).unflatten(-1, (-1, 16))
+            out[pre + "mlp.experts.down_proj_scales"] = torch.stack([s for _, s in q2])
+        else:
+            out[pre + "mlp.experts.gate_up_proj"] = w13.transpose(1, 2)          # [E, H, 2I]
+            out[pre + "mlp.experts.down_proj"] = w2.transpose(1, 2)              # [E, I, H]
+    return {k: v.detach().clone().contiguous() for k, v in out.items()}
+
+
+def test_gpt_oss_engine_and_checkpoint_layouts(tmp_path):
+    """GPT-OSS shape: sinks, alternating window / full layers, biased router and experts, OAI SwiGLU, a hidden
+    size that is no multiple of the kernels' tile.  Chunked prefill with batching keeps the greedy tokens; the
+    published checkpoint layout (bf16 and mxfp4 expert stacks) loads back into the same model."""
+    import json
+    from safetensors.torch import save_file
+    from vllm_torchtpu_b200.config import ModelConfig
+    from vllm_torchtpu_b200.quantization.fp4 import dequantize_mxfp4
+    prompts = [np.random.RandomState(3).randint(0, 1000, size=n).tolist() for n in (9, 40, 23)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    kw = dict(device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    src = LLM("tiny-gpt-oss", max_num_batched_tokens=256, **kw)
+    want = [src.generate([p], sp)[0].outputs[0].token_ids for p in prompts]
+    many = LLM("tiny-gpt-oss", max_num_batched_tokens=16, **kw)
+    assert [o.outputs[0].token_ids for o in many.generate(prompts, sp)] == want
+    model = src.engine.runner.model
+    assert [l.self_attn.attn.sliding_window for l in model.layers] == [8, None, 8, None]
+    assert model.layers[0].mlp.experts.w2.shape[1] == 256 and model.layers[0].self_attn.attn.sinks is model.layers[0].sinks
+    mc = ModelConfig.from_hf_dict(_gpt_oss_hf_cfg())
+    assert mc.architecture == "gpt_oss" and mc.moe_bias and mc.hidden_act.startswith("swigluoai") \
+        and mc.layer_sliding == (True, False, True, False) and mc.quant_ignored == ("self_attn",)
+    # the experts' bias and activation against the definition, one token
+    moe = model.layers[1].mlp.experts
+    x = torch.randn(1, 192) * 0.5
+    ids, w = moe.route(x)
+    got = moe.method.apply(moe, x, ids, w)[0]
+    ref_out = torch.zeros(192)
+    I = moe.intermediate_size
+    for j in range(2):
+        e = int(ids[0, j])
+        h = x[0] @ moe.w13[e].t() + moe.b13[e]
+        g, u = h[:I].clamp(max=7.0), h[I:].clamp(-7.0, 7.0)
+        act = (u + 1) * g * torch.sigmoid(1.702 * g)
+        ref_out += w[0, j] * (act @ moe.w2[e, :192].t() + moe.b2[e, :192])
+    torch.testing.assert_close(got, ref_out, rtol=1e-4, atol=1e-4)
+    # bf16 checkpoint in the published layout
+    d = tmp_path / "bf16"
+    d.mkdir()
+    save_file(_gpt_oss_tensors(model, packed=False), str(d / "model.safetensors"))
+    json.dump(_gpt_oss_hf_cfg(), open(d / "config.json", "w"))
+    dst = LLM(str(d), dtype="float32", **kw)
+    assert [dst.generate([p], sp)[0].outputs[0].token_ids for p in prompts] == want
+    torch.testing.assert_close(dst.engine.runner.model.layers[2].sinks, model.layers[2].sinks)
+    # mxfp4 expert stacks stay packed; attention stays unquantised
+    d4 = tmp_path / "mxfp4"
+    d4.mkdir()
+    t4 = _gpt_oss_tensors(model, packed=True)
+    save_file(t4, str(d4 / "model.safetensors"))
+    json.dump(_gpt_oss_hf_cfg(quantization_config={"quant_method": "mxfp4"}), open(d4 / "config.json", "w"))
+    q = LLM(str(d4), dtype="float32", **kw)
+    qm = q.engine.runner.model
+    e4 = qm.layers[0].mlp.experts
+    assert e4.w13.dtype == torch.uint8 and qm.layers[0].self_attn.qkv.weight.dtype == torch.float32
+    blocks = t4["model.layers.0.mlp.experts.gate_up_proj_blocks"][3].flatten(-2)
+    torch.testing.assert_close(e4.w13[3], torch.cat([blocks[0::2], blocks[1::2]], 0))
+    I = e4.intermediate_size
+    torch.testing.assert_close(dequantize_mxfp4(e4.w13[3], e4.w13_scale[3])[:I].float(),
+                               dequantize_mxfp4(*[t.contiguous() for t in (blocks[0::2], t4["model.layers.0.mlp.experts.gate_up_proj_scales"][3][0::2])]).float())
+    outs = q.generate(prompts, sp)
+    assert all(len(o.outputs[0].token_ids) == 8 for o in outs)

@@ -105,3 +105,41 @@ def test_route_post_kernel_matches_reference(sim):
     assert not y[50:].float().abs().sum().item() and cu().check_status() == 0
     want = ref.moe_experts(x, w13, w2, got_ids, got_w, 0)
     assert (y.float() - want.float()).abs().max().item() <= 3e-2 * want.float().abs().max().item() + 2e-2
+
+
+@pytest.mark.parametrize("packed", [False, True])
+def test_experts_with_biases_oai_swiglu_and_padded_hidden(packed):
+    """GPT-OSS style experts on the device: expert biases through the grouped bias kernel, the OAI SwiGLU kernel,
+    a hidden size (192) below the down projection's padded 256 rows; bf16 experts and packed mxfp4 experts."""
+    cu()                                             # the kernel module first: it pulls in its sub-modules itself
+    from vllm_torchtpu_b200.ops import cuda_fp4
+    from vllm_torchtpu_b200.ops import reference as ref
+    from vllm_torchtpu_b200.quantization.fp4 import dequantize_mxfp4, quantize_mxfp4
+    g = torch.Generator(device=DEV).manual_seed(2)
+    T, H, Hp, I, E, k = 45, 192, 256, 128, 8, 2
+    x = torch.randn(T, H, device=DEV, generator=g).bfloat16()
+    w13 = (torch.randn(E, 2 * I, H, device=DEV, generator=g) * 0.08).bfloat16()
+    w2 = torch.zeros(E, Hp, I, device=DEV, dtype=torch.bfloat16)
+    w2[:, :H] = (torch.randn(E, H, I, device=DEV, generator=g) * 0.08).bfloat16()
+    b13 = (torch.randn(E, 2 * I, device=DEV, generator=g) * 0.1).bfloat16()
+    b2 = torch.zeros(E, Hp, device=DEV, dtype=torch.bfloat16)
+    b2[:, :H] = (torch.randn(E, H, device=DEV, generator=g) * 0.1).bfloat16()
+    logits = torch.randn(T, E, device=DEV, generator=g)
+    wt, ids = torch.topk(torch.softmax(logits, -1), k, -1)
+    ids, wt = ids.int().contiguous(), wt.float().contiguous()
+    act = "swigluoai:1.702:7.0"
+    if packed:
+        q13 = [quantize_mxfp4(w13[e].float()) for e in range(E)]
+        q2 = [quantize_mxfp4(w2[e].float()) for e in range(E)]
+        w13q, s13 = torch.stack([a for a, _ in q13]), torch.stack([b for _, b in q13])
+        w2q, s2 = torch.stack([a for a, _ in q2]), torch.stack([b for _, b in q2])
+        got = cuda_fp4.moe_experts_w4a16(x, w13q, s13, w2q, s2, ids, wt, 0, "mxfp4", act=act, b13=b13, b2=b2)
+        w13 = torch.stack([dequantize_mxfp4(w13q[e], s13[e]) for e in range(E)]).bfloat16()
+        w2 = torch.stack([dequantize_mxfp4(w2q[e], s2[e]) for e in range(E)]).bfloat16()
+    else:
+        got = cu().moe_experts(x, w13, w2, ids, wt, 0, act=act, b13=b13, b2=b2)
+    torch.cuda.synchronize()
+    assert got.shape == (T, H) and cu().check_status() == 0
+    want = ref.moe_experts(x, w13, w2, ids, wt, 0, act=act, b13=b13, b2=b2)
+    err = (got.float() - want.float()).abs().max().item()
+    assert err <= 3e-2 * want.float().abs().max().item() + 2e-2, err

@@ -49,6 +49,10 @@ class ModelConfig:
     tie_word_embeddings: bool = False
     qk_norm: bool = False                # Qwen3 per-head RMSNorm on q and k
     attention_bias: bool = False         # Qwen2 qkv bias
+    attention_out_bias: bool = False     # GPT-OSS: bias on the output projection too
+    layer_sliding: tuple = ()            # per layer: sliding-window attention (True) or full attention; () = all alike
+    moe_bias: bool = False               # router and expert biases (GPT-OSS)
+    quant_ignored: tuple = ()            # substrings of layer names that stay unquantised besides lm_head / embed / router
     sliding_window: Optional[int] = None
     logit_softcap: Optional[float] = None
     attn_sinks: bool = False
@@ -175,6 +179,18 @@ class ModelConfig:
             mc.num_experts_per_tok = cfg["num_experts_per_tok"]
             mc.moe_intermediate_size = cfg["intermediate_size"]
             mc.moe_renormalize = True
+        elif arch.startswith("GptOss"):
+            mc.architecture = "gpt_oss"
+            mc.attention_bias = mc.attention_out_bias = bool(cfg.get("attention_bias", True))
+            mc.num_experts = cfg["num_local_experts"]
+            mc.num_experts_per_tok = cfg.get("num_experts_per_tok", cfg.get("experts_per_token", 4))
+            mc.moe_intermediate_size = cfg["intermediate_size"]
+            mc.moe_renormalize, mc.moe_scoring, mc.moe_bias = True, "softmax", True
+            mc.hidden_act = f"swigluoai:1.702:{float(cfg.get('swiglu_limit', 7.0))}"
+            types = cfg.get("layer_types") or ["sliding_attention", "full_attention"]
+            mc.layer_sliding = tuple(t == "sliding_attention" for t in types)
+            mc.sliding_window = cfg.get("sliding_window", 128)
+            mc.quant_ignored = ("self_attn",)           # only the experts are mxfp4 in the published checkpoints
         elif arch.startswith("Qwen2Moe"):
             mc.architecture, mc.attention_bias = "qwen3_moe", True
             mc.num_experts = cfg["num_experts"]
@@ -296,6 +312,17 @@ def model_preset(name: str) -> ModelConfig:
     if n in ("tiny-moe",):
         return _preset(name="tiny-moe", architecture="qwen3_moe", qk_norm=True, dtype=torch.float32,
                        num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, max_model_len=256)
+    if n in ("tiny-gpt-oss",):
+        # GPT-OSS shape in small: sinks, alternating 8-token window / full attention, biases everywhere, OAI SwiGLU;
+        # hidden 192 is not a multiple of 128 (like 2880), so the padded down projection is exercised
+        return _preset(name="tiny-gpt-oss", architecture="gpt_oss", dtype=torch.float32, num_layers=4,
+                       hidden_size=192, num_q_heads=4, num_kv_heads=2, head_dim=64, vocab_size=1024,
+                       intermediate_size=128, max_model_len=256, num_experts=8, num_experts_per_tok=2,
+                       moe_intermediate_size=128, moe_bias=True, attention_bias=True, attention_out_bias=True,
+                       hidden_act="swigluoai:1.702:7.0", sliding_window=8, layer_sliding=(True, False),
+                       rope_theta=150000.0,
+                       rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64,
+                                     "beta_fast": 32.0, "beta_slow": 1.0, "truncate": False})
     if n in ("tiny-mla",):
         return _preset(name="tiny-mla", architecture="deepseek_v3", dtype=torch.float32, num_layers=3,
                        num_q_heads=4, num_kv_heads=4, head_dim=48, first_dense_layers=1,

@@ -221,9 +221,48 @@ __global__ void moe_route_post_kernel(int* __restrict__ ids, float* __restrict__
     w[i] = 1.f / (float)k;
   }
 }
+// y[r, :] += bias[e, :] for the rows r of expert e (rows grouped by expert: group_off[e] <= r < group_off[e + 1]);
+// expert biases of MoE blocks whose experts carry them (in front of the activation and behind the down projection).
+__global__ void group_bias_add_kernel(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ bias,
+                                      const int* __restrict__ group_off, int R, int N, int ldy, int E) {
+  for (int r = blockIdx.x; r < R; r += gridDim.x) {
+    if (r >= group_off[E]) break;                   // rows behind the last group are padding
+    int lo = 0, hi = E;                             // largest e with group_off[e] <= r
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (group_off[mid] <= r) lo = mid; else hi = mid;
+    }
+    const bf16x8* b = reinterpret_cast<const bf16x8*>(bias + (size_t)lo * N);
+    bf16x8* row = reinterpret_cast<bf16x8*>(y + (size_t)r * ldy);
+    for (int i = threadIdx.x; i < (N >> 3); i += blockDim.x) {
+      bf16x8 v = row[i];
+      const bf16x8 w = b[i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(v.v[j]), c = __bfloat1622float2(w.v[j]);
+        v.v[j] = __floats2bfloat162_rn(a.x + c.x, a.y + c.y);
+      }
+      row[i] = v;
+    }
+  }
+}
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_group_bias_add(void* y, const void* bias, const int* group_off, int R, int N, int ldy, int E,
+                                   cudaStream_t stream) {
+  if (R <= 0 || N <= 0 || E <= 0) return 0;
+  if (N % 8 || ldy % 8) {
+    b200_set_last_error("group_bias_add: width and row stride must be multiples of 8", __FILE__, __LINE__);
+    return -1;
+  }
+  const int blocks = R < 148 * 8 ? R : 148 * 8;
+  group_bias_add_kernel<<<blocks, 128, 0, stream>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)bias, group_off, R, N,
+                                                    ldy, E);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int b200_moe_route_post(int* ids, float* w, int T, int k, int E, const int* num_valid, int sim,
                                    cudaStream_t stream) {

@@ -71,18 +71,49 @@ class FusedMoE:
         self.num_local_experts = self.num_experts // self.ep_size
         lo = self.ep_rank * self.num_local_experts
         self.expert_range = (lo, lo + self.num_local_experts)
+        self.has_bias = bool(getattr(cfg, "moe_bias", False))      # router and expert biases (GPT-OSS)
         self.gate = ReplicatedLinear(f"{name}.gate", cfg.hidden_size, cfg.num_experts, dtype=cfg.dtype,
-                                     device=device, quant_config=None)
+                                     device=device, quant_config=None, bias=self.has_bias)
+        self.b13 = self.b2 = None
         self.score_bias = None
         if cfg.moe_score_bias:
             self.score_bias = torch.zeros(cfg.num_experts, dtype=torch.float32, device=device)
         self.method = get_moe_method(quant_config, name)
         self.method.create_weights(self)
 
+    def alloc_biases(self) -> None:
+        from ..quantization.unquantized import padded_hidden
+        E, I = self.num_local_experts, self.intermediate_size
+        self.b13 = torch.zeros(E, 2 * I, dtype=self.dtype, device=self.device)
+        self.b2 = torch.zeros(E, padded_hidden(self), dtype=self.dtype, device=self.device)
+
+    def load_expert_bias(self, local_e: int, gate_b, up_b, down_b) -> None:
+        """Unsharded bias vectors of one expert (gate [I_full], up [I_full], down [H]); under tensor parallelism
+        the gate / up slices follow the weight rows and the down bias is split evenly (the ranks' partial
+        outputs are summed)."""
+        if self.b13 is None:
+            self.alloc_biases()
+        I, r = self.intermediate_size, self.tp_rank
+        self.b13[local_e, :I] = gate_b[r * I:(r + 1) * I].to(self.b13.dtype)
+        self.b13[local_e, I:] = up_b[r * I:(r + 1) * I].to(self.b13.dtype)
+        self.b2[local_e, :self.hidden_size] = (down_b.float() / self.tp_size).to(self.b2.dtype)
+
     def init_dummy(self, std: float, seed: int) -> None:
         # router logits come from N(0,1) gate weights so that routing is well spread
         self.gate.init_dummy(1.0, seed)
         self.method.init_dummy(self, std, seed)
+        if self.has_bias:
+            from .linear import seeded_normal
+            self.alloc_biases()
+            I, H = self.intermediate_size, self.hidden_size
+            lo = self.expert_range[0]
+            for e in range(self.num_local_experts):
+                self.b13[e] = seeded_normal(f"{self.name}.experts.{lo + e}.b13", (2 * I,), 0.05, self.dtype,
+                                            self.device, seed)
+                self.b2[e, :H] = seeded_normal(f"{self.name}.experts.{lo + e}.b2", (H,), 0.05, self.dtype,
+                                               self.device, seed) / self.tp_size
+            self.gate.bias = seeded_normal(f"{self.name}.gate.bias", (self.num_experts,), 0.1, self.dtype,
+                                           self.device, seed)
         if self.score_bias is not None:
             from .linear import seeded_normal
             self.score_bias = seeded_normal(f"{self.name}.bias", (self.num_experts,), 0.01, torch.float32,

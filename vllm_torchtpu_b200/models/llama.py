@@ -136,7 +136,8 @@ class LlamaAttention:
                                      cfg.num_kv_heads, cfg.head_dim, unpadded_q=cfg.num_q_heads_unpadded,
                                      bias=cfg.attention_bias, **kw)
         self.o = OProjParallelLinear(f"{name}.o_proj", cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim,
-                                     cfg.hidden_size, unpadded_q=cfg.num_q_heads_unpadded, **kw)
+                                     cfg.hidden_size, unpadded_q=cfg.num_q_heads_unpadded,
+                                     bias=getattr(cfg, "attention_out_bias", False), **kw)
         self.q_norm_w = self.k_norm_w = None
         if cfg.qk_norm:
             self.q_norm_w = torch.ones(cfg.head_dim, dtype=cfg.dtype, device=device)
@@ -196,7 +197,8 @@ class LlamaForCausalLM:
         self.pp_first = st.pp.is_first
         self.pp_last = st.pp.is_last
         quant = QuantConfig(cfg.quantization, cfg.weight_block_size,
-                            ignored_layers=("lm_head", "embed", "gate.")) if cfg.quantization else None
+                            ignored_layers=("lm_head", "embed", "gate.") + tuple(getattr(cfg, "quant_ignored", ()))) \
+            if cfg.quantization else None
         lo, hi = layer_range if layer_range else (0, cfg.num_layers)
         self.layer_range = (lo, hi)
         self.layers = [self.layer_cls(i, cfg, device, quant) for i in range(lo, hi)]

@@ -103,12 +103,48 @@ _MIXTRAL_EXPERT = {"w1": "gate_proj", "w3": "up_proj", "w2": "down_proj"}
 def canonical_name(name: str) -> str:
     """Checkpoint name → the Llama / Qwen-MoE naming the loader walks: Mixtral keeps its experts under
     ``block_sparse_moe`` with ``w1 / w3 / w2`` for gate / up / down."""
+    if ".mlp.router." in name:                       # GPT-OSS names its router "router"
+        name = name.replace(".mlp.router.", ".mlp.gate.")
     if ".block_sparse_moe." in name:
         name = name.replace(".block_sparse_moe.", ".mlp.")
         m = re.match(r"^(.*\.experts\.\d+\.)(w[123])(\..+)$", name)
         if m:
             name = m.group(1) + _MIXTRAL_EXPERT[m.group(2)] + m.group(3)
     return name
+
+
+_OSS_EXPERT_TENSORS = ("gate_up_proj", "down_proj", "gate_up_proj_bias", "down_proj_bias", "gate_up_proj_blocks",
+                       "gate_up_proj_scales", "down_proj_blocks", "down_proj_scales")
+
+
+def _load_oss_experts(moe, parts: dict) -> None:
+    """GPT-OSS expert stacks.  bf16: ``gate_up_proj`` [E, H, 2I] and ``down_proj`` [E, I, H] (input-major);
+    mxfp4: ``*_blocks`` [E, rows, K / 32, 16] packed nibbles with ``*_scales`` [E, rows, K / 32].  Gate and up
+    alternate along the 2I axis (gate at the even positions) in weights and biases alike."""
+    from ..quantization.fp4 import Mxfp4MoEMethod, dequantize_mxfp4
+    lo, hi = moe.expert_range
+    if moe.w13 is None:
+        moe.method.alloc(moe)
+    packed = "gate_up_proj_blocks" in parts
+    for e in range(lo, hi):
+        if packed:
+            gu_q = parts["gate_up_proj_blocks"][e].flatten(-2)            # [2I, H / 2]
+            gu_s = parts["gate_up_proj_scales"][e]
+            d_q = parts["down_proj_blocks"][e].flatten(-2)                # [H, I / 2]
+            d_s = parts["down_proj_scales"][e]
+            w13_q, w13_s = torch.cat([gu_q[0::2], gu_q[1::2]], 0), torch.cat([gu_s[0::2], gu_s[1::2]], 0)
+            if isinstance(moe.method, Mxfp4MoEMethod) and moe.tp_size == 1:
+                moe.method.load_packed_expert(moe, e - lo, w13_q.contiguous(), w13_s.contiguous(), d_q, d_s)
+            else:
+                w13 = dequantize_mxfp4(w13_q.contiguous(), w13_s.contiguous())
+                I = w13.shape[0] // 2
+                moe.method.load_expert(moe, e - lo, w13[:I], w13[I:], dequantize_mxfp4(d_q.contiguous(), d_s.contiguous()))
+        else:
+            gu = parts["gate_up_proj"][e].t()                             # [2I, H]
+            moe.method.load_expert(moe, e - lo, gu[0::2], gu[1::2], parts["down_proj"][e].t())
+        if "gate_up_proj_bias" in parts:
+            b = parts["gate_up_proj_bias"][e]
+            moe.load_expert_bias(e - lo, b[0::2], b[1::2], parts["down_proj_bias"][e])
 
 
 def load_named_tensors(model, tensors, names: set, source: str = "memory") -> None:
@@ -217,6 +253,10 @@ def load_named_tensors(model, tensors, names: set, source: str = "memory") -> No
                 a.qkv.load_weight(t)                     # Phi-3: q, k, v rows already stacked in this order
             elif om and hasattr(a, "o"):
                 linear_piece(("o", li), a.o, {"o": ap + "o_proj"}, "o", om.group(1), t, ap + "o_proj")
+            elif sub == "o_proj.bias" and hasattr(a, "o"):
+                a.o.bias = t.to(device=a.o.device, dtype=a.o.dtype).contiguous()
+            elif sub == "sinks" and hasattr(layer, "load_sinks"):
+                layer.load_sinks(t)
             elif sub == "q_norm.weight" and a.q_norm_w is not None:
                 _set_vec(a.q_norm_w, t)
             elif sub == "k_norm.weight" and a.k_norm_w is not None:
@@ -257,6 +297,17 @@ def load_named_tensors(model, tensors, names: set, source: str = "memory") -> No
                 moe = mlp.experts
                 if sub == "gate.weight":
                     moe.gate.load_weight(t)
+                elif sub == "gate.bias":
+                    moe.gate.bias = t.to(device=moe.gate.device, dtype=moe.gate.dtype).contiguous()
+                elif sub.startswith("experts.") and sub[len("experts."):] in _OSS_EXPERT_TENSORS:
+                    # GPT-OSS: one tensor per projection for the whole expert stack (bf16 or mxfp4 blocks + scales)
+                    key = sub[len("experts."):]
+                    g = open_groups.get(("oss", li))
+                    if g is None:
+                        need = {k for k in _OSS_EXPERT_TENSORS if f"{mp}experts.{k}" in names}
+                        g = open_groups[("oss", li)] = _Collector(need, lambda parts, moe=moe: _load_oss_experts(moe, parts))
+                    if g.add(key, t):
+                        del open_groups[("oss", li)]
                 elif sub == "gate.e_score_correction_bias" and moe.score_bias is not None:
                     _set_vec(moe.score_bias, t)
                 elif sub == "shared_expert_gate.weight" and getattr(mlp, "shared_gate", None) is not None:

@@ -12,6 +12,9 @@ def get_model_class(cfg: ModelConfig):
     if a == "qwen3_moe":
         from .qwen3_moe import Qwen3MoeForCausalLM
         return Qwen3MoeForCausalLM
+    if a == "gpt_oss":
+        from .gpt_oss import GptOssForCausalLM
+        return GptOssForCausalLM
     if a == "deepseek_v3":
         from .deepseek_v3 import DeepseekV3ForCausalLM
         return DeepseekV3ForCausalLM
@@ -25,4 +28,4 @@ def get_model_class(cfg: ModelConfig):
 
 
 def supported_architectures() -> list[str]:
-    return ["llama", "qwen3_moe", "deepseek_v3", "qwen3_next", "kimi_linear"]
+    return ["llama", "qwen3_moe", "gpt_oss", "deepseek_v3", "qwen3_next", "kimi_linear"]

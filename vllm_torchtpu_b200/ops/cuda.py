@@ -716,12 +716,26 @@ def p2p_all_reduce(x, heap):
     return x
 
 
-from .cuda_moe import (EpState, gemm_swiglu, grouped_gemm, moe_experts, moe_experts_ep, moe_route_post,  # noqa: E402,F401
-                       moe_permute, moe_route, moe_unpermute)
-from .cuda_fp8 import (fp8_block_gemm, fp8_block_gemm_push, fp8_block_gemm_push_quantised,  # noqa: E402,F401
-                       fp8_block_gemm_quantised, fp8_per_tensor_gemm, fp8_rowwise_gemm, grouped_fp8_gemm, int8_gemm,  # noqa: E402,F401
-                       moe_experts_ep_fp8, moe_experts_fp8, quant_act_1x128, quant_act_int8, quant_rows_1x128)
-from .cuda_fp4 import grouped_w4a16_gemm, moe_experts_w4a16, w4a16_gemm  # noqa: E402,F401
-from .cuda_gdn import gdn_forward, kda_forward, short_conv  # noqa: E402,F401
-from .cuda_mla import (mla_absorb, mla_paged_attention, mla_unabsorb, mla_write_cache,  # noqa: E402,F401
-                       permute_rows, rope_rows)
+# Kernels of the sub-modules under this module's name (``cuda.moe_experts`` ...), resolved on first use: the
+# sub-modules import this module, so importing them here would make ``import ops.cuda_fp4`` depend on who came first.
+_SUBMODULE_EXPORTS = {
+    "cuda_moe": ("EpState", "gemm_swiglu", "group_bias_add", "grouped_gemm", "moe_experts", "moe_experts_ep",
+                 "moe_route_post", "moe_permute", "moe_route", "moe_unpermute"),
+    "cuda_fp8": ("fp8_block_gemm", "fp8_block_gemm_push", "fp8_block_gemm_push_quantised", "fp8_block_gemm_quantised",
+                 "fp8_per_tensor_gemm", "fp8_rowwise_gemm", "grouped_fp8_gemm", "int8_gemm", "moe_experts_ep_fp8",
+                 "moe_experts_fp8", "quant_act_1x128", "quant_act_int8", "quant_rows_1x128"),
+    "cuda_fp4": ("grouped_w4a16_gemm", "moe_experts_w4a16", "w4a16_gemm", "w4a16_int4_gemm", "dequant_w4", "dequant_int4"),
+    "cuda_gdn": ("gdn_forward", "kda_forward", "short_conv"),
+    "cuda_mla": ("mla_absorb", "mla_paged_attention", "mla_unabsorb", "mla_write_cache", "permute_rows", "rope_rows"),
+}
+_EXPORT_HOME = {name: mod for mod, names in _SUBMODULE_EXPORTS.items() for name in names}
+
+
+def __getattr__(name: str):
+    mod = _EXPORT_HOME.get(name)
+    if mod is None:
+        raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+    import importlib
+    value = getattr(importlib.import_module(f"{__package__}.{mod}"), name)
+    globals()[name] = value
+    return value

@@ -112,7 +112,7 @@ def grouped_w4a16_gemm(x_perm, w_packed, scales, group_off, avg_rows: int, fmt: 
 
 
 def moe_experts_w4a16(x, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, expert_offset: int, fmt: str = "mxfp4",
-                      act: str = "silu"):
+                      act: str = "silu", b13=None, b2=None):
     """4-bit experts: permute -> grouped W4A16 GEMM (gate | up) -> SiLU*mul -> grouped W4A16 GEMM -> un-permute."""
     from . import cuda_moe
     T, H = x.shape
@@ -121,6 +121,11 @@ def moe_experts_w4a16(x, w13, w13_scale, w2, w2_scale, topk_ids, topk_w, expert_
     x_perm, group_off, _, inv_pos = cuda_moe.moe_permute(x.contiguous(), topk_ids.contiguous(), expert_offset, E_local)
     avg = (T * k + E_local - 1) // E_local
     h = grouped_w4a16_gemm(x_perm, w13, w13_scale, group_off, avg, fmt)
+    if b13 is not None:
+        cuda_moe.group_bias_add(h, b13, group_off)
     a = _c.silu_and_mul(h) if act == "silu" else _c.gated_act_and_mul(h, act)
     y = grouped_w4a16_gemm(a, w2, w2_scale, group_off, avg, fmt)
-    return cuda_moe.moe_unpermute(y, inv_pos, topk_w.contiguous(), T)
+    if b2 is not None:
+        cuda_moe.group_bias_add(y, b2, group_off)
+    out = cuda_moe.moe_unpermute(y, inv_pos, topk_w.contiguous(), T)
+    return out if out.shape[1] == H else out[:, :H].contiguous()      # down projection padded to the tile width

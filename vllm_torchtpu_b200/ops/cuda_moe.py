@@ -106,7 +106,17 @@ def moe_unpermute(y, inv_pos, topk_w, T: int):
     return out
 
 
-def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0, act: str = "silu"):
+def group_bias_add(y, bias, group_off):
+    """In place: y[r] += bias[e] for the rows of expert e (rows grouped by expert through ``group_off``)."""
+    _c._require_bf16(y, bias)
+    R, N = y.shape
+    _c._check(_c.lib().b200_group_bias_add(_c._p(y), _c._p(bias), _c._p(group_off), c_int(R), c_int(N),
+                                           c_int(y.stride(0)), c_int(bias.shape[0]), _c._stream()), "group_bias_add")
+    count_launch()
+    return y
+
+
+def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0, act: str = "silu", b13=None, b2=None):
     """Σ_k w_k · FFN_e(x) over the local experts: permute → grouped SwiGLU GEMM → grouped GEMM →
     weighted un-permute.  w13: [E_local, 2I, H] (gate rows first), w2: [E_local, H, I]."""
     T, H = x.shape
@@ -114,13 +124,20 @@ def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0, act: str =
     k = topk_ids.shape[1]
     x_perm, group_off, _, inv_pos = moe_permute(x.contiguous(), topk_ids.contiguous(), expert_offset, E_local)
     avg = (T * k + E_local - 1) // E_local
-    if act == "silu":
+    if act == "silu" and b13 is None:
         h = grouped_gemm(x_perm, w13, group_off, True, avg)          # SiLU * mul in the GEMM epilogue
     else:
-        # other gated activations: one grouped GEMM over the stacked [gate; up] rows, then the activation kernel
-        h = _c.gated_act_and_mul(grouped_gemm(x_perm, w13, group_off, False, avg), act)
+        # other gated activations / expert biases: one grouped GEMM over the stacked [gate; up] rows, bias,
+        # then the activation kernel
+        h = grouped_gemm(x_perm, w13, group_off, False, avg)
+        if b13 is not None:
+            group_bias_add(h, b13, group_off)
+        h = _c.gated_act_and_mul(h, act)
     y = grouped_gemm(h, w2, group_off, False, avg)
-    return moe_unpermute(y, inv_pos, topk_w.contiguous(), T)
+    if b2 is not None:
+        group_bias_add(y, b2, group_off)
+    out = moe_unpermute(y, inv_pos, topk_w.contiguous(), T)
+    return out if out.shape[1] == H else out[:, :H].contiguous()      # down projection padded to the tile width
 
 
 # ----------------------------------------------------------------- expert parallel, fused plane

@@ -392,9 +392,10 @@ def moe_route_post(ids, w, num_experts: int, num_valid=None, sim: str = ""):
     return ids, w
 
 
-def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0, act: str = "silu"):
+def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0, act: str = "silu", b13=None, b2=None):
     """Σ_k w_k · FFN_e(x) over the experts this rank owns.  w13: [E_local, 2I, H] (gate rows first),
-    w2: [E_local, H, I]; ``act``: gated activation (``parse_gated_act``)."""
+    w2: [E_local, H, I] (rows beyond H, padding for the kernels' tile width, are ignored); ``act``: gated
+    activation (``parse_gated_act``); optional expert biases b13 [E_local, 2I], b2 [E_local, H]."""
     T, H = x.shape
     E_local = w13.shape[0]
     out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
@@ -406,8 +407,12 @@ def moe_experts(x, w13, w2, topk_ids, topk_w, expert_offset: int = 0, act: str =
             continue
         wt = (topk_w * sel).sum(-1)[rows]
         h = xf[rows] @ w13[e].float().t()
+        if b13 is not None:
+            h = (h.to(x.dtype).float() + b13[e].float())
         a = gated_act_and_mul(h, act).to(x.dtype).float()
-        y = (a @ w2[e].float().t()).to(x.dtype).float()
+        y = (a @ w2[e, :H].float().t()).to(x.dtype).float()
+        if b2 is not None:
+            y = (y + b2[e, :H].float()).to(x.dtype).float()
         out[rows] += y * wt[:, None]
     return out.to(x.dtype)
 

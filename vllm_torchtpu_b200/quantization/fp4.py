@@ -144,13 +144,20 @@ class Mxfp4MoEMethod:
                                                 moe.device, seed))
             c.append(q); d.append(s)
         moe.w13, moe.w13_scale, moe.w2, moe.w2_scale = map(torch.stack, (a, b, c, d))
+        from .unquantized import padded_hidden
+        if padded_hidden(moe) != H:          # zero rows up to the kernels' tile (e8m0 scale byte 0 = 2^-127)
+            extra = padded_hidden(moe) - H
+            moe.w2 = torch.nn.functional.pad(moe.w2, (0, 0, 0, extra)).contiguous()
+            moe.w2_scale = torch.nn.functional.pad(moe.w2_scale, (0, 0, 0, extra)).contiguous()
 
     def alloc(self, moe) -> None:
         E, I, H = moe.num_local_experts, moe.intermediate_size, moe.hidden_size
         moe.w13 = torch.zeros(E, 2 * I, H // 2, dtype=torch.uint8, device=moe.device)
-        moe.w2 = torch.zeros(E, H, I // 2, dtype=torch.uint8, device=moe.device)
+        from .unquantized import padded_hidden
+        Hp = padded_hidden(moe)
+        moe.w2 = torch.zeros(E, Hp, I // 2, dtype=torch.uint8, device=moe.device)
         moe.w13_scale = torch.zeros(E, 2 * I, H // 32, dtype=torch.uint8, device=moe.device)
-        moe.w2_scale = torch.zeros(E, H, I // 32, dtype=torch.uint8, device=moe.device)
+        moe.w2_scale = torch.zeros(E, Hp, I // 32, dtype=torch.uint8, device=moe.device)
 
     def load_expert(self, moe, local_e, gate, up, down, scales=(None, None, None)) -> None:
         """One expert from a bf16 (or block-scaled fp8) checkpoint, quantised to mxfp4 here."""
@@ -159,18 +166,29 @@ class Mxfp4MoEMethod:
         q, s = quantize_mxfp4(torch.cat([g, u], 0).to(moe.device).float())
         moe.w13[local_e], moe.w13_scale[local_e] = q, s
         q, s = quantize_mxfp4(d.to(moe.device).float())
-        moe.w2[local_e], moe.w2_scale[local_e] = q, s
+        moe.w2[local_e, :moe.hidden_size], moe.w2_scale[local_e, :moe.hidden_size] = q, s
+
+    def load_packed_expert(self, moe, local_e, w13_q, w13_s, w2_q, w2_s) -> None:
+        """One expert that is mxfp4 in the checkpoint already: packed nibbles [rows, K / 2] and e8m0 scales
+        [rows, K / 32], gate rows first in w13; stored as they are."""
+        if moe.tp_size != 1:
+            raise NotImplementedError("packed mxfp4 experts are loaded unsharded (expert parallelism or one rank)")
+        moe.w13[local_e], moe.w13_scale[local_e] = w13_q.to(moe.device), w13_s.to(moe.device)
+        moe.w2[local_e, :moe.hidden_size] = w2_q.to(moe.device)
+        moe.w2_scale[local_e, :moe.hidden_size] = w2_s.to(moe.device)
 
     def apply(self, moe, x, topk_ids, topk_w):
         I, H = moe.intermediate_size, moe.hidden_size
-        if x.is_cuda and x.dtype == torch.bfloat16 and H % 128 == 0 and I % 128 == 0:
+        kw = dict(act=moe.activation, b13=getattr(moe, "b13", None), b2=getattr(moe, "b2", None))
+        if x.is_cuda and x.dtype == torch.bfloat16 and H % 64 == 0 and I % 64 == 0:
+            # K of both GEMMs a multiple of 64; N = 2I a multiple of 128, N = hidden padded to 128 at load
             return ops.cuda_ops().moe_experts_w4a16(x, moe.w13, moe.w13_scale, moe.w2, moe.w2_scale, topk_ids, topk_w,
-                                                    moe.expert_range[0], "mxfp4", act=moe.activation)
+                                                    moe.expert_range[0], "mxfp4", **kw)
         w13 = dequantize_mxfp4(moe.w13, moe.w13_scale).to(x.dtype)
         w2 = dequantize_mxfp4(moe.w2, moe.w2_scale).to(x.dtype)
         if x.is_cuda:
-            return ops.cuda_ops().moe_experts(x, w13, w2, topk_ids, topk_w, moe.expert_range[0], act=moe.activation)
-        return ops.ref.moe_experts(x, w13, w2, topk_ids, topk_w, moe.expert_range[0], act=moe.activation)
+            return ops.cuda_ops().moe_experts(x, w13, w2, topk_ids, topk_w, moe.expert_range[0], **kw)
+        return ops.ref.moe_experts(x, w13, w2, topk_ids, topk_w, moe.expert_range[0], **kw)
 
     def weight_bytes(self, moe) -> int:
         return sum(t.numel() for t in (moe.w13, moe.w2, moe.w13_scale, moe.w2_scale))

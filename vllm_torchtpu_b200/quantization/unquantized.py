@@ -75,6 +75,12 @@ def expert_tp_shard(moe, gate, up, down):
     return gate[r * I:(r + 1) * I], up[r * I:(r + 1) * I], down[:, r * I:(r + 1) * I]
 
 
+def padded_hidden(moe) -> int:
+    """Rows of the down projection: the hidden size rounded up to the GEMM kernels' 128-row tile (hidden sizes
+    such as 2880 are not a multiple of it); the extra rows are zero and the output is cut back."""
+    return (moe.hidden_size + 127) // 128 * 128
+
+
 class UnquantizedMoEMethod:
     name = "unquantized"
 
@@ -93,6 +99,8 @@ class UnquantizedMoEMethod:
             w2.append(seeded_normal(f"{moe.name}.experts.{e}.w2", (H, I), std, moe.dtype, moe.device, seed))
         moe.w13 = torch.stack(w13).contiguous()
         moe.w2 = torch.stack(w2).contiguous()
+        if padded_hidden(moe) != H:
+            moe.w2 = torch.nn.functional.pad(moe.w2, (0, 0, 0, padded_hidden(moe) - H)).contiguous()
 
     def load_expert(self, moe, local_e, gate, up, down, scales=(None, None, None)) -> None:
         """Unsharded checkpoint matrices of one expert; the intermediate dimension is sliced for this
@@ -101,18 +109,18 @@ class UnquantizedMoEMethod:
         I = moe.intermediate_size
         moe.w13[local_e, :I] = gate.to(moe.w13.dtype)
         moe.w13[local_e, I:] = up.to(moe.w13.dtype)
-        moe.w2[local_e] = down.to(moe.w2.dtype)
+        moe.w2[local_e, :moe.hidden_size] = down.to(moe.w2.dtype)
 
     def alloc(self, moe) -> None:
         E, I, H = moe.num_local_experts, moe.intermediate_size, moe.hidden_size
         moe.w13 = torch.zeros(E, 2 * I, H, dtype=moe.dtype, device=moe.device)
-        moe.w2 = torch.zeros(E, H, I, dtype=moe.dtype, device=moe.device)
+        moe.w2 = torch.zeros(E, padded_hidden(moe), I, dtype=moe.dtype, device=moe.device)
 
     def apply(self, moe, x, topk_ids, topk_w):
+        kw = dict(act=moe.activation, b13=getattr(moe, "b13", None), b2=getattr(moe, "b2", None))
         if x.is_cuda:
-            return ops.cuda_ops().moe_experts(x, moe.w13, moe.w2, topk_ids, topk_w, moe.expert_range[0],
-                                              act=moe.activation)
-        return ops.ref.moe_experts(x, moe.w13, moe.w2, topk_ids, topk_w, moe.expert_range[0], act=moe.activation)
+            return ops.cuda_ops().moe_experts(x, moe.w13, moe.w2, topk_ids, topk_w, moe.expert_range[0], **kw)
+        return ops.ref.moe_experts(x, moe.w13, moe.w2, topk_ids, topk_w, moe.expert_range[0], **kw)
 
     def apply_fused_ep(self, moe, x, topk_ids, topk_w, comm):
         return ops.cuda_ops().moe_experts_ep(x, moe.w13, moe.w2, topk_ids, topk_w, comm.heap, moe.num_experts)
