@@ -110,13 +110,60 @@ class LLM:
 
     def generate(self, prompts: Sequence, sampling_params: Union[SamplingParams, Sequence, None] = None,
                  ) -> list:
+        """One ``RequestOutput`` per prompt, in input order, with ``sampling_params.n`` completions each.
+        Stop strings are matched on the detokenised text while the requests run; a request that produced one
+        is ended there and its text is cut in front of the string."""
+        from ..entrypoints.stop_strings import StopStringMatcher, truncate_at_stop
         if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
             prompts = [prompts]
         sps = sampling_params if isinstance(sampling_params, (list, tuple)) else \
             [sampling_params or SamplingParams()] * len(prompts)
-        ids = [self.engine.add_request(self._encode(p), sp) for p, sp in zip(prompts, sps)]
-        self.engine.run_until_done()
+        groups, watch = [], {}
+        for p, sp in zip(prompts, sps):
+            sp = sp or SamplingParams()
+            sp.verify()
+            if sp.stop and self.tokenizer is None:
+                raise ValueError("stop strings need a tokenizer")
+            ids = self._encode(p)
+            group = [self.engine.add_request(ids, sp) for _ in range(sp.n)]
+            groups.append((group, sp))
+            if sp.stop:
+                for rid in group:
+                    watch[rid] = [StopStringMatcher(sp.stop, sp.include_stop_str_in_output), 0]
         reqs = self.engine.scheduler.requests
+        if watch:
+            while self.engine.has_unfinished():
+                self.engine.step()
+                for rid in list(watch):
+                    req = reqs.get(rid)
+                    if req is None or req.status.finished:
+                        del watch[rid]
+                        continue
+                    m, seen = watch[rid]
+                    if len(req.output_token_ids) == seen:
+                        continue
+                    watch[rid][1] = len(req.output_token_ids)
+                    if m.push(self.tokenizer.decode(req.output_token_ids))[1]:
+                        self.engine.abort_request(rid)
+                        del watch[rid]
+        else:
+            self.engine.run_until_done()
         detok = self.tokenizer.decode if self.tokenizer is not None else None
-        outs = [RequestOutput.from_request(reqs.pop(i), detok) for i in ids]
+        outs = []
+        for group, sp in groups:
+            out = None
+            for i, rid in enumerate(group):
+                o = RequestOutput.from_request(reqs.pop(rid), detok)
+                c = o.outputs[0]
+                c.index = i
+                if sp.stop and c.text is not None:
+                    c.text, hit = truncate_at_stop(c.text, sp.stop, sp.include_stop_str_in_output)
+                    if hit is not None:
+                        c.finish_reason, c.stop_reason = "stop", hit
+                if out is None:
+                    out = o
+                else:
+                    out.outputs.append(c)
+                    out.finished = out.finished and o.finished
+            outs.append(out)
         return outs

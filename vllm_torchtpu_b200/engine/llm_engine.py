@@ -203,6 +203,11 @@ class LLMEngine:
                              f"max_model_len ({self.cfg.model.max_model_len})")
         if not prompt_token_ids:
             raise ValueError("empty prompt")
+        sp.verify()
+        if sp.has_logit_adjust and (self.cfg.speculative or self.cfg.parallel.pipeline_parallel_size > 1):
+            # verification rows and pipeline stages sample without the per-step logit edits
+            raise ValueError("penalties, logit_bias, allowed_token_ids and min_p are not supported together with "
+                             "speculative decoding or pipeline parallelism")
         rid = request_id or f"req-{self._next_id}"
         self._next_id += 1
         if self._queue_op(("add", (list(prompt_token_ids), sp), dict(request_id=rid, mm_items=mm_items,

@@ -64,7 +64,20 @@ def _sampling_from_body(body: dict) -> SamplingParams:
         min_tokens=int(body.get("min_tokens", 0) or 0), ignore_eos=bool(body.get("ignore_eos", False)),
         stop_token_ids=list(body.get("stop_token_ids") or []), logprobs=_logprobs_from_body(body),
         prompt_logprobs=body.get("prompt_logprobs"), lora_name=body.get("lora_name"),
-        seed=body.get("seed"), structured=_structured_spec(body))
+        seed=body.get("seed"), structured=_structured_spec(body),
+        n=int(body.get("n") or 1), stop=_stop_from_body(body),
+        include_stop_str_in_output=bool(body.get("include_stop_str_in_output", False)),
+        min_p=float(body.get("min_p") or 0.0), presence_penalty=float(body.get("presence_penalty") or 0.0),
+        frequency_penalty=float(body.get("frequency_penalty") or 0.0),
+        repetition_penalty=float(body.get("repetition_penalty") or 1.0),
+        logit_bias=body.get("logit_bias") or None, allowed_token_ids=body.get("allowed_token_ids") or None)
+
+
+def _stop_from_body(body: dict) -> list:
+    stop = body.get("stop")
+    if stop is None:
+        return []
+    return [stop] if isinstance(stop, str) else list(stop)
 
 
 def build_app(engine, model_name: str, tokenizer=None):
@@ -103,6 +116,7 @@ def build_app(engine, model_name: str, tokenizer=None):
     async def run(body: dict, prompt_ids: list, chat: bool):
         try:
             sp = _sampling_from_body(body)
+            sp.verify()
             from ..platform import B200Platform
             B200Platform.validate_request(sp)
         except ValueError as e:
@@ -121,8 +135,8 @@ def build_app(engine, model_name: str, tokenizer=None):
                 raise HTTPException(400, f"bad mm_items: {e}")
         obj = "chat.completion" if chat else "text_completion"
 
-        def chunk_payload(text, finish, final_item=None):
-            choice = {"index": 0, "finish_reason": finish}
+        def chunk_payload(text, finish, final_item=None, index=0):
+            choice = {"index": index, "finish_reason": finish}
             if chat:
                 choice["delta" if body.get("stream") else "message"] = {"role": "assistant", "content": text}
             else:
@@ -139,37 +153,104 @@ def build_app(engine, model_name: str, tokenizer=None):
             return out
 
         final_item_tokens = [0]
+        n = sp.n
+        if sp.stop and tokenizer is None:
+            raise HTTPException(400, "stop strings need a tokenizer: send stop_token_ids")
+
+        async def events(i):
+            """Completion i as (index, text that may be shown, new token ids, logprobs, finish reason, item,
+            ended).  With stop strings the text lags the tokens by what could still become a stop string."""
+            from .stop_strings import StopStringMatcher
+            m = StopStringMatcher(sp.stop, sp.include_stop_str_in_output) if sp.stop else None
+            gen = aeng.generate(rid if n == 1 else f"{rid}-{i}", prompt_ids, sp, kvp, mm)
+            toks = []
+            try:
+                async for item in gen:
+                    toks += item.new_token_ids
+                    if item.error or m is None:
+                        yield i, decode(item.new_token_ids), item.new_token_ids, item.logprobs, \
+                            item.finish_reason, item, item.finished
+                        continue
+                    text, hit = m.push(decode(toks), final=item.finished)
+                    yield i, text, item.new_token_ids, item.logprobs, \
+                        ("stop" if hit else item.finish_reason), item, (hit or item.finished)
+                    if hit:
+                        return          # closing the generator aborts the request
+            finally:
+                await gen.aclose()
+
+        async def merged():
+            if n == 1:
+                async for ev in events(0):
+                    yield ev
+                return
+            import asyncio
+            q: asyncio.Queue = asyncio.Queue()
+
+            async def pump(i):
+                try:
+                    async for ev in events(i):
+                        await q.put(ev)
+                finally:
+                    await q.put(None)
+            tasks = [asyncio.create_task(pump(i)) for i in range(n)]
+            left = n
+            try:
+                while left:
+                    ev = await q.get()
+                    if ev is None:
+                        left -= 1
+                    else:
+                        yield ev
+            finally:
+                for t in tasks:
+                    t.cancel()
+
         if body.get("stream"):
             async def sse():
-                async for item in aeng.generate(rid, prompt_ids, sp, kvp, mm):
-                    final_item_tokens[0] += len(item.new_token_ids)
+                left = n
+                async for i, text, new_ids, lps_i, finish, item, ended in merged():
+                    final_item_tokens[0] += len(new_ids)
                     if item.error:
                         yield f"data: {json.dumps({'error': item.error})}\n\n"
                         break
-                    payload = chunk_payload(decode(item.new_token_ids), item.finish_reason,
-                                            item if item.finished else None)
-                    if item.logprobs:
-                        payload["choices"][0]["logprobs"] = _logprobs_payload(item.new_token_ids, item.logprobs,
-                                                                              decode)
+                    left -= bool(ended)
+                    payload = chunk_payload(text, finish, item if ended and not left else None, index=i)
+                    if lps_i:
+                        payload["choices"][0]["logprobs"] = _logprobs_payload(new_ids, lps_i, decode)
                     yield f"data: {json.dumps(payload)}\n\n"
                 yield "data: [DONE]\n\n"
             return StreamingResponse(sse(), media_type="text/event-stream")
-        toks, lps, last = [], [], None
-        async for item in aeng.generate(rid, prompt_ids, sp, kvp, mm):
-            toks += item.new_token_ids
-            lps += item.logprobs or []
-            last = item
-        if last is not None and last.error:
-            raise HTTPException(500, last.error)
-        final_item_tokens[0] = len(toks)
-        payload = chunk_payload(decode(toks), last.finish_reason if last else None, last)
-        payload["choices"][0]["token_ids"] = toks
-        if lps:
-            payload["choices"][0]["logprobs"] = _logprobs_payload(toks, lps, decode)
-        if last is not None and last.prompt_logprobs:
-            payload["choices"][0]["prompt_logprobs"] = [
-                None if e is None else {"token_id": e["token_id"], "logprob": e["logprob"], "rank": e["rank"]}
-                for e in last.prompt_logprobs]
+        acc = [{"text": [], "toks": [], "lps": [], "finish": None, "last": None} for _ in range(n)]
+        async for i, text, new_ids, lps_i, finish, item, ended in merged():
+            c = acc[i]
+            c["text"].append(text)
+            c["toks"] += new_ids
+            c["lps"] += lps_i or []
+            c["finish"], c["last"] = finish, item
+            if item.error:
+                raise HTTPException(500, item.error)
+        final_item_tokens[0] = sum(len(c["toks"]) for c in acc)
+        payload = None
+        for i, c in enumerate(acc):
+            toks, last = c["toks"], c["last"]
+            text = "".join(c["text"]) if sp.stop else decode(toks)
+            one = chunk_payload(text, c["finish"], last if i == n - 1 else None, index=i)
+            ch = one["choices"][0]
+            ch["token_ids"] = toks
+            if c["lps"]:
+                ch["logprobs"] = _logprobs_payload(toks, c["lps"], decode)
+            if last is not None and last.prompt_logprobs:
+                ch["prompt_logprobs"] = [
+                    None if e is None else {"token_id": e["token_id"], "logprob": e["logprob"], "rank": e["rank"]}
+                    for e in last.prompt_logprobs]
+            if payload is None:
+                payload = one
+            else:
+                payload["choices"].append(ch)
+                for k in ("usage", "kv_transfer_params"):
+                    if k in one:
+                        payload[k] = one[k]
         return JSONResponse(payload)
 
     @app.post("/v1/completions")

@@ -12,6 +12,7 @@ class CompletionOutput:
     text: Optional[str] = None
     finish_reason: Optional[str] = None
     logprobs: Optional[list] = None
+    stop_reason: Optional[str] = None      # the stop string that ended the text, if one did
 
 
 @dataclass

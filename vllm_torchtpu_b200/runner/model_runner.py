@@ -456,6 +456,9 @@ class ModelRunner:
             r_i = torch.tensor(ex["mask_rows"], dtype=torch.long, device=logits.device)
             t_i = torch.tensor(ex["mask_ids"], dtype=torch.long, device=logits.device)
             logits[r_i, t_i] = float("-inf")
+        if ex is not None and ex["adjust"]:
+            from .logit_adjust import apply_logit_adjust
+            apply_logit_adjust(logits, ex["adjust"], self.last_tokens)
         if self.is_cuda:
             # noise comes from Philox inside the kernel, keyed by (seed, step counter in device memory)
             tokens = ops.cuda_ops().sample(logits, dv("temperature", R, torch.float32), dv("top_k", R),
@@ -498,11 +501,12 @@ class ModelRunner:
             ex["out"].setdefault("prompt", []).append((rid, targets, k, pack))
 
     def _plan_extras(self, p):
-        """Per-step work outside the plain sample: logprobs of the sampled tokens, the min_tokens mask and
-        prompt logprobs.  Steps that need any of it run eagerly."""
+        """Per-step work outside the plain sample: logprobs of the sampled tokens, the min_tokens mask,
+        logit edits (penalties, bias, allowed tokens, min-p) and prompt logprobs.  Steps that need any of it
+        run eagerly."""
         if p.get("has_spec") or get_state().pp.size > 1:
             return None
-        lp_rows, lp_ks, mask_rows, mask_ids, prompt = [], [], [], [], []
+        lp_rows, lp_ks, mask_rows, mask_ids, prompt, adjust = [], [], [], [], [], []
         qsl = p["qsl_np"]
         for i, s in enumerate(p["scheds"]):
             req = s.request
@@ -522,16 +526,22 @@ class ModelRunner:
                         if 0 <= t < self.mcfg.vocab_size:
                             mask_rows.append(i)
                             mask_ids.append(int(t))
+                if sp.has_logit_adjust:
+                    from .logit_adjust import plan_row
+                    # a token sampled by a step whose result the host has not read yet is counted from
+                    # the device-resident last-token table
+                    inflight = self.batch.slot_of.get(req.request_id) if req.num_output_placeholders > 1 else None
+                    adjust.append(plan_row(i, sp, req.prompt_token_ids, req.output_token_ids, inflight))
             if sp.prompt_logprobs is not None and s.start < req.num_prompt_tokens:
                 lo = int(qsl[i])
                 n_rows = min(int(qsl[i + 1]) - lo, req.num_prompt_tokens - s.start)
                 targets = list(req.prompt_token_ids[s.start + 1: s.start + n_rows + 1])
                 if targets:
                     prompt.append((req.request_id, lo, lo + len(targets), targets, int(sp.prompt_logprobs)))
-        if not (lp_rows or mask_rows or prompt):
+        if not (lp_rows or mask_rows or prompt or adjust):
             return None
         return {"lp_rows": lp_rows, "lp_ks": lp_ks, "mask_rows": mask_rows, "mask_ids": mask_ids,
-                "prompt": prompt, "out": {}}
+                "prompt": prompt, "adjust": adjust, "out": {}}
 
     def _pp_handoff(self):
         if getattr(self, "_pp", None) is None:
