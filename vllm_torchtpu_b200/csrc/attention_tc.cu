@@ -51,6 +51,7 @@ struct Params {
   const float* sinks;
   int* status;
   int max_blocks, block_size, Hq, Hkv, G, BQ, req_begin, req_end, window;
+  int non_causal;                 // 1: every query row sees the whole sequence (encoders, diffusion)
   long long num_blocks;
   float scale_log2, softcap;
 };
@@ -143,7 +144,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   }
   const bool active = r >= 0 && seq_len > 0 && q_len > 0;
   const int ctx = seq_len - q_len;
-  const int kv_end = active ? min(seq_len, ctx + q0 + p.BQ) : 0;      // causal bound of the tile
+  // causal bound of the tile; the whole sequence without the mask
+  const int kv_end = active ? (p.non_causal ? seq_len : min(seq_len, ctx + q0 + p.BQ)) : 0;
   int kv_begin = 0;
   if (active && p.window > 0) kv_begin = max(0, ctx + q0 - p.window + 1) / BKV * BKV;
   const int nchunks = active ? (kv_end - kv_begin + BKV - 1) / BKV : 0;
@@ -264,7 +266,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int row = qd * 32 + lane;                       // TMEM lane = tile row
     const int pos_local = row / p.G, head = h * p.G + row % p.G;
     const bool row_ok = active && (q0 + pos_local) < q_len;
-    const int lim = ctx + q0 + pos_local;                 // last visible key of this row
+    const int lim = p.non_causal ? seq_len - 1 : ctx + q0 + pos_local;    // last visible key of this row
     constexpr int HC = BKV / 2, HD = D / 2;
     float acc[HD];
 #pragma unroll
@@ -449,11 +451,11 @@ using namespace b200;
 // Requests [req_begin, req_end) of a ragged batch; num_tiles_64 = sum over them of ceil(q_len / 64)
 // (the tile count of 64-row query blocks, from which the grid for 128 / G positions per tile is bounded).
 // head_dim 128, q heads per kv head in {1, 2, 4, 8}, block_size a multiple of 16.
-extern "C" int b200_attn_prefill_tc(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
-                                    const int* seq_lens, const int* qsl, int req_begin, int req_end,
-                                    int num_tiles_64, int total_tokens, int max_blocks, int block_size,
-                                    long long num_blocks, int Hq, int Hkv, int D, float scale, int window,
-                                    float softcap, const float* sinks, int* status, cudaStream_t stream) {
+static int attn_prefill_tc_impl(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                                const int* seq_lens, const int* qsl, int req_begin, int req_end, int num_tiles_64,
+                                int total_tokens, int max_blocks, int block_size, long long num_blocks, int Hq,
+                                int Hkv, int D, float scale, int window, float softcap, const float* sinks,
+                                int* status, int non_causal, cudaStream_t stream) {
   if (req_end <= req_begin || num_tiles_64 <= 0) return 0;
   const int G = Hkv > 0 ? Hq / Hkv : 0;
   if (D != 128 || Hq % Hkv || (G != 1 && G != 2 && G != 4 && G != 8) || block_size % 16) {
@@ -467,6 +469,7 @@ extern "C" int b200_attn_prefill_tc(const void* q, const void* kv, void* out, fl
   p.sinks = sinks; p.status = status;
   p.max_blocks = max_blocks; p.block_size = block_size; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.BQ = fa::BM / G;
   p.req_begin = req_begin; p.req_end = req_end; p.window = window; p.num_blocks = num_blocks;
+  p.non_causal = non_causal;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.softcap = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
   CUtensorMap tmQ, tmKV;
@@ -486,6 +489,28 @@ extern "C" int b200_attn_prefill_tc(const void* q, const void* kv, void* out, fl
   B200_CUDA_CHECK(launch_pdl(fa::attn_prefill_tc_kernel, grid, dim3(fa::NUM_THREADS), (size_t)fa::SMEM_TOTAL, stream,
                              tmQ, tmKV, p));
   return 0;
+}
+
+extern "C" int b200_attn_prefill_tc(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                                    const int* seq_lens, const int* qsl, int req_begin, int req_end,
+                                    int num_tiles_64, int total_tokens, int max_blocks, int block_size,
+                                    long long num_blocks, int Hq, int Hkv, int D, float scale, int window,
+                                    float softcap, const float* sinks, int* status, cudaStream_t stream) {
+  return attn_prefill_tc_impl(q, kv, out, lse, block_tables, seq_lens, qsl, req_begin, req_end, num_tiles_64,
+                              total_tokens, max_blocks, block_size, num_blocks, Hq, Hkv, D, scale, window, softcap,
+                              sinks, status, 0, stream);
+}
+
+// Bidirectional form (vision encoders, diffusion transformers): each request's q_len equals its seq_len and
+// every row sees every key.  No window, soft-cap or sinks.
+extern "C" int b200_attn_encoder_tc(const void* q, const void* kv, void* out, float* lse, const int* block_tables,
+                                    const int* seq_lens, const int* qsl, int req_begin, int req_end,
+                                    int num_tiles_64, int total_tokens, int max_blocks, int block_size,
+                                    long long num_blocks, int Hq, int Hkv, int D, float scale, int* status,
+                                    cudaStream_t stream) {
+  return attn_prefill_tc_impl(q, kv, out, lse, block_tables, seq_lens, qsl, req_begin, req_end, num_tiles_64,
+                              total_tokens, max_blocks, block_size, num_blocks, Hq, Hkv, D, scale, 0, 0.f, nullptr,
+                              status, 1, stream);
 }
 
 // see b200_bad_index_count_attention

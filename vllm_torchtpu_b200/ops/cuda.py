@@ -408,8 +408,10 @@ def paged_attention(q, kv_cache, meta, scale, *, sliding_window=None, softcap=No
 def encoder_attention(q, k, v, cu_seqlens, scale=None):
     """Bidirectional attention over a ragged batch of sequences (vision encoders).  q [T, Hq, D], k / v
     [T, Hkv, D] bf16, ``cu_seqlens`` = list of R + 1 token offsets.  Keys and values are packed into the
-    paged layout of the attention kernels and the prefill kernel runs with the causal mask off
-    (reference: src/vllm_torchtpu/kernels/flash_attention/ — segment-id flash attention)."""
+    paged layout of the attention kernels and the prefill kernel runs with the causal mask off: the tcgen05
+    kernel for 128-wide heads, the mma.sync kernel for 64-wide ones
+    (reference: src/vllm_torchtpu/kernels/flash_attention/ — segment-id flash attention;
+    kernels/diffusion_attention/kernel.py — dense attention of the diffusion transformers)."""
     _require_bf16(q, k, v)
     T, Hq, D = q.shape
     Hkv = k.shape[1]
@@ -439,10 +441,18 @@ def encoder_attention(q, k, v, cu_seqlens, scale=None):
     tiles = sum(-(-n // 64) for n in lens)
     sc = float(scale) if scale is not None else D ** -0.5
     qc = q.contiguous()
-    _check(lib().b200_attn_encoder(
-        _p(qc), _p(cache), _p(out), c_void_p(0), _p(bt_d), _p(sl), _p(qsl), c_int(0), c_int(R), c_int(tiles),
-        c_int(max_blocks), c_int(bs), c_longlong(NB), c_int(Hq), c_int(Hkv), c_int(D), c_float(sc), _stream()),
-        "attn_encoder")
+    if D == 128 and Hq // Hkv in (1, 2, 4, 8) and envs.B200_ATTN_PREFILL_IMPL == "tc":
+        # the tcgen05 prefill kernel with the causal mask off: one CTA per (kv head, 128 / G positions)
+        ws = Workspace.get(dev)
+        _check(lib().b200_attn_encoder_tc(
+            _p(qc), _p(cache), _p(out), c_void_p(0), _p(bt_d), _p(sl), _p(qsl), c_int(0), c_int(R), c_int(tiles),
+            c_int(T), c_int(max_blocks), c_int(bs), c_longlong(NB), c_int(Hq), c_int(Hkv), c_int(D), c_float(sc),
+            _p(ws.status), _stream()), "attn_encoder_tc")
+    else:
+        _check(lib().b200_attn_encoder(
+            _p(qc), _p(cache), _p(out), c_void_p(0), _p(bt_d), _p(sl), _p(qsl), c_int(0), c_int(R), c_int(tiles),
+            c_int(max_blocks), c_int(bs), c_longlong(NB), c_int(Hq), c_int(Hkv), c_int(D), c_float(sc), _stream()),
+            "attn_encoder")
     count_launch()
     return out
 
