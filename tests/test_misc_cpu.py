@@ -1,4 +1,5 @@
 """Envs registry, env validation, profile options, phase classification, parallel layouts, CLI parsing."""
+import os
 import pytest
 
 from vllm_torchtpu_b200 import env_validation, envs
@@ -211,3 +212,56 @@ def test_example_scripts_run_on_cpu():
     spec.loader.exec_module(mod)
     outs = mod.main(["--device", "cpu", "--speculative-config", '{"method": "ngram", "num_speculative_tokens": 2}'])
     assert len(outs) == 2
+
+
+def _pull_worker(uri, cache, q):
+    from vllm_torchtpu_b200.models import model_source as ms
+    q.put(ms.ensure_local_aux_files(uri, cache))
+
+
+def test_aux_files_of_a_uri_model_are_pulled_once_per_host(tmp_path):
+    """Ranks that share a host serialise on a lock: one pulls the non-weight files, the others find them; a
+    pull that died half-way is started over; weights are never copied."""
+    import multiprocessing as mp
+    import shutil
+
+    from vllm_torchtpu_b200.models import model_source as ms
+    src = tmp_path / "bucket" / "model"
+    src.mkdir(parents=True)
+    for name, body in (("config.json", "{}"), ("tokenizer.json", "{}"), ("merges.txt", "a b"),
+                       ("modeling_custom.py", "x = 1"), ("model-00001.safetensors", "W" * 64), ("notes.bin", "b")):
+        (src / name).write_text(body)
+    log = tmp_path / "fetch.log"
+
+    def counting_fetch(uri, name, dst):
+        with open(log, "a") as f:
+            f.write(name + "\n")
+        shutil.copyfile(os.path.join(uri[len("count://"):], name), dst)
+    ms.register_fetcher("count", lambda uri: sorted(os.listdir(uri[len("count://"):])), counting_fetch)
+    uri, cache = f"count://{src}", str(tmp_path / "cache")
+    ctx = mp.get_context("fork")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_pull_worker, args=(uri, cache, q)) for _ in range(4)]
+    [p.start() for p in procs]
+    dirs = {q.get(timeout=60) for _ in procs}
+    [p.join(60) for p in procs]
+    assert len(dirs) == 1 and all(p.exitcode == 0 for p in procs)
+    local = dirs.pop()
+    assert local == ms.local_dir_for(uri, cache) and ms.is_complete(local)
+    assert sorted(log.read_text().split()) == ["config.json", "merges.txt", "modeling_custom.py", "tokenizer.json"]
+    assert not os.path.exists(os.path.join(local, "model-00001.safetensors"))
+    # a crashed pull: the mark of a pull in progress without the completion mark
+    os.remove(os.path.join(local, ".b200_aux_complete"))
+    open(os.path.join(local, ".b200_pulling"), "w").close()
+    os.remove(os.path.join(local, "tokenizer.json"))
+    assert ms.ensure_local_aux_files(uri, cache) == local and os.path.exists(os.path.join(local, "tokenizer.json"))
+    assert len(log.read_text().split()) == 8
+    # file:// models: aux files local, weights read in place; plain paths pass through; unknown schemes refuse
+    aux, weights = ms.resolve_model(f"file://{src}", cache)
+    assert weights == str(src) and os.path.exists(os.path.join(aux, "config.json")) and aux != str(src)
+    assert ms.resolve_model(str(src)) == (str(src), str(src))
+    with pytest.raises(ValueError, match="fetcher"):
+        ms.ensure_local_aux_files("s3://bucket/model", cache)
+    (src / "config.json").unlink()
+    with pytest.raises(FileNotFoundError):
+        ms.ensure_local_aux_files(f"file://{src}", str(tmp_path / "cache2"))

@@ -47,6 +47,18 @@ def test_safetensors_roundtrip_dense_and_moe(tmp_path):
         dst = LLM(str(d), device="cpu", max_num_seqs=4, block_size=16, init_dist=False, dtype="float32")
         got = [o.outputs[0].token_ids for o in dst.generate(_prompts(), sp)]
         assert got == want, preset
+        if preset == "tiny-llama":
+            # the same checkpoint named by a URI: configuration pulled to a host-local directory, weights read
+            # in place
+            import os
+            os.environ["HOME"], home = str(tmp_path / "home"), os.environ.get("HOME")
+            try:
+                uri = LLM(f"file://{d}", device="cpu", max_num_seqs=4, block_size=16, init_dist=False, dtype="float32")
+            finally:
+                if home is not None:
+                    os.environ["HOME"] = home
+            assert [o.outputs[0].token_ids for o in uri.generate(_prompts(), sp)] == want
+            assert (tmp_path / "home" / ".cache" / "vllm_torchtpu_b200" / "model_source").is_dir()
 
 
 def _rewrite_checkpoint(d, rename):

@@ -35,12 +35,17 @@ class LLM:
                  additional_config: Optional[dict] = None, load_format: str = "auto",
                  world_size: Optional[int] = None, init_dist: bool = True):
         import os
-        model_path = None
+        model_path = tokenizer_path = None
         if isinstance(model, ModelConfig):
             mc = model
-        elif os.path.isdir(str(model)):
-            mc = ModelConfig.from_pretrained(model)
-            model_path = model
+        elif os.path.isdir(str(model)) or "://" in str(model):
+            # a URI: configuration and tokenizer are copied to this host once, weights are read from the source
+            from ..models.model_source import resolve_model
+            aux_dir, weights = resolve_model(str(model))
+            if "://" in str(weights):
+                raise ValueError(f"weights of {model} need a streaming reader for their scheme; none is built in")
+            mc = ModelConfig.from_pretrained(aux_dir)
+            model_path, tokenizer_path = weights, aux_dir
         else:
             mc = model_preset(model)
         if max_model_len:
@@ -77,7 +82,7 @@ class LLM:
         if tokenizer is None and model_path:
             try:
                 from transformers import AutoTokenizer
-                self.tokenizer = AutoTokenizer.from_pretrained(model_path)
+                self.tokenizer = AutoTokenizer.from_pretrained(tokenizer_path or model_path)
             except Exception:
                 self.tokenizer = None
         if self.tokenizer is not None and getattr(self.tokenizer, "eos_token_id", None) is not None:

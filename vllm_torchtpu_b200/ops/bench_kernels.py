@@ -534,10 +534,52 @@ def bench_gemm_sustained(T, N, K, seconds=3.0, impl="tcgen05") -> dict:
 LLAMA8B_SHAPES = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336), (128256, 4096)]
 
 
+def bench_omni(S=8192, H=16, D=128, iters=10) -> list:
+    """Diffusion-transformer kernels at one sequence of S tokens: the tcgen05 attention kernel without the causal
+    mask (timed on a pre-packed paged layout, as the kernel sees it) and the fused q/k norm + RoPE over
+    H * D channels."""
+    from ctypes import c_float, c_int, c_longlong, c_void_p
+
+    from ..omni.ops import qk_norm_rope
+    from ..omni.rope import rope_table_1d
+    from . import cuda
+    pk, tag = peaks()
+    bs = 16
+    nblk = -(-S // bs)
+    cache = (torch.randn(nblk, 2, H, bs, D, device="cuda") * 0.5).bfloat16()
+    bt = torch.arange(nblk, device="cuda", dtype=torch.int32).view(1, nblk).contiguous()
+    q = torch.randn(S, H, D, device="cuda").bfloat16()
+    out = torch.empty_like(q)
+    qsl = torch.tensor([0, S], device="cuda", dtype=torch.int32)
+    sl = torch.tensor([S], device="cuda", dtype=torch.int32)
+    ws = cuda.Workspace.get(q.device)
+    tiles = -(-S // 64)
+
+    def attn():
+        cuda._check(cuda.lib().b200_attn_encoder_tc(
+            cuda._p(q), cuda._p(cache), cuda._p(out), c_void_p(0), cuda._p(bt), cuda._p(sl), cuda._p(qsl), c_int(0),
+            c_int(1), c_int(tiles), c_int(S), c_int(nblk), c_int(bs), c_longlong(nblk), c_int(H), c_int(H), c_int(D),
+            c_float(D ** -0.5), cuda._p(ws.status), cuda._stream()), "attn_encoder_tc")
+    ms = time_fn(attn, iters)
+    flops = 4.0 * D * S * S * H
+    rows = [{"op": "attn_non_causal_tc", "S": S, "heads": H, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+             "frac_of_bf16_peak": round(flops / ms / 1e9 / pk["bf16_tflops"], 3), "peaks": tag}]
+    C = H * D
+    qkv = torch.randn(S, 3 * C, device="cuda").bfloat16()
+    wq, wk = torch.ones(C, device="cuda").bfloat16(), torch.ones(C, device="cuda").bfloat16()
+    cos, sin = rope_table_1d(S, D, device="cuda")
+    ms = time_fn(lambda: qk_norm_rope(qkv, wq, wk, cos, sin, H, H, D), iters)
+    nbytes = 4.0 * S * C * 2 + 4.0 * S * D       # q, k read and written; two fp32 tables of D / 2 per token
+    rows.append({"op": "qk_norm_rope", "T": S, "channels": C, "ms": round(ms, 4),
+                 "gbs": round(nbytes / ms / 1e6, 1), "frac_of_hbm_peak": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3),
+                 "peaks": tag})
+    return rows
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "fp8-gemm", "w4a16-gemm", "misc", "gemm-swiglu", "gemm-sweep", "gemm-sustained", "attn-decode", "attn-prefill",
-                                     "decode-layer", "decode-model", "all"])
+                                     "decode-layer", "decode-model", "omni", "all"])
     ap.add_argument("--T", type=int, default=64)
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
@@ -562,6 +604,9 @@ def main():
                     continue
                 for impl in ("tcgen05", "cublas"):
                     print(json.dumps(bench_gemm(T, N, K, max(5, a.iters // 2), impl, check=(T <= 1024))))
+    if a.what == "omni":
+        for r in bench_omni(a.q, a.T, 128, a.iters):
+            print(json.dumps(r))
     if a.what == "w4a16-gemm":
         for r in bench_w4a16(a.T, a.N, a.K, a.iters):
             print(json.dumps(r))
