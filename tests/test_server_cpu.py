@@ -172,3 +172,67 @@ def test_update_weights_and_reload_kernel_routes(tmp_path):
         llm.engine.reload_kernels = busy
         assert c.post("/reload_kernel").status_code == 409
     app.state.async_engine.shutdown()
+
+
+def test_launch_exports_once_then_serves_the_artifact(tmp_path):
+    """``launch`` splits the serve command line, exports into a cache keyed by model + export flags, and
+    replaces itself with the server over the artifact; a second launch reuses the artifact."""
+    import json
+    import os
+    import socket
+    import subprocess
+    import sys
+    import time
+    import urllib.request
+
+    from vllm_torchtpu_b200.entrypoints.cli import main
+    cache = str(tmp_path / "exports")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    argv = ["launch", "tiny-llama", "--device", "cpu", "--host", "127.0.0.1", "--port", str(port), "--max-num-seqs", "4",
+            "--max-model-len", "128", "--scheduler-cls", "default", "--export-cache", cache]
+    env = dict(os.environ, B200_LOG_LEVEL="WARNING")
+    out = subprocess.run([sys.executable, "-m", "vllm_torchtpu_b200"] + argv + ["--dry-run"], capture_output=True,
+                         text=True, env=env, timeout=120)
+    plan = json.loads(out.stdout.strip().splitlines()[-1])
+    assert plan["cached"] is False and plan["world_size"] == 1
+    assert "--max-num-seqs" in plan["export"] and "--port" not in plan["export"]
+    assert "--port" in plan["serve"] and "--max-num-seqs" not in plan["serve"] and plan["serve"][4] == plan["artifact"]
+    # other export flags -> another artifact; other front-end flags -> the same one
+    alt = subprocess.run([sys.executable, "-m", "vllm_torchtpu_b200"] + argv + ["--dry-run", "--block-size", "32"],
+                         capture_output=True, text=True, env=env, timeout=120)
+    assert json.loads(alt.stdout.strip().splitlines()[-1])["artifact"] != plan["artifact"]
+    proc = subprocess.Popen([sys.executable, "-m", "vllm_torchtpu_b200"] + argv, env=env, stdout=subprocess.PIPE,
+                            stderr=subprocess.STDOUT, text=True)
+    try:
+        deadline, up = time.time() + 180, False
+        while time.time() < deadline and proc.poll() is None:
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2) as r:
+                    up = r.status == 200
+                    break
+            except OSError:
+                time.sleep(0.5)
+        assert up, "the server did not come up"
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions", method="POST",
+                                     headers={"Content-Type": "application/json"},
+                                     data=json.dumps({"prompt": [1, 2, 3, 4], "max_tokens": 3, "temperature": 0,
+                                                      "ignore_eos": True}).encode())
+        with urllib.request.urlopen(req, timeout=60) as r:
+            body = json.loads(r.read())
+        assert len(body["choices"][0]["token_ids"]) == 3
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(30)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+    assert os.path.isfile(os.path.join(plan["artifact"], "metadata.json"))
+    with open(os.path.join(plan["artifact"], "metadata.json")) as f:
+        meta = json.load(f)
+    assert meta["engine"]["max_num_seqs"] == 4 and meta["engine"]["max_model_len"] == 128
+    assert main(argv + ["--dry-run"]) == 0          # the artifact is found again (printed as cached)
+    again = subprocess.run([sys.executable, "-m", "vllm_torchtpu_b200"] + argv + ["--dry-run"], capture_output=True,
+                           text=True, env=env, timeout=120)
+    assert json.loads(again.stdout.strip().splitlines()[-1])["cached"] is True

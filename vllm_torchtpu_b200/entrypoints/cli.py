@@ -70,6 +70,13 @@ def main(argv=None) -> int:
     s.add_argument("--host", default="0.0.0.0")
     s.add_argument("--port", type=int, default=8000)
     s.add_argument("--served-model-name", default=None)
+    ln = sub.add_parser("launch", help="export once (cached), then serve the exported artifact")
+    add_engine_args(ln)
+    ln.add_argument("--host", default="0.0.0.0")
+    ln.add_argument("--port", type=int, default=8000)
+    ln.add_argument("--served-model-name", default=None)
+    ln.add_argument("--export-cache", default=None, help="directory the exported artifacts are cached in")
+    ln.add_argument("--dry-run", action="store_true", help="print the export and serve commands and stop")
     p = sub.add_parser("proxy", help="prefill/decode disaggregation proxy")
     p.add_argument("--prefiller-hosts", nargs="+", default=["127.0.0.1"])
     p.add_argument("--prefiller-ports", nargs="+", type=int, default=[8100])
@@ -101,6 +108,9 @@ def main(argv=None) -> int:
         for name, var in sorted(envs.declared().items()):
             print(f"{name:40s} {var.type.__name__:6s} default={var.default!r}  {var.doc}")
         return 0
+    if a.cmd == "launch":
+        from .launcher import launch
+        return launch(a, ln)
     if a.cmd == "validate-export":
         from ..export import validate_serving_dir
         problems = validate_serving_dir(a.path)
@@ -122,7 +132,16 @@ def main(argv=None) -> int:
         from ..kv_transfer.controller import run_controller
         run_controller(a.host, a.port, a.ttl)
         return 0
-    llm = make_llm(a)
+    if os.path.isfile(os.path.join(str(a.model), "metadata.json")) and \
+            os.path.isdir(os.path.join(str(a.model), "serving_checkpoint")):
+        # an exported artifact: checked against its manifest, its recorded plan gives the defaults and the
+        # flags given on this command line override them
+        from ..export import load_serving_dir
+        given = {k: v for k, v in vars(a).items()
+                 if k not in ("cmd", "model", "host", "port", "served_model_name", "device") and v != s.get_default(k)}
+        llm = load_serving_dir(a.model, a.device, **given)
+    else:
+        llm = make_llm(a)
     rank = int(os.environ.get("RANK", "0"))
     name = a.served_model_name or llm.engine.cfg.model.name
     # several ranks: rank 0 takes the HTTP requests and broadcasts them step by step, the others follow
