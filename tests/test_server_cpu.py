@@ -236,3 +236,86 @@ def test_launch_exports_once_then_serves_the_artifact(tmp_path):
     again = subprocess.run([sys.executable, "-m", "vllm_torchtpu_b200"] + argv + ["--dry-run"], capture_output=True,
                            text=True, env=env, timeout=120)
     assert json.loads(again.stdout.strip().splitlines()[-1])["cached"] is True
+
+
+class _PieceTokenizer:
+    """Token id -> a fixed piece of text; enough for structured decoding and function calling over HTTP."""
+
+    def __init__(self, vocab):
+        self.vocab = vocab
+
+    def __len__(self):
+        return len(self.vocab)
+
+    def encode(self, text):
+        return [3 + (ord(c) % 50) for c in text][:64] or [3]
+
+    def decode(self, ids):
+        return "".join(self.vocab[t] for t in ids)
+
+
+def test_function_calling_batched_prompts_and_utility_routes():
+    import json
+
+    from vllm_torchtpu_b200.entrypoints.tool_calls import extract_tool_calls, structured_spec_for, validate_tools
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+        "type": "object", "properties": {"ok": {"type": "boolean"}, "n": {"enum": [0, 7]}}, "required": ["ok", "n"]}}},
+        {"type": "function", "function": {"name": "noop"}}]
+    # the parser and the request checks on their own
+    assert validate_tools({}) == ([], None) and validate_tools({"tools": tools})[1] == "auto"
+    assert validate_tools({"tools": tools, "tool_choice": {"type": "function", "function": {"name": "noop"}}})[1] == "noop"
+    for bad in ({"tool_choice": "required"}, {"tools": [{"type": "function"}]},
+                {"tools": tools, "tool_choice": {"function": {"name": "missing"}}}, {"tools": tools, "tool_choice": "x"}):
+        with pytest.raises(ValueError):
+            validate_tools(bad)
+    assert structured_spec_for(tools, "auto") is None and "json" in structured_spec_for(tools, "required")
+    text = 'Let me look.\n<tool_call>\n{"name": "get_weather", "arguments": {"ok": true, "n": 3}}\n</tool_call>' \
+           '<tool_call>{"name": "unknown", "arguments": {}}</tool_call>'
+    content, calls = extract_tool_calls(text, tools, "auto")
+    assert content == "Let me look." and len(calls) == 1 and calls[0]["function"]["name"] == "get_weather"
+    assert json.loads(calls[0]["function"]["arguments"]) == {"ok": True, "n": 3}
+    assert extract_tool_calls("plain answer", tools, "auto") == ("plain answer", [])
+    assert extract_tool_calls(text, tools, "none") == (text, [])
+    _, calls = extract_tool_calls('[{"name": "noop", "parameters": {}}]', tools, "required")
+    assert calls[0]["function"] == {"name": "noop", "arguments": "{}"}
+
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    V = llm.engine.cfg.model.vocab_size
+    pieces = ['{', '}', '"', ':', ',', ' ', 'ok', 'n', 'true', 'false', '0', '1', '7', '42', 'x', 'y']
+    tok = _PieceTokenizer(pieces + [f"<{i}>" for i in range(V - len(pieces))])
+    llm.engine.eos_token_id = V - 1
+    app = build_app(llm.engine, "tiny-llama", tok)
+    msgs = [{"role": "user", "content": "weather?"}]
+    with TestClient(app) as c:
+        # a named function: the arguments are constrained to its parameter schema
+        r = c.post("/v1/chat/completions", json={
+            "messages": msgs, "tools": tools, "max_tokens": 40, "temperature": 0,
+            "tool_choice": {"type": "function", "function": {"name": "get_weather"}}})
+        assert r.status_code == 200, r.text
+        ch = r.json()["choices"][0]
+        assert ch["finish_reason"] == "tool_calls" and ch["message"]["content"] is None
+        call = ch["message"]["tool_calls"][0]
+        args = json.loads(call["function"]["arguments"])
+        assert call["function"]["name"] == "get_weather" and isinstance(args["ok"], bool) and args["n"] in (0, 7)
+        # the same as a stream: the calls come as one delta of the last chunk
+        with c.stream("POST", "/v1/chat/completions", json={
+                "messages": msgs, "tools": tools, "max_tokens": 40, "temperature": 0, "stream": True,
+                "tool_choice": {"type": "function", "function": {"name": "get_weather"}}}) as s:
+            chunks = [json.loads(l[5:]) for l in s.iter_lines() if l.startswith("data: {")]
+        last = chunks[-1]["choices"][0]
+        assert last["finish_reason"] == "tool_calls" and last["delta"]["tool_calls"][0]["index"] == 0
+        assert c.post("/v1/chat/completions", json={"messages": msgs, "tool_choice": "required"}).status_code == 400
+        # several prompts in one completion request
+        r = c.post("/v1/completions", json={"prompt": [[1, 2, 3], [4, 5, 6, 7]], "max_tokens": 2, "temperature": 0,
+                                            "ignore_eos": True, "n": 2}).json()
+        assert [ch["index"] for ch in r["choices"]] == [0, 1, 2, 3]
+        assert r["usage"] == dict(r["usage"], prompt_tokens=7, completion_tokens=8, total_tokens=15)
+        assert c.post("/v1/completions", json={"prompt": [[1], [2]], "stream": True}).status_code == 400
+        # utility routes
+        t = c.post("/tokenize", json={"prompt": "abc"}).json()
+        assert t["count"] == 3 and t["tokens"] == tok.encode("abc")
+        assert c.post("/tokenize", json={"messages": msgs}).json()["count"] > 0
+        assert c.post("/detokenize", json={"tokens": [0, 6, 1]}).json() == {"prompt": "{ok}"}
+        assert c.post("/detokenize", json={"tokens": "x"}).status_code == 400
+        assert c.get("/version").json()["version"] and c.get("/ping").json() == {"status": "ok"}
+    app.state.async_engine.shutdown()

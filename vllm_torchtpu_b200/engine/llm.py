@@ -88,6 +88,12 @@ class LLM:
         if self.tokenizer is not None and getattr(self.tokenizer, "eos_token_id", None) is not None:
             self.engine.eos_token_id = self.tokenizer.eos_token_id
 
+    def _decode(self, ids) -> str:
+        try:
+            return self.tokenizer.decode(ids, skip_special_tokens=True)
+        except TypeError:                                # tokenizers without the flag
+            return self.tokenizer.decode(ids)
+
     def _encode(self, prompt) -> list:
         if isinstance(prompt, str):
             if self.tokenizer is None:
@@ -148,12 +154,12 @@ class LLM:
                     if len(req.output_token_ids) == seen:
                         continue
                     watch[rid][1] = len(req.output_token_ids)
-                    if m.push(self.tokenizer.decode(req.output_token_ids))[1]:
+                    if m.push(self._decode(req.output_token_ids))[1]:
                         self.engine.abort_request(rid)
                         del watch[rid]
         else:
             self.engine.run_until_done()
-        detok = self.tokenizer.decode if self.tokenizer is not None else None
+        detok = self._decode if self.tokenizer is not None else None
         outs = []
         for group, sp in groups:
             out = None

@@ -1,8 +1,9 @@
 """OpenAI-compatible HTTP server.
 
-Routes: ``/v1/completions``, ``/v1/chat/completions`` (both with SSE streaming),
-``/v1/models``, ``/health``, ``/metrics`` (Prometheus text), ``/start_profile`` and
-``/stop_profile``.  ``kv_transfer_params`` is accepted in requests and returned in
+Routes: ``/v1/completions`` (one or several prompts), ``/v1/chat/completions`` (function calling through
+``tools`` / ``tool_choice``), both with SSE streaming, ``/v1/embeddings``, ``/v1/models``, ``/tokenize``,
+``/detokenize``, ``/version``, ``/health``, ``/ping``, ``/metrics`` (Prometheus text), LoRA load / unload,
+``/update_weights``, ``/reload_kernel``, ``/start_profile`` and ``/stop_profile``.  ``kv_transfer_params`` is accepted in requests and returned in
 responses so the disaggregation proxy can chain a prefill and a decode instance
 (reference surface: README.md:63-82, docs/user_guide/disaggregated_serving.md:98-108).
 
@@ -73,6 +74,14 @@ def _sampling_from_body(body: dict) -> SamplingParams:
         logit_bias=body.get("logit_bias") or None, allowed_token_ids=body.get("allowed_token_ids") or None)
 
 
+def _template_kwargs(body: dict):
+    """Extra keyword arguments of the chat template; ``tools`` reach the template this way."""
+    kw = dict(body.get("chat_template_kwargs") or {})
+    if body.get("tools") and body.get("tool_choice") != "none":
+        kw.setdefault("tools", body["tools"])
+    return kw or None
+
+
 def _stop_from_body(body: dict) -> list:
     stop = body.get("stop")
     if stop is None:
@@ -101,7 +110,18 @@ def build_app(engine, model_name: str, tokenizer=None):
     def decode(ids: list) -> str:
         if tokenizer is None:
             return " ".join(str(i) for i in ids)
-        return tokenizer.decode(ids)
+        try:
+            return tokenizer.decode(ids, skip_special_tokens=True)
+        except TypeError:
+            return tokenizer.decode(ids)
+
+    def visible(ids: list, finish, sp) -> list:
+        """The token ids whose text is shown: the end-of-sequence or stop token that ended a completion is
+        reported in ``token_ids`` but is not part of the text."""
+        if finish == "stop" and ids and not sp.include_stop_str_in_output and \
+                (ids[-1] in sp.stop_token_ids or ids[-1] == engine.eos_token_id):
+            return ids[:-1]
+        return ids
 
     def chat_prompt(body: dict) -> list:
         from .chat_template import build_chat_prompt
@@ -109,18 +129,29 @@ def build_app(engine, model_name: str, tokenizer=None):
             return build_chat_prompt(tokenizer, encode, body.get("messages", []),
                                      add_generation_prompt=body.get("add_generation_prompt", True),
                                      continue_final_message=bool(body.get("continue_final_message", False)),
-                                     chat_template_kwargs=body.get("chat_template_kwargs"))
+                                     chat_template_kwargs=_template_kwargs(body))
         except ValueError as e:
             raise HTTPException(400, str(e))
 
     async def run(body: dict, prompt_ids: list, chat: bool):
+        tools, tool_choice = [], None
         try:
+            if chat:
+                from .tool_calls import structured_spec_for, validate_tools
+                tools, tool_choice = validate_tools(body)
+                forced = structured_spec_for(tools, tool_choice)
+                if forced is not None:
+                    body = dict(body, structured_outputs=forced)
             sp = _sampling_from_body(body)
             sp.verify()
             from ..platform import B200Platform
             B200Platform.validate_request(sp)
         except ValueError as e:
             raise HTTPException(400, str(e))
+        if sp.structured and tokenizer is not None and getattr(engine, "vocab_strings", None) is None:
+            # the grammar matcher needs the text of every token; built on the first structured request
+            from ..structured import vocab_strings_of
+            engine.vocab_strings = vocab_strings_of(tokenizer, engine.cfg.model.vocab_size)
         rid = f"{'chatcmpl' if chat else 'cmpl'}-{uuid.uuid4().hex}"
         created = int(time.time())
         kvp = body.get("kv_transfer_params")
@@ -168,10 +199,10 @@ def build_app(engine, model_name: str, tokenizer=None):
                 async for item in gen:
                     toks += item.new_token_ids
                     if item.error or m is None:
-                        yield i, decode(item.new_token_ids), item.new_token_ids, item.logprobs, \
-                            item.finish_reason, item, item.finished
+                        yield i, decode(visible(item.new_token_ids, item.finish_reason, sp)), item.new_token_ids, \
+                            item.logprobs, item.finish_reason, item, item.finished
                         continue
-                    text, hit = m.push(decode(toks), final=item.finished)
+                    text, hit = m.push(decode(visible(toks, item.finish_reason, sp)), final=item.finished)
                     yield i, text, item.new_token_ids, item.logprobs, \
                         ("stop" if hit else item.finish_reason), item, (hit or item.finished)
                     if hit:
@@ -207,6 +238,8 @@ def build_app(engine, model_name: str, tokenizer=None):
                     t.cancel()
 
         if body.get("stream"):
+            seen_text: dict = {}
+
             async def sse():
                 left = n
                 async for i, text, new_ids, lps_i, finish, item, ended in merged():
@@ -218,6 +251,16 @@ def build_app(engine, model_name: str, tokenizer=None):
                     payload = chunk_payload(text, finish, item if ended and not left else None, index=i)
                     if lps_i:
                         payload["choices"][0]["logprobs"] = _logprobs_payload(new_ids, lps_i, decode)
+                    if tools:
+                        # the text streams as it comes; calls found in a finished completion follow as one delta
+                        seen_text[i] = seen_text.get(i, "") + text
+                        if ended:
+                            from .tool_calls import extract_tool_calls
+                            _, calls = extract_tool_calls(seen_text[i], tools, tool_choice)
+                            if calls:
+                                ch = payload["choices"][0]
+                                ch["delta"]["tool_calls"] = [dict(c, index=j) for j, c in enumerate(calls)]
+                                ch["finish_reason"] = "tool_calls"
                     yield f"data: {json.dumps(payload)}\n\n"
                 yield "data: [DONE]\n\n"
             return StreamingResponse(sse(), media_type="text/event-stream")
@@ -234,9 +277,15 @@ def build_app(engine, model_name: str, tokenizer=None):
         payload = None
         for i, c in enumerate(acc):
             toks, last = c["toks"], c["last"]
-            text = "".join(c["text"]) if sp.stop else decode(toks)
+            text = "".join(c["text"]) if sp.stop else decode(visible(toks, c["finish"], sp))
             one = chunk_payload(text, c["finish"], last if i == n - 1 else None, index=i)
             ch = one["choices"][0]
+            if tools:
+                from .tool_calls import extract_tool_calls
+                content, calls = extract_tool_calls(text, tools, tool_choice)
+                if calls:
+                    ch["message"]["content"], ch["message"]["tool_calls"] = content, calls
+                    ch["finish_reason"] = "tool_calls"
             ch["token_ids"] = toks
             if c["lps"]:
                 ch["logprobs"] = _logprobs_payload(toks, c["lps"], decode)
@@ -256,7 +305,51 @@ def build_app(engine, model_name: str, tokenizer=None):
     @app.post("/v1/completions")
     async def completions(request: Request):
         body = await request.json()
-        return await run(body, encode(body.get("prompt", "")), chat=False)
+        prompt = body.get("prompt", "")
+        batch = isinstance(prompt, list) and len(prompt) > 1 and not isinstance(prompt[0], int)
+        if not batch:
+            return await run(body, encode(prompt), chat=False)
+        # several prompts in one request: they run concurrently and come back as choices in prompt order
+        if body.get("stream"):
+            raise HTTPException(400, "streaming takes one prompt per request")
+        import asyncio
+        parts = await asyncio.gather(*[run(body, encode(p), chat=False) for p in prompt])
+        merged = None
+        for k, resp in enumerate(parts):
+            one = json.loads(resp.body)
+            for ch in one["choices"]:
+                ch["index"] += k * int(body.get("n") or 1)
+            if merged is None:
+                merged = one
+            else:
+                merged["choices"] += one["choices"]
+                for key in ("prompt_tokens", "completion_tokens", "total_tokens"):
+                    merged["usage"][key] += one["usage"][key]
+        return JSONResponse(merged)
+
+    @app.post("/tokenize")
+    async def tokenize(request: Request):
+        body = await request.json()
+        ids = chat_prompt(body) if body.get("messages") is not None else encode(body.get("prompt", ""))
+        return {"tokens": ids, "count": len(ids), "max_model_len": engine.cfg.model.max_model_len}
+
+    @app.post("/detokenize")
+    async def detokenize(request: Request):
+        body = await request.json()
+        toks = body.get("tokens")
+        if not isinstance(toks, list) or any(not isinstance(t, int) for t in toks):
+            raise HTTPException(400, "tokens must be a list of token ids")
+        return {"prompt": decode(toks)}
+
+    @app.get("/version")
+    async def version():
+        from .. import __version__
+        return {"version": __version__}
+
+    @app.get("/ping")
+    @app.post("/ping")
+    async def ping():
+        return {"status": "ok"}
 
     @app.post("/v1/chat/completions")
     async def chat_completions(request: Request):

@@ -31,7 +31,12 @@ class RequestOutput:
 
     @staticmethod
     def from_request(req, detokenize=None) -> "RequestOutput":
-        text = detokenize(req.output_token_ids) if detokenize else None
+        shown = req.output_token_ids
+        sp = req.sampling_params
+        if req.status.value == "stop" and shown and not getattr(sp, "include_stop_str_in_output", False) and \
+                (shown[-1] in sp.stop_token_ids or shown[-1] == req.eos_token_id):
+            shown = shown[:-1]              # the token that ended the completion is not part of its text
+        text = detokenize(shown) if detokenize else None
         ttft = (req.first_token_time - req.arrival_time) if req.first_token_time else None
         lat = (req.finish_time - req.arrival_time) if req.finish_time else None
         return RequestOutput(
