@@ -319,3 +319,29 @@ def test_function_calling_batched_prompts_and_utility_routes():
         assert c.post("/detokenize", json={"tokens": "x"}).status_code == 400
         assert c.get("/version").json()["version"] and c.get("/ping").json() == {"status": "ok"}
     app.state.async_engine.shutdown()
+
+
+def test_metrics_histograms_and_vllm_compatible_names(client):
+    for n in (2, 5):
+        r = client.post("/v1/completions", json={"prompt": [9, 8, 7, 6], "max_tokens": n, "temperature": 0,
+                                                 "ignore_eos": True})
+        assert r.status_code == 200
+    text = client.get("/metrics").text
+    series = {}
+    for line in text.splitlines():
+        if line and not line.startswith("#"):
+            name, val = line.rsplit(" ", 1)
+            series[name] = float(val)
+    lab = 'model_name="tiny-llama"'
+    assert series["b200_generation_tokens_total"] == series[f"vllm:generation_tokens_total{{{lab}}}"] >= 7
+    assert series["vllm:request_success_total{" + lab + ',finished_reason="length"}'] >= 2
+    cnt = series[f"vllm:time_to_first_token_seconds_count{{{lab}}}"]
+    assert cnt >= 2 and series[f'vllm:time_to_first_token_seconds_bucket{{{lab},le="+Inf"}}'] == cnt
+    assert series[f"vllm:e2e_request_latency_seconds_sum{{{lab}}}"] >= series[f"vllm:time_to_first_token_seconds_sum{{{lab}}}"]
+    assert series[f"vllm:time_per_output_token_seconds_count{{{lab}}}"] >= 2
+    assert series[f"vllm:request_queue_time_seconds_count{{{lab}}}"] == cnt
+    assert series["b200_request_generation_tokens_sum"] >= 7 and series["b200_prefix_cache_queries_total"] >= 8
+    # cumulative buckets never decrease
+    buckets = [v for k, v in series.items() if k.startswith("b200_e2e_request_latency_seconds_bucket")]
+    assert buckets == sorted(buckets)
+    assert "# TYPE vllm:num_requests_running gauge" in text and "# TYPE b200_kv_cache_usage gauge" in text

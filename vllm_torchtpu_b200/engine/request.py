@@ -40,6 +40,7 @@ class Request:
     num_cached_tokens: int = 0          # prefix-cache hits at admission
     block_ids: list = field(default_factory=list)
     spec_token_ids: list = field(default_factory=list)
+    scheduled_time: Optional[float] = None     # first admission to the running set
     first_token_time: Optional[float] = None
     finish_time: Optional[float] = None
     error: Optional[str] = None

@@ -70,7 +70,7 @@ class Scheduler:
         self.abort_on_preemption = abort_on_preemption
         self.step_id = 0
         self.async_mode = scheduler_config.async_scheduling
-        self.stats = {"preemptions": 0, "prefix_hit_tokens": 0, "scheduled_tokens": 0}
+        self.stats = {"preemptions": 0, "prefix_hit_tokens": 0, "prefix_query_tokens": 0, "scheduled_tokens": 0}
         self._in_batch: set[str] = set()
         self._delayed_blocks: dict = {}
 
@@ -204,6 +204,9 @@ class Scheduler:
                 self.waiting.remove(req)
                 req.num_cached_tokens = max(req.num_cached_tokens, req.num_computed_tokens)
                 self.stats["prefix_hit_tokens"] += num_cached
+                if req.scheduled_time is None:
+                    req.scheduled_time = time.monotonic()
+                    self.stats["prefix_query_tokens"] += req.num_prompt_tokens
                 req.status = RequestStatus.RUNNING
                 self.running.append(req)
                 scheduled.append(self._make_sched(req, n, list(req.block_ids)))

@@ -50,6 +50,8 @@ class AsyncEngine:
         self._loop: Optional[asyncio.AbstractEventLoop] = None
         self.metrics = {"requests": 0, "output_tokens": 0, "prompt_tokens": 0, "steps": 0,
                         "ttft_sum": 0.0, "ttft_n": 0}
+        from .metrics import ServingMetrics
+        self.serving_metrics = ServingMetrics(engine.cfg.model.name)
         self._thread = threading.Thread(target=self._run, name="EngineLoop", daemon=True)
         self._thread.start()
 
@@ -105,6 +107,7 @@ class AsyncEngine:
                                           (req.prompt_logprobs or None) if done else None,
                                           getattr(req, "pooled", None) if done else None))
                     if done:
+                        self.serving_metrics.observe_finished(req)
                         eng.scheduler.requests.pop(rid, None)
             del finished
 

@@ -426,15 +426,11 @@ def build_app(engine, model_name: str, tokenizer=None):
     @app.get("/metrics")
     async def metrics():
         m = aeng.metrics
-        sch = engine.scheduler
-        lines = [f"b200_requests_total {m['requests']}", f"b200_prompt_tokens_total {m['prompt_tokens']}",
-                 f"b200_generation_tokens_total {m['output_tokens']}", f"b200_engine_steps_total {m['steps']}",
-                 f"b200_num_requests_running {len(sch.running)}", f"b200_num_requests_waiting {len(sch.waiting)}",
-                 f"b200_kv_cache_usage {sch.kv.pool.usage:.6f}", f"b200_preemptions_total {sch.stats['preemptions']}",
-                 f"b200_prefix_cache_hit_tokens_total {sch.stats['prefix_hit_tokens']}"]
+        aeng.serving_metrics.model_name = model_name
+        text = aeng.serving_metrics.render(m, engine)
         if m["ttft_n"]:
-            lines.append(f"b200_time_to_first_token_seconds_mean {m['ttft_sum'] / m['ttft_n']:.6f}")
-        return PlainTextResponse("\n".join(lines) + "\n")
+            text += f"b200_time_to_first_token_seconds_mean {m['ttft_sum'] / m['ttft_n']:.6f}\n"
+        return PlainTextResponse(text)
 
     @app.post("/reload_kernel")
     async def reload_kernel(request: Request):
