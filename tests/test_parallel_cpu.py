@@ -76,6 +76,15 @@ def test_dp2_with_expert_parallel_and_async_scheduling_terminates_together():
     assert _run(2, "dpep", "tiny-moe", "--async", "--closed-loop") == one
 
 
+def test_dp2_vocab_sharded_over_the_replicas_matches_single_process():
+    """Embedding table and lm_head sharded over the two replicas: ids are gathered and embeddings
+    reduce-scattered, hidden rows gathered (padded to the agreed row count) and logits exchanged by all-to-all;
+    uneven request counts, a replica that runs placeholder steps, and async scheduling."""
+    one = _run(1, "tp", "tiny-moe")
+    assert _run(2, "dpep", "tiny-moe", "--dp-vocab") == one
+    assert _run(2, "dpep", "tiny-moe", "--dp-vocab", "--async", "--closed-loop") == one
+
+
 def test_tp2_lora_matches_single_process(single):
     """Adapters sharded like the base weights (B rows of column-parallel targets, A columns of row-parallel
     targets with the partial update added before the all-reduce) reproduce the one-process tokens."""
@@ -125,3 +134,70 @@ def test_export_from_a_tensor_parallel_engine(tmp_path):
     meta["parallel"]["world_size"] = 3
     json.dump(meta, open(os.path.join(out, "metadata.json"), "w"))
     assert any("parallel plan" in p for p in validate_serving_dir(out))
+
+
+def test_dp_vocab_exchange_with_an_uneven_vocabulary():
+    """Three replicas as threads over an in-memory communicator, a vocabulary that does not divide by three,
+    different row counts padded to an agreed one: embeddings and logits equal the unsharded computation."""
+    import threading
+
+    import torch
+
+    from vllm_torchtpu_b200.parallel.dp_vocab import DpVocabParallel
+    n, V, H, T = 3, 10, 8, 5
+    shared, bar = [None] * n, threading.Barrier(n)
+
+    class ThreadComm:
+        def __init__(self, rank):
+            self.size, self.rank = n, rank
+
+        def _swap(self, x):
+            shared[self.rank] = x
+            bar.wait()
+            got = list(shared)
+            bar.wait()
+            return got
+
+        def all_gather(self, x, dim=0):
+            return torch.cat(self._swap(x), dim)
+
+        def reduce_scatter(self, x, dim=0):
+            tot = sum(self._swap(x))
+            k = tot.shape[0] // n
+            return tot[self.rank * k:(self.rank + 1) * k].clone()
+
+        def all_to_all(self, x, split_dim=0, concat_dim=0):
+            got = self._swap(x.chunk(n, dim=split_dim))
+            return torch.cat([got[src][self.rank] for src in range(n)], dim=concat_dim)
+
+    g = torch.Generator().manual_seed(0)
+    table, head = torch.randn(V, H, generator=g), torch.randn(V, H, generator=g)
+    ids = [torch.randint(0, V, (T,), generator=g) for _ in range(n)]
+    rows = [torch.randn(r + 1, H, generator=g) for r in range(n)]          # 1, 2 and 3 rows
+    out, errs = [None] * n, []
+
+    def work(r):
+        try:
+            dv = DpVocabParallel(ThreadComm(r), V)
+            t, h = dv.shard_rows(table), dv.shard_rows(head)
+            assert t.shape == (4, H) and dv.shard_rows(t) is t              # padded shard; idempotent
+            dv.rows = 4
+            out[r] = (dv.embed(ids[r], t), dv.logits(rows[r], h))
+            dv.rows = 2
+            if r == 2:
+                try:
+                    dv.logits(rows[r], h)
+                    errs.append("more rows than agreed were accepted")
+                except RuntimeError:
+                    pass
+        except Exception as e:                       # noqa: BLE001 - reported by the main thread
+            errs.append(repr(e))
+            bar.abort()
+    ts = [threading.Thread(target=work, args=(r,)) for r in range(n)]
+    [t.start() for t in ts]
+    [t.join(60) for t in ts]
+    assert not errs, errs
+    for r in range(n):
+        torch.testing.assert_close(out[r][0], table[ids[r]])
+        torch.testing.assert_close(out[r][1], rows[r] @ head.T, rtol=1e-5, atol=1e-5)
+        assert out[r][1].shape == (r + 1, V)

@@ -33,6 +33,8 @@ def main():
     elif mode == "dpep":
         kw["data_parallel_size"] = world
         kw["enable_expert_parallel"] = True
+    if "--dp-vocab" in sys.argv:
+        kw["additional_config"] = {"dp_vocab_parallel": True}
     llm = LLM(model, device="cpu", max_num_seqs=8, max_num_batched_tokens=64, block_size=16,
               num_gpu_blocks_override=64, async_scheduling="--async" in sys.argv, **kw)
     rng = np.random.RandomState(0)
@@ -88,6 +90,10 @@ def main():
         # every rank calls the exporter; rank 0 writes the directory
         from vllm_torchtpu_b200.export import export_serving_dir
         export_serving_dir(llm, sys.argv[sys.argv.index("--export") + 1])
+    if "--dp-vocab" in sys.argv:
+        # each replica keeps half of the embedding table and of the lm_head
+        m = llm.engine.runner.model
+        assert m.embed.shape[0] == -(-vocab // world) and m.lm_head.shape[0] == -(-vocab // world), m.embed.shape
     if rank == 0:
         print("RESULT " + json.dumps({"tokens": toks}), flush=True)
     if world > 1:

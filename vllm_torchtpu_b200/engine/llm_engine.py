@@ -204,6 +204,9 @@ class LLMEngine:
         if not prompt_token_ids:
             raise ValueError("empty prompt")
         sp.verify()
+        if sp.prompt_logprobs is not None and getattr(self.runner.model, "dp_vocab", None) is not None:
+            raise ValueError("prompt_logprobs are not available with dp_vocab_parallel (the lm_head exchange runs "
+                             "once per step on every replica)")
         if sp.has_logit_adjust and (self.cfg.speculative or self.cfg.parallel.pipeline_parallel_size > 1):
             # verification rows and pipeline stages sample without the per-step logit edits
             raise ValueError("penalties, logit_bias, allowed_token_ids and min_p are not supported together with "
@@ -271,6 +274,8 @@ class LLMEngine:
         items = list(named_tensors.items()) if isinstance(named_tensors, dict) else list(named_tensors)
         from ..models.loader import load_named_tensors
         load_named_tensors(self.runner.model, iter(items), {n for n, _ in items}, source="update_weights")
+        if getattr(self.runner.model, "dp_vocab", None) is not None:
+            self.runner.model.enable_dp_vocab(self.runner.model.dp_vocab)      # a replaced table is sharded again
         self.scheduler.kv.pool.reset_prefix_cache()
         mega = getattr(self.runner.model, "decode_mega", None)
         if mega is not None:
@@ -364,7 +369,13 @@ class LLMEngine:
                          or any(o.scheduled for o, _ in self._inflight)) else 0
             throttled = hasattr(self.scheduler, "throttle_prefills")
             pending = self.scheduler.pending_prefill_tokens() if throttled else 0
-            agreed = DeviceCommunicator(st.dp, None).cpu_all_reduce_max([t_pad, eager, busy, pending])
+            dpv = getattr(self.runner.model, "dp_vocab", None)
+            rows = self.runner.logits_rows(out) if dpv is not None else 0
+            agreed = DeviceCommunicator(st.dp, None).cpu_all_reduce_max([t_pad, eager, busy, pending, rows])
+            if dpv is not None:
+                # every replica pads its lm_head rows to one count that follows from the agreed values alone: a
+                # decode step padded up to an agreed request bucket projects that many rows
+                dpv.rows = max(agreed[4], agreed[0] if agreed[0] in self.cfg.request_buckets else 0)
             self._dp_group_busy = bool(agreed[2])
             if throttled:
                 # replicas admit prefills in the same steps, so that one replica's long prefill does

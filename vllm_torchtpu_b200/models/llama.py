@@ -303,8 +303,20 @@ class LlamaForCausalLM:
         h, _ = ops.fused_add_rms_norm(hidden, residual, self.norm, self.cfg.rms_norm_eps)
         return h
 
+    def enable_dp_vocab(self, dp_vocab) -> None:
+        """Keep only this data-parallel replica's rows of the embedding table and the lm_head
+        (``parallel/dp_vocab.py``); idempotent, called again after the weights are replaced."""
+        tied = self.lm_head is self.embed
+        if self.embed is not None:
+            self.embed = dp_vocab.shard_rows(self.embed)
+        if self.lm_head is not None:
+            self.lm_head = self.embed if tied else dp_vocab.shard_rows(self.lm_head)
+        self.dp_vocab = dp_vocab
+
     def compute_logits(self, hidden_rows):
         """hidden_rows [R, H] → logits [R, V] (all-gathered over the vocab shards)."""
+        if getattr(self, "dp_vocab", None) is not None:
+            return self.dp_vocab.logits(hidden_rows, self.lm_head)
         logits = ops.gemm(hidden_rows, self.lm_head)
         comm = get_tp_comm()
         if comm.size > 1 and self.vocab_shard is not None:

@@ -202,8 +202,26 @@ class ModelRunner:
             per_rank = min(-(-self.max_tokens // st.tp.size), envs.B200_MOE_EP_CALL_TOKENS)
             ensure_ep_heap(per_rank, self.mcfg.num_experts_per_tok, self.mcfg.hidden_size,
                            self.mcfg.moe_intermediate_size, self.mcfg.num_experts)
+        if (self.cfg.additional or {}).get("dp_vocab_parallel"):
+            self._enable_dp_vocab()
         logger.info("model %s loaded: %.2f GB weights on this rank in %.1fs", self.mcfg.name,
                     self.model.weight_bytes() / 1e9, time.time() - t0)
+
+    def _enable_dp_vocab(self) -> None:
+        """Shard the embedding table and the lm_head over the data-parallel replicas (opt-in through
+        ``additional_config={"dp_vocab_parallel": true}``)."""
+        st = get_state()
+        if not (st.dp.size > 1 and st.expert_parallel):
+            raise ValueError("dp_vocab_parallel needs data-parallel replicas coupled by expert parallelism "
+                             "(they step in lockstep, which the exchanges rely on)")
+        if st.tp.size > 1 or st.pp.size > 1 or self.dcp_size > 1:
+            raise ValueError("dp_vocab_parallel is built for replicas of one GPU (no TP / PP / DCP inside a replica)")
+        if self.cfg.speculative:
+            raise ValueError("dp_vocab_parallel and speculative decoding are exclusive (drafters call the lm_head a "
+                             "data-dependent number of times)")
+        from ..parallel.communicator import DeviceCommunicator
+        from ..parallel.dp_vocab import DpVocabParallel
+        self.model.enable_dp_vocab(DpVocabParallel(DeviceCommunicator(st.dp, None), self.mcfg.vocab_size))
 
     def _alloc_step_buffers(self) -> None:
         mb = self.batch.max_blocks
@@ -632,6 +650,12 @@ class ModelRunner:
     def _embed(self, ids, token_src):
         if self.model.embed is None:
             return None
+        dpv = getattr(self.model, "dp_vocab", None)
+        if dpv is not None:
+            # the table is sharded over the replicas: resolve the on-device token feedback first, then exchange
+            use_last = token_src >= 0
+            real = torch.where(use_last, self.last_tokens[token_src.clamp_min(0).long()], ids)
+            return dpv.embed(real, self.model.embed)
         if self.is_cuda:
             return ops.cuda_ops().embedding(ids, self.model.embed, token_src, self.last_tokens)
         use_last = token_src >= 0
@@ -662,6 +686,17 @@ class ModelRunner:
         if decode_only and not self.cfg.enforce_eager and self.is_cuda:
             return pad_to_bucket(len(scheds), self.cfg.request_buckets), 0
         return T, 0 if decode_only else 1
+
+    def logits_rows(self, out) -> int:
+        """Rows this step hands to the lm_head before any lockstep padding (for the replicas' agreement when
+        the vocabulary is sharded over them)."""
+        n = len(out.scheduled)
+        if not n:
+            return 1                                   # a placeholder step projects one row
+        decode_only = all(s.num_new_tokens == 1 and s.start > 0 for s in out.scheduled)
+        if decode_only and not self.cfg.enforce_eager and self.is_cuda:
+            return pad_to_bucket(n, self.cfg.request_buckets)
+        return n
 
     def execute_dummy_batch(self, T: int) -> None:
         """A step without requests for a replica that must take part in the group's collectives:
@@ -751,6 +786,7 @@ class ModelRunner:
         use_graph = (self.is_cuda and p["decode_only"] and not self.cfg.enforce_eager
                      and p["T_pad"] == p["R_pad"] and envs.B200_CUDA_GRAPHS and self._step_bitmask is None and lora_idx is None
                      and self._step_extras is None and not self.keep_hidden and self.dcp_size == 1
+                     and getattr(self.model, "dp_vocab", None) is None
                      and get_state().pp.size == 1)          # pipeline stages hand off through host threads
         if use_graph:
             key = (R, p["all_greedy"])
