@@ -76,6 +76,14 @@ def test_dp2_with_expert_parallel_and_async_scheduling_terminates_together():
     assert _run(2, "dpep", "tiny-moe", "--async", "--closed-loop") == one
 
 
+def test_pipelined_moe_plane_matches_single_process():
+    """The expert-parallel all-gather plane in token chunks whose collectives are started ahead of / finished
+    behind the neighbouring chunks' expert GEMMs: same tokens, under TP-coupled EP and under DP lockstep."""
+    one = _run(1, "tp", "tiny-moe")
+    assert _run(2, "ep", "tiny-moe", "--moe-pipeline") == one
+    assert _run(2, "dpep", "tiny-moe", "--moe-pipeline") == one
+
+
 def test_dp2_vocab_sharded_over_the_replicas_matches_single_process():
     """Embedding table and lm_head sharded over the two replicas: ids are gathered and embeddings
     reduce-scattered, hidden rows gathered (padded to the agreed row count) and logits exchanged by all-to-all;

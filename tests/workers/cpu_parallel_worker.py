@@ -33,6 +33,9 @@ def main():
     elif mode == "dpep":
         kw["data_parallel_size"] = world
         kw["enable_expert_parallel"] = True
+    if "--moe-pipeline" in sys.argv:
+        # the all-gather plane in three chunks per step, chunks of at least two tokens
+        os.environ["B200_MOE_PIPELINE_CHUNKS"], os.environ["B200_MOE_PIPELINE_MIN_CHUNK_TOKENS"] = "3", "2"
     if "--dp-vocab" in sys.argv:
         kw["additional_config"] = {"dp_vocab_parallel": True}
     llm = LLM(model, device="cpu", max_num_seqs=8, max_num_batched_tokens=64, block_size=16,
@@ -94,6 +97,9 @@ def main():
         # each replica keeps half of the embedding table and of the lm_head
         m = llm.engine.runner.model
         assert m.embed.shape[0] == -(-vocab // world) and m.lm_head.shape[0] == -(-vocab // world), m.embed.shape
+    if "--moe-pipeline" in sys.argv:
+        from vllm_torchtpu_b200.layers import moe as moe_layer
+        assert moe_layer.PIPELINED_CALLS > 0
     if rank == 0:
         print("RESULT " + json.dumps({"tokens": toks}), flush=True)
     if world > 1:

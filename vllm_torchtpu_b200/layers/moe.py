@@ -51,6 +51,8 @@ def expert_placement(num_experts: int, ep_size: int, policy: str = "linear",
     raise ValueError(policy)
 
 
+PIPELINED_CALLS = 0          # calls of the pipelined all-gather plane (tests and diagnostics)
+
 class FusedMoE:
     def __init__(self, name: str, cfg, device, quant_config=None):
         st = get_state()
@@ -151,10 +153,47 @@ class FusedMoE:
                 and getattr(comm.heap, "ep_state", None) is not None
                 and x.shape[0] >= envs.B200_MOE_FUSED_EP_MIN_TOKENS and hasattr(self.method, "apply_fused_ep")):
             return self._forward_fused_ep(x, topk_ids, topk_w, comm)
+        chunks = envs.B200_MOE_PIPELINE_CHUNKS
+        if chunks > 1 and x.shape[0] >= chunks * envs.B200_MOE_PIPELINE_MIN_CHUNK_TOKENS and comm.size > 1 and \
+                not (x.is_cuda and torch.cuda.is_current_stream_capturing()):
+            return self._forward_pipelined(x, topk_ids, topk_w, comm, chunks)
         # all-gather / reduce-scatter plane: rows must be equal on every rank (DP lockstep pads them)
         hx, hw, hi = comm.dispatch(x, topk_w, topk_ids)
         y = self.method.apply(self, hx, hi, hw)
         return comm.combine(y)
+
+    def _forward_pipelined(self, x, topk_ids, topk_w, comm, chunks: int):
+        """All-gather -> grouped expert GEMMs -> reduce-scatter over token chunks, with the collectives of the
+        neighbouring chunks in flight while a chunk's experts run: the gather of chunk i + 1 is started before
+        the experts of chunk i, the reduce-scatter of chunk i runs under the experts of chunk i + 1.  The
+        collectives are issued in the same order on every rank (the chunk bounds follow from the common row
+        count) and run on the process group's own stream; ``wait`` orders them against this stream.
+        (reference: src/vllm_torchtpu/layers/adapter/pipelined_fused_moe.py:14-60 - chunked all-gather and
+        reduce-scatter overlapped with the grouped matmuls)"""
+        global PIPELINED_CALLS
+        PIPELINED_CALLS += 1
+        T = x.shape[0]
+        step = -(-T // chunks)
+        bounds = [(lo, min(T, lo + step)) for lo in range(0, T, step)]
+
+        def start(i):
+            lo, hi = bounds[i]
+            return [comm.all_gather_start(t[lo:hi]) for t in (x, topk_w, topk_ids)]
+        pending = start(0)
+        tails = []
+        for i in range(len(bounds)):
+            nxt = start(i + 1) if i + 1 < len(bounds) else None
+            for _, work in pending:
+                work.wait()
+            hx, hw, hi_ = (t for t, _ in pending)
+            y = self.method.apply(self, hx, hi_, hw)
+            tails.append(comm.reduce_scatter_start(y))
+            pending = nxt
+        outs = []
+        for get, work in tails:
+            work.wait()
+            outs.append(get())
+        return torch.cat(outs, 0)
 
     def _forward_fused_ep(self, x, topk_ids, topk_w, comm):
         """Fused dispatch/combine plane.  The ranks of a TP group hold identical tokens, so each

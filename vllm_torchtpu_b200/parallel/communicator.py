@@ -111,6 +111,27 @@ class DeviceCommunicator:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group.cpu_group)
         return t.tolist()
 
+    # ---- collectives that return before they finish (pipelined MoE plane) --------
+    def all_gather_start(self, x: torch.Tensor):
+        """Rows of every rank, concatenated on dim 0: (output tensor, handle); the output is valid after
+        ``handle.wait()``."""
+        out = torch.empty((self.size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        work = dist.all_gather_into_tensor(out, x.contiguous(), group=self.group.device_group, async_op=True)
+        return out, work
+
+    def reduce_scatter_start(self, x: torch.Tensor):
+        """Sum over the ranks, this rank's slice of dim 0: (getter, handle); ``getter()`` after
+        ``handle.wait()`` gives the slice."""
+        x = x.contiguous()
+        assert x.shape[0] % self.size == 0
+        n = x.shape[0] // self.size
+        if not x.is_cuda:
+            work = dist.all_reduce(x, group=self.group.device_group, async_op=True)     # gloo has no reduce-scatter
+            return (lambda: x[self.rank * n:(self.rank + 1) * n]), work
+        out = torch.empty((n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        work = dist.reduce_scatter_tensor(out, x, group=self.group.device_group, async_op=True)
+        return (lambda: out), work
+
     # ---- MoE data plane ---------------------------------------------------------
     def dispatch(self, hidden, topk_w, topk_ids):
         if self.size == 1:
