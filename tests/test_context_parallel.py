@@ -56,3 +56,48 @@ def test_dcp_sharding_and_merge():
     lses.append(torch.full((T, H), float("-inf")))
     got, _ = ref.merge_attn_states(outs, lses)
     torch.testing.assert_close(got, full, rtol=1e-4, atol=1e-4)
+
+
+def test_pcp_step_split_covers_every_token_once_and_balances_work():
+    """The step plan of the engine's prefill context parallelism: pieces are a partition of each chunk, rank 0 owns
+    the piece that ends it, causal work is balanced, short chunks and decode tokens stay replicated."""
+    from types import SimpleNamespace
+
+    import numpy as np
+
+    from vllm_torchtpu_b200.engine.scheduler import ScheduledRequest
+    from vllm_torchtpu_b200.runner.pcp_step import bind_rows, piece_bounds, split_step
+    from vllm_torchtpu_b200.sampling_params import SamplingParams
+    for lo, n, P in ((0, 64, 2), (37, 101, 4), (5, 16, 2)):
+        b = piece_bounds(lo, n, P)
+        assert b[0][0] == lo and b[-1][1] == lo + n and all(x[1] == y[0] for x, y in zip(b, b[1:]))
+        assert all(hi > lo_ for lo_, hi in b) and max(hi - l for l, hi in b) - min(hi - l for l, hi in b) <= 1
+        work = [sum((hi * (hi + 1) - l * (l + 1)) // 2 for l, hi in (b[r], b[2 * P - 1 - r])) for r in range(P)]
+        assert max(work) / min(work) < 1.25
+
+    def sched(rid, start, n, **sp):
+        req = SimpleNamespace(request_id=rid, sampling_params=SamplingParams(**sp))
+        return ScheduledRequest(req, n, start, samples=True)
+    scheds = [sched("dec", 40, 1), sched("long", 64, 100), sched("short", 0, 10), sched("plp", 0, 90, prompt_logprobs=1)]
+    slot_of = {"dec": 0, "long": 1, "short": 2, "plp": 3}
+    bt = np.arange(4 * 32, dtype=np.int32).reshape(4, 32)            # request i owns blocks 32 i .. 32 i + 31
+    seen = []
+    for rank in range(2):
+        local, plan = split_step(scheds, 2, rank, 16, slot_of, bt, 16, "cpu")
+        assert [s.request.request_id for s in local] == ["dec", "short", "plp", "long", "long"]
+        head, tail = local[3], local[4]
+        assert not head.samples and tail.samples and plan.counts == [50, 50] and plan.own == 50
+        seen += list(range(head.start, head.start + head.num_new_tokens))
+        seen += list(range(tail.start, tail.start + tail.num_new_tokens))
+        if rank == 0:
+            assert tail.start + tail.num_new_tokens == 164          # the chunk's last token is on rank 0
+        # the other rank's rows: positions of its two pieces, slots inside the request's own blocks
+        other = split_step(scheds, 2, 1 - rank, 16, slot_of, bt, 16, "cpu")[0]
+        want = [p for s in other[3:] for p in range(s.start, s.start + s.num_new_tokens)]
+        assert plan.others_pos.tolist() == want
+        assert plan.others_slots.tolist() == [(32 + p // 16) * 16 + p % 16 for p in want]
+        assert plan.others_idx.tolist() == list(range((1 - rank) * 50, (1 - rank) * 50 + 50))
+        bind_rows(plan, [local[0], local[1], local[2], head, tail], "cpu")
+        assert plan.mute_rows == [3] and plan.fix_rows.tolist() == [4]
+    assert sorted(seen) == list(range(64, 164))
+    assert split_step(scheds[:1] + scheds[2:3], 2, 0, 16, slot_of, bt, 16, "cpu")[1] is None

@@ -76,6 +76,16 @@ def test_dp2_with_expert_parallel_and_async_scheduling_terminates_together():
     assert _run(2, "dpep", "tiny-moe", "--async", "--closed-loop") == one
 
 
+def test_prefill_context_parallel_in_the_engine_matches_single_process(single):
+    """Prefill chunks cut into head-tail pieces over two ranks (a 23-token prompt in one chunk, a 70-token one in
+    chunks of 64 + 6, the short prompt and all decode steps replicated): every rank's cache is completed from the
+    gathered keys / values and all ranks sample the tokens of the single-process engine."""
+    assert _run(2, "pcp", "tiny-llama") == single
+    assert _run(2, "pcp", "tiny-llama", "--async") == single
+    # two PCP ranks of two tensor-parallel ranks each
+    assert _run(4, "pcp", "tiny-llama", "--tp2", timeout=400) == single
+
+
 def test_pipelined_moe_plane_matches_single_process():
     """The expert-parallel all-gather plane in token chunks whose collectives are started ahead of / finished
     behind the neighbouring chunks' expert GEMMs: same tokens, under TP-coupled EP and under DP lockstep."""

@@ -25,6 +25,11 @@ def main():
         kw["tensor_parallel_size"] = world
         kw["decode_context_parallel_size"] = world
         kw["cp_kv_cache_interleave_size"] = 2 if "--il2" in sys.argv else 1
+    elif mode == "pcp":
+        # prefill chunks of 16 tokens and more are cut into pieces over the ranks
+        os.environ["B200_PCP_MIN_TOKENS"] = "16"
+        kw["prefill_context_parallel_size"] = world if "--tp2" not in sys.argv else world // 2
+        kw["tensor_parallel_size"] = 1 if "--tp2" not in sys.argv else 2
     elif mode == "pp":
         kw["pipeline_parallel_size"] = world
     elif mode == "ep":
@@ -97,6 +102,8 @@ def main():
         # each replica keeps half of the embedding table and of the lm_head
         m = llm.engine.runner.model
         assert m.embed.shape[0] == -(-vocab // world) and m.lm_head.shape[0] == -(-vocab // world), m.embed.shape
+    if mode == "pcp":
+        assert llm.engine.runner.stats.get("pcp_split_steps", 0) >= 2, llm.engine.runner.stats
     if "--moe-pipeline" in sys.argv:
         from vllm_torchtpu_b200.layers import moe as moe_layer
         assert moe_layer.PIPELINED_CALLS > 0

@@ -105,6 +105,8 @@ _decl("B200_FP8_ROWS_SKIP_PROMOTE", bool, False,
 _decl("B200_SAFETENSORS_PREFETCH", bool, True, "checkpoint loading: ask the kernel to read the next file ahead")
 _decl("B200_LOAD_EVICT_PAGE_CACHE", bool, False,
       "checkpoint loading: drop every consumed file from the page cache (large checkpoints on small hosts)")
+_decl("B200_PCP_MIN_TOKENS", int, 512,
+      "prefill context parallelism: shortest prefill chunk that is split over the ranks (shorter ones are replicated)")
 _decl("B200_MOE_PIPELINE_CHUNKS", int, 0,
       "expert-parallel all-gather plane: split a step's tokens into this many chunks and overlap each chunk's "
       "collectives with its neighbours' expert GEMMs (0 / 1: off)")

@@ -33,10 +33,21 @@ class PagedAttention:
         self.k_scale, self.v_scale = k_scale, v_scale
 
     def forward(self, qkv: torch.Tensor, kv_cache: torch.Tensor, meta: AttentionMetadata) -> torch.Tensor:
-        q = ops.rope_and_cache(qkv, meta.positions, self.inv_freq, kv_cache, meta.slot_mapping,
+        positions, slots = meta.positions, meta.slot_mapping
+        T_local = qkv.shape[0]
+        if meta.pcp is not None:
+            # prefill context parallelism: the k / v columns of the other ranks' pieces are gathered and stored
+            # with this rank's own, so the pages are complete before the attention reads them
+            from ..parallel.communicator import get_pcp_comm
+            from ..runner.pcp_step import gather_remote_kv
+            qkv, positions, slots = gather_remote_kv(meta.pcp, qkv, positions, slots,
+                                                     self.num_q_heads * self.head_dim, meta.num_tokens, get_pcp_comm())
+        q = ops.rope_and_cache(qkv, positions, self.inv_freq, kv_cache, slots,
                                self.num_q_heads, self.num_kv_heads, self.head_dim,
                                self.rope_interleaved, self.q_norm_w, self.k_norm_w, self.eps,
                                self.k_scale, self.v_scale)
+        if meta.pcp is not None:
+            q = q[:T_local]
         if meta.dcp_size > 1:
             from ..parallel.dcp import dcp_attention
             out = dcp_attention(self, q, kv_cache, meta)

@@ -163,6 +163,17 @@ def get_ep_comm() -> DeviceCommunicator:
     return _ep_comm
 
 
+_pcp_comm: Optional[DeviceCommunicator] = None
+
+
+def get_pcp_comm() -> DeviceCommunicator:
+    global _pcp_comm
+    st = get_state()
+    if _pcp_comm is None or _pcp_comm.group is not st.pcp:
+        _pcp_comm = DeviceCommunicator(st.pcp, None)
+    return _pcp_comm
+
+
 def get_dcp_comm() -> DeviceCommunicator:
     global _dcp_comm
     st = get_state()

@@ -43,6 +43,15 @@ class PcpStaticSupportValidator:
             raise ValueError("sliding-window models are not supported under PCP")
         if self.cfg.speculative:
             raise ValueError("speculative decoding is not supported under PCP")
+        if m.is_mla or getattr(m, "is_hybrid_gdn", False):
+            raise ValueError("PCP in the engine splits GQA attention layers; latent-attention and linear-attention "
+                             "models are not supported")
+        if p.enable_expert_parallel or p.data_parallel_size > 1:
+            raise ValueError("PCP ranks compute different numbers of rows per step; expert parallelism and "
+                             "data-parallel lockstep need equal rows and are not supported together with it")
+        if p.decode_context_parallel_size > 1:
+            raise ValueError("PCP completes every rank's KV cache; it is not combined with a position-sharded "
+                             "cache (DCP)")
 
 
 @dataclass

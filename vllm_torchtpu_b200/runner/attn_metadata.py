@@ -38,6 +38,7 @@ class AttentionMetadata:
     state_slots: Optional[torch.Tensor] = None
     # verification step on a hybrid: recurrent layers hand their snapshots and inputs to this object
     state_rollback: Optional[object] = None
+    pcp: Optional[object] = None          # PcpStepPlan of a step whose prefill chunks are split over PCP ranks
     # padded sizes when running inside a captured graph
     padded_num_reqs: Optional[int] = None
     padded_num_tokens: Optional[int] = None

@@ -446,6 +446,10 @@ class ModelRunner:
             self._prompt_logprobs(hidden, residual, ex)
         rows = self._select_rows(hidden, residual, meta.logits_indices)
         h = self.model.finalize(*rows)
+        if getattr(meta, "pcp", None) is not None:
+            from ..parallel.communicator import get_pcp_comm
+            from .pcp_step import broadcast_sample_rows
+            h = broadcast_sample_rows(meta.pcp, h, get_pcp_comm())
         if self.keep_hidden:
             self._last_h = h
         if self.keep_all_hidden:
@@ -730,12 +734,32 @@ class ModelRunner:
             self._update_batch(out)
             return StepResult([], [], None, None, 0)
         self._update_batch(out)
+        self._pcp_plan = None
+        st_ = get_state()
+        if st_.pcp.size > 1:
+            # long prefill chunks are cut into pieces and this rank computes two of them (runner/pcp_step.py)
+            from types import SimpleNamespace
+            from .pcp_step import bind_rows, split_step
+            mm = self.mm_manager.items if self.mm_manager is not None else {}
+            local, self._pcp_plan = split_step(out.scheduled, st_.pcp.size, st_.pcp.rank_in_group,
+                                               envs.B200_PCP_MIN_TOKENS, self.batch.slot_of, self.batch.block_table,
+                                               self.block_size, self.device, has_mm=lambda rid: rid in mm)
+            if self._pcp_plan is not None:
+                if pad_tokens_to:
+                    raise RuntimeError("prefill context parallelism and data-parallel lockstep are exclusive")
+                out = SimpleNamespace(scheduled=local)
         p = self._prepare_inputs(out, pad_tokens_to=abs(pad_tokens_to))
         if pad_tokens_to < 0:
             p["decode_only"] = False
         bufs, n, R, T = p["bufs"], p["n"], p["R_pad"], p["T_pad"]
+        if self._pcp_plan is not None:
+            bind_rows(self._pcp_plan, p["scheds"], self.device)
+            # a piece that ends no chunk stores no token (its slot belongs to the piece that does)
+            bufs.host_view("batch_slots", R)[self._pcp_plan.mute_rows] = -1
+            self.stats["pcp_split_steps"] = self.stats.get("pcp_split_steps", 0) + 1
         self.stats["h2d_bytes"] += bufs.upload(R)
         meta = self._make_meta(p)
+        meta.pcp = self._pcp_plan
         self._pending_rollback = None
         if p.get("has_spec") and self.mcfg.is_hybrid_gdn:
             # recurrent layers fold all k + 1 rows into their state: keep what it takes to undo rejected ones
