@@ -210,18 +210,52 @@ def test_kda_recurrence_reduces_to_gdn_and_is_chunk_invariant():
     assert float(gb.min()) >= -5.0 and float(gb.max()) <= 0.0
 
 
-def test_kimi_linear_hybrid_engine_is_chunk_and_batch_invariant():
-    """KDA layers (conv window + per-channel-decay state in slot pools) next to full attention: chunked
-    prefill and batching leave the greedy tokens unchanged."""
+@pytest.mark.parametrize("preset", ["tiny-kda", "tiny-kda-mla"])
+def test_kimi_linear_hybrid_engine_is_chunk_and_batch_invariant(preset):
+    """KDA layers (conv window + per-channel-decay state in slot pools) next to full attention - grouped-query
+    attention, or latent attention without rotary embeddings as in the published layout: chunked prefill and
+    batching leave the greedy tokens unchanged."""
     sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
-    one = LLM("tiny-kda", device="cpu", max_num_seqs=4, max_num_batched_tokens=256, block_size=16, init_dist=False)
+    one = LLM(preset, device="cpu", max_num_seqs=4, max_num_batched_tokens=256, block_size=16, init_dist=False)
     want = [one.generate([p], sp)[0].outputs[0].token_ids for p in _prompts()]
-    many = LLM("tiny-kda", device="cpu", max_num_seqs=4, max_num_batched_tokens=16, block_size=16, init_dist=False)
+    many = LLM(preset, device="cpu", max_num_seqs=4, max_num_batched_tokens=16, block_size=16, init_dist=False)
     got = [o.outputs[0].token_ids for o in many.generate(_prompts(), sp)]
     assert got == want
 
 
-@pytest.mark.parametrize("preset", ["tiny-gdn", "tiny-kda"])
+def test_kimi_linear_latent_attention_layers_and_config_mapping():
+    """The Kimi-Linear configuration with latent attention maps onto the hybrid model: KDA layers keep state pools,
+    the full-attention layers get a latent cache, and without rotary embeddings the output does not depend on
+    where the rotary base sits."""
+    from vllm_torchtpu_b200.config import ModelConfig, model_preset
+    hf = {"architectures": ["KimiLinearForCausalLM"], "num_hidden_layers": 4, "hidden_size": 256, "vocab_size": 1024,
+          "num_attention_heads": 4, "num_key_value_heads": 4, "head_dim": 72, "intermediate_size": 512,
+          "kv_lora_rank": 64, "qk_nope_head_dim": 32, "qk_rope_head_dim": 16, "v_head_dim": 32, "mla_use_nope": True,
+          "linear_attn_config": {"full_attn_layers": [4], "kda_layers": [1, 2, 3], "num_heads": 4, "head_dim": 32,
+                                 "short_conv_kernel_size": 4}, "torch_dtype": "float32"}
+    mc = ModelConfig.from_hf_dict(hf)
+    assert mc.architecture == "kimi_linear" and mc.is_mla and mc.mla_use_nope and mc.kv_lora_rank == 64
+    llm = LLM("tiny-kda-mla", device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    m = llm.engine.runner.model
+    kinds = [type(l.self_attn).__name__ for l in m.layers]
+    assert kinds == ["KimiDeltaAttention"] * 3 + ["MLAAttention"]
+    caches = llm.engine.runner.kv_caches
+    assert isinstance(caches[0], tuple) and caches[3].shape[1:] == (16, 64 + 16)
+    assert m.kv_bytes_per_block(16, torch.float32) == 16 * 80 * 4
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    base = llm.generate(_prompts(), sp)
+    cfg2 = model_preset("tiny-kda-mla")
+    cfg2.rope_theta = 123.0                                   # no rotary embeddings: the base must not matter
+    other = LLM(cfg2, device="cpu", max_num_seqs=4, block_size=16, init_dist=False).generate(_prompts(), sp)
+    assert [o.outputs[0].token_ids for o in other] == [o.outputs[0].token_ids for o in base]
+    assert float(m.layers[3].self_attn.inv_freq.abs().max()) == 0.0
+    cfg3 = model_preset("tiny-kda-mla")
+    cfg3.mla_use_nope = False
+    roped = LLM(cfg3, device="cpu", max_num_seqs=4, block_size=16, init_dist=False)
+    assert float(roped.engine.runner.model.layers[3].self_attn.inv_freq.abs().max()) == 1.0
+
+
+@pytest.mark.parametrize("preset", ["tiny-gdn", "tiny-kda", "tiny-kda-mla"])
 def test_speculative_decoding_on_hybrids_rolls_recurrent_state_back(preset):
     """Verification steps fold k + 1 rows into the recurrent state; rejected drafts are undone from a snapshot
     plus a replay of the accepted rows, so the tokens equal plain decoding.  The drafter of this test knows the

@@ -77,6 +77,7 @@ class ModelConfig:
     qk_nope_head_dim: int = 0
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
+    mla_use_nope: bool = False           # latent attention without rotary embeddings (Kimi-Linear: positions come from the KDA layers)
     # sparse MLA (DSA indexer)
     index_topk: int = 0
     index_n_heads: int = 0
@@ -245,6 +246,15 @@ class ModelConfig:
             mc.moe_intermediate_size = cfg.get("moe_intermediate_size", 0)
             mc.num_shared_experts = cfg.get("num_shared_experts", 0)
             del kda_layers
+            if cfg.get("kv_lora_rank"):
+                # the full-attention layers are multi-head latent attention (the published checkpoints)
+                mc.q_lora_rank = cfg.get("q_lora_rank") or 0
+                mc.kv_lora_rank = cfg["kv_lora_rank"]
+                mc.qk_nope_head_dim = cfg["qk_nope_head_dim"]
+                mc.qk_rope_head_dim = cfg["qk_rope_head_dim"]
+                mc.v_head_dim = cfg["v_head_dim"]
+                mc.mla_use_nope = bool(cfg.get("mla_use_nope", False))
+                mc.rope_interleaved = True
         elif arch.startswith("Qwen3"):
             mc.architecture, mc.qk_norm = "llama", True
         elif arch.startswith(("DeepseekV3", "DeepseekV2", "DeepseekV32")):
@@ -277,7 +287,7 @@ class ModelConfig:
             raise ValueError(f"partial_rotary_factor {prf}: rotary embeddings over a part of the head are not built")
         if cfg.get("attn_output_gate"):
             raise ValueError("attn_output_gate (gated attention output) is not built")
-        if mc.architecture != "deepseek_v3" and mc.head_dim not in (64, 128):
+        if not mc.is_mla and mc.head_dim not in (64, 128):
             raise ValueError(f"head_dim {mc.head_dim}: the attention kernels are built for 64 and 128")
         q = cfg.get("quantization_config")
         if q:
@@ -338,6 +348,13 @@ def model_preset(name: str) -> ModelConfig:
         return _preset(name="tiny-kda", architecture="kimi_linear", dtype=torch.float32,
                        num_layers=4, full_attention_interval=4, gdn_num_k_heads=4, gdn_num_v_heads=4,
                        gdn_head_k_dim=32, gdn_head_v_dim=32, kda_gate_rank=16, max_model_len=256)
+    if n in ("tiny-kda-mla",):
+        # the Kimi-Linear layout: KDA layers with every fourth layer latent attention without rotary embeddings
+        return _preset(name="tiny-kda-mla", architecture="kimi_linear", dtype=torch.float32,
+                       num_layers=4, full_attention_interval=4, gdn_num_k_heads=4, gdn_num_v_heads=4,
+                       gdn_head_k_dim=32, gdn_head_v_dim=32, kda_gate_rank=16, max_model_len=256,
+                       kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                       rope_interleaved=True, mla_use_nope=True)
     if n in ("tiny-gdn",):
         return _preset(name="tiny-gdn", architecture="qwen3_next", qk_norm=True, dtype=torch.float32,
                        num_layers=4, full_attention_interval=2, gdn_num_k_heads=2, gdn_num_v_heads=4,

@@ -56,6 +56,8 @@ class MLAAttention:
         self.w_uv = None            # [H, kv_lora, vdim]
         self.o = RowParallelLinear(f"{name}.o_proj", cfg.num_q_heads * self.vdim, cfg.hidden_size, **kw)
         self.inv_freq = ops.ref.rope_inv_freq(self.rope, cfg.rope_theta, cfg.rope_scaling).to(device)
+        if getattr(cfg, "mla_use_nope", False):
+            self.inv_freq = torch.zeros_like(self.inv_freq)       # angle 0 everywhere: the rotation is the identity
         af = ops.ref.rope_attention_factor(cfg.rope_scaling)
         self.scale = qk ** -0.5 * af * af
         if cfg.rope_scaling and "factor" in cfg.rope_scaling:

@@ -118,6 +118,10 @@ class KimiLinearDecoderLayer(Qwen3NextDecoderLayer):
         self.full_attention = cfg.layer_is_full_attention(idx)
         if self.full_attention:
             LlamaDecoderLayer.__init__(self, idx, cfg, device, quant)
+            if cfg.is_mla:
+                # the published layout: latent attention in the full-attention layers (absorbed form, latent cache)
+                from .deepseek_v3 import MLAAttention
+                self.self_attn = MLAAttention(f"model.layers.{idx}.self_attn", cfg, device, quant)
             return
         name = f"model.layers.{idx}"
         self.idx = idx
@@ -130,3 +134,30 @@ class KimiLinearDecoderLayer(Qwen3NextDecoderLayer):
 
 class KimiLinearForCausalLM(Qwen3NextForCausalLM):
     layer_cls = KimiLinearDecoderLayer
+
+    def init_dummy(self) -> None:
+        super().init_dummy()
+        if self.cfg.is_mla:
+            for l in self.layers:
+                if l.full_attention:
+                    l.self_attn.init_dummy(self.cfg.init_std, self.cfg.seed)     # adds the absorbed kv_b matrices
+
+    def weight_bytes(self) -> int:
+        n = super().weight_bytes()
+        if self.cfg.is_mla:
+            for l in self.layers:
+                if l.full_attention:
+                    n += sum(t.numel() * t.element_size() for t in (l.self_attn.w_uk, l.self_attn.w_uv))
+        return n
+
+    def kv_cache_shape(self, num_blocks: int, block_size: int) -> tuple:
+        if self.cfg.is_mla:
+            return (num_blocks, block_size, self.cfg.kv_lora_rank + self.cfg.qk_rope_head_dim)
+        return super().kv_cache_shape(num_blocks, block_size)
+
+    def kv_bytes_per_block(self, block_size: int, kv_dtype: torch.dtype) -> int:
+        if not self.cfg.is_mla:
+            return super().kv_bytes_per_block(block_size, kv_dtype)
+        n_full = sum(1 for l in self.layers if l.full_attention)
+        return n_full * block_size * (self.cfg.kv_lora_rank + self.cfg.qk_rope_head_dim) * \
+            torch.empty((), dtype=kv_dtype).element_size()
