@@ -345,3 +345,35 @@ def test_metrics_histograms_and_vllm_compatible_names(client):
     buckets = [v for k, v in series.items() if k.startswith("b200_e2e_request_latency_seconds_bucket")]
     assert buckets == sorted(buckets)
     assert "# TYPE vllm:num_requests_running gauge" in text and "# TYPE b200_kv_cache_usage gauge" in text
+
+
+def test_metrics_carry_offload_and_transfer_statistics():
+    """A second request with the same prompt is served from the host store: the external prefix-cache counters and
+    the renderer's view of a P2P connector's statistics."""
+    from vllm_torchtpu_b200.entrypoints.metrics import ServingMetrics
+    from vllm_torchtpu_b200.kv_transfer.stats import KVConnectorStats
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=4, block_size=16, init_dist=False,
+              kv_transfer_config={"kv_connector": "B200OffloadingConnector", "kv_role": "kv_both",
+                                  "kv_connector_extra_config": {"num_blocks": 32}})
+    app = build_app(llm.engine, "tiny-llama", None)
+    body = {"prompt": list(range(1, 50)), "max_tokens": 2, "temperature": 0, "ignore_eos": True}
+    with TestClient(app) as c:
+        assert c.post("/v1/completions", json=body).status_code == 200
+        assert c.post("/v1/completions", json=body).status_code == 200
+        text = c.get("/metrics").text
+    app.state.async_engine.shutdown()
+    vals = {l.rsplit(" ", 1)[0]: float(l.rsplit(" ", 1)[1]) for l in text.splitlines() if l and l[0] != "#"}
+    assert vals["b200_external_prefix_cache_hits_total"] >= 32          # two full blocks of the repeated prompt
+    assert vals["b200_external_prefix_cache_queries_total"] >= 49
+    compat = vals['vllm:external_prefix_cache_hits_total{model_name="tiny-llama"}']
+    assert compat == vals["b200_external_prefix_cache_hits_total"]
+    # P2P statistics through the same renderer
+    from types import SimpleNamespace
+    st = KVConnectorStats()
+    st.record_load(4, 0.01, ok=True)
+    st.record_send(3, expired=False)
+    st.record_send(2, expired=True)
+    conn = SimpleNamespace(scheduler=SimpleNamespace(s=SimpleNamespace(stats=st)), worker=SimpleNamespace(s=SimpleNamespace(stats=st)))
+    lines = ServingMetrics._connector_lines(conn, 'model_name="m"')
+    assert 'b200_kv_loads_total{result="ok"} 1' in lines and 'b200_kv_blocks_total{direction="out"} 3' in lines
+    assert 'b200_kv_sends_total{result="expired"} 1' in lines and sum(l.startswith("b200_kv_loads_total") for l in lines) == 2

@@ -138,4 +138,42 @@ class ServingMetrics:
                             out.append(f'{name}{{{labels}{sep}finished_reason="{reason}"}} {n}')
                     else:
                         out.append(f"{name}{{{labels}}} {values[base]}" if labels else f"{name} {values[base]}")
+        out += self._connector_lines(getattr(engine, "connector", None), label)
         return "\n".join(out) + "\n"
+
+    @staticmethod
+    def _connector_lines(connector, label: str) -> list:
+        """KV-transfer and offload statistics of the engine's connector(s), when there is one."""
+        if connector is None:
+            return []
+        halves = []
+        for part in [connector] + list(getattr(connector, "connectors", []) or []):
+            halves += [getattr(part, "scheduler", None), getattr(part, "worker", None)]
+        for side in ("scheduler", "worker"):
+            halves += list(getattr(getattr(connector, side, None), "parts", []) or [])     # multi connector
+        out, seen = [], set()
+        for h in halves:
+            st = getattr(h, "stats", None)
+            if st is None:
+                st = getattr(getattr(h, "s", None), "stats", None)      # state shared by the two P2P halves
+            if st is None or id(st) in seen:
+                continue
+            seen.add(id(st))
+            if isinstance(st, dict) and "external_hits" in st:
+                for base, key in (("external_prefix_cache_queries_total", "external_queries"),
+                                  ("external_prefix_cache_hits_total", "external_hits")):
+                    out += [f"# TYPE b200_{base} counter", f"b200_{base} {st[key]}",
+                            f"# TYPE vllm:{base} counter", f"vllm:{base}{{{label}}} {st[key]}"]
+            elif hasattr(st, "snapshot"):
+                s = st.snapshot()
+                out += ["# TYPE b200_kv_loads_total counter",
+                        f'b200_kv_loads_total{{result="ok"}} {s["loads_ok"]}',
+                        f'b200_kv_loads_total{{result="failed"}} {s["loads_failed"]}',
+                        "# TYPE b200_kv_blocks_total counter",
+                        f'b200_kv_blocks_total{{direction="in"}} {s["blocks_loaded"]}',
+                        f'b200_kv_blocks_total{{direction="out"}} {s["blocks_sent"]}',
+                        "# TYPE b200_kv_sends_total counter",
+                        f'b200_kv_sends_total{{result="pulled"}} {s["sends_pulled"]}',
+                        f'b200_kv_sends_total{{result="expired"}} {s["sends_expired"]}',
+                        "# TYPE b200_kv_load_seconds_p50 gauge", f'b200_kv_load_seconds_p50 {s["load_p50_s"]:.6f}']
+        return out

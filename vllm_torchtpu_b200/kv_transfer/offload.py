@@ -117,6 +117,8 @@ class OffloadSchedulerHalf(SchedulerConnectorBase):
         self.store, self.bs = store, block_size
         self._loads, self._saves = [], []
         self._pending_load: dict = {}
+        # prompt tokens looked up in / served from the host store (admitted requests only)
+        self.stats = {"external_queries": 0, "external_hits": 0}
 
     def request_not_admitted(self, request) -> None:
         """The scheduler asked for matches but could not admit the request in this step: give the
@@ -140,6 +142,8 @@ class OffloadSchedulerHalf(SchedulerConnectorBase):
 
     def update_state_after_alloc(self, request, block_ids, num_external):
         have, slots = self._pending_load.pop(request.request_id)
+        self.stats["external_queries"] += request.num_prompt_tokens
+        self.stats["external_hits"] += len(slots) * self.bs
         self._loads.append((request.request_id, slots, list(block_ids)[have:have + len(slots)]))
 
     def request_finished(self, request, block_ids):
