@@ -142,7 +142,7 @@ class OffloadSchedulerHalf(SchedulerConnectorBase):
 
     def update_state_after_alloc(self, request, block_ids, num_external):
         have, slots = self._pending_load.pop(request.request_id)
-        self.stats["external_queries"] += request.num_prompt_tokens
+        self.stats["external_queries"] += getattr(request, "num_prompt_tokens", request.num_tokens)
         self.stats["external_hits"] += len(slots) * self.bs
         self._loads.append((request.request_id, slots, list(block_ids)[have:have + len(slots)]))
 
