@@ -210,3 +210,20 @@ def test_server_n_stop_and_penalties():
         assert c.post("/v1/completions", json=dict(body, presence_penalty=9)).status_code == 400
         assert c.post("/v1/completions", json=dict(body, stop=[""])).status_code == 400
     app.state.async_engine.shutdown()
+
+
+def test_llm_chat_renders_conversations_through_the_template():
+    llm = _llm()
+    sp = SamplingParams(max_tokens=4, ignore_eos=True)
+    conv = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hello"}]
+    one = llm.chat(conv, sp)
+    assert len(one) == 1 and len(one[0].outputs[0].token_ids) == 4
+    # the plain transcript of a tokenizer without a template: "role: content" lines + an open assistant turn
+    want = llm.tokenizer.encode("system: be brief\nuser: hello\nassistant:")
+    assert one[0].prompt_token_ids == want
+    two = llm.chat([conv, conv + [{"role": "assistant", "content": "hi"}, {"role": "user", "content": "more"}]], sp)
+    assert len(two) == 2 and two[0].outputs[0].token_ids == one[0].outputs[0].token_ids
+    cont = llm.chat(conv + [{"role": "assistant", "content": "abc"}], sp, continue_final_message=True)
+    assert cont[0].prompt_token_ids == llm.tokenizer.encode("system: be brief\nuser: hello\nassistant: abc")
+    with pytest.raises(ValueError):
+        llm.chat(conv, sp, continue_final_message=True)

@@ -103,6 +103,21 @@ class LLM:
             return list(prompt["prompt_token_ids"])
         return list(prompt)
 
+    def chat(self, messages, sampling_params: Union[SamplingParams, Sequence, None] = None, *,
+             add_generation_prompt: bool = True, continue_final_message: bool = False,
+             chat_template_kwargs: Optional[dict] = None, tools: Optional[list] = None) -> list:
+        """One conversation (a list of {role, content} messages) or a list of conversations -> ``RequestOutput``
+        objects, through the tokenizer's chat template (``tools`` are handed to the template)."""
+        from ..entrypoints.chat_template import build_chat_prompt
+        convs = messages if messages and isinstance(messages[0], list) else [messages]
+        kw = dict(chat_template_kwargs or {})
+        if tools:
+            kw.setdefault("tools", tools)
+        prompts = [build_chat_prompt(self.tokenizer, self._encode, list(c), add_generation_prompt=add_generation_prompt,
+                                     continue_final_message=continue_final_message, chat_template_kwargs=kw or None)
+                   for c in convs]
+        return self.generate(prompts, sampling_params)
+
     def embed(self, prompts: Sequence, pooling: str = "last", normalize: bool = True) -> list:
         """Pooled final hidden state per prompt (``last`` token or ``mean`` over the prompt), optionally
         L2-normalised: the embedding-model path (reference: src/vllm_torchtpu/runner/tpu_pooling.py)."""

@@ -95,7 +95,8 @@ def plan(a, parser) -> dict:
     cache_root = a.export_cache or os.path.join(os.path.expanduser("~"), ".cache", "vllm_torchtpu_b200", "exports")
     exp, srv = split_args(a, parser)
     out = artifact_dir(a, exp, cache_root)
-    world = a.tensor_parallel_size * a.pipeline_parallel_size * a.data_parallel_size
+    world = a.tensor_parallel_size * a.pipeline_parallel_size * a.data_parallel_size * \
+        a.prefill_context_parallel_size
     return {"artifact": out, "world_size": world,
             "export": _wrap(world, ["export", a.model, "--output", out] + exp),
             "serve": _wrap(world, ["serve", out] + srv)}
