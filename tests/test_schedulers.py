@@ -214,3 +214,25 @@ def test_scheduler_randomised_run_keeps_the_block_pool_consistent(seed, caching,
     assert s.stats["preemptions"] > 0                 # the pool is small enough to force recomputation
     done_or_aborted = {rid for rid, r in submitted.items() if r.status.finished}
     assert done_or_aborted == set(submitted)
+
+
+def test_priority_scheduler_admits_by_priority_and_preempts_the_least_important():
+    """One request fits the batch at a time: the order of completion follows (priority, arrival), whatever the
+    order of submission; the default scheduler keeps arrival order."""
+    from vllm_torchtpu_b200.engine.llm import LLM
+    from vllm_torchtpu_b200.sampling_params import SamplingParams
+    sp = SamplingParams(max_tokens=3, ignore_eos=True)
+    prompts = [[1, 2, 3], [4, 5, 6], [7, 8, 9], [10, 11, 12]]
+    prios = [5, 1, 3, 1]
+    order = {}
+    for cls in ("priority", "default"):
+        llm = LLM("tiny-llama", device="cpu", max_num_seqs=1, block_size=16, init_dist=False, scheduler_cls=cls)
+        ids = [llm.engine.add_request(p, sp, priority=pr) for p, pr in zip(prompts, prios)]
+        done = []
+        while llm.engine.has_unfinished():
+            done += [r.request_id for r in llm.engine.step()]
+        order[cls] = [ids.index(r) for r in done]
+    assert order["priority"] == [1, 3, 2, 0] and order["default"] == [0, 1, 2, 3]
+    llm = LLM("tiny-llama", device="cpu", max_num_seqs=1, block_size=16, init_dist=False, scheduler_cls="priority")
+    outs = llm.generate(prompts, sp, priority=prios)
+    assert [len(o.outputs[0].token_ids) for o in outs] == [3, 3, 3, 3]

@@ -135,7 +135,7 @@ class LLM:
         return vecs
 
     def generate(self, prompts: Sequence, sampling_params: Union[SamplingParams, Sequence, None] = None,
-                 ) -> list:
+                 priority: Optional[Sequence] = None) -> list:
         """One ``RequestOutput`` per prompt, in input order, with ``sampling_params.n`` completions each.
         Stop strings are matched on the detokenised text while the requests run; a request that produced one
         is ended there and its text is cut in front of the string."""
@@ -145,13 +145,14 @@ class LLM:
         sps = sampling_params if isinstance(sampling_params, (list, tuple)) else \
             [sampling_params or SamplingParams()] * len(prompts)
         groups, watch = [], {}
-        for p, sp in zip(prompts, sps):
+        prios = list(priority) if priority is not None else [0] * len(prompts)
+        for k, (p, sp) in enumerate(zip(prompts, sps)):
             sp = sp or SamplingParams()
             sp.verify()
             if sp.stop and self.tokenizer is None:
                 raise ValueError("stop strings need a tokenizer")
             ids = self._encode(p)
-            group = [self.engine.add_request(ids, sp) for _ in range(sp.n)]
+            group = [self.engine.add_request(ids, sp, priority=prios[k]) for _ in range(sp.n)]
             groups.append((group, sp))
             if sp.stop:
                 for rid in group:

@@ -192,7 +192,7 @@ class LLMEngine:
     # ---- requests ---------------------------------------------------------------
     def add_request(self, prompt_token_ids: list, sampling_params: Optional[SamplingParams] = None,
                     request_id: Optional[str] = None, kv_transfer_params: Optional[dict] = None,
-                    mm_items: Optional[list] = None) -> str:
+                    mm_items: Optional[list] = None, priority: int = 0) -> str:
         """``mm_items``: [(patches [num_patches, patch_dim], prompt_offset), ...] — images or video chunks
         whose embeddings replace the placeholder tokens starting at ``prompt_offset`` (needs
         ``enable_vision`` first)."""
@@ -214,7 +214,8 @@ class LLMEngine:
         rid = request_id or f"req-{self._next_id}"
         self._next_id += 1
         if self._queue_op(("add", (list(prompt_token_ids), sp), dict(request_id=rid, mm_items=mm_items,
-                                                                      kv_transfer_params=kv_transfer_params))):
+                                                                      kv_transfer_params=kv_transfer_params,
+                                                                      priority=priority))):
             return rid          # applied on every rank, this one included, at the next step
         if sp.structured:
             if self.runner.structured is None:
@@ -234,7 +235,7 @@ class LLMEngine:
                     self.runner.mm_manager.remove_request(rid)
                     raise ValueError("a multimodal item's placeholder range runs past the prompt")
         self.scheduler.add_request(Request(rid, list(prompt_token_ids), sp, self.eos_token_id,
-                                           kv_transfer_params=kv_transfer_params))
+                                           kv_transfer_params=kv_transfer_params, priority=int(priority)))
         return rid
 
     def enable_vision(self, vision_cfg, max_patches_per_batch: int = 8192):

@@ -63,9 +63,10 @@ class AsyncEngine:
                 while True:
                     kind, payload = self._inbox.get_nowait()
                     if kind == "add":
-                        rid, toks, sp, kvp, mm = payload
+                        rid, toks, sp, kvp, mm, prio = payload
                         try:
-                            eng.add_request(toks, sp, request_id=rid, kv_transfer_params=kvp, mm_items=mm)
+                            eng.add_request(toks, sp, request_id=rid, kv_transfer_params=kvp, mm_items=mm,
+                                            priority=prio)
                         except Exception as e:       # noqa: BLE001 - reported to the caller
                             self._emit(StreamItem(rid, [], True, "error", error=str(e)))
                     elif kind == "abort":
@@ -131,13 +132,13 @@ class AsyncEngine:
 
     async def generate(self, request_id: str, prompt_token_ids: list, sp: SamplingParams,
                        kv_transfer_params: Optional[dict] = None,
-                       mm_items: Optional[list] = None) -> AsyncIterator[StreamItem]:
+                       mm_items: Optional[list] = None, priority: int = 0) -> AsyncIterator[StreamItem]:
         self._loop = asyncio.get_running_loop()
         q: asyncio.Queue = asyncio.Queue()
         self._streams[request_id] = q
         self.metrics["requests"] += 1
         self.metrics["prompt_tokens"] += len(prompt_token_ids)
-        self._inbox.put(("add", (request_id, list(prompt_token_ids), sp, kv_transfer_params, mm_items)))
+        self._inbox.put(("add", (request_id, list(prompt_token_ids), sp, kv_transfer_params, mm_items, int(priority))))
         try:
             while True:
                 item = await q.get()

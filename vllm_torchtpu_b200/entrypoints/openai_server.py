@@ -193,7 +193,8 @@ def build_app(engine, model_name: str, tokenizer=None):
             ended).  With stop strings the text lags the tokens by what could still become a stop string."""
             from .stop_strings import StopStringMatcher
             m = StopStringMatcher(sp.stop, sp.include_stop_str_in_output) if sp.stop else None
-            gen = aeng.generate(rid if n == 1 else f"{rid}-{i}", prompt_ids, sp, kvp, mm)
+            gen = aeng.generate(rid if n == 1 else f"{rid}-{i}", prompt_ids, sp, kvp, mm,
+                                priority=int(body.get("priority") or 0))
             toks = []
             try:
                 async for item in gen:

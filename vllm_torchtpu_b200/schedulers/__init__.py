@@ -20,4 +20,7 @@ def get_scheduler_class(name: str):
     if name == "srpt":
         from .srpt import SrptPrefillScheduler
         return SrptPrefillScheduler
+    if name == "priority":
+        from .priority import PriorityScheduler
+        return PriorityScheduler
     raise ValueError(f"unknown scheduler {name!r}")
